@@ -1,0 +1,2 @@
+"""inferloop_b200: a small, whole inference engine for one GPU (sm_100a)."""
+__version__ = "0.1.0"

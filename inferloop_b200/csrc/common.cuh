@@ -1,0 +1,84 @@
+// Shared helpers for the sm_100a kernels of this package.
+//
+// Every launcher is an `extern "C"` function that takes raw device pointers, sizes and
+// the stream to launch on, validates its arguments, and returns 0 or a negative code
+// after recording a message that `ilb_last_error()` of the same library returns.
+// Nothing here allocates device memory: callers own every buffer.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+
+namespace ilb {
+
+static thread_local char g_error[512] = "";
+
+static inline int fail(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return -1;
+}
+
+static inline int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail("%s: launch failed: %s", what, cudaGetErrorString(e));
+  return 0;
+}
+
+#define ILB_REQUIRE(cond, ...)            \
+  do {                                    \
+    if (!(cond)) return ilb::fail(__VA_ARGS__); \
+  } while (0)
+
+// Element type codes shared with the Python side.
+enum DType : int { kF32 = 0, kBF16 = 1 };
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a thread block of up to 1024 threads; every thread gets the result.
+// `scratch` must hold 33 floats of shared memory.  The order of additions is fixed
+// by the block size alone.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    const int nwarps = (blockDim.x + 31) >> 5;
+    float t = lane < nwarps ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+}  // namespace ilb
+
+#define ILB_EXPORT extern "C" __attribute__((visibility("default")))
+
+// One copy per library.
+#define ILB_DEFINE_LAST_ERROR() \
+  ILB_EXPORT const char* ilb_last_error() { return ilb::g_error; }

@@ -1,0 +1,177 @@
+// Row-wise and element-wise kernels: embedding gather, RMSNorm, SwiGLU product,
+// row gather and the rotation table.  All arithmetic is in 32-bit (the rotation
+// angle in 64-bit); bfloat16 appears only as a storage type of inputs or outputs.
+//
+// Formulas (reference, by path within its project):
+//   RMSNorm  x / sqrt(mean(x^2) + eps) * w   crates/testing/cpu/reference-ops/src/kernels.rs:38-54
+//   SiLU     x * sigmoid(x), two-branch sigmoid  kernels.rs:12-22
+//   RoPE     angle_i = pos / theta^(2i/rd)       kernels.rs:217-241
+#include "common.cuh"
+
+using namespace ilb;
+
+// ---------------------------------------------------------------- embedding gather
+template <typename TT>
+__global__ void embed_kernel(const int* __restrict__ tokens, const TT* __restrict__ table,
+                             float* __restrict__ out, int hidden, int vocab) {
+  const int t = blockIdx.x;
+  const int tok = tokens[t];
+  const bool ok = tok >= 0 && tok < vocab;
+  const TT* row = table + (size_t)(ok ? tok : 0) * hidden;
+  float* o = out + (size_t)t * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = ok ? to_float(row[i]) : 0.f;
+}
+
+ILB_EXPORT int ilb_embed(const int* tokens, const void* table, int table_dtype, float* out,
+                         int n_tokens, int hidden, int vocab, cudaStream_t stream) {
+  ILB_REQUIRE(n_tokens >= 0 && hidden > 0 && vocab > 0, "embed: bad sizes T=%d H=%d V=%d",
+              n_tokens, hidden, vocab);
+  if (n_tokens == 0) return 0;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (table_dtype == kF32)
+    embed_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, out, hidden, vocab);
+  else if (table_dtype == kBF16)
+    embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, out, hidden, vocab);
+  else
+    return fail("embed: unknown table dtype %d", table_dtype);
+  return check_launch("embed");
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// One block per row.  The block size depends on the width alone, so the order of the
+// additions for a row never depends on how many rows the launch holds.
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                               TO* __restrict__ out, int width, float eps) {
+  __shared__ float scratch[33];
+  const float* row = x + (size_t)blockIdx.x * width;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = row[i];
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+  TO* o = out + (size_t)blockIdx.x * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    o[i] = from_float<TO>(row[i] * inv * w[i]);
+}
+
+static inline int norm_threads(int width) {
+  if (width >= 2048) return 256;
+  if (width >= 512) return 128;
+  if (width >= 128) return 64;
+  return 32;
+}
+
+ILB_EXPORT int ilb_rmsnorm(const float* x, const float* w, void* out, int out_dtype, int rows,
+                           int width, float eps, cudaStream_t stream) {
+  ILB_REQUIRE(rows >= 0 && width > 0, "rmsnorm: bad sizes rows=%d width=%d", rows, width);
+  ILB_REQUIRE(eps > 0.f, "rmsnorm: eps must be positive");
+  if (rows == 0) return 0;
+  const int threads = norm_threads(width);
+  if (out_dtype == kF32)
+    rmsnorm_kernel<float><<<rows, threads, 0, stream>>>(x, w, (float*)out, width, eps);
+  else if (out_dtype == kBF16)
+    rmsnorm_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>(x, w, (__nv_bfloat16*)out, width, eps);
+  else
+    return fail("rmsnorm: unknown output dtype %d", out_dtype);
+  return check_launch("rmsnorm");
+}
+
+// ---------------------------------------------------------------- SwiGLU product
+__device__ __forceinline__ float sigmoid_stable(float x) {
+  if (x >= 0.f) return 1.0f / (1.0f + expf(-x));
+  const float e = expf(x);
+  return e / (1.0f + e);
+}
+
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate, const T* __restrict__ up,
+                                T* __restrict__ out, int rows, int width, int in_stride) {
+  const size_t n = (size_t)rows * width;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / width), c = (int)(i % width);
+    const float g = to_float(gate[(size_t)r * in_stride + c]);
+    const float u = to_float(up[(size_t)r * in_stride + c]);
+    out[i] = from_float<T>(g * sigmoid_stable(g) * u);
+  }
+}
+
+// gate = in[:, 0:width], up = in[:, width:2*width] of a [rows, in_stride] matrix.
+ILB_EXPORT int ilb_silu_mul(const void* in, void* out, int dtype, int rows, int width,
+                            int in_stride, cudaStream_t stream) {
+  ILB_REQUIRE(rows >= 0 && width > 0 && in_stride >= 2 * width, "silu_mul: bad sizes");
+  if (rows == 0) return 0;
+  const size_t n = (size_t)rows * width;
+  const int threads = 256;
+  const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
+  if (dtype == kF32)
+    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)in, (const float*)in + width, (float*)out, rows, width, in_stride);
+  else if (dtype == kBF16)
+    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)in, (const __nv_bfloat16*)in + width, (__nv_bfloat16*)out, rows, width, in_stride);
+  else
+    return fail("silu_mul: unknown dtype %d", dtype);
+  return check_launch("silu_mul");
+}
+
+// ---------------------------------------------------------------- row gather
+__global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ idx,
+                                   float* __restrict__ out, int width, int n_rows_in) {
+  const int r = idx[blockIdx.x];
+  const bool ok = r >= 0 && r < n_rows_in;
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    out[(size_t)blockIdx.x * width + i] = ok ? x[(size_t)r * width + i] : 0.f;
+}
+
+ILB_EXPORT int ilb_gather_rows(const float* x, const int* idx, float* out, int n_out, int width,
+                               int n_rows_in, cudaStream_t stream) {
+  ILB_REQUIRE(n_out >= 0 && width > 0, "gather_rows: bad sizes");
+  if (n_out == 0) return 0;
+  gather_rows_kernel<<<n_out, 256, 0, stream>>>(x, idx, out, width, n_rows_in);
+  return check_launch("gather_rows");
+}
+
+// ---------------------------------------------------------------- rotation table
+// cos/sin of pos * inv_freq[i], angle and functions evaluated in 64-bit and rounded once
+// to 32-bit, so the table is as good as a 32-bit number can be at any position.
+__global__ void rope_table_kernel(const int* __restrict__ positions,
+                                  const double* __restrict__ inv_freq,
+                                  float2* __restrict__ table, int n_tokens, int half) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_tokens * half) return;
+  const int t = i / half, f = i % half;
+  const double angle = (double)positions[t] * inv_freq[f];
+  double s, c;
+  sincos(angle, &s, &c);
+  table[i] = make_float2((float)c, (float)s);
+}
+
+ILB_EXPORT int ilb_rope_table(const int* positions, const double* inv_freq, float* table,
+                              int n_tokens, int half, cudaStream_t stream) {
+  ILB_REQUIRE(n_tokens >= 0 && half > 0, "rope_table: bad sizes");
+  if (n_tokens == 0) return 0;
+  const int n = n_tokens * half;
+  rope_table_kernel<<<(n + 127) / 128, 128, 0, stream>>>(positions, inv_freq, (float2*)table, n_tokens, half);
+  return check_launch("rope_table");
+}
+
+// ---------------------------------------------------------------- x += y (32-bit)
+__global__ void add_inplace_kernel(float* __restrict__ x, const float* __restrict__ y, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    x[i] += y[i];
+}
+
+ILB_EXPORT int ilb_add_inplace(float* x, const float* y, long long n, cudaStream_t stream) {
+  ILB_REQUIRE(n >= 0, "add_inplace: bad size");
+  if (n == 0) return 0;
+  const int threads = 256;
+  long long blocks = (n + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  add_inplace_kernel<<<(int)blocks, threads, 0, stream>>>(x, y, (size_t)n);
+  return check_launch("add_inplace");
+}
+
+ILB_DEFINE_LAST_ERROR()

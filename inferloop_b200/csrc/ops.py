@@ -1,0 +1,224 @@
+"""Python face of the CUDA kernels: thin, checked ctypes calls on torch tensors.
+
+Every function launches on torch's current stream of the tensors' device and returns
+without synchronising.  There is no CPU path: a tensor that is not on a CUDA device, or
+a library that cannot be built or loaded, raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import load_module
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported element type {t.dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream(t: torch.Tensor) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _need(t: Optional[torch.Tensor], what: str, dtype: Optional[torch.dtype] = None,
+          contiguous: bool = True) -> None:
+    if t is None:
+        return
+    if not t.is_cuda:
+        raise KernelError(f"{what}: tensor is on {t.device}; inferloop_b200 kernels run on CUDA only")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{what}: tensor must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{what}: expected {dtype}, found {t.dtype}")
+
+
+def _call(module: str, fn: str, *args) -> None:
+    lib = load_module(module)
+    f = getattr(lib, fn)
+    f.restype = ctypes.c_int
+    rc = f(*args)
+    if rc != 0:
+        raise KernelError(lib.ilb_last_error().decode())
+
+
+def _i(v) -> ctypes.c_int:
+    return ctypes.c_int(int(v))
+
+
+def _f(v) -> ctypes.c_float:
+    return ctypes.c_float(float(v))
+
+
+# --------------------------------------------------------------------------- rows
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, :] = table[tokens[t], :] widened to 32-bit."""
+    _need(tokens, "embed tokens", torch.int32); _need(table, "embed table"); _need(out, "embed out", torch.float32)
+    T, H = out.shape
+    if tokens.numel() != T or table.shape[1] != H:
+        raise KernelError("embed: shapes do not agree")
+    _call("elementwise", "ilb_embed", _ptr(tokens), _ptr(table), _i(_code(table)), _ptr(out),
+          _i(T), _i(H), _i(table.shape[0]), _stream(out))
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out = x / sqrt(mean(x^2) + eps) * weight over the last dimension; x is 32-bit."""
+    _need(x, "rmsnorm x", torch.float32); _need(weight, "rmsnorm weight", torch.float32); _need(out, "rmsnorm out")
+    width = x.shape[-1]
+    if weight.numel() != width or out.shape != x.shape:
+        raise KernelError("rmsnorm: shapes do not agree")
+    rows = x.numel() // width
+    _call("elementwise", "ilb_rmsnorm", _ptr(x), _ptr(weight), _ptr(out), _i(_code(out)),
+          _i(rows), _i(width), _f(eps), _stream(x))
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(gate_up[:, :I]) * gate_up[:, I:2I]."""
+    _need(gate_up, "silu_mul in"); _need(out, "silu_mul out", gate_up.dtype)
+    rows, width = out.shape
+    if gate_up.shape[0] != rows or gate_up.shape[1] != 2 * width:
+        raise KernelError("silu_mul: shapes do not agree")
+    _call("elementwise", "ilb_silu_mul", _ptr(gate_up), _ptr(out), _i(_code(out)), _i(rows),
+          _i(width), _i(gate_up.shape[1]), _stream(out))
+
+
+def gather_rows(x: torch.Tensor, index: torch.Tensor, out: torch.Tensor) -> None:
+    _need(x, "gather x", torch.float32); _need(index, "gather index", torch.int32); _need(out, "gather out", torch.float32)
+    if out.shape[0] != index.numel() or out.shape[1] != x.shape[1]:
+        raise KernelError("gather_rows: shapes do not agree")
+    _call("elementwise", "ilb_gather_rows", _ptr(x), _ptr(index), _ptr(out), _i(out.shape[0]),
+          _i(x.shape[1]), _i(x.shape[0]), _stream(x))
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = (cos, sin)(positions[t] * inv_freq[i]); inv_freq is 64-bit."""
+    _need(positions, "rope positions", torch.int32); _need(inv_freq, "rope inv_freq", torch.float64)
+    _need(out, "rope table", torch.float32)
+    T, half = positions.numel(), inv_freq.numel()
+    if tuple(out.shape) != (T, half, 2):
+        raise KernelError("rope_table: out must be [T, rotary_dim/2, 2]")
+    _call("elementwise", "ilb_rope_table", _ptr(positions), _ptr(inv_freq), _ptr(out), _i(T),
+          _i(half), _stream(out))
+
+
+def add_inplace(x: torch.Tensor, y: torch.Tensor) -> None:
+    _need(x, "add x", torch.float32); _need(y, "add y", torch.float32)
+    if x.numel() != y.numel():
+        raise KernelError("add_inplace: sizes differ")
+    _call("elementwise", "ilb_add_inplace", _ptr(x), _ptr(y), ctypes.c_longlong(x.numel()), _stream(x))
+
+
+# --------------------------------------------------------------------------- GEMM
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
+              bias: Optional[torch.Tensor] = None, accumulate: bool = False) -> None:
+    """out (+)= a @ w.T (+ bias) with 32-bit fused multiply-adds in a fixed order."""
+    _need(a, "gemm a"); _need(w, "gemm w", a.dtype); _need(out, "gemm out")
+    _need(bias, "gemm bias", torch.float32)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N) or (bias is not None and bias.numel() != N):
+        raise KernelError(f"gemm: shapes do not agree: a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if accumulate and out.dtype != torch.float32:
+        raise KernelError("gemm: accumulation needs a 32-bit output")
+    _call("gemm_simt", "ilb_gemm_simt", _ptr(a), _ptr(w), _ptr(bias), _ptr(out), _i(_code(a)),
+          _i(_code(out)), _i(M), _i(N), _i(K), _i(K), _i(K), _i(N), _i(1 if accumulate else 0),
+          _stream(out))
+
+
+# --------------------------------------------------------------------------- attention
+def qk_norm_rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.Tensor],
+                       k_weight: Optional[torch.Tensor], eps: float,
+                       rope: Optional[torch.Tensor], rotary_dim: int, positions: torch.Tensor,
+                       seq_of_token: torch.Tensor, block_table: Optional[torch.Tensor],
+                       page_size: int, k_cache: Optional[torch.Tensor],
+                       v_cache: Optional[torch.Tensor], nq: int, nkv: int, d: int) -> None:
+    """Per-head q/k RMSNorm, rotation, q -> q_out, k/v -> cache pages (see qk_norm_rope.cu)."""
+    _need(qkv, "qkv"); _need(q_out, "q_out", qkv.dtype)
+    _need(q_weight, "q_norm weight", torch.float32); _need(k_weight, "k_norm weight", torch.float32)
+    _need(rope, "rope table", torch.float32); _need(positions, "positions", torch.int32)
+    _need(seq_of_token, "seq_of_token", torch.int32); _need(block_table, "block table", torch.int32)
+    _need(k_cache, "k cache"); _need(v_cache, "v cache")
+    T = qkv.shape[0]
+    if k_cache is not None:
+        if tuple(k_cache.shape[1:]) != (nkv, page_size, d) or v_cache.shape != k_cache.shape:
+            raise KernelError(f"cache shape {tuple(k_cache.shape)} is not [pages, {nkv}, {page_size}, {d}]")
+        if block_table is None:
+            raise KernelError("a cache write needs a block table")
+    max_blocks = 0 if block_table is None else block_table.shape[1]
+    num_pages = 0 if k_cache is None else k_cache.shape[0]
+    cache_code = _code(k_cache) if k_cache is not None else _code(qkv)
+    _call("qk_norm_rope", "ilb_qk_norm_rope_cache", _ptr(qkv), _ptr(q_out), _i(_code(qkv)),
+          _ptr(q_weight), _ptr(k_weight), _f(eps), _ptr(rope), _i(rotary_dim), _ptr(positions),
+          _ptr(seq_of_token), _ptr(block_table), _i(max_blocks), _i(page_size), _i(num_pages),
+          _ptr(k_cache), _ptr(v_cache), _i(cache_code), _i(T), _i(nq), _i(nkv), _i(d),
+          _i(qkv.shape[1]), _i(q_out.shape[1]), _stream(qkv))
+
+
+def paged_attention_simple(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
+                           v_cache: torch.Tensor, positions: torch.Tensor,
+                           seq_of_token: torch.Tensor, block_table: torch.Tensor, window: int,
+                           scale: float, nq: int, nkv: int, d: int) -> None:
+    _need(q, "attention q"); _need(out, "attention out", q.dtype)
+    _need(k_cache, "k cache"); _need(v_cache, "v cache", k_cache.dtype)
+    _need(positions, "positions", torch.int32); _need(seq_of_token, "seq_of_token", torch.int32)
+    _need(block_table, "block table", torch.int32)
+    num_pages, nkv_c, page_size, d_c = k_cache.shape
+    if (nkv_c, d_c) != (nkv, d):
+        raise KernelError("attention: cache shape does not match the heads")
+    _call("attention_simple", "ilb_paged_attention_simple", _ptr(q), _ptr(out), _i(_code(q)),
+          _ptr(k_cache), _ptr(v_cache), _i(_code(k_cache)), _ptr(positions), _ptr(seq_of_token),
+          _ptr(block_table), _i(block_table.shape[1]), _i(page_size), _i(num_pages),
+          _i(window or 0), _f(scale), _i(q.shape[0]), _i(nq), _i(nkv), _i(d), _i(q.shape[1]),
+          _i(out.shape[1]), _stream(q))
+
+
+# --------------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor, out: torch.Tensor, bad: Optional[torch.Tensor] = None) -> None:
+    _need(logits, "argmax logits", torch.float32); _need(out, "argmax out", torch.int32)
+    _need(bad, "argmax flags", torch.int32)
+    rows, vocab = logits.shape
+    _call("sampling", "ilb_argmax", _ptr(logits), _ptr(out), _ptr(bad), _i(rows), _i(vocab),
+          _i(logits.stride(0)), _stream(logits))
+
+
+def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
+                       out: torch.Tensor, bad: Optional[torch.Tensor] = None) -> None:
+    _need(logits, "sample logits", torch.float32); _need(temperature, "temperature", torch.float32)
+    _need(uniform, "uniform", torch.float64); _need(out, "sample out", torch.int32)
+    _need(bad, "sample flags", torch.int32)
+    rows, vocab = logits.shape
+    _call("sampling", "ilb_sample_temperature", _ptr(logits), _ptr(temperature), _ptr(uniform),
+          _ptr(out), _ptr(bad), _i(rows), _i(vocab), _i(logits.stride(0)), _stream(logits))
+
+
+# --------------------------------------------------------------------------- tensor-core GEMM
+def gemm_tc_eligible(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    return False
+
+
+def gemm_tc(a, w, out, bias=None, accumulate=False) -> None:
+    raise KernelError("tensor-core GEMM is not built")
+
+
+# --------------------------------------------------------------------------- attention dispatch
+def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+              step, block_table: torch.Tensor, window: int, scale: float, nq: int, nkv: int,
+              d: int) -> None:
+    """Causal attention of the step's tokens over the cache; picks the kernel."""
+    paged_attention_simple(q, out, k_cache, v_cache, step.positions, step.seq_of_token,
+                           block_table, window, scale, nq, nkv, d)

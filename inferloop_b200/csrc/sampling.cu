@@ -1,0 +1,193 @@
+// Token selection on the device.
+//
+// argmax: highest logit of a row, the lowest index among equals; a row that holds a value
+// that is not finite is flagged (the reference treats it as an error:
+// crates/engine/workloads/src/sampling.rs:175-192; two-stage device arg-max:
+// crates/backend/cuda-kernels/src/tile/sampling/greedy_kernels.rs:17-100).
+//
+// sample_temperature: one draw from softmax(logits / T) by the reference's rule
+// (sampling.rs:146-168, :210-226): candidates are walked from the highest logit down
+// (lower index first among equals) and the first one whose cumulative normalised weight
+// exceeds the uniform number u is taken.  No sort is made: the logit at which the
+// cumulative weight crosses u is found by bisection on the ordered bit pattern of the
+// 32-bit values (33 passes over the row), then ties at that value are walked by index.
+// Weights and sums are 64-bit, as in the reference; only the ORDER of the additions
+// differs, which can move the crossing point by rounding of the sums alone.
+#include <math.h>
+#include "common.cuh"
+
+using namespace ilb;
+
+constexpr int kThreads = 1024;
+
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
+  return v > bv || (v == bv && i < bi);
+}
+
+__global__ void __launch_bounds__(kThreads)
+argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int* __restrict__ bad,
+              int vocab, int stride) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  __shared__ int sbad;
+  const float* row = logits + (size_t)blockIdx.x * stride;
+  if (threadIdx.x == 0) sbad = 0;
+  __syncthreads();
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  bool nonfinite = false;
+  for (int i = threadIdx.x; i < vocab; i += kThreads) {
+    const float v = row[i];
+    if (!isfinite(v)) nonfinite = true;
+    if (better(v, i, bv, bi)) { bv = v; bi = i; }
+  }
+  if (nonfinite) sbad = 1;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    bv = sv[lane]; bi = si[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) {
+      out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+      if (bad != nullptr) bad[blockIdx.x] = sbad;
+    }
+  }
+}
+
+ILB_EXPORT int ilb_argmax(const float* logits, int* out, int* bad, int rows, int vocab, int stride,
+                          cudaStream_t stream) {
+  ILB_REQUIRE(rows >= 0 && vocab > 0 && stride >= vocab, "argmax: bad sizes");
+  if (rows == 0) return 0;
+  argmax_kernel<<<rows, kThreads, 0, stream>>>(logits, out, bad, vocab, stride);
+  return check_launch("argmax");
+}
+
+// Map a float to an unsigned key whose order is the order of the floats.
+__device__ __forceinline__ unsigned ordered_key(float v) {
+  const unsigned u = __float_as_uint(v);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ __forceinline__ double block_sum_f64(double v, double* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    double t = scratch[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+__global__ void __launch_bounds__(kThreads)
+sample_temperature_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+                          const double* __restrict__ uniform, int* __restrict__ out,
+                          int* __restrict__ bad, int vocab, int stride) {
+  __shared__ double scratch[33];
+  __shared__ float smax[33];
+  __shared__ int sflag;
+  const float* row = logits + (size_t)blockIdx.x * stride;
+  const double inv_t = 1.0 / (double)temperature[blockIdx.x];
+  const double u = uniform[blockIdx.x];
+  if (threadIdx.x == 0) sflag = 0;
+  __syncthreads();
+  // pass 0: maximum and finiteness
+  float mx = -INFINITY;
+  bool nonfinite = false;
+  for (int i = threadIdx.x; i < vocab; i += kThreads) {
+    const float v = row[i];
+    if (!isfinite(v)) nonfinite = true;
+    mx = fmaxf(mx, v);
+  }
+  if (nonfinite) sflag = 1;
+  mx = warp_max(mx);
+  if ((threadIdx.x & 31) == 0) smax[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = smax[threadIdx.x];
+    t = warp_max(t);
+    if (threadIdx.x == 0) smax[32] = t;
+  }
+  __syncthreads();
+  mx = smax[32];
+  if (sflag) {
+    if (threadIdx.x == 0) { out[blockIdx.x] = 0; if (bad) bad[blockIdx.x] = 1; }
+    return;
+  }
+  // pass 1: total weight
+  double part = 0.0;
+  for (int i = threadIdx.x; i < vocab; i += kThreads)
+    part += exp(((double)row[i] - (double)mx) * inv_t);
+  const double total = block_sum_f64(part, scratch);
+  const double target = u * total;
+  // Bisection: the largest key K such that the weight of all logits with key > K is
+  // <= target; the crossing happens among the logits whose key equals the answer.
+  unsigned lo = 0u, hi = ordered_key(mx);      // invariant: mass(> hi) = 0 <= target
+  // mass(> key) is non-increasing in key.  Find the smallest key with mass(> key) <= target.
+  while (lo < hi) {
+    const unsigned mid = lo + ((hi - lo) >> 1);
+    double above = 0.0;
+    for (int i = threadIdx.x; i < vocab; i += kThreads) {
+      const float v = row[i];
+      if (ordered_key(v) > mid) above += exp(((double)v - (double)mx) * inv_t);
+    }
+    above = block_sum_f64(above, scratch);
+    if (above <= target) hi = mid; else lo = mid + 1;
+  }
+  // Weight strictly above the crossing value, then walk its equals in index order.
+  double above = 0.0;
+  for (int i = threadIdx.x; i < vocab; i += kThreads) {
+    const float v = row[i];
+    if (ordered_key(v) > hi) above += exp(((double)v - (double)mx) * inv_t);
+  }
+  above = block_sum_f64(above, scratch);
+  if (threadIdx.x == 0) {
+    int chosen = -1, last = -1;
+    double cumulative = above;
+    for (int i = 0; i < vocab; ++i) {
+      const float v = row[i];
+      if (ordered_key(v) != hi) continue;
+      last = i;
+      cumulative += exp(((double)v - (double)mx) * inv_t);
+      if (target < cumulative) { chosen = i; break; }
+    }
+    if (chosen < 0) chosen = last;   // rounding left the crossing past the last equal
+    if (chosen < 0) {                // u at the very end: the last candidate of the walk
+      float best = INFINITY; int bi = 0;
+      for (int i = 0; i < vocab; ++i) if (row[i] <= best) { best = row[i]; bi = i; }
+      chosen = bi;
+    }
+    out[blockIdx.x] = chosen;
+    if (bad) bad[blockIdx.x] = 0;
+  }
+}
+
+ILB_EXPORT int ilb_sample_temperature(const float* logits, const float* temperature,
+                                      const double* uniform, int* out, int* bad, int rows,
+                                      int vocab, int stride, cudaStream_t stream) {
+  ILB_REQUIRE(rows >= 0 && vocab > 0 && stride >= vocab, "sample_temperature: bad sizes");
+  if (rows == 0) return 0;
+  sample_temperature_kernel<<<rows, kThreads, 0, stream>>>(logits, temperature, uniform, out, bad,
+                                                           vocab, stride);
+  return check_launch("sample_temperature");
+}
+
+ILB_DEFINE_LAST_ERROR()

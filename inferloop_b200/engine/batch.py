@@ -1,0 +1,100 @@
+"""The batch of one step, as the kernels see it.
+
+A step is a list of entries (request, its next tokens, the places whose logits are
+wanted).  The reference's task is either a prompt span or one decode token
+(crates/foundation/ir/src/execution.rs:85-93); here both are simply "the next tokens of
+a request", of any length, so a step may hold portions of prompts beside single decoded
+tokens, cut anywhere.  All tokens are laid side by side, each request's tokens
+contiguous and in order (which a mixer with sequential state relies on), with per-token
+position and sequence index and per-sequence offsets, lengths, slots and block tables.
+All of it travels to the device as ONE int32 buffer.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+
+@dataclass
+class StepEntry:
+    request: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()      # indices into `tokens` whose logits are wanted
+
+
+@dataclass
+class StepContext:
+    n_tokens: int
+    n_seqs: int
+    n_logit_rows: int
+    # device int32 tensors
+    tokens: torch.Tensor           # [T]
+    positions: torch.Tensor        # [T] absolute position of each token
+    seq_of_token: torch.Tensor     # [T] index of the token's sequence in this batch
+    cu_q: torch.Tensor             # [S + 1] offsets of each sequence's tokens
+    kv_len: torch.Tensor           # [S] tokens in the cache after this step
+    slots: torch.Tensor            # [S] state slot of each sequence
+    logit_rows: torch.Tensor       # [R] token rows whose logits are wanted
+    block_tables: Dict[int, torch.Tensor]   # group -> [S, max_blocks]
+    # host copies, for planning launches and for parts written in Python
+    requests: List[Hashable] = field(default_factory=list)
+    h_q_start: List[int] = field(default_factory=list)     # first position of each sequence's tokens
+    h_q_len: List[int] = field(default_factory=list)
+    h_kv_len: List[int] = field(default_factory=list)
+    h_slots: List[int] = field(default_factory=list)
+    max_q_len: int = 0
+    max_kv_len: int = 0
+    decode_only: bool = False
+    position_tables: Dict[object, torch.Tensor] = field(default_factory=dict)
+
+
+class StepStager:
+    """Packs a step's integer arrays into pinned host memory and copies them to the
+    device with one transfer.  Two staging buffers alternate, each guarded by an event,
+    so packing step n+1 never overwrites memory that step n's copy still reads."""
+
+    def __init__(self, device: torch.device, capacity: int = 1 << 16) -> None:
+        self.device = device
+        self._cap = 0
+        self._host: List[torch.Tensor] = []
+        self._events: List[Optional[torch.cuda.Event]] = [None, None]
+        self._dev: Optional[torch.Tensor] = None
+        self._turn = 0
+        self._grow(capacity)
+
+    def _grow(self, capacity: int) -> None:
+        self._cap = int(capacity)
+        self._host = [torch.empty(self._cap, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._events = [None, None]
+        self._dev = torch.empty(self._cap, dtype=torch.int32, device=self.device)
+
+    def stage(self, arrays: Sequence[np.ndarray]) -> List[torch.Tensor]:
+        """Copy the int32 arrays to the device; returns one device view per array.
+        Each array starts on a 16-byte boundary."""
+        offsets, total = [], 0
+        for a in arrays:
+            offsets.append(total)
+            total += (a.size + 3) // 4 * 4
+        if total > self._cap:
+            torch.cuda.current_stream(self.device).synchronize()
+            self._grow(max(total, 2 * self._cap))
+        i = self._turn
+        self._turn ^= 1
+        if self._events[i] is not None:
+            self._events[i].synchronize()
+        host = self._host[i]
+        hv = host.numpy()
+        for a, off in zip(arrays, offsets):
+            hv[off:off + a.size] = a.reshape(-1)
+        self._dev[:total].copy_(host[:total], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        self._events[i] = ev
+        return [self._dev[off:off + a.size].view(*a.shape) for a, off in zip(arrays, offsets)]
+
+    @property
+    def bytes_last(self) -> int:
+        return self._cap * 4

@@ -1,0 +1,216 @@
+"""The step function: run a batch of (request, its next tokens) from the cache.
+
+`ModelRunner.step(entries)` runs only the tokens it is given, as one batch, and returns
+the 32-bit logits at the wanted places.  It is the single path from tokens to logits:
+trace replay, the scheduler and the Python entry point all call it.  The reference's
+counterpart is `BackendProvider::submit/poll` over a list of `ExecutionTask`s
+(crates/foundation/spi/src/backend.rs:340-345, :403); there a task continues the
+backend's own history cursor (crates/foundation/ir/src/tokens.rs:171-180), here the
+cursor is the cache manager's committed length of the request.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Callable, Dict, Hashable, List, Mapping, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.pages import OutOfPages
+from ..config.registry import read_model_config
+from ..config.spec import ModelSpec
+from ..models.decoder import DecoderModel
+from ..parts.base import BuildContext, Workspace
+from ..weights.loader import load_weights
+from ..weights.random_init import random_weights
+from .batch import StepContext, StepEntry, StepStager
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+          "f32": torch.float32, "fp32": torch.float32}
+
+
+def parse_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"dtype {name} is not served; use bfloat16 or float32")
+        return name
+    try:
+        return DTYPES[str(name).lower()]
+    except KeyError:
+        raise ValueError(f"unknown dtype {name!r}; use bfloat16 or float32") from None
+
+
+def require_cuda(device) -> torch.device:
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        raise RuntimeError(f"inferloop_b200 runs on a CUDA device only, not on {dev}")
+    if not torch.cuda.is_available():
+        raise RuntimeError("inferloop_b200 needs a CUDA device (sm_100a) and found none; "
+                           "there is no CPU path")
+    return dev
+
+
+class ModelRunner:
+    def __init__(self, spec: ModelSpec, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype,
+                 device: torch.device, page_size: int, num_pages: int, max_requests: int) -> None:
+        self.spec = spec
+        self.dtype = dtype
+        self.device = device
+        self.ctx = BuildContext(dtype=dtype, device=device, workspace=Workspace(device))
+        self.model = DecoderModel(spec, self.ctx)
+        self.model.bind(tensors)
+        self.cache = CacheManager(self.model.cache_needs(), page_size, num_pages, max_requests,
+                                  dtype=dtype, device=device, run_order=spec.run_order)
+        self.stager = StepStager(device)
+        self.steps_run = 0
+        self.tokens_run = 0
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_folder(cls, folder: str, dtype="bfloat16", device="cuda:0", page_size: int = 16,
+                    num_pages: int = 256, max_requests: int = 64, registry=None,
+                    allow_unexpected: bool = False,
+                    progress: Optional[Callable[[str], None]] = None) -> "ModelRunner":
+        dev = require_cuda(device)
+        dt = parse_dtype(dtype)
+        path = os.path.join(folder, "config.json")
+        if not os.path.exists(path):
+            raise FileNotFoundError(f"{folder}: no config.json")
+        with open(path, "r", encoding="utf-8") as fh:
+            text = fh.read(1 << 20)     # bounded read (storage/source.rs:265-313)
+        _, _, spec = read_model_config(text, registry)
+        decls = DecoderModel(spec, BuildContext(dt, None, Workspace(None))).declare_weights()
+        tensors, _ = load_weights(folder, decls, spec.weight_prefixes, spec.embedding_name, dt, dev,
+                                  allow_unexpected=allow_unexpected, progress=progress)
+        return cls(spec, tensors, dt, dev, page_size, num_pages, max_requests)
+
+    @classmethod
+    def from_config(cls, config: Mapping, seed: int, dtype="bfloat16", device="cuda:0",
+                    page_size: int = 16, num_pages: int = 256, max_requests: int = 64,
+                    registry=None) -> "ModelRunner":
+        """Random weights made on the device (no folder is written)."""
+        dev = require_cuda(device)
+        dt = parse_dtype(dtype)
+        _, _, spec = read_model_config(json.dumps(dict(config)), registry)
+        decls = DecoderModel(spec, BuildContext(dt, None, Workspace(None))).declare_weights()
+        tensors = random_weights(decls, seed, dt, dev)
+        return cls(spec, tensors, dt, dev, page_size, num_pages, max_requests)
+
+    # ------------------------------------------------------------------ requests
+    def begin(self, request: Hashable) -> None:
+        self.cache.begin(request)
+
+    def end(self, request: Hashable) -> None:
+        self.cache.release(request)
+
+    def is_live(self, request: Hashable) -> bool:
+        return self.cache.has(request)
+
+    def can_run(self, entries: Sequence[StepEntry]) -> bool:
+        """Whether every group has the pages this step would take."""
+        need: Dict[int, int] = {}
+        for e in entries:
+            cur = self.cache.length(e.request) if self.cache.has(e.request) else 0
+            if self.cache.has(e.request):
+                per = self.cache.pages_needed(e.request, cur + len(e.tokens))
+            else:
+                per = {g.index: -(-len(e.tokens) // self.cache.page_size) for g in self.cache.groups}
+            for g, n in per.items():
+                need[g] = need.get(g, 0) + n
+        free = self.cache.free_pages()
+        return all(need.get(g, 0) <= free[g] for g in free)
+
+    # ------------------------------------------------------------------ the step
+    def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Take pages for the step (all entries or none) and stage its arrays."""
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        seen = set()
+        for e in entries:
+            if e.request in seen:
+                raise ValueError(f"request {e.request!r} appears twice in one step")
+            seen.add(e.request)
+            if len(e.tokens) == 0:
+                raise ValueError(f"request {e.request!r} brings no tokens")
+            for w in e.want:
+                if not (0 <= w < len(e.tokens)):
+                    raise ValueError(f"request {e.request!r}: wanted place {w} is outside its {len(e.tokens)} tokens")
+            for t in e.tokens:
+                if not (0 <= int(t) < self.spec.vocab_size):
+                    raise ValueError(f"request {e.request!r}: token {t} is outside the vocabulary of {self.spec.vocab_size}")
+        fresh = [e.request for e in entries if not self.cache.has(e.request)]
+        for r in fresh:
+            self.cache.begin(r)
+        try:
+            if not self.can_run(entries):
+                raise OutOfPages(f"step of {sum(len(e.tokens) for e in entries)} tokens does not fit: "
+                                 f"free pages {self.cache.free_pages()}")
+            for e in entries:
+                new_len = self.cache.length(e.request) + len(e.tokens)
+                if new_len > self.spec.max_positions:
+                    raise ValueError(f"request {e.request!r} would reach {new_len} tokens; the model's "
+                                     f"limit is {self.spec.max_positions}")
+            for e in entries:
+                self.cache.ensure(e.request, self.cache.length(e.request) + len(e.tokens))
+        except Exception:
+            for r in fresh:
+                self.cache.release(r)
+            raise
+
+        S = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        tokens = np.empty(T, np.int32)
+        positions = np.empty(T, np.int32)
+        seq_of = np.empty(T, np.int32)
+        cu_q = np.zeros(S + 1, np.int32)
+        kv_len = np.empty(S, np.int32)
+        slots = np.empty(S, np.int32)
+        rows: List[int] = []
+        q_start, q_len = [], []
+        off = 0
+        for s, e in enumerate(entries):
+            n = len(e.tokens)
+            cur = self.cache.length(e.request)
+            tokens[off:off + n] = np.asarray(e.tokens, dtype=np.int64)
+            positions[off:off + n] = np.arange(cur, cur + n, dtype=np.int32)
+            seq_of[off:off + n] = s
+            cu_q[s + 1] = off + n
+            kv_len[s] = cur + n
+            slots[s] = self.cache.slot_of(e.request)
+            rows.extend(off + int(w) for w in e.want)
+            q_start.append(cur)
+            q_len.append(n)
+            off += n
+        reqs = [e.request for e in entries]
+        max_blocks = (self.cache.max_blocks(reqs) + 7) // 8 * 8
+        tables = []
+        for g in self.cache.groups:
+            tb = np.full((S, max_blocks), -1, np.int32)
+            for s, r in enumerate(reqs):
+                row = self.cache.block_table(g.index, r)
+                tb[s, :len(row)] = row
+            tables.append(tb)
+        logit_rows = np.asarray(rows, dtype=np.int32)
+        staged = self.stager.stage([tokens, positions, seq_of, cu_q, kv_len, slots, logit_rows] + tables)
+        return StepContext(
+            n_tokens=T, n_seqs=S, n_logit_rows=len(rows),
+            tokens=staged[0], positions=staged[1], seq_of_token=staged[2], cu_q=staged[3],
+            kv_len=staged[4], slots=staged[5], logit_rows=staged[6],
+            block_tables={g.index: staged[7 + i] for i, g in enumerate(self.cache.groups)},
+            requests=reqs, h_q_start=q_start, h_q_len=q_len, h_kv_len=[int(x) for x in kv_len],
+            h_slots=[int(x) for x in slots], max_q_len=max(q_len), max_kv_len=int(kv_len.max()),
+            decode_only=all(n == 1 for n in q_len))
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run the entries as one batch; returns logits [wanted, vocab] (32-bit, on the
+        device, in the order of the entries and of each entry's `want`).  The tensor is a
+        scratch buffer: it is valid until the next step."""
+        ctx = self.prepare(entries)
+        logits = self.model.forward(ctx, self.cache)
+        for e in entries:
+            self.cache.commit(e.request, self.cache.length(e.request) + len(e.tokens))
+        self.steps_run += 1
+        self.tokens_run += ctx.n_tokens
+        return logits

@@ -1,0 +1,102 @@
+"""A decoder assembled from a :class:`ModelSpec`: token table, the blocks in their run
+order, final norm and output matrix.  It runs whatever the spec lists; the only thing it
+knows is the order embedding -> layers -> selected rows -> norm -> logits, which is the
+reference's lowering too (crates/model/recipes/src/decoder.rs:93-154).  Logits are
+computed only for the rows that are asked for, as the reference copies only the rows it
+reads before its output matrix
+(crates/backend/cuda-kernels/src/tile/projection/prompt_logits_kernels.rs:15-49).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Mapping, Optional
+
+import torch
+
+from ..config.spec import ModelSpec
+from ..csrc import ops
+from ..parts import registry
+from ..parts.base import BuildContext, CacheNeeds, Workspace
+from ..parts.linear import linear
+from ..weights.decl import WeightDecl
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, ctx: BuildContext) -> None:
+        self.spec = spec
+        self.ctx = ctx
+        self.blocks = [registry.build_block(layer, ctx, layer.prefix) for layer in spec.layers]
+        self.final_norm = registry.build_norm(
+            spec.final_norm, ctx, _strip_weight(spec.final_norm_name), width=spec.hidden_size)
+        self.embedding: Optional[torch.Tensor] = None
+        self.head: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------ weights
+    def declare_weights(self) -> List[WeightDecl]:
+        s = self.spec
+        out = [WeightDecl(s.embedding_name, (s.vocab_size, s.hidden_size), role="table")]
+        for b in self.blocks:
+            out += b.declare_weights()
+        out += self.final_norm.declare_weights()
+        if s.head_name is not None:
+            out.append(WeightDecl(s.head_name, (s.vocab_size, s.hidden_size), root=True))
+        names = [d.name for d in out]
+        if len(set(names)) != len(names):
+            dup = sorted({n for n in names if names.count(n) > 1})
+            raise ValueError(f"tensor names declared twice: {dup}")
+        return out
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        s = self.spec
+        self.embedding = tensors[s.embedding_name].contiguous()
+        for b in self.blocks:
+            b.bind(tensors)
+        self.final_norm.bind(tensors)
+        self.head = self.embedding if s.head_name is None else tensors[s.head_name].contiguous()
+
+    def cache_needs(self) -> List[CacheNeeds]:
+        return [b.cache_needs() for b in self.blocks]
+
+    def weight_bytes(self) -> int:
+        """Bytes of every weight one step reads once (the table is read by row only)."""
+        seen, total = set(), 0
+        for b in self.blocks:
+            for part in (b,) + tuple(getattr(b, n) for n in ("norm1", "mixer", "norm2", "ffn") if hasattr(b, n)):
+                for v in vars(part).values():
+                    if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
+                        seen.add(v.data_ptr())
+                        total += v.numel() * v.element_size()
+        if self.head is not None:
+            total += self.head.numel() * self.head.element_size()
+        return total
+
+    # ------------------------------------------------------------------ run
+    def forward(self, step, caches) -> torch.Tensor:
+        """Run the step's tokens through every run-order entry; returns 32-bit logits
+        [len(step.logit_rows), vocab] (a workspace buffer, valid until the next step)."""
+        s, ws = self.spec, self.ctx.workspace
+        T = step.n_tokens
+        hidden = ws.buffer("model.hidden", (T, s.hidden_size), torch.float32)
+        ops.embed(step.tokens, self.embedding, hidden)
+        for entry in s.run_order:
+            self.blocks[entry.layer].forward(hidden, step, caches.layer_cache(entry))
+        R = step.n_logit_rows
+        if R == 0:
+            return ws.buffer("model.logits", (0, s.vocab_size), torch.float32)
+        rows = ws.buffer("model.rows", (R, s.hidden_size), torch.float32)
+        ops.gather_rows(hidden, step.logit_rows, rows)
+        normed = ws.buffer("model.rows_normed", (R, s.hidden_size), self.ctx.dtype)
+        self.final_norm.forward(rows, normed)
+        logits = ws.buffer("model.logits", (R, s.vocab_size), torch.float32)
+        linear(normed, self.head, logits)
+        return logits
+
+
+def _strip_weight(name: str) -> str:
+    """"norm.weight" -> "norm." (the norm part appends its own tensor name)."""
+    return name[: -len("weight")] if name.endswith("weight") else name
+
+
+def declare_weights(spec: ModelSpec) -> List[WeightDecl]:
+    """The tensors a spec needs, without touching a device."""
+    ctx = BuildContext(dtype=torch.float32, device=None, workspace=Workspace(None))
+    return DecoderModel(spec, ctx).declare_weights()
