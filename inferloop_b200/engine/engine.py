@@ -1,0 +1,214 @@
+"""The Python entry point: `Engine(model, ...)`, `submit`, `step`, `generate`.
+
+The reference has no Python in its serving path; its programming surface is the Rust
+`Engine::{new, submit, tick, poll_completed, take_completed}`
+(crates/engine/runtime/src/engine/mod.rs:118-159) driven by the `infer run` loop
+`while !engine.is_idle() { engine.tick(now) }`
+(crates/service/cli/src/support/execution.rs:16-46).  This class keeps those verbs and
+the option names of its command line (crates/service/cli/src/arguments.rs:17-93):
+block_size, num_gpu_blocks_override, max_num_batched_tokens, max_model_len,
+max_output_tokens, max_num_seqs, gpu_memory_utilization, device.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Dict, Hashable, List, Mapping, Optional, Sequence, Union
+
+import torch
+
+from ..sampling import host as host_sampler
+from ..sampling.device import DeviceSampler
+from ..sampling.params import SamplingParams
+from .batch import StepEntry
+from .runner import ModelRunner, parse_dtype, require_cuda
+from .scheduler import CapacityError, Request, Scheduler, SchedulerConfig, StepPlan
+
+DEFAULT_BLOCK_SIZE = 16            # crates/engine/runtime/src/config.rs:19
+DEFAULT_GPU_MEMORY_UTILIZATION = 0.9
+
+
+@dataclass
+class TokenOutput:
+    request: Hashable
+    token: int
+    index: int                  # index among the request's generated tokens
+    finished: bool
+    finish_reason: Optional[str] = None
+
+
+class Engine:
+    def __init__(self, model: Union[str, Mapping], dtype="bfloat16", device: Union[int, str] = 0,
+                 block_size: int = DEFAULT_BLOCK_SIZE, num_gpu_blocks_override: Optional[int] = None,
+                 max_num_batched_tokens: Optional[int] = None, max_model_len: Optional[int] = None,
+                 max_output_tokens: Optional[int] = None, max_num_seqs: int = 64,
+                 gpu_memory_utilization: float = DEFAULT_GPU_MEMORY_UTILIZATION,
+                 prefill_chunk_tokens: int = 512, random_weights_seed: Optional[int] = None,
+                 cuda_graphs: bool = True, runner=None) -> None:
+        """`model`: a folder with config.json and safetensors, or a config mapping
+        together with `random_weights_seed` (weights are then made on the device)."""
+        self.block_size = int(block_size)
+        self.max_output_tokens = max_output_tokens
+        if runner is not None:
+            self.runner = runner
+        else:
+            dev = require_cuda(f"cuda:{device}" if isinstance(device, int) else device)
+            dt = parse_dtype(dtype)
+            pages = num_gpu_blocks_override
+            first_pages = pages if pages is not None else 1
+            if isinstance(model, (str, os.PathLike)):
+                self.runner = ModelRunner.from_folder(
+                    str(model), dtype=dt, device=dev, page_size=self.block_size,
+                    num_pages=first_pages, max_requests=max(max_num_seqs, 1))
+            else:
+                if random_weights_seed is None:
+                    raise ValueError("a config mapping needs random_weights_seed")
+                self.runner = ModelRunner.from_config(
+                    model, random_weights_seed, dtype=dt, device=dev, page_size=self.block_size,
+                    num_pages=first_pages, max_requests=max(max_num_seqs, 1))
+            if pages is None:
+                self.runner.resize_cache(self._pages_from_memory(dev, gpu_memory_utilization, max_num_seqs,
+                                                                 max_model_len), max(max_num_seqs, 1))
+        spec_len = self.runner.spec.max_positions
+        self.max_model_len = min(int(max_model_len), spec_len) if max_model_len else spec_len
+        cfg = SchedulerConfig(
+            max_num_seqs=max_num_seqs,
+            max_num_batched_tokens=max_num_batched_tokens or max(prefill_chunk_tokens + max_num_seqs - 1, 1),
+            prefill_chunk_tokens=prefill_chunk_tokens, max_model_len=self.max_model_len)
+        self.scheduler = Scheduler(self.runner.cache, cfg)
+        self.sampler = DeviceSampler(self.runner.device) if getattr(self.runner, "device", None) is not None else None
+        self.cuda_graphs = cuda_graphs
+        self._next_id = 0
+        self.requests: Dict[Hashable, Request] = {}
+
+    # ------------------------------------------------------------------ sizing
+    def _pages_from_memory(self, dev, utilization: float, max_num_seqs: int,
+                           max_model_len: Optional[int]) -> int:
+        """budget = min(total * utilization - used, free - 1 GiB)
+        (crates/service/cli/src/backend/cuda.rs:52-64), less room for activations."""
+        free, total = torch.cuda.mem_get_info(dev)
+        used = total - free
+        budget = min(total * utilization - used, free - (1 << 30))
+        budget -= 4 << 30          # activations and logits of the largest step
+        per_page = sum(g.page_bytes(torch.empty((), dtype=self.runner.cache.dtype).element_size())
+                       for g in self.runner.cache.groups)
+        if per_page == 0:
+            return 1
+        pages = int(max(budget, 0) // per_page)
+        want = (max_model_len or self.runner.spec.max_positions)
+        cap = -(-want // self.block_size) * max(max_num_seqs, 1)   # no request set can use more
+        pages = min(pages, cap)
+        if pages < 1:
+            raise CapacityError("no device memory is left for the cache")
+        return pages
+
+    # ------------------------------------------------------------------ requests
+    def submit(self, tokens: Sequence[int], sampling: Optional[SamplingParams] = None,
+               max_new_tokens: int = 16, request_id: Optional[Hashable] = None) -> Hashable:
+        params = sampling or SamplingParams()
+        if request_id is None:
+            while self._next_id in self.requests:
+                self._next_id += 1
+            request_id = self._next_id
+            self._next_id += 1
+        elif request_id in self.requests and self.requests[request_id].status != "finished":
+            raise ValueError(f"duplicate request id {request_id!r}")
+        vocab = self.runner.spec.vocab_size
+        toks = [int(t) for t in tokens]
+        for t in toks:
+            if not (0 <= t < vocab):
+                raise ValueError(f"token {t} is outside the vocabulary of {vocab}")
+        if self.max_output_tokens is not None:
+            max_new_tokens = min(max_new_tokens, int(self.max_output_tokens))
+        req = Request(request_id, toks, params, int(max_new_tokens))
+        self.scheduler.add(req)
+        self.requests[request_id] = req
+        return request_id
+
+    def is_idle(self) -> bool:
+        return not self.scheduler.has_work()
+
+    # ------------------------------------------------------------------ one step
+    def step(self) -> List[TokenOutput]:
+        """Plan one step, run it, draw the tokens it yields; returns them."""
+        plan = self.scheduler.plan()
+        if not plan.work:
+            return []
+        entries = [StepEntry(w.request.id, w.tokens, [w.count - 1] if w.samples else []) for w in plan.work]
+        logits = self.runner.step(entries)
+        sampling_work = [w for w in plan.work if w.samples]
+        sampled = self._sample(logits, sampling_work)
+        finished = {r.id for r in self.scheduler.complete(plan, sampled)}
+        out = []
+        for w in sampling_work:
+            r = w.request
+            out.append(TokenOutput(r.id, sampled[r.id], len(r.generated) - 1, r.id in finished,
+                                   r.finish_reason if r.id in finished else None))
+        return out
+
+    def _sample(self, logits: torch.Tensor, work) -> Dict[Hashable, int]:
+        """Row i of `logits` belongs to work[i].  Plain greedy and plain temperature rows
+        are drawn on the device; rows with filters or penalties are read back and drawn by
+        the host sampler.  The draw's position is the index of the token being generated
+        (crates/engine/runtime/src/pipeline/completion/cpu.rs:104)."""
+        if not work:
+            return {}
+        rows = len(work)
+        out: Dict[Hashable, int] = {}
+        kinds = ["greedy" if w.request.params.uses_plain_greedy()
+                 else "temperature" if w.request.params.uses_plain_temperature() else "host" for w in work]
+        if self.sampler is None:
+            kinds = ["host"] * rows
+        if "greedy" in kinds:
+            self.sampler.greedy_launch(logits)
+            ids = self.sampler.read(rows)
+            for w, k, t in zip(work, kinds, ids):
+                if k == "greedy":
+                    out[w.request.id] = t
+        if "temperature" in kinds:
+            temps = [w.request.params.temperature if k == "temperature" else 1.0 for w, k in zip(work, kinds)]
+            us = [host_sampler.uniform(w.request.params.seed, host_sampler.request_key(w.request.id),
+                                       len(w.request.generated)) for w in work]
+            self.sampler.temperature_launch(logits, temps, us)
+            ids = self.sampler.read(rows)
+            for w, k, t in zip(work, kinds, ids):
+                if k == "temperature":
+                    out[w.request.id] = t
+        if "host" in kinds:
+            idx = [i for i, k in enumerate(kinds) if k == "host"]
+            host = logits[idx].float().cpu().numpy() if hasattr(logits, "cpu") else logits[idx]
+            for j, i in enumerate(idx):
+                r = work[i].request
+                out[r.id] = host_sampler.sample(
+                    host[j], r.params, host_sampler.request_key(r.id), len(r.generated),
+                    prompt=r.prompt, generated=r.generated)
+        return out
+
+    # ------------------------------------------------------------------ whole jobs
+    def generate(self, prompts: Sequence[Sequence[int]], sampling: Union[SamplingParams, Sequence[SamplingParams], None] = None,
+                 max_new_tokens: Union[int, Sequence[int]] = 16) -> List[List[int]]:
+        """Generate for every prompt (token ids in, token ids out); returns the generated
+        tokens in the order of the prompts."""
+        n = len(prompts)
+        params = list(sampling) if isinstance(sampling, (list, tuple)) else [sampling] * n
+        limits = list(max_new_tokens) if isinstance(max_new_tokens, (list, tuple)) else [max_new_tokens] * n
+        ids = [self.submit(p, s, m) for p, s, m in zip(prompts, params, limits)]
+        while not self.is_idle():
+            self.step()
+        return [list(self.requests[i].generated) for i in ids]
+
+    def result(self, request_id: Hashable) -> Request:
+        return self.requests[request_id]
+
+    def inspect(self) -> dict:
+        """Counterpart of the reference's RuntimeInspection
+        (crates/engine/runtime/src/engine/mod.rs:49-90)."""
+        s = self.scheduler
+        return {
+            "waiting": len(s.waiting), "running": len(s.running), "finished": len(s.finished),
+            "steps": getattr(self.runner, "steps_run", 0), "tokens": getattr(self.runner, "tokens_run", 0),
+            "scheduler": dict(s.stats), "cache": self.runner.cache.inspect(),
+            "max_model_len": self.max_model_len,
+            "max_num_seqs": s.config.max_num_seqs,
+            "max_num_batched_tokens": s.config.max_num_batched_tokens,
+        }

@@ -52,6 +52,105 @@ def require_cuda(device) -> torch.device:
     return dev
 
 
+def step_fits(cache: CacheManager, entries: Sequence[StepEntry]) -> bool:
+    """Whether every group has the pages this step would take."""
+    need: Dict[int, int] = {}
+    for e in entries:
+        cur = cache.length(e.request) if cache.has(e.request) else 0
+        if cache.has(e.request):
+            per = cache.pages_needed(e.request, cur + len(e.tokens))
+        else:
+            per = {g.index: -(-len(e.tokens) // cache.page_size) for g in cache.groups}
+        for g, n in per.items():
+            need[g] = need.get(g, 0) + n
+    free = cache.free_pages()
+    return all(need.get(g, 0) <= free[g] for g in free)
+
+
+
+def prepare_step(cache: CacheManager, stager: StepStager, entries: Sequence[StepEntry],
+                 vocab_size: int, max_positions: int) -> StepContext:
+    """Take pages for the step (all entries or none) and stage its arrays."""
+    if not entries:
+        raise ValueError("a step needs at least one entry")
+    seen = set()
+    for e in entries:
+        if e.request in seen:
+            raise ValueError(f"request {e.request!r} appears twice in one step")
+        seen.add(e.request)
+        if len(e.tokens) == 0:
+            raise ValueError(f"request {e.request!r} brings no tokens")
+        for w in e.want:
+            if not (0 <= w < len(e.tokens)):
+                raise ValueError(f"request {e.request!r}: wanted place {w} is outside its {len(e.tokens)} tokens")
+        for t in e.tokens:
+            if not (0 <= int(t) < vocab_size):
+                raise ValueError(f"request {e.request!r}: token {t} is outside the vocabulary of {vocab_size}")
+    fresh = [e.request for e in entries if not cache.has(e.request)]
+    for r in fresh:
+        cache.begin(r)
+    try:
+        if not step_fits(cache, entries):
+            raise OutOfPages(f"step of {sum(len(e.tokens) for e in entries)} tokens does not fit: "
+                             f"free pages {cache.free_pages()}")
+        for e in entries:
+            new_len = cache.length(e.request) + len(e.tokens)
+            if new_len > max_positions:
+                raise ValueError(f"request {e.request!r} would reach {new_len} tokens; the model's "
+                                 f"limit is {max_positions}")
+        for e in entries:
+            cache.ensure(e.request, cache.length(e.request) + len(e.tokens))
+    except Exception:
+        for r in fresh:
+            cache.release(r)
+        raise
+
+    S = len(entries)
+    T = sum(len(e.tokens) for e in entries)
+    tokens = np.empty(T, np.int32)
+    positions = np.empty(T, np.int32)
+    seq_of = np.empty(T, np.int32)
+    cu_q = np.zeros(S + 1, np.int32)
+    kv_len = np.empty(S, np.int32)
+    slots = np.empty(S, np.int32)
+    rows: List[int] = []
+    q_start, q_len = [], []
+    off = 0
+    for s, e in enumerate(entries):
+        n = len(e.tokens)
+        cur = cache.length(e.request)
+        tokens[off:off + n] = np.asarray(e.tokens, dtype=np.int64)
+        positions[off:off + n] = np.arange(cur, cur + n, dtype=np.int32)
+        seq_of[off:off + n] = s
+        cu_q[s + 1] = off + n
+        kv_len[s] = cur + n
+        slots[s] = cache.slot_of(e.request)
+        rows.extend(off + int(w) for w in e.want)
+        q_start.append(cur)
+        q_len.append(n)
+        off += n
+    reqs = [e.request for e in entries]
+    max_blocks = (cache.max_blocks(reqs) + 7) // 8 * 8
+    tables = []
+    for g in cache.groups:
+        tb = np.full((S, max_blocks), -1, np.int32)
+        for s, r in enumerate(reqs):
+            row = cache.block_table(g.index, r)
+            tb[s, :len(row)] = row
+        tables.append(tb)
+    logit_rows = np.asarray(rows, dtype=np.int32)
+    staged = stager.stage([tokens, positions, seq_of, cu_q, kv_len, slots, logit_rows] + tables)
+    return StepContext(
+        n_tokens=T, n_seqs=S, n_logit_rows=len(rows),
+        tokens=staged[0], positions=staged[1], seq_of_token=staged[2], cu_q=staged[3],
+        kv_len=staged[4], slots=staged[5], logit_rows=staged[6],
+        block_tables={g.index: staged[7 + i] for i, g in enumerate(cache.groups)},
+        requests=reqs, h_q_start=q_start, h_q_len=q_len, h_kv_len=[int(x) for x in kv_len],
+        h_slots=[int(x) for x in slots], max_q_len=max(q_len), max_kv_len=int(kv_len.max()),
+        decode_only=all(n == 1 for n in q_len))
+
+
+
 class ModelRunner:
     def __init__(self, spec: ModelSpec, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype,
                  device: torch.device, page_size: int, num_pages: int, max_requests: int) -> None:
@@ -98,6 +197,16 @@ class ModelRunner:
         tensors = random_weights(decls, seed, dt, dev)
         return cls(spec, tensors, dt, dev, page_size, num_pages, max_requests)
 
+    def resize_cache(self, num_pages: int, max_requests: int) -> None:
+        """Replace the cache by one of another size; only while no request is live."""
+        if self.cache.live_requests():
+            raise RuntimeError("the cache cannot be resized while requests are live")
+        page_size = self.cache.page_size
+        self.cache = None
+        torch.cuda.empty_cache()
+        self.cache = CacheManager(self.model.cache_needs(), page_size, num_pages, max_requests,
+                                  dtype=self.dtype, device=self.device, run_order=self.spec.run_order)
+
     # ------------------------------------------------------------------ requests
     def begin(self, request: Hashable) -> None:
         self.cache.begin(request)
@@ -110,98 +219,12 @@ class ModelRunner:
 
     def can_run(self, entries: Sequence[StepEntry]) -> bool:
         """Whether every group has the pages this step would take."""
-        need: Dict[int, int] = {}
-        for e in entries:
-            cur = self.cache.length(e.request) if self.cache.has(e.request) else 0
-            if self.cache.has(e.request):
-                per = self.cache.pages_needed(e.request, cur + len(e.tokens))
-            else:
-                per = {g.index: -(-len(e.tokens) // self.cache.page_size) for g in self.cache.groups}
-            for g, n in per.items():
-                need[g] = need.get(g, 0) + n
-        free = self.cache.free_pages()
-        return all(need.get(g, 0) <= free[g] for g in free)
+        return step_fits(self.cache, entries)
 
     # ------------------------------------------------------------------ the step
     def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
         """Take pages for the step (all entries or none) and stage its arrays."""
-        if not entries:
-            raise ValueError("a step needs at least one entry")
-        seen = set()
-        for e in entries:
-            if e.request in seen:
-                raise ValueError(f"request {e.request!r} appears twice in one step")
-            seen.add(e.request)
-            if len(e.tokens) == 0:
-                raise ValueError(f"request {e.request!r} brings no tokens")
-            for w in e.want:
-                if not (0 <= w < len(e.tokens)):
-                    raise ValueError(f"request {e.request!r}: wanted place {w} is outside its {len(e.tokens)} tokens")
-            for t in e.tokens:
-                if not (0 <= int(t) < self.spec.vocab_size):
-                    raise ValueError(f"request {e.request!r}: token {t} is outside the vocabulary of {self.spec.vocab_size}")
-        fresh = [e.request for e in entries if not self.cache.has(e.request)]
-        for r in fresh:
-            self.cache.begin(r)
-        try:
-            if not self.can_run(entries):
-                raise OutOfPages(f"step of {sum(len(e.tokens) for e in entries)} tokens does not fit: "
-                                 f"free pages {self.cache.free_pages()}")
-            for e in entries:
-                new_len = self.cache.length(e.request) + len(e.tokens)
-                if new_len > self.spec.max_positions:
-                    raise ValueError(f"request {e.request!r} would reach {new_len} tokens; the model's "
-                                     f"limit is {self.spec.max_positions}")
-            for e in entries:
-                self.cache.ensure(e.request, self.cache.length(e.request) + len(e.tokens))
-        except Exception:
-            for r in fresh:
-                self.cache.release(r)
-            raise
-
-        S = len(entries)
-        T = sum(len(e.tokens) for e in entries)
-        tokens = np.empty(T, np.int32)
-        positions = np.empty(T, np.int32)
-        seq_of = np.empty(T, np.int32)
-        cu_q = np.zeros(S + 1, np.int32)
-        kv_len = np.empty(S, np.int32)
-        slots = np.empty(S, np.int32)
-        rows: List[int] = []
-        q_start, q_len = [], []
-        off = 0
-        for s, e in enumerate(entries):
-            n = len(e.tokens)
-            cur = self.cache.length(e.request)
-            tokens[off:off + n] = np.asarray(e.tokens, dtype=np.int64)
-            positions[off:off + n] = np.arange(cur, cur + n, dtype=np.int32)
-            seq_of[off:off + n] = s
-            cu_q[s + 1] = off + n
-            kv_len[s] = cur + n
-            slots[s] = self.cache.slot_of(e.request)
-            rows.extend(off + int(w) for w in e.want)
-            q_start.append(cur)
-            q_len.append(n)
-            off += n
-        reqs = [e.request for e in entries]
-        max_blocks = (self.cache.max_blocks(reqs) + 7) // 8 * 8
-        tables = []
-        for g in self.cache.groups:
-            tb = np.full((S, max_blocks), -1, np.int32)
-            for s, r in enumerate(reqs):
-                row = self.cache.block_table(g.index, r)
-                tb[s, :len(row)] = row
-            tables.append(tb)
-        logit_rows = np.asarray(rows, dtype=np.int32)
-        staged = self.stager.stage([tokens, positions, seq_of, cu_q, kv_len, slots, logit_rows] + tables)
-        return StepContext(
-            n_tokens=T, n_seqs=S, n_logit_rows=len(rows),
-            tokens=staged[0], positions=staged[1], seq_of_token=staged[2], cu_q=staged[3],
-            kv_len=staged[4], slots=staged[5], logit_rows=staged[6],
-            block_tables={g.index: staged[7 + i] for i, g in enumerate(self.cache.groups)},
-            requests=reqs, h_q_start=q_start, h_q_len=q_len, h_kv_len=[int(x) for x in kv_len],
-            h_slots=[int(x) for x in slots], max_q_len=max(q_len), max_kv_len=int(kv_len.max()),
-            decode_only=all(n == 1 for n in q_len))
+        return prepare_step(self.cache, self.stager, entries, self.spec.vocab_size, self.spec.max_positions)
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run the entries as one batch; returns logits [wanted, vocab] (32-bit, on the

@@ -1,0 +1,58 @@
+"""Token selection on the device for the two plain cases: the highest logit, and a draw
+from softmax(logits / T).  Only token ids (and a finiteness flag) come back to the host.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import torch
+
+from ..csrc import ops
+from .host import request_key, uniform
+from .params import SamplingParams
+
+
+class DeviceSampler:
+    def __init__(self, device: torch.device, max_rows: int = 256) -> None:
+        self.device = device
+        self._cap = 0
+        self._grow(max_rows)
+
+    def _grow(self, rows: int) -> None:
+        self._cap = rows
+        self.out = torch.empty(rows, dtype=torch.int32, device=self.device)
+        self.bad = torch.empty(rows, dtype=torch.int32, device=self.device)
+        self.temperature = torch.empty(rows, dtype=torch.float32, device=self.device)
+        self.uniform = torch.empty(rows, dtype=torch.float64, device=self.device)
+        self.h_out = torch.empty(2 * rows, dtype=torch.int32).pin_memory()
+        self.h_temp = torch.empty(rows, dtype=torch.float32).pin_memory()
+        self.h_uniform = torch.empty(rows, dtype=torch.float64).pin_memory()
+
+    def greedy_launch(self, logits: torch.Tensor) -> None:
+        """Arg-max of every row into `self.out` (no synchronisation)."""
+        rows = logits.shape[0]
+        if rows > self._cap:
+            self._grow(max(rows, 2 * self._cap))
+        ops.argmax(logits, self.out[:rows], self.bad[:rows])
+
+    def temperature_launch(self, logits: torch.Tensor, temperatures: Sequence[float],
+                           uniforms: Sequence[float]) -> None:
+        rows = logits.shape[0]
+        if rows > self._cap:
+            self._grow(max(rows, 2 * self._cap))
+        self.h_temp[:rows] = torch.tensor(list(temperatures), dtype=torch.float32)
+        self.h_uniform[:rows] = torch.tensor(list(uniforms), dtype=torch.float64)
+        self.temperature[:rows].copy_(self.h_temp[:rows], non_blocking=True)
+        self.uniform[:rows].copy_(self.h_uniform[:rows], non_blocking=True)
+        ops.sample_temperature(logits, self.temperature[:rows], self.uniform[:rows],
+                               self.out[:rows], self.bad[:rows])
+
+    def read(self, rows: int) -> List[int]:
+        """Token ids of the last launch (synchronises); raises on non-finite logits."""
+        self.h_out[:rows].copy_(self.out[:rows], non_blocking=True)
+        self.h_out[rows:2 * rows].copy_(self.bad[:rows], non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        vals = self.h_out[:2 * rows].tolist()
+        if any(vals[rows:]):
+            raise ValueError("invalid sampling logits (a non-finite value)")
+        return vals[:rows]

@@ -1,0 +1,307 @@
+"""The engine against the plain implementation, in every way of cutting the work, in
+32-bit and in bfloat16 (GPU).  All cases go through ModelRunner.step, the step function
+that generation uses; two of them go through the bin/trace_run program itself."""
+import json
+import os
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from helpers import (BF16_REL_OF_MAX, CONFIGS, Trace, assert_close, check_trace, make_model_folder,
+                     random_tokens, run_trace_inprocess, run_trace_program)
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [1, 7, 16, 33, 90, 120], "B": [3, 12, 31, 64, 100, 150], "C": [5, 40, 77, 130, 200, 64]}
+DTYPES = ["float32", "bfloat16"]
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for name, (cfg, seed, _) in CONFIGS.items():
+        out[name] = make_model_folder(str(tmp_path_factory.mktemp("model") / name), cfg, seed)
+    return out
+
+
+@pytest.fixture(scope="module")
+def requests_of():
+    return {name: {f"r{i}": random_tokens(n, CONFIGS[name][0]["vocab_size"], 1000 + 17 * i + n)
+                   for i, n in enumerate(lens)} for name, lens in LENGTHS.items()}
+
+
+_REF = {}
+
+
+def reference(folders, requests_of, name, dtype):
+    """Plain logits [len, vocab] of every request, whole, computed once."""
+    key = (name, dtype)
+    if key not in _REF:
+        model = plain.PlainModel(folders[name], round_to_bf16=(dtype == "bfloat16"))
+        _REF[key] = {rid: model.logits(toks) for rid, toks in requests_of[name].items()}
+    return _REF[key]
+
+
+_RUNNERS = {}
+
+
+def runner_for(folders, name, dtype, num_pages=256):
+    from inferloop_b200.engine import ModelRunner
+    key = (name, dtype, num_pages)
+    if key not in _RUNNERS:
+        _RUNNERS[key] = ModelRunner.from_folder(folders[name], dtype=dtype, page_size=CONFIGS[name][2],
+                                                num_pages=num_pages, max_requests=8)
+    r = _RUNNERS[key]
+    for rid in r.cache.live_requests():
+        r.end(rid)
+    return r
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_each_request_alone_and_whole(folders, requests_of, name, dtype):
+    trace = Trace()
+    for rid, toks in requests_of[name].items():
+        trace.step([(rid, toks, list(range(len(toks))))], end=[rid])
+    r = runner_for(folders, name, dtype)
+    check_trace(run_trace_inprocess(r, trace), trace, reference(folders, requests_of, name, dtype), dtype, f"{name} whole")
+    r.cache.check()
+    assert all(v == 256 for v in r.cache.free_pages().values())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_most_in_one_step_then_the_last_32_one_by_one(folders, requests_of, name, dtype):
+    trace = Trace()
+    for rid, toks in requests_of[name].items():
+        head = max(1, len(toks) - 32)
+        trace.step([(rid, toks[:head], [head - 1])])
+        for i in range(head, len(toks)):
+            trace.step([(rid, [toks[i]], [0])], end=[rid] if i == len(toks) - 1 else [])
+        if head == len(toks):
+            trace.step([], end=[rid])
+    r = runner_for(folders, name, dtype)
+    check_trace(run_trace_inprocess(r, trace), trace, reference(folders, requests_of, name, dtype), dtype, f"{name} decode")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_portions_of_changing_size(folders, requests_of, name, dtype):
+    sizes = [7, 2, 13, 3, 2, 21, 5, 2, 9, 1, 17]
+    trace = Trace()
+    for k, (rid, toks) in enumerate(requests_of[name].items()):
+        i, j = 0, k
+        while i < len(toks):
+            n = min(sizes[j % len(sizes)], len(toks) - i)
+            trace.step([(rid, toks[i:i + n], list(range(n)))], end=[rid] if i + n == len(toks) else [])
+            i += n
+            j += 1
+    r = runner_for(folders, name, dtype)
+    check_trace(run_trace_inprocess(r, trace), trace, reference(folders, requests_of, name, dtype), dtype, f"{name} portions")
+
+
+def mixed_trace(reqs, seed=0, tail=12):
+    """Up to four live requests; each step holds portions of some beside single decoded
+    tokens of others, some requests sit a step out; a finished request's place is taken
+    by the next one.  Returns the trace and the most tokens held at any time (each
+    request rounded up to 64)."""
+    rng = random.Random(seed)
+    # every request runs twice, so late arrivals land on pages others have given back
+    queue = [(f"{rid}.{rep}", rid) for rep in range(2) for rid in reqs]
+    rng.shuffle(queue)
+    live, cursor = [], {}
+    trace, peak = Trace(), 0
+    alias = {}
+    while queue or live:
+        while queue and len(live) < 4:
+            tid, rid = queue.pop()
+            live.append(tid); cursor[tid] = 0; alias[tid] = rid
+        entries, ended = [], []
+        for tid in list(live):
+            toks = reqs[alias[tid]]
+            if len(live) > 1 and rng.random() < 0.25:
+                continue                                       # sits this step out
+            left = len(toks) - cursor[tid]
+            n = 1 if left <= tail else min(left - tail, rng.choice([2, 3, 5, 8, 13, 17, 29]))
+            want = list(range(n)) if rng.random() < 0.7 else [n - 1]
+            entries.append((tid, toks[cursor[tid]:cursor[tid] + n], want))
+            cursor[tid] += n
+            if cursor[tid] == len(toks):
+                ended.append(tid)
+        held = sum(-(-cursor[t] // 64) * 64 for t in live)
+        peak = max(peak, held)
+        if entries:
+            trace.step(entries, end=ended)
+        for tid in ended:
+            live.remove(tid)
+    return trace, peak, alias
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_mixed_batches_on_few_pages(folders, requests_of, name, dtype):
+    from inferloop_b200.engine import ModelRunner
+    reqs = requests_of[name]
+    trace, peak, alias = mixed_trace(reqs, seed=len(name) + ord(name))
+    page = CONFIGS[name][2]
+    r = ModelRunner.from_folder(folders[name], dtype=dtype, page_size=page, num_pages=peak // page, max_requests=8)
+    out = run_trace_inprocess(r, trace)
+    ref = reference(folders, requests_of, name, dtype)
+    check_trace(out, trace, {tid: ref[rid] for tid, rid in alias.items()}, dtype, f"{name} mixed")
+    info = r.cache.inspect()
+    assert all(g["reuses"] > 0 for g in info["groups"]), "the pool was large enough that no page was used again"
+    assert all(g["free"] == g["total"] for g in info["groups"])
+    assert any(len(s["entries"]) >= 3 and any(len(e["tokens"]) > 1 for e in s["entries"])
+               and any(len(e["tokens"]) == 1 for e in s["entries"]) for s in trace.steps)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_the_trace_program_itself(folders, requests_of, dtype, tmp_path):
+    """bin/trace_run as a separate process, on a mixed trace with few pages."""
+    name = "B"
+    reqs = requests_of[name]
+    trace, peak, alias = mixed_trace(reqs, seed=99)
+    out = run_trace_program(folders[name], dtype, trace, str(tmp_path / "out"), max_tokens=peak,
+                            block_size=CONFIGS[name][2])
+    ref = reference(folders, requests_of, name, dtype)
+    check_trace(out, trace, {tid: ref[rid] for tid, rid in alias.items()}, dtype, "trace_run")
+    written = sorted(int(f[:-4]) for f in os.listdir(tmp_path / "out"))
+    assert written == sorted(trace.rows)           # a file exactly where something was wanted
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(folders, dtype, tmp_path):
+    """A short prompt, then 700 tokens one by one: every page edge is crossed many times."""
+    cfg = dict(CONFIGS["A"][0], max_position_embeddings=1024)
+    d = make_model_folder(str(tmp_path / "long"), cfg, 3)
+    toks = random_tokens(740, cfg["vocab_size"], 5)
+    ref = plain.PlainModel(d, round_to_bf16=(dtype == "bfloat16")).logits(toks)
+    from inferloop_b200.engine import ModelRunner, StepEntry
+    r = ModelRunner.from_folder(d, dtype=dtype, page_size=4, num_pages=190, max_requests=2)
+    got = [r.step([StepEntry("x", toks[:40], list(range(40)))]).float().cpu().clone()]
+    for i in range(40, len(toks)):
+        got.append(r.step([StepEntry("x", [toks[i]], [0])]).float().cpu().clone())
+    assert_close(torch.cat(got), ref, dtype, "long decoding")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_the_first_tokens_of_a_sequence(folders, requests_of, name, dtype):
+    """Position 0 alone, then 1, then 2: the smallest caches there are."""
+    toks = requests_of[name]["r3"]
+    ref = reference(folders, requests_of, name, dtype)["r3"]
+    trace = Trace()
+    for i in range(6):
+        trace.step([("r3", [toks[i]], [0])])
+    trace.step([("r3", toks[6:8], [0, 1])], end=["r3"])
+    r = runner_for(folders, name, dtype)
+    check_trace(run_trace_inprocess(r, trace), trace, {"r3": ref}, dtype, f"{name} first tokens")
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_float32_logits_do_not_depend_on_the_cut_at_all(folders, requests_of, name):
+    """On the 32-bit path the order of every sum is fixed per position, so two ways of
+    cutting give the same bits."""
+    toks = requests_of[name]["r4"]
+    r = runner_for(folders, name, "float32")
+    from inferloop_b200.engine import StepEntry
+    whole = r.step([StepEntry("w", toks, list(range(len(toks))))]).cpu().clone()
+    r.end("w")
+    parts, i = [], 0
+    other = requests_of[name]["r2"]
+    for n in [5, 2, 30, 1, 1, 9, 400]:
+        n = min(n, len(toks) - i)
+        if n <= 0:
+            break
+        entries = [StepEntry("p", toks[i:i + n], list(range(n)))]
+        if i == 0:
+            entries.insert(0, StepEntry("other", other, []))      # company in the batch
+        parts.append(r.step(entries).cpu().clone())
+        i += n
+    assert torch.equal(torch.cat(parts), whole)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(folders, name, dtype):
+    from inferloop_b200 import Engine, SamplingParams
+    cfg, _, page = CONFIGS[name]
+    lens = [1, 7, 16, 33] if name == "A" else [3, 12, 31, 64, 100, 150]
+    new = 16 if name == "A" else 24
+    prompts = [random_tokens(n, cfg["vocab_size"], 50 + n) for n in lens]
+    engine = Engine(folders[name], dtype=dtype, block_size=page, num_gpu_blocks_override=96,
+                    max_num_seqs=4, prefill_chunk_tokens=32, max_num_batched_tokens=40)
+    got = engine.generate(prompts, SamplingParams(), max_new_tokens=new)
+    model = plain.PlainModel(folders[name], round_to_bf16=(dtype == "bfloat16"))
+    for p, g in zip(prompts, got):
+        assert len(g) == new
+        if dtype == "float32":
+            assert g == plain.generate(model, p, new), "greedy tokens differ from the plain implementation"
+        else:
+            # teacher-forced: every token the engine chose is within the bfloat16 bound of the best
+            ref = model.logits(p + g)[len(p) - 1:-1]
+            bound = BF16_REL_OF_MAX * float(ref.abs().max())
+            for i, t in enumerate(g):
+                assert ref[i, t] >= ref[i].max() - 2 * bound
+    info = engine.inspect()
+    assert info["running"] == 0 and all(g["free"] == g["total"] for g in info["cache"]["groups"])
+    assert info["scheduler"]["steps"] < sum(lens) // 8 + new * 3      # it batched, it did not serialise
+
+
+def test_temperature_generation_matches_the_plain_sampler(folders):
+    """Tiny B's workload: portions of 32 mixed with decode steps, 24 tokens at T = 0.8
+    with a fixed seed; in 32-bit the trajectory equals the plain implementation's."""
+    from inferloop_b200 import Engine, SamplingParams
+    cfg, _, page = CONFIGS["B"]
+    prompts = [random_tokens(n, cfg["vocab_size"], 70 + n) for n in (3, 12, 31, 64)]
+    engine = Engine(folders["B"], dtype="float32", block_size=page, num_gpu_blocks_override=64,
+                    max_num_seqs=4, prefill_chunk_tokens=32)
+    params = SamplingParams(temperature=0.8, seed=1234)
+    got = engine.generate(prompts, params, max_new_tokens=24)
+    model = plain.PlainModel(folders["B"])
+    for rid, (p, g) in enumerate(zip(prompts, got)):
+        assert g == plain.generate(model, p, 24, temperature=0.8, seed=1234, request=rid)
+    # filters go through the host sampler
+    engine2 = Engine(folders["B"], dtype="float32", block_size=page, num_gpu_blocks_override=64, max_num_seqs=4)
+    g2 = engine2.generate(prompts[:2], SamplingParams(temperature=0.9, top_k=5, top_p=0.9, seed=7), 8)
+    for rid, (p, g) in enumerate(zip(prompts[:2], g2)):
+        seq = list(p)
+        for n, t in enumerate(g):
+            want = plain.sample(model.logits(seq)[-1].float().tolist(), 0.9, 7, rid, n, top_k=5, top_p=0.9)
+            assert t == want
+            seq.append(t)
+
+
+def test_page_pressure_in_the_engine_gives_the_same_tokens(folders):
+    """So few pages that requests are preempted and recomputed: tokens do not change."""
+    from inferloop_b200 import Engine, SamplingParams
+    cfg, _, page = CONFIGS["B"]
+    prompts = [random_tokens(n, cfg["vocab_size"], 90 + n) for n in (31, 64, 40, 12, 55)]
+    roomy = Engine(folders["B"], dtype="float32", block_size=page, num_gpu_blocks_override=128, max_num_seqs=4,
+                   prefill_chunk_tokens=32)
+    want = roomy.generate(prompts, SamplingParams(), 20)
+    tight = Engine(folders["B"], dtype="float32", block_size=page, num_gpu_blocks_override=21, max_num_seqs=4,
+                   prefill_chunk_tokens=32)
+    got = tight.generate(prompts, SamplingParams(), 20)
+    assert got == want
+    assert tight.inspect()["scheduler"]["preemptions"] > 0
+
+
+def test_refusals(folders, tmp_path):
+    from inferloop_b200.engine import ModelRunner, StepEntry
+    from inferloop_b200.cache import OutOfPages
+    with pytest.raises(RuntimeError, match="CUDA device only"):
+        ModelRunner.from_folder(folders["A"], device="cpu")
+    r = ModelRunner.from_folder(folders["A"], dtype="float32", page_size=4, num_pages=4, max_requests=2)
+    with pytest.raises(OutOfPages):
+        r.step([StepEntry("a", list(range(17)), [])])
+    assert not r.is_live("a") and r.cache.free_pages() == {0: 4}
+    with pytest.raises(ValueError, match="vocabulary"):
+        r.step([StepEntry("a", [999], [])])
+    with pytest.raises(ValueError, match="twice"):
+        r.step([StepEntry("a", [1], []), StepEntry("a", [2], [])])
+    with pytest.raises(ValueError, match="outside its"):
+        r.step([StepEntry("a", [1], [1])])

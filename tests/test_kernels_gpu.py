@@ -1,0 +1,277 @@
+"""Each kernel alone against a plain 64-bit statement of the same operation, at sizes
+other than the engine configurations' (GPU)."""
+import math
+import random
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def tol(dtype, ref, scale=1.0):
+    """float32: 1e-5 + 1e-5 |ref|; bfloat16 outputs: one rounding of the result (2^-8
+    relative) on top of that."""
+    if dtype == "float32":
+        return 1e-5 * scale + 1e-5 * ref.abs()
+    return 1e-5 * scale + (2.0 ** -8) * ref.abs() + 2.0 ** -8 * scale * 0.05
+
+
+def close(got, ref, dtype, scale=1.0, what=""):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    err = (got - ref).abs()
+    bad = err > tol(dtype, ref, scale)
+    assert not bad.any(), f"{what}: {int(bad.sum())} bad, max err {err.max().item():.3e} at {torch.nonzero(bad)[0].tolist()}"
+
+
+def ops():
+    from inferloop_b200.csrc import ops as o
+    return o
+
+
+@pytest.mark.parametrize("table_dtype", ["float32", "bfloat16"])
+def test_embed(table_dtype):
+    V, H = 517, 72
+    table = torch.randn(V, H).to(DT[table_dtype])
+    tokens = torch.tensor([0, 516, 3, 3, 100], dtype=torch.int32)
+    out = torch.empty(5, H, device="cuda")
+    ops().embed(tokens.cuda(), table.cuda(), out)
+    assert torch.equal(out.cpu(), table.float()[tokens.long()])
+
+
+@pytest.mark.parametrize("width,rows,eps", [(72, 5, 1e-6), (100, 3, 1e-5), (4096, 2, 1e-6), (5120, 1, 1e-6), (48, 17, 3e-6)])
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+def test_rmsnorm(width, rows, eps, out_dtype):
+    x = torch.randn(rows, width) * 3
+    w = 1 + 0.1 * torch.randn(width)
+    out = torch.empty(rows, width, dtype=DT[out_dtype], device="cuda")
+    ops().rmsnorm(x.cuda(), w.cuda(), eps, out)
+    xd = x.double()
+    ref = xd / torch.sqrt((xd * xd).mean(-1, keepdim=True) + eps) * w.double()
+    close(out, ref, out_dtype, what="rmsnorm")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_silu_mul(dtype):
+    rows, width = 7, 176
+    gu = (torch.randn(rows, 2 * width) * 4).to(DT[dtype])
+    gu[0, 0], gu[0, 1] = 80.0, -80.0          # far tails must not overflow
+    out = torch.empty(rows, width, dtype=DT[dtype], device="cuda")
+    ops().silu_mul(gu.cuda(), out)
+    g, u = gu.double()[:, :width], gu.double()[:, width:]
+    close(out, g * torch.sigmoid(g) * u, dtype, what="silu_mul")
+    assert torch.isfinite(out).all()
+
+
+def test_gather_rows_and_rope_table():
+    x = torch.randn(9, 40)
+    idx = torch.tensor([8, 0, 3, 3], dtype=torch.int32)
+    out = torch.empty(4, 40, device="cuda")
+    ops().gather_rows(x.cuda(), idx.cuda(), out)
+    assert torch.equal(out.cpu(), x[idx.long()])
+    pos = torch.tensor([0, 1, 77, 4095, 131071], dtype=torch.int32)
+    for theta, rd in ((10000.0, 16), (1e6, 128), (50000.0, 24)):
+        inv = torch.tensor([theta ** (-(2.0 * i) / rd) for i in range(rd // 2)], dtype=torch.float64)
+        table = torch.empty(5, rd // 2, 2, device="cuda")
+        ops().rope_table(pos.cuda(), inv.cuda(), table)
+        angle = pos.double()[:, None] * inv[None, :]
+        ref = torch.stack([torch.cos(angle), torch.sin(angle)], -1)
+        assert (table.double().cpu() - ref).abs().max() < 1e-7      # one rounding to 32-bit
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 96, 64), (5, 100, 72), (16, 515, 80), (17, 64, 200), (130, 224, 96), (64, 1000, 1024)])
+@pytest.mark.parametrize("in_dtype,out_dtype", [("float32", "float32"), ("bfloat16", "bfloat16"), ("bfloat16", "float32")])
+@pytest.mark.parametrize("bias,accumulate", [(False, False), (True, True)])
+def test_gemm_simt(M, N, K, in_dtype, out_dtype, bias, accumulate):
+    if accumulate and out_dtype != "float32":
+        pytest.skip("accumulation needs a 32-bit output")
+    a = torch.randn(M, K).to(DT[in_dtype])
+    w = (torch.randn(N, K) * 0.05).to(DT[in_dtype])
+    b = torch.randn(N) if bias else None
+    base = torch.randn(M, N)
+    out = base.clone().to(DT[out_dtype]).cuda() if accumulate else torch.empty(M, N, dtype=DT[out_dtype], device="cuda")
+    ops().gemm_simt(a.cuda(), w.cuda(), out, None if b is None else b.cuda(), accumulate)
+    ref = a.double() @ w.double().T
+    if bias:
+        ref = ref + b.double()
+    if accumulate:
+        ref = ref + base.double()
+    close(out, ref, out_dtype, scale=float(ref.abs().max()), what="gemm")
+
+
+def test_gemm_simt_rows_do_not_depend_on_the_batch():
+    """The same row gives the same bits alone, among 5 rows and among 100 rows."""
+    K, N = 136, 200
+    a = torch.randn(100, K).cuda()
+    w = torch.randn(N, K).cuda()
+    outs = []
+    for M in (1, 5, 16, 17, 100):
+        out = torch.empty(M, N, device="cuda")
+        ops().gemm_simt(a[:M].contiguous(), w, out)
+        outs.append(out[0].clone())
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
+
+
+# ------------------------------------------------------------------ attention pieces
+def build_cache(seqs_kv, nkv, d, page_size, num_pages, dtype, seed=0):
+    """Scatter each sequence's keys/values into shuffled pages; returns cache tensors and
+    the block table [S, max_blocks]."""
+    rng = random.Random(seed)
+    pages = list(range(num_pages))
+    rng.shuffle(pages)
+    k_cache = torch.full((num_pages, nkv, page_size, d), 7.0)      # stale contents must not matter
+    v_cache = torch.full((num_pages, nkv, page_size, d), -9.0)
+    max_blocks = max(-(-k.shape[0] // page_size) for k, _ in seqs_kv)
+    table = torch.full((len(seqs_kv), max_blocks), -1, dtype=torch.int32)
+    for s, (k, v) in enumerate(seqs_kv):
+        for b in range(-(-k.shape[0] // page_size)):
+            page = pages.pop()
+            table[s, b] = page
+            n = min(page_size, k.shape[0] - b * page_size)
+            k_cache[page, :, :n] = k[b * page_size:b * page_size + n].transpose(0, 1)
+            v_cache[page, :, :n] = v[b * page_size:b * page_size + n].transpose(0, 1)
+    return k_cache.to(dtype), v_cache.to(dtype), table
+
+
+def ref_attention(q, k, v, pos, window):
+    """q [nq, d] at position pos over keys k, v [n, nkv, d] (64-bit)."""
+    nq, d = q.shape
+    nkv = k.shape[1]
+    lo = max(0, pos + 1 - window) if window else 0
+    out = torch.zeros(nq, d, dtype=torch.float64)
+    for h in range(nq):
+        kh = h // (nq // nkv)
+        s = (k[lo:pos + 1, kh] @ q[h]) / math.sqrt(d)
+        out[h] = torch.softmax(s, 0) @ v[lo:pos + 1, kh]
+    return out
+
+
+@pytest.mark.parametrize("nq,nkv,d,page_size,window", [(4, 2, 16, 4, 0), (6, 2, 32, 8, 0), (5, 5, 48, 16, 20),
+                                                         (8, 1, 80, 16, 0), (3, 3, 256, 32, 33), (32, 8, 128, 16, 0)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_paged_attention_mixed_batch(nq, nkv, d, page_size, window, dtype):
+    """Three sequences: a whole prompt, a portion that starts mid-sequence, one decode
+    token; pages shuffled; compared per token with the plain softmax."""
+    torch.manual_seed(nq * 100 + d)
+    lens = [37, 90, 131]                  # keys in the cache after the step
+    q_lens = [37, 23, 1]                  # tokens of this step
+    seqs = [(torch.randn(n, nkv, d).to(DT[dtype]).double(), torch.randn(n, nkv, d).to(DT[dtype]).double()) for n in lens]
+    k_cache, v_cache, table = build_cache([(k.float(), v.float()) for k, v in seqs], nkv, d, page_size, 40, DT[dtype])
+    T = sum(q_lens)
+    q = (torch.randn(T, nq * d)).to(DT[dtype])
+    positions, seq_of = [], []
+    for s, (n, ql) in enumerate(zip(lens, q_lens)):
+        positions += list(range(n - ql, n))
+        seq_of += [s] * ql
+    out = torch.empty(T, nq * d, dtype=DT[dtype], device="cuda")
+    ops().paged_attention_simple(q.cuda(), out, k_cache.cuda(), v_cache.cuda(),
+                                 torch.tensor(positions, dtype=torch.int32).cuda(),
+                                 torch.tensor(seq_of, dtype=torch.int32).cuda(), table.cuda(),
+                                 window, 1.0 / math.sqrt(d), nq, nkv, d)
+    ref = torch.stack([ref_attention(q[t].double().view(nq, d), *seqs[seq_of[t]], positions[t], window).reshape(-1)
+                       for t in range(T)])
+    close(out, ref, dtype, scale=1.0, what="attention")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_finds_one_far_key_and_respects_the_window_edge(dtype):
+    """One key among hundreds is made to dominate; the output must be its value.  With a
+    window, a dominant key just outside must be ignored and one just inside found."""
+    nq, nkv, d, page = 2, 1, 32, 16
+    n = 700
+    torch.manual_seed(1)
+    k = torch.randn(n, nkv, d) * 0.1
+    v = torch.arange(n, dtype=torch.float32)[:, None, None].expand(n, nkv, d).clone()   # value = its position
+    qv = torch.randn(nq * d) * 0.1
+    for far, window, expect in ((13, 0, 13.0), (699 - 50 + 1, 50, 650.0), (699 - 50, 50, None), (352, 0, 352.0)):
+        kk = k.clone()
+        direction = torch.randn(d)
+        direction /= direction.norm()
+        kk[far, 0] = direction * 40
+        q = qv.clone().view(nq, d)
+        q[:] = direction * 40                   # score 1600 / sqrt(32): everything else vanishes
+        k_cache, v_cache, table = build_cache([(kk, v)], nkv, d, page, 64, DT[dtype], seed=far)
+        out = torch.empty(1, nq * d, dtype=DT[dtype], device="cuda")
+        ops().paged_attention_simple(q.reshape(1, -1).to(DT[dtype]).cuda(), out, k_cache.cuda(), v_cache.cuda(),
+                                     torch.tensor([n - 1], dtype=torch.int32).cuda(),
+                                     torch.tensor([0], dtype=torch.int32).cuda(), table.cuda(),
+                                     window, 1.0 / math.sqrt(d), nq, nkv, d)
+        got = out.float().cpu()
+        if expect is not None:
+            assert torch.allclose(got, torch.full_like(got, expect), rtol=2.0 ** -8), (far, window, got[0, :4])
+        else:       # the dominant key is outside: the result is an average over the window
+            assert 650.0 <= got.min().item() and got.max().item() <= 699.0
+
+
+@pytest.mark.parametrize("nq,nkv,d,rd,page_size", [(4, 2, 16, 16, 4), (6, 2, 32, 32, 8), (5, 5, 48, 24, 16), (8, 2, 128, 128, 16), (2, 1, 80, 80, 32)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("use_norm", [True, False])
+def test_qk_norm_rope_cache(nq, nkv, d, rd, page_size, dtype, use_norm):
+    torch.manual_seed(d)
+    T, S = 11, 2
+    eps, theta = 1e-5, 1e6
+    width = (nq + 2 * nkv) * d
+    qkv = torch.randn(T, width).to(DT[dtype])
+    qw, kw = 1 + 0.1 * torch.randn(d), 1 + 0.1 * torch.randn(d)
+    positions = torch.tensor([5, 6, 7, 8, 9, 10, 11, 40, 41, 42, 43], dtype=torch.int32)
+    seq_of = torch.tensor([0] * 7 + [1] * 4, dtype=torch.int32)
+    num_pages = 24
+    max_blocks = -(-44 // page_size)
+    perm = torch.randperm(num_pages)[:S * max_blocks].to(torch.int32).view(S, max_blocks)
+    inv = torch.tensor([theta ** (-(2.0 * i) / rd) for i in range(rd // 2)], dtype=torch.float64)
+    table = torch.empty(T, rd // 2, 2, device="cuda")
+    ops().rope_table(positions.cuda(), inv.cuda(), table)
+    k_cache = torch.zeros(num_pages, nkv, page_size, d, dtype=DT[dtype], device="cuda")
+    v_cache = torch.zeros_like(k_cache)
+    q_out = torch.empty(T, nq * d, dtype=DT[dtype], device="cuda")
+    ops().qk_norm_rope_cache(qkv.cuda(), q_out, qw.cuda() if use_norm else None, kw.cuda() if use_norm else None,
+                             eps, table, rd, positions.cuda(), seq_of.cuda(), perm.cuda(), page_size,
+                             k_cache, v_cache, nq, nkv, d)
+    x = qkv.double()
+    q, k, v = x[:, :nq * d].view(T, nq, d), x[:, nq * d:(nq + nkv) * d].view(T, nkv, d), x[:, (nq + nkv) * d:].view(T, nkv, d)
+
+    def norm(t, w):
+        return t / torch.sqrt((t * t).mean(-1, keepdim=True) + eps) * w.double() if use_norm else t
+
+    def rope(t):
+        half = rd // 2
+        ang = positions.double()[:, None] * inv[None, :]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        out = t.clone()
+        a, b = t[..., :half], t[..., half:rd]
+        out[..., :half] = a * c - b * s
+        out[..., half:rd] = a * s + b * c
+        return out
+
+    q_ref, k_ref = rope(norm(q, qw)), rope(norm(k, kw))
+    close(q_out.view(T, nq, d), q_ref, dtype, scale=float(q_ref.abs().max()), what="q")
+    kc, vc = k_cache.double().cpu(), v_cache.double().cpu()
+    written = torch.zeros(num_pages, page_size, dtype=torch.bool)
+    for t in range(T):
+        p = int(positions[t]); page = int(perm[seq_of[t], p // page_size]); slot = p % page_size
+        close(kc[page, :, slot], k_ref[t], dtype, scale=float(k_ref.abs().max()), what=f"k token {t}")
+        close(vc[page, :, slot], v[t], dtype, scale=float(v.abs().max()), what=f"v token {t}")
+        written[page, slot] = True
+    assert (kc.abs().sum((1, 3))[~written] == 0).all(), "a slot no token owns was written"
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    from inferloop_b200.csrc.ops import KernelError
+    o = ops()
+    with pytest.raises(KernelError, match="CUDA only"):
+        o.rmsnorm(torch.randn(2, 8), torch.ones(8), 1e-6, torch.empty(2, 8))
+    q = torch.randn(1, 2 * 272, device="cuda")
+    kc = torch.zeros(2, 1, 16, 272, device="cuda")
+    with pytest.raises(KernelError, match="head size"):
+        o.paged_attention_simple(q, torch.empty_like(q), kc, kc, torch.zeros(1, dtype=torch.int32, device="cuda"),
+                                 torch.zeros(1, dtype=torch.int32, device="cuda"),
+                                 torch.zeros(1, 1, dtype=torch.int32, device="cuda"), 0, 1.0, 2, 1, 272)
+    with pytest.raises(KernelError, match="multiple"):
+        kc = torch.zeros(2, 2, 16, 16, device="cuda")
+        q = torch.randn(1, 3 * 16, device="cuda")
+        o.paged_attention_simple(q, torch.empty_like(q), kc, kc, torch.zeros(1, dtype=torch.int32, device="cuda"),
+                                 torch.zeros(1, dtype=torch.int32, device="cuda"),
+                                 torch.zeros(1, 1, dtype=torch.int32, device="cuda"), 0, 1.0, 3, 2, 16)

@@ -1,0 +1,99 @@
+"""Sampling: the host sampler against the plain rules (no GPU) and the device kernels
+against the host sampler (GPU)."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from inferloop_b200.sampling import SamplingParams, host
+
+
+def test_params_ranges():
+    SamplingParams(temperature=0.7, top_k=5, top_p=0.9, min_p=0.1, presence_penalty=-2.0, repetition_penalty=1.3)
+    for bad in (dict(temperature=-1), dict(top_k=0), dict(top_p=0.0), dict(top_p=1.5), dict(min_p=2.0),
+                dict(presence_penalty=3.0), dict(repetition_penalty=0.0), dict(temperature=float("nan"))):
+        with pytest.raises(ValueError):
+            SamplingParams(**bad)
+    assert SamplingParams().uses_plain_greedy() and not SamplingParams(presence_penalty=0.5).uses_plain_greedy()
+    assert SamplingParams(eos_token=3, eos_tokens=(5,)).is_eos(5) and SamplingParams(eos_token=3).is_eos(3)
+
+
+def test_host_sampler_equals_the_plain_rules():
+    rng = np.random.default_rng(0)
+    for trial in range(60):
+        logits = rng.standard_normal(97).astype(np.float32) * 3
+        if trial % 5 == 0:
+            logits[10] = logits[40] = logits.max() + 1       # equal maxima
+        kw = [dict(temperature=0.0), dict(temperature=0.8), dict(temperature=1.3, top_k=9),
+              dict(temperature=0.6, top_p=0.7), dict(temperature=1.0, min_p=0.2),
+              dict(temperature=0.9, top_k=20, top_p=0.8, min_p=0.05)][trial % 6]
+        p = SamplingParams(seed=trial, **kw)
+        want = plain.sample(logits.tolist(), p.temperature, p.seed, request=7, position=trial,
+                            top_k=p.top_k, top_p=p.top_p, min_p=p.min_p)
+        assert host.sample(logits, p, 7, trial) == want
+    assert host.uniform(5, 9, 2) == plain.uniform_for(5, 9, 2)
+
+
+def test_penalties():
+    logits = np.array([2.0, -1.0, 1.9, 0.5], dtype=np.float32)
+    p = SamplingParams(repetition_penalty=2.0)
+    assert host.sample(logits, p, 0, 0, prompt=[0]) == 2                 # 2.0 / 2 < 1.9
+    p = SamplingParams(presence_penalty=0.2)
+    assert host.sample(logits, p, 0, 0, prompt=[0], generated=[]) == 0  # presence counts generated only
+    assert host.sample(logits, p, 0, 0, generated=[0]) == 2
+    with pytest.raises(ValueError):
+        host.sample(logits, SamplingParams(repetition_penalty=1.5), 0, 0, prompt=[9])
+    with pytest.raises(ValueError):
+        host.sample(np.array([0.0, np.inf], dtype=np.float32), SamplingParams(), 0, 0)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("vocab", [257, 1000, 151936])
+def test_device_argmax(vocab):
+    from inferloop_b200.csrc import ops
+    g = torch.Generator().manual_seed(vocab)
+    logits = torch.randn(5, vocab, generator=g)
+    logits[1, 7] = logits[1, vocab - 3] = 50.0          # equal maxima: the lower index wins
+    logits[2, vocab - 1] = 60.0
+    dev = logits.cuda()
+    out = torch.empty(5, dtype=torch.int32, device="cuda")
+    bad = torch.empty(5, dtype=torch.int32, device="cuda")
+    ops.argmax(dev, out, bad)
+    assert out.tolist() == [host.greedy(r.numpy()) for r in logits]
+    assert out.tolist()[1] == 7 and out.tolist()[2] == vocab - 1 and bad.tolist() == [0] * 5
+    dev[3, 11] = float("nan")
+    ops.argmax(dev, out, bad)
+    assert bad.tolist() == [0, 0, 0, 1, 0]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("vocab", [320, 5003])
+def test_device_temperature_draw_equals_the_host_rule(vocab):
+    from inferloop_b200.csrc import ops
+    rows = 64
+    g = torch.Generator().manual_seed(vocab + 1)
+    logits = torch.randn(rows, vocab, generator=g) * 2
+    logits[3, 5] = logits[3, 100] = logits[3].max() + 0.5      # equals at the top
+    logits[4, :] = 0.25                                         # all equal
+    temps = [0.5 + 0.02 * i for i in range(rows)]
+    us = [host.uniform(11, 3, i) for i in range(rows)]
+    us[5], us[6] = 0.0, 1.0 - 2 ** -53
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    bad = torch.empty(rows, dtype=torch.int32, device="cuda")
+    ops.sample_temperature(logits.cuda(), torch.tensor(temps, dtype=torch.float32).cuda(),
+                           torch.tensor(us, dtype=torch.float64).cuda(), out, bad)
+    got = out.tolist()
+    assert bad.tolist() == [0] * rows
+    same = 0
+    for i in range(rows):
+        # the host rule with the same uniform number
+        order = np.lexsort((np.arange(vocab), -logits[i].double().numpy()))
+        w = np.exp((logits[i].double().numpy()[order] - logits[i].max().item()) / float(np.float32(temps[i])))
+        c = np.cumsum(w / w.sum())
+        want = int(order[min(int(np.searchsorted(c, us[i], side="right")), vocab - 1)])
+        if got[i] == want:
+            same += 1
+        else:   # sums in another order may move the crossing by rounding: then u sits on a boundary
+            k = list(order).index(got[i])
+            assert abs(c[k] - us[i]) < 1e-9 or (k > 0 and abs(c[k - 1] - us[i]) < 1e-9), (i, got[i], want)
+    assert same >= rows - 1

@@ -1,0 +1,155 @@
+"""The scheduler's decisions (no GPU), against a runner that executes nothing."""
+import pytest
+
+from fake_runner import FakeRunner
+from helpers import random_tokens
+from inferloop_b200.engine.engine import Engine
+from inferloop_b200.engine.scheduler import CapacityError
+from inferloop_b200.sampling import SamplingParams
+
+
+def make(runner, **kw):
+    kw.setdefault("max_num_seqs", 4)
+    kw.setdefault("prefill_chunk_tokens", 8)
+    kw.setdefault("max_num_batched_tokens", 12)
+    return Engine(None, runner=runner, **kw)
+
+
+PROMPTS = [random_tokens(n, 50, 100 + n) for n in (3, 12, 31, 20, 7, 26)]
+
+
+def serial_tokens(params, max_new=10):
+    out = []
+    for i, p in enumerate(PROMPTS):
+        e = make(FakeRunner(num_pages=64), max_num_seqs=1)
+        e.submit(p, params, max_new, request_id=i)
+        while not e.is_idle():
+            e.step()
+        out.append(e.result(i).generated)
+    return out
+
+
+@pytest.mark.parametrize("params", [SamplingParams(), SamplingParams(temperature=0.8, seed=3),
+                                    SamplingParams(temperature=1.1, top_k=7, top_p=0.9, seed=5)])
+def test_mixed_batches_give_the_tokens_of_serial_runs(params):
+    want = serial_tokens(params)
+    runner = FakeRunner(num_pages=64)
+    e = make(runner)
+    ids = [e.submit(p, params, 10, request_id=i) for i, p in enumerate(PROMPTS)]
+    while not e.is_idle():
+        e.step()
+    assert [e.result(i).generated for i in ids] == want
+    mixed = [s for s in runner.steps if any(n > 1 for _, n in s) and any(n == 1 for _, n in s)]
+    assert mixed, "no step held a prompt portion beside a decode token"
+    assert all(sum(n for _, n in s) <= 12 and len(s) <= 4 for s in runner.steps)
+    assert all(n <= 8 for s in runner.steps for _, n in s)
+    assert all(v == 64 for v in runner.cache.free_pages().values())      # nothing leaked
+    assert runner.cache.slots.num_free == runner.cache.slots.num_slots
+
+
+def test_first_come_first_served_and_sequence_cap():
+    runner = FakeRunner(num_pages=64)
+    e = make(runner, max_num_seqs=2, max_num_batched_tokens=64, prefill_chunk_tokens=64)
+    for i, p in enumerate(PROMPTS[:4]):
+        e.submit(p, None, 3, request_id=i)
+    e.step()
+    assert [r for r, _ in runner.steps[0]] == [0, 1]
+    while not e.is_idle():
+        e.step()
+    first_seen = []
+    for s in runner.steps:
+        for r, _ in s:
+            if r not in first_seen:
+                first_seen.append(r)
+    assert first_seen == [0, 1, 2, 3]
+    assert all(len(s) <= 2 for s in runner.steps)
+
+
+def test_pages_run_out_preempt_by_recompute_same_tokens():
+    want = serial_tokens(SamplingParams(), max_new=12)
+    # 9 pages of 4 tokens: the six requests cannot all be held at once
+    runner = FakeRunner(num_pages=11)
+    e = make(runner, max_num_seqs=4)
+    ids = [e.submit(p, None, 12, request_id=i) for i, p in enumerate(PROMPTS)]
+    guard = 0
+    while not e.is_idle():
+        e.step()
+        guard += 1
+        assert guard < 2000, "no progress"
+    assert [e.result(i).generated for i in ids] == want
+    assert e.scheduler.stats["preemptions"] > 0
+    assert any(e.result(i).preemptions > 0 for i in ids)
+    assert all(v == 11 for v in runner.cache.free_pages().values())
+    assert runner.cache.groups[0].pool.reuses > 0
+
+
+def test_window_group_lets_long_requests_through():
+    runner = FakeRunner(num_pages=40, window=6)
+    e = make(runner)
+    ids = [e.submit(p, None, 8, request_id=i) for i, p in enumerate(PROMPTS[:3])]
+    while not e.is_idle():
+        e.step()
+    assert runner.cache.inspect()["window_pages_released"] > 0
+    assert all(v == 40 for v in runner.cache.free_pages().values())
+
+
+def test_a_request_too_large_for_the_cache_is_refused():
+    e = make(FakeRunner(num_pages=4))
+    with pytest.raises(CapacityError):
+        e.submit(random_tokens(30, 50, 1), None, 4)
+    with pytest.raises(ValueError, match="max_model_len"):
+        make(FakeRunner(max_positions=32)).submit(random_tokens(30, 50, 1), None, 4)
+    with pytest.raises(ValueError, match="vocabulary"):
+        make(FakeRunner()).submit([1, 2, 99], None, 4)
+    with pytest.raises(ValueError, match="empty"):
+        make(FakeRunner()).submit([], None, 4)
+    dup = make(FakeRunner())
+    dup.submit([1], None, 2, request_id="x")
+    with pytest.raises(ValueError):
+        dup.submit([2], None, 2, request_id="x")
+
+
+def test_eos_and_length_finish():
+    runner = FakeRunner(num_pages=64)
+    e = make(runner)
+    p = PROMPTS[1]
+    e.submit(p, None, 6, request_id=0)
+    while not e.is_idle():
+        e.step()
+    free_run = e.result(0).generated
+    assert len(free_run) == 6 and e.result(0).finish_reason == "length"
+    e2 = make(FakeRunner(num_pages=64))
+    e2.submit(p, SamplingParams(eos_token=free_run[2]), 6, request_id=0)
+    while not e2.is_idle():
+        e2.step()
+    stop = free_run.index(free_run[2])
+    assert e2.result(0).generated == free_run[:stop + 1] and e2.result(0).finish_reason == "eos"
+    e3 = make(FakeRunner(num_pages=64), max_output_tokens=2)
+    e3.submit(p, None, 6, request_id=0)
+    while not e3.is_idle():
+        e3.step()
+    assert e3.result(0).generated == free_run[:2]
+
+
+def test_half_portion_rule():
+    # 3 decoding requests leave 5 of 8 budget tokens: a portion of 8 gets the 5 (>= half)
+    runner = FakeRunner(num_pages=64)
+    e = make(runner, max_num_batched_tokens=11, prefill_chunk_tokens=8)   # floor: 8 + 4 - 1
+    for i in range(3):
+        e.submit([1, 2], None, 20, request_id=i)
+    e.step()
+    e.submit(random_tokens(30, 50, 9), None, 2, request_id="late")
+    e.step()
+    last = dict(runner.steps[-1])
+    assert last["late"] == 8 and all(last[i] == 1 for i in range(3))
+    e2 = make(FakeRunner(num_pages=64), max_num_batched_tokens=11, prefill_chunk_tokens=8, max_num_seqs=4)
+    e2.scheduler.config.max_num_batched_tokens = 6       # decodes take 3, 3 left < half of 8
+    for i in range(3):
+        e2.submit([1, 2], None, 20, request_id=i)
+    e2.step()
+    e2.submit(random_tokens(30, 50, 9), None, 2, request_id="late")
+    e2.step()
+    assert "late" not in dict(e2.runner.steps[-1])
+    e2.scheduler.config.max_num_batched_tokens = 7       # 4 left >= half of 8
+    e2.step()
+    assert dict(e2.runner.steps[-1])["late"] == 4
