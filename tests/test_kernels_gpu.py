@@ -159,7 +159,7 @@ def test_paged_attention_mixed_batch(nq, nkv, d, page_size, window, dtype):
     lens = [37, 90, 131]                  # keys in the cache after the step
     q_lens = [37, 23, 1]                  # tokens of this step
     seqs = [(torch.randn(n, nkv, d).to(DT[dtype]).double(), torch.randn(n, nkv, d).to(DT[dtype]).double()) for n in lens]
-    k_cache, v_cache, table = build_cache([(k.float(), v.float()) for k, v in seqs], nkv, d, page_size, 40, DT[dtype])
+    k_cache, v_cache, table = build_cache([(k.float(), v.float()) for k, v in seqs], nkv, d, page_size, 72, DT[dtype])
     T = sum(q_lens)
     q = (torch.randn(T, nq * d)).to(DT[dtype])
     positions, seq_of = [], []
