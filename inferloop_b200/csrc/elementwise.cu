@@ -174,4 +174,28 @@ ILB_EXPORT int ilb_add_inplace(float* x, const float* y, long long n, cudaStream
   return check_launch("add_inplace");
 }
 
+// ---------------------------------------------------------------- decode feedback
+// After a decode step drew one token per sequence: make the next step's inputs on the
+// device (token <- drawn id, position and cache length advance by one), so that a run of
+// decode steps needs no host round trip.
+__global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict__ positions,
+                                      int* __restrict__ kv_len, const int* __restrict__ drawn,
+                                      int n_live, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  if (i < n_live) {
+    tokens[i] = drawn[i];
+    positions[i] += 1;
+    kv_len[i] += 1;
+  }
+}
+
+ILB_EXPORT int ilb_decode_advance(int* tokens, int* positions, int* kv_len, const int* drawn,
+                                  int n_live, int n, cudaStream_t stream) {
+  ILB_REQUIRE(n >= 0 && n_live >= 0 && n_live <= n, "decode_advance: bad sizes");
+  if (n == 0) return 0;
+  decode_advance_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tokens, positions, kv_len, drawn, n_live, n);
+  return check_launch("decode_advance");
+}
+
 ILB_DEFINE_LAST_ERROR()

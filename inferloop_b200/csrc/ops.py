@@ -48,7 +48,12 @@ def _need(t: Optional[torch.Tensor], what: str, dtype: Optional[torch.dtype] = N
         raise KernelError(f"{what}: expected {dtype}, found {t.dtype}")
 
 
+LAUNCHES = 0          # kernels launched through this module since import
+
+
 def _call(module: str, fn: str, *args) -> None:
+    global LAUNCHES
+    LAUNCHES += 1
     lib = load_module(module)
     f = getattr(lib, fn)
     f.restype = ctypes.c_int
@@ -121,6 +126,15 @@ def add_inplace(x: torch.Tensor, y: torch.Tensor) -> None:
     if x.numel() != y.numel():
         raise KernelError("add_inplace: sizes differ")
     _call("elementwise", "ilb_add_inplace", _ptr(x), _ptr(y), ctypes.c_longlong(x.numel()), _stream(x))
+
+
+def decode_advance(tokens: torch.Tensor, positions: torch.Tensor, kv_len: torch.Tensor,
+                   drawn: torch.Tensor, n_live: int) -> None:
+    """tokens[:n_live] = drawn[:n_live]; positions and kv_len of those advance by one."""
+    for t, what in ((tokens, "tokens"), (positions, "positions"), (kv_len, "kv_len"), (drawn, "drawn")):
+        _need(t, what, torch.int32)
+    _call("elementwise", "ilb_decode_advance", _ptr(tokens), _ptr(positions), _ptr(kv_len), _ptr(drawn),
+          _i(n_live), _i(tokens.numel()), _stream(tokens))
 
 
 # --------------------------------------------------------------------------- GEMM

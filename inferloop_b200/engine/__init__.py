@@ -1,4 +1,4 @@
 from .batch import StepContext, StepEntry
-from .runner import ModelRunner, parse_dtype
+from .runner import ModelRunner, parse_dtype, prepare_step
 
-__all__ = ["StepContext", "StepEntry", "ModelRunner", "parse_dtype"]
+__all__ = ["StepContext", "StepEntry", "ModelRunner", "parse_dtype", "prepare_step"]

@@ -71,9 +71,21 @@ class StepStager:
         self._events = [None, None]
         self._dev = torch.empty(self._cap, dtype=torch.int32, device=self.device)
 
-    def stage(self, arrays: Sequence[np.ndarray]) -> List[torch.Tensor]:
+    @staticmethod
+    def layout(shapes: Sequence[Sequence[int]]) -> int:
+        """int32 elements that arrays of these shapes occupy when staged."""
+        total = 0
+        for shp in shapes:
+            n = 1
+            for d in shp:
+                n *= int(d)
+            total += (n + 3) // 4 * 4
+        return total
+
+    def stage(self, arrays: Sequence[np.ndarray], dest: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
         """Copy the int32 arrays to the device; returns one device view per array.
-        Each array starts on a 16-byte boundary."""
+        Each array starts on a 16-byte boundary.  `dest`, if given, is the device buffer
+        that receives them (it must be large enough); otherwise the stager's own."""
         offsets, total = [], 0
         for a in arrays:
             offsets.append(total)
@@ -89,12 +101,17 @@ class StepStager:
         hv = host.numpy()
         for a, off in zip(arrays, offsets):
             hv[off:off + a.size] = a.reshape(-1)
-        self._dev[:total].copy_(host[:total], non_blocking=True)
+        dev = self._dev if dest is None else dest
+        if dev.numel() < total:
+            raise ValueError(f"staging destination holds {dev.numel()} elements, {total} are needed")
+        dev[:total].copy_(host[:total], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record(torch.cuda.current_stream(self.device))
         self._events[i] = ev
-        return [self._dev[off:off + a.size].view(*a.shape) for a, off in zip(arrays, offsets)]
+        self.last_elements = total
+        return [dev[off:off + a.size].view(*a.shape) for a, off in zip(arrays, offsets)]
 
     @property
     def bytes_last(self) -> int:
-        return self._cap * 4
+        """Bytes the last staged step sent to the device."""
+        return getattr(self, "last_elements", 0) * 4

@@ -135,9 +135,16 @@ class Engine:
         if not plan.work:
             return []
         entries = [StepEntry(w.request.id, w.tokens, [w.count - 1] if w.samples else []) for w in plan.work]
-        logits = self.runner.step(entries)
         sampling_work = [w for w in plan.work if w.samples]
-        sampled = self._sample(logits, sampling_work)
+        if (self.sampler is not None and sampling_work
+                and all(w.request.params.uses_plain_greedy() for w in sampling_work)):
+            # the arg-max rides in the step's own launch sequence; only ids come back
+            _, drawn = self.runner.step(entries, draw_greedy=True)
+            ids = self.sampler.read_ids(drawn)
+            sampled = {w.request.id: t for w, t in zip(sampling_work, ids)}
+        else:
+            logits = self.runner.step(entries)
+            sampled = self._sample(logits, sampling_work)
         finished = {r.id for r in self.scheduler.complete(plan, sampled)}
         out = []
         for w in sampling_work:

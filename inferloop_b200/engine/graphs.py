@@ -1,0 +1,134 @@
+"""Decode steps as replayed CUDA graphs.
+
+A step in which every request brings exactly one token is launch-bound when run kernel
+by kernel.  Such steps are recorded once per batch-size bucket and replayed: the batch's
+integer arrays live at fixed device addresses that are overwritten before each replay, and
+every kernel reads the batch from there.  The reference does the same with one resident
+decode graph whose control row is rewritten on-stream before each replay
+(crates/backend/cuda/src/resident/program.rs; metadata row:
+crates/backend/cuda-kernels/src/tile/state/metadata_kernels.rs:87-101); its fixed graph
+widths are the buckets here.  A step smaller than its bucket is padded with dummy
+sequences that hold no pages.
+
+A recorded graph also holds the addresses of the model's scratch buffers; when one of
+them has been reallocated since (a larger prompt step grew it), the graph is recorded
+again.
+"""
+from __future__ import annotations
+
+import gc
+import weakref
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..csrc import ops
+from .batch import StepContext, StepEntry, StepStager
+
+BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+
+def bucket_for(n: int) -> Optional[int]:
+    for b in BUCKETS:
+        if n <= b:
+            return b
+    return None
+
+
+@dataclass
+class _Recorded:
+    graph: torch.cuda.CUDAGraph
+    ints: torch.Tensor                 # the batch arrays, fixed address
+    ctx: StepContext                   # views into `ints`
+    logits: torch.Tensor
+    workspace_generation: int
+    kernels: int                       # launches recorded
+    drawn: Optional[torch.Tensor] = None
+
+
+class DecodeGraphs:
+    def __init__(self, runner, max_blocks: int) -> None:
+        self._runner = weakref.ref(runner)     # the runner owns this object, not the reverse
+        self.max_blocks = int(max_blocks)
+        self._recorded: Dict[tuple, _Recorded] = {}
+        self.replays = 0
+
+    @property
+    def runner(self):
+        r = self._runner()
+        if r is None:
+            raise RuntimeError("the model runner of these graphs is gone")
+        return r
+
+    @staticmethod
+    def eligible(entries: Sequence[StepEntry]) -> bool:
+        return all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+
+    def _shapes(self, bucket: int) -> List[tuple]:
+        groups = len(self.runner.cache.groups)
+        return [(bucket,), (bucket,), (bucket,), (bucket + 1,), (bucket,), (bucket,), (bucket,)] + \
+               [(bucket, self.max_blocks)] * groups
+
+    def _prepare(self, entries: Sequence[StepEntry], bucket: int, ints: torch.Tensor) -> StepContext:
+        from .runner import prepare_step
+        r = self.runner
+        return prepare_step(r.cache, r.stager, entries, r.spec.vocab_size, r.spec.max_positions,
+                            pad_seqs=bucket - len(entries), max_blocks=self.max_blocks, dest=ints)
+
+    def _record(self, key: tuple, entries: Sequence[StepEntry], bucket: int, with_argmax: bool) -> _Recorded:
+        r = self.runner
+        ints = torch.zeros(StepStager.layout(self._shapes(bucket)), dtype=torch.int32, device=r.device)
+        ctx = self._prepare(entries, bucket, ints)
+        drawn = torch.zeros(bucket, dtype=torch.int32, device=r.device) if with_argmax else None
+        # Once eagerly: builds kernels, sizes every scratch buffer, and does this step's work.
+        logits = r.model.forward(ctx, r.cache)
+        if with_argmax:
+            ops.argmax(logits, drawn, None)
+        torch.cuda.current_stream(r.device).synchronize()
+        generation = r.ctx.workspace.generation
+        graph = torch.cuda.CUDAGraph()
+        before = ops.LAUNCHES
+        ctx.position_tables.clear()
+        # Nothing may be destroyed on the device while the recording is open: an older
+        # graph released by the garbage collector in that window invalidates it.
+        gc.collect()
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                logits = r.model.forward(ctx, r.cache)
+                if with_argmax:
+                    ops.argmax(logits, drawn, None)
+        finally:
+            if gc_was_on:
+                gc.enable()
+        kernels = ops.LAUNCHES - before
+        if r.ctx.workspace.generation != generation:
+            raise RuntimeError("a scratch buffer was reallocated while a graph was recorded")
+        rec = _Recorded(graph, ints, ctx, logits, generation, kernels, drawn)
+        self._recorded[key] = rec
+        return rec
+
+    def step(self, entries: Sequence[StepEntry], with_argmax: bool = False):
+        """Run a decode-only step.  Returns (logits[:n], drawn[:n] or None, kernels
+        launched).  The very first step of a bucket runs eagerly while it is recorded."""
+        n = len(entries)
+        bucket = bucket_for(n)
+        if bucket is None:
+            raise ValueError(f"{n} sequences exceed the largest decode bucket {BUCKETS[-1]}")
+        key = (bucket, with_argmax)
+        rec = self._recorded.get(key)
+        if rec is not None and rec.workspace_generation != self.runner.ctx.workspace.generation:
+            del self._recorded[key]
+            rec = None
+        if rec is None:
+            rec = self._record(key, entries, bucket, with_argmax)     # ran the step eagerly
+        else:
+            self._prepare(entries, bucket, rec.ints)
+            rec.graph.replay()
+            self.replays += 1
+        return rec.logits[:n], (rec.drawn[:n] if with_argmax else None), rec.kernels
+
+    def recorded(self, n: int, with_argmax: bool) -> Optional[_Recorded]:
+        return self._recorded.get((bucket_for(n), with_argmax))

@@ -69,8 +69,14 @@ def step_fits(cache: CacheManager, entries: Sequence[StepEntry]) -> bool:
 
 
 def prepare_step(cache: CacheManager, stager: StepStager, entries: Sequence[StepEntry],
-                 vocab_size: int, max_positions: int) -> StepContext:
-    """Take pages for the step (all entries or none) and stage its arrays."""
+                 vocab_size: int, max_positions: int, pad_seqs: int = 0,
+                 max_blocks: Optional[int] = None, dest: Optional[torch.Tensor] = None) -> StepContext:
+    """Take pages for the step (all entries or none) and stage its arrays.
+
+    `pad_seqs` appends that many one-token dummy sequences (token 0, position 0, no pages,
+    slot -1): their cache writes are dropped and their rows are never read, which lets a
+    step of any size run in a launch shape made for a larger one.  `max_blocks` fixes the
+    width of the block tables; `dest` receives the arrays instead of the stager's buffer."""
     if not entries:
         raise ValueError("a step needs at least one entry")
     seen = set()
@@ -105,14 +111,14 @@ def prepare_step(cache: CacheManager, stager: StepStager, entries: Sequence[Step
             cache.release(r)
         raise
 
-    S = len(entries)
-    T = sum(len(e.tokens) for e in entries)
-    tokens = np.empty(T, np.int32)
-    positions = np.empty(T, np.int32)
-    seq_of = np.empty(T, np.int32)
+    S = len(entries) + pad_seqs
+    T = sum(len(e.tokens) for e in entries) + pad_seqs
+    tokens = np.zeros(T, np.int32)
+    positions = np.zeros(T, np.int32)
+    seq_of = np.zeros(T, np.int32)
     cu_q = np.zeros(S + 1, np.int32)
-    kv_len = np.empty(S, np.int32)
-    slots = np.empty(S, np.int32)
+    kv_len = np.zeros(S, np.int32)
+    slots = np.full(S, -1, np.int32)
     rows: List[int] = []
     q_start, q_len = [], []
     off = 0
@@ -129,8 +135,17 @@ def prepare_step(cache: CacheManager, stager: StepStager, entries: Sequence[Step
         q_start.append(cur)
         q_len.append(n)
         off += n
+    for s in range(len(entries), S):          # padding
+        seq_of[off] = s
+        cu_q[s + 1] = off + 1
+        rows.append(off)
+        off += 1
     reqs = [e.request for e in entries]
-    max_blocks = (cache.max_blocks(reqs) + 7) // 8 * 8
+    need_blocks = cache.max_blocks(reqs)
+    if max_blocks is None:
+        max_blocks = (need_blocks + 7) // 8 * 8
+    elif need_blocks > max_blocks:
+        raise ValueError(f"a request holds {need_blocks} blocks, the table is {max_blocks} wide")
     tables = []
     for g in cache.groups:
         tb = np.full((S, max_blocks), -1, np.int32)
@@ -139,21 +154,22 @@ def prepare_step(cache: CacheManager, stager: StepStager, entries: Sequence[Step
             tb[s, :len(row)] = row
         tables.append(tb)
     logit_rows = np.asarray(rows, dtype=np.int32)
-    staged = stager.stage([tokens, positions, seq_of, cu_q, kv_len, slots, logit_rows] + tables)
+    staged = stager.stage([tokens, positions, seq_of, cu_q, kv_len, slots, logit_rows] + tables, dest)
     return StepContext(
         n_tokens=T, n_seqs=S, n_logit_rows=len(rows),
         tokens=staged[0], positions=staged[1], seq_of_token=staged[2], cu_q=staged[3],
         kv_len=staged[4], slots=staged[5], logit_rows=staged[6],
         block_tables={g.index: staged[7 + i] for i, g in enumerate(cache.groups)},
         requests=reqs, h_q_start=q_start, h_q_len=q_len, h_kv_len=[int(x) for x in kv_len],
-        h_slots=[int(x) for x in slots], max_q_len=max(q_len), max_kv_len=int(kv_len.max()),
+        h_slots=[int(x) for x in slots[:len(entries)]], max_q_len=max(q_len), max_kv_len=int(kv_len.max()),
         decode_only=all(n == 1 for n in q_len))
 
 
 
 class ModelRunner:
     def __init__(self, spec: ModelSpec, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype,
-                 device: torch.device, page_size: int, num_pages: int, max_requests: int) -> None:
+                 device: torch.device, page_size: int, num_pages: int, max_requests: int,
+                 cuda_graphs: bool = True) -> None:
         self.spec = spec
         self.dtype = dtype
         self.device = device
@@ -165,6 +181,13 @@ class ModelRunner:
         self.stager = StepStager(device)
         self.steps_run = 0
         self.tokens_run = 0
+        self.kernels_last_step = 0
+        # Decode-only steps replay recorded graphs when every part reads its batch from
+        # device memory (a part that loops over host-side batch facts cannot be replayed).
+        self.graphs = None
+        if cuda_graphs and all(b.graph_safe for b in self.model.blocks):
+            from .graphs import DecodeGraphs
+            self.graphs = DecodeGraphs(self, -(-spec.max_positions // page_size))
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -206,6 +229,9 @@ class ModelRunner:
         torch.cuda.empty_cache()
         self.cache = CacheManager(self.model.cache_needs(), page_size, num_pages, max_requests,
                                   dtype=self.dtype, device=self.device, run_order=self.spec.run_order)
+        if self.graphs is not None:          # recorded graphs point into the old cache
+            from .graphs import DecodeGraphs
+            self.graphs = DecodeGraphs(self, -(-self.spec.max_positions // page_size))
 
     # ------------------------------------------------------------------ requests
     def begin(self, request: Hashable) -> None:
@@ -226,14 +252,29 @@ class ModelRunner:
         """Take pages for the step (all entries or none) and stage its arrays."""
         return prepare_step(self.cache, self.stager, entries, self.spec.vocab_size, self.spec.max_positions)
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], draw_greedy: bool = False):
         """Run the entries as one batch; returns logits [wanted, vocab] (32-bit, on the
         device, in the order of the entries and of each entry's `want`).  The tensor is a
-        scratch buffer: it is valid until the next step."""
-        ctx = self.prepare(entries)
-        logits = self.model.forward(ctx, self.cache)
+        scratch buffer: it is valid until the next step.  With `draw_greedy` the arg-max
+        of every row is computed in the same launch sequence and (logits, ids) is
+        returned, ids being an int32 device tensor."""
+        from ..csrc import ops
+        before = ops.LAUNCHES
+        drawn = None
+        if self.graphs is not None and self.graphs.eligible(entries) and len(entries) <= 256:
+            logits, drawn, kernels = self.graphs.step(entries, with_argmax=draw_greedy)
+            self.kernels_last_step = kernels
+            n_tokens = len(entries)
+        else:
+            ctx = self.prepare(entries)
+            logits = self.model.forward(ctx, self.cache)
+            n_tokens = ctx.n_tokens
+            if draw_greedy and logits.shape[0]:
+                drawn = self.ctx.workspace.buffer("runner.drawn", (logits.shape[0],), torch.int32)
+                ops.argmax(logits, drawn, None)
+            self.kernels_last_step = ops.LAUNCHES - before
         for e in entries:
             self.cache.commit(e.request, self.cache.length(e.request) + len(e.tokens))
         self.steps_run += 1
-        self.tokens_run += ctx.n_tokens
-        return logits
+        self.tokens_run += n_tokens
+        return (logits, drawn) if draw_greedy else logits

@@ -28,6 +28,7 @@ from .linear import linear
 
 
 class GQAttention(Mixer):
+    graph_safe = True
     def __init__(self, spec, ctx, prefix: str = "") -> None:
         super().__init__(spec, ctx, prefix)
         self.hidden = int(spec["hidden_size"])

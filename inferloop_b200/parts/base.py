@@ -90,6 +90,11 @@ class CacheNeeds:
 
 
 class Part:
+    # True when forward() only launches kernels that read the batch from device memory,
+    # so that a recorded launch sequence can be replayed for another batch of the same
+    # shape.  A part that loops over host-side batch facts must leave this False.
+    graph_safe = False
+
     def __init__(self, spec: PartSpec, ctx: BuildContext, prefix: str = "") -> None:
         self.spec = spec
         self.ctx = ctx

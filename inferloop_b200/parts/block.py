@@ -26,6 +26,10 @@ class PreNormBlock(Block):
         self.mixer = registry.build("mixer", layer.mixer, ctx, mixer_prefix)
         self.ffn = registry.build("feed_forward", layer.feed_forward, ctx, ffn_prefix)
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(p.graph_safe for p in (self.norm1, self.mixer, self.norm2, self.ffn))
+
     def declare_weights(self) -> List[WeightDecl]:
         return (self.norm1.declare_weights() + self.mixer.declare_weights()
                 + self.norm2.declare_weights() + self.ffn.declare_weights())

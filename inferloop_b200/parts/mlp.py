@@ -19,6 +19,7 @@ from .registry import register
 
 
 class SwiGLU(FeedForward):
+    graph_safe = True
     def __init__(self, spec, ctx, prefix: str = "") -> None:
         super().__init__(spec, ctx, prefix)
         self.hidden = int(spec["hidden_size"])

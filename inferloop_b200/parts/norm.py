@@ -14,6 +14,7 @@ from .registry import register
 
 
 class RMSNorm(Norm):
+    graph_safe = True
     """spec: eps; width is given by the owner through `prefix`-named weight of `width`."""
 
     def __init__(self, spec, ctx, prefix: str = "", width: int = 0, name: str = "weight") -> None:

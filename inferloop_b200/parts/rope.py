@@ -21,6 +21,7 @@ from .registry import register
 
 
 class RopeNeox(PositionEncoding):
+    graph_safe = True
     def __init__(self, spec, ctx, prefix: str = "") -> None:
         super().__init__(spec, ctx, prefix)
         self.theta = float(spec["theta"])
@@ -52,6 +53,7 @@ class RopeNeox(PositionEncoding):
 
 
 class NoPosition(PositionEncoding):
+    graph_safe = True
     """A mixer that wants no position signal."""
 
     def table(self, step):

@@ -56,3 +56,13 @@ class DeviceSampler:
         if any(vals[rows:]):
             raise ValueError("invalid sampling logits (a non-finite value)")
         return vals[:rows]
+
+    def read_ids(self, drawn: torch.Tensor) -> List[int]:
+        """Token ids that a step already drew on the device (synchronises)."""
+        rows = drawn.numel()
+        if rows > self._cap:
+            self._grow(max(rows, 2 * self._cap))
+        self.h_out[:rows].copy_(drawn, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        self.d2h_bytes_last = rows * 4
+        return self.h_out[:rows].tolist()
