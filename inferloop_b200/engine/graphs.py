@@ -132,3 +132,54 @@ class DecodeGraphs:
 
     def recorded(self, n: int, with_argmax: bool) -> Optional[_Recorded]:
         return self._recorded.get((bucket_for(n), with_argmax))
+
+    def run_greedy(self, entries: Sequence[StepEntry], n_steps: int) -> torch.Tensor:
+        """`n_steps` greedy decode steps back to back without a host round trip: each
+        step's arg-max becomes the next step's token on the device.  `entries` hold each
+        request's next token.  Pages for all steps are taken up front.  Returns the drawn
+        ids [n_steps, len(entries)] (int32, device); the requests' cache lengths advance by
+        n_steps."""
+        r = self.runner
+        n = len(entries)
+        if not self.eligible(entries):
+            raise ValueError("run_greedy takes one token per request, logits wanted")
+        bucket = bucket_for(n)
+        if bucket is None:
+            raise ValueError(f"{n} sequences exceed the largest decode bucket")
+        for e in entries:                       # all pages first, or none
+            if not r.cache.has(e.request):
+                raise ValueError(f"request {e.request!r} is not live")
+        need: Dict[int, int] = {}
+        for e in entries:
+            for g, k in r.cache.pages_needed(e.request, r.cache.length(e.request) + n_steps).items():
+                need[g] = need.get(g, 0) + k
+        free = r.cache.free_pages()
+        if any(need.get(g, 0) > free[g] for g in free):
+            from ..cache.pages import OutOfPages
+            raise OutOfPages(f"{n_steps} decode steps of {n} requests need {need}, free {free}")
+        for e in entries:
+            r.cache.ensure(e.request, r.cache.length(e.request) + n_steps)
+        out = torch.empty((n_steps, bucket), dtype=torch.int32, device=r.device)
+        key = (bucket, True)
+        rec = self._recorded.get(key)
+        if rec is not None and rec.workspace_generation != r.ctx.workspace.generation:
+            del self._recorded[key]
+            rec = None
+        first = 0
+        if rec is None:
+            rec = self._record(key, entries, bucket, True)      # step 0 ran eagerly
+            out[0].copy_(rec.drawn)
+            ops.decode_advance(rec.ctx.tokens, rec.ctx.positions, rec.ctx.kv_len, rec.drawn, n)
+            first = 1
+        else:
+            self._prepare(entries, bucket, rec.ints)
+        for i in range(first, n_steps):
+            rec.graph.replay()
+            out[i].copy_(rec.drawn)
+            ops.decode_advance(rec.ctx.tokens, rec.ctx.positions, rec.ctx.kv_len, rec.drawn, n)
+        self.replays += n_steps - first
+        for e in entries:
+            r.cache.commit(e.request, r.cache.length(e.request) + n_steps)
+        r.steps_run += n_steps
+        r.tokens_run += n_steps * n
+        return out[:, :n]
