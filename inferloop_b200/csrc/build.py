@@ -31,6 +31,7 @@ NVCC_FLAGS = [
 MODULES: Dict[str, List[str]] = {
     "elementwise": [],
     "gemm_simt": [],
+    "gemm_tcgen05": [],
     "qk_norm_rope": [],
     "attention_simple": [],
     "sampling": [],

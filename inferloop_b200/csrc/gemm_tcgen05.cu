@@ -1,0 +1,463 @@
+// bfloat16 matrix product on the 5th-generation tensor cores of sm_100a:
+//     out[M,N] (+)= A[M,K] * W[N,K]^T (+ bias[N]),  32-bit accumulation in tensor memory.
+//
+// One kernel serves decode-shaped (few tokens) and prefill-shaped (many tokens) products.
+// tcgen05.mma computes D[128 x BN] = X[128 x K] * Y[BN x K]^T with both operands K-major in
+// shared memory.  With few tokens the operands are swapped: X is a 128-row tile of the
+// WEIGHT and Y the (padded) tokens, so every tensor-core row does useful work and the
+// kernel is a pure stream of weight tiles; with many tokens X is a 128-token tile and Y a
+// tile of BN weight rows.
+//
+// Per CTA (192 threads), one output tile and one contiguous range of K:
+//   warp 0      one lane issues the TMA loads (cp.async.bulk.tensor, 128-byte swizzle,
+//               no cluster multicast) into a ring of STAGES buffers;
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (4 per 64-wide K
+//               block) and tcgen05.commit to hand buffers back and to signal the end;
+//   warps 2-5   read the accumulator with tcgen05.ld and write the result.
+// When K is split over several CTAs (decode shapes have too few tiles to fill 148 SMs),
+// each CTA stores its partial tile to a 32-bit workspace and takes a ticket; the CTA that
+// takes the last ticket of a tile adds the partials in split order, so the sum does not
+// depend on which CTA finished first, and writes the result.  There is no spin-wait on
+// another CTA anywhere.  Every mbarrier wait is bounded: on expiry the kernel raises a
+// flag in global memory, drains what it armed, frees its tensor memory and returns.
+//
+// The reference computes these products with JIT-compiled tile kernels that target no
+// architecture in particular, or with cuBLAS (crates/backend/cuda-kernels/src/tile/
+// projection/prefill_gemm_kernels.rs:11-69, small_gemm_kernels.rs:10-29;
+// crates/backend/cuda/src/device/cublaslt.rs:38-42).
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+#include "common.cuh"
+
+using namespace ilb;
+
+namespace {
+
+constexpr int kBlockK = 64;            // bf16 elements per K block = one 128-byte swizzle row
+constexpr int kTileX = 128;            // rows of the X operand = MMA M
+constexpr int kThreads = 192;
+constexpr uint32_t kWaitLimit = 1u << 22;
+
+enum Epilogue : int { kStore = 0, kAccumulate = 1 };
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kWaitLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+
+// K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, 8-row
+// groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// D = 32-bit, A and B = bfloat16, both K-major, N and M encoded.
+__host__ __device__ constexpr uint32_t instr_desc(int mma_m, int mma_n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(mma_n >> 3) << 17) | ((uint32_t)(mma_m >> 4) << 24);
+}
+
+__device__ __forceinline__ void tmem_load_32(uint32_t addr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(addr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_load_16(uint32_t addr, float (&v)[32]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(addr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct Params {
+  void* out;                 // [M, N], bf16 or f32
+  const float* bias;         // [N] or null
+  float* partial;            // split-K workspace: [tiles][splits][BN][128] floats
+  int* tickets;              // one counter per tile, zero between launches
+  int* error_flag;           // set to 1 when a bounded wait ran out
+  int M, N, K, ldo;
+  int x_rows, y_rows;        // extents of the X and Y operands (N, M when swapped, else M, N)
+  int k_blocks;              // ceil(K / 64)
+  int splits;                // CTAs per tile along K
+  int epilogue;              // Epilogue
+  int out_f32;               // element type of out
+};
+
+// One (x tile, y tile, split) per CTA:  blockIdx.x = x tile, blockIdx.y = y tile, blockIdx.z = split.
+template <int BN, int STAGES, bool SWAP>
+__global__ void __launch_bounds__(kThreads)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, const Params p) {
+  constexpr uint32_t kBytesX = kTileX * kBlockK * 2;
+  constexpr uint32_t kBytesY = BN * kBlockK * 2;
+  constexpr uint32_t kStageBytes = kBytesX + kBytesY;          // multiples of 1024
+  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;            // power of two >= 32
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // dynamic shared memory is only 16-byte aligned by contract; align by hand
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * kStageBytes);
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, done_bar = empty0 + 8 * STAGES;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * STAGES + 1);
+  volatile int* flags = reinterpret_cast<volatile int*>(bars + 2 * STAGES + 2);   // [0] = failed, [1] = last ticket
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int x0 = blockIdx.x * kTileX, y0 = blockIdx.y * BN;
+  const int split = blockIdx.z;
+  // K blocks of this split: an even share, the first `rem` splits one more
+  const int share = p.k_blocks / p.splits, rem = p.k_blocks % p.splits;
+  const int kb_begin = split * share + (split < rem ? split : rem);
+  const int kb_count = share + (split < rem ? 1 : 0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    mbar_init(done_bar, 1);
+    flags[0] = 0; flags[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int armed = 0;
+      bool ok = true;
+      for (int i = 0; i < kb_count && ok; ++i) {
+        const int s = i % STAGES;
+        if (i >= STAGES) ok = mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1);
+        if (!ok) break;
+        const uint32_t dst = base + s * kStageBytes;
+        mbar_expect_tx(full0 + 8 * s, kStageBytes);
+        tma_load_2d(dst, &map_x, full0 + 8 * s, (kb_begin + i) * kBlockK, x0);
+        tma_load_2d(dst + kBytesX, &map_y, full0 + 8 * s, (kb_begin + i) * kBlockK, y0);
+        armed = i + 1;
+      }
+      if (!ok) { flags[0] = 1; if (p.error_flag) *p.error_flag = 1; }
+      (void)armed;
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(kTileX, BN);
+      bool ok = true;
+      for (int i = 0; i < kb_count && ok; ++i) {
+        const int s = i % STAGES;
+        ok = mbar_wait(full0 + 8 * s, (i / STAGES) & 1);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t a = base + s * kStageBytes;
+        const uint64_t da = smem_desc(a), db = smem_desc(a + kBytesX);
+#pragma unroll
+        for (int k = 0; k < kBlockK / 16; ++k)
+          mma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        tcgen05_commit(empty0 + 8 * s);       // the buffer is free once these MMAs have read it
+      }
+      if (!ok) { flags[0] = 1; if (p.error_flag) *p.error_flag = 1; }
+      tcgen05_commit(done_bar);               // arrives when every MMA issued so far is complete
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5)
+    const int quad = warp & 3;                // tensor-memory lanes 32*quad .. 32*quad+31
+    const int xr = x0 + quad * 32 + lane;     // this thread's row of the X operand
+    bool ok = mbar_wait(done_bar, 0);
+    tcgen05_fence_after();
+    if (!ok) { flags[0] = 1; if (p.error_flag) *p.error_flag = 1; }
+    const bool failed = flags[0] != 0;
+    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+    float* my_partial = p.partial + ((size_t)tile * p.splits + split) * (size_t)(BN * kTileX);
+
+    constexpr int CH = BN < 32 ? BN : 32;     // columns per tensor-memory read
+    bool last = p.splits == 1;
+    if (p.splits > 1 && !failed) {
+      // 1. park this split's tile: [col][row] so that a warp writes 128 contiguous bytes
+      for (int c0 = 0; c0 < BN; c0 += CH) {
+        float v[32];
+        if (CH == 32) tmem_load_32(taddr + c0, v); else tmem_load_16(taddr + c0, v);
+#pragma unroll
+        for (int c = 0; c < CH; ++c) my_partial[(size_t)(c0 + c) * kTileX + quad * 32 + lane] = v[c];
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        const int t = atomicAdd(p.tickets + tile, 1);
+        flags[1] = (t == p.splits - 1) ? 1 : 0;
+        if (t == p.splits - 1) p.tickets[tile] = 0;          // ready for the next launch
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      last = flags[1] != 0;
+      if (last) __threadfence();
+    }
+    if (last && !failed) {
+      const float* tile_partials = p.partial + (size_t)tile * p.splits * (size_t)(BN * kTileX);
+      for (int c0 = 0; c0 < BN; c0 += CH) {
+        float v[32];
+        if (p.splits == 1) {
+          if (CH == 32) tmem_load_32(taddr + c0, v); else tmem_load_16(taddr + c0, v);
+        } else {
+#pragma unroll
+          for (int c = 0; c < CH; ++c) v[c] = 0.f;
+          for (int s = 0; s < p.splits; ++s) {               // fixed order: split 0, 1, 2, ...
+            const float* src = tile_partials + (size_t)s * (BN * kTileX) + quad * 32 + lane;
+#pragma unroll
+            for (int c = 0; c < CH; ++c) v[c] += __ldcg(src + (size_t)(c0 + c) * kTileX);
+          }
+        }
+        if (SWAP) {
+          // X rows are output features n = xr; columns are tokens m = y0 + c
+          if (xr < p.N) {
+            const float b = p.bias ? p.bias[xr] : 0.f;
+#pragma unroll
+            for (int c = 0; c < CH; ++c) {
+              const int m = y0 + c0 + c;
+              if (m < p.M) {
+                const size_t o = (size_t)m * p.ldo + xr;
+                float r = v[c] + b;
+                if (p.out_f32) {
+                  float* dst = (float*)p.out + o;
+                  if (p.epilogue == kAccumulate) r += *dst;
+                  *dst = r;
+                } else {
+                  ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(r);
+                }
+              }
+            }
+          }
+        } else {
+          // X rows are tokens m = xr; columns are output features n = y0 + c
+          if (xr < p.M) {
+#pragma unroll
+            for (int c = 0; c < CH; ++c) {
+              const int n = y0 + c0 + c;
+              if (n < p.N) {
+                const size_t o = (size_t)xr * p.ldo + n;
+                float r = v[c] + (p.bias ? p.bias[n] : 0.f);
+                if (p.out_f32) {
+                  float* dst = (float*)p.out + o;
+                  if (p.epilogue == kAccumulate) r += *dst;
+                  *dst = r;
+                } else {
+                  ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(r);
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr; int rows, cols, ld, box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = std::hash<const void*>()(k.ptr);
+    for (int v : {k.rows, k.cols, k.ld, k.box_rows}) h = h * 1000003u ^ std::hash<int>()(v);
+    return h;
+  }
+};
+
+// A [rows, cols] bf16 matrix with leading dimension ld (elements); box = [box_rows, 64].
+int make_map(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  const MapKey key{ptr, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> g(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return 0; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail("gemm_tc: cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("gemm_tc: cuTensorMapEncodeTiled failed with code %d (rows %d cols %d ld %d)", (int)r, rows, cols, ld);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return 0;
+}
+
+template <int BN, int STAGES, bool SWAP>
+int launch(const CUtensorMap& mx, const CUtensorMap& my, const Params& p, dim3 grid, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)STAGES * (kTileX * kBlockK * 2 + BN * kBlockK * 2) + 1024 + (2 * STAGES + 3) * 8;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail("gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  gemm_tc_kernel<BN, STAGES, SWAP><<<grid, kThreads, smem, stream>>>(mx, my, p);
+  return check_launch("gemm_tc");
+}
+
+}  // namespace
+
+// Elements of 32-bit workspace and tickets a call may need, for the caller to allocate.
+ILB_EXPORT long long ilb_gemm_tc_workspace_floats() { return 8ll << 20; }   // 32 MiB
+ILB_EXPORT int ilb_gemm_tc_max_tickets() { return 4096; }
+
+// What the kernel can take: bf16 operands, K and the leading dimensions multiples of 8
+// (16-byte rows for TMA), 16-byte aligned bases.
+ILB_EXPORT int ilb_gemm_tc_supported(int M, int N, int K, int lda, int ldw) {
+  return (M > 0 && N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0) ? 1 : 0;
+}
+
+ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void* out, int out_f32,
+                           int M, int N, int K, int lda, int ldw, int ldo, int accumulate,
+                           float* workspace, long long workspace_floats, int* tickets, int n_tickets,
+                           int* error_flag, int force_splits, cudaStream_t stream) {
+  ILB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
+  ILB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
+              "gemm_tc: K (%d) and the leading dimensions (%d, %d) must be multiples of 8", K, lda, ldw);
+  ILB_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
+  ILB_REQUIRE(!accumulate || out_f32, "gemm_tc: accumulation needs a 32-bit output");
+  ILB_REQUIRE(ldo >= N, "gemm_tc: output leading dimension too small");
+
+  Params p{};
+  p.out = out; p.bias = bias; p.partial = workspace; p.tickets = tickets; p.error_flag = error_flag;
+  p.M = M; p.N = N; p.K = K; p.ldo = ldo;
+  p.k_blocks = (K + kBlockK - 1) / kBlockK;
+  p.epilogue = accumulate ? kAccumulate : kStore;
+  p.out_f32 = out_f32;
+
+  const bool swap = M <= 128;
+  int bn;
+  if (swap) bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+  else bn = N >= 256 ? 256 : 128;
+  const int x_rows = swap ? N : M, y_rows = swap ? M : N;
+  p.x_rows = x_rows; p.y_rows = y_rows;
+  const int tiles_x = (x_rows + kTileX - 1) / kTileX, tiles_y = (y_rows + bn - 1) / bn;
+  const int tiles = tiles_x * tiles_y;
+
+  // Split K until roughly two CTAs per SM are in flight, keeping at least 4 K blocks each.
+  int splits = 1;
+  if (force_splits > 0) {
+    splits = force_splits;
+  } else if (tiles < 2 * 148) {
+    splits = (2 * 148 + tiles - 1) / tiles;
+    const int cap = p.k_blocks / 4 > 0 ? p.k_blocks / 4 : 1;
+    if (splits > cap) splits = cap;
+    if (splits > 16) splits = 16;
+  }
+  if (splits > p.k_blocks) splits = p.k_blocks;
+  if (splits > 1) {
+    const long long need = (long long)tiles * splits * bn * kTileX;
+    if (workspace == nullptr || tickets == nullptr || need > workspace_floats || tiles > n_tickets) splits = 1;
+  }
+  p.splits = splits;
+
+  CUtensorMap mx, my;
+  const void* X = swap ? W : A;
+  const void* Y = swap ? A : W;
+  const int ldx = swap ? ldw : lda, ldy = swap ? lda : ldw;
+  if (make_map(&mx, X, x_rows, K, ldx, kTileX)) return -1;
+  if (make_map(&my, Y, y_rows, K, ldy, bn)) return -1;
+  dim3 grid(tiles_x, tiles_y, splits);
+  ILB_REQUIRE(tiles_y <= 65535 && splits <= 65535, "gemm_tc: grid too large");
+
+  if (swap) {
+    switch (bn) {
+      case 16: return launch<16, 8, true>(mx, my, p, grid, stream);
+      case 32: return launch<32, 8, true>(mx, my, p, grid, stream);
+      case 64: return launch<64, 6, true>(mx, my, p, grid, stream);
+      default: return launch<128, 4, true>(mx, my, p, grid, stream);
+    }
+  }
+  if (bn == 256) return launch<256, 4, false>(mx, my, p, grid, stream);
+  return launch<128, 5, false>(mx, my, p, grid, stream);
+}
+
+ILB_DEFINE_LAST_ERROR()

@@ -221,12 +221,65 @@ def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, uniform:
 
 
 # --------------------------------------------------------------------------- tensor-core GEMM
+class _TcState:
+    """Per-device scratch of the tensor-core GEMM: split-K workspace, tile tickets (zero
+    between launches) and the flag a kernel raises when a bounded wait runs out."""
+
+    def __init__(self, device: torch.device) -> None:
+        lib = load_module("gemm_tcgen05")
+        lib.ilb_gemm_tc_workspace_floats.restype = ctypes.c_longlong
+        self.floats = int(lib.ilb_gemm_tc_workspace_floats())
+        self.n_tickets = int(lib.ilb_gemm_tc_max_tickets())
+        self.workspace = torch.empty(self.floats, dtype=torch.float32, device=device)
+        self.tickets = torch.zeros(self.n_tickets, dtype=torch.int32, device=device)
+        self.error = torch.zeros(1, dtype=torch.int32, device=device)
+
+
+_TC: dict = {}
+TC_ENABLED = True          # tests switch it off to exercise the fallback
+
+
+def _tc_state(device: torch.device) -> _TcState:
+    st = _TC.get(device)
+    if st is None:
+        st = _TC[device] = _TcState(device)
+    return st
+
+
 def gemm_tc_eligible(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
-    return False
+    """bfloat16 operands whose rows are multiples of 16 bytes (TMA's rule)."""
+    if not TC_ENABLED or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return False
+    K = a.shape[1]
+    return (K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and a.shape[0] > 0)
 
 
-def gemm_tc(a, w, out, bias=None, accumulate=False) -> None:
-    raise KernelError("tensor-core GEMM is not built")
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+            accumulate: bool = False, force_splits: int = 0) -> None:
+    """out (+)= a @ w.T (+ bias) on tcgen05 tensor cores (see gemm_tcgen05.cu)."""
+    _need(a, "gemm a", torch.bfloat16); _need(w, "gemm w", torch.bfloat16); _need(out, "gemm out")
+    _need(bias, "gemm bias", torch.float32)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N) or (bias is not None and bias.numel() != N):
+        raise KernelError(f"gemm: shapes do not agree: a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if accumulate and out.dtype != torch.float32:
+        raise KernelError("gemm: accumulation needs a 32-bit output")
+    st = _tc_state(a.device)
+    _call("gemm_tcgen05", "ilb_gemm_tc", _ptr(a), _ptr(w), _ptr(bias), _ptr(out),
+          _i(1 if out.dtype == torch.float32 else 0), _i(M), _i(N), _i(K), _i(a.stride(0)), _i(w.stride(0)),
+          _i(out.stride(0)), _i(1 if accumulate else 0), _ptr(st.workspace), ctypes.c_longlong(st.floats),
+          _ptr(st.tickets), _i(st.n_tickets), _ptr(st.error), _i(force_splits), _stream(out))
+
+
+def check_device_errors() -> None:
+    """Raise if a kernel gave up a bounded wait since the last check (synchronises)."""
+    for dev, st in _TC.items():
+        if int(st.error.item()) != 0:
+            st.error.zero_()
+            st.tickets.zero_()
+            raise KernelError(f"a tensor-core GEMM on {dev} gave up waiting on a barrier; its output is invalid")
 
 
 # --------------------------------------------------------------------------- attention dispatch

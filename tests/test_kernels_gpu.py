@@ -275,3 +275,60 @@ def test_kernels_refuse_what_they_cannot_do():
         o.paged_attention_simple(q, torch.empty_like(q), kc, kc, torch.zeros(1, dtype=torch.int32, device="cuda"),
                                  torch.zeros(1, dtype=torch.int32, device="cuda"),
                                  torch.zeros(1, 1, dtype=torch.int32, device="cuda"), 0, 1.0, 3, 2, 16)
+
+
+# ------------------------------------------------------------------ tensor-core GEMM
+TC_SHAPES = [(1, 128, 64), (3, 200, 72), (8, 512, 4096), (16, 4096, 1024), (17, 300, 136), (33, 96, 512),
+             (64, 1000, 1024), (65, 256, 256), (128, 384, 320), (129, 520, 264), (300, 515 * 1 + 5, 96), (512, 1024, 2048)]
+
+
+@pytest.mark.parametrize("M,N,K", TC_SHAPES)
+@pytest.mark.parametrize("out_dtype,bias,accumulate", [("bfloat16", False, False), ("float32", True, True), ("float32", False, False)])
+def test_gemm_tcgen05(M, N, K, out_dtype, bias, accumulate):
+    o = ops()
+    torch.manual_seed(M * 7 + N)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
+    b = torch.randn(N) if bias else None
+    base = torch.randn(M, N)
+    out = base.clone().cuda() if accumulate else torch.full((M, N), float("nan"), dtype=DT[out_dtype], device="cuda")
+    assert o.gemm_tc_eligible(a.cuda(), w.cuda(), out)
+    o.gemm_tc(a.cuda(), w.cuda(), out, None if b is None else b.cuda(), accumulate)
+    o.check_device_errors()
+    ref = a.double() @ w.double().T
+    if bias:
+        ref = ref + b.double()
+    if accumulate:
+        ref = ref + base.double()
+    close(out, ref, out_dtype, scale=float(ref.abs().max()), what=f"gemm_tc {M}x{N}x{K}")
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 5, 8])
+def test_gemm_tcgen05_split_k_is_deterministic_and_reusable(splits):
+    """Partials are added in split order by whichever CTA arrives last: two runs give the
+    same bits, and the tickets are back at zero for the next launch."""
+    o = ops()
+    M, N, K = 8, 640, 2048
+    a = torch.randn(M, K).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16).cuda()
+    outs = []
+    for _ in range(3):
+        out = torch.empty(M, N, device="cuda")
+        o.gemm_tc(a, w, out, force_splits=splits)
+        outs.append(out.clone())
+    o.check_device_errors()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    ref = a.double().cpu() @ w.double().cpu().T
+    close(outs[0], ref, "float32", scale=float(ref.abs().max()), what="split-k")
+    from inferloop_b200.csrc.ops import _tc_state
+    assert int(_tc_state(a.device).tickets.abs().sum()) == 0
+
+
+def test_gemm_tcgen05_refuses_unaligned_rows():
+    o = ops()
+    a = torch.randn(4, 100).to(torch.bfloat16).cuda()       # 200-byte rows: not a multiple of 16
+    w = torch.randn(32, 100).to(torch.bfloat16).cuda()
+    out = torch.empty(4, 32, device="cuda")
+    assert not o.gemm_tc_eligible(a, w, out)
+    with pytest.raises(o.KernelError, match="multiples of 8"):
+        o.gemm_tc(a, w, out)
