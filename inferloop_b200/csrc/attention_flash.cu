@@ -1,0 +1,504 @@
+// Causal grouped-query attention over the paged bfloat16 cache on tensor cores
+// (mma.sync m16n8k16, 32-bit accumulation and softmax), for prefill and for decode.
+//
+// Rows of a tile are (token, query head within its kv group) pairs of ONE kv head, so the
+// keys and values of that head are loaded once for the whole group.  Keys and values come
+// from the cache pages through the block table into shared memory with cp.async, 64 keys a
+// tile; S = Q K^T and O += P V run as m16n8k16 MMAs with the online-softmax rescaling in
+// between, all statistics in 32-bit, exponentials as exp2 of log2(e)-scaled scores.
+//
+//   prefill  one CTA = 64 rows (4 warps x 16) of one sequence and kv head; it walks the
+//            key tiles from the window start to the last row's position (double buffered).
+//   decode   one token per sequence: the keys are cut into chunks of `chunk` keys whose
+//            boundaries depend on the key index alone; one CTA per (kv head, sequence,
+//            chunk), its 4 warps take 64 keys each.  A CTA parks (max, sum, O) of its chunk
+//            in a 32-bit scratch buffer and takes a ticket; the CTA with the last ticket of
+//            a (sequence, kv head) merges the chunks in chunk order and writes the output.
+//            Nothing ever waits on another CTA.
+//
+// The reference's counterparts: `attention::decode_tiled` (prefill, query tiles on MMAs),
+// `partial_gqa_lanes` + `merge_gqa` (split-KV decode with the group's heads padded to 16
+// MMA rows) in crates/backend/cuda-kernels/src/tile/attention/
+// resident_attention_prefill_kernels.rs:378-469 and resident_attention_decode_kernels.rs:
+// 131-226, :417-451, :497-598; masked scores are dropped and rows without keys give 0
+// (:460-468 of the former).  Formula: crates/testing/cpu/reference-ops/src/kernels.rs:251-297.
+#include <math.h>
+#include "common.cuh"
+
+using namespace ilb;
+
+namespace {
+
+constexpr int kTileKeys = 64;
+constexpr int kWarps = 4;
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct Cache {
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  int page_size, num_pages, nkv;
+};
+
+// Copy keys [key0, key0 + 64) of kv head `kvh` into a [64][D + 8] tile; rows whose key is
+// outside [lo, hi) or whose page is not held are zero-filled.  NT threads take part.
+template <int D, int NT>
+__device__ __forceinline__ void load_tile(__nv_bfloat16* dst, const __nv_bfloat16* cache, const Cache& c,
+                                          const int* __restrict__ table, int max_blocks, int kvh, int key0,
+                                          int lo, int hi, int tid) {
+  constexpr int kStride = D + 8;
+  constexpr int kChunks = D / 8;                 // 16-byte pieces per row
+  for (int idx = tid; idx < kTileKeys * kChunks; idx += NT) {
+    const int r = idx / kChunks, ch = idx % kChunks;
+    const int key = key0 + r;
+    const __nv_bfloat16* src = cache;
+    int bytes = 0;
+    if (key >= lo && key < hi) {
+      const int blk = key / c.page_size;
+      const int page = blk < max_blocks ? table[blk] : -1;
+      if (page >= 0 && page < c.num_pages) {
+        src = cache + (((size_t)page * c.nkv + kvh) * c.page_size + (key % c.page_size)) * D + ch * 8;
+        bytes = 16;
+      }
+    }
+    cp_async_16(smem_u32(dst + r * kStride + ch * 8), src, bytes);
+  }
+}
+
+// State of 16 rows held by one warp: thread (g = lane / 4, t = lane % 4) owns rows g and
+// g + 8, columns 2t, 2t + 1 of every 8-wide block.
+template <int D>
+struct RowState {
+  float o[D / 8][4];
+  float m[2], l[2];
+  __device__ __forceinline__ void init() {
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
+    m[0] = m[1] = -INFINITY;
+    l[0] = l[1] = 0.f;
+  }
+};
+
+// One 64-key tile for one warp's 16 rows.  pos[2] / lo[2]: last and first visible key of
+// rows g and g + 8 (pos < lo hides everything).  `hi`: keys >= hi do not exist.
+template <int D>
+__device__ __forceinline__ void tile_step(RowState<D>& st, const uint32_t (&q)[D / 16][4],
+                                          const __nv_bfloat16* ks, const __nv_bfloat16* vs, int key0,
+                                          const int (&pos)[2], const int (&lo)[2], int hi, float scale_log2, int lane) {
+  constexpr int kStride = D + 8;
+  const int g = lane >> 2, t = lane & 3;
+  float s[8][4];
+#pragma unroll
+  for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[nb][e] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < D / 16; kk += 2) {
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb) {
+      uint32_t r0, r1, r2, r3;
+      ldmatrix_x4(smem_u32(ks + (nb * 8 + (lane & 7)) * kStride + kk * 16 + (lane >> 3) * 8), r0, r1, r2, r3);
+      mma_16816(s[nb], q[kk], r0, r1);
+      mma_16816(s[nb], q[kk + 1], r2, r3);
+    }
+  }
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int key = key0 + nb * 8 + 2 * t + (e & 1);
+      const int r = e >> 1;
+      const bool ok = key <= pos[r] && key >= lo[r] && key < hi;
+      s[nb][e] = ok ? s[nb][e] * scale_log2 : -INFINITY;
+      mx[r] = fmaxf(mx[r], s[nb][e]);
+    }
+  float corr[2], base[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    const float m_new = fmaxf(st.m[r], mx[r]);
+    base[r] = (m_new == -INFINITY) ? 0.f : m_new;
+    corr[r] = exp2f(st.m[r] - base[r]);           // -inf -> 0
+    st.m[r] = m_new;
+  }
+  float sum[2] = {0.f, 0.f};
+#pragma unroll
+  for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float p = exp2f(s[nb][e] - base[e >> 1]);
+      s[nb][e] = p;
+      sum[e >> 1] += p;
+    }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) st.l[r] = st.l[r] * corr[r] + sum[r];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) {
+    st.o[i][0] *= corr[0]; st.o[i][1] *= corr[0];
+    st.o[i][2] *= corr[1]; st.o[i][3] *= corr[1];
+  }
+#pragma unroll
+  for (int kb = 0; kb < 4; ++kb) {                 // 16 keys per step
+    uint32_t a[4];
+    a[0] = pack_bf16(s[2 * kb][0], s[2 * kb][1]);
+    a[1] = pack_bf16(s[2 * kb][2], s[2 * kb][3]);
+    a[2] = pack_bf16(s[2 * kb + 1][0], s[2 * kb + 1][1]);
+    a[3] = pack_bf16(s[2 * kb + 1][2], s[2 * kb + 1][3]);
+#pragma unroll
+    for (int nd = 0; nd < D / 16; ++nd) {
+      uint32_t r0, r1, r2, r3;
+      ldmatrix_x4_trans(smem_u32(vs + (kb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kStride + nd * 16 + (lane >> 4) * 8),
+                        r0, r1, r2, r3);
+      mma_16816(st.o[2 * nd], a, r0, r1);
+      mma_16816(st.o[2 * nd + 1], a, r2, r3);
+    }
+  }
+}
+
+// Q rows g and g + 8 of a warp as A fragments; a null pointer gives a zero row.
+template <int D>
+__device__ __forceinline__ void load_q(uint32_t (&q)[D / 16][4], const __nv_bfloat16* row0, const __nv_bfloat16* row1, int lane) {
+  const int t = lane & 3;
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const int c = kk * 16 + 2 * t;
+    q[kk][0] = row0 ? *reinterpret_cast<const uint32_t*>(row0 + c) : 0u;
+    q[kk][1] = row1 ? *reinterpret_cast<const uint32_t*>(row1 + c) : 0u;
+    q[kk][2] = row0 ? *reinterpret_cast<const uint32_t*>(row0 + c + 8) : 0u;
+    q[kk][3] = row1 ? *reinterpret_cast<const uint32_t*>(row1 + c + 8) : 0u;
+  }
+}
+
+// ------------------------------------------------------------------ prefill
+struct PrefillParams {
+  const __nv_bfloat16* q; __nv_bfloat16* out;
+  Cache cache;
+  const int* positions; const int* cu_q; const int* block_table;
+  int max_blocks, n_seqs, nq, window, q_stride, out_stride;
+  float scale_log2;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kWarps * 32)
+prefill_kernel(const PrefillParams p) {
+  constexpr int kStride = D + 8;
+  constexpr int kTileElems = kTileKeys * kStride;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [2][K, V][64][D + 8]
+  const int G = p.nq / p.cache.nkv;
+  const int kvh = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+
+  // which sequence and which 64-row tile of it
+  int seq = 0, tile = blockIdx.x;
+  for (; seq < p.n_seqs; ++seq) {
+    const int rows = (p.cu_q[seq + 1] - p.cu_q[seq]) * G;
+    const int tiles = (rows + 63) / 64;
+    if (tile < tiles) break;
+    tile -= tiles;
+  }
+  if (seq >= p.n_seqs) return;
+  const int tok0 = p.cu_q[seq], q_len = p.cu_q[seq + 1] - tok0;
+  const int* table = p.block_table + (size_t)seq * p.max_blocks;
+
+  // this thread's two rows
+  int pos[2], lo[2], tok[2], head[2];
+  bool live[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = tile * 64 + warp * 16 + g + 8 * r;
+    const int tl = row / G;
+    live[r] = tl < q_len;
+    tok[r] = tok0 + (live[r] ? tl : 0);
+    head[r] = kvh * G + row % G;
+    pos[r] = live[r] ? p.positions[tok[r]] : -1;
+    lo[r] = (live[r] && p.window > 0 && pos[r] + 1 > p.window) ? pos[r] + 1 - p.window : 0;
+    if (!live[r]) lo[r] = 0;
+  }
+  // keys the whole CTA needs: from the smallest window start to the largest position
+  const int first_tl = (tile * 64) / G;
+  const int last_tl = min(q_len - 1, (tile * 64 + 63) / G);
+  const int pos_first = p.positions[tok0 + first_tl], pos_last = p.positions[tok0 + last_tl];
+  const int key_lo = (p.window > 0 && pos_first + 1 > p.window) ? pos_first + 1 - p.window : 0;
+  const int hi = pos_last + 1;
+
+  uint32_t q[D / 16][4];
+  load_q<D>(q, live[0] ? p.q + (size_t)tok[0] * p.q_stride + (size_t)head[0] * D : nullptr,
+            live[1] ? p.q + (size_t)tok[1] * p.q_stride + (size_t)head[1] * D : nullptr, lane);
+  RowState<D> st;
+  st.init();
+
+  const int first_tile = key_lo / kTileKeys, n_tiles = (hi + kTileKeys - 1) / kTileKeys - first_tile;
+  auto issue = [&](int i) {
+    __nv_bfloat16* buf = smem + (i & 1) * 2 * kTileElems;
+    const int key0 = (first_tile + i) * kTileKeys;
+    load_tile<D, kWarps * 32>(buf, p.cache.k, p.cache, table, p.max_blocks, kvh, key0, key_lo, hi, threadIdx.x);
+    load_tile<D, kWarps * 32>(buf + kTileElems, p.cache.v, p.cache, table, p.max_blocks, kvh, key0, key_lo, hi, threadIdx.x);
+    cp_async_commit();
+  };
+  issue(0);
+  for (int i = 0; i < n_tiles; ++i) {
+    if (i + 1 < n_tiles) { issue(i + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    __syncthreads();
+    const __nv_bfloat16* buf = smem + (i & 1) * 2 * kTileElems;
+    const int key0 = (first_tile + i) * kTileKeys;
+    // a warp whose rows cannot see this tile skips the math (the barrier is kept)
+    const int wpos = __reduce_max_sync(0xffffffffu, max(pos[0], pos[1]));
+    if (key0 <= wpos) tile_step<D>(st, q, buf, buf + kTileElems, key0, pos, lo, hi, p.scale_log2, lane);
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float l = st.l[r];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (!live[r]) continue;
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    __nv_bfloat16* dst = p.out + (size_t)tok[r] * p.out_stride + (size_t)head[r] * D;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i)
+      *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t) = pack_bf16(st.o[i][2 * r] * inv, st.o[i][2 * r + 1] * inv);
+  }
+}
+
+// ------------------------------------------------------------------ decode
+struct DecodeParams {
+  const __nv_bfloat16* q; __nv_bfloat16* out;
+  Cache cache;
+  const int* positions; const int* cu_q; const int* block_table;
+  float* scratch;      // [seqs][nkv][chunks][G][D + 2]
+  int* tickets;        // [seqs * nkv], zero between launches
+  int max_blocks, n_seqs, nq, window, q_stride, out_stride, chunk, max_chunks, rows16;
+  float scale_log2;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kWarps * 32)
+decode_kernel(const DecodeParams p) {
+  constexpr int kStride = D + 8;
+  constexpr int kTileElems = kTileKeys * kStride;
+  constexpr int kRec = D + 2;                      // O row, then max and sum
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [warps][K, V][64][D + 8]
+  __shared__ int s_last;
+  const int G = p.nq / p.cache.nkv;
+  const int kvh = blockIdx.x, seq = blockIdx.y, chunk_i = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int tok = p.cu_q[seq];
+  const int pos = p.positions[tok];
+  if (p.cu_q[seq + 1] - tok != 1) return;          // decode handles one token per sequence
+  const int lo = (p.window > 0 && pos + 1 > p.window) ? pos + 1 - p.window : 0;
+  const int hi = pos + 1;
+  const int c_lo = lo / p.chunk, c_hi = pos / p.chunk;
+  if (chunk_i < c_lo || chunk_i > c_hi) return;
+  const int n_chunks = c_hi - c_lo + 1;
+  const int* table = p.block_table + (size_t)seq * p.max_blocks;
+  const int key_begin = chunk_i * p.chunk;
+  const int key_end = min(key_begin + p.chunk, hi);
+  float* rec_base = p.scratch + (((size_t)seq * p.cache.nkv + kvh) * p.max_chunks) * (size_t)(G * kRec);
+
+  __nv_bfloat16* kt = smem + warp * 2 * kTileElems;
+  __nv_bfloat16* vt = kt + kTileElems;
+  // merge area (reuses nothing of the tiles): [warps][16][D + 2] floats after the tiles
+  float* merge = reinterpret_cast<float*>(smem + kWarps * 2 * kTileElems);
+
+  for (int rb = 0; rb < p.rows16; rb += 16) {      // 16 query heads of the group at a time
+    RowState<D> st;
+    st.init();
+    int rpos[2], rlo[2];
+    const __nv_bfloat16* qrow[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int h = rb + g + 8 * r;
+      const bool live = h < G;
+      rpos[r] = live ? pos : -1;
+      rlo[r] = lo;
+      qrow[r] = live ? p.q + (size_t)tok * p.q_stride + (size_t)(kvh * G + h) * D : nullptr;
+    }
+    uint32_t q[D / 16][4];
+    load_q<D>(q, qrow[0], qrow[1], lane);
+    // this warp's keys: tiles warp, warp + 4, ... of the chunk
+    for (int key0 = key_begin + warp * kTileKeys; key0 < key_end; key0 += kWarps * kTileKeys) {
+      __syncwarp();
+      load_tile<D, 32>(kt, p.cache.k, p.cache, table, p.max_blocks, kvh, key0, lo, key_end, lane);
+      load_tile<D, 32>(vt, p.cache.v, p.cache, table, p.max_blocks, kvh, key0, lo, key_end, lane);
+      cp_async_commit();
+      cp_async_wait<0>();
+      __syncwarp();
+      tile_step<D>(st, q, kt, vt, key0, rpos, rlo, key_end, p.scale_log2, lane);
+    }
+    // ---- merge the four warps (fixed order) into the chunk's record
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float l = st.l[r];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      float* row = merge + ((size_t)warp * 16 + g + 8 * r) * kRec;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) { row[i * 8 + 2 * t] = st.o[i][2 * r]; row[i * 8 + 2 * t + 1] = st.o[i][2 * r + 1]; }
+      if (t == 0) { row[D] = st.m[r]; row[D + 1] = l; }
+    }
+    __syncthreads();
+    float* rec = rec_base + ((size_t)chunk_i * G + rb) * kRec;
+    for (int idx = threadIdx.x; idx < 16 * kRec; idx += kWarps * 32) {
+      const int row = idx / kRec, c = idx % kRec;
+      if (rb + row >= G) break;
+      float m_all = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) m_all = fmaxf(m_all, merge[((size_t)w * 16 + row) * kRec + D]);
+      float acc = 0.f;
+      if (c == D) acc = m_all;
+      else {
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+          const float mw = merge[((size_t)w * 16 + row) * kRec + D];
+          const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m_all);
+          acc += merge[((size_t)w * 16 + row) * kRec + c] * f;      // c == D + 1 sums l the same way
+        }
+      }
+      rec[idx] = acc;
+    }
+    __syncthreads();
+  }
+  // ---- ticket: the last chunk of this (sequence, kv head) merges all chunks in order
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* ticket = p.tickets + seq * p.cache.nkv + kvh;
+    const int tk = atomicAdd(ticket, 1);
+    s_last = (tk == n_chunks - 1) ? 1 : 0;
+    if (tk == n_chunks - 1) *ticket = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < G * D; idx += kWarps * 32) {
+    const int h = idx / D, c = idx % D;
+    float m_all = -INFINITY;
+    for (int ci = c_lo; ci <= c_hi; ++ci) m_all = fmaxf(m_all, __ldcg(rec_base + ((size_t)ci * G + h) * kRec + D));
+    float o = 0.f, l = 0.f;
+    for (int ci = c_lo; ci <= c_hi; ++ci) {
+      const float* rec = rec_base + ((size_t)ci * G + h) * kRec;
+      const float mc = __ldcg(rec + D);
+      const float f = (mc == -INFINITY) ? 0.f : exp2f(mc - m_all);
+      o += __ldcg(rec + c) * f;
+      l += __ldcg(rec + D + 1) * f;
+    }
+    p.out[(size_t)tok * p.out_stride + (size_t)(kvh * G + h) * D + c] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+  }
+}
+
+template <int D> size_t prefill_smem() { return (size_t)2 * 2 * kTileKeys * (D + 8) * 2; }
+template <int D> size_t decode_smem() { return (size_t)kWarps * 2 * kTileKeys * (D + 8) * 2 + (size_t)kWarps * 16 * (D + 2) * 4; }
+
+template <int D>
+int launch_prefill(const PrefillParams& p, int n_tiles, cudaStream_t stream) {
+  static bool configured = false;
+  const size_t smem = prefill_smem<D>();
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail("attention prefill: cannot reserve %zu bytes of shared memory", smem);
+    configured = true;
+  }
+  prefill_kernel<D><<<dim3(n_tiles, p.cache.nkv), kWarps * 32, smem, stream>>>(p);
+  return check_launch("attention prefill");
+}
+
+template <int D>
+int launch_decode(const DecodeParams& p, cudaStream_t stream) {
+  static bool configured = false;
+  const size_t smem = decode_smem<D>();
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail("attention decode: cannot reserve %zu bytes of shared memory", smem);
+    configured = true;
+  }
+  decode_kernel<D><<<dim3(p.cache.nkv, p.n_seqs, p.max_chunks), kWarps * 32, smem, stream>>>(p);
+  return check_launch("attention decode");
+}
+
+}  // namespace
+
+// Head sizes the tensor-core kernels are built for; any other size takes the exact kernel.
+ILB_EXPORT int ilb_attention_flash_supported(int d) { return (d == 32 || d == 64 || d == 96 || d == 128) ? 1 : 0; }
+
+ILB_EXPORT int ilb_attention_prefill(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                     const int* positions, const int* cu_q, const int* block_table,
+                                     int max_blocks, int page_size, int num_pages, int window, float scale,
+                                     int n_seqs, int n_tiles, int nq, int nkv, int d, int q_stride, int out_stride,
+                                     cudaStream_t stream) {
+  ILB_REQUIRE(ilb_attention_flash_supported(d), "attention prefill: head size %d is not built (32, 64, 96, 128 are)", d);
+  ILB_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention prefill: %d query heads are not a multiple of %d kv heads", nq, nkv);
+  ILB_REQUIRE(n_seqs > 0 && n_tiles > 0 && nkv <= 65535, "attention prefill: bad grid");
+  ILB_REQUIRE(page_size > 0 && max_blocks > 0 && num_pages > 0 && window >= 0, "attention prefill: bad cache geometry");
+  ILB_REQUIRE(q_stride % 2 == 0 && out_stride % 2 == 0 && ((uintptr_t)q % 4 == 0) && ((uintptr_t)out % 4 == 0) &&
+              ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0), "attention prefill: misaligned operands");
+  PrefillParams p{(const __nv_bfloat16*)q, (__nv_bfloat16*)out,
+                  Cache{(const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, page_size, num_pages, nkv},
+                  positions, cu_q, block_table, max_blocks, n_seqs, nq, window, q_stride, out_stride, scale * kLog2e};
+  switch (d) {
+    case 32: return launch_prefill<32>(p, n_tiles, stream);
+    case 64: return launch_prefill<64>(p, n_tiles, stream);
+    case 96: return launch_prefill<96>(p, n_tiles, stream);
+    default: return launch_prefill<128>(p, n_tiles, stream);
+  }
+}
+
+// scratch: n_seqs * nkv * max_chunks * (nq / nkv) * (d + 2) floats; tickets: n_seqs * nkv ints, zero.
+ILB_EXPORT int ilb_attention_decode(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                    const int* positions, const int* cu_q, const int* block_table,
+                                    int max_blocks, int page_size, int num_pages, int window, float scale,
+                                    int n_seqs, int nq, int nkv, int d, int q_stride, int out_stride,
+                                    int chunk, int max_chunks, float* scratch, long long scratch_floats,
+                                    int* tickets, int n_tickets, cudaStream_t stream) {
+  ILB_REQUIRE(ilb_attention_flash_supported(d), "attention decode: head size %d is not built (32, 64, 96, 128 are)", d);
+  ILB_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention decode: %d query heads are not a multiple of %d kv heads", nq, nkv);
+  ILB_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && max_chunks > 0 && max_chunks <= 65535, "attention decode: bad grid");
+  ILB_REQUIRE(chunk > 0 && chunk % (kWarps * kTileKeys) == 0, "attention decode: chunk %d must be a multiple of %d", chunk, kWarps * kTileKeys);
+  ILB_REQUIRE(page_size > 0 && max_blocks > 0 && num_pages > 0 && window >= 0, "attention decode: bad cache geometry");
+  const int G = nq / nkv, rows16 = (G + 15) / 16 * 16;
+  ILB_REQUIRE((long long)n_seqs * nkv * max_chunks * G * (d + 2) <= scratch_floats, "attention decode: scratch too small");
+  ILB_REQUIRE(n_seqs * nkv <= n_tickets, "attention decode: too few tickets");
+  DecodeParams p{(const __nv_bfloat16*)q, (__nv_bfloat16*)out,
+                 Cache{(const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, page_size, num_pages, nkv},
+                 positions, cu_q, block_table, scratch, tickets, max_blocks, n_seqs, nq, window, q_stride, out_stride,
+                 chunk, max_chunks, rows16, scale * kLog2e};
+  switch (d) {
+    case 32: return launch_decode<32>(p, stream);
+    case 64: return launch_decode<64>(p, stream);
+    case 96: return launch_decode<96>(p, stream);
+    default: return launch_decode<128>(p, stream);
+  }
+}
+
+ILB_DEFINE_LAST_ERROR()

@@ -34,6 +34,7 @@ MODULES: Dict[str, List[str]] = {
     "gemm_tcgen05": [],
     "qk_norm_rope": [],
     "attention_simple": [],
+    "attention_flash": [],
     "sampling": [],
 }
 

@@ -283,9 +283,71 @@ def check_device_errors() -> None:
 
 
 # --------------------------------------------------------------------------- attention dispatch
+DECODE_CHUNK_MIN = 256      # keys per decode CTA; boundaries depend on the key index alone
+
+
+def decode_chunk_for(max_positions: int) -> int:
+    """Chunk length of split-KV decode for a model that reaches `max_positions`: 256 keys,
+    or more for very long contexts so that a sequence never has more than 32 chunks."""
+    chunk = DECODE_CHUNK_MIN
+    while chunk * 32 < max_positions:
+        chunk *= 2
+    return chunk
+
+
+def attention_flash_supported(d: int) -> bool:
+    return d in (32, 64, 96, 128)
+
+
+def attention_prefill(q, out, k_cache, v_cache, positions, cu_q, block_table, window, scale, n_seqs,
+                      n_tiles, nq, nkv, d) -> None:
+    for t, w in ((q, "q"), (out, "out"), (k_cache, "k cache"), (v_cache, "v cache")):
+        _need(t, "attention " + w, torch.bfloat16)
+    num_pages, _, page_size, _ = k_cache.shape
+    _call("attention_flash", "ilb_attention_prefill", _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache),
+          _ptr(positions), _ptr(cu_q), _ptr(block_table), _i(block_table.shape[1]), _i(page_size),
+          _i(num_pages), _i(window or 0), _f(scale), _i(n_seqs), _i(n_tiles), _i(nq), _i(nkv), _i(d),
+          _i(q.shape[1]), _i(out.shape[1]), _stream(q))
+
+
+def attention_decode(q, out, k_cache, v_cache, positions, cu_q, block_table, window, scale, n_seqs,
+                     nq, nkv, d, chunk, max_chunks, scratch, tickets) -> None:
+    for t, w in ((q, "q"), (out, "out"), (k_cache, "k cache"), (v_cache, "v cache")):
+        _need(t, "attention " + w, torch.bfloat16)
+    _need(scratch, "attention scratch", torch.float32); _need(tickets, "attention tickets", torch.int32)
+    num_pages, _, page_size, _ = k_cache.shape
+    _call("attention_flash", "ilb_attention_decode", _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache),
+          _ptr(positions), _ptr(cu_q), _ptr(block_table), _i(block_table.shape[1]), _i(page_size),
+          _i(num_pages), _i(window or 0), _f(scale), _i(n_seqs), _i(nq), _i(nkv), _i(d), _i(q.shape[1]),
+          _i(out.shape[1]), _i(chunk), _i(max_chunks), _ptr(scratch), ctypes.c_longlong(scratch.numel()),
+          _ptr(tickets), _i(tickets.numel()), _stream(q))
+
+
 def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
               step, block_table: torch.Tensor, window: int, scale: float, nq: int, nkv: int,
-              d: int) -> None:
-    """Causal attention of the step's tokens over the cache; picks the kernel."""
-    paged_attention_simple(q, out, k_cache, v_cache, step.positions, step.seq_of_token,
-                           block_table, window, scale, nq, nkv, d)
+              d: int, workspace=None, decode_chunk: int = DECODE_CHUNK_MIN) -> None:
+    """Causal attention of the step's tokens over the cache; picks the kernel: the
+    tensor-core kernels for a bfloat16 cache and a head size they are built for (split-KV
+    when every sequence brings one token), else the exact kernel."""
+    fast = (q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and attention_flash_supported(d)
+            and workspace is not None and FLASH_ENABLED)
+    if not fast:
+        paged_attention_simple(q, out, k_cache, v_cache, step.positions, step.seq_of_token,
+                               block_table, window, scale, nq, nkv, d)
+        return
+    G = nq // nkv
+    if step.decode_only:
+        page_size = k_cache.shape[2]
+        capacity = block_table.shape[1] * page_size
+        max_chunks = max(1, -(-capacity // decode_chunk))
+        scratch = workspace.buffer("attn.decode_scratch", (step.n_seqs * nkv * max_chunks * G * (d + 2),), torch.float32)
+        tickets = workspace.zeroed("attn.decode_tickets", (max(step.n_seqs * nkv, 4096),), torch.int32)
+        attention_decode(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
+                         step.n_seqs, nq, nkv, d, decode_chunk, max_chunks, scratch, tickets)
+    else:
+        n_tiles = sum(-(-n * G // 64) for n in step.h_q_len)
+        attention_prefill(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
+                          step.n_seqs, n_tiles, nq, nkv, d)
+
+
+FLASH_ENABLED = True       # tests switch it off to exercise the exact kernel in bfloat16

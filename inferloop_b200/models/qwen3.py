@@ -36,6 +36,7 @@ def build_spec(cfg: Qwen3Config) -> ModelSpec:
             qk_norm_eps=cfg.rms_norm_eps,
             bias=cfg.attention_bias,
             window=cfg.layer_window(i),
+            max_positions=cfg.max_position_embeddings,
             position=position,
         )
         ffn = PartSpec.make(

@@ -42,6 +42,9 @@ class GQAttention(Mixer):
         self.bias = bool(spec.get("bias", False))
         self.window = spec.get("window")
         self.scale = 1.0 / math.sqrt(self.d)
+        # split-KV decode cuts the keys at multiples of this, fixed per model so that the
+        # cut never depends on the batch
+        self.decode_chunk = ops.decode_chunk_for(int(spec.get("max_positions", 4096)))
         self.position = registry.build("position", spec["position"], ctx)
         self.rotary_dim = int(spec["position"].get("rotary_dim", 0))
         p = prefix
@@ -96,7 +99,7 @@ class GQAttention(Mixer):
             self.nq, self.nkv, self.d)
         o = ws.buffer("attn.o", (T, self.nq * self.d), dt)
         ops.attention(q, o, cache.k, cache.v, step, table, self.window or 0, self.scale,
-                      self.nq, self.nkv, self.d)
+                      self.nq, self.nkv, self.d, workspace=ws, decode_chunk=self.decode_chunk)
         linear(o, self.w_o, residual, self.b_o, accumulate=True)
 
 

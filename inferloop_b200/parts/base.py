@@ -50,6 +50,20 @@ class Workspace:
             self.generation += 1
         return buf[:n].view(*shape)
 
+    def zeroed(self, tag: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        """Like :meth:`buffer`, but zero when (re)allocated.  For counters that kernels
+        leave at zero after every launch: the zero is written once, not per call."""
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = (tag, dtype)
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < n:
+            buf = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+            self.generation += 1
+        return buf[:n].view(*shape)
+
     def nbytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._buffers.values())
 

@@ -332,3 +332,100 @@ def test_gemm_tcgen05_refuses_unaligned_rows():
     assert not o.gemm_tc_eligible(a, w, out)
     with pytest.raises(o.KernelError, match="multiples of 8"):
         o.gemm_tc(a, w, out)
+
+
+# ------------------------------------------------------------------ tensor-core attention
+def close_flash(got, ref, vmax, what):
+    """The tensor-core kernels round the probabilities to bfloat16 before the value
+    product (as the reference's grouped decode does), so each output carries up to
+    2^-9 * sum_j p_j |v_j| <= 2^-9 * max|v| of error besides the rounding of the result:
+    bound 2^-8 * (|ref| + max|v|)."""
+    got, ref = got.double().cpu(), ref.double().cpu()
+    assert torch.isfinite(got).all(), f"{what}: non-finite output"
+    err = (got - ref).abs()
+    bad = err > (2.0 ** -8) * (ref.abs() + vmax)
+    assert not bad.any(), f"{what}: {int(bad.sum())} bad, max err {err.max().item():.3e} at {torch.nonzero(bad)[0].tolist()}"
+
+
+class _Step:
+    """The few batch facts the attention dispatcher reads."""
+
+    def __init__(self, positions, seq_of, cu_q, q_lens):
+        self.positions = torch.tensor(positions, dtype=torch.int32).cuda()
+        self.seq_of_token = torch.tensor(seq_of, dtype=torch.int32).cuda()
+        self.cu_q = torch.tensor(cu_q, dtype=torch.int32).cuda()
+        self.h_q_len = list(q_lens)
+        self.n_seqs = len(q_lens)
+        self.decode_only = all(n == 1 for n in q_lens)
+
+
+def run_flash(q, seqs, lens, q_lens, nq, nkv, d, page_size, window, chunk=256, seed=0):
+    from inferloop_b200.parts import Workspace
+    o = ops()
+    n_pages = sum(-(-n // page_size) for n in lens) + 3
+    k_cache, v_cache, table = build_cache([(k.float(), v.float()) for k, v in seqs], nkv, d, page_size, n_pages,
+                                          torch.bfloat16, seed=seed)
+    positions, seq_of, cu = [], [], [0]
+    for s, (n, ql) in enumerate(zip(lens, q_lens)):
+        positions += list(range(n - ql, n))
+        seq_of += [s] * ql
+        cu.append(cu[-1] + ql)
+    step = _Step(positions, seq_of, cu, q_lens)
+    out = torch.full((len(positions), nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ws = Workspace(torch.device("cuda:0"))
+    for _ in range(2):      # twice: the tickets must be back at zero after the first launch
+        o.attention(q.cuda(), out, k_cache.cuda(), v_cache.cuda(), step, table.cuda(), window, 1.0 / math.sqrt(d),
+                    nq, nkv, d, workspace=ws, decode_chunk=chunk)
+    return out, positions, seq_of
+
+
+@pytest.mark.parametrize("nq,nkv,d,page_size,window", [(4, 2, 32, 4, 0), (6, 2, 64, 8, 0), (5, 5, 96, 16, 20),
+                                                         (32, 8, 128, 16, 0), (8, 1, 128, 16, 0), (40, 2, 64, 32, 0),
+                                                         (3, 3, 128, 16, 33)])
+def test_flash_prefill_mixed_batch(nq, nkv, d, page_size, window):
+    torch.manual_seed(nq + d)
+    lens, q_lens = [37, 90, 131, 300], [37, 23, 1, 70]
+    seqs = [(torch.randn(n, nkv, d).to(torch.bfloat16).double(), torch.randn(n, nkv, d).to(torch.bfloat16).double()) for n in lens]
+    q = torch.randn(sum(q_lens), nq * d).to(torch.bfloat16)
+    out, positions, seq_of = run_flash(q, seqs, lens, q_lens, nq, nkv, d, page_size, window)
+    ref = torch.stack([ref_attention(q[t].double().view(nq, d), *seqs[seq_of[t]], positions[t], window).reshape(-1)
+                       for t in range(len(positions))])
+    close_flash(out, ref, max(float(v.abs().max()) for _, v in seqs), "flash prefill")
+
+
+@pytest.mark.parametrize("nq,nkv,d,page_size,window,chunk", [(4, 2, 32, 4, 0, 256), (6, 2, 64, 8, 0, 256), (5, 5, 96, 16, 300, 256),
+                                                               (32, 8, 128, 16, 0, 256), (8, 1, 128, 16, 0, 512), (40, 2, 64, 32, 0, 256)])
+def test_flash_decode_split_kv(nq, nkv, d, page_size, window, chunk):
+    """One token per sequence, lengths below, at and far above the chunk length."""
+    torch.manual_seed(nq + d + 1)
+    lens = [1, 2, 63, 64, 65, 256, 257, 700, 1030, 1537]
+    q_lens = [1] * len(lens)
+    seqs = [(torch.randn(n, nkv, d).to(torch.bfloat16).double(), torch.randn(n, nkv, d).to(torch.bfloat16).double()) for n in lens]
+    q = torch.randn(len(lens), nq * d).to(torch.bfloat16)
+    out, positions, seq_of = run_flash(q, seqs, lens, q_lens, nq, nkv, d, page_size, window, chunk)
+    ref = torch.stack([ref_attention(q[t].double().view(nq, d), *seqs[seq_of[t]], positions[t], window).reshape(-1)
+                       for t in range(len(positions))])
+    close_flash(out, ref, max(float(v.abs().max()) for _, v in seqs), "flash decode")
+
+
+@pytest.mark.parametrize("q_len", [1, 5])
+def test_flash_attention_finds_one_far_key_and_respects_the_window_edge(q_len):
+    nq, nkv, d, page = 4, 1, 64, 16
+    n = 900
+    torch.manual_seed(2)
+    k = torch.randn(n, nkv, d) * 0.1
+    v = torch.arange(n, dtype=torch.float32)[:, None, None].expand(n, nkv, d).clone()
+    for far, window, expect in ((13, 0, 13.0), (899 - 50 + 1, 50, 850.0), (899 - 50, 50, None), (511, 0, 511.0), (512, 0, 512.0)):
+        kk = k.clone()
+        direction = torch.randn(d)
+        direction /= direction.norm()
+        kk[far, 0] = direction * 40
+        q = torch.randn(q_len, nq, d) * 0.01
+        q[-1, :] = direction * 40                     # only the last token looks for the far key
+        out, _, _ = run_flash(q.reshape(q_len, -1).to(torch.bfloat16), [(kk.to(torch.bfloat16).double(), v.double())],
+                              [n], [q_len], nq, nkv, d, page, window, seed=far)
+        got = out[-1].float().cpu()
+        if expect is not None:
+            assert torch.allclose(got, torch.full_like(got, expect), rtol=2.0 ** -7), (far, window, got[:4])
+        else:
+            assert 850.0 <= got.min().item() and got.max().item() <= 899.0
