@@ -8,17 +8,20 @@
 // kernel is a pure stream of weight tiles; with many tokens X is a 128-token tile and Y a
 // tile of BN weight rows.
 //
-// Per CTA (192 threads), one output tile and one contiguous range of K:
+// The grid is persistent: one CTA per SM, each taking an equal, contiguous run of
+// (output tile, 64-wide K block) units ("stream-K"), so all SMs stream operands for the
+// whole kernel whatever the number of tiles.  Per CTA (192 threads):
 //   warp 0      one lane issues the TMA loads (cp.async.bulk.tensor, 128-byte swizzle,
 //               no cluster multicast) into a ring of STAGES buffers;
-//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (4 per 64-wide K
-//               block) and tcgen05.commit to hand buffers back and to signal the end;
-//   warps 2-5   read the accumulator with tcgen05.ld and write the result.
-// When K is split over several CTAs (decode shapes have too few tiles to fill 148 SMs),
-// each CTA stores its partial tile to a 32-bit workspace and takes a ticket; the CTA that
-// takes the last ticket of a tile adds the partials in split order, so the sum does not
-// depend on which CTA finished first, and writes the result.  There is no spin-wait on
-// another CTA anywhere.  Every mbarrier wait is bounded: on expiry the kernel raises a
+//   warp 1      allocates tensor memory (two accumulators); one lane issues tcgen05.mma
+//               (4 per 64-wide K block) and tcgen05.commit to hand buffers back and to
+//               signal that an accumulator is complete;
+//   warps 2-5   read an accumulator with tcgen05.ld and write the result while the next
+//               tile accumulates in the other one.
+// A tile whose K range is shared by several CTAs: each stores its share to a 32-bit
+// workspace slot and takes a ticket; the CTA that takes the last ticket of the tile adds
+// the shares in K order, so the sum does not depend on which CTA finished first, and
+// writes the result.  There is no spin-wait on another CTA anywhere.  Every mbarrier wait is bounded: on expiry the kernel raises a
 // flag in global memory, drains what it armed, frees its tensor memory and returns.
 //
 // The reference computes these products with JIT-compiled tile kernels that target no
@@ -126,46 +129,55 @@ __device__ __forceinline__ void tmem_load_16(uint32_t addr, float (&v)[32]) {
 struct Params {
   void* out;                 // [M, N], bf16 or f32
   const float* bias;         // [N] or null
-  float* partial;            // split-K workspace: [tiles][splits][BN][128] floats
+  float* partial;            // stream-K workspace: two slots of [BN][128] floats per CTA
   int* tickets;              // one counter per tile, zero between launches
   int* error_flag;           // set to 1 when a bounded wait ran out
   int M, N, K, ldo;
-  int x_rows, y_rows;        // extents of the X and Y operands (N, M when swapped, else M, N)
+  int tiles_x, tiles_y;      // tiles of the X operand (128 rows) and of the Y operand (BN rows)
   int k_blocks;              // ceil(K / 64)
-  int splits;                // CTAs per tile along K
+  long long units;           // tiles_x * tiles_y * k_blocks
   int epilogue;              // Epilogue
   int out_f32;               // element type of out
 };
 
-// One (x tile, y tile, split) per CTA:  blockIdx.x = x tile, blockIdx.y = y tile, blockIdx.z = split.
+// Work is cut stream-K fashion: a unit is one 64-wide K block of one output tile; the
+// grid's CTAs take equal, contiguous runs of units, so a CTA handles the tail of one tile,
+// some whole tiles, and the head of another.
+struct Schedule {
+  long long units; int grid, k_blocks;
+  __device__ __forceinline__ long long start(int c) const { return (long long)c * units / grid; }
+  __device__ __forceinline__ int cta_of(long long u) const { return (int)(((u + 1) * grid - 1) / units); }
+  // slot of CTA c's contribution to the tile whose first unit is `tile_first`
+  __device__ __forceinline__ int slot(int c, long long tile_first) const { return 2 * c + (start(c) >= tile_first ? 0 : 1); }
+};
+
 template <int BN, int STAGES, bool SWAP>
 __global__ void __launch_bounds__(kThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, const Params p) {
   constexpr uint32_t kBytesX = kTileX * kBlockK * 2;
   constexpr uint32_t kBytesY = BN * kBlockK * 2;
   constexpr uint32_t kStageBytes = kBytesX + kBytesY;          // multiples of 1024
-  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;            // power of two >= 32
+  constexpr uint32_t kAccCols = BN < 32 ? 32 : BN;             // columns of one accumulator
+  constexpr uint32_t kTmemCols = 2 * kAccCols;                 // two accumulators; a power of two >= 64
+  constexpr int kTileFloats = BN * kTileX;
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // dynamic shared memory is only 16-byte aligned by contract; align by hand
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * kStageBytes);
-  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, done_bar = empty0 + 8 * STAGES;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * STAGES + 1);
-  volatile int* flags = reinterpret_cast<volatile int*>(bars + 2 * STAGES + 2);   // [0] = failed, [1] = last ticket
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES;
+  const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* flags = reinterpret_cast<volatile int*>(bars + 2 * STAGES + 5);   // [0] = failed, [1] = last ticket
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int x0 = blockIdx.x * kTileX, y0 = blockIdx.y * BN;
-  const int split = blockIdx.z;
-  // K blocks of this split: an even share, the first `rem` splits one more
-  const int share = p.k_blocks / p.splits, rem = p.k_blocks % p.splits;
-  const int kb_begin = split * share + (split < rem ? split : rem);
-  const int kb_count = share + (split < rem ? 1 : 0);
+  const Schedule sch{p.units, (int)gridDim.x, p.k_blocks};
+  const long long u_begin = sch.start(blockIdx.x), u_end = sch.start(blockIdx.x + 1);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-    mbar_init(done_bar, 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 128); }
     flags[0] = 0; flags[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -181,128 +193,168 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      int armed = 0;
       bool ok = true;
-      for (int i = 0; i < kb_count && ok; ++i) {
-        const int s = i % STAGES;
-        if (i >= STAGES) ok = mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1);
-        if (!ok) break;
-        const uint32_t dst = base + s * kStageBytes;
-        mbar_expect_tx(full0 + 8 * s, kStageBytes);
-        tma_load_2d(dst, &map_x, full0 + 8 * s, (kb_begin + i) * kBlockK, x0);
-        tma_load_2d(dst + kBytesX, &map_y, full0 + 8 * s, (kb_begin + i) * kBlockK, y0);
-        armed = i + 1;
+      uint32_t it = 0;
+      for (long long u = u_begin; u < u_end && ok;) {
+        const long long tile = u / p.k_blocks;
+        const int kb0 = (int)(u % p.k_blocks);
+        const int cnt = (int)min((long long)(p.k_blocks - kb0), u_end - u);
+        const int x0 = (int)(tile % p.tiles_x) * kTileX, y0 = (int)(tile / p.tiles_x) * BN;
+        for (int i = 0; i < cnt; ++i, ++it) {
+          const uint32_t s = it % STAGES;
+          if (it >= STAGES) ok = mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1);
+          if (!ok) break;
+          const uint32_t dst = base + s * kStageBytes;
+          mbar_expect_tx(full0 + 8 * s, kStageBytes);
+          tma_load_2d(dst, &map_x, full0 + 8 * s, (kb0 + i) * kBlockK, x0);
+          tma_load_2d(dst + kBytesX, &map_y, full0 + 8 * s, (kb0 + i) * kBlockK, y0);
+        }
+        u += cnt;
       }
       if (!ok) { flags[0] = 1; if (p.error_flag) *p.error_flag = 1; }
-      (void)armed;
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(kTileX, BN);
       bool ok = true;
-      for (int i = 0; i < kb_count && ok; ++i) {
-        const int s = i % STAGES;
-        ok = mbar_wait(full0 + 8 * s, (i / STAGES) & 1);
+      uint32_t it = 0, seg = 0;
+      for (long long u = u_begin; u < u_end && ok; ++seg) {
+        const int kb0 = (int)(u % p.k_blocks);
+        const int cnt = (int)min((long long)(p.k_blocks - kb0), u_end - u);
+        const uint32_t b = seg & 1;
+        ok = mbar_wait(tempty0 + 8 * b, ((seg >> 1) & 1) ^ 1);     // the epilogue has drained this accumulator
         if (!ok) break;
         tcgen05_fence_after();
-        const uint32_t a = base + s * kStageBytes;
-        const uint64_t da = smem_desc(a), db = smem_desc(a + kBytesX);
+        const uint32_t acc = tmem_base + b * kAccCols;
+        for (int i = 0; i < cnt; ++i, ++it) {
+          const uint32_t s = it % STAGES;
+          ok = mbar_wait(full0 + 8 * s, (it / STAGES) & 1);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t a = base + s * kStageBytes;
+          const uint64_t da = smem_desc(a), db = smem_desc(a + kBytesX);
 #pragma unroll
-        for (int k = 0; k < kBlockK / 16; ++k)
-          mma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
-        tcgen05_commit(empty0 + 8 * s);       // the buffer is free once these MMAs have read it
+          for (int k = 0; k < kBlockK / 16; ++k)
+            mma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          tcgen05_commit(empty0 + 8 * s);       // the buffer is free once these MMAs have read it
+        }
+        tcgen05_commit(tfull0 + 8 * b);         // arrives when every MMA issued so far is complete
+        u += cnt;
       }
-      if (!ok) { flags[0] = 1; if (p.error_flag) *p.error_flag = 1; }
-      tcgen05_commit(done_bar);               // arrives when every MMA issued so far is complete
+      if (!ok) {
+        flags[0] = 1; if (p.error_flag) *p.error_flag = 1;
+        tcgen05_commit(tfull0); tcgen05_commit(tfull0 + 8);       // let the epilogue leave its wait
+      }
     }
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5)
     const int quad = warp & 3;                // tensor-memory lanes 32*quad .. 32*quad+31
-    const int xr = x0 + quad * 32 + lane;     // this thread's row of the X operand
-    bool ok = mbar_wait(done_bar, 0);
-    tcgen05_fence_after();
-    if (!ok) { flags[0] = 1; if (p.error_flag) *p.error_flag = 1; }
-    const bool failed = flags[0] != 0;
-    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
-    const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-    float* my_partial = p.partial + ((size_t)tile * p.splits + split) * (size_t)(BN * kTileX);
-
+    const int row = quad * 32 + lane;         // row of the tile this thread owns
     constexpr int CH = BN < 32 ? BN : 32;     // columns per tensor-memory read
-    bool last = p.splits == 1;
-    if (p.splits > 1 && !failed) {
-      // 1. park this split's tile: [col][row] so that a warp writes 128 contiguous bytes
-      for (int c0 = 0; c0 < BN; c0 += CH) {
-        float v[32];
-        if (CH == 32) tmem_load_32(taddr + c0, v); else tmem_load_16(taddr + c0, v);
-#pragma unroll
-        for (int c = 0; c < CH; ++c) my_partial[(size_t)(c0 + c) * kTileX + quad * 32 + lane] = v[c];
-      }
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (threadIdx.x == 64) {
-        const int t = atomicAdd(p.tickets + tile, 1);
-        flags[1] = (t == p.splits - 1) ? 1 : 0;
-        if (t == p.splits - 1) p.tickets[tile] = 0;          // ready for the next launch
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      last = flags[1] != 0;
-      if (last) __threadfence();
-    }
-    if (last && !failed) {
-      const float* tile_partials = p.partial + (size_t)tile * p.splits * (size_t)(BN * kTileX);
-      for (int c0 = 0; c0 < BN; c0 += CH) {
-        float v[32];
-        if (p.splits == 1) {
+    uint32_t seg = 0;
+    bool failed = false;
+    for (long long u = u_begin; u < u_end && !failed; ++seg) {
+      const long long tile = u / p.k_blocks;
+      const int kb0 = (int)(u % p.k_blocks);
+      const int cnt = (int)min((long long)(p.k_blocks - kb0), u_end - u);
+      u += cnt;
+      const int x0 = (int)(tile % p.tiles_x) * kTileX, y0 = (int)(tile / p.tiles_x) * BN;
+      const int xr = x0 + row;
+      const uint32_t b = seg & 1;
+      if (!mbar_wait(tfull0 + 8 * b, (seg >> 1) & 1)) { flags[0] = 1; if (p.error_flag) *p.error_flag = 1; }
+      tcgen05_fence_after();
+      failed = flags[0] != 0;
+      if (failed) break;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + b * kAccCols;
+      const bool whole = cnt == p.k_blocks;
+      const long long tile_first = tile * p.k_blocks;
+      bool last = whole;
+      int c_first = 0, c_last = 0;
+      if (!whole) {
+        // 1. park this CTA's share of the tile: [col][row], a warp writes 128 contiguous bytes
+        float* mine = p.partial + (size_t)sch.slot(blockIdx.x, tile_first) * kTileFloats;
+        for (int c0 = 0; c0 < BN; c0 += CH) {
+          float v[32];
           if (CH == 32) tmem_load_32(taddr + c0, v); else tmem_load_16(taddr + c0, v);
-        } else {
 #pragma unroll
-          for (int c = 0; c < CH; ++c) v[c] = 0.f;
-          for (int s = 0; s < p.splits; ++s) {               // fixed order: split 0, 1, 2, ...
-            const float* src = tile_partials + (size_t)s * (BN * kTileX) + quad * 32 + lane;
+          for (int c = 0; c < CH; ++c) mine[(size_t)(c0 + c) * kTileX + row] = v[c];
+        }
+        tcgen05_fence_before();
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tempty0 + 8 * b) : "memory");
+        c_first = sch.cta_of(tile_first);
+        c_last = sch.cta_of(tile_first + p.k_blocks - 1);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) {
+          const int t = atomicAdd(p.tickets + tile, 1);
+          const int n = c_last - c_first + 1;
+          flags[1] = (t == n - 1) ? 1 : 0;
+          if (t == n - 1) p.tickets[tile] = 0;               // ready for the next launch
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        last = flags[1] != 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");        // flags[1] is reused by the next segment
+        if (last) __threadfence();
+      }
+      if (last) {
+        for (int c0 = 0; c0 < BN; c0 += CH) {
+          float v[32];
+          if (whole) {
+            if (CH == 32) tmem_load_32(taddr + c0, v); else tmem_load_16(taddr + c0, v);
+          } else {
 #pragma unroll
-            for (int c = 0; c < CH; ++c) v[c] += __ldcg(src + (size_t)(c0 + c) * kTileX);
+            for (int c = 0; c < CH; ++c) v[c] = 0.f;
+            for (int cc = c_first; cc <= c_last; ++cc) {       // fixed order: increasing K
+              const float* src = p.partial + (size_t)sch.slot(cc, tile_first) * kTileFloats + row;
+#pragma unroll
+              for (int c = 0; c < CH; ++c) v[c] += __ldcg(src + (size_t)(c0 + c) * kTileX);
+            }
+          }
+          if (SWAP) {
+            // X rows are output features n = xr; columns are tokens m = y0 + c
+            if (xr < p.N) {
+              const float bv = p.bias ? p.bias[xr] : 0.f;
+#pragma unroll
+              for (int c = 0; c < CH; ++c) {
+                const int m = y0 + c0 + c;
+                if (m < p.M) {
+                  const size_t o = (size_t)m * p.ldo + xr;
+                  float r = v[c] + bv;
+                  if (p.out_f32) {
+                    float* dst = (float*)p.out + o;
+                    if (p.epilogue == kAccumulate) r += *dst;
+                    *dst = r;
+                  } else {
+                    ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(r);
+                  }
+                }
+              }
+            }
+          } else {
+            // X rows are tokens m = xr; columns are output features n = y0 + c
+            if (xr < p.M) {
+#pragma unroll
+              for (int c = 0; c < CH; ++c) {
+                const int n = y0 + c0 + c;
+                if (n < p.N) {
+                  const size_t o = (size_t)xr * p.ldo + n;
+                  float r = v[c] + (p.bias ? p.bias[n] : 0.f);
+                  if (p.out_f32) {
+                    float* dst = (float*)p.out + o;
+                    if (p.epilogue == kAccumulate) r += *dst;
+                    *dst = r;
+                  } else {
+                    ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(r);
+                  }
+                }
+              }
+            }
           }
         }
-        if (SWAP) {
-          // X rows are output features n = xr; columns are tokens m = y0 + c
-          if (xr < p.N) {
-            const float b = p.bias ? p.bias[xr] : 0.f;
-#pragma unroll
-            for (int c = 0; c < CH; ++c) {
-              const int m = y0 + c0 + c;
-              if (m < p.M) {
-                const size_t o = (size_t)m * p.ldo + xr;
-                float r = v[c] + b;
-                if (p.out_f32) {
-                  float* dst = (float*)p.out + o;
-                  if (p.epilogue == kAccumulate) r += *dst;
-                  *dst = r;
-                } else {
-                  ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(r);
-                }
-              }
-            }
-          }
-        } else {
-          // X rows are tokens m = xr; columns are output features n = y0 + c
-          if (xr < p.M) {
-#pragma unroll
-            for (int c = 0; c < CH; ++c) {
-              const int n = y0 + c0 + c;
-              if (n < p.N) {
-                const size_t o = (size_t)xr * p.ldo + n;
-                float r = v[c] + (p.bias ? p.bias[n] : 0.f);
-                if (p.out_f32) {
-                  float* dst = (float*)p.out + o;
-                  if (p.epilogue == kAccumulate) r += *dst;
-                  *dst = r;
-                } else {
-                  ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(r);
-                }
-              }
-            }
-          }
+        if (whole) {
+          tcgen05_fence_before();
+          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tempty0 + 8 * b) : "memory");
         }
       }
     }
@@ -370,9 +422,20 @@ int make_map(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int 
   return 0;
 }
 
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
 template <int BN, int STAGES, bool SWAP>
-int launch(const CUtensorMap& mx, const CUtensorMap& my, const Params& p, dim3 grid, cudaStream_t stream) {
-  constexpr size_t smem = (size_t)STAGES * (kTileX * kBlockK * 2 + BN * kBlockK * 2) + 1024 + (2 * STAGES + 3) * 8;
+int launch(const CUtensorMap& mx, const CUtensorMap& my, const Params& p, int grid, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)STAGES * (kTileX * kBlockK * 2 + BN * kBlockK * 2) + 1024 + (2 * STAGES + 6) * 8;
+  static_assert(smem <= 227 * 1024, "stage ring does not fit shared memory");
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -385,9 +448,10 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, const Params& p, dim3 g
 
 }  // namespace
 
-// Elements of 32-bit workspace and tickets a call may need, for the caller to allocate.
-ILB_EXPORT long long ilb_gemm_tc_workspace_floats() { return 8ll << 20; }   // 32 MiB
-ILB_EXPORT int ilb_gemm_tc_max_tickets() { return 4096; }
+// Elements of 32-bit workspace and tickets a call may need, for the caller to allocate:
+// two [256][128] slots per CTA of the largest grid, one ticket per output tile.
+ILB_EXPORT long long ilb_gemm_tc_workspace_floats() { return 2ll * 256 * 256 * 128; }
+ILB_EXPORT int ilb_gemm_tc_max_tickets() { return 1 << 16; }
 
 // What the kernel can take: bf16 operands, K and the leading dimensions multiples of 8
 // (16-byte rows for TMA), 16-byte aligned bases.
@@ -395,16 +459,18 @@ ILB_EXPORT int ilb_gemm_tc_supported(int M, int N, int K, int lda, int ldw) {
   return (M > 0 && N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0) ? 1 : 0;
 }
 
+// max_ctas > 0 caps the grid (tests use it to force many partial tiles).
 ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void* out, int out_f32,
                            int M, int N, int K, int lda, int ldw, int ldo, int accumulate,
                            float* workspace, long long workspace_floats, int* tickets, int n_tickets,
-                           int* error_flag, int force_splits, cudaStream_t stream) {
+                           int* error_flag, int max_ctas, cudaStream_t stream) {
   ILB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
   ILB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
               "gemm_tc: K (%d) and the leading dimensions (%d, %d) must be multiples of 8", K, lda, ldw);
   ILB_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
   ILB_REQUIRE(!accumulate || out_f32, "gemm_tc: accumulation needs a 32-bit output");
   ILB_REQUIRE(ldo >= N, "gemm_tc: output leading dimension too small");
+  ILB_REQUIRE(workspace != nullptr && tickets != nullptr, "gemm_tc: workspace and tickets are required");
 
   Params p{};
   p.out = out; p.bias = bias; p.partial = workspace; p.tickets = tickets; p.error_flag = error_flag;
@@ -418,26 +484,16 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   if (swap) bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
   else bn = N >= 256 ? 256 : 128;
   const int x_rows = swap ? N : M, y_rows = swap ? M : N;
-  p.x_rows = x_rows; p.y_rows = y_rows;
-  const int tiles_x = (x_rows + kTileX - 1) / kTileX, tiles_y = (y_rows + bn - 1) / bn;
-  const int tiles = tiles_x * tiles_y;
+  p.tiles_x = (x_rows + kTileX - 1) / kTileX;
+  p.tiles_y = (y_rows + bn - 1) / bn;
+  const long long tiles = (long long)p.tiles_x * p.tiles_y;
+  p.units = tiles * p.k_blocks;
+  ILB_REQUIRE(tiles <= n_tickets, "gemm_tc: %lld output tiles exceed the %d tickets", tiles, n_tickets);
 
-  // Split K until roughly two CTAs per SM are in flight, keeping at least 4 K blocks each.
-  int splits = 1;
-  if (force_splits > 0) {
-    splits = force_splits;
-  } else if (tiles < 2 * 148) {
-    splits = (2 * 148 + tiles - 1) / tiles;
-    const int cap = p.k_blocks / 4 > 0 ? p.k_blocks / 4 : 1;
-    if (splits > cap) splits = cap;
-    if (splits > 16) splits = 16;
-  }
-  if (splits > p.k_blocks) splits = p.k_blocks;
-  if (splits > 1) {
-    const long long need = (long long)tiles * splits * bn * kTileX;
-    if (workspace == nullptr || tickets == nullptr || need > workspace_floats || tiles > n_tickets) splits = 1;
-  }
-  p.splits = splits;
+  long long grid = sm_count();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (grid > p.units) grid = p.units;
+  ILB_REQUIRE(2 * grid * bn * kTileX <= workspace_floats, "gemm_tc: workspace too small");
 
   CUtensorMap mx, my;
   const void* X = swap ? W : A;
@@ -445,19 +501,17 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   const int ldx = swap ? ldw : lda, ldy = swap ? lda : ldw;
   if (make_map(&mx, X, x_rows, K, ldx, kTileX)) return -1;
   if (make_map(&my, Y, y_rows, K, ldy, bn)) return -1;
-  dim3 grid(tiles_x, tiles_y, splits);
-  ILB_REQUIRE(tiles_y <= 65535 && splits <= 65535, "gemm_tc: grid too large");
 
   if (swap) {
     switch (bn) {
-      case 16: return launch<16, 8, true>(mx, my, p, grid, stream);
-      case 32: return launch<32, 8, true>(mx, my, p, grid, stream);
-      case 64: return launch<64, 6, true>(mx, my, p, grid, stream);
-      default: return launch<128, 4, true>(mx, my, p, grid, stream);
+      case 16: return launch<16, 10, true>(mx, my, p, (int)grid, stream);
+      case 32: return launch<32, 9, true>(mx, my, p, (int)grid, stream);
+      case 64: return launch<64, 8, true>(mx, my, p, (int)grid, stream);
+      default: return launch<128, 6, true>(mx, my, p, (int)grid, stream);
     }
   }
-  if (bn == 256) return launch<256, 4, false>(mx, my, p, grid, stream);
-  return launch<128, 5, false>(mx, my, p, grid, stream);
+  if (bn == 256) return launch<256, 4, false>(mx, my, p, (int)grid, stream);
+  return launch<128, 6, false>(mx, my, p, (int)grid, stream);
 }
 
 ILB_DEFINE_LAST_ERROR()

@@ -256,7 +256,7 @@ def gemm_tc_eligible(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> boo
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-            accumulate: bool = False, force_splits: int = 0) -> None:
+            accumulate: bool = False, max_ctas: int = 0) -> None:
     """out (+)= a @ w.T (+ bias) on tcgen05 tensor cores (see gemm_tcgen05.cu)."""
     _need(a, "gemm a", torch.bfloat16); _need(w, "gemm w", torch.bfloat16); _need(out, "gemm out")
     _need(bias, "gemm bias", torch.float32)
@@ -270,7 +270,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
     _call("gemm_tcgen05", "ilb_gemm_tc", _ptr(a), _ptr(w), _ptr(bias), _ptr(out),
           _i(1 if out.dtype == torch.float32 else 0), _i(M), _i(N), _i(K), _i(a.stride(0)), _i(w.stride(0)),
           _i(out.stride(0)), _i(1 if accumulate else 0), _ptr(st.workspace), ctypes.c_longlong(st.floats),
-          _ptr(st.tickets), _i(st.n_tickets), _ptr(st.error), _i(force_splits), _stream(out))
+          _ptr(st.tickets), _i(st.n_tickets), _ptr(st.error), _i(max_ctas), _stream(out))
 
 
 def check_device_errors() -> None:

@@ -303,23 +303,25 @@ def test_gemm_tcgen05(M, N, K, out_dtype, bias, accumulate):
     close(out, ref, out_dtype, scale=float(ref.abs().max()), what=f"gemm_tc {M}x{N}x{K}")
 
 
-@pytest.mark.parametrize("splits", [1, 2, 3, 5, 8])
-def test_gemm_tcgen05_split_k_is_deterministic_and_reusable(splits):
-    """Partials are added in split order by whichever CTA arrives last: two runs give the
-    same bits, and the tickets are back at zero for the next launch."""
+@pytest.mark.parametrize("max_ctas", [0, 1, 3, 7, 50])
+@pytest.mark.parametrize("M,N,K", [(8, 640, 2048), (200, 700, 1024)])
+def test_gemm_tcgen05_shared_tiles_are_deterministic_and_reusable(max_ctas, M, N, K):
+    """However the K blocks of a tile are shared among CTAs, the shares are added in K
+    order by whichever CTA arrives last: runs give the same bits, and the tickets are back
+    at zero for the next launch."""
     o = ops()
-    M, N, K = 8, 640, 2048
+    torch.manual_seed(max_ctas + M)
     a = torch.randn(M, K).to(torch.bfloat16).cuda()
     w = (torch.randn(N, K) * 0.05).to(torch.bfloat16).cuda()
     outs = []
     for _ in range(3):
         out = torch.empty(M, N, device="cuda")
-        o.gemm_tc(a, w, out, force_splits=splits)
+        o.gemm_tc(a, w, out, max_ctas=max_ctas)
         outs.append(out.clone())
     o.check_device_errors()
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     ref = a.double().cpu() @ w.double().cpu().T
-    close(outs[0], ref, "float32", scale=float(ref.abs().max()), what="split-k")
+    close(outs[0], ref, "float32", scale=float(ref.abs().max()), what="stream-k")
     from inferloop_b200.csrc.ops import _tc_state
     assert int(_tc_state(a.device).tickets.abs().sum()) == 0
 
