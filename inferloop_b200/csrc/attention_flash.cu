@@ -11,7 +11,8 @@
 //            key tiles from the window start to the last row's position (double buffered).
 //   decode   one token per sequence: the keys are cut into chunks of `chunk` keys whose
 //            boundaries depend on the key index alone; one CTA per (kv head, sequence,
-//            chunk), its 4 warps take 64 keys each.  A CTA parks (max, sum, O) of its chunk
+//            chunk) walks its chunk in 64-key tiles (double buffered), each of its 4 warps
+//            taking 16 keys of every tile.  A CTA parks (max, sum, O) of its chunk
 //            in a 32-bit scratch buffer and takes a ticket; the CTA with the last ticket of
 //            a (sequence, kv head) merges the chunks in chunk order and writes the output.
 //            Nothing ever waits on another CTA.
@@ -66,28 +67,55 @@ struct Cache {
   int page_size, num_pages, nkv;
 };
 
-// Copy keys [key0, key0 + 64) of kv head `kvh` into a [64][D + 8] tile; rows whose key is
-// outside [lo, hi) or whose page is not held are zero-filled.  NT threads take part.
+// Copy keys [key0, key0 + 64) of kv head `kvh` of BOTH caches into two [64][D + 8] tiles;
+// rows whose key is outside [lo, hi) or whose page is not held are zero-filled.  NT
+// threads take part; each owns one 16-byte column of the rows it copies, so its page
+// lookups are independent of one another and are issued together.
 template <int D, int NT>
-__device__ __forceinline__ void load_tile(__nv_bfloat16* dst, const __nv_bfloat16* cache, const Cache& c,
-                                          const int* __restrict__ table, int max_blocks, int kvh, int key0,
-                                          int lo, int hi, int tid) {
+__device__ __forceinline__ void load_tiles(__nv_bfloat16* kdst, __nv_bfloat16* vdst, const Cache& c,
+                                           const int* __restrict__ table, int max_blocks, int kvh, int key0,
+                                           int lo, int hi, int tid) {
   constexpr int kStride = D + 8;
   constexpr int kChunks = D / 8;                 // 16-byte pieces per row
-  for (int idx = tid; idx < kTileKeys * kChunks; idx += NT) {
-    const int r = idx / kChunks, ch = idx % kChunks;
-    const int key = key0 + r;
-    const __nv_bfloat16* src = cache;
-    int bytes = 0;
-    if (key >= lo && key < hi) {
+  if constexpr (NT % kChunks == 0 && (kTileKeys * kChunks) % NT == 0) {
+    constexpr int kRowsPerIter = NT / kChunks;
+    constexpr int kIters = kTileKeys / kRowsPerIter;
+    const int ch = tid % kChunks, r0 = tid / kChunks;
+    size_t off[kIters];
+    int bytes[kIters];
+#pragma unroll
+    for (int it = 0; it < kIters; ++it) {
+      const int key = key0 + r0 + it * kRowsPerIter;
       const int blk = key / c.page_size;
-      const int page = blk < max_blocks ? table[blk] : -1;
-      if (page >= 0 && page < c.num_pages) {
-        src = cache + (((size_t)page * c.nkv + kvh) * c.page_size + (key % c.page_size)) * D + ch * 8;
-        bytes = 16;
-      }
+      const bool in = key >= lo && key < hi && blk < max_blocks;
+      const int page = in ? __ldg(table + blk) : -1;
+      const bool ok = page >= 0 && page < c.num_pages;
+      off[it] = ok ? (((size_t)page * c.nkv + kvh) * c.page_size + (key % c.page_size)) * D + ch * 8 : 0;
+      bytes[it] = ok ? 16 : 0;
     }
-    cp_async_16(smem_u32(dst + r * kStride + ch * 8), src, bytes);
+#pragma unroll
+    for (int it = 0; it < kIters; ++it) {
+      const int r = r0 + it * kRowsPerIter;
+      cp_async_16(smem_u32(kdst + r * kStride + ch * 8), c.k + off[it], bytes[it]);
+      cp_async_16(smem_u32(vdst + r * kStride + ch * 8), c.v + off[it], bytes[it]);
+    }
+  } else {
+    for (int idx = tid; idx < kTileKeys * kChunks; idx += NT) {
+      const int r = idx / kChunks, ch = idx % kChunks;
+      const int key = key0 + r;
+      size_t off = 0;
+      int bytes = 0;
+      if (key >= lo && key < hi) {
+        const int blk = key / c.page_size;
+        const int page = blk < max_blocks ? __ldg(table + blk) : -1;
+        if (page >= 0 && page < c.num_pages) {
+          off = (((size_t)page * c.nkv + kvh) * c.page_size + (key % c.page_size)) * D + ch * 8;
+          bytes = 16;
+        }
+      }
+      cp_async_16(smem_u32(kdst + r * kStride + ch * 8), c.k + off, bytes);
+      cp_async_16(smem_u32(vdst + r * kStride + ch * 8), c.v + off, bytes);
+    }
   }
 }
 
@@ -107,23 +135,25 @@ struct RowState {
   }
 };
 
-// One 64-key tile for one warp's 16 rows.  pos[2] / lo[2]: last and first visible key of
-// rows g and g + 8 (pos < lo hides everything).  `hi`: keys >= hi do not exist.
-template <int D>
+// NB * 8 keys (rows of `ks` / `vs`, the first being key `key0`) for one warp's 16 rows.
+// pos[2] / lo[2]: last and first visible key of rows g and g + 8 (pos < lo hides
+// everything).  `hi`: keys >= hi do not exist.
+template <int D, int NB>
 __device__ __forceinline__ void tile_step(RowState<D>& st, const uint32_t (&q)[D / 16][4],
                                           const __nv_bfloat16* ks, const __nv_bfloat16* vs, int key0,
                                           const int (&pos)[2], const int (&lo)[2], int hi, float scale_log2, int lane) {
+  static_assert(NB % 2 == 0, "keys are consumed 16 at a time");
   constexpr int kStride = D + 8;
   const int g = lane >> 2, t = lane & 3;
-  float s[8][4];
+  float s[NB][4];
 #pragma unroll
-  for (int nb = 0; nb < 8; ++nb)
+  for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
     for (int e = 0; e < 4; ++e) s[nb][e] = 0.f;
 #pragma unroll
   for (int kk = 0; kk < D / 16; kk += 2) {
 #pragma unroll
-    for (int nb = 0; nb < 8; ++nb) {
+    for (int nb = 0; nb < NB; ++nb) {
       uint32_t r0, r1, r2, r3;
       ldmatrix_x4(smem_u32(ks + (nb * 8 + (lane & 7)) * kStride + kk * 16 + (lane >> 3) * 8), r0, r1, r2, r3);
       mma_16816(s[nb], q[kk], r0, r1);
@@ -132,7 +162,7 @@ __device__ __forceinline__ void tile_step(RowState<D>& st, const uint32_t (&q)[D
   }
   float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-  for (int nb = 0; nb < 8; ++nb)
+  for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int key = key0 + nb * 8 + 2 * t + (e & 1);
@@ -153,7 +183,7 @@ __device__ __forceinline__ void tile_step(RowState<D>& st, const uint32_t (&q)[D
   }
   float sum[2] = {0.f, 0.f};
 #pragma unroll
-  for (int nb = 0; nb < 8; ++nb)
+  for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float p = exp2f(s[nb][e] - base[e >> 1]);
@@ -168,7 +198,7 @@ __device__ __forceinline__ void tile_step(RowState<D>& st, const uint32_t (&q)[D
     st.o[i][2] *= corr[1]; st.o[i][3] *= corr[1];
   }
 #pragma unroll
-  for (int kb = 0; kb < 4; ++kb) {                 // 16 keys per step
+  for (int kb = 0; kb < NB / 2; ++kb) {            // 16 keys per step
     uint32_t a[4];
     a[0] = pack_bf16(s[2 * kb][0], s[2 * kb][1]);
     a[1] = pack_bf16(s[2 * kb][2], s[2 * kb][3]);
@@ -211,6 +241,8 @@ struct PrefillParams {
 template <int D>
 __global__ void __launch_bounds__(kWarps * 32)
 prefill_kernel(const PrefillParams p) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
   constexpr int kStride = D + 8;
   constexpr int kTileElems = kTileKeys * kStride;
   extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -262,8 +294,7 @@ prefill_kernel(const PrefillParams p) {
   auto issue = [&](int i) {
     __nv_bfloat16* buf = smem + (i & 1) * 2 * kTileElems;
     const int key0 = (first_tile + i) * kTileKeys;
-    load_tile<D, kWarps * 32>(buf, p.cache.k, p.cache, table, p.max_blocks, kvh, key0, key_lo, hi, threadIdx.x);
-    load_tile<D, kWarps * 32>(buf + kTileElems, p.cache.v, p.cache, table, p.max_blocks, kvh, key0, key_lo, hi, threadIdx.x);
+    load_tiles<D, kWarps * 32>(buf, buf + kTileElems, p.cache, table, p.max_blocks, kvh, key0, key_lo, hi, threadIdx.x);
     cp_async_commit();
   };
   issue(0);
@@ -274,7 +305,7 @@ prefill_kernel(const PrefillParams p) {
     const int key0 = (first_tile + i) * kTileKeys;
     // a warp whose rows cannot see this tile skips the math (the barrier is kept)
     const int wpos = __reduce_max_sync(0xffffffffu, max(pos[0], pos[1]));
-    if (key0 <= wpos) tile_step<D>(st, q, buf, buf + kTileElems, key0, pos, lo, hi, p.scale_log2, lane);
+    if (key0 <= wpos) tile_step<D, 8>(st, q, buf, buf + kTileElems, key0, pos, lo, hi, p.scale_log2, lane);
     __syncthreads();
   }
 #pragma unroll
@@ -305,18 +336,22 @@ struct DecodeParams {
 template <int D>
 __global__ void __launch_bounds__(kWarps * 32)
 decode_kernel(const DecodeParams p) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
   constexpr int kStride = D + 8;
   constexpr int kTileElems = kTileKeys * kStride;
   constexpr int kRec = D + 2;                      // O row, then max and sum
+  constexpr int kKeysPerWarp = kTileKeys / kWarps; // each warp takes 16 keys of every tile
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [warps][K, V][64][D + 8]
+  __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [2][K, V][64][D + 8]
+  float* merge = reinterpret_cast<float*>(smem_raw);                  // reused once the tiles are consumed
   __shared__ int s_last;
   const int G = p.nq / p.cache.nkv;
   const int kvh = blockIdx.x, seq = blockIdx.y, chunk_i = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int tok = p.cu_q[seq];
-  const int pos = p.positions[tok];
   if (p.cu_q[seq + 1] - tok != 1) return;          // decode handles one token per sequence
+  const int pos = p.positions[tok];
   const int lo = (p.window > 0 && pos + 1 > p.window) ? pos + 1 - p.window : 0;
   const int hi = pos + 1;
   const int c_lo = lo / p.chunk, c_hi = pos / p.chunk;
@@ -325,14 +360,19 @@ decode_kernel(const DecodeParams p) {
   const int* table = p.block_table + (size_t)seq * p.max_blocks;
   const int key_begin = chunk_i * p.chunk;
   const int key_end = min(key_begin + p.chunk, hi);
+  const int n_tiles = (key_end - key_begin + kTileKeys - 1) / kTileKeys;
   float* rec_base = p.scratch + (((size_t)seq * p.cache.nkv + kvh) * p.max_chunks) * (size_t)(G * kRec);
 
-  __nv_bfloat16* kt = smem + warp * 2 * kTileElems;
-  __nv_bfloat16* vt = kt + kTileElems;
-  // merge area (reuses nothing of the tiles): [warps][16][D + 2] floats after the tiles
-  float* merge = reinterpret_cast<float*>(smem + kWarps * 2 * kTileElems);
+  auto issue = [&](int i) {
+    __nv_bfloat16* buf = smem + (i & 1) * 2 * kTileElems;
+    const int key0 = key_begin + i * kTileKeys;
+    load_tiles<D, kWarps * 32>(buf, buf + kTileElems, p.cache, table, p.max_blocks, kvh, key0, lo, key_end, threadIdx.x);
+    cp_async_commit();
+  };
 
   for (int rb = 0; rb < p.rows16; rb += 16) {      // 16 query heads of the group at a time
+    issue(0);
+    if (n_tiles > 1) issue(1);
     RowState<D> st;
     st.init();
     int rpos[2], rlo[2];
@@ -347,15 +387,17 @@ decode_kernel(const DecodeParams p) {
     }
     uint32_t q[D / 16][4];
     load_q<D>(q, qrow[0], qrow[1], lane);
-    // this warp's keys: tiles warp, warp + 4, ... of the chunk
-    for (int key0 = key_begin + warp * kTileKeys; key0 < key_end; key0 += kWarps * kTileKeys) {
-      __syncwarp();
-      load_tile<D, 32>(kt, p.cache.k, p.cache, table, p.max_blocks, kvh, key0, lo, key_end, lane);
-      load_tile<D, 32>(vt, p.cache.v, p.cache, table, p.max_blocks, kvh, key0, lo, key_end, lane);
-      cp_async_commit();
-      cp_async_wait<0>();
-      __syncwarp();
-      tile_step<D>(st, q, kt, vt, key0, rpos, rlo, key_end, p.scale_log2, lane);
+    for (int i = 0; i < n_tiles; ++i) {
+      if (i + 1 < n_tiles) cp_async_wait<1>(); else cp_async_wait<0>();
+      __syncthreads();
+      const __nv_bfloat16* buf = smem + (i & 1) * 2 * kTileElems;
+      const int key0 = key_begin + i * kTileKeys + warp * kKeysPerWarp;
+      if (key0 < key_end)
+        tile_step<D, kKeysPerWarp / 8>(st, q, buf + warp * kKeysPerWarp * kStride,
+                                       buf + kTileElems + warp * kKeysPerWarp * kStride, key0, rpos, rlo, key_end,
+                                       p.scale_log2, lane);
+      __syncthreads();
+      if (i + 2 < n_tiles) issue(i + 2);
     }
     // ---- merge the four warps (fixed order) into the chunk's record
 #pragma unroll
@@ -370,25 +412,35 @@ decode_kernel(const DecodeParams p) {
     }
     __syncthreads();
     float* rec = rec_base + ((size_t)chunk_i * G + rb) * kRec;
-    for (int idx = threadIdx.x; idx < 16 * kRec; idx += kWarps * 32) {
+    const int live_rows = min(16, G - rb);
+    for (int idx = threadIdx.x; idx < live_rows * kRec; idx += kWarps * 32) {
       const int row = idx / kRec, c = idx % kRec;
-      if (rb + row >= G) break;
-      float m_all = -INFINITY;
+      float mw[kWarps], m_all = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < kWarps; ++w) m_all = fmaxf(m_all, merge[((size_t)w * 16 + row) * kRec + D]);
+      for (int w = 0; w < kWarps; ++w) { mw[w] = merge[((size_t)w * 16 + row) * kRec + D]; m_all = fmaxf(m_all, mw[w]); }
       float acc = 0.f;
       if (c == D) acc = m_all;
       else {
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) {
-          const float mw = merge[((size_t)w * 16 + row) * kRec + D];
-          const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m_all);
+          const float f = (mw[w] == -INFINITY) ? 0.f : exp2f(mw[w] - m_all);
           acc += merge[((size_t)w * 16 + row) * kRec + c] * f;      // c == D + 1 sums l the same way
         }
       }
       rec[idx] = acc;
     }
     __syncthreads();
+  }
+  if (n_chunks == 1) {
+    // the only chunk: its record is the answer (read back through L2 by the writers' block)
+    __threadfence_block();
+    for (int idx = threadIdx.x; idx < G * D; idx += kWarps * 32) {
+      const int h = idx / D, c = idx % D;
+      const float* rec = rec_base + ((size_t)chunk_i * G + h) * kRec;
+      const float l = rec[D + 1];
+      p.out[(size_t)tok * p.out_stride + (size_t)(kvh * G + h) * D + c] = __float2bfloat16_rn(l > 0.f ? rec[c] / l : 0.f);
+    }
+    return;
   }
   // ---- ticket: the last chunk of this (sequence, kv head) merges all chunks in order
   __threadfence();
@@ -402,24 +454,56 @@ decode_kernel(const DecodeParams p) {
   __syncthreads();
   if (!s_last) return;
   __threadfence();
+  // weights of the chunks per head: f[h][ci] = 2^(m_ci - M) / L, all loads issued at once
+  float* fw = merge;                               // [G][n_chunks]
+  for (int h = threadIdx.x; h < G; h += kWarps * 32) {
+    float m_all = -INFINITY;
+    for (int c0 = c_lo; c0 <= c_hi; c0 += 8) {
+      float mm[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mm[j] = (c0 + j <= c_hi) ? __ldcg(rec_base + ((size_t)(c0 + j) * G + h) * kRec + D) : -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) m_all = fmaxf(m_all, mm[j]);
+    }
+    float l_all = 0.f;
+    for (int c0 = c_lo; c0 <= c_hi; c0 += 8) {
+      float mm[8], ll[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const bool ok = c0 + j <= c_hi;
+        mm[j] = ok ? __ldcg(rec_base + ((size_t)(c0 + j) * G + h) * kRec + D) : -INFINITY;
+        ll[j] = ok ? __ldcg(rec_base + ((size_t)(c0 + j) * G + h) * kRec + D + 1) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float f = (mm[j] == -INFINITY) ? 0.f : exp2f(mm[j] - m_all);
+        if (c0 + j <= c_hi) fw[h * n_chunks + (c0 + j - c_lo)] = f;
+        l_all += ll[j] * f;                        // chunk order
+      }
+    }
+    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+    for (int ci = 0; ci < n_chunks; ++ci) fw[h * n_chunks + ci] *= inv;
+  }
+  __syncthreads();
   for (int idx = threadIdx.x; idx < G * D; idx += kWarps * 32) {
     const int h = idx / D, c = idx % D;
-    float m_all = -INFINITY;
-    for (int ci = c_lo; ci <= c_hi; ++ci) m_all = fmaxf(m_all, __ldcg(rec_base + ((size_t)ci * G + h) * kRec + D));
-    float o = 0.f, l = 0.f;
-    for (int ci = c_lo; ci <= c_hi; ++ci) {
-      const float* rec = rec_base + ((size_t)ci * G + h) * kRec;
-      const float mc = __ldcg(rec + D);
-      const float f = (mc == -INFINITY) ? 0.f : exp2f(mc - m_all);
-      o += __ldcg(rec + c) * f;
-      l += __ldcg(rec + D + 1) * f;
+    float o = 0.f;
+    for (int c0 = 0; c0 < n_chunks; c0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = (c0 + j < n_chunks) ? __ldcg(rec_base + ((size_t)(c_lo + c0 + j) * G + h) * kRec + c) : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) if (c0 + j < n_chunks) o += v[j] * fw[h * n_chunks + c0 + j];
     }
-    p.out[(size_t)tok * p.out_stride + (size_t)(kvh * G + h) * D + c] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+    p.out[(size_t)tok * p.out_stride + (size_t)(kvh * G + h) * D + c] = __float2bfloat16_rn(o);
   }
 }
 
 template <int D> size_t prefill_smem() { return (size_t)2 * 2 * kTileKeys * (D + 8) * 2; }
-template <int D> size_t decode_smem() { return (size_t)kWarps * 2 * kTileKeys * (D + 8) * 2 + (size_t)kWarps * 16 * (D + 2) * 4; }
+template <int D> size_t decode_smem() {
+  const size_t tiles = (size_t)2 * 2 * kTileKeys * (D + 8) * 2, merge = (size_t)kWarps * 16 * (D + 2) * 4;
+  return tiles > merge ? tiles : merge;
+}
 
 template <int D>
 int launch_prefill(const PrefillParams& p, int n_tiles, cudaStream_t stream) {
@@ -430,7 +514,7 @@ int launch_prefill(const PrefillParams& p, int n_tiles, cudaStream_t stream) {
     if (e != cudaSuccess) return fail("attention prefill: cannot reserve %zu bytes of shared memory", smem);
     configured = true;
   }
-  prefill_kernel<D><<<dim3(n_tiles, p.cache.nkv), kWarps * 32, smem, stream>>>(p);
+  ilb::launch(prefill_kernel<D>, dim3(n_tiles, p.cache.nkv), dim3(kWarps * 32), smem, stream, p);
   return check_launch("attention prefill");
 }
 
@@ -443,7 +527,7 @@ int launch_decode(const DecodeParams& p, cudaStream_t stream) {
     if (e != cudaSuccess) return fail("attention decode: cannot reserve %zu bytes of shared memory", smem);
     configured = true;
   }
-  decode_kernel<D><<<dim3(p.cache.nkv, p.n_seqs, p.max_chunks), kWarps * 32, smem, stream>>>(p);
+  ilb::launch(decode_kernel<D>, dim3(p.cache.nkv, p.n_seqs, p.max_chunks), dim3(kWarps * 32), smem, stream, p);
   return check_launch("attention decode");
 }
 

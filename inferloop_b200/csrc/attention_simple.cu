@@ -26,6 +26,8 @@ paged_attention_simple_kernel(const TQ* __restrict__ q, TQ* __restrict__ out,
                               const int* __restrict__ block_table, int max_blocks, int page_size,
                               int num_pages, int window, float scale, int nq, int nkv, int d,
                               int q_stride, int out_stride) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
   __shared__ float qs[kMaxHeadDim];
   __shared__ float red_m[kWarps], red_l[kWarps];
   __shared__ float red_acc[kWarps][kMaxHeadDim];
@@ -120,7 +122,7 @@ ILB_EXPORT int ilb_paged_attention_simple(
   if (n_tokens == 0) return 0;
   dim3 grid(n_tokens, nq);
 #define ILB_LAUNCH(TQ, TC)                                                                    \
-  paged_attention_simple_kernel<TQ, TC><<<grid, kWarps * 32, 0, stream>>>(                     \
+  ilb::launch(paged_attention_simple_kernel<TQ, TC>, dim3(grid), dim3(kWarps * 32), 0, stream,                      \
       (const TQ*)q, (TQ*)out, (const TC*)k_cache, (const TC*)v_cache, positions, seq_of_token, \
       block_table, max_blocks, page_size, num_pages, window, scale, nq, nkv, d, q_stride,      \
       out_stride)

@@ -133,6 +133,12 @@ def compile_module(name: str, verbose: bool = False) -> str:
             os.remove(tmp)
         raise BuildError(f"nvcc failed for {name}.cu:\n{' '.join(cmd)}\n{out}")
     os.replace(tmp, final)
+    for old in os.listdir(out_dir):          # libraries of older sources are of no use
+        if old.startswith(name + "-") and old.endswith(".so") and old != os.path.basename(final):
+            try:
+                os.remove(os.path.join(out_dir, old))
+            except OSError:
+                pass
     _say(f"built {os.path.basename(final)} in {time.time() - t0:.1f} s")
     if verbose and out:
         print(out, file=sys.stderr)

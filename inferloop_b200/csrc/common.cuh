@@ -10,6 +10,8 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <stdarg.h>
+#include <stdlib.h>
+#include <utility>
 
 namespace ilb {
 
@@ -73,6 +75,43 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   }
   __syncthreads();
   return scratch[32];
+}
+
+// ---------------------------------------------------------------- dependent launches
+// Every kernel of this package is launched with programmatic stream serialization: it
+// may become resident while the kernel before it in the stream is still running.  The
+// contract each kernel keeps: it calls pdl_wait() before it reads or writes anything in
+// global memory that an earlier kernel may write or read (kernel parameters and weights
+// are free), and it calls pdl_launch_dependents() once letting the next kernel start
+// cannot hurt.  pdl_wait() returns when the preceding kernel has completed and its
+// writes are visible, so chains of such kernels stay ordered.  ILB_PDL=0 in the
+// environment launches everything the ordinary, fully serialized way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("ILB_PDL");
+    on = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return on != 0;
+}
+
+template <typename... KArgs, typename... Args>
+static inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
 }
 
 }  // namespace ilb

@@ -14,6 +14,8 @@ using namespace ilb;
 template <typename TT>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TT* __restrict__ table,
                              float* __restrict__ out, int hidden, int vocab) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
   const int t = blockIdx.x;
   const int tok = tokens[t];
   const bool ok = tok >= 0 && tok < vocab;
@@ -29,9 +31,9 @@ ILB_EXPORT int ilb_embed(const int* tokens, const void* table, int table_dtype, 
   if (n_tokens == 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == kF32)
-    embed_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, out, hidden, vocab);
+    ilb::launch(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table, out, hidden, vocab);
   else if (table_dtype == kBF16)
-    embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, out, hidden, vocab);
+    ilb::launch(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table, out, hidden, vocab);
   else
     return fail("embed: unknown table dtype %d", table_dtype);
   return check_launch("embed");
@@ -39,10 +41,56 @@ ILB_EXPORT int ilb_embed(const int* tokens, const void* table, int table_dtype, 
 
 // ---------------------------------------------------------------- RMSNorm
 // One block per row.  The block size depends on the width alone, so the order of the
-// additions for a row never depends on how many rows the launch holds.
+// additions for a row never depends on how many rows the launch holds.  A row of up to
+// 4 * 1024 * kVec elements is read once with 16-byte loads and kept in registers.
+constexpr int kVec = 2;                 // float4 loads per thread
+
+template <typename TO>
+__global__ void __launch_bounds__(1024)
+rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out,
+                   int width, float eps) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  __shared__ float scratch[33];
+  const float4* row = reinterpret_cast<const float4*>(x + (size_t)blockIdx.x * width);
+  const float4* w4 = reinterpret_cast<const float4*>(w);
+  const int n4 = width / 4;
+  float4 v[kVec], g[kVec];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kVec; ++i) {
+    const int j = threadIdx.x + i * blockDim.x;
+    v[i] = j < n4 ? row[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+    g[i] = j < n4 ? w4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+    ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+  TO* o = out + (size_t)blockIdx.x * width;
+#pragma unroll
+  for (int i = 0; i < kVec; ++i) {
+    const int j = threadIdx.x + i * blockDim.x;
+    if (j >= n4) continue;
+    const float a = v[i].x * inv * g[i].x, b = v[i].y * inv * g[i].y;
+    const float c = v[i].z * inv * g[i].z, d = v[i].w * inv * g[i].w;
+    if constexpr (sizeof(TO) == 4) {
+      reinterpret_cast<float4*>(o)[j] = make_float4(a, b, c, d);
+    } else {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(o)[j] = pk;
+    }
+  }
+}
+
 template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                TO* __restrict__ out, int width, float eps) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
   __shared__ float scratch[33];
   const float* row = x + (size_t)blockIdx.x * width;
   float ss = 0.f;
@@ -68,14 +116,25 @@ ILB_EXPORT int ilb_rmsnorm(const float* x, const float* w, void* out, int out_dt
                            int width, float eps, cudaStream_t stream) {
   ILB_REQUIRE(rows >= 0 && width > 0, "rmsnorm: bad sizes rows=%d width=%d", rows, width);
   ILB_REQUIRE(eps > 0.f, "rmsnorm: eps must be positive");
+  ILB_REQUIRE(out_dtype == kF32 || out_dtype == kBF16, "rmsnorm: unknown output dtype %d", out_dtype);
   if (rows == 0) return 0;
+  const bool vec = width % 4 == 0 && width >= 1024 && width <= 4 * 1024 * kVec &&
+                   ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0);
+  if (vec) {
+    // threads = width / (4 * kVec) rounded up to a warp: the row is read exactly once
+    int threads = (width / 4 + kVec - 1) / kVec;
+    threads = (threads + 31) / 32 * 32;
+    if (out_dtype == kF32)
+      ilb::launch(rmsnorm_vec_kernel<float>, dim3(rows), dim3(threads), 0, stream, x, w, (float*)out, width, eps);
+    else
+      ilb::launch(rmsnorm_vec_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, x, w, (__nv_bfloat16*)out, width, eps);
+    return check_launch("rmsnorm");
+  }
   const int threads = norm_threads(width);
   if (out_dtype == kF32)
-    rmsnorm_kernel<float><<<rows, threads, 0, stream>>>(x, w, (float*)out, width, eps);
-  else if (out_dtype == kBF16)
-    rmsnorm_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>(x, w, (__nv_bfloat16*)out, width, eps);
+    ilb::launch(rmsnorm_kernel<float>, dim3(rows), dim3(threads), 0, stream, x, w, (float*)out, width, eps);
   else
-    return fail("rmsnorm: unknown output dtype %d", out_dtype);
+    ilb::launch(rmsnorm_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, x, w, (__nv_bfloat16*)out, width, eps);
   return check_launch("rmsnorm");
 }
 
@@ -89,6 +148,8 @@ __device__ __forceinline__ float sigmoid_stable(float x) {
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate, const T* __restrict__ up,
                                 T* __restrict__ out, int rows, int width, int in_stride) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
   const size_t n = (size_t)rows * width;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (size_t)gridDim.x * blockDim.x) {
@@ -108,9 +169,9 @@ ILB_EXPORT int ilb_silu_mul(const void* in, void* out, int dtype, int rows, int 
   const int threads = 256;
   const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
   if (dtype == kF32)
-    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)in, (const float*)in + width, (float*)out, rows, width, in_stride);
+    ilb::launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)in, (const float*)in + width, (float*)out, rows, width, in_stride);
   else if (dtype == kBF16)
-    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)in, (const __nv_bfloat16*)in + width, (__nv_bfloat16*)out, rows, width, in_stride);
+    ilb::launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)in, (const __nv_bfloat16*)in + width, (__nv_bfloat16*)out, rows, width, in_stride);
   else
     return fail("silu_mul: unknown dtype %d", dtype);
   return check_launch("silu_mul");
@@ -119,6 +180,8 @@ ILB_EXPORT int ilb_silu_mul(const void* in, void* out, int dtype, int rows, int 
 // ---------------------------------------------------------------- row gather
 __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ idx,
                                    float* __restrict__ out, int width, int n_rows_in) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
   const int r = idx[blockIdx.x];
   const bool ok = r >= 0 && r < n_rows_in;
   for (int i = threadIdx.x; i < width; i += blockDim.x)
@@ -129,7 +192,7 @@ ILB_EXPORT int ilb_gather_rows(const float* x, const int* idx, float* out, int n
                                int n_rows_in, cudaStream_t stream) {
   ILB_REQUIRE(n_out >= 0 && width > 0, "gather_rows: bad sizes");
   if (n_out == 0) return 0;
-  gather_rows_kernel<<<n_out, 256, 0, stream>>>(x, idx, out, width, n_rows_in);
+  ilb::launch(gather_rows_kernel, dim3(n_out), dim3(256), 0, stream, x, idx, out, width, n_rows_in);
   return check_launch("gather_rows");
 }
 
@@ -139,6 +202,8 @@ ILB_EXPORT int ilb_gather_rows(const float* x, const int* idx, float* out, int n
 __global__ void rope_table_kernel(const int* __restrict__ positions,
                                   const double* __restrict__ inv_freq,
                                   float2* __restrict__ table, int n_tokens, int half) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_tokens * half) return;
   const int t = i / half, f = i % half;
@@ -153,12 +218,14 @@ ILB_EXPORT int ilb_rope_table(const int* positions, const double* inv_freq, floa
   ILB_REQUIRE(n_tokens >= 0 && half > 0, "rope_table: bad sizes");
   if (n_tokens == 0) return 0;
   const int n = n_tokens * half;
-  rope_table_kernel<<<(n + 127) / 128, 128, 0, stream>>>(positions, inv_freq, (float2*)table, n_tokens, half);
+  ilb::launch(rope_table_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, positions, inv_freq, (float2*)table, n_tokens, half);
   return check_launch("rope_table");
 }
 
 // ---------------------------------------------------------------- x += y (32-bit)
 __global__ void add_inplace_kernel(float* __restrict__ x, const float* __restrict__ y, size_t n) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (size_t)gridDim.x * blockDim.x)
     x[i] += y[i];
@@ -170,7 +237,7 @@ ILB_EXPORT int ilb_add_inplace(float* x, const float* y, long long n, cudaStream
   const int threads = 256;
   long long blocks = (n + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  add_inplace_kernel<<<(int)blocks, threads, 0, stream>>>(x, y, (size_t)n);
+  ilb::launch(add_inplace_kernel, dim3((int)blocks), dim3(threads), 0, stream, x, y, (size_t)n);
   return check_launch("add_inplace");
 }
 
@@ -181,6 +248,8 @@ ILB_EXPORT int ilb_add_inplace(float* x, const float* y, long long n, cudaStream
 __global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict__ positions,
                                       int* __restrict__ kv_len, const int* __restrict__ drawn,
                                       int n_live, int n) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   if (i < n_live) {
@@ -194,7 +263,7 @@ ILB_EXPORT int ilb_decode_advance(int* tokens, int* positions, int* kv_len, cons
                                   int n_live, int n, cudaStream_t stream) {
   ILB_REQUIRE(n >= 0 && n_live >= 0 && n_live <= n, "decode_advance: bad sizes");
   if (n == 0) return 0;
-  decode_advance_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tokens, positions, kv_len, drawn, n_live, n);
+  ilb::launch(decode_advance_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tokens, positions, kv_len, drawn, n_live, n);
   return check_launch("decode_advance");
 }
 

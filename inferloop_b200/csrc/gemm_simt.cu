@@ -17,6 +17,8 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W,
                  const float* __restrict__ bias, TO* __restrict__ out, int M, int N, int K,
                  int lda, int ldw, int ldo, int accumulate) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
   constexpr int BK = 16;
   constexpr int THREADS = (BM / TM) * (BN / TN);
   __shared__ float As[BK][BM + 1];
@@ -79,12 +81,12 @@ static int launch(const void* A, const void* W, const float* bias, void* out, in
   if (M <= 16) {
     constexpr int BM = 16, BN = 32, TM = 2, TN = 2;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_simt_kernel<TA, TO, BM, BN, TM, TN><<<grid, (BM / TM) * (BN / TN), 0, stream>>>(
+    ilb::launch(gemm_simt_kernel<TA, TO, BM, BN, TM, TN>, dim3(grid), dim3((BM / TM) * (BN / TN)), 0, stream, 
         (const TA*)A, (const TA*)W, bias, (TO*)out, M, N, K, lda, ldw, ldo, accumulate);
   } else {
     constexpr int BM = 64, BN = 64, TM = 4, TN = 4;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_simt_kernel<TA, TO, BM, BN, TM, TN><<<grid, (BM / TM) * (BN / TN), 0, stream>>>(
+    ilb::launch(gemm_simt_kernel<TA, TO, BM, BN, TM, TN>, dim3(grid), dim3((BM / TM) * (BN / TN)), 0, stream, 
         (const TA*)A, (const TA*)W, bias, (TO*)out, M, N, K, lda, ldw, ldo, accumulate);
   }
   return check_launch("gemm_simt");

@@ -21,7 +21,10 @@
 // A tile whose K range is shared by several CTAs: each stores its share to a 32-bit
 // workspace slot and takes a ticket; the CTA that takes the last ticket of the tile adds
 // the shares in K order, so the sum does not depend on which CTA finished first, and
-// writes the result.  There is no spin-wait on another CTA anywhere.  Every mbarrier wait is bounded: on expiry the kernel raises a
+// writes the result.  There is no spin-wait on another CTA anywhere.
+// Decode-shaped launches keep their ring below half of an SM's shared memory, so the CTA
+// of the NEXT product can become resident beside this one and have its weight tiles in
+// flight before this kernel has finished (dependent launch, see common.cuh).  Every mbarrier wait is bounded: on expiry the kernel raises a
 // flag in global memory, drains what it armed, frees its tensor memory and returns.
 //
 // The reference computes these products with JIT-compiled tile kernels that target no
@@ -152,7 +155,7 @@ struct Schedule {
 };
 
 template <int BN, int STAGES, bool SWAP>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, (SWAP && BN <= 32) ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, const Params p) {
   constexpr uint32_t kBytesX = kTileX * kBlockK * 2;
   constexpr uint32_t kBytesY = BN * kBlockK * 2;
@@ -171,6 +174,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* flags = reinterpret_cast<volatile int*>(bars + 2 * STAGES + 5);   // [0] = failed, [1] = last ticket
 
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const Schedule sch{p.units, (int)gridDim.x, p.k_blocks};
   const long long u_begin = sch.start(blockIdx.x), u_end = sch.start(blockIdx.x + 1);
@@ -192,24 +196,46 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
+    // The weight operand depends on no earlier kernel, so the first ring of weight
+    // tiles is requested before this kernel waits for its predecessor; the activation
+    // tiles of those stages follow the wait.
     if (lane == 0) {
       bool ok = true;
-      uint32_t it = 0;
-      for (long long u = u_begin; u < u_end && ok;) {
+      const uint32_t n_units = (uint32_t)(u_end - u_begin);
+      const uint32_t n_early = n_units < (uint32_t)STAGES ? n_units : (uint32_t)STAGES;
+      auto coords = [&](uint32_t it, int& kcol, int& x0, int& y0) {
+        const long long u = u_begin + it;
         const long long tile = u / p.k_blocks;
-        const int kb0 = (int)(u % p.k_blocks);
-        const int cnt = (int)min((long long)(p.k_blocks - kb0), u_end - u);
-        const int x0 = (int)(tile % p.tiles_x) * kTileX, y0 = (int)(tile / p.tiles_x) * BN;
-        for (int i = 0; i < cnt; ++i, ++it) {
-          const uint32_t s = it % STAGES;
-          if (it >= STAGES) ok = mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1);
-          if (!ok) break;
-          const uint32_t dst = base + s * kStageBytes;
-          mbar_expect_tx(full0 + 8 * s, kStageBytes);
-          tma_load_2d(dst, &map_x, full0 + 8 * s, (kb0 + i) * kBlockK, x0);
-          tma_load_2d(dst + kBytesX, &map_y, full0 + 8 * s, (kb0 + i) * kBlockK, y0);
-        }
-        u += cnt;
+        kcol = (int)(u % p.k_blocks) * kBlockK;
+        x0 = (int)(tile % p.tiles_x) * kTileX;
+        y0 = (int)(tile / p.tiles_x) * BN;
+      };
+      for (uint32_t it = 0; it < n_early; ++it) {
+        int kcol, x0, y0;
+        coords(it, kcol, x0, y0);
+        const uint32_t dst = base + it * kStageBytes;
+        mbar_expect_tx(full0 + 8 * it, kStageBytes);
+        if (SWAP) tma_load_2d(dst, &map_x, full0 + 8 * it, kcol, x0);
+        else tma_load_2d(dst + kBytesX, &map_y, full0 + 8 * it, kcol, y0);
+      }
+      pdl_wait();
+      for (uint32_t it = 0; it < n_early; ++it) {
+        int kcol, x0, y0;
+        coords(it, kcol, x0, y0);
+        const uint32_t dst = base + it * kStageBytes;
+        if (SWAP) tma_load_2d(dst + kBytesX, &map_y, full0 + 8 * it, kcol, y0);
+        else tma_load_2d(dst, &map_x, full0 + 8 * it, kcol, x0);
+      }
+      for (uint32_t it = n_early; it < n_units; ++it) {
+        const uint32_t s = it % STAGES;
+        ok = mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1);
+        if (!ok) break;
+        int kcol, x0, y0;
+        coords(it, kcol, x0, y0);
+        const uint32_t dst = base + s * kStageBytes;
+        mbar_expect_tx(full0 + 8 * s, kStageBytes);
+        tma_load_2d(dst, &map_x, full0 + 8 * s, kcol, x0);
+        tma_load_2d(dst + kBytesX, &map_y, full0 + 8 * s, kcol, y0);
       }
       if (!ok) { flags[0] = 1; if (p.error_flag) *p.error_flag = 1; }
     }
@@ -249,6 +275,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5)
+    pdl_wait();                               // outputs, shares and tickets belong to earlier kernels until now
     const int quad = warp & 3;                // tensor-memory lanes 32*quad .. 32*quad+31
     const int row = quad * 32 + lane;         // row of the tile this thread owns
     constexpr int CH = BN < 32 ? BN : 32;     // columns per tensor-memory read
@@ -305,10 +332,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           } else {
 #pragma unroll
             for (int c = 0; c < CH; ++c) v[c] = 0.f;
-            for (int cc = c_first; cc <= c_last; ++cc) {       // fixed order: increasing K
-              const float* src = p.partial + (size_t)sch.slot(cc, tile_first) * kTileFloats + row;
+            // shares are fetched kBatch CTAs at a time so that their loads are all in
+            // flight together; they are added in the fixed order of increasing K
+            constexpr int kBatch = CH == 16 ? 4 : 2;
+            for (int cc = c_first; cc <= c_last; cc += kBatch) {
+              float a[kBatch][CH];
 #pragma unroll
-              for (int c = 0; c < CH; ++c) v[c] += __ldcg(src + (size_t)(c0 + c) * kTileX);
+              for (int j = 0; j < kBatch; ++j) {
+                const bool on = cc + j <= c_last;
+                const float* src = p.partial + (size_t)sch.slot(on ? cc + j : cc, tile_first) * kTileFloats + row;
+#pragma unroll
+                for (int c = 0; c < CH; ++c) a[j][c] = on ? __ldcg(src + (size_t)(c0 + c) * kTileX) : 0.f;
+              }
+#pragma unroll
+              for (int j = 0; j < kBatch; ++j)
+#pragma unroll
+                for (int c = 0; c < CH; ++c) v[c] += a[j][c];
             }
           }
           if (SWAP) {
@@ -442,7 +481,7 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, const Params& p, int gr
     if (e != cudaSuccess) return fail("gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  gemm_tc_kernel<BN, STAGES, SWAP><<<grid, kThreads, smem, stream>>>(mx, my, p);
+  ilb::launch(gemm_tc_kernel<BN, STAGES, SWAP>, dim3(grid), dim3(kThreads), smem, stream, mx, my, p);
   return check_launch("gemm_tc");
 }
 
@@ -490,7 +529,9 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   p.units = tiles * p.k_blocks;
   ILB_REQUIRE(tiles <= n_tickets, "gemm_tc: %lld output tiles exceed the %d tickets", tiles, n_tickets);
 
-  long long grid = sm_count();
+  // Up to 32 tokens: two CTAs per SM (their rings are sized for it), one streams while
+  // the other is in its prologue or epilogue.  Wider token tiles keep one CTA and a deep ring.
+  long long grid = (swap && bn <= 32) ? 2ll * sm_count() : sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (grid > p.units) grid = p.units;
   ILB_REQUIRE(2 * grid * bn * kTileX <= workspace_floats, "gemm_tc: workspace too small");
@@ -504,8 +545,8 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
 
   if (swap) {
     switch (bn) {
-      case 16: return launch<16, 10, true>(mx, my, p, (int)grid, stream);
-      case 32: return launch<32, 9, true>(mx, my, p, (int)grid, stream);
+      case 16: return launch<16, 5, true>(mx, my, p, (int)grid, stream);
+      case 32: return launch<32, 5, true>(mx, my, p, (int)grid, stream);
       case 64: return launch<64, 8, true>(mx, my, p, (int)grid, stream);
       default: return launch<128, 6, true>(mx, my, p, (int)grid, stream);
     }

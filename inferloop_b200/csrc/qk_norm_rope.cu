@@ -29,6 +29,8 @@ qk_norm_rope_kernel(const TQ* __restrict__ qkv, TQ* __restrict__ q_out,
                     const int* __restrict__ block_table, int max_blocks, int page_size,
                     int num_pages, TC* __restrict__ k_cache, TC* __restrict__ v_cache,
                     int n_tokens, int nq, int nkv, int d, int qkv_stride, int q_out_stride) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -108,7 +110,7 @@ ILB_EXPORT int ilb_qk_norm_rope_cache(
   dim3 grid(n_tokens, (nq + 2 * nkv + kWarpsPerBlock - 1) / kWarpsPerBlock);
   const size_t smem = (size_t)kWarpsPerBlock * d * sizeof(float);
 #define ILB_LAUNCH(TQ, TC)                                                                   \
-  qk_norm_rope_kernel<TQ, TC><<<grid, kWarpsPerBlock * 32, smem, stream>>>(                   \
+  ilb::launch(qk_norm_rope_kernel<TQ, TC>, dim3(grid), dim3(kWarpsPerBlock * 32), smem, stream,                    \
       (const TQ*)qkv, (TQ*)q_out, q_weight, k_weight, eps, (const float2*)rope_table,         \
       rotary_dim, positions, seq_of_token, block_table, max_blocks, page_size, num_pages,     \
       (TC*)k_cache, (TC*)v_cache, n_tokens, nq, nkv, d, qkv_stride, q_out_stride)

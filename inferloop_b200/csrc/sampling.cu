@@ -27,6 +27,8 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
 __global__ void __launch_bounds__(kThreads)
 argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int* __restrict__ bad,
               int vocab, int stride) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
   __shared__ float sv[32];
   __shared__ int si[32];
   __shared__ int sbad;
@@ -70,7 +72,7 @@ ILB_EXPORT int ilb_argmax(const float* logits, int* out, int* bad, int rows, int
                           cudaStream_t stream) {
   ILB_REQUIRE(rows >= 0 && vocab > 0 && stride >= vocab, "argmax: bad sizes");
   if (rows == 0) return 0;
-  argmax_kernel<<<rows, kThreads, 0, stream>>>(logits, out, bad, vocab, stride);
+  ilb::launch(argmax_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, out, bad, vocab, stride);
   return check_launch("argmax");
 }
 
@@ -101,6 +103,8 @@ __global__ void __launch_bounds__(kThreads)
 sample_temperature_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
                           const double* __restrict__ uniform, int* __restrict__ out,
                           int* __restrict__ bad, int vocab, int stride) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
   __shared__ double scratch[33];
   __shared__ float smax[33];
   __shared__ int sflag;
@@ -185,7 +189,7 @@ ILB_EXPORT int ilb_sample_temperature(const float* logits, const float* temperat
                                       int vocab, int stride, cudaStream_t stream) {
   ILB_REQUIRE(rows >= 0 && vocab > 0 && stride >= vocab, "sample_temperature: bad sizes");
   if (rows == 0) return 0;
-  sample_temperature_kernel<<<rows, kThreads, 0, stream>>>(logits, temperature, uniform, out, bad,
+  ilb::launch(sample_temperature_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, temperature, uniform, out, bad,
                                                            vocab, stride);
   return check_launch("sample_temperature");
 }
