@@ -585,4 +585,65 @@ ILB_EXPORT int ilb_attention_decode(const void* q, void* out, const void* k_cach
   }
 }
 
+// ------------------------------------------------------------------ decode without allocation
+// See attention_decode_static.h for who needs this and what it costs.
+#include "attention_decode_static.h"
+#include <mutex>
+
+// Counters first (they are cleared before every launch), then the chunk records.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_static_ptr[kMaxDevices] = {};
+std::mutex g_static_mu;
+
+// Device address of g_static_scratch on the current device.  In host code the array's name
+// is only a handle; the address a kernel can use comes from cudaGetSymbolAddress, asked
+// once per device with that device current.
+int static_scratch(void** ptr) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail("attention decode (static): cudaGetDevice failed: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail("attention decode (static): device ordinal %d is outside 0..%d", dev, kMaxDevices - 1);
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail("attention decode (static): cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+    g_static_ptr[dev] = p;
+  }
+  *ptr = g_static_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+ILB_EXPORT int ilb_attention_decode_static(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                           const int* positions, const int* cu_q, const int* block_table,
+                                           int max_blocks, int page_size, int num_pages, int window, float scale,
+                                           int n_seqs, int nq, int nkv, int d, int q_stride, int out_stride,
+                                           int chunk, int max_chunks, cudaStream_t stream) {
+  ILB_REQUIRE(n_seqs > 0 && nq > 0 && nkv > 0 && nq % nkv == 0 && d > 0 && max_chunks > 0,
+              "attention decode (static): bad sizes");
+  const long long need = (long long)n_seqs * nkv * max_chunks * (nq / nkv) * (d + 2);
+  ILB_REQUIRE(need <= (long long)kStaticScratchFloats,
+              "attention decode (static): %d sequences x %d kv heads x %d chunks x %d heads x (%d + 2) = %lld floats of "
+              "scratch exceed the built-in %d; use ilb_attention_decode with a buffer of your own",
+              n_seqs, nkv, max_chunks, nq / nkv, d, need, (int)kStaticScratchFloats);
+  ILB_REQUIRE((long long)n_seqs * nkv <= (long long)kStaticTickets,
+              "attention decode (static): %d sequences x %d kv heads exceed the built-in %d counters",
+              n_seqs, nkv, (int)kStaticTickets);
+  void* base = nullptr;
+  if (static_scratch(&base)) return -1;
+  int* tickets = reinterpret_cast<int*>(base);
+  float* records = reinterpret_cast<float*>(static_cast<unsigned char*>(base) + (size_t)kStaticTickets * 4);
+  // The counters must read zero when the kernel starts, whatever an earlier call left.
+  cudaError_t e = cudaMemsetAsync(tickets, 0, (size_t)kStaticTickets * 4, stream);
+  if (e != cudaSuccess) return fail("attention decode (static): clearing the counters failed: %s", cudaGetErrorString(e));
+  return ilb_attention_decode(q, out, k_cache, v_cache, positions, cu_q, block_table, max_blocks, page_size, num_pages,
+                              window, scale, n_seqs, nq, nkv, d, q_stride, out_stride, chunk, max_chunks, records,
+                              (long long)kStaticScratchFloats, tickets, (int)kStaticTickets, stream);
+}
+
 ILB_DEFINE_LAST_ERROR()
