@@ -138,20 +138,48 @@ struct Params {
   int M, N, K, ldo;
   int tiles_x, tiles_y;      // tiles of the X operand (128 rows) and of the Y operand (BN rows)
   int k_blocks;              // ceil(K / 64)
-  long long units;           // tiles_x * tiles_y * k_blocks
+  long long units;           // K blocks of the tiles that are shared out stream-K fashion
+  int dp_waves;              // whole-tile rounds before that: CTA c takes tiles c, c + grid, ...
+  long long sk_tile0;        // first tile of the stream-K part = dp_waves * grid
   int epilogue;              // Epilogue
   int out_f32;               // element type of out
 };
 
-// Work is cut stream-K fashion: a unit is one 64-wide K block of one output tile; the
-// grid's CTAs take equal, contiguous runs of units, so a CTA handles the tail of one tile,
-// some whole tiles, and the head of another.
+// Work: first `dp_waves` rounds of WHOLE tiles in wave order (round w: CTA c takes tile
+// w * grid + c, so the CTAs of a round work on neighbouring tiles and share operand tiles
+// in L2), then the remaining tiles stream-K fashion: a unit is one 64-wide K block of one
+// of those tiles and the CTAs take equal, contiguous runs of units, so a CTA handles the
+// tail of one tile, some whole tiles, and the head of another.  `units`, `start`, `cta_of`
+// and `slot` speak of the stream-K part only.
 struct Schedule {
   long long units; int grid, k_blocks;
   __device__ __forceinline__ long long start(int c) const { return (long long)c * units / grid; }
   __device__ __forceinline__ int cta_of(long long u) const { return (int)(((u + 1) * grid - 1) / units); }
   // slot of CTA c's contribution to the tile whose first unit is `tile_first`
   __device__ __forceinline__ int slot(int c, long long tile_first) const { return 2 * c + (start(c) >= tile_first ? 0 : 1); }
+};
+
+// The segments (tile, first K block, number of K blocks) of one CTA, in order.
+struct Segments {
+  int w, dp_waves, grid, cta, k_blocks;
+  long long u, u_end, sk_tile0;
+  __device__ Segments(const Params& p, const Schedule& sch, int cta_, int grid_)
+      : w(0), dp_waves(p.dp_waves), grid(grid_), cta(cta_), k_blocks(p.k_blocks),
+        u(sch.start(cta_)), u_end(sch.start(cta_ + 1)), sk_tile0(p.sk_tile0) {}
+  // sk_first: first stream-K unit of the tile, or -1 for a whole tile of the wave part
+  __device__ __forceinline__ bool next(long long& tile, int& kb0, int& cnt, long long& sk_first) {
+    if (w < dp_waves) {
+      tile = (long long)w * grid + cta; kb0 = 0; cnt = k_blocks; sk_first = -1; ++w;
+      return true;
+    }
+    if (u >= u_end) return false;
+    const long long t = u / k_blocks;
+    tile = sk_tile0 + t; kb0 = (int)(u % k_blocks);
+    cnt = (int)min((long long)(k_blocks - kb0), u_end - u);
+    sk_first = t * k_blocks;
+    u += cnt;
+    return true;
+  }
 };
 
 template <int BN, int STAGES, bool SWAP>
@@ -176,8 +204,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const Schedule sch{p.units, (int)gridDim.x, p.k_blocks};
-  const long long u_begin = sch.start(blockIdx.x), u_end = sch.start(blockIdx.x + 1);
+  const Schedule sch{p.units > 0 ? p.units : 1, (int)gridDim.x, p.k_blocks};
+  const long long u_begin = p.units > 0 ? sch.start(blockIdx.x) : 0, u_end = p.units > 0 ? sch.start(blockIdx.x + 1) : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -201,12 +229,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // tiles of those stages follow the wait.
     if (lane == 0) {
       bool ok = true;
-      const uint32_t n_units = (uint32_t)(u_end - u_begin);
+      const uint32_t n_dp = (uint32_t)p.dp_waves * (uint32_t)p.k_blocks;
+      const uint32_t n_units = n_dp + (uint32_t)(u_end - u_begin);
       const uint32_t n_early = n_units < (uint32_t)STAGES ? n_units : (uint32_t)STAGES;
       auto coords = [&](uint32_t it, int& kcol, int& x0, int& y0) {
-        const long long u = u_begin + it;
-        const long long tile = u / p.k_blocks;
-        kcol = (int)(u % p.k_blocks) * kBlockK;
+        long long tile;
+        if (it < n_dp) {
+          tile = (long long)(it / p.k_blocks) * gridDim.x + blockIdx.x;
+          kcol = (int)(it % p.k_blocks) * kBlockK;
+        } else {
+          const long long u = u_begin + (it - n_dp);
+          tile = p.sk_tile0 + u / p.k_blocks;
+          kcol = (int)(u % p.k_blocks) * kBlockK;
+        }
         x0 = (int)(tile % p.tiles_x) * kTileX;
         y0 = (int)(tile / p.tiles_x) * BN;
       };
@@ -245,9 +280,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       constexpr uint32_t idesc = instr_desc(kTileX, BN);
       bool ok = true;
       uint32_t it = 0, seg = 0;
-      for (long long u = u_begin; u < u_end && ok; ++seg) {
-        const int kb0 = (int)(u % p.k_blocks);
-        const int cnt = (int)min((long long)(p.k_blocks - kb0), u_end - u);
+      Segments segs(p, sch, blockIdx.x, gridDim.x);
+      if (p.units <= 0) segs.u_end = segs.u = 0;
+      long long tile_, sk_first_;
+      int kb0, cnt;
+      for (; ok && segs.next(tile_, kb0, cnt, sk_first_); ++seg) {
         const uint32_t b = seg & 1;
         ok = mbar_wait(tempty0 + 8 * b, ((seg >> 1) & 1) ^ 1);     // the epilogue has drained this accumulator
         if (!ok) break;
@@ -266,7 +303,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           tcgen05_commit(empty0 + 8 * s);       // the buffer is free once these MMAs have read it
         }
         tcgen05_commit(tfull0 + 8 * b);         // arrives when every MMA issued so far is complete
-        u += cnt;
       }
       if (!ok) {
         flags[0] = 1; if (p.error_flag) *p.error_flag = 1;
@@ -281,11 +317,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     constexpr int CH = BN < 32 ? BN : 32;     // columns per tensor-memory read
     uint32_t seg = 0;
     bool failed = false;
-    for (long long u = u_begin; u < u_end && !failed; ++seg) {
-      const long long tile = u / p.k_blocks;
-      const int kb0 = (int)(u % p.k_blocks);
-      const int cnt = (int)min((long long)(p.k_blocks - kb0), u_end - u);
-      u += cnt;
+    Segments segs(p, sch, blockIdx.x, gridDim.x);
+    if (p.units <= 0) segs.u_end = segs.u = 0;
+    long long tile, tile_first;
+    int kb0, cnt;
+    for (; !failed && segs.next(tile, kb0, cnt, tile_first); ++seg) {
       const int x0 = (int)(tile % p.tiles_x) * kTileX, y0 = (int)(tile / p.tiles_x) * BN;
       const int xr = x0 + row;
       const uint32_t b = seg & 1;
@@ -295,7 +331,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       if (failed) break;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + b * kAccCols;
       const bool whole = cnt == p.k_blocks;
-      const long long tile_first = tile * p.k_blocks;
       bool last = whole;
       int c_first = 0, c_last = 0;
       if (!whole) {
@@ -372,7 +407,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             }
           } else {
             // X rows are tokens m = xr; columns are output features n = y0 + c
-            if (xr < p.M) {
+            const int n0 = y0 + c0;
+            const bool full = n0 + CH <= p.N && (p.ldo % 8 == 0) && ((uintptr_t)p.out % 16 == 0);
+            if (xr < p.M && full) {
+              // a whole chunk of this row: 16-byte accesses
+              const size_t o = (size_t)xr * p.ldo + n0;
+              if (p.bias) {
+#pragma unroll
+                for (int c = 0; c < CH; ++c) v[c] += p.bias[n0 + c];
+              }
+              if (p.out_f32) {
+                float4* dst = reinterpret_cast<float4*>((float*)p.out + o);
+#pragma unroll
+                for (int c = 0; c < CH / 4; ++c) {
+                  float4 r = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+                  if (p.epilogue == kAccumulate) {
+                    const float4 old = dst[c];
+                    r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w;
+                  }
+                  dst[c] = r;
+                }
+              } else {
+                uint4* dst = reinterpret_cast<uint4*>((__nv_bfloat16*)p.out + o);
+#pragma unroll
+                for (int c = 0; c < CH / 8; ++c) {
+                  uint4 r;
+                  __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * c], v[8 * c + 1]);
+                  __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * c + 2], v[8 * c + 3]);
+                  __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * c + 4], v[8 * c + 5]);
+                  __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * c + 6], v[8 * c + 7]);
+                  r.x = *reinterpret_cast<uint32_t*>(&h0); r.y = *reinterpret_cast<uint32_t*>(&h1);
+                  r.z = *reinterpret_cast<uint32_t*>(&h2); r.w = *reinterpret_cast<uint32_t*>(&h3);
+                  dst[c] = r;
+                }
+              }
+            } else if (xr < p.M) {
 #pragma unroll
               for (int c = 0; c < CH; ++c) {
                 const int n = y0 + c0 + c;
@@ -526,14 +595,18 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   p.tiles_x = (x_rows + kTileX - 1) / kTileX;
   p.tiles_y = (y_rows + bn - 1) / bn;
   const long long tiles = (long long)p.tiles_x * p.tiles_y;
-  p.units = tiles * p.k_blocks;
   ILB_REQUIRE(tiles <= n_tickets, "gemm_tc: %lld output tiles exceed the %d tickets", tiles, n_tickets);
 
   // Up to 32 tokens: two CTAs per SM (their rings are sized for it), one streams while
   // the other is in its prologue or epilogue.  Wider token tiles keep one CTA and a deep ring.
   long long grid = (swap && bn <= 32) ? 2ll * sm_count() : sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-  if (grid > p.units) grid = p.units;
+  if (grid > tiles * p.k_blocks) grid = tiles * p.k_blocks;
+  // Prefill shapes: whole tiles in wave order first (operands shared in L2), the last
+  // partial wave stream-K.  Decode shapes: everything stream-K (weights are read once anyway).
+  p.dp_waves = swap ? 0 : (int)(tiles / grid);
+  p.sk_tile0 = (long long)p.dp_waves * grid;
+  p.units = (tiles - p.sk_tile0) * p.k_blocks;
   ILB_REQUIRE(2 * grid * bn * kTileX <= workspace_floats, "gemm_tc: workspace too small");
 
   CUtensorMap mx, my;
