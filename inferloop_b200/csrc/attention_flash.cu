@@ -454,48 +454,73 @@ decode_kernel(const DecodeParams p) {
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  // weights of the chunks per head: f[h][ci] = 2^(m_ci - M) / L, all loads issued at once
+  // weights of the chunks per head: f[h][ci] = 2^(m_ci - M) / L.  One warp per head, one
+  // lane per chunk (32 chunks a round), so every record is fetched once and all fetches
+  // of a round are in flight together; sums run in chunk order within a lane's stride and
+  // are combined by a fixed shuffle tree.
   float* fw = merge;                               // [G][n_chunks]
-  for (int h = threadIdx.x; h < G; h += kWarps * 32) {
+  for (int h = warp; h < G; h += kWarps) {
     float m_all = -INFINITY;
-    for (int c0 = c_lo; c0 <= c_hi; c0 += 8) {
-      float mm[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) mm[j] = (c0 + j <= c_hi) ? __ldcg(rec_base + ((size_t)(c0 + j) * G + h) * kRec + D) : -INFINITY;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) m_all = fmaxf(m_all, mm[j]);
+    for (int c0 = 0; c0 < n_chunks; c0 += 32) {
+      const int ci = c0 + lane;
+      const float mc = ci < n_chunks ? __ldcg(rec_base + ((size_t)(c_lo + ci) * G + h) * kRec + D) : -INFINITY;
+      m_all = fmaxf(m_all, mc);
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, o));
     float l_all = 0.f;
-    for (int c0 = c_lo; c0 <= c_hi; c0 += 8) {
-      float mm[8], ll[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const bool ok = c0 + j <= c_hi;
-        mm[j] = ok ? __ldcg(rec_base + ((size_t)(c0 + j) * G + h) * kRec + D) : -INFINITY;
-        ll[j] = ok ? __ldcg(rec_base + ((size_t)(c0 + j) * G + h) * kRec + D + 1) : 0.f;
+    for (int c0 = 0; c0 < n_chunks; c0 += 32) {
+      const int ci = c0 + lane;
+      float f = 0.f, l = 0.f;
+      if (ci < n_chunks) {
+        const float* rec = rec_base + ((size_t)(c_lo + ci) * G + h) * kRec;
+        const float mc = __ldcg(rec + D);
+        l = __ldcg(rec + D + 1);
+        f = (mc == -INFINITY) ? 0.f : exp2f(mc - m_all);
+        fw[h * n_chunks + ci] = f;
       }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float f = (mm[j] == -INFINITY) ? 0.f : exp2f(mm[j] - m_all);
-        if (c0 + j <= c_hi) fw[h * n_chunks + (c0 + j - c_lo)] = f;
-        l_all += ll[j] * f;                        // chunk order
-      }
+      l_all += l * f;
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l_all += __shfl_xor_sync(0xffffffffu, l_all, o);
     const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-    for (int ci = 0; ci < n_chunks; ++ci) fw[h * n_chunks + ci] *= inv;
+    __syncwarp();
+    for (int ci = lane; ci < n_chunks; ci += 32) fw[h * n_chunks + ci] *= inv;
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < G * D; idx += kWarps * 32) {
-    const int h = idx / D, c = idx % D;
-    float o = 0.f;
+  // every output element: its chunks' values, eight fetches in flight per element and the
+  // elements of a thread unrolled so that their fetches overlap too
+  constexpr int kPerThread = 4;
+  for (int base = 0; base < G * D; base += kWarps * 32 * kPerThread) {
+    float o[kPerThread];
+#pragma unroll
+    for (int e = 0; e < kPerThread; ++e) o[e] = 0.f;
     for (int c0 = 0; c0 < n_chunks; c0 += 8) {
-      float v[8];
+      float v[kPerThread][8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = (c0 + j < n_chunks) ? __ldcg(rec_base + ((size_t)(c_lo + c0 + j) * G + h) * kRec + c) : 0.f;
+      for (int e = 0; e < kPerThread; ++e) {
+        const int idx = base + e * kWarps * 32 + threadIdx.x;
+        const int h = idx / D, c = idx % D;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) if (c0 + j < n_chunks) o += v[j] * fw[h * n_chunks + c0 + j];
+        for (int j = 0; j < 8; ++j)
+          v[e][j] = (idx < G * D && c0 + j < n_chunks) ? __ldcg(rec_base + ((size_t)(c_lo + c0 + j) * G + h) * kRec + c) : 0.f;
+      }
+#pragma unroll
+      for (int e = 0; e < kPerThread; ++e) {
+        const int idx = base + e * kWarps * 32 + threadIdx.x;
+        const int h = idx < G * D ? idx / D : 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) if (c0 + j < n_chunks) o[e] += v[e][j] * fw[h * n_chunks + c0 + j];
+      }
     }
-    p.out[(size_t)tok * p.out_stride + (size_t)(kvh * G + h) * D + c] = __float2bfloat16_rn(o);
+#pragma unroll
+    for (int e = 0; e < kPerThread; ++e) {
+      const int idx = base + e * kWarps * 32 + threadIdx.x;
+      if (idx < G * D) {
+        const int h = idx / D, c = idx % D;
+        p.out[(size_t)tok * p.out_stride + (size_t)(kvh * G + h) * D + c] = __float2bfloat16_rn(o[e]);
+      }
+    }
   }
 }
 

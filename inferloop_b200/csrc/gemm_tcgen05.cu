@@ -567,7 +567,7 @@ ILB_EXPORT int ilb_gemm_tc_supported(int M, int N, int K, int lda, int ldw) {
   return (M > 0 && N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0) ? 1 : 0;
 }
 
-// max_ctas > 0 caps the grid (tests use it to force many partial tiles).
+// max_ctas > 0 sets the grid (tests use it to force many shared tiles).
 ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void* out, int out_f32,
                            int M, int N, int K, int lda, int ldw, int ldo, int accumulate,
                            float* workspace, long long workspace_floats, int* tickets, int n_tickets,
@@ -599,8 +599,18 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
 
   // Up to 32 tokens: two CTAs per SM (their rings are sized for it), one streams while
   // the other is in its prologue or epilogue.  Wider token tiles keep one CTA and a deep ring.
-  long long grid = (swap && bn <= 32) ? 2ll * sm_count() : sm_count();
-  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  // When the tiles are fewer than the CTAs that fit, every tile is cut into the same number
+  // of K ranges (at most 8), so that no CTA straddles two tiles and a tile's shares are few;
+  // otherwise the persistent grid takes contiguous runs of units.
+  const long long cap = (swap && bn <= 32) ? 2ll * sm_count() : sm_count();
+  long long grid = cap;
+  if (swap && tiles <= cap) {
+    long long split = cap / tiles;
+    if (split > 8) split = 8;
+    if (split > p.k_blocks) split = p.k_blocks;
+    grid = tiles * split;
+  }
+  if (max_ctas > 0) grid = max_ctas;       // tests and tuning runs choose the grid themselves
   if (grid > tiles * p.k_blocks) grid = tiles * p.k_blocks;
   // Prefill shapes: whole tiles in wave order first (operands shared in L2), the last
   // partial wave stream-K.  Decode shapes: everything stream-K (weights are read once anyway).
