@@ -251,8 +251,9 @@ prefill_kernel(const PrefillParams p) {
   const int kvh = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 
-  // which sequence and which 64-row tile of it
-  int seq = 0, tile = blockIdx.x;
+  // which sequence and which 64-row tile of it; the last tiles of a prompt see the most
+  // keys, so they are handed out first and the short ones fill the tail of the launch
+  int seq = 0, tile = (int)gridDim.x - 1 - (int)blockIdx.x;
   for (; seq < p.n_seqs; ++seq) {
     const int rows = (p.cu_q[seq + 1] - p.cu_q[seq]) * G;
     const int tiles = (rows + 63) / 64;

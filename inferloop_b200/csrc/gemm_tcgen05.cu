@@ -1,5 +1,7 @@
 // bfloat16 matrix product on the 5th-generation tensor cores of sm_100a:
-//     out[M,N] (+)= A[M,K] * W[N,K]^T (+ bias[N]),  32-bit accumulation in tensor memory.
+//     out[M,N] (+)= A[M,K] * W[N,K]^T (+ bias[N]),  32-bit accumulation in tensor memory,
+// or, for a weight whose rows interleave 64 gate rows with their 64 up rows,
+//     out[M,N/2] = silu(gate) * up   (the SwiGLU product in the epilogue).
 //
 // One kernel serves decode-shaped (few tokens) and prefill-shaped (many tokens) products.
 // tcgen05.mma computes D[128 x BN] = X[128 x K] * Y[BN x K]^T with both operands K-major in
@@ -45,7 +47,7 @@ constexpr int kTileX = 128;            // rows of the X operand = MMA M
 constexpr int kThreads = 192;
 constexpr uint32_t kWaitLimit = 1u << 22;
 
-enum Epilogue : int { kStore = 0, kAccumulate = 1 };
+enum Epilogue : int { kStore = 0, kAccumulate = 1, kSwiGLU = 2 };
 
 // ------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -201,6 +203,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* flags = reinterpret_cast<volatile int*>(bars + 2 * STAGES + 5);   // [0] = failed, [1] = last ticket
+  float* xch = reinterpret_cast<float*>(bars + 2 * STAGES + 6);                    // [32][64], SwiGLU exchange (swap mode)
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -360,15 +363,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         if (last) __threadfence();
       }
       if (last) {
-        for (int c0 = 0; c0 < BN; c0 += CH) {
-          float v[32];
+        // values of columns c0 .. c0 + CH of this thread's row: from the accumulator, or the
+        // tile's shares added in the fixed order of increasing K
+        auto fetch = [&](int c0, float (&v)[32]) {
           if (whole) {
             if (CH == 32) tmem_load_32(taddr + c0, v); else tmem_load_16(taddr + c0, v);
           } else {
 #pragma unroll
             for (int c = 0; c < CH; ++c) v[c] = 0.f;
-            // shares are fetched kBatch CTAs at a time so that their loads are all in
-            // flight together; they are added in the fixed order of increasing K
+            // shares are fetched kBatch CTAs at a time so that their loads are all in flight
             constexpr int kBatch = CH == 16 ? 4 : 2;
             for (int cc = c_first; cc <= c_last; cc += kBatch) {
               float a[kBatch][CH];
@@ -385,6 +388,80 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 for (int c = 0; c < CH; ++c) v[c] += a[j][c];
             }
           }
+        };
+        if (p.epilogue == kSwiGLU) {
+          // The weight rows come in blocks of 64 gate rows followed by their 64 up rows; the
+          // output has half as many features: out[m, i] = silu(gate_i) * up_i.
+          const int half_n = p.N / 2;
+          if (SWAP) {
+            // gate rows are tile rows 0..63, up rows 64..127: the up half hands its values to
+            // the gate half through shared memory
+            const int i = (x0 / kTileX) * 64 + (row & 63);
+            for (int c0 = 0; c0 < BN; c0 += CH) {
+              float v[32];
+              fetch(c0, v);
+              if (row >= 64) {
+#pragma unroll
+                for (int c = 0; c < CH; ++c) xch[c * 64 + (row - 64)] = v[c];
+              }
+              asm volatile("bar.sync 1, 128;" ::: "memory");
+              if (row < 64 && i < half_n) {
+#pragma unroll
+                for (int c = 0; c < CH; ++c) {
+                  const int m = y0 + c0 + c;
+                  if (m < p.M) {
+                    const float g = v[c], u = xch[c * 64 + row];
+                    const float r = g / (1.0f + __expf(-g)) * u;
+                    const size_t o = (size_t)m * p.ldo + i;
+                    if (p.out_f32) ((float*)p.out)[o] = r; else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(r);
+                  }
+                }
+              }
+              asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+          } else {
+            // columns come in blocks of 64 gate then 64 up; a thread holds both halves
+            for (int cb = 0; cb < BN; cb += 128) {
+              for (int c0 = cb; c0 < cb + 64; c0 += CH) {
+                float g[32], u[32];
+                fetch(c0, g);
+                fetch(c0 + 64, u);
+                const int i0 = (y0 + cb) / 2 + (c0 - cb);
+                float r[32];
+#pragma unroll
+                for (int c = 0; c < CH; ++c) r[c] = g[c] / (1.0f + __expf(-g[c])) * u[c];
+                if (xr < p.M) {
+                  const size_t o = (size_t)xr * p.ldo + i0;
+                  const bool full = i0 + CH <= half_n && (p.ldo % 8 == 0) && ((uintptr_t)p.out % 16 == 0) && !p.out_f32;
+                  if (full) {
+                    uint4* dst = reinterpret_cast<uint4*>((__nv_bfloat16*)p.out + o);
+#pragma unroll
+                    for (int c = 0; c < CH / 8; ++c) {
+                      uint4 q;
+                      __nv_bfloat162 h0 = __floats2bfloat162_rn(r[8 * c], r[8 * c + 1]);
+                      __nv_bfloat162 h1 = __floats2bfloat162_rn(r[8 * c + 2], r[8 * c + 3]);
+                      __nv_bfloat162 h2 = __floats2bfloat162_rn(r[8 * c + 4], r[8 * c + 5]);
+                      __nv_bfloat162 h3 = __floats2bfloat162_rn(r[8 * c + 6], r[8 * c + 7]);
+                      q.x = *reinterpret_cast<uint32_t*>(&h0); q.y = *reinterpret_cast<uint32_t*>(&h1);
+                      q.z = *reinterpret_cast<uint32_t*>(&h2); q.w = *reinterpret_cast<uint32_t*>(&h3);
+                      dst[c] = q;
+                    }
+                  } else {
+#pragma unroll
+                    for (int c = 0; c < CH; ++c) {
+                      if (i0 + c < half_n) {
+                        if (p.out_f32) ((float*)p.out)[o + c] = r[c]; else ((__nv_bfloat16*)p.out)[o + c] = __float2bfloat16_rn(r[c]);
+                      }
+                    }
+                  }
+                }
+              }
+            }
+          }
+        } else
+        for (int c0 = 0; c0 < BN; c0 += CH) {
+          float v[32];
+          fetch(c0, v);
           if (SWAP) {
             // X rows are output features n = xr; columns are tokens m = y0 + c
             if (xr < p.N) {
@@ -542,7 +619,8 @@ int sm_count() {
 
 template <int BN, int STAGES, bool SWAP>
 int launch(const CUtensorMap& mx, const CUtensorMap& my, const Params& p, int grid, cudaStream_t stream) {
-  constexpr size_t smem = (size_t)STAGES * (kTileX * kBlockK * 2 + BN * kBlockK * 2) + 1024 + (2 * STAGES + 6) * 8;
+  constexpr size_t smem = (size_t)STAGES * (kTileX * kBlockK * 2 + BN * kBlockK * 2) + 1024 + (2 * STAGES + 6) * 8 +
+                          (SWAP ? 32 * 64 * 4 : 0);
   static_assert(smem <= 227 * 1024, "stage ring does not fit shared memory");
   static bool configured = false;
   if (!configured) {
@@ -569,22 +647,28 @@ ILB_EXPORT int ilb_gemm_tc_supported(int M, int N, int K, int lda, int ldw) {
 
 // max_ctas > 0 sets the grid (tests use it to force many shared tiles).
 ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void* out, int out_f32,
-                           int M, int N, int K, int lda, int ldw, int ldo, int accumulate,
+                           int M, int N, int K, int lda, int ldw, int ldo, int accumulate /* Epilogue */,
                            float* workspace, long long workspace_floats, int* tickets, int n_tickets,
                            int* error_flag, int max_ctas, cudaStream_t stream) {
   ILB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
   ILB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
               "gemm_tc: K (%d) and the leading dimensions (%d, %d) must be multiples of 8", K, lda, ldw);
   ILB_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
-  ILB_REQUIRE(!accumulate || out_f32, "gemm_tc: accumulation needs a 32-bit output");
-  ILB_REQUIRE(ldo >= N, "gemm_tc: output leading dimension too small");
+  ILB_REQUIRE(accumulate >= 0 && accumulate <= 2, "gemm_tc: unknown epilogue %d", accumulate);
+  ILB_REQUIRE(accumulate != 1 || out_f32, "gemm_tc: accumulation needs a 32-bit output");
+  if (accumulate == 2) {
+    ILB_REQUIRE(N % 128 == 0 && bias == nullptr, "gemm_tc: the SwiGLU epilogue needs N (%d) a multiple of 128 and no bias", N);
+    ILB_REQUIRE(ldo >= N / 2, "gemm_tc: output leading dimension too small");
+  } else {
+    ILB_REQUIRE(ldo >= N, "gemm_tc: output leading dimension too small");
+  }
   ILB_REQUIRE(workspace != nullptr && tickets != nullptr, "gemm_tc: workspace and tickets are required");
 
   Params p{};
   p.out = out; p.bias = bias; p.partial = workspace; p.tickets = tickets; p.error_flag = error_flag;
   p.M = M; p.N = N; p.K = K; p.ldo = ldo;
   p.k_blocks = (K + kBlockK - 1) / kBlockK;
-  p.epilogue = accumulate ? kAccumulate : kStore;
+  p.epilogue = accumulate;
   p.out_f32 = out_f32;
 
   const bool swap = M <= 128;

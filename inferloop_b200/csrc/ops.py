@@ -256,20 +256,24 @@ def gemm_tc_eligible(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> boo
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-            accumulate: bool = False, max_ctas: int = 0) -> None:
-    """out (+)= a @ w.T (+ bias) on tcgen05 tensor cores (see gemm_tcgen05.cu)."""
+            accumulate: bool = False, max_ctas: int = 0, swiglu: bool = False) -> None:
+    """out (+)= a @ w.T (+ bias) on tcgen05 tensor cores (see gemm_tcgen05.cu).  With
+    `swiglu`, `w` holds blocks of 64 gate rows followed by their 64 up rows and `out` is
+    [M, N/2] = silu(gate) * up."""
     _need(a, "gemm a", torch.bfloat16); _need(w, "gemm w", torch.bfloat16); _need(out, "gemm out")
     _need(bias, "gemm bias", torch.float32)
     M, K = a.shape
     N = w.shape[0]
-    if w.shape[1] != K or tuple(out.shape) != (M, N) or (bias is not None and bias.numel() != N):
+    n_out = N // 2 if swiglu else N
+    if w.shape[1] != K or tuple(out.shape) != (M, n_out) or (bias is not None and bias.numel() != N):
         raise KernelError(f"gemm: shapes do not agree: a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
-    if accumulate and out.dtype != torch.float32:
-        raise KernelError("gemm: accumulation needs a 32-bit output")
+    if accumulate and (out.dtype != torch.float32 or swiglu):
+        raise KernelError("gemm: accumulation needs a 32-bit output and no SwiGLU epilogue")
     st = _tc_state(a.device)
+    mode = 2 if swiglu else (1 if accumulate else 0)
     _call("gemm_tcgen05", "ilb_gemm_tc", _ptr(a), _ptr(w), _ptr(bias), _ptr(out),
           _i(1 if out.dtype == torch.float32 else 0), _i(M), _i(N), _i(K), _i(a.stride(0)), _i(w.stride(0)),
-          _i(out.stride(0)), _i(1 if accumulate else 0), _ptr(st.workspace), ctypes.c_longlong(st.floats),
+          _i(out.stride(0)), _i(mode), _ptr(st.workspace), ctypes.c_longlong(st.floats),
           _ptr(st.tickets), _i(st.n_tickets), _ptr(st.error), _i(max_ctas), _stream(out))
 
 

@@ -3,7 +3,12 @@
 (crates/model/recipes/src/decoder.rs:467-502; silu(z) = z * sigmoid(z) with the
 two-branch sigmoid of crates/testing/cpu/reference-ops/src/kernels.rs:12-22.)  The gate
 and up matrices are concatenated at load into one [2 I, H] matrix so one GEMM produces
-both.
+both.  On the bfloat16 path, when I is a multiple of 64, their rows are interleaved in
+blocks of 64 (64 gate rows, then the 64 up rows of the same features) and the product
+silu(gate) * up is taken in the GEMM's epilogue, so the [T, 2 I] intermediate is never
+written (the reference pairs the two projections in one launch and multiplies in a second:
+crates/backend/cuda-kernels/src/tile/projection/prefill_gemm_kernels.rs:11-69,
+tile/mlp/mlp_kernels.rs:27-36); otherwise the product is a kernel of its own.
 """
 from __future__ import annotations
 
@@ -27,6 +32,7 @@ class SwiGLU(FeedForward):
         self.names = {"gate": prefix + "gate_proj.weight", "up": prefix + "up_proj.weight",
                       "down": prefix + "down_proj.weight"}
         self.w_gate_up = self.w_down = None
+        self.fused = False
 
     def declare_weights(self) -> List[WeightDecl]:
         n = self.names
@@ -36,16 +42,29 @@ class SwiGLU(FeedForward):
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         n = self.names
-        self.w_gate_up = torch.cat([tensors[n["gate"]], tensors[n["up"]]], dim=0).contiguous()
+        gate, up = tensors[n["gate"]], tensors[n["up"]]
+        self.fused = (gate.dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0)
+        if self.fused:
+            blocks = self.inter // 64
+            self.w_gate_up = torch.stack(
+                [gate.view(blocks, 64, self.hidden), up.view(blocks, 64, self.hidden)], dim=1
+            ).reshape(2 * self.inter, self.hidden).contiguous()
+        else:
+            self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = tensors[n["down"]].contiguous()
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, step) -> None:
         T = x.shape[0]
         ws, dt = self.ctx.workspace, self.ctx.dtype
-        gate_up = ws.buffer("mlp.gate_up", (T, 2 * self.inter), dt)
-        linear(x, self.w_gate_up, gate_up)
         act = ws.buffer("mlp.act", (T, self.inter), dt)
-        ops.silu_mul(gate_up, act)
+        if self.fused and ops.gemm_tc_eligible(x, self.w_gate_up, act):
+            ops.gemm_tc(x, self.w_gate_up, act, swiglu=True)
+        elif self.fused:
+            raise ops.KernelError("SwiGLU: the interleaved weight needs the tensor-core GEMM, which refused this input")
+        else:
+            gate_up = ws.buffer("mlp.gate_up", (T, 2 * self.inter), dt)
+            linear(x, self.w_gate_up, gate_up)
+            ops.silu_mul(gate_up, act)
         linear(act, self.w_down, residual, accumulate=True)
 
 

@@ -431,3 +431,24 @@ def test_flash_attention_finds_one_far_key_and_respects_the_window_edge(q_len):
             assert torch.allclose(got, torch.full_like(got, expect), rtol=2.0 ** -7), (far, window, got[:4])
         else:
             assert 850.0 <= got.min().item() and got.max().item() <= 899.0
+
+
+@pytest.mark.parametrize("M,I,K,max_ctas", [(1, 64, 64, 0), (8, 192, 256, 0), (8, 12288 // 8, 512, 0), (40, 128, 136, 0),
+                                            (100, 320, 1024, 7), (130, 128, 64, 0), (300, 448, 512, 0), (2048, 1536, 512, 0),
+                                            (300, 448, 512, 5), (8, 192, 2048, 50)])
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
+def test_gemm_tcgen05_swiglu_epilogue(M, I, K, max_ctas, out_dtype):
+    """Weight rows in blocks of 64 gate + 64 up; out = silu(x Wg^T) * (x Wu^T)."""
+    o = ops()
+    torch.manual_seed(M + I)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    wg = (torch.randn(I, K) * 0.1).to(torch.bfloat16)
+    wu = (torch.randn(I, K) * 0.1).to(torch.bfloat16)
+    w = torch.stack([wg.view(I // 64, 64, K), wu.view(I // 64, 64, K)], dim=1).reshape(2 * I, K).contiguous()
+    out = torch.full((M, I), float("nan"), dtype=DT[out_dtype], device="cuda")
+    o.gemm_tc(a.cuda(), w.cuda(), out, swiglu=True, max_ctas=max_ctas)
+    o.check_device_errors()
+    g = a.double() @ wg.double().T
+    u = a.double() @ wu.double().T
+    ref = g * torch.sigmoid(g) * u
+    close(out, ref, out_dtype, scale=float(ref.abs().max()), what=f"swiglu {M}x{I}x{K}")

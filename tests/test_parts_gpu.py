@@ -111,11 +111,13 @@ def test_attention_part(dtype, nq, nkv, d, hidden, bias, qk_norm, window, rot):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_swiglu_part(dtype):
+@pytest.mark.parametrize("inter", [136, 192])          # 192: a multiple of 64, the fused epilogue in bfloat16
+def test_swiglu_part(dtype, inter):
     from inferloop_b200.parts import build
     ctx = env(dtype)
-    part = build("feed_forward", PartSpec.make("swiglu", hidden_size=56, intermediate_size=136), ctx, "ffn.")
+    part = build("feed_forward", PartSpec.make("swiglu", hidden_size=56, intermediate_size=inter), ctx, "ffn.")
     w = give(part, dtype, seed=8)
+    assert part.fused == (dtype == "bfloat16" and inter % 64 == 0)
     x = torch.randn(13, 56).to(DT[dtype])
     residual = torch.randn(13, 56)
     out = residual.clone().cuda()
