@@ -167,7 +167,9 @@ struct Segments {
   long long u, u_end, sk_tile0;
   __device__ Segments(const Params& p, const Schedule& sch, int cta_, int grid_)
       : w(0), dp_waves(p.dp_waves), grid(grid_), cta(cta_), k_blocks(p.k_blocks),
-        u(sch.start(cta_)), u_end(sch.start(cta_ + 1)), sk_tile0(p.sk_tile0) {}
+        u(0), u_end(0), sk_tile0(p.sk_tile0) {
+    if (p.units > 0 && cta_ < sch.grid) { u = sch.start(cta_); u_end = sch.start(cta_ + 1); }
+  }
   // sk_first: first stream-K unit of the tile, or -1 for a whole tile of the wave part
   __device__ __forceinline__ bool next(long long& tile, int& kb0, int& cnt, long long& sk_first) {
     if (w < dp_waves) {
@@ -207,8 +209,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const Schedule sch{p.units > 0 ? p.units : 1, (int)gridDim.x, p.k_blocks};
-  const long long u_begin = p.units > 0 ? sch.start(blockIdx.x) : 0, u_end = p.units > 0 ? sch.start(blockIdx.x + 1) : 0;
+  // The stream-K part is shared by the first min(grid, units) CTAs, so that every CTA that
+  // takes part holds at least one unit (a tile's sharers are then consecutive CTAs).
+  const int sk_grid = p.units < (long long)gridDim.x ? (int)p.units : (int)gridDim.x;
+  const Schedule sch{p.units > 0 ? p.units : 1, sk_grid > 0 ? sk_grid : 1, p.k_blocks};
+  const bool in_sk = p.units > 0 && (int)blockIdx.x < sk_grid;
+  const long long u_begin = in_sk ? sch.start(blockIdx.x) : 0, u_end = in_sk ? sch.start(blockIdx.x + 1) : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -284,7 +290,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       bool ok = true;
       uint32_t it = 0, seg = 0;
       Segments segs(p, sch, blockIdx.x, gridDim.x);
-      if (p.units <= 0) segs.u_end = segs.u = 0;
       long long tile_, sk_first_;
       int kb0, cnt;
       for (; ok && segs.next(tile_, kb0, cnt, sk_first_); ++seg) {
@@ -321,7 +326,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     uint32_t seg = 0;
     bool failed = false;
     Segments segs(p, sch, blockIdx.x, gridDim.x);
-    if (p.units <= 0) segs.u_end = segs.u = 0;
     long long tile, tile_first;
     int kb0, cnt;
     for (; !failed && segs.next(tile, kb0, cnt, tile_first); ++seg) {

@@ -79,6 +79,7 @@ class Engine:
         self.sampler = DeviceSampler(self.runner.device) if getattr(self.runner, "device", None) is not None else None
         self.cuda_graphs = cuda_graphs
         self._next_id = 0
+        self._steps_since_check = 0
         self.requests: Dict[Hashable, Request] = {}
 
     # ------------------------------------------------------------------ sizing
@@ -145,6 +146,11 @@ class Engine:
         else:
             logits = self.runner.step(entries)
             sampled = self._sample(logits, sampling_work)
+        # a kernel that gave up a bounded wait leaves a flag on the device; looking costs a
+        # small read, so it is done now and then and at the end of generate()
+        self._steps_since_check += 1
+        if self.sampler is not None and self._steps_since_check >= 64:
+            self.check_device()
         finished = {r.id for r in self.scheduler.complete(plan, sampled)}
         out = []
         for w in sampling_work:
@@ -191,6 +197,12 @@ class Engine:
                     prompt=r.prompt, generated=r.generated)
         return out
 
+    def check_device(self) -> None:
+        """Raise if any kernel reported that it gave up waiting (its outputs are invalid)."""
+        from ..csrc import ops
+        self._steps_since_check = 0
+        ops.check_device_errors()
+
     # ------------------------------------------------------------------ whole jobs
     def generate(self, prompts: Sequence[Sequence[int]], sampling: Union[SamplingParams, Sequence[SamplingParams], None] = None,
                  max_new_tokens: Union[int, Sequence[int]] = 16) -> List[List[int]]:
@@ -202,6 +214,8 @@ class Engine:
         ids = [self.submit(p, s, m) for p, s, m in zip(prompts, params, limits)]
         while not self.is_idle():
             self.step()
+        if self.sampler is not None:
+            self.check_device()
         return [list(self.requests[i].generated) for i in ids]
 
     def result(self, request_id: Hashable) -> Request:

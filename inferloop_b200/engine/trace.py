@@ -69,6 +69,8 @@ def main(argv: List[str] | None = None) -> int:
                 host.tofile(os.path.join(args.out, f"{step_no}.f32"))
             else:
                 torch.cuda.current_stream(runner.device).synchronize()
+            from ..csrc import ops
+            ops.check_device_errors()
         for rid in rec.get("end", []):
             if runner.is_live(rid):
                 runner.end(rid)

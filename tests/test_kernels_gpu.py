@@ -278,7 +278,9 @@ def test_kernels_refuse_what_they_cannot_do():
 
 
 # ------------------------------------------------------------------ tensor-core GEMM
-TC_SHAPES = [(1, 128, 64), (3, 200, 72), (8, 512, 4096), (16, 4096, 1024), (17, 300, 136), (33, 96, 512),
+# (256, 19200, 64) and (300, 9728, 128): one whole-tile round, then 2 tiles of 1-2 K blocks
+# shared by far fewer CTAs than the grid holds
+TC_SHAPES = [(256, 19200, 64), (300, 9728, 128), (1, 128, 64), (3, 200, 72), (8, 512, 4096), (16, 4096, 1024), (17, 300, 136), (33, 96, 512),
              (64, 1000, 1024), (65, 256, 256), (128, 384, 320), (129, 520, 264), (300, 515 * 1 + 5, 96), (512, 1024, 2048)]
 
 
