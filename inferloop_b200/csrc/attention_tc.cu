@@ -1,0 +1,515 @@
+// Causal grouped-query prefill attention over the paged bfloat16 cache on the tcgen05
+// tensor cores: S = Q K^T and O += P V as tcgen05.mma with both accumulators in tensor
+// memory, operands brought by TMA straight from the cache pages.
+//
+// One CTA = one kv head and 128 rows, a row being a (token, query head of the group)
+// pair, so 128 / G tokens of one sequence; it walks that sequence's keys 128 at a time.
+//   warp 0   one lane looks up the pages of the next 128 keys in the block table and issues
+//            the TMA loads: K and V each as one box per page and 64-wide slice of the head
+//            (128-byte swizzle; a page that is not held is requested outside the tensor, which
+//            TMA fills with zeros); Q once.
+//   warp 1   allocates tensor memory (S: 128 columns, O: head-size columns); one lane issues
+//            S = Q K^T for tile j+1 as soon as the softmax warps have read S of tile j, then
+//            O += P V for tile j when P is in shared memory.  V is used as it lies in the
+//            cache ([key][d], the "MN-major" operand form), no transpose.
+//   warps 2-9  two threads per row (row = tensor-memory lane, each thread half of the tile's
+//            keys): read S into registers, exchange the row maximum through shared memory,
+//            keep the running maximum and sum in 32-bit, write P as bfloat16
+//            into the swizzled operand tile, and rescales O in tensor memory only when the
+//            maximum has grown by more than 2^8 (any fixed reference maximum gives the same
+//            quotient; the threshold only bounds the magnitudes).  At the end it divides O by
+//            the sum and writes the row.
+// Every mbarrier wait is bounded; on expiry a flag is raised, the CTA drains and frees its
+// tensor memory.  No cluster, no multicast.
+//
+// Reference counterparts: the query-tile prefill kernel on MMAs
+// (crates/backend/cuda-kernels/src/tile/attention/resident_attention_prefill_kernels.rs:378-469)
+// and the CuTe-generated sm_100a artifact that the reference ships for another geometry only
+// (crates/backend/cuda/kernels/fa4-attention/README.md:30-34).  Formula:
+// crates/testing/cpu/reference-ops/src/kernels.rs:251-297.
+#include <cuda.h>
+#include <math.h>
+#include <mutex>
+#include <unordered_map>
+#include "common.cuh"
+
+using namespace ilb;
+
+namespace {
+
+constexpr int kRows = 128;             // rows of a CTA = MMA M
+constexpr int kKeys = 128;             // keys per tile = MMA N of S, K extent of P V
+constexpr int kThreads = 320;           // TMA warp, MMA warp, 8 softmax warps (two threads per row)
+constexpr int kStages = 2;
+constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleStep = 8.0f;   // log2 units
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kWaitLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// K-major operand (rows of 128 bytes along K, 8-row groups 1024 bytes apart), 128-byte swizzle.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// MN-major operand: 128-byte rows run along MN (64 elements), one row per K index, 8 K
+// indices per 1024-byte group (stride byte offset); the next 64 MN elements are
+// `mn_group_bytes` further (leading byte offset).  128-byte swizzle.
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t mn_group_bytes) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)((mn_group_bytes >> 4) & 0x3FFF) << 16) |
+         ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// D 32-bit, A bfloat16 K-major, B bfloat16 K-major or MN-major.
+__host__ __device__ constexpr uint32_t instr_desc(int mma_m, int mma_n, int b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(mma_n >> 3) << 17) |
+         ((uint32_t)(mma_m >> 4) << 24);
+}
+__device__ __forceinline__ void tmem_load_32(uint32_t addr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(addr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_store_32(uint32_t addr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(addr),
+        "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+struct Params {
+  __nv_bfloat16* out;
+  const int* positions; const int* cu_q; const int* block_table;
+  int* error_flag;
+  int max_blocks, n_seqs, nq, nkv, window, out_stride, page_size, num_pages;
+  float scale_log2;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                  const __grid_constant__ CUtensorMap map_v, const Params p) {
+  constexpr int kChunks = D / 64;                       // 64-wide slices of the head
+  constexpr uint32_t kSlice = kRows * 128;              // bytes of a [128][64] bf16 slice
+  constexpr uint32_t kQBytes = kChunks * kSlice;
+  constexpr uint32_t kKBytes = kChunks * kSlice;        // [slice][128 keys][64]
+  constexpr uint32_t kVBytes = kChunks * kSlice;        // [slice of d][128 keys][64]
+  constexpr uint32_t kPBytes = 2 * kSlice;              // [slice of keys][128 rows][64]
+  constexpr uint32_t kTmemCols = 256;                   // S: 128, O: D (<= 128)
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();                      // q, the cache and the step's arrays come from earlier work in the stream
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t q_s = base, k_s = q_s + kQBytes, v_s = k_s + kStages * kKBytes, p_s = v_s + kStages * kVBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (p_s - base) + kPBytes);
+  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t q_full = bar0, k_full = bar0 + 8, k_empty = k_full + 8 * kStages, v_full = k_empty + 8 * kStages,
+                 v_empty = v_full + 8 * kStages, s_full = v_empty + 8 * kStages, s_free = s_full + 8,
+                 p_full = s_free + 8, o_done = p_full + 8;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 5 + 4 * kStages);
+  volatile int* failed = reinterpret_cast<volatile int*>(bars + 6 + 4 * kStages);
+  float* xmax = reinterpret_cast<float*>(bars + 8 + 4 * kStages);      // [2][2][128] row maxima, then [2][128] row sums
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = p.nq / p.nkv;
+  const int kvh = blockIdx.y;
+  const int tokens_per_tile = kRows / G;
+
+  // which sequence and which row tile of it; long tiles first
+  int seq = 0, tile = (int)gridDim.x - 1 - (int)blockIdx.x;
+  for (; seq < p.n_seqs; ++seq) {
+    const int n = p.cu_q[seq + 1] - p.cu_q[seq];
+    const int tiles = (n + tokens_per_tile - 1) / tokens_per_tile;
+    if (tile < tiles) break;
+    tile -= tiles;
+  }
+  if (seq >= p.n_seqs) return;
+  const int tok0 = p.cu_q[seq], q_len = p.cu_q[seq + 1] - tok0;
+  const int t_first = tile * tokens_per_tile;
+  const int t_last = min(q_len, t_first + tokens_per_tile) - 1;
+  // positions are written by the step's staging copy, an earlier operation in the stream
+  const int pos_first = p.positions[tok0 + t_first], pos_last = p.positions[tok0 + t_last];
+  const int key_lo = (p.window > 0 && pos_first + 1 > p.window) ? pos_first + 1 - p.window : 0;
+  const int first_tile = key_lo / kKeys;
+  const int n_tiles = pos_last / kKeys - first_tile + 1;
+  const int* table = p.block_table + (size_t)seq * p.max_blocks;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(k_full + 8 * s, 1); mbar_init(k_empty + 8 * s, 1);
+      mbar_init(v_full + 8 * s, 1); mbar_init(v_empty + 8 * s, 1);
+    }
+    mbar_init(s_full, 1); mbar_init(s_free, 256); mbar_init(p_full, 256); mbar_init(o_done, 1);
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + kKeys;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      bool ok = true;
+      mbar_expect_tx(q_full, kQBytes);
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) tma_load_3d(q_s + c * kSlice, &map_q, q_full, c * 64, kvh * G, tok0 + t_first);
+      const int pages_per_tile = kKeys / p.page_size;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % kStages;
+        const int key0 = (first_tile + j) * kKeys;
+        int pages[8];                                     // page_size >= 16: at most 8 pages per tile
+        for (int i = 0; i < pages_per_tile; ++i) {
+          const int blk = key0 / p.page_size + i;
+          const int page = blk < p.max_blocks ? __ldg(table + blk) : -1;
+          pages[i] = (page >= 0 && page < p.num_pages && key0 + i * p.page_size <= pos_last) ? page : p.num_pages;
+        }
+        if (j >= kStages) ok = mbar_wait(k_empty + 8 * s, ((j / kStages) - 1) & 1);
+        if (!ok) break;
+        mbar_expect_tx(k_full + 8 * s, kKBytes);
+        for (int i = 0; i < pages_per_tile; ++i)
+#pragma unroll
+          for (int c = 0; c < kChunks; ++c)
+            tma_load_4d(k_s + s * kKBytes + c * kSlice + i * p.page_size * 128, &map_k, k_full + 8 * s, c * 64, 0, kvh, pages[i]);
+        if (j >= kStages) ok = mbar_wait(v_empty + 8 * s, ((j / kStages) - 1) & 1);
+        if (!ok) break;
+        mbar_expect_tx(v_full + 8 * s, kVBytes);
+        for (int i = 0; i < pages_per_tile; ++i)
+#pragma unroll
+          for (int c = 0; c < kChunks; ++c)
+            tma_load_4d(v_s + s * kVBytes + c * kSlice + i * p.page_size * 128, &map_v, v_full + 8 * s, c * 64, 0, kvh, pages[i]);
+      }
+      if (!ok) { *failed = 1; if (p.error_flag) *p.error_flag = 1; }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = instr_desc(kRows, kKeys, 0);
+      constexpr uint32_t idesc_o = instr_desc(kRows, D, 1);
+      bool ok = mbar_wait(q_full, 0);
+      auto issue_s = [&](int j) {          // S = Q K_j^T
+        const int s = j % kStages;
+        ok = ok && mbar_wait(k_full + 8 * s, (j / kStages) & 1);
+        if (j > 0) ok = ok && mbar_wait(s_free, (j - 1) & 1);
+        if (!ok) return;
+        tcgen05_fence_after();
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            mma_bf16(tmem_s, desc_k_major(q_s + c * kSlice) + 2 * k, desc_k_major(k_s + s * kKBytes + c * kSlice) + 2 * k,
+                     idesc_s, (c > 0 || k > 0) ? 1u : 0u);
+        tcgen05_commit(k_empty + 8 * s);
+        tcgen05_commit(s_full);
+      };
+      if (ok) issue_s(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) issue_s(j + 1);
+        const int s = j % kStages;
+        ok = ok && mbar_wait(p_full, j & 1);
+        ok = ok && mbar_wait(v_full + 8 * s, (j / kStages) & 1);
+        if (!ok) break;
+        tcgen05_fence_after();
+#pragma unroll
+        for (int k = 0; k < kKeys / 16; ++k)   // 16 keys a step: 32 bytes along P's rows, two 8-key groups of V
+          mma_bf16(tmem_o, desc_k_major(p_s + (k / 4) * kSlice) + 2 * (k % 4),
+                   desc_mn_major(v_s + s * kVBytes + k * 2048, kSlice), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+        tcgen05_commit(v_empty + 8 * s);
+        tcgen05_commit(o_done);
+      }
+      if (!ok) {
+        *failed = 1; if (p.error_flag) *p.error_flag = 1;
+        tcgen05_commit(s_full); tcgen05_commit(o_done);       // let the softmax warps leave their waits
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax, correction, output
+    // Two threads per row: warps 2-5 take keys 0..63 of a tile (and the first half of the
+    // head's columns of O), warps 6-9 keys 64..127 (and the second half).
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    const int tl = t_first + row / G;
+    const bool live = tl < q_len;
+    const int head = kvh * G + row % G;
+    const int pos = live ? p.positions[tok0 + tl] : -1;
+    const int lo = (live && p.window > 0 && pos + 1 > p.window) ? pos + 1 - p.window : 0;
+    constexpr int kOCols = D / 2;                      // columns of O this thread owns
+    float m_used = -1e30f, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int key0 = (first_tile + j) * kKeys + half * 64;
+      // `ok` only ever changes through waits that all 256 threads share, so they leave the
+      // loop together and nobody is left alone at the named barrier below
+      if (!mbar_wait(s_full, j & 1)) ok = false;
+      tcgen05_fence_after();
+      if (!ok) break;
+      float v[64];
+      {
+        float a[32], b2[32];
+        tmem_load_32(tmem_s + lane_addr + half * 64, a);
+        tmem_load_32(tmem_s + lane_addr + half * 64 + 32, b2);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) { v[c] = a[c]; v[32 + c] = b2[c]; }
+      }
+      tcgen05_fence_before();
+      mbar_arrive(s_free);                             // S is in registers: the next Q K^T may overwrite it
+      // scores in log2 units; keys this row may not see become -inf
+      const bool all_visible = key0 + 63 <= pos && key0 >= lo;
+      float mx = -INFINITY;
+      if (all_visible) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) { v[c] *= p.scale_log2; mx = fmaxf(mx, v[c]); }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          const int key = key0 + c;
+          v[c] = (key <= pos && key >= lo) ? v[c] * p.scale_log2 : -INFINITY;
+          mx = fmaxf(mx, v[c]);
+        }
+      }
+      xmax[(j & 1) * 256 + half * 128 + row] = mx;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      mx = fmaxf(mx, xmax[(j & 1) * 256 + (half ^ 1) * 128 + row]);
+      // the operand tile P and the accumulator O are free once the previous P V has run
+      if (j > 0 && !mbar_wait(o_done, (j - 1) & 1)) ok = false;
+      tcgen05_fence_after();
+      if (!ok) break;
+      const bool grow = mx > m_used + kRescaleStep;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = grow ? mx : m_used;
+        const float corr = exp2f(m_used - m_new);
+        if (j > 0) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < kOCols; c0 += 32) {
+            float o[32];
+            tmem_load_32(tmem_o + lane_addr + half * kOCols + c0, o);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c] *= corr;
+            tmem_store_32(tmem_o + lane_addr + half * kOCols + c0, o);
+          }
+        }
+        l *= corr;
+        m_used = m_new;
+      }
+      // exponentials, row sum, P as bfloat16 into the swizzled operand tile (slice = half)
+      float sum = 0.f;
+      uint8_t* prow = smem + (p_s - base) + half * kSlice + (row / 8) * 1024 + (row % 8) * 128;
+#pragma unroll
+      for (int piece = 0; piece < 8; ++piece) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float e0 = exp2f(v[piece * 8 + 2 * e] - m_used), e1 = exp2f(v[piece * 8 + 2 * e + 1] - m_used);
+          __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+          const float2 r = __bfloat1622float2(h);      // the sum runs over what the P V product will use
+          sum += r.x + r.y;
+          packed[e] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(prow + ((piece ^ (row % 8)) * 16)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      }
+      l += sum;
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core
+      tcgen05_fence_before();
+      mbar_arrive(p_full);
+    }
+    if (ok && !mbar_wait(o_done, (n_tiles - 1) & 1)) ok = false;
+    tcgen05_fence_after();
+    if (!ok) { *failed = 1; if (p.error_flag) *p.error_flag = 1; }
+    // the two halves of a row add their sums
+    xmax[512 + half * 128 + row] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    l += xmax[512 + (half ^ 1) * 128 + row];
+    if (ok) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* dst = p.out + (size_t)(tok0 + (live ? tl : 0)) * p.out_stride + (size_t)head * D + half * kOCols;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kOCols; c0 += 32) {
+        float o[32];
+        tmem_load_32(tmem_o + lane_addr + half * kOCols + c0, o);       // collective: every lane of the warp takes part
+        if (live) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 w;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(o[8 * q] * inv, o[8 * q + 1] * inv);
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(o[8 * q + 2] * inv, o[8 * q + 3] * inv);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(o[8 * q + 4] * inv, o[8 * q + 5] * inv);
+            __nv_bfloat162 h3 = __floats2bfloat162_rn(o[8 * q + 6] * inv, o[8 * q + 7] * inv);
+            w.x = *reinterpret_cast<uint32_t*>(&h0); w.y = *reinterpret_cast<uint32_t*>(&h1);
+            w.z = *reinterpret_cast<uint32_t*>(&h2); w.w = *reinterpret_cast<uint32_t*>(&h3);
+            *reinterpret_cast<uint4*>(dst + c0 + 8 * q) = w;
+          }
+        }
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  });
+  return fn;
+}
+
+int encode(CUtensorMap* out, const void* ptr, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
+           const cuuint32_t* box, const char* what) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail("attention (tensor cores): cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("attention (tensor cores): cuTensorMapEncodeTiled failed for %s with code %d", what, (int)r);
+  return 0;
+}
+
+template <int D>
+int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, int n_tiles,
+           cudaStream_t stream) {
+  constexpr int kChunks = D / 64;
+  constexpr size_t smem = (size_t)kChunks * kRows * 128 * (1 + 2 * kStages) + 2 * kRows * 128 + 1024 + (8 + 4 * kStages) * 8 + 768 * 4;
+  static_assert(smem <= 227 * 1024, "tiles do not fit shared memory");
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail("attention (tensor cores): cannot reserve %zu bytes of shared memory", smem);
+    configured = true;
+  }
+  ilb::launch(prefill_tc_kernel<D>, dim3(n_tiles, p.nkv), dim3(kThreads), smem, stream, mq, mk, mv, p);
+  return check_launch("attention prefill (tensor cores)");
+}
+
+}  // namespace
+
+// Geometry this kernel is built for; everything else takes attention_flash / attention_simple.
+ILB_EXPORT int ilb_attention_tc_supported(int nq, int nkv, int d, int page_size) {
+  if (nkv <= 0 || nq % nkv != 0) return 0;
+  const int g = nq / nkv;
+  return ((d == 64 || d == 128) && g <= 128 && 128 % g == 0 &&
+          (page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128)) ? 1 : 0;
+}
+
+// n_tiles = sum over sequences of ceil(q_len / (128 / G)).
+ILB_EXPORT int ilb_attention_prefill_tc(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                        const int* positions, const int* cu_q, const int* block_table,
+                                        int max_blocks, int page_size, int num_pages, int window, float scale,
+                                        int n_tokens, int n_seqs, int n_tiles, int nq, int nkv, int d,
+                                        int q_stride, int out_stride, int* error_flag, cudaStream_t stream) {
+  ILB_REQUIRE(ilb_attention_tc_supported(nq, nkv, d, page_size),
+              "attention (tensor cores): heads %d/%d, head size %d, page size %d are not built", nq, nkv, d, page_size);
+  ILB_REQUIRE(n_tokens > 0 && n_seqs > 0 && n_tiles > 0 && nkv <= 65535 && max_blocks > 0 && num_pages > 0 && window >= 0,
+              "attention (tensor cores): bad sizes");
+  ILB_REQUIRE(q_stride % 8 == 0 && out_stride % 8 == 0 && ((uintptr_t)q % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
+              ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0), "attention (tensor cores): misaligned operands");
+  const int G = nq / nkv;
+  CUtensorMap mq, mk, mv;
+  {   // q as (d, heads, tokens); a box is 64 x G x 128/G = the 128 rows of a tile, one slice of the head
+    const cuuint64_t dims[3] = {(cuuint64_t)d, (cuuint64_t)nq, (cuuint64_t)n_tokens};
+    const cuuint64_t strides[2] = {(cuuint64_t)d * 2, (cuuint64_t)q_stride * 2};
+    const cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(kRows / G)};
+    if (encode(&mq, q, 3, dims, strides, box, "q")) return -1;
+  }
+  {   // cache as (d, key in page, kv head, page); a box is one page of one head, one slice of the head
+    const cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)page_size, (cuuint64_t)nkv, (cuuint64_t)num_pages};
+    const cuuint64_t strides[3] = {(cuuint64_t)d * 2, (cuuint64_t)d * 2 * page_size, (cuuint64_t)d * 2 * page_size * nkv};
+    const cuuint32_t box[4] = {64, (cuuint32_t)page_size, 1, 1};
+    if (encode(&mk, k_cache, 4, dims, strides, box, "k cache")) return -1;
+    if (encode(&mv, v_cache, 4, dims, strides, box, "v cache")) return -1;
+  }
+  Params p{(__nv_bfloat16*)out, positions, cu_q, block_table, error_flag, max_blocks, n_seqs, nq, nkv, window,
+           out_stride, page_size, num_pages, scale * kLog2e};
+  return d == 64 ? launch<64>(mq, mk, mv, p, n_tiles, stream) : launch<128>(mq, mk, mv, p, n_tiles, stream);
+}
+
+ILB_DEFINE_LAST_ERROR()

@@ -35,6 +35,7 @@ MODULES: Dict[str, List[str]] = {
     "qk_norm_rope": [],
     "attention_simple": [],
     "attention_flash": [],
+    "attention_tc": [],
     "sampling": [],
 }
 

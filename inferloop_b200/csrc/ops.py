@@ -222,8 +222,8 @@ def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, uniform:
 
 # --------------------------------------------------------------------------- tensor-core GEMM
 class _TcState:
-    """Per-device scratch of the tensor-core GEMM: split-K workspace, tile tickets (zero
-    between launches) and the flag a kernel raises when a bounded wait runs out."""
+    """Per-device scratch of the tensor-core kernels: the GEMM's split-K workspace and tile
+    tickets (zero between launches), and the flag a kernel raises when a bounded wait runs out."""
 
     def __init__(self, device: torch.device) -> None:
         lib = load_module("gemm_tcgen05")
@@ -283,7 +283,7 @@ def check_device_errors() -> None:
         if int(st.error.item()) != 0:
             st.error.zero_()
             st.tickets.zero_()
-            raise KernelError(f"a tensor-core GEMM on {dev} gave up waiting on a barrier; its output is invalid")
+            raise KernelError(f"a tensor-core kernel on {dev} gave up waiting on a barrier; its output is invalid")
 
 
 # --------------------------------------------------------------------------- attention dispatch
@@ -301,6 +301,28 @@ def decode_chunk_for(max_positions: int) -> int:
 
 def attention_flash_supported(d: int) -> bool:
     return d in (32, 64, 96, 128)
+
+
+def attention_tc_supported(nq: int, nkv: int, d: int, page_size: int) -> bool:
+    """Geometries the tcgen05 prefill attention is built for."""
+    if nkv <= 0 or nq % nkv:
+        return False
+    g = nq // nkv
+    return d in (64, 128) and g <= 128 and 128 % g == 0 and page_size in (16, 32, 64, 128)
+
+
+def attention_prefill_tc(q, out, k_cache, v_cache, positions, cu_q, block_table, window, scale, n_seqs,
+                         n_tiles, nq, nkv, d) -> None:
+    """Prefill attention on tcgen05 tensor cores (attention_tc.cu); n_tiles counts tiles of
+    128 / (nq / nkv) tokens over the sequences."""
+    for t, w in ((q, "q"), (out, "out"), (k_cache, "k cache"), (v_cache, "v cache")):
+        _need(t, "attention " + w, torch.bfloat16)
+    num_pages, _, page_size, _ = k_cache.shape
+    st = _tc_state(q.device)
+    _call("attention_tc", "ilb_attention_prefill_tc", _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache),
+          _ptr(positions), _ptr(cu_q), _ptr(block_table), _i(block_table.shape[1]), _i(page_size),
+          _i(num_pages), _i(window or 0), _f(scale), _i(q.shape[0]), _i(n_seqs), _i(n_tiles), _i(nq), _i(nkv),
+          _i(d), _i(q.shape[1]), _i(out.shape[1]), _ptr(st.error), _stream(q))
 
 
 def attention_prefill(q, out, k_cache, v_cache, positions, cu_q, block_table, window, scale, n_seqs,
@@ -348,6 +370,11 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
         tickets = workspace.zeroed("attn.decode_tickets", (max(step.n_seqs * nkv, 4096),), torch.int32)
         attention_decode(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
                          step.n_seqs, nq, nkv, d, decode_chunk, max_chunks, scratch, tickets)
+    elif TC_ATTENTION_ENABLED and attention_tc_supported(nq, nkv, d, k_cache.shape[2]):
+        per_tile = 128 // G
+        n_tiles = sum(-(-n // per_tile) for n in step.h_q_len)
+        attention_prefill_tc(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
+                             step.n_seqs, n_tiles, nq, nkv, d)
     else:
         n_tiles = sum(-(-n * G // 64) for n in step.h_q_len)
         attention_prefill(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
@@ -355,3 +382,4 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
 
 
 FLASH_ENABLED = True       # tests switch it off to exercise the exact kernel in bfloat16
+TC_ATTENTION_ENABLED = True   # tests switch it off to reach the mma.sync prefill kernel at its geometries

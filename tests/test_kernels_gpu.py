@@ -454,3 +454,53 @@ def test_gemm_tcgen05_swiglu_epilogue(M, I, K, max_ctas, out_dtype):
     u = a.double() @ wu.double().T
     ref = g * torch.sigmoid(g) * u
     close(out, ref, out_dtype, scale=float(ref.abs().max()), what=f"swiglu {M}x{I}x{K}")
+
+
+# ------------------------------------------------------------------ tcgen05 prefill attention
+@pytest.mark.parametrize("nq,nkv,d,page_size,window", [(32, 8, 128, 16, 0), (8, 1, 128, 16, 0), (4, 2, 64, 32, 0),
+                                                         (16, 16, 64, 16, 0), (32, 8, 128, 64, 100), (2, 2, 128, 128, 0),
+                                                         (64, 2, 64, 16, 300)])
+def test_tc_prefill_mixed_batch(nq, nkv, d, page_size, window):
+    """Whole prompts, a portion that starts mid-sequence, single tokens, a long prompt whose
+    row tiles cross many key tiles; pages shuffled."""
+    o = ops()
+    assert o.attention_tc_supported(nq, nkv, d, page_size)
+    torch.manual_seed(nq * 3 + d)
+    lens, q_lens = [37, 390, 131, 700, 129], [37, 123, 1, 700, 2]
+    seqs = [(torch.randn(n, nkv, d).to(torch.bfloat16).double(), torch.randn(n, nkv, d).to(torch.bfloat16).double()) for n in lens]
+    q = torch.randn(sum(q_lens), nq * d).to(torch.bfloat16)
+    out, positions, seq_of = run_flash(q, seqs, lens, q_lens, nq, nkv, d, page_size, window)
+    o.check_device_errors()
+    ref = torch.stack([ref_attention(q[t].double().view(nq, d), *seqs[seq_of[t]], positions[t], window).reshape(-1)
+                       for t in range(len(positions))])
+    close_flash(out, ref, max(float(v.abs().max()) for _, v in seqs), "tc prefill")
+    # the mma.sync kernel at the same geometry, for the record that both paths are alive
+    o.TC_ATTENTION_ENABLED = False
+    try:
+        out2, _, _ = run_flash(q, seqs, lens, q_lens, nq, nkv, d, page_size, window)
+    finally:
+        o.TC_ATTENTION_ENABLED = True
+    close_flash(out2, ref, max(float(v.abs().max()) for _, v in seqs), "flash prefill")
+
+
+def test_tc_prefill_finds_one_far_key_and_respects_the_window_edge():
+    nq, nkv, d, page = 4, 1, 128, 16
+    n = 900
+    torch.manual_seed(4)
+    k = torch.randn(n, nkv, d) * 0.1
+    v = torch.arange(n, dtype=torch.float32)[:, None, None].expand(n, nkv, d).clone()
+    for far, window, expect in ((13, 0, 13.0), (899 - 50 + 1, 50, 850.0), (899 - 50, 50, None), (511, 0, 511.0), (640, 0, 640.0)):
+        kk = k.clone()
+        direction = torch.randn(d)
+        direction /= direction.norm()
+        kk[far, 0] = direction * 40
+        q = torch.randn(5, nq, d) * 0.01
+        q[-1, :] = direction * 40
+        out, _, _ = run_flash(q.reshape(5, -1).to(torch.bfloat16), [(kk.to(torch.bfloat16).double(), v.double())],
+                              [n], [5], nq, nkv, d, page, window, seed=far)
+        ops().check_device_errors()
+        got = out[-1].float().cpu()
+        if expect is not None:
+            assert torch.allclose(got, torch.full_like(got, expect), rtol=2.0 ** -7), (far, window, got[:4])
+        else:
+            assert 850.0 <= got.min().item() and got.max().item() <= 899.0
