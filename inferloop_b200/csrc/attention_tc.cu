@@ -221,38 +221,47 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
+    // A tile is up to 16 boxes per tensor (one per page and 64-wide slice of the head); the
+    // warp's lanes issue them side by side, lanes 0-15 the K boxes and 16-31 the V boxes,
+    // after lane 0 has seen the stage free and armed its barrier.
     if (lane == 0) {
-      bool ok = true;
       mbar_expect_tx(q_full, kQBytes);
 #pragma unroll
       for (int c = 0; c < kChunks; ++c) tma_load_3d(q_s + c * kSlice, &map_q, q_full, c * 64, kvh * G, tok0 + t_first);
-      const int pages_per_tile = kKeys / p.page_size;
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % kStages;
-        const int key0 = (first_tile + j) * kKeys;
-        int pages[8];                                     // page_size >= 16: at most 8 pages per tile
-        for (int i = 0; i < pages_per_tile; ++i) {
-          const int blk = key0 / p.page_size + i;
-          const int page = blk < p.max_blocks ? __ldg(table + blk) : -1;
-          pages[i] = (page >= 0 && page < p.num_pages && key0 + i * p.page_size <= pos_last) ? page : p.num_pages;
-        }
-        if (j >= kStages) ok = mbar_wait(k_empty + 8 * s, ((j / kStages) - 1) & 1);
-        if (!ok) break;
-        mbar_expect_tx(k_full + 8 * s, kKBytes);
-        for (int i = 0; i < pages_per_tile; ++i)
-#pragma unroll
-          for (int c = 0; c < kChunks; ++c)
-            tma_load_4d(k_s + s * kKBytes + c * kSlice + i * p.page_size * 128, &map_k, k_full + 8 * s, c * 64, 0, kvh, pages[i]);
-        if (j >= kStages) ok = mbar_wait(v_empty + 8 * s, ((j / kStages) - 1) & 1);
-        if (!ok) break;
-        mbar_expect_tx(v_full + 8 * s, kVBytes);
-        for (int i = 0; i < pages_per_tile; ++i)
-#pragma unroll
-          for (int c = 0; c < kChunks; ++c)
-            tma_load_4d(v_s + s * kVBytes + c * kSlice + i * p.page_size * 128, &map_v, v_full + 8 * s, c * 64, 0, kvh, pages[i]);
-      }
-      if (!ok) { *failed = 1; if (p.error_flag) *p.error_flag = 1; }
     }
+    const int pages_per_tile = kKeys / p.page_size;
+    const int box = lane & 15, box_page = box / kChunks, box_slice = box % kChunks;
+    const bool has_box = box < pages_per_tile * kChunks;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int s = j % kStages;
+      const int key0 = (first_tile + j) * kKeys;
+      int page = p.num_pages;                             // outside the tensor: TMA fills zeros
+      if (has_box) {
+        const int blk = key0 / p.page_size + box_page;
+        const int pg = blk < p.max_blocks ? __ldg(table + blk) : -1;
+        if (pg >= 0 && pg < p.num_pages && key0 + box_page * p.page_size <= pos_last) page = pg;
+      }
+      if (lane == 0) {
+        if (j >= kStages) ok = mbar_wait(k_empty + 8 * s, ((j / kStages) - 1) & 1);
+        if (ok) mbar_expect_tx(k_full + 8 * s, kKBytes);
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      if (has_box && lane < 16)
+        tma_load_4d(k_s + s * kKBytes + box_slice * kSlice + box_page * p.page_size * 128, &map_k, k_full + 8 * s,
+                    box_slice * 64, 0, kvh, page);
+      if (lane == 0) {
+        if (j >= kStages) ok = mbar_wait(v_empty + 8 * s, ((j / kStages) - 1) & 1);
+        if (ok) mbar_expect_tx(v_full + 8 * s, kVBytes);
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      if (has_box && lane >= 16)
+        tma_load_4d(v_s + s * kVBytes + box_slice * kSlice + box_page * p.page_size * 128, &map_v, v_full + 8 * s,
+                    box_slice * 64, 0, kvh, page);
+    }
+    if (!ok && lane == 0) { *failed = 1; if (p.error_flag) *p.error_flag = 1; }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
