@@ -131,6 +131,24 @@ __device__ __forceinline__ void tmem_load_16(uint32_t addr, float (&v)[32]) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// ---- thread-block cluster: barrier over all threads of the cluster, reads of a peer's shared memory
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ float ld_peer_f32(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
 struct Params {
   void* out;                 // [M, N], bf16 or f32
   const float* bias;         // [N] or null
@@ -145,6 +163,7 @@ struct Params {
   long long sk_tile0;        // first tile of the stream-K part = dp_waves * grid
   int epilogue;              // Epilogue
   int out_f32;               // element type of out
+  int cluster;               // > 1: a tile's K ranges belong to the CTAs of one cluster, added through their shared memory
 };
 
 // Work: first `dp_waves` rounds of WHOLE tiles in wave order (round w: CTA c takes tile
@@ -340,6 +359,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       const bool whole = cnt == p.k_blocks;
       bool last = whole;
       int c_first = 0, c_last = 0;
+      if (SWAP && !whole && p.cluster > 1) {
+        // This CTA's share goes to its own shared memory ([col][row]; the stage ring is idle,
+        // every load into it has been consumed); the cluster adds the shares after the roles.
+        float* red = reinterpret_cast<float*>(smem);
+        for (int c0 = 0; c0 < BN; c0 += CH) {
+          float v[32];
+          if (CH == 32) tmem_load_32(taddr + c0, v); else tmem_load_16(taddr + c0, v);
+#pragma unroll
+          for (int c = 0; c < CH; ++c) red[(c0 + c) * kTileX + row] = v[c];
+        }
+        break;
+      }
       if (!whole) {
         // 1. park this CTA's share of the tile: [col][row], a warp writes 128 contiguous bytes
         float* mine = p.partial + (size_t)sch.slot(blockIdx.x, tile_first) * kTileFloats;
@@ -470,19 +501,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             // X rows are output features n = xr; columns are tokens m = y0 + c
             if (xr < p.N) {
               const float bv = p.bias ? p.bias[xr] : 0.f;
+              if (p.epilogue == kAccumulate) {
+                // all the old values first: the loads are in flight together
+                float old[CH];
+#pragma unroll
+                for (int c = 0; c < CH; ++c) {
+                  const int m = y0 + c0 + c;
+                  old[c] = m < p.M ? __ldcg((const float*)p.out + (size_t)m * p.ldo + xr) : 0.f;
+                }
+#pragma unroll
+                for (int c = 0; c < CH; ++c) v[c] += old[c];
+              }
 #pragma unroll
               for (int c = 0; c < CH; ++c) {
                 const int m = y0 + c0 + c;
                 if (m < p.M) {
                   const size_t o = (size_t)m * p.ldo + xr;
-                  float r = v[c] + bv;
-                  if (p.out_f32) {
-                    float* dst = (float*)p.out + o;
-                    if (p.epilogue == kAccumulate) r += *dst;
-                    *dst = r;
-                  } else {
-                    ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(r);
-                  }
+                  const float r = v[c] + bv;
+                  if (p.out_f32) ((float*)p.out)[o] = r;
+                  else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(r);
                 }
               }
             }
@@ -547,6 +584,65 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
       }
     }
+  }
+  if (SWAP && p.cluster > 1) {
+    // The S CTAs of a cluster hold the S consecutive K ranges of one tile.  CTA r adds, in the
+    // order of increasing K, the shares of its 1/S of the tile's rows and writes them out.
+    cluster_sync_all();
+    if (warp >= 2 && flags[0] == 0) {
+      const int S = p.cluster;
+      const int r = (int)cluster_rank();
+      const long long tile = blockIdx.x / S;
+      const int x0 = (int)(tile % p.tiles_x) * kTileX, y0 = (int)(tile / p.tiles_x) * BN;
+      const bool sw = p.epilogue == kSwiGLU;
+      const int rows_per = (sw ? 64 : kTileX) / S;          // rows (gate rows) of this CTA
+      const int t = threadIdx.x - 64;
+      const int row = r * rows_per + t % rows_per;
+      const int cstep = 128 / rows_per;
+      const int n = sw ? (x0 / kTileX) * 64 + row : x0 + row;   // output feature
+      const int n_end = sw ? p.N / 2 : p.N;
+      const float bv = (p.bias && n < n_end) ? p.bias[n] : 0.f;
+      constexpr int kCols = 4;                                  // columns a thread has in flight
+      for (int cb = t / rows_per; cb < BN; cb += cstep * kCols) {
+        float acc[kCols], up[kCols], old[kCols];
+#pragma unroll
+        for (int j = 0; j < kCols; ++j) {
+          const int m = y0 + cb + j * cstep;
+          acc[j] = 0.f; up[j] = 0.f;
+          old[j] = (p.epilogue == kAccumulate && cb + j * cstep < BN && m < p.M && n < n_end)
+                       ? __ldcg((const float*)p.out + (size_t)m * p.ldo + n) : 0.f;
+        }
+        // every peer's share is requested before the first is used; the sums run in K order
+        for (int part = 0; part < (sw ? 2 : 1); ++part) {
+          float share[8][kCols];
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+#pragma unroll
+            for (int j = 0; j < kCols; ++j) {
+              const int c = cb + j * cstep;
+              share[q][j] = (q < S && c < BN)
+                                ? ld_peer_f32(base + (uint32_t)(c * kTileX + part * 64 + row) * 4u, (uint32_t)q) : 0.f;
+            }
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+#pragma unroll
+            for (int j = 0; j < kCols; ++j) {
+              if (part == 0) acc[j] += share[q][j]; else up[j] += share[q][j];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kCols; ++j) {
+          const int c = cb + j * cstep, m = y0 + c;
+          if (c < BN && m < p.M && n < n_end) {
+            const float g = acc[j];
+            const float v = sw ? g / (1.0f + __expf(-g)) * up[j] : g + bv + old[j];
+            const size_t o = (size_t)m * p.ldo + n;
+            if (p.out_f32) ((float*)p.out)[o] = v; else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
+          }
+        }
+      }
+    }
+    cluster_sync_all();                  // nobody leaves while a peer may still read its shares
   }
   tcgen05_fence_before();
   __syncthreads();
@@ -622,17 +718,60 @@ int sm_count() {
 }
 
 template <int BN, int STAGES, bool SWAP>
-int launch(const CUtensorMap& mx, const CUtensorMap& my, const Params& p, int grid, cudaStream_t stream) {
-  constexpr size_t smem = (size_t)STAGES * (kTileX * kBlockK * 2 + BN * kBlockK * 2) + 1024 + (2 * STAGES + 6) * 8 +
-                          (SWAP ? 32 * 64 * 4 : 0);
+constexpr size_t smem_bytes() {
+  return (size_t)STAGES * (kTileX * kBlockK * 2 + BN * kBlockK * 2) + 1024 + (2 * STAGES + 6) * 8 + (SWAP ? 32 * 64 * 4 : 0);
+}
+
+template <int BN, int STAGES, bool SWAP>
+int configure() {
+  constexpr size_t smem = smem_bytes<BN, STAGES, SWAP>();
   static_assert(smem <= 227 * 1024, "stage ring does not fit shared memory");
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail("gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    // two CTAs of the small rings share an SM only with the largest shared-memory carve-out
+    cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
-  ilb::launch(gemm_tc_kernel<BN, STAGES, SWAP>, dim3(grid), dim3(kThreads), smem, stream, mx, my, p);
+  return 0;
+}
+
+// How many clusters of `split` CTAs of this kernel the device holds at a time (0 if unknown).
+template <int BN, int STAGES, bool SWAP>
+int active_clusters(int split) {
+  static int cache[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+  if (split < 1 || split > 8) return 0;
+  if (cache[split] != 0) return cache[split] < 0 ? 0 : cache[split];
+  if (configure<BN, STAGES, SWAP>()) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(split * 256);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem_bytes<BN, STAGES, SWAP>();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)split; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<BN, STAGES, SWAP>, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+  cache[split] = n > 0 ? n : -1;
+  return n > 0 ? n : 0;
+}
+
+int active_clusters_for(int bn, int split) {
+  switch (bn) {
+    case 16: return active_clusters<16, 5, true>(split);
+    case 32: return active_clusters<32, 5, true>(split);
+    case 64: return active_clusters<64, 8, true>(split);
+    default: return active_clusters<128, 6, true>(split);
+  }
+}
+
+template <int BN, int STAGES, bool SWAP>
+int launch(const CUtensorMap& mx, const CUtensorMap& my, const Params& p, int grid, cudaStream_t stream) {
+  constexpr size_t smem = smem_bytes<BN, STAGES, SWAP>();
+  if (configure<BN, STAGES, SWAP>()) return -1;
+  ilb::launch_cluster(gemm_tc_kernel<BN, STAGES, SWAP>, dim3(grid), dim3(kThreads), smem, stream, p.cluster, mx, my, p);
   return check_launch("gemm_tc");
 }
 
@@ -643,6 +782,8 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, const Params& p, int gr
 ILB_EXPORT long long ilb_gemm_tc_workspace_floats() { return 2ll * 256 * 256 * 128; }
 ILB_EXPORT int ilb_gemm_tc_max_tickets() { return 1 << 16; }
 
+// Clusters of `split` CTAs of the decode kernel for token tiles of `bn` that fit the device at once.
+ILB_EXPORT int ilb_gemm_tc_active_clusters(int bn, int split) { return active_clusters_for(bn, split); }
 // What the kernel can take: bf16 operands, K and the leading dimensions multiples of 8
 // (16-byte rows for TMA), 16-byte aligned bases.
 ILB_EXPORT int ilb_gemm_tc_supported(int M, int N, int K, int lda, int ldw) {
@@ -692,11 +833,20 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   // otherwise the persistent grid takes contiguous runs of units.
   const long long cap = (swap && bn <= 32) ? 2ll * sm_count() : sm_count();
   long long grid = cap;
-  if (swap && tiles <= cap) {
-    long long split = cap / tiles;
-    if (split > 8) split = 8;
-    if (split > p.k_blocks) split = p.k_blocks;
+  p.cluster = 1;
+  if (swap && tiles <= cap && max_ctas <= 0) {
+    // every tile is cut into 1, 2, 4 or 8 K ranges, one per CTA of a cluster that adds them
+    // through shared memory: no workspace round trip and no tickets
+    long long split = 1;
+    while (split < 8 && tiles * split * 2 <= cap && split * 2 <= p.k_blocks) split *= 2;
+    // all clusters resident at once, or the stragglers cost a second round
+    // All clusters resident at once, or the stragglers cost a second round.  The occupancy
+    // query counts one CTA of this kernel per SM; the small rings run two per SM, and then a
+    // cluster of `split` CTAs takes the SMs of a cluster of split / 2.
+    const bool two_per_sm = bn <= 32;
+    while (split > 1 && active_clusters_for(bn, (int)(two_per_sm ? split / 2 : split)) < tiles) split /= 2;
     grid = tiles * split;
+    p.cluster = (int)split;
   }
   if (max_ctas > 0) grid = max_ctas;       // tests and tuning runs choose the grid themselves
   if (grid > tiles * p.k_blocks) grid = tiles * p.k_blocks;
