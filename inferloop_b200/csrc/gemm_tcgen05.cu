@@ -206,7 +206,7 @@ struct Segments {
 };
 
 template <int BN, int STAGES, bool SWAP>
-__global__ void __launch_bounds__(kThreads, (SWAP && BN <= 32) ? 2 : 1)
+__global__ void __launch_bounds__(kThreads, SWAP ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, const Params p) {
   constexpr uint32_t kBytesX = kTileX * kBlockK * 2;
   constexpr uint32_t kBytesY = BN * kBlockK * 2;
@@ -762,8 +762,8 @@ int active_clusters_for(int bn, int split) {
   switch (bn) {
     case 16: return active_clusters<16, 5, true>(split);
     case 32: return active_clusters<32, 5, true>(split);
-    case 64: return active_clusters<64, 8, true>(split);
-    default: return active_clusters<128, 6, true>(split);
+    case 64: return active_clusters<64, 4, true>(split);
+    default: return active_clusters<128, 3, true>(split);
   }
 }
 
@@ -826,12 +826,11 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   const long long tiles = (long long)p.tiles_x * p.tiles_y;
   ILB_REQUIRE(tiles <= n_tickets, "gemm_tc: %lld output tiles exceed the %d tickets", tiles, n_tickets);
 
-  // Up to 32 tokens: two CTAs per SM (their rings are sized for it), one streams while
-  // the other is in its prologue or epilogue.  Wider token tiles keep one CTA and a deep ring.
-  // When the tiles are fewer than the CTAs that fit, every tile is cut into the same number
-  // of K ranges (at most 8), so that no CTA straddles two tiles and a tile's shares are few;
-  // otherwise the persistent grid takes contiguous runs of units.
-  const long long cap = (swap && bn <= 32) ? 2ll * sm_count() : sm_count();
+  // Decode shapes (swap): two CTAs per SM (the rings are sized for it), one streams while
+  // the other is in its prologue or epilogue.  When the tiles are fewer than the CTAs that
+  // fit, every tile is cut into the same number of K ranges (at most 8), so that no CTA
+  // straddles two tiles; otherwise the persistent grid takes contiguous runs of units.
+  const long long cap = swap ? 2ll * sm_count() : sm_count();
   long long grid = cap;
   p.cluster = 1;
   if (swap && tiles <= cap && max_ctas <= 0) {
@@ -843,7 +842,7 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
     // All clusters resident at once, or the stragglers cost a second round.  The occupancy
     // query counts one CTA of this kernel per SM; the small rings run two per SM, and then a
     // cluster of `split` CTAs takes the SMs of a cluster of split / 2.
-    const bool two_per_sm = bn <= 32;
+    const bool two_per_sm = true;
     while (split > 1 && active_clusters_for(bn, (int)(two_per_sm ? split / 2 : split)) < tiles) split /= 2;
     grid = tiles * split;
     p.cluster = (int)split;
@@ -868,8 +867,8 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
     switch (bn) {
       case 16: return launch<16, 5, true>(mx, my, p, (int)grid, stream);
       case 32: return launch<32, 5, true>(mx, my, p, (int)grid, stream);
-      case 64: return launch<64, 8, true>(mx, my, p, (int)grid, stream);
-      default: return launch<128, 6, true>(mx, my, p, (int)grid, stream);
+      case 64: return launch<64, 4, true>(mx, my, p, (int)grid, stream);
+      default: return launch<128, 3, true>(mx, my, p, (int)grid, stream);
     }
   }
   if (bn == 256) return launch<256, 4, false>(mx, my, p, (int)grid, stream);
