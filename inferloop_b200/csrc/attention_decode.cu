@@ -1,0 +1,536 @@
+// Split-KV decode attention over the paged bfloat16 cache: one token per sequence, the
+// keys of a (sequence, kv head) shared out over the CTAs of a thread-block cluster, K and
+// V tiles brought by TMA straight from the cache pages, the partial results merged through
+// the cluster's shared memory.
+//
+//   grid     (S, kv heads, sequences), clusters of S = 1..16 along x, S chosen so that all
+//            CTAs of the launch are resident at once.  The visible keys are cut into 32-key
+//            tiles; tile i goes to CTA i % S of the cluster.
+//   warp 2   producer: 8 lanes look up the pages of a tile (lookups of the next four tiles are
+//            always in flight) and issue its boxes: K and V, each as one box per page part
+//            and 64-wide slice of the head, 128-byte swizzle, into a ring of 3 to 12 stages guarded
+//            by full/empty mbarriers.  A page that is not held is requested outside the tensor,
+//            which TMA fills with zeros.
+//   warps 0-1  consumers: the group's query heads are the 16 rows of an m16n8k16 MMA; each
+//            warp takes 16 keys of every tile: S = Q K^T, online softmax in 32-bit, O += P V
+//            with ldmatrix from the swizzled tiles.
+//   merge    every warp leaves (max, sum, O) of its keys in its CTA's shared memory; after a
+//            cluster barrier the threads of the whole cluster each take output elements and
+//            add the cluster's records in a fixed order, reading the peers' shared memory directly.
+//            No scratch buffer, no tickets, no second pass through L2.
+// Every mbarrier wait is bounded; on expiry a flag is raised and the CTA still walks to
+// the cluster barriers, so nobody is left waiting.  No multicast.
+//
+// Reference counterparts: `partial_gqa_lanes` + `merge_gqa`, split-KV decode with the
+// group's heads padded to 16 MMA rows
+// (crates/backend/cuda-kernels/src/tile/attention/resident_attention_decode_kernels.rs:
+// 131-226, :417-451, :497-598).  Formula: crates/testing/cpu/reference-ops/src/kernels.rs:251-297.
+#include <cuda.h>
+#include <math.h>
+#include <mutex>
+#include <unordered_map>
+#include "common.cuh"
+
+using namespace ilb;
+
+namespace {
+
+constexpr int kKeys = 32;              // keys per tile
+constexpr int kMaxSplit = 16;          // CTAs of a cluster: 1, 2, 4, 8 or 16
+constexpr int kConsumers = 2;          // warps, 16 keys of a tile each
+constexpr int kThreads = (kConsumers + 1) * 32;
+constexpr int kAhead = 4;              // tiles whose page lookups are in flight
+constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kWaitLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_f32(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+struct Params {
+  const __nv_bfloat16* q; __nv_bfloat16* out;
+  const int* positions; const int* cu_q; const int* block_table;
+  int* error_flag;
+  int max_blocks, n_seqs, nq, nkv, window, q_stride, out_stride, page_size, num_pages;
+  int split;                           // CTAs of a cluster = ways a sequence's tiles are dealt out
+  float scale_log2;
+};
+
+// Address of the 16-byte piece `chunk` (0..7) of row `row` in a [rows][128 bytes] slice
+// written by TMA with the 128-byte swizzle (the slice starts on a 1024-byte boundary).
+__device__ __forceinline__ uint32_t swz(uint32_t slice, int row, int chunk) {
+  return slice + (uint32_t)row * 128u + (uint32_t)((chunk ^ (row & 7)) << 4);
+}
+
+// 16 rows (query heads) of one warp: thread (g = lane / 4, t = lane % 4) owns rows g and
+// g + 8, columns 2t, 2t + 1 of every 8-wide block.
+template <int D>
+struct RowState {
+  float o[D / 8][4];
+  float m[2], l[2];
+  __device__ __forceinline__ void init() {
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
+    m[0] = m[1] = -INFINITY;
+    l[0] = l[1] = 0.f;
+  }
+};
+
+// 16 keys (rows row0 .. row0 + 15 of the tile's K and V slices, the first being key
+// `key0`) against the warp's 16 query rows.  live[r]: row g + 8r is a head of the group;
+// keys outside [lo, hi) are not seen.
+template <int D>
+__device__ __forceinline__ void tile_step(RowState<D>& st, const uint32_t (&q)[D / 16][4], uint32_t ks, uint32_t vs,
+                                          int row0, int key0, const bool (&live)[2], int lo, int hi, float scale_log2,
+                                          int lane) {
+  constexpr uint32_t kSlice = kKeys * 128;           // bytes of one 64-wide slice of a tile
+  const int t = lane & 3;
+  float s[2][4];
+#pragma unroll
+  for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[nb][e] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < D / 16; kk += 2) {
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+      uint32_t r0, r1, r2, r3;
+      const int col = kk * 16 + (lane >> 3) * 8;       // element of the head
+      ldmatrix_x4(swz(ks + (col >> 6) * kSlice, row0 + nb * 8 + (lane & 7), (col & 63) >> 3), r0, r1, r2, r3);
+      mma_16816(s[nb], q[kk], r0, r1);
+      mma_16816(s[nb], q[kk + 1], r2, r3);
+    }
+  }
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int key = key0 + nb * 8 + 2 * t + (e & 1);
+      const int r = e >> 1;
+      const bool ok = live[r] && key >= lo && key < hi;
+      s[nb][e] = ok ? s[nb][e] * scale_log2 : -INFINITY;
+      mx[r] = fmaxf(mx[r], s[nb][e]);
+    }
+  float corr[2], base[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    const float m_new = fmaxf(st.m[r], mx[r]);
+    base[r] = (m_new == -INFINITY) ? 0.f : m_new;
+    corr[r] = exp2f(st.m[r] - base[r]);           // -inf -> 0
+    st.m[r] = m_new;
+  }
+  float sum[2] = {0.f, 0.f};
+#pragma unroll
+  for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float p = exp2f(s[nb][e] - base[e >> 1]);
+      s[nb][e] = p;
+      sum[e >> 1] += p;
+    }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) st.l[r] = st.l[r] * corr[r] + sum[r];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) {
+    st.o[i][0] *= corr[0]; st.o[i][1] *= corr[0];
+    st.o[i][2] *= corr[1]; st.o[i][3] *= corr[1];
+  }
+  uint32_t a[4];
+  a[0] = pack_bf16(s[0][0], s[0][1]);
+  a[1] = pack_bf16(s[0][2], s[0][3]);
+  a[2] = pack_bf16(s[1][0], s[1][1]);
+  a[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+  for (int nd = 0; nd < D / 16; ++nd) {
+    uint32_t r0, r1, r2, r3;
+    const int col = nd * 16 + (lane >> 4) * 8;
+    ldmatrix_x4_trans(swz(vs + (col >> 6) * kSlice, row0 + (lane & 7) + ((lane >> 3) & 1) * 8, (col & 63) >> 3), r0, r1, r2, r3);
+    mma_16816(st.o[2 * nd], a, r0, r1);
+    mma_16816(st.o[2 * nd + 1], a, r2, r3);
+  }
+}
+
+template <int D, int kStages>
+__global__ void __launch_bounds__(kThreads)
+decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const Params p) {
+  constexpr int kSlices = D / 64;
+  constexpr uint32_t kSlice = kKeys * 128;                 // bytes: one slice of one tensor of a tile
+  constexpr uint32_t kTensor = kSlices * kSlice;           // K (or V) of a tile
+  constexpr uint32_t kStage = 2 * kTensor;
+  constexpr int kRec = D + 2;                              // O row, then max and sum
+  static_assert(kConsumers * 16 * kRec * 4 <= kStages * (int)kStage, "records must fit the tile ring");
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
+  float* rec = reinterpret_cast<float*>(smem);             // [consumers][16][D + 2], once the tiles are consumed
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStage);
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * kStages;
+  volatile int* failed = reinterpret_cast<volatile int*>(bars + 2 * kStages);
+
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, kConsumers); }
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_wait();
+
+  const int G = p.nq / p.nkv;
+  const int rank = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+  const int tok = p.cu_q[seq];
+  if (p.cu_q[seq + 1] - tok != 1) return;                  // the whole cluster leaves together
+  const int pos = p.positions[tok];
+  const int lo = (p.window > 0 && pos + 1 > p.window) ? pos + 1 - p.window : 0;
+  const int hi = pos + 1;
+  const int first_tile = lo / kKeys;
+  const int n_tiles = (hi + kKeys - 1) / kKeys - first_tile;
+  const int kSplit = p.split;
+  const int n_my = rank < n_tiles ? (n_tiles - rank + kSplit - 1) / kSplit : 0;
+  const int* table = p.block_table + (size_t)seq * p.max_blocks;
+  const int rows16 = (G + 15) / 16 * 16;
+  const int n_rounds = rows16 / 16;
+  auto key_of = [&](int j) { return (first_tile + rank + j * kSplit) * kKeys; };
+
+  for (int round = 0; round < n_rounds; ++round) {         // 16 query heads of the group at a time
+    const int rb = round * 16;
+    const int it0 = round * n_my;                          // tiles this CTA has streamed before this round
+    if (warp == kConsumers) {
+      // ------------------------------------------------------------ producer
+      const int box_keys = p.page_size < kKeys ? p.page_size : kKeys;
+      const int parts = kKeys / box_keys;
+      const int per_tensor = kSlices * parts;
+      const int b = lane;
+      const bool has_box = b < 2 * per_tensor;
+      const int which = b / per_tensor, rem = b % per_tensor, slice = rem / parts, part = rem % parts;
+      auto lookup = [&](int j) {                           // page of this lane's box of tile j, or one past the tensor
+        int page = p.num_pages;
+        if (has_box && j < n_my) {
+          const int key = key_of(j) + part * box_keys;
+          const int blk = key / p.page_size;
+          if (key < hi && blk < p.max_blocks) {
+            const int pg = __ldg(table + blk);
+            if (pg >= 0 && pg < p.num_pages) page = pg;
+          }
+        }
+        return page;
+      };
+      int pg[kAhead];
+#pragma unroll
+      for (int i = 0; i < kAhead; ++i) pg[i] = lookup(i);
+      bool ok = true;
+      for (int j0 = 0; j0 < n_my && ok; j0 += kAhead) {
+#pragma unroll
+        for (int i = 0; i < kAhead; ++i) {
+          const int j = j0 + i;
+          if (j >= n_my || !ok) break;
+          const int it = it0 + j, s = it % kStages;
+          if (lane == 0) {
+            if (it >= kStages) ok = mbar_wait(empty0 + 8 * s, ((it / kStages) - 1) & 1);
+            if (ok) mbar_expect_tx(full0 + 8 * s, kStage);
+          }
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (!ok) break;
+          if (has_box)
+            tma_load_4d(base + s * kStage + which * kTensor + slice * kSlice + part * box_keys * 128,
+                        which == 0 ? &map_k : &map_v, full0 + 8 * s, slice * 64, (key_of(j) + part * box_keys) % p.page_size,
+                        kvh, pg[i]);
+          pg[i] = lookup(j + kAhead);
+        }
+      }
+      if (!ok && lane == 0) { *failed = 1; if (p.error_flag) *p.error_flag = 1; }
+    } else {
+      // ------------------------------------------------------------ consumers
+      const int g = lane >> 2, t = lane & 3;
+      RowState<D> st;
+      st.init();
+      bool live[2];
+      uint32_t q[D / 16][4];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) live[r] = rb + g + 8 * r < G;
+      {
+        const __nv_bfloat16* row0 = live[0] ? p.q + (size_t)tok * p.q_stride + (size_t)(kvh * G + rb + g) * D : nullptr;
+        const __nv_bfloat16* row1 = live[1] ? p.q + (size_t)tok * p.q_stride + (size_t)(kvh * G + rb + g + 8) * D : nullptr;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const int c = kk * 16 + 2 * t;
+          q[kk][0] = row0 ? *reinterpret_cast<const uint32_t*>(row0 + c) : 0u;
+          q[kk][1] = row1 ? *reinterpret_cast<const uint32_t*>(row1 + c) : 0u;
+          q[kk][2] = row0 ? *reinterpret_cast<const uint32_t*>(row0 + c + 8) : 0u;
+          q[kk][3] = row1 ? *reinterpret_cast<const uint32_t*>(row1 + c + 8) : 0u;
+        }
+      }
+      bool ok = true;
+      for (int j = 0; j < n_my && ok; ++j) {
+        const int it = it0 + j, s = it % kStages;
+        ok = mbar_wait(full0 + 8 * s, (it / kStages) & 1);
+        if (!ok) break;
+        const int key0 = key_of(j) + warp * 16;
+        if (key0 < hi)
+          tile_step<D>(st, q, base + s * kStage, base + s * kStage + kTensor, warp * 16, key0, live, lo, hi, p.scale_log2, lane);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + 8 * s);
+      }
+      if (!ok && lane == 0) { *failed = 1; if (p.error_flag) *p.error_flag = 1; }
+      __syncwarp();
+      // both consumer warps are past their last tile before a record overwrites the ring
+      asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        float l = st.l[r];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        float* row = rec + ((size_t)warp * 16 + g + 8 * r) * kRec;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) { row[i * 8 + 2 * t] = st.o[i][2 * r]; row[i * 8 + 2 * t + 1] = st.o[i][2 * r + 1]; }
+        if (t == 0) { row[D] = st.m[r]; row[D + 1] = l; }
+      }
+    }
+    cluster_sync_all();
+    // ---- merge: element e of the group's output from all records, CTA after CTA, warp after warp
+    const int live_rows = min(16, G - rb);
+    const uint32_t rec_addr = smem_u32(rec);
+    const int n_rec = kSplit * kConsumers;
+    for (int e = rank * kThreads + threadIdx.x; e < live_rows * D; e += kSplit * kThreads) {
+      const int row = e / D, c = e % D;
+      auto rec_of = [&](int i) { return rec_addr + (uint32_t)(((i % kConsumers) * 16 + row) * kRec) * 4u; };
+      float m_all = -INFINITY;
+      for (int i0 = 0; i0 < n_rec; i0 += 8) {                // the records' maxima, eight loads in flight
+        float m[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          m[i] = i0 + i < n_rec ? ld_peer_f32(rec_of(i0 + i) + D * 4u, (uint32_t)((i0 + i) / kConsumers)) : -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m_all = fmaxf(m_all, m[i]);
+      }
+      float l_all = 0.f, o = 0.f;
+      for (int i0 = 0; i0 < n_rec; i0 += 8) {
+        float m[8], l[8], v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const bool on = i0 + i < n_rec;
+          const uint32_t a = rec_of(on ? i0 + i : 0), peer = (uint32_t)((on ? i0 + i : 0) / kConsumers);
+          m[i] = on ? ld_peer_f32(a + D * 4u, peer) : -INFINITY;
+          l[i] = on ? ld_peer_f32(a + (D + 1) * 4u, peer) : 0.f;
+          v[i] = on ? ld_peer_f32(a + (uint32_t)c * 4u, peer) : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float f = (m[i] == -INFINITY) ? 0.f : exp2f(m[i] - m_all);
+          l_all += l[i] * f;
+          o += v[i] * f;
+        }
+      }
+      p.out[(size_t)tok * p.out_stride + (size_t)(kvh * G + rb + row) * D + c] = __float2bfloat16_rn(l_all > 0.f ? o / l_all : 0.f);
+    }
+    cluster_sync_all();                                    // the records stay until every peer has read them
+    // the next round's TMA writes land where ordinary stores and loads have just been
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr; int d, page_size, nkv, num_pages;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && d == o.d && page_size == o.page_size && nkv == o.nkv && num_pages == o.num_pages;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = std::hash<const void*>()(k.ptr);
+    for (int v : {k.d, k.page_size, k.nkv, k.num_pages}) h = h * 1000003u ^ std::hash<int>()(v);
+    return h;
+  }
+};
+
+// The cache as (d, key in page, kv head, page); a box is up to 32 keys of one page and head, one slice of the head.
+int cache_map(CUtensorMap* out, const void* ptr, int d, int page_size, int nkv, int num_pages) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  const MapKey key{ptr, d, page_size, nkv, num_pages};
+  std::lock_guard<std::mutex> g(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return 0; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail("attention decode: cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)page_size, (cuuint64_t)nkv, (cuuint64_t)num_pages};
+  const cuuint64_t strides[3] = {(cuuint64_t)d * 2, (cuuint64_t)d * 2 * page_size, (cuuint64_t)d * 2 * page_size * nkv};
+  const cuuint32_t box[4] = {64, (cuuint32_t)(page_size < kKeys ? page_size : kKeys), 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("attention decode: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return 0;
+}
+
+template <int D, int STAGES>
+constexpr size_t smem_bytes() { return (size_t)STAGES * 2 * (D / 64) * kKeys * 128 + 1024 + (2 * STAGES + 1) * 8; }
+
+template <int D, int STAGES>
+int configure() {
+  static bool configured = false;
+  if (!configured) {
+    constexpr size_t smem = smem_bytes<D, STAGES>();
+    static_assert(smem <= 227 * 1024, "tile ring does not fit shared memory");
+    cudaError_t e = cudaFuncSetAttribute(decode_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail("attention decode: cannot reserve %zu bytes of shared memory", smem);
+    cudaFuncSetAttribute(decode_kernel<D, STAGES>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(decode_kernel<D, STAGES>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    configured = true;
+  }
+  return 0;
+}
+
+// Clusters of `split` CTAs of this kernel that the device holds at a time (0 if it cannot tell or cannot run them).
+template <int D, int STAGES>
+int active_clusters(int split) {
+  static int cache[kMaxSplit + 1] = {};
+  if (split < 1 || split > kMaxSplit) return 0;
+  if (cache[split] != 0) return cache[split] < 0 ? 0 : cache[split];
+  if (configure<D, STAGES>()) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(split, 64, 8);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem_bytes<D, STAGES>();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)split; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, decode_kernel<D, STAGES>, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+  cache[split] = n > 0 ? n : -1;
+  return n > 0 ? n : 0;
+}
+
+template <int D, int STAGES>
+int launch(const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, cudaStream_t stream) {
+  if (configure<D, STAGES>()) return -1;
+  ilb::launch_cluster(decode_kernel<D, STAGES>, dim3(p.split, p.nkv, p.n_seqs), dim3(kThreads), smem_bytes<D, STAGES>(), stream,
+                      p.split, mk, mv, p);
+  return check_launch("attention decode");
+}
+
+// The ways a sequence's tiles are dealt out and the depth of the tile ring: as many CTAs as
+// fit the device at once, and the shared memory that this leaves to each of them.
+template <int D>
+int launch_for(const CUtensorMap& mk, const CUtensorMap& mv, Params& p, cudaStream_t stream) {
+  const long long pairs = (long long)p.n_seqs * p.nkv;
+  int split = kMaxSplit;
+  while (split > 1 && active_clusters<D, 3>(split) < pairs) split /= 2;
+  p.split = split;
+  if (active_clusters<D, 12>(split) >= pairs) return launch<D, 12>(mk, mv, p, stream);
+  if (active_clusters<D, 6>(split) >= pairs) return launch<D, 6>(mk, mv, p, stream);
+  return launch<D, 3>(mk, mv, p, stream);
+}
+
+}  // namespace
+
+// Geometry this kernel is built for; everything else takes the ticketed kernel of attention_flash.
+ILB_EXPORT int ilb_attention_decode_tma_supported(int nq, int nkv, int d, int page_size) {
+  if (nkv <= 0 || nq <= 0 || nq % nkv != 0) return 0;
+  return ((d == 64 || d == 128) && (page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128)) ? 1 : 0;
+}
+
+ILB_EXPORT int ilb_attention_decode_tma(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                        const int* positions, const int* cu_q, const int* block_table,
+                                        int max_blocks, int page_size, int num_pages, int window, float scale,
+                                        int n_seqs, int nq, int nkv, int d, int q_stride, int out_stride,
+                                        int* error_flag, cudaStream_t stream) {
+  ILB_REQUIRE(ilb_attention_decode_tma_supported(nq, nkv, d, page_size),
+              "attention decode: heads %d/%d, head size %d, page size %d are not built", nq, nkv, d, page_size);
+  ILB_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && nkv <= 65535 && max_blocks > 0 && num_pages > 0 && window >= 0,
+              "attention decode: bad sizes");
+  ILB_REQUIRE(q_stride % 2 == 0 && ((uintptr_t)q % 4 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0),
+              "attention decode: misaligned operands");
+  CUtensorMap mk, mv;
+  if (cache_map(&mk, k_cache, d, page_size, nkv, num_pages)) return -1;
+  if (cache_map(&mv, v_cache, d, page_size, nkv, num_pages)) return -1;
+  Params p{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, positions, cu_q, block_table, error_flag,
+           max_blocks, n_seqs, nq, nkv, window, q_stride, out_stride, page_size, num_pages, 1, scale * kLog2e};
+  return d == 64 ? launch_for<64>(mk, mv, p, stream) : launch_for<128>(mk, mv, p, stream);
+}
+
+ILB_DEFINE_LAST_ERROR()

@@ -36,6 +36,7 @@ MODULES: Dict[str, List[str]] = {
     "attention_simple": [],
     "attention_flash": [],
     "attention_tc": [],
+    "attention_decode": [],
     "sampling": [],
 }
 

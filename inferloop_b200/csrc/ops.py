@@ -349,6 +349,25 @@ def attention_decode(q, out, k_cache, v_cache, positions, cu_q, block_table, win
           _ptr(tickets), _i(tickets.numel()), _stream(q))
 
 
+def attention_decode_tma_supported(nq: int, nkv: int, d: int, page_size: int) -> bool:
+    """Geometries the cluster-merged TMA decode attention is built for."""
+    return nkv > 0 and nq > 0 and nq % nkv == 0 and d in (64, 128) and page_size in (16, 32, 64, 128)
+
+
+def attention_decode_tma(q, out, k_cache, v_cache, positions, cu_q, block_table, window, scale, n_seqs,
+                         nq, nkv, d) -> None:
+    """Split-KV decode whose tiles come by TMA and whose partial results meet inside a
+    thread-block cluster (no scratch)."""
+    for t, w in ((q, "q"), (out, "out"), (k_cache, "k cache"), (v_cache, "v cache")):
+        _need(t, "attention " + w, torch.bfloat16)
+    num_pages, _, page_size, _ = k_cache.shape
+    st = _tc_state(q.device)
+    _call("attention_decode", "ilb_attention_decode_tma", _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache),
+          _ptr(positions), _ptr(cu_q), _ptr(block_table), _i(block_table.shape[1]), _i(page_size),
+          _i(num_pages), _i(window or 0), _f(scale), _i(n_seqs), _i(nq), _i(nkv), _i(d), _i(q.shape[1]),
+          _i(out.shape[1]), _ptr(st.error), _stream(q))
+
+
 def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
               step, block_table: torch.Tensor, window: int, scale: float, nq: int, nkv: int,
               d: int, workspace=None, decode_chunk: int = DECODE_CHUNK_MIN) -> None:
@@ -362,7 +381,10 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
                                block_table, window, scale, nq, nkv, d)
         return
     G = nq // nkv
-    if step.decode_only:
+    if step.decode_only and DECODE_CLUSTER_ENABLED and attention_decode_tma_supported(nq, nkv, d, k_cache.shape[2]):
+        attention_decode_tma(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
+                             step.n_seqs, nq, nkv, d)
+    elif step.decode_only:
         page_size = k_cache.shape[2]
         capacity = block_table.shape[1] * page_size
         max_chunks = max(1, -(-capacity // decode_chunk))
@@ -381,5 +403,6 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
                           step.n_seqs, n_tiles, nq, nkv, d)
 
 
+DECODE_CLUSTER_ENABLED = True   # tests switch it off to reach the ticketed split-KV decode kernel
 FLASH_ENABLED = True       # tests switch it off to exercise the exact kernel in bfloat16
 TC_ATTENTION_ENABLED = True   # tests switch it off to reach the mma.sync prefill kernel at its geometries

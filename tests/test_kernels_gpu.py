@@ -363,7 +363,9 @@ class _Step:
         self.decode_only = all(n == 1 for n in q_lens)
 
 
-def run_flash(q, seqs, lens, q_lens, nq, nkv, d, page_size, window, chunk=256, seed=0):
+def run_flash(q, seqs, lens, q_lens, nq, nkv, d, page_size, window, chunk=256, seed=0, cluster=True):
+    """`cluster`: split-KV decode merges inside a thread-block cluster (the default of the
+    dispatcher) or through scratch records and tickets."""
     from inferloop_b200.parts import Workspace
     o = ops()
     n_pages = sum(-(-n // page_size) for n in lens) + 3
@@ -377,9 +379,14 @@ def run_flash(q, seqs, lens, q_lens, nq, nkv, d, page_size, window, chunk=256, s
     step = _Step(positions, seq_of, cu, q_lens)
     out = torch.full((len(positions), nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
     ws = Workspace(torch.device("cuda:0"))
-    for _ in range(2):      # twice: the tickets must be back at zero after the first launch
-        o.attention(q.cuda(), out, k_cache.cuda(), v_cache.cuda(), step, table.cuda(), window, 1.0 / math.sqrt(d),
-                    nq, nkv, d, workspace=ws, decode_chunk=chunk)
+    was = o.DECODE_CLUSTER_ENABLED
+    o.DECODE_CLUSTER_ENABLED = cluster
+    try:
+        for _ in range(2):      # twice: the tickets must be back at zero after the first launch
+            o.attention(q.cuda(), out, k_cache.cuda(), v_cache.cuda(), step, table.cuda(), window, 1.0 / math.sqrt(d),
+                        nq, nkv, d, workspace=ws, decode_chunk=chunk)
+    finally:
+        o.DECODE_CLUSTER_ENABLED = was
     return out, positions, seq_of
 
 
@@ -399,21 +406,23 @@ def test_flash_prefill_mixed_batch(nq, nkv, d, page_size, window):
 
 @pytest.mark.parametrize("nq,nkv,d,page_size,window,chunk", [(4, 2, 32, 4, 0, 256), (6, 2, 64, 8, 0, 256), (5, 5, 96, 16, 300, 256),
                                                                (32, 8, 128, 16, 0, 256), (8, 1, 128, 16, 0, 512), (40, 2, 64, 32, 0, 256)])
-def test_flash_decode_split_kv(nq, nkv, d, page_size, window, chunk):
-    """One token per sequence, lengths below, at and far above the chunk length."""
+@pytest.mark.parametrize("cluster", [True, False])
+def test_flash_decode_split_kv(nq, nkv, d, page_size, window, chunk, cluster):
+    """One token per sequence, lengths below, at and far above the chunk length (ticketed
+    kernel) and with fewer tiles than the cluster has CTAs, exactly as many, and many more."""
     torch.manual_seed(nq + d + 1)
-    lens = [1, 2, 63, 64, 65, 256, 257, 700, 1030, 1537]
+    lens = [1, 2, 31, 32, 33, 63, 64, 65, 255, 256, 257, 700, 1030, 1537]
     q_lens = [1] * len(lens)
     seqs = [(torch.randn(n, nkv, d).to(torch.bfloat16).double(), torch.randn(n, nkv, d).to(torch.bfloat16).double()) for n in lens]
     q = torch.randn(len(lens), nq * d).to(torch.bfloat16)
-    out, positions, seq_of = run_flash(q, seqs, lens, q_lens, nq, nkv, d, page_size, window, chunk)
+    out, positions, seq_of = run_flash(q, seqs, lens, q_lens, nq, nkv, d, page_size, window, chunk, cluster=cluster)
     ref = torch.stack([ref_attention(q[t].double().view(nq, d), *seqs[seq_of[t]], positions[t], window).reshape(-1)
                        for t in range(len(positions))])
     close_flash(out, ref, max(float(v.abs().max()) for _, v in seqs), "flash decode")
 
 
-@pytest.mark.parametrize("q_len", [1, 5])
-def test_flash_attention_finds_one_far_key_and_respects_the_window_edge(q_len):
+@pytest.mark.parametrize("q_len,cluster", [(1, True), (1, False), (5, True)])
+def test_flash_attention_finds_one_far_key_and_respects_the_window_edge(q_len, cluster):
     nq, nkv, d, page = 4, 1, 64, 16
     n = 900
     torch.manual_seed(2)
@@ -427,7 +436,7 @@ def test_flash_attention_finds_one_far_key_and_respects_the_window_edge(q_len):
         q = torch.randn(q_len, nq, d) * 0.01
         q[-1, :] = direction * 40                     # only the last token looks for the far key
         out, _, _ = run_flash(q.reshape(q_len, -1).to(torch.bfloat16), [(kk.to(torch.bfloat16).double(), v.double())],
-                              [n], [q_len], nq, nkv, d, page, window, seed=far)
+                              [n], [q_len], nq, nkv, d, page, window, seed=far, cluster=cluster)
         got = out[-1].float().cpu()
         if expect is not None:
             assert torch.allclose(got, torch.full_like(got, expect), rtol=2.0 ** -7), (far, window, got[:4])
