@@ -44,7 +44,7 @@ namespace {
 
 constexpr int kBlockK = 64;            // bf16 elements per K block = one 128-byte swizzle row
 constexpr int kTileX = 128;            // rows of the X operand = MMA M
-constexpr int kThreads = 192;
+constexpr int threads_for(int ms) { return 64 + 128 * ms; }   // TMA warp, MMA warp, four epilogue warps per 128 rows
 constexpr uint32_t kWaitLimit = 1u << 22;
 
 enum Epilogue : int { kStore = 0, kAccumulate = 1, kSwiGLU = 2 };
@@ -85,6 +85,9 @@ __device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// silu(g) * u with the fast reciprocal: the quotient is within 2 ulp, far inside what the
+// bfloat16 result keeps, and an epilogue thread has 128 of these per tile.
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 __device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
@@ -160,7 +163,7 @@ struct Params {
   int k_blocks;              // ceil(K / 64)
   long long units;           // K blocks of the tiles that are shared out stream-K fashion
   int dp_waves;              // whole-tile rounds before that: CTA c takes tiles c, c + grid, ...
-  long long sk_tile0;        // first tile of the stream-K part = dp_waves * grid
+  long long sk_tile0;        // tiles of those rounds (the last round may be short) = first tile of the stream-K part
   int epilogue;              // Epilogue
   int out_f32;               // element type of out
   int cluster;               // > 1: a tile's K ranges belong to the CTAs of one cluster, added through their shared memory
@@ -193,7 +196,8 @@ struct Segments {
   __device__ __forceinline__ bool next(long long& tile, int& kb0, int& cnt, long long& sk_first) {
     if (w < dp_waves) {
       tile = (long long)w * grid + cta; kb0 = 0; cnt = k_blocks; sk_first = -1; ++w;
-      return true;
+      if (tile < sk_tile0) return true;
+      w = dp_waves;                                 // the last round has no tile for this CTA
     }
     if (u >= u_end) return false;
     const long long t = u / k_blocks;
@@ -205,15 +209,24 @@ struct Segments {
   }
 };
 
-template <int BN, int STAGES, bool SWAP>
-__global__ void __launch_bounds__(kThreads, SWAP ? 2 : 1)
+// MS = 128-row blocks of the X operand per tile.  MS = 1: one accumulator per tile, two of
+// them in tensor memory, so a tile is written out while the next accumulates.  MS = 2 (many
+// tokens): a tile is 256 x BN, its two halves share every Y block that comes in, which cuts
+// the bytes per flop that L2 has to deliver by a third; both accumulators belong to the
+// tile, and eight epilogue warps drain them together.
+template <int BN, int STAGES, bool SWAP, int MS>
+__global__ void __launch_bounds__(threads_for(MS), SWAP ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, const Params p) {
-  constexpr uint32_t kBytesX = kTileX * kBlockK * 2;
+  static_assert(MS == 1 || (MS == 2 && !SWAP), "two row blocks per tile only for the many-token form");
+  constexpr uint32_t kBytesX1 = kTileX * kBlockK * 2;          // one 128-row block of X
+  constexpr uint32_t kBytesX = MS * kBytesX1;
   constexpr uint32_t kBytesY = BN * kBlockK * 2;
   constexpr uint32_t kStageBytes = kBytesX + kBytesY;          // multiples of 1024
   constexpr uint32_t kAccCols = BN < 32 ? 32 : BN;             // columns of one accumulator
   constexpr uint32_t kTmemCols = 2 * kAccCols;                 // two accumulators; a power of two >= 64
-  constexpr int kTileFloats = BN * kTileX;
+  constexpr int kTileFloats = BN * kTileX;                     // one 128-row block of a tile
+  constexpr int kBufs = MS == 1 ? 2 : 1;                       // tiles that tensor memory holds
+  constexpr int kEpiThreads = 128 * MS;
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // dynamic shared memory is only 16-byte aligned by contract; align by hand
@@ -237,7 +250,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 128); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, kEpiThreads); }
     flags[0] = 0; flags[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -257,47 +270,64 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // tiles of those stages follow the wait.
     if (lane == 0) {
       bool ok = true;
-      const uint32_t n_dp = (uint32_t)p.dp_waves * (uint32_t)p.k_blocks;
+      long long my_tiles = (long long)blockIdx.x < p.sk_tile0 ? (p.sk_tile0 - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+      if (my_tiles > p.dp_waves) my_tiles = p.dp_waves;
+      const uint32_t n_dp = (uint32_t)my_tiles * (uint32_t)p.k_blocks;
       const uint32_t n_units = n_dp + (uint32_t)(u_end - u_begin);
       const uint32_t n_early = n_units < (uint32_t)STAGES ? n_units : (uint32_t)STAGES;
-      auto coords = [&](uint32_t it, int& kcol, int& x0, int& y0) {
-        long long tile;
-        if (it < n_dp) {
-          tile = (long long)(it / p.k_blocks) * gridDim.x + blockIdx.x;
-          kcol = (int)(it % p.k_blocks) * kBlockK;
-        } else {
-          const long long u = u_begin + (it - n_dp);
-          tile = p.sk_tile0 + u / p.k_blocks;
-          kcol = (int)(u % p.k_blocks) * kBlockK;
+      // The units of this CTA in order, one K block a step; the divisions that find a tile's
+      // place happen once per segment, not per block: this lane's issue rate bounds the ring.
+      struct Units {
+        Segments segs;
+        int tiles_x, kb, left, x0, y0;
+        __device__ Units(const Params& p, const Schedule& sch) : segs(p, sch, blockIdx.x, gridDim.x), tiles_x(p.tiles_x), kb(0), left(0), x0(0), y0(0) {}
+        __device__ __forceinline__ bool next(int& kcol, int& x, int& y) {
+          if (left == 0) {
+            long long tile, sk_first;
+            int kb0, cnt;
+            if (!segs.next(tile, kb0, cnt, sk_first)) return false;
+            kb = kb0; left = cnt;
+            x0 = (int)(tile % tiles_x) * (MS * kTileX);
+            y0 = (int)(tile / tiles_x) * BN;
+          }
+          kcol = kb * kBlockK; x = x0; y = y0;
+          ++kb; --left;
+          return true;
         }
-        x0 = (int)(tile % p.tiles_x) * kTileX;
-        y0 = (int)(tile / p.tiles_x) * BN;
       };
-      for (uint32_t it = 0; it < n_early; ++it) {
-        int kcol, x0, y0;
-        coords(it, kcol, x0, y0);
-        const uint32_t dst = base + it * kStageBytes;
-        mbar_expect_tx(full0 + 8 * it, kStageBytes);
-        if (SWAP) tma_load_2d(dst, &map_x, full0 + 8 * it, kcol, x0);
-        else tma_load_2d(dst + kBytesX, &map_y, full0 + 8 * it, kcol, y0);
+      auto load_x = [&](uint32_t dst, uint32_t bar, int kcol, int x0) {
+#pragma unroll
+        for (int ms = 0; ms < MS; ++ms) tma_load_2d(dst + ms * kBytesX1, &map_x, bar, kcol, x0 + ms * kTileX);
+      };
+      {
+        Units early(p, sch);
+        for (uint32_t it = 0; it < n_early; ++it) {
+          int kcol, x0, y0;
+          early.next(kcol, x0, y0);
+          const uint32_t dst = base + it * kStageBytes;
+          mbar_expect_tx(full0 + 8 * it, kStageBytes);
+          if (SWAP) load_x(dst, full0 + 8 * it, kcol, x0);
+          else tma_load_2d(dst + kBytesX, &map_y, full0 + 8 * it, kcol, y0);
+        }
       }
       pdl_wait();
+      Units units(p, sch);
       for (uint32_t it = 0; it < n_early; ++it) {
         int kcol, x0, y0;
-        coords(it, kcol, x0, y0);
+        units.next(kcol, x0, y0);
         const uint32_t dst = base + it * kStageBytes;
         if (SWAP) tma_load_2d(dst + kBytesX, &map_y, full0 + 8 * it, kcol, y0);
-        else tma_load_2d(dst, &map_x, full0 + 8 * it, kcol, x0);
+        else load_x(dst, full0 + 8 * it, kcol, x0);
       }
       for (uint32_t it = n_early; it < n_units; ++it) {
         const uint32_t s = it % STAGES;
         ok = mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1);
         if (!ok) break;
         int kcol, x0, y0;
-        coords(it, kcol, x0, y0);
+        if (!units.next(kcol, x0, y0)) break;
         const uint32_t dst = base + s * kStageBytes;
         mbar_expect_tx(full0 + 8 * s, kStageBytes);
-        tma_load_2d(dst, &map_x, full0 + 8 * s, kcol, x0);
+        load_x(dst, full0 + 8 * s, kcol, x0);
         tma_load_2d(dst + kBytesX, &map_y, full0 + 8 * s, kcol, y0);
       }
       if (!ok) { flags[0] = 1; if (p.error_flag) *p.error_flag = 1; }
@@ -312,21 +342,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       long long tile_, sk_first_;
       int kb0, cnt;
       for (; ok && segs.next(tile_, kb0, cnt, sk_first_); ++seg) {
-        const uint32_t b = seg & 1;
-        ok = mbar_wait(tempty0 + 8 * b, ((seg >> 1) & 1) ^ 1);     // the epilogue has drained this accumulator
+        const uint32_t b = seg % kBufs;
+        ok = mbar_wait(tempty0 + 8 * b, ((seg / kBufs) & 1) ^ 1);  // the epilogue has drained this accumulator
         if (!ok) break;
         tcgen05_fence_after();
-        const uint32_t acc = tmem_base + b * kAccCols;
+        const uint32_t acc = tmem_base + (MS == 1 ? b * kAccCols : 0u);
         for (int i = 0; i < cnt; ++i, ++it) {
           const uint32_t s = it % STAGES;
           ok = mbar_wait(full0 + 8 * s, (it / STAGES) & 1);
           if (!ok) break;
           tcgen05_fence_after();
           const uint32_t a = base + s * kStageBytes;
-          const uint64_t da = smem_desc(a), db = smem_desc(a + kBytesX);
+          const uint64_t db = smem_desc(a + kBytesX);
 #pragma unroll
-          for (int k = 0; k < kBlockK / 16; ++k)
-            mma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          for (int ms = 0; ms < MS; ++ms) {
+            const uint64_t da = smem_desc(a + ms * kBytesX1);
+#pragma unroll
+            for (int k = 0; k < kBlockK / 16; ++k)
+              mma_bf16(acc + ms * kAccCols, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          }
           tcgen05_commit(empty0 + 8 * s);       // the buffer is free once these MMAs have read it
         }
         tcgen05_commit(tfull0 + 8 * b);         // arrives when every MMA issued so far is complete
@@ -337,10 +371,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       }
     }
   } else {
-    // ---------------------------------------------------------------- epilogue (warps 2..5)
+    // ---------------------------------------------------------------- epilogue (warps 2..5, and 6..9 for the second row block)
     pdl_wait();                               // outputs, shares and tickets belong to earlier kernels until now
     const int quad = warp & 3;                // tensor-memory lanes 32*quad .. 32*quad+31
-    const int row = quad * 32 + lane;         // row of the tile this thread owns
+    const int ms = (warp - 2) >> 2;           // row block of the tile
+    const int row = quad * 32 + lane;         // row of that block this thread owns
     constexpr int CH = BN < 32 ? BN : 32;     // columns per tensor-memory read
     uint32_t seg = 0;
     bool failed = false;
@@ -348,14 +383,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     long long tile, tile_first;
     int kb0, cnt;
     for (; !failed && segs.next(tile, kb0, cnt, tile_first); ++seg) {
-      const int x0 = (int)(tile % p.tiles_x) * kTileX, y0 = (int)(tile / p.tiles_x) * BN;
+      const int x0 = (int)(tile % p.tiles_x) * (MS * kTileX) + ms * kTileX, y0 = (int)(tile / p.tiles_x) * BN;
       const int xr = x0 + row;
-      const uint32_t b = seg & 1;
-      if (!mbar_wait(tfull0 + 8 * b, (seg >> 1) & 1)) { flags[0] = 1; if (p.error_flag) *p.error_flag = 1; }
+      const uint32_t b = seg % kBufs;
+      if (!mbar_wait(tfull0 + 8 * b, (seg / kBufs) & 1)) { flags[0] = 1; if (p.error_flag) *p.error_flag = 1; }
       tcgen05_fence_after();
       failed = flags[0] != 0;
       if (failed) break;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + b * kAccCols;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (MS == 1 ? b : (uint32_t)ms) * kAccCols;
       const bool whole = cnt == p.k_blocks;
       bool last = whole;
       int c_first = 0, c_last = 0;
@@ -373,7 +408,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       }
       if (!whole) {
         // 1. park this CTA's share of the tile: [col][row], a warp writes 128 contiguous bytes
-        float* mine = p.partial + (size_t)sch.slot(blockIdx.x, tile_first) * kTileFloats;
+        float* mine = p.partial + ((size_t)sch.slot(blockIdx.x, tile_first) * MS + ms) * kTileFloats;
         for (int c0 = 0; c0 < BN; c0 += CH) {
           float v[32];
           if (CH == 32) tmem_load_32(taddr + c0, v); else tmem_load_16(taddr + c0, v);
@@ -385,16 +420,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         c_first = sch.cta_of(tile_first);
         c_last = sch.cta_of(tile_first + p.k_blocks - 1);
         __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
         if (threadIdx.x == 64) {
           const int t = atomicAdd(p.tickets + tile, 1);
           const int n = c_last - c_first + 1;
           flags[1] = (t == n - 1) ? 1 : 0;
           if (t == n - 1) p.tickets[tile] = 0;               // ready for the next launch
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
         last = flags[1] != 0;
-        asm volatile("bar.sync 1, 128;" ::: "memory");        // flags[1] is reused by the next segment
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");        // flags[1] is reused by the next segment
         if (last) __threadfence();
       }
       if (last) {
@@ -413,7 +448,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
               for (int j = 0; j < kBatch; ++j) {
                 const bool on = cc + j <= c_last;
-                const float* src = p.partial + (size_t)sch.slot(on ? cc + j : cc, tile_first) * kTileFloats + row;
+                const float* src = p.partial + ((size_t)sch.slot(on ? cc + j : cc, tile_first) * MS + ms) * kTileFloats + row;
 #pragma unroll
                 for (int c = 0; c < CH; ++c) a[j][c] = on ? __ldcg(src + (size_t)(c0 + c) * kTileX) : 0.f;
               }
@@ -446,7 +481,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                   const int m = y0 + c0 + c;
                   if (m < p.M) {
                     const float g = v[c], u = xch[c * 64 + row];
-                    const float r = g / (1.0f + __expf(-g)) * u;
+                    const float r = silu_mul(g, u);
                     const size_t o = (size_t)m * p.ldo + i;
                     if (p.out_f32) ((float*)p.out)[o] = r; else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(r);
                   }
@@ -464,7 +499,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 const int i0 = (y0 + cb) / 2 + (c0 - cb);
                 float r[32];
 #pragma unroll
-                for (int c = 0; c < CH; ++c) r[c] = g[c] / (1.0f + __expf(-g[c])) * u[c];
+                for (int c = 0; c < CH; ++c) r[c] = silu_mul(g[c], u[c]);
                 if (xr < p.M) {
                   const size_t o = (size_t)xr * p.ldo + i0;
                   const bool full = i0 + CH <= half_n && (p.ldo % 8 == 0) && ((uintptr_t)p.out % 16 == 0) && !p.out_f32;
@@ -635,7 +670,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           const int c = cb + j * cstep, m = y0 + c;
           if (c < BN && m < p.M && n < n_end) {
             const float g = acc[j];
-            const float v = sw ? g / (1.0f + __expf(-g)) * up[j] : g + bv + old[j];
+            const float v = sw ? silu_mul(g, up[j]) : g + bv + old[j];
             const size_t o = (size_t)m * p.ldo + n;
             if (p.out_f32) ((float*)p.out)[o] = v; else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
           }
@@ -717,21 +752,21 @@ int sm_count() {
   return n;
 }
 
-template <int BN, int STAGES, bool SWAP>
+template <int BN, int STAGES, bool SWAP, int MS = 1>
 constexpr size_t smem_bytes() {
-  return (size_t)STAGES * (kTileX * kBlockK * 2 + BN * kBlockK * 2) + 1024 + (2 * STAGES + 6) * 8 + (SWAP ? 32 * 64 * 4 : 0);
+  return (size_t)STAGES * (MS * kTileX * kBlockK * 2 + BN * kBlockK * 2) + 1024 + (2 * STAGES + 6) * 8 + (SWAP ? 32 * 64 * 4 : 0);
 }
 
-template <int BN, int STAGES, bool SWAP>
+template <int BN, int STAGES, bool SWAP, int MS = 1>
 int configure() {
-  constexpr size_t smem = smem_bytes<BN, STAGES, SWAP>();
+  constexpr size_t smem = smem_bytes<BN, STAGES, SWAP, MS>();
   static_assert(smem <= 227 * 1024, "stage ring does not fit shared memory");
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP, MS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail("gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     // two CTAs of the small rings share an SM only with the largest shared-memory carve-out
-    cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP, MS>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
   return 0;
@@ -746,14 +781,14 @@ int active_clusters(int split) {
   if (configure<BN, STAGES, SWAP>()) return 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(split * 256);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(threads_for(1));
   cfg.dynamicSmemBytes = smem_bytes<BN, STAGES, SWAP>();
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = (unsigned)split; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr; cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<BN, STAGES, SWAP>, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<BN, STAGES, SWAP, 1>, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
   cache[split] = n > 0 ? n : -1;
   return n > 0 ? n : 0;
 }
@@ -767,19 +802,23 @@ int active_clusters_for(int bn, int split) {
   }
 }
 
-template <int BN, int STAGES, bool SWAP>
+template <int BN, int STAGES, bool SWAP, int MS = 1>
 int launch(const CUtensorMap& mx, const CUtensorMap& my, const Params& p, int grid, cudaStream_t stream) {
-  constexpr size_t smem = smem_bytes<BN, STAGES, SWAP>();
-  if (configure<BN, STAGES, SWAP>()) return -1;
-  ilb::launch_cluster(gemm_tc_kernel<BN, STAGES, SWAP>, dim3(grid), dim3(kThreads), smem, stream, p.cluster, mx, my, p);
+  constexpr size_t smem = smem_bytes<BN, STAGES, SWAP, MS>();
+  if (configure<BN, STAGES, SWAP, MS>()) return -1;
+  ilb::launch_cluster(gemm_tc_kernel<BN, STAGES, SWAP, MS>, dim3(grid), dim3(threads_for(MS)), smem, stream, p.cluster, mx, my, p);
   return check_launch("gemm_tc");
 }
 
 }  // namespace
 
 // Elements of 32-bit workspace and tickets a call may need, for the caller to allocate:
-// two [256][128] slots per CTA of the largest grid, one ticket per output tile.
-ILB_EXPORT long long ilb_gemm_tc_workspace_floats() { return 2ll * 256 * 256 * 128; }
+// two slots of a whole tile (up to 256 x 256) per CTA of the largest persistent grid (one
+// CTA per SM for those tiles), one ticket per output tile.
+ILB_EXPORT long long ilb_gemm_tc_workspace_floats() {
+  const long long ctas = sm_count() > 152 ? sm_count() : 152;
+  return 2ll * ctas * 256 * 256;
+}
 ILB_EXPORT int ilb_gemm_tc_max_tickets() { return 1 << 16; }
 
 // Clusters of `split` CTAs of the decode kernel for token tiles of `bn` that fit the device at once.
@@ -817,11 +856,25 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   p.out_f32 = out_f32;
 
   const bool swap = M <= 128;
-  int bn;
-  if (swap) bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
-  else bn = N >= 256 ? 256 : 128;
+  int bn, ms = 1;                                    // ms: 128-row blocks of X per tile
+  if (swap) {
+    bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+  } else {
+    // Many tokens: the tile shape that keeps the most SMs busy in whole rounds, larger tiles
+    // counting for more because they move fewer bytes per flop.
+    const struct { int ms, bn; double worth; } shapes[3] = {{2, 256, 1.0}, {1, 256, 0.85}, {1, 128, 0.7}};
+    double best = -1.0;
+    bn = 128;
+    for (const auto& c : shapes) {
+      if (c.bn > 128 && N < 256) continue;
+      const long long t = (long long)((M + c.ms * kTileX - 1) / (c.ms * kTileX)) * ((N + c.bn - 1) / c.bn);
+      const long long rounds = (t + sm_count() - 1) / sm_count();
+      const double score = (double)t / (double)(rounds * sm_count()) * c.worth;
+      if (score > best) { best = score; bn = c.bn; ms = c.ms; }
+    }
+  }
   const int x_rows = swap ? N : M, y_rows = swap ? M : N;
-  p.tiles_x = (x_rows + kTileX - 1) / kTileX;
+  p.tiles_x = (x_rows + ms * kTileX - 1) / (ms * kTileX);
   p.tiles_y = (y_rows + bn - 1) / bn;
   const long long tiles = (long long)p.tiles_x * p.tiles_y;
   ILB_REQUIRE(tiles <= n_tickets, "gemm_tc: %lld output tiles exceed the %d tickets", tiles, n_tickets);
@@ -838,7 +891,6 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
     // through shared memory: no workspace round trip and no tickets
     long long split = 1;
     while (split < 8 && tiles * split * 2 <= cap && split * 2 <= p.k_blocks) split *= 2;
-    // all clusters resident at once, or the stragglers cost a second round
     // All clusters resident at once, or the stragglers cost a second round.  The occupancy
     // query counts one CTA of this kernel per SM; the small rings run two per SM, and then a
     // cluster of `split` CTAs takes the SMs of a cluster of split / 2.
@@ -847,14 +899,34 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
     grid = tiles * split;
     p.cluster = (int)split;
   }
-  if (max_ctas > 0) grid = max_ctas;       // tests and tuning runs choose the grid themselves
-  if (grid > tiles * p.k_blocks) grid = tiles * p.k_blocks;
-  // Prefill shapes: whole tiles in wave order first (operands shared in L2), the last
-  // partial wave stream-K.  Decode shapes: everything stream-K (weights are read once anyway).
-  p.dp_waves = swap ? 0 : (int)(tiles / grid);
-  p.sk_tile0 = (long long)p.dp_waves * grid;
+  if (!swap && max_ctas <= 0) {
+    // Many tokens.  Tiles that share an operand block must want it at the same time, or every
+    // CTA streams its own copy from memory: whole tiles in rounds of equal size, all CTAs
+    // of a round starting at K block 0 together; when the tiles would leave most SMs idle,
+    // every tile is cut into the same number of K ranges instead.
+    const long long sms = sm_count();
+    if (tiles * 2 <= sms) {
+      long long split = sms / tiles;
+      if (split > 8) split = 8;
+      if (split > p.k_blocks) split = p.k_blocks;
+      grid = tiles * split;
+      p.dp_waves = 0;
+      p.sk_tile0 = 0;
+    } else {
+      const long long rounds = (tiles + sms - 1) / sms;
+      grid = (tiles + rounds - 1) / rounds;
+      p.dp_waves = (int)rounds;
+      p.sk_tile0 = tiles;
+    }
+  } else {
+    if (max_ctas > 0) grid = max_ctas;       // tests and tuning runs choose the grid themselves
+    if (grid > tiles * p.k_blocks) grid = tiles * p.k_blocks;
+    // whole tiles in wave order first, the last partial wave stream-K; decode shapes: everything stream-K
+    p.dp_waves = swap ? 0 : (int)(tiles / grid);
+    p.sk_tile0 = (long long)p.dp_waves * grid;
+  }
   p.units = (tiles - p.sk_tile0) * p.k_blocks;
-  ILB_REQUIRE(2 * grid * bn * kTileX <= workspace_floats, "gemm_tc: workspace too small");
+  ILB_REQUIRE(2 * grid * ms * bn * kTileX <= workspace_floats, "gemm_tc: workspace too small");
 
   CUtensorMap mx, my;
   const void* X = swap ? W : A;
@@ -871,6 +943,7 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
       default: return launch<128, 3, true>(mx, my, p, (int)grid, stream);
     }
   }
+  if (bn == 256 && ms == 2) return launch<256, 3, false, 2>(mx, my, p, (int)grid, stream);
   if (bn == 256) return launch<256, 4, false>(mx, my, p, (int)grid, stream);
   return launch<128, 6, false>(mx, my, p, (int)grid, stream);
 }
