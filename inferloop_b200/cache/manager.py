@@ -11,19 +11,24 @@ when the request ends (crates/engine/runtime/src/pipeline/lifecycle.rs:242-251) 
 group with a window, as soon as every position of a page is older than any key a future
 token can read.  A released entry of a block table becomes -1; kernels never follow it.
 
-Everything here is host bookkeeping; with `device=None` no memory is allocated, which
-is how the ledger is tested without a GPU.
+The bookkeeping (pools, block tables, lengths, slots) lives in the C++ host library
+(`host/ilb_host.cpp`, `Ledger`); this class owns the device tensors, gives requests of any
+hashable type a number, and turns the library's codes into exceptions.  With `device=None`
+no memory is allocated, which is how the ledger is tested without a GPU.
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import torch
 
+from .. import host
+
 from ..config.spec import RunEntry
 from ..parts.base import CacheNeeds, PagedKVNeed, SlotStateNeed
-from .pages import OutOfPages, PageLedgerError, PagePool
+from .pages import OutOfPages, OwnerIds, PageLedgerError, PagePool, raise_for
 from .slots import OutOfSlots, SlotPool
 
 
@@ -48,7 +53,6 @@ class PageGroup:
     pool: PagePool
     page_size: int
     storage: Optional[torch.Tensor] = None
-    tables: Dict[Hashable, List[int]] = field(default_factory=dict)
 
     def page_bytes(self, element_size: int) -> int:
         return (len(self.layers) * 2 * self.need.kv_heads * self.page_size
@@ -73,26 +77,42 @@ class CacheManager:
         self.groups: List[PageGroup] = []
         self._group_of_layer: Dict[int, int] = {}
         self._index_in_group: Dict[int, int] = {}
+        found: List[Tuple[PagedKVNeed, List[int]]] = []
         for layer in owners:
             need = self.layer_needs[layer].paged
             if need is None:
                 continue
-            for g in self.groups:
-                if g.need == need:
+            for gi, (n, layers) in enumerate(found):
+                if n == need:
                     break
             else:
-                g = PageGroup(len(self.groups), need, [], PagePool(num_pages), self.page_size)
-                self.groups.append(g)
-            self._group_of_layer[layer] = g.index
-            self._index_in_group[layer] = len(g.layers)
-            g.layers.append(layer)
+                gi = len(found)
+                found.append((need, []))
+            self._group_of_layer[layer] = gi
+            self._index_in_group[layer] = len(found[gi][1])
+            found[gi][1].append(layer)
+        if found and num_pages <= 0:
+            raise ValueError("a page pool needs at least one page")
+        if max_requests <= 0:
+            raise ValueError("a slot pool needs at least one slot")
+        self._lib = host.lib()
+        self._ids = OwnerIds()
+        windows = (ctypes.c_int * max(1, len(found)))(*[(-1 if n.window is None else int(n.window)) for n, _ in found])
+        h = ctypes.c_void_p()
+        rc = self._lib.ilb_ledger_new(len(found), windows, int(num_pages), self.page_size, int(max_requests), ctypes.byref(h))
+        if rc:
+            raise_for(rc)
+        self._h = h
+        for gi, (need, layers) in enumerate(found):
+            pool = PagePool(num_pages, _handle=self._lib.ilb_ledger_pool(self._h, gi), _ids=self._ids)
+            self.groups.append(PageGroup(gi, need, layers, pool, self.page_size))
         if device is not None:
             for g in self.groups:
                 g.storage = torch.zeros(
                     (len(g.layers), 2, num_pages, g.need.kv_heads, self.page_size, g.need.head_dim),
                     dtype=dtype, device=device)
         # fixed-size state
-        self.slots = SlotPool(max_requests)
+        self.slots = SlotPool(max_requests, _handle=self._lib.ilb_ledger_slots(self._h), _ids=self._ids)
         self._slot_state: Dict[Tuple[int, str], torch.Tensor] = {}
         self._slot_needs: Dict[int, Tuple[SlotStateNeed, ...]] = {}
         for layer in owners:
@@ -103,115 +123,103 @@ class CacheManager:
                     for need in needs:
                         self._slot_state[(layer, need.name)] = torch.zeros(
                             (max_requests,) + tuple(need.shape), dtype=need.dtype, device=device)
-        self._length: Dict[Hashable, int] = {}
-        self.stats = {"begun": 0, "released": 0, "window_pages_released": 0}
+        self._live: Dict[Hashable, int] = {}        # request -> its number in the ledger
+
+    def __del__(self) -> None:
+        h = getattr(self, "_h", None)
+        if h is not None and h.value:
+            self._lib.ilb_ledger_free(h)
+            self._h = None
+
+    @property
+    def stats(self) -> Dict[str, int]:
+        out = (ctypes.c_longlong * 4)()
+        self._lib.ilb_ledger_stats(self._h, out)
+        return {"begun": out[0], "released": out[1], "window_pages_released": out[2]}
+
+    @property
+    def handle(self) -> ctypes.c_void_p:
+        """The C++ ledger (for the step builder)."""
+        return self._h
+
+    def id_of(self, request: Hashable) -> int:
+        """The number under which the ledger knows a live request."""
+        return self._live[request]
 
     # ------------------------------------------------------------------ requests
     def has(self, request: Hashable) -> bool:
-        return request in self._length
+        return request in self._live
 
     def length(self, request: Hashable) -> int:
         """Tokens of `request` whose keys and values are in the cache."""
-        return self._length[request]
+        return self._lib.ilb_ledger_length(self._h, self._live[request])
 
     def live_requests(self) -> List[Hashable]:
-        return list(self._length)
+        return list(self._live)
 
     def begin(self, request: Hashable) -> int:
         """Register a request: takes its state slot (zeroed), no pages yet."""
-        if request in self._length:
+        if request in self._live:
             raise ValueError(f"request {request!r} is already live")
-        slot = self.slots.take(request)
+        rid = self._ids.of(request)
+        slot = self._lib.ilb_ledger_begin(self._h, rid)
+        if slot < 0:
+            self._ids.forget(request)
+            raise_for(slot, self._ids)
+        self._live[request] = rid
         for t in self._slot_state.values():
             t[slot].zero_()
-        self._length[request] = 0
-        for g in self.groups:
-            g.tables[request] = []
-        self.stats["begun"] += 1
         return slot
 
     def slot_of(self, request: Hashable) -> int:
-        return self.slots.slot_of(request)
-
-    def _first_needed_block(self, g: PageGroup, first_query_pos: int) -> int:
-        """Blocks below this index hold only keys no present or future token reads."""
-        if g.need.window is None:
-            return 0
-        oldest_key = max(0, first_query_pos - g.need.window + 1)
-        return oldest_key // self.page_size
+        return self._lib.ilb_ledger_slot_of(self._h, self._live[request])
 
     def pages_needed(self, request: Hashable, new_length: int) -> Dict[int, int]:
         """Pages each group must still take to cover tokens [0, new_length), after the
         pages a window lets go are counted as returned."""
-        cur = self._length[request]
-        out = {}
-        for g in self.groups:
-            table = g.tables[request]
-            want = -(-new_length // self.page_size)
-            first = self._first_needed_block(g, cur)
-            releasable = sum(1 for b in range(min(first, len(table))) if table[b] >= 0)
-            out[g.index] = max(0, want - len(table)) - releasable
-        return out
+        out = (ctypes.c_int * max(1, len(self.groups)))()
+        rc = self._lib.ilb_ledger_pages_needed(self._h, self._live[request], int(new_length), out)
+        if rc < 0:
+            raise_for(rc, self._ids)
+        return {g.index: out[g.index] for g in self.groups}
 
     def ensure(self, request: Hashable, new_length: int) -> None:
         """Make room for tokens [length, new_length) in every group, or raise OutOfPages
         and change nothing but pages a window had already let go."""
-        cur = self._length[request]
-        if new_length < cur:
-            raise ValueError(f"request {request!r} cannot shrink from {cur} to {new_length}")
-        for g in self.groups:   # first give back what a window has passed
-            table = g.tables[request]
-            first = self._first_needed_block(g, cur)
-            gone = [table[b] for b in range(min(first, len(table))) if table[b] >= 0]
-            if gone:
-                g.pool.give_back(request, gone)
-                for b in range(min(first, len(table))):
-                    table[b] = -1
-                self.stats["window_pages_released"] += len(gone)
-        want = -(-new_length // self.page_size)
-        for g in self.groups:
-            extra = want - len(g.tables[request])
-            if extra > g.pool.num_free:
-                raise OutOfPages(
-                    f"request {request!r} needs {extra} more pages in group {g.index}, "
-                    f"{g.pool.num_free} free of {g.pool.num_pages}")
-        for g in self.groups:
-            extra = want - len(g.tables[request])
-            if extra > 0:
-                g.tables[request].extend(g.pool.take(request, extra))
+        rc = self._lib.ilb_ledger_ensure(self._h, self._live[request], int(new_length))
+        if rc < 0:
+            raise_for(rc, self._ids)
 
     def commit(self, request: Hashable, new_length: int) -> None:
         """Record that tokens up to `new_length` are now in the cache."""
-        want = -(-new_length // self.page_size)
-        for g in self.groups:
-            if len(g.tables[request]) < want:
-                raise PageLedgerError(
-                    f"request {request!r} commits {new_length} tokens but holds "
-                    f"{len(g.tables[request])} blocks in group {g.index}")
-        if new_length < self._length[request]:
-            raise ValueError("commit cannot shrink a request")
-        self._length[request] = new_length
+        rc = self._lib.ilb_ledger_commit(self._h, self._live[request], int(new_length))
+        if rc < 0:
+            raise_for(rc, self._ids)
 
     def release(self, request: Hashable) -> None:
         """The request ends (or is preempted): all its pages and its slot come back."""
-        if request not in self._length:
+        if request not in self._live:
             raise ValueError(f"request {request!r} is not live")
-        for g in self.groups:
-            table = g.tables.pop(request)
-            g.pool.give_back(request, [p for p in table if p >= 0])
-        self.slots.give_back(request)
-        del self._length[request]
-        self.stats["released"] += 1
+        rc = self._lib.ilb_ledger_release(self._h, self._live[request])
+        if rc < 0:
+            raise_for(rc, self._ids)
+        del self._live[request]
+        self._ids.forget(request)
 
     # ------------------------------------------------------------------ views
     def block_table(self, group: int, request: Hashable) -> List[int]:
-        return self.groups[group].tables[request]
+        n = self._lib.ilb_ledger_table_len(self._h, int(group), self._live[request])
+        if n < 0:
+            raise_for(n, self._ids)
+        out = (ctypes.c_int * max(1, n))()
+        self._lib.ilb_ledger_table(self._h, int(group), self._live[request], out, n)
+        return list(out[:n])
 
     def max_blocks(self, requests: Sequence[Hashable]) -> int:
         m = 1
         for g in self.groups:
             for r in requests:
-                m = max(m, len(g.tables[r]))
+                m = max(m, self._lib.ilb_ledger_table_len(self._h, g.index, self._live[r]))
         return m
 
     def layer_cache(self, entry: RunEntry) -> LayerCache:
@@ -231,29 +239,16 @@ class CacheManager:
 
     def check(self) -> None:
         """Ledger invariants: every page free or held once; tables and pools agree."""
-        for g in self.groups:
-            g.pool.check()
-            seen: Dict[int, Hashable] = {}
-            for r, table in g.tables.items():
-                for p in table:
-                    if p < 0:
-                        continue
-                    if p in seen:
-                        raise PageLedgerError(f"page {p} of group {g.index} is in the tables of {seen[p]!r} and {r!r}")
-                    seen[p] = r
-                    if g.pool.owner_of(p) != r:
-                        raise PageLedgerError(f"page {p} is in {r!r}'s table but owned by {g.pool.owner_of(p)!r}")
-            held = g.pool.num_pages - g.pool.num_free
-            if held != len(seen):
-                raise PageLedgerError(f"group {g.index}: {held} pages held, {len(seen)} in tables (a page is lost)")
-        self.slots.check()
+        rc = self._lib.ilb_ledger_check(self._h)
+        if rc < 0:
+            raise_for(rc, self._ids)
 
     def inspect(self) -> dict:
         """Counterpart of the reference's KvCacheInspection
         (crates/foundation/ir/src/diagnostics.rs:80-98)."""
         return {
             "block_size": self.page_size,
-            "live_requests": len(self._length),
+            "live_requests": len(self._live),
             "groups": [{
                 "index": g.index, "layers": list(g.layers), "kv_heads": g.need.kv_heads,
                 "head_dim": g.need.head_dim, "window": g.need.window,

@@ -6,10 +6,16 @@ that is free, or that another owner holds, is an error rather than a silent repa
 The reference keeps the same facts per page as `{generation, references}` with leases
 that are checked on return (crates/engine/state/src/blocks.rs:8-28, :70-82, :208-225);
 without prefix sharing one owner per page is enough.
+
+The ledger itself is C++ (`host/ilb_host.cpp`, `Pool`); this class gives owners of any
+hashable type a number and turns the library's codes into exceptions.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Dict, Hashable, List, Optional
+
+from .. import host
 
 
 class OutOfPages(RuntimeError):
@@ -20,25 +26,90 @@ class PageLedgerError(RuntimeError):
     """A page was freed twice, freed by a stranger, or is otherwise misaccounted."""
 
 
+class OwnerIds:
+    """Numbers for owners of any hashable type (the C++ side knows owners as integers)."""
+
+    def __init__(self) -> None:
+        self._id: Dict[Hashable, int] = {}
+        self._name: Dict[int, Hashable] = {}
+        self._next = 0
+
+    def of(self, owner: Hashable) -> int:
+        i = self._id.get(owner)
+        if i is None:
+            i = self._id[owner] = self._next
+            self._name[i] = owner
+            self._next += 1
+        return i
+
+    def name(self, i: int) -> Optional[Hashable]:
+        return self._name.get(i)
+
+    def forget(self, owner: Hashable) -> None:
+        i = self._id.pop(owner, None)
+        if i is not None:
+            self._name.pop(i, None)
+
+    def legend(self) -> str:
+        if not self._id or len(self._id) > 8:
+            return ""
+        return " (owners: " + ", ".join(f"{i}={o!r}" for o, i in self._id.items()) + ")"
+
+
+def raise_for(code: int, ids: Optional[OwnerIds] = None) -> None:
+    """Turn a negative return code of the host library into the matching exception."""
+    msg = host.last_error() + (ids.legend() if ids is not None else "")
+    if code == host.OUT_OF_PAGES:
+        raise OutOfPages(msg)
+    if code == host.LEDGER:
+        raise PageLedgerError(msg)
+    if code == host.OUT_OF_SLOTS:
+        from .slots import OutOfSlots
+        raise OutOfSlots(msg)
+    raise ValueError(msg)
+
+
 class PagePool:
-    def __init__(self, num_pages: int) -> None:
-        if num_pages <= 0:
-            raise ValueError("a page pool needs at least one page")
+    def __init__(self, num_pages: int, _handle: Optional[int] = None, _ids: Optional[OwnerIds] = None) -> None:
+        self._lib = host.lib()
+        self._owned = _handle is None
+        if _handle is None:
+            if num_pages <= 0:
+                raise ValueError("a page pool needs at least one page")
+            h = ctypes.c_void_p()
+            rc = self._lib.ilb_pool_new(int(num_pages), ctypes.byref(h))
+            if rc:
+                raise_for(rc)
+            _handle = h.value
+        self._h = ctypes.c_void_p(_handle)
         self.num_pages = int(num_pages)
-        # Last freed, first reused: a page that comes back is handed out again at once,
-        # which keeps the working set small and makes stale contents show up early.
-        self._free: List[int] = list(range(self.num_pages - 1, -1, -1))
-        self._owner: List[Optional[Hashable]] = [None] * self.num_pages
-        self.allocations = 0
-        self.reuses = 0
-        self._ever_used = [False] * self.num_pages
+        self._ids = _ids if _ids is not None else OwnerIds()
+
+    def __del__(self) -> None:
+        if getattr(self, "_owned", False) and getattr(self, "_h", None) is not None:
+            self._lib.ilb_pool_free(self._h)
+            self._h = None
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return self._lib.ilb_pool_num_free(self._h)
+
+    def _counters(self):
+        out = (ctypes.c_longlong * 2)()
+        self._lib.ilb_pool_counters(self._h, out)
+        return out[0], out[1]
+
+    @property
+    def allocations(self) -> int:
+        return self._counters()[0]
+
+    @property
+    def reuses(self) -> int:
+        return self._counters()[1]
 
     def owner_of(self, page: int) -> Optional[Hashable]:
-        return self._owner[page]
+        i = self._lib.ilb_pool_owner_of(self._h, int(page))
+        return None if i < 0 else self._ids.name(i)
 
     def take(self, owner: Hashable, count: int) -> List[int]:
         """`count` pages for `owner`, or OutOfPages with nothing taken."""
@@ -46,45 +117,24 @@ class PagePool:
             raise ValueError("owner must not be None")
         if count < 0:
             raise ValueError("negative page count")
-        if count > len(self._free):
-            raise OutOfPages(f"need {count} pages, {len(self._free)} free of {self.num_pages}")
-        out = []
-        for _ in range(count):
-            p = self._free.pop()
-            if self._owner[p] is not None:
-                raise PageLedgerError(f"free list held page {p}, which {self._owner[p]!r} owns")
-            self._owner[p] = owner
-            self.allocations += 1
-            if self._ever_used[p]:
-                self.reuses += 1
-            self._ever_used[p] = True
-            out.append(p)
-        return out
+        out = (ctypes.c_int * max(1, count))()
+        rc = self._lib.ilb_pool_take(self._h, self._ids.of(owner), int(count), out)
+        if rc < 0:
+            raise_for(rc, self._ids)
+        return list(out[:count])
 
     def give_back(self, owner: Hashable, pages: List[int]) -> None:
-        for p in pages:
-            if not (0 <= p < self.num_pages):
-                raise PageLedgerError(f"page {p} is outside the pool of {self.num_pages}")
-            if self._owner[p] is None:
-                raise PageLedgerError(f"page {p} freed twice (by {owner!r})")
-            if self._owner[p] != owner:
-                raise PageLedgerError(f"page {p} belongs to {self._owner[p]!r}, not {owner!r}")
-        if len(set(pages)) != len(pages):
-            raise PageLedgerError(f"{owner!r} returns a page twice in one call: {pages}")
-        for p in pages:
-            self._owner[p] = None
-            self._free.append(p)
+        arr = (ctypes.c_int * max(1, len(pages)))(*[int(p) for p in pages])
+        rc = self._lib.ilb_pool_give_back(self._h, self._ids.of(owner), arr, len(pages))
+        if rc < 0:
+            raise_for(rc, self._ids)
 
     def check(self) -> None:
         """Every page is free or owned, never both, never neither, none listed twice."""
-        free = set(self._free)
-        if len(free) != len(self._free):
-            raise PageLedgerError("a page is on the free list twice")
-        for p in range(self.num_pages):
-            owned = self._owner[p] is not None
-            if owned == (p in free):
-                raise PageLedgerError(
-                    f"page {p} is {'both owned and free' if owned else 'neither owned nor free'}")
+        rc = self._lib.ilb_pool_check(self._h)
+        if rc < 0:
+            raise_for(rc, self._ids)
 
     def held_by(self, owner: Hashable) -> List[int]:
-        return [p for p, o in enumerate(self._owner) if o == owner]
+        i = self._ids.of(owner)
+        return [p for p in range(self.num_pages) if self._lib.ilb_pool_owner_of(self._h, p) == i]

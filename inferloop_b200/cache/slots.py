@@ -6,10 +6,16 @@ carries state of its own (a recurrent matrix, a convolution history) finds it at
 (crates/backend/cuda/src/resident/slot_batch.rs:364-403).  The attention-only
 architecture built here declares no such state, but the slot is allocated all the same
 so that a layer that needs it has it.
+
+The pool itself is C++ (`host/ilb_host.cpp`, `Slots`).
 """
 from __future__ import annotations
 
-from typing import Dict, Hashable, List, Optional
+import ctypes
+from typing import Hashable, Optional
+
+from .. import host
+from .pages import OwnerIds, raise_for
 
 
 class OutOfSlots(RuntimeError):
@@ -17,46 +23,49 @@ class OutOfSlots(RuntimeError):
 
 
 class SlotPool:
-    def __init__(self, num_slots: int) -> None:
-        if num_slots <= 0:
-            raise ValueError("a slot pool needs at least one slot")
+    def __init__(self, num_slots: int, _handle: Optional[int] = None, _ids: Optional[OwnerIds] = None) -> None:
+        self._lib = host.lib()
+        self._owned = _handle is None
+        if _handle is None:
+            if num_slots <= 0:
+                raise ValueError("a slot pool needs at least one slot")
+            h = ctypes.c_void_p()
+            rc = self._lib.ilb_slots_new(int(num_slots), ctypes.byref(h))
+            if rc:
+                raise_for(rc)
+            _handle = h.value
+        self._h = ctypes.c_void_p(_handle)
         self.num_slots = int(num_slots)
-        self._free: List[int] = list(range(self.num_slots - 1, -1, -1))
-        self._holder: List[Optional[Hashable]] = [None] * self.num_slots
-        self._slot_of: Dict[Hashable, int] = {}
+        self._ids = _ids if _ids is not None else OwnerIds()
+
+    def __del__(self) -> None:
+        if getattr(self, "_owned", False) and getattr(self, "_h", None) is not None:
+            self._lib.ilb_slots_free(self._h)
+            self._h = None
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return self._lib.ilb_slots_num_free(self._h)
 
     def slot_of(self, owner: Hashable) -> int:
-        return self._slot_of[owner]
+        s = self._lib.ilb_slots_slot_of(self._h, self._ids.of(owner))
+        if s < 0:
+            raise KeyError(owner)
+        return s
 
     def take(self, owner: Hashable) -> int:
-        if owner in self._slot_of:
-            raise ValueError(f"{owner!r} already holds slot {self._slot_of[owner]}")
-        if not self._free:
-            raise OutOfSlots(f"all {self.num_slots} state slots are in use")
-        s = self._free.pop()
-        self._holder[s] = owner
-        self._slot_of[owner] = s
+        s = self._lib.ilb_slots_take(self._h, self._ids.of(owner))
+        if s < 0:
+            raise_for(s, self._ids)
         return s
 
     def give_back(self, owner: Hashable) -> int:
-        if owner not in self._slot_of:
-            raise ValueError(f"{owner!r} holds no slot")
-        s = self._slot_of.pop(owner)
-        self._holder[s] = None
-        self._free.append(s)
+        s = self._lib.ilb_slots_give_back(self._h, self._ids.of(owner))
+        if s < 0:
+            raise_for(s, self._ids)
         return s
 
     def check(self) -> None:
-        free = set(self._free)
-        if len(free) != len(self._free):
-            raise RuntimeError("a slot is on the free list twice")
-        for s in range(self.num_slots):
-            if (self._holder[s] is not None) == (s in free):
-                raise RuntimeError(f"slot {s} is misaccounted")
-        for owner, s in self._slot_of.items():
-            if self._holder[s] != owner:
-                raise RuntimeError(f"slot {s} of {owner!r} is recorded for {self._holder[s]!r}")
+        rc = self._lib.ilb_slots_check(self._h)
+        if rc < 0:
+            raise RuntimeError(host.last_error())

@@ -82,6 +82,31 @@ class StepStager:
             total += (n + 3) // 4 * 4
         return total
 
+    def claim(self, elements: int) -> Tuple[int, torch.Tensor]:
+        """A pinned host buffer of at least `elements` int32 that no copy in flight still
+        reads: (its turn, the buffer).  Fill it, then `send` it."""
+        if elements > self._cap:
+            torch.cuda.current_stream(self.device).synchronize()
+            self._grow(max(int(elements), 2 * self._cap))
+        i = self._turn
+        self._turn ^= 1
+        if self._events[i] is not None:
+            self._events[i].synchronize()
+        return i, self._host[i]
+
+    def send(self, turn: int, total: int, dest: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Copy the first `total` elements of the claimed buffer to the device (to `dest`
+        if given, else to the stager's own buffer); returns the device buffer."""
+        dev = self._dev if dest is None else dest
+        if dev.numel() < total:
+            raise ValueError(f"staging destination holds {dev.numel()} elements, {total} are needed")
+        dev[:total].copy_(self._host[turn][:total], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        self._events[turn] = ev
+        self.last_elements = total
+        return dev
+
     def stage(self, arrays: Sequence[np.ndarray], dest: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
         """Copy the int32 arrays to the device; returns one device view per array.
         Each array starts on a 16-byte boundary.  `dest`, if given, is the device buffer

@@ -10,13 +10,16 @@ cursor is the cache manager's committed length of the request.
 """
 from __future__ import annotations
 
+import ctypes
 import json
 import os
+import re
 from typing import Callable, Dict, Hashable, List, Mapping, Optional, Sequence
 
 import numpy as np
 import torch
 
+from .. import host
 from ..cache.manager import CacheManager
 from ..cache.pages import OutOfPages
 from ..config.registry import read_model_config
@@ -52,20 +55,53 @@ def require_cuda(device) -> torch.device:
     return dev
 
 
+class _Packed:
+    """A step's entries as the flat arrays the host library reads."""
+
+    def __init__(self, cache: CacheManager, entries: Sequence[StepEntry]) -> None:
+        n = len(entries)
+        self.n = n
+        self.req = (ctypes.c_longlong * max(1, n))(*[(cache.id_of(e.request) if cache.has(e.request) else -1)
+                                                     for e in entries])
+        self.n_tok = (ctypes.c_int * max(1, n))(*[len(e.tokens) for e in entries])
+        self.n_want = (ctypes.c_int * max(1, n))(*[len(e.want) for e in entries])
+        total = sum(self.n_tok[:n])
+        try:
+            tok = np.fromiter((int(t) for e in entries for t in e.tokens), dtype=np.int64, count=total)
+        except (TypeError, ValueError):
+            raise ValueError("token ids must be integers") from None
+        # an id that does not fit 32 bits becomes -1, which the check reports as outside the vocabulary
+        self.tok = np.where((tok < 0) | (tok > 0x7FFFFFFF), -1, tok).astype(np.int32)
+        self.want = np.fromiter((int(w) for e in entries for w in e.want), dtype=np.int32, count=sum(self.n_want[:n]))
+
+    @staticmethod
+    def ptr(a: np.ndarray):
+        return a.ctypes.data_as(ctypes.POINTER(ctypes.c_int))
+
+    def refresh(self, cache: CacheManager, entries: Sequence[StepEntry]) -> None:
+        for i, e in enumerate(entries):
+            self.req[i] = cache.id_of(e.request)
+
+
+def _raise_step_error(code: int, entries: Sequence[StepEntry]) -> None:
+    """The library names entries by index; the exception names the request."""
+    msg = re.sub(r"request #(\d+)", lambda m: f"request {entries[int(m.group(1))].request!r}", host.last_error())
+    if code == host.OUT_OF_PAGES:
+        raise OutOfPages(msg)
+    raise ValueError(msg)
+
+
 def step_fits(cache: CacheManager, entries: Sequence[StepEntry]) -> bool:
     """Whether every group has the pages this step would take."""
-    need: Dict[int, int] = {}
-    for e in entries:
-        cur = cache.length(e.request) if cache.has(e.request) else 0
-        if cache.has(e.request):
-            per = cache.pages_needed(e.request, cur + len(e.tokens))
-        else:
-            per = {g.index: -(-len(e.tokens) // cache.page_size) for g in cache.groups}
-        for g, n in per.items():
-            need[g] = need.get(g, 0) + n
-    free = cache.free_pages()
-    return all(need.get(g, 0) <= free[g] for g in free)
-
+    if not entries:
+        return True
+    n = len(entries)
+    req = (ctypes.c_longlong * n)(*[(cache.id_of(e.request) if cache.has(e.request) else -1) for e in entries])
+    n_tok = (ctypes.c_int * n)(*[len(e.tokens) for e in entries])
+    rc = host.lib().ilb_step_fits(cache.handle, n, req, n_tok)
+    if rc < 0:
+        _raise_step_error(rc, entries)
+    return rc == 1
 
 
 def prepare_step(cache: CacheManager, stager: StepStager, entries: Sequence[StepEntry],
@@ -76,22 +112,21 @@ def prepare_step(cache: CacheManager, stager: StepStager, entries: Sequence[Step
     `pad_seqs` appends that many one-token dummy sequences (token 0, position 0, no pages,
     slot -1): their cache writes are dropped and their rows are never read, which lets a
     step of any size run in a launch shape made for a larger one.  `max_blocks` fixes the
-    width of the block tables; `dest` receives the arrays instead of the stager's buffer."""
+    width of the block tables; `dest` receives the arrays instead of the stager's buffer.
+    Checking, page accounting and packing are the C++ host library's."""
     if not entries:
         raise ValueError("a step needs at least one entry")
+    lib = host.lib()
     seen = set()
     for e in entries:
         if e.request in seen:
             raise ValueError(f"request {e.request!r} appears twice in one step")
         seen.add(e.request)
-        if len(e.tokens) == 0:
-            raise ValueError(f"request {e.request!r} brings no tokens")
-        for w in e.want:
-            if not (0 <= w < len(e.tokens)):
-                raise ValueError(f"request {e.request!r}: wanted place {w} is outside its {len(e.tokens)} tokens")
-        for t in e.tokens:
-            if not (0 <= int(t) < vocab_size):
-                raise ValueError(f"request {e.request!r}: token {t} is outside the vocabulary of {vocab_size}")
+    pk = _Packed(cache, entries)
+    rc = lib.ilb_step_check(cache.handle, pk.n, pk.req, pk.n_tok, pk.ptr(pk.tok), pk.n_want, pk.ptr(pk.want),
+                            int(vocab_size), int(max_positions))
+    if rc < 0:
+        _raise_step_error(rc, entries)
     fresh = [e.request for e in entries if not cache.has(e.request)]
     for r in fresh:
         cache.begin(r)
@@ -100,68 +135,47 @@ def prepare_step(cache: CacheManager, stager: StepStager, entries: Sequence[Step
             raise OutOfPages(f"step of {sum(len(e.tokens) for e in entries)} tokens does not fit: "
                              f"free pages {cache.free_pages()}")
         for e in entries:
-            new_len = cache.length(e.request) + len(e.tokens)
-            if new_len > max_positions:
-                raise ValueError(f"request {e.request!r} would reach {new_len} tokens; the model's "
-                                 f"limit is {max_positions}")
-        for e in entries:
             cache.ensure(e.request, cache.length(e.request) + len(e.tokens))
     except Exception:
         for r in fresh:
             cache.release(r)
         raise
+    pk.refresh(cache, entries)
 
-    S = len(entries) + pad_seqs
-    T = sum(len(e.tokens) for e in entries) + pad_seqs
-    tokens = np.zeros(T, np.int32)
-    positions = np.zeros(T, np.int32)
-    seq_of = np.zeros(T, np.int32)
-    cu_q = np.zeros(S + 1, np.int32)
-    kv_len = np.zeros(S, np.int32)
-    slots = np.full(S, -1, np.int32)
-    rows: List[int] = []
-    q_start, q_len = [], []
-    off = 0
-    for s, e in enumerate(entries):
-        n = len(e.tokens)
-        cur = cache.length(e.request)
-        tokens[off:off + n] = np.asarray(e.tokens, dtype=np.int64)
-        positions[off:off + n] = np.arange(cur, cur + n, dtype=np.int32)
-        seq_of[off:off + n] = s
-        cu_q[s + 1] = off + n
-        kv_len[s] = cur + n
-        slots[s] = cache.slot_of(e.request)
-        rows.extend(off + int(w) for w in e.want)
-        q_start.append(cur)
-        q_len.append(n)
-        off += n
-    for s in range(len(entries), S):          # padding
-        seq_of[off] = s
-        cu_q[s + 1] = off + 1
-        rows.append(off)
-        off += 1
     reqs = [e.request for e in entries]
+    S = len(entries) + pad_seqs
+    T = int(pk.tok.size) + pad_seqs
+    R = int(pk.want.size) + pad_seqs
     need_blocks = cache.max_blocks(reqs)
     if max_blocks is None:
         max_blocks = (need_blocks + 7) // 8 * 8
     elif need_blocks > max_blocks:
         raise ValueError(f"a request holds {need_blocks} blocks, the table is {max_blocks} wide")
-    tables = []
-    for g in cache.groups:
-        tb = np.full((S, max_blocks), -1, np.int32)
-        for s, r in enumerate(reqs):
-            row = cache.block_table(g.index, r)
-            tb[s, :len(row)] = row
-        tables.append(tb)
-    logit_rows = np.asarray(rows, dtype=np.int32)
-    staged = stager.stage([tokens, positions, seq_of, cu_q, kv_len, slots, logit_rows] + tables, dest)
+    n_groups = len(cache.groups)
+    bound = StepStager.layout([(T,), (T,), (T,), (S + 1,), (S,), (S,), (R,)] + [(S, max_blocks)] * n_groups)
+    turn, hostbuf = stager.claim(bound)
+    offsets = (ctypes.c_longlong * (7 + n_groups))()
+    total = lib.ilb_step_build(cache.handle, pk.n, pk.req, pk.n_tok, pk.ptr(pk.tok), pk.n_want, pk.ptr(pk.want),
+                               int(pad_seqs), int(max_blocks), int(vocab_size), int(max_positions),
+                               ctypes.c_void_p(hostbuf.data_ptr()), hostbuf.numel(), offsets)
+    if total < 0:
+        _raise_step_error(int(total), entries)
+    dev = stager.send(turn, int(total), dest)
+    view = lambda k, n, shape=None: (dev[offsets[k]:offsets[k] + n] if shape is None
+                                     else dev[offsets[k]:offsets[k] + n].view(*shape))
+    hv = hostbuf.numpy()
+    kv_len = hv[offsets[4]:offsets[4] + S]
+    slots = hv[offsets[5]:offsets[5] + len(entries)]
+    q_len = [len(e.tokens) for e in entries]
+    h_kv = [int(x) for x in kv_len]
+    q_start = [h_kv[i] - q_len[i] for i in range(len(entries))]
     return StepContext(
-        n_tokens=T, n_seqs=S, n_logit_rows=len(rows),
-        tokens=staged[0], positions=staged[1], seq_of_token=staged[2], cu_q=staged[3],
-        kv_len=staged[4], slots=staged[5], logit_rows=staged[6],
-        block_tables={g.index: staged[7 + i] for i, g in enumerate(cache.groups)},
-        requests=reqs, h_q_start=q_start, h_q_len=q_len, h_kv_len=[int(x) for x in kv_len],
-        h_slots=[int(x) for x in slots[:len(entries)]], max_q_len=max(q_len), max_kv_len=int(kv_len.max()),
+        n_tokens=T, n_seqs=S, n_logit_rows=R,
+        tokens=view(0, T), positions=view(1, T), seq_of_token=view(2, T), cu_q=view(3, S + 1),
+        kv_len=view(4, S), slots=view(5, S), logit_rows=view(6, R),
+        block_tables={g.index: view(7 + i, S * max_blocks, (S, max_blocks)) for i, g in enumerate(cache.groups)},
+        requests=reqs, h_q_start=q_start, h_q_len=q_len, h_kv_len=h_kv,
+        h_slots=[int(x) for x in slots], max_q_len=max(q_len), max_kv_len=max(h_kv),
         decode_only=all(n == 1 for n in q_len))
 
 

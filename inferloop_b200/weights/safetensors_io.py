@@ -10,8 +10,8 @@ trailing bytes.  The file is mapped read-only and tensors are views of the mappi
 """
 from __future__ import annotations
 
+import ctypes
 import json
-import mmap
 import os
 import struct
 from dataclasses import dataclass
@@ -54,87 +54,74 @@ def _no_duplicates(pairs):
 
 
 class SafetensorsFile:
-    """One mapped .safetensors file."""
+    """One mapped .safetensors file.  The mapping, the header's parse and every check of
+    it are the C++ host library's (`host/ilb_host.cpp`, `st_*`); tensors are views of the
+    mapped bytes."""
 
     def __init__(self, path: str) -> None:
+        from .. import host
         self.path = path
-        size = os.path.getsize(path)
-        if size < 8:
-            raise SafetensorsError(f"{path}: file is shorter than its 8-byte length field")
-        self._fh = open(path, "rb")
-        (n,) = struct.unpack("<Q", self._fh.read(8))
-        if n > MAX_HEADER_BYTES:
-            raise SafetensorsError(f"{path}: header of {n} bytes exceeds {MAX_HEADER_BYTES}")
-        if 8 + n > size:
-            raise SafetensorsError(f"{path}: header length {n} runs past the end of the file")
+        self._lib = host.lib()
+        h = ctypes.c_void_p()
+        rc = self._lib.ilb_st_open(os.fsencode(path), ctypes.byref(h))
+        if rc:
+            msg = host.last_error()
+            if rc == host.IO and not os.path.exists(path):
+                raise FileNotFoundError(msg)
+            raise SafetensorsError(msg)
+        self._h = h
+        self.data_start = self._lib.ilb_st_data_start(h)
+        self._payload = self._lib.ilb_st_payload(h) or 0
+        meta = self._lib.ilb_st_metadata(h).decode("utf-8", "replace")
         try:
-            header = json.loads(self._fh.read(n).decode("utf-8"),
-                                object_pairs_hook=_no_duplicates)
-        except (UnicodeDecodeError, json.JSONDecodeError) as e:
-            raise SafetensorsError(f"{path}: header is not valid JSON: {e}") from None
-        if not isinstance(header, dict):
-            raise SafetensorsError(f"{path}: header must be a JSON object")
-        self.metadata = header.pop("__metadata__", None) or {}
-        self.data_start = 8 + n
-        payload = size - self.data_start
+            self.metadata = (json.loads(meta) if meta else None) or {}
+        except json.JSONDecodeError:
+            self.metadata = {}
         entries: Dict[str, TensorEntry] = {}
-        for name, info in header.items():
-            try:
-                dtype = info["dtype"]
-                shape = tuple(int(s) for s in info["shape"])
-                begin, end = (int(x) for x in info["data_offsets"])
-            except (KeyError, TypeError, ValueError):
-                raise SafetensorsError(f"{path}: malformed entry for {name!r}") from None
-            if dtype not in _DTYPES:
-                raise SafetensorsError(f"{path}: {name}: unsupported dtype {dtype}")
-            if any(s < 0 for s in shape) or begin < 0 or end < begin or end > payload:
-                raise SafetensorsError(f"{path}: {name}: offsets [{begin}, {end}) outside payload")
-            count = 1
-            for s in shape:
-                count *= s
-            if count * _DTYPES[dtype][1] != end - begin:
-                raise SafetensorsError(
-                    f"{path}: {name}: shape {list(shape)} of {dtype} needs "
-                    f"{count * _DTYPES[dtype][1]} bytes, entry spans {end - begin}")
-            entries[name] = TensorEntry(name, dtype, shape, begin, end)
-        cursor = 0
-        for e in sorted(entries.values(), key=lambda e: (e.begin, e.end)):
-            if e.begin < cursor:
-                raise SafetensorsError(f"{path}: {e.name} overlaps the tensor before it")
-            if e.begin > cursor:
-                raise SafetensorsError(f"{path}: gap of {e.begin - cursor} bytes before {e.name}")
-            cursor = e.end
-        if cursor != payload:
-            raise SafetensorsError(f"{path}: {payload - cursor} trailing bytes after the last tensor")
+        name, dtype = ctypes.c_char_p(), ctypes.c_char_p()
+        ndim = ctypes.c_int()
+        shape = ctypes.POINTER(ctypes.c_longlong)()
+        begin, end = ctypes.c_longlong(), ctypes.c_longlong()
+        for i in range(self._lib.ilb_st_count(h)):
+            self._lib.ilb_st_entry(h, i, ctypes.byref(name), ctypes.byref(dtype), ctypes.byref(ndim),
+                                   ctypes.byref(shape), ctypes.byref(begin), ctypes.byref(end))
+            n = name.value.decode("utf-8")
+            d = dtype.value.decode("ascii")
+            if d not in _DTYPES:
+                self.close()
+                raise SafetensorsError(f"{path}: {n}: unsupported dtype {d}")
+            entries[n] = TensorEntry(n, d, tuple(int(shape[k]) for k in range(ndim.value)), begin.value, end.value)
         self.entries = entries
-        self._map = mmap.mmap(self._fh.fileno(), 0, access=mmap.ACCESS_READ) if size else None
 
     def names(self) -> List[str]:
         return list(self.entries)
 
     def tensor(self, name: str) -> torch.Tensor:
-        """A read-only view of the mapped bytes (do not write through it)."""
+        """A read-only view of the mapped bytes (do not write through it).  The view keeps
+        this object, and with it the mapping, alive."""
         e = self.entries[name]
         dtype, width = _DTYPES[e.dtype]
-        count = (e.end - e.begin) // width
-        if count == 0:
+        nbytes = e.end - e.begin
+        if nbytes == 0:
             return torch.empty(e.shape, dtype=dtype)
+        buf = (ctypes.c_ubyte * nbytes).from_address(self._payload + e.begin)
+        buf._keep = self                      # the mapping must outlive the view
         import warnings
         with warnings.catch_warnings():
             warnings.simplefilter("ignore")  # the mapping is read-only by design
-            flat = torch.frombuffer(self._map, dtype=dtype, count=count,
-                                    offset=self.data_start + e.begin)
+            flat = torch.frombuffer(buf, dtype=dtype, count=nbytes // width)
         return flat.view(e.shape)
 
     def close(self) -> None:
-        # Views handed out keep the mapping alive through the buffer protocol; closing
-        # with live views raises BufferError, which is left to the garbage collector.
-        try:
-            if self._map is not None:
-                self._map.close()
-        except BufferError:
-            pass
-        self._fh.close()
+        """Drops this object's own hold on the mapping; it is unmapped when the last tensor
+        view is gone too."""
+        self.entries = dict(getattr(self, "entries", {}))
+
+    def __del__(self) -> None:
+        h = getattr(self, "_h", None)
+        if h is not None and h.value:
+            self._lib.ilb_st_close(h)
+            self._h = None
 
 
 def write_safetensors(path: str, tensors: Mapping[str, torch.Tensor] | Iterable[Tuple[str, torch.Tensor]],
