@@ -223,7 +223,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   constexpr uint32_t kBytesY = BN * kBlockK * 2;
   constexpr uint32_t kStageBytes = kBytesX + kBytesY;          // multiples of 1024
   constexpr uint32_t kAccCols = BN < 32 ? 32 : BN;             // columns of one accumulator
-  constexpr uint32_t kTmemCols = 2 * kAccCols;                 // two accumulators; a power of two >= 64
+  constexpr uint32_t kTmemCols = 2 * kAccCols <= 64 ? 64 : 2 * kAccCols <= 128 ? 128 : 2 * kAccCols <= 256 ? 256 : 512;   // two accumulators; a power of two
   constexpr int kTileFloats = BN * kTileX;                     // one 128-row block of a tile
   constexpr int kBufs = MS == 1 ? 2 : 1;                       // tiles that tensor memory holds
   constexpr int kEpiThreads = 128 * MS;
@@ -862,11 +862,12 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   } else {
     // Many tokens: the tile shape that keeps the most SMs busy in whole rounds, larger tiles
     // counting for more because they move fewer bytes per flop.
-    const struct { int ms, bn; double worth; } shapes[3] = {{2, 256, 1.0}, {1, 256, 0.85}, {1, 128, 0.7}};
+    const struct { int ms, bn; double worth; } shapes[4] = {{2, 256, 1.0}, {2, 192, 0.93}, {1, 256, 0.85}, {1, 128, 0.7}};
     double best = -1.0;
     bn = 128;
     for (const auto& c : shapes) {
       if (c.bn > 128 && N < 256) continue;
+      if (c.bn % 128 != 0 && accumulate == 2) continue;        // the SwiGLU epilogue pairs 64-column blocks
       const long long t = (long long)((M + c.ms * kTileX - 1) / (c.ms * kTileX)) * ((N + c.bn - 1) / c.bn);
       const long long rounds = (t + sm_count() - 1) / sm_count();
       const double score = (double)t / (double)(rounds * sm_count()) * c.worth;
@@ -944,6 +945,7 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
     }
   }
   if (bn == 256 && ms == 2) return launch<256, 3, false, 2>(mx, my, p, (int)grid, stream);
+  if (bn == 192) return launch<192, 3, false, 2>(mx, my, p, (int)grid, stream);
   if (bn == 256) return launch<256, 4, false>(mx, my, p, (int)grid, stream);
   return launch<128, 6, false>(mx, my, p, (int)grid, stream);
 }
