@@ -212,7 +212,8 @@ __device__ __forceinline__ void tile_step(RowState<D>& st, const uint32_t (&q)[D
 
 template <int D, int kStages>
 __global__ void __launch_bounds__(kThreads)
-decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const Params p) {
+decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+              const __grid_constant__ CUtensorMap map_k_run, const __grid_constant__ CUtensorMap map_v_run, const Params p) {
   constexpr int kSlices = D / 64;
   constexpr uint32_t kSlice = kKeys * 128;                 // bytes: one slice of one tensor of a tile
   constexpr uint32_t kTensor = kSlices * kSlice;           // K (or V) of a tile
@@ -293,7 +294,15 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
           }
           ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
           if (!ok) break;
-          if (has_box)
+          // The TMA unit's time per box hardly depends on its size: two 16-key pages that
+          // follow one another in the pool come as one box.
+          const int page_nb = __shfl_down_sync(0xffffffffu, pg[i], 1);
+          const bool run = has_box && parts == 2 && part == 0 && pg[i] + 1 < p.num_pages && page_nb == pg[i] + 1;
+          const bool covered = __shfl_up_sync(0xffffffffu, run ? 1 : 0, 1) != 0 && part == 1;
+          if (run)
+            tma_load_4d(base + s * kStage + which * kTensor + slice * kSlice, which == 0 ? &map_k_run : &map_v_run,
+                        full0 + 8 * s, slice * 64, 0, kvh, pg[i]);
+          else if (has_box && !covered)
             tma_load_4d(base + s * kStage + which * kTensor + slice * kSlice + part * box_keys * 128,
                         which == 0 ? &map_k : &map_v, full0 + 8 * s, slice * 64, (key_of(j) + part * box_keys) % p.page_size,
                         kvh, pg[i]);
@@ -410,24 +419,25 @@ EncodeTiledFn encode_fn() {
 }
 
 struct MapKey {
-  const void* ptr; int d, page_size, nkv, num_pages;
+  const void* ptr; int d, page_size, nkv, num_pages, run;
   bool operator==(const MapKey& o) const {
-    return ptr == o.ptr && d == o.d && page_size == o.page_size && nkv == o.nkv && num_pages == o.num_pages;
+    return ptr == o.ptr && d == o.d && page_size == o.page_size && nkv == o.nkv && num_pages == o.num_pages && run == o.run;
   }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey& k) const {
     size_t h = std::hash<const void*>()(k.ptr);
-    for (int v : {k.d, k.page_size, k.nkv, k.num_pages}) h = h * 1000003u ^ std::hash<int>()(v);
+    for (int v : {k.d, k.page_size, k.nkv, k.num_pages, k.run}) h = h * 1000003u ^ std::hash<int>()(v);
     return h;
   }
 };
 
-// The cache as (d, key in page, kv head, page); a box is up to 32 keys of one page and head, one slice of the head.
-int cache_map(CUtensorMap* out, const void* ptr, int d, int page_size, int nkv, int num_pages) {
+// The cache as (d, key in page, kv head, page); a box is up to 32 keys of one page and head,
+// one slice of the head; `run` pages of fewer keys that follow one another make one box.
+int cache_map(CUtensorMap* out, const void* ptr, int d, int page_size, int nkv, int num_pages, int run) {
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   static std::mutex mu;
-  const MapKey key{ptr, d, page_size, nkv, num_pages};
+  const MapKey key{ptr, d, page_size, nkv, num_pages, run};
   std::lock_guard<std::mutex> g(mu);
   auto it = cache.find(key);
   if (it != cache.end()) { *out = it->second; return 0; }
@@ -435,7 +445,7 @@ int cache_map(CUtensorMap* out, const void* ptr, int d, int page_size, int nkv, 
   if (!fn) return fail("attention decode: cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)page_size, (cuuint64_t)nkv, (cuuint64_t)num_pages};
   const cuuint64_t strides[3] = {(cuuint64_t)d * 2, (cuuint64_t)d * 2 * page_size, (cuuint64_t)d * 2 * page_size * nkv};
-  const cuuint32_t box[4] = {64, (cuuint32_t)(page_size < kKeys ? page_size : kKeys), 1, 1};
+  const cuuint32_t box[4] = {64, (cuuint32_t)(page_size < kKeys ? page_size : kKeys), 1, (cuuint32_t)run};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -486,24 +496,24 @@ int active_clusters(int split) {
 }
 
 template <int D, int STAGES>
-int launch(const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, cudaStream_t stream) {
+int launch(const CUtensorMap (&m)[4], const Params& p, cudaStream_t stream) {
   if (configure<D, STAGES>()) return -1;
   ilb::launch_cluster(decode_kernel<D, STAGES>, dim3(p.split, p.nkv, p.n_seqs), dim3(kThreads), smem_bytes<D, STAGES>(), stream,
-                      p.split, mk, mv, p);
+                      p.split, m[0], m[1], m[2], m[3], p);
   return check_launch("attention decode");
 }
 
 // The ways a sequence's tiles are dealt out and the depth of the tile ring: as many CTAs as
 // fit the device at once, and the shared memory that this leaves to each of them.
 template <int D>
-int launch_for(const CUtensorMap& mk, const CUtensorMap& mv, Params& p, cudaStream_t stream) {
+int launch_for(const CUtensorMap (&m)[4], Params& p, cudaStream_t stream) {
   const long long pairs = (long long)p.n_seqs * p.nkv;
   int split = kMaxSplit;
   while (split > 1 && active_clusters<D, 3>(split) < pairs) split /= 2;
   p.split = split;
-  if (active_clusters<D, 12>(split) >= pairs) return launch<D, 12>(mk, mv, p, stream);
-  if (active_clusters<D, 6>(split) >= pairs) return launch<D, 6>(mk, mv, p, stream);
-  return launch<D, 3>(mk, mv, p, stream);
+  if (active_clusters<D, 12>(split) >= pairs) return launch<D, 12>(m, p, stream);
+  if (active_clusters<D, 6>(split) >= pairs) return launch<D, 6>(m, p, stream);
+  return launch<D, 3>(m, p, stream);
 }
 
 }  // namespace
@@ -525,12 +535,15 @@ ILB_EXPORT int ilb_attention_decode_tma(const void* q, void* out, const void* k_
               "attention decode: bad sizes");
   ILB_REQUIRE(q_stride % 2 == 0 && ((uintptr_t)q % 4 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0),
               "attention decode: misaligned operands");
-  CUtensorMap mk, mv;
-  if (cache_map(&mk, k_cache, d, page_size, nkv, num_pages)) return -1;
-  if (cache_map(&mv, v_cache, d, page_size, nkv, num_pages)) return -1;
+  CUtensorMap m[4];                      // K, V, and the same with boxes of two pages
+  const int run = page_size < kKeys ? kKeys / page_size : 1;
+  if (cache_map(&m[0], k_cache, d, page_size, nkv, num_pages, 1)) return -1;
+  if (cache_map(&m[1], v_cache, d, page_size, nkv, num_pages, 1)) return -1;
+  if (cache_map(&m[2], k_cache, d, page_size, nkv, num_pages, run)) return -1;
+  if (cache_map(&m[3], v_cache, d, page_size, nkv, num_pages, run)) return -1;
   Params p{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, positions, cu_q, block_table, error_flag,
            max_blocks, n_seqs, nq, nkv, window, q_stride, out_stride, page_size, num_pages, 1, scale * kLog2e};
-  return d == 64 ? launch_for<64>(mk, mv, p, stream) : launch_for<128>(mk, mv, p, stream);
+  return d == 64 ? launch_for<64>(m, p, stream) : launch_for<128>(m, p, stream);
 }
 
 ILB_DEFINE_LAST_ERROR()

@@ -140,6 +140,13 @@ __device__ __forceinline__ void tmem_store_32(uint32_t addr, const float (&v)[32
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// 2^x by the special-function unit (2 ulp; the result is rounded to bfloat16 anyway).
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct Params {
   __nv_bfloat16* out;
   const int* positions; const int* cu_q; const int* block_table;
@@ -151,7 +158,8 @@ struct Params {
 template <int D>
 __global__ void __launch_bounds__(kThreads)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                  const __grid_constant__ CUtensorMap map_v, const Params p) {
+                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_k_run,
+                  const __grid_constant__ CUtensorMap map_v_run, const Params p) {
   constexpr int kChunks = D / 64;                       // 64-wide slices of the head
   constexpr uint32_t kSlice = kRows * 128;              // bytes of a [128][64] bf16 slice
   constexpr uint32_t kQBytes = kChunks * kSlice;
@@ -233,22 +241,37 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int box = lane & 15, box_page = box / kChunks, box_slice = box % kChunks;
     const bool has_box = box < pages_per_tile * kChunks;
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int s = j % kStages;
-      const int key0 = (first_tile + j) * kKeys;
+    auto lookup = [&](int j) {                            // page of this lane's box of tile j
       int page = p.num_pages;                             // outside the tensor: TMA fills zeros
-      if (has_box) {
+      if (has_box && j < n_tiles) {
+        const int key0 = (first_tile + j) * kKeys;
         const int blk = key0 / p.page_size + box_page;
         const int pg = blk < p.max_blocks ? __ldg(table + blk) : -1;
         if (pg >= 0 && pg < p.num_pages && key0 + box_page * p.page_size <= pos_last) page = pg;
       }
+      return page;
+    };
+    int page_next = lookup(0);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int s = j % kStages;
+      const int page = page_next;
+      page_next = lookup(j + 1);                          // in flight while this tile's boxes are issued
       if (lane == 0) {
         if (j >= kStages) ok = mbar_wait(k_empty + 8 * s, ((j / kStages) - 1) & 1);
         if (ok) mbar_expect_tx(k_full + 8 * s, kKBytes);
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
-      if (has_box && lane < 16)
+      // The TMA unit takes tens of nanoseconds per box whatever its size, and a tile is up to
+      // 32 boxes of 2 KB.  When the tile's pages follow one another in the pool (the usual
+      // case: pages are handed out in order) one box per slice spans all of them.
+      const int first_page = __shfl_sync(0xffffffffu, page, 0);
+      const bool run = __all_sync(0xffffffffu, !has_box || page == first_page + box_page) &&
+                       first_page + pages_per_tile <= p.num_pages;
+      if (run) {
+        if (lane < kChunks)
+          tma_load_4d(k_s + s * kKBytes + lane * kSlice, &map_k_run, k_full + 8 * s, lane * 64, 0, kvh, first_page);
+      } else if (has_box && lane < 16)
         tma_load_4d(k_s + s * kKBytes + box_slice * kSlice + box_page * p.page_size * 128, &map_k, k_full + 8 * s,
                     box_slice * 64, 0, kvh, page);
       if (lane == 0) {
@@ -257,7 +280,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
-      if (has_box && lane >= 16)
+      if (run) {
+        if (lane >= 16 && lane < 16 + kChunks)
+          tma_load_4d(v_s + s * kVBytes + (lane - 16) * kSlice, &map_v_run, v_full + 8 * s, (lane - 16) * 64, 0, kvh, first_page);
+      } else if (has_box && lane >= 16)
         tma_load_4d(v_s + s * kVBytes + box_slice * kSlice + box_page * p.page_size * 128, &map_v, v_full + 8 * s,
                     box_slice * 64, 0, kvh, page);
     }
@@ -336,20 +362,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
       tcgen05_fence_before();
       mbar_arrive(s_free);                             // S is in registers: the next Q K^T may overwrite it
-      // scores in log2 units; keys this row may not see become -inf
+      // raw scores stay in v (the scale is positive and folds into the exponent's multiply-add);
+      // keys this row may not see become -inf; the maximum is taken in log2 units
       const bool all_visible = key0 + 63 <= pos && key0 >= lo;
       float mx = -INFINITY;
       if (all_visible) {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) { v[c] *= p.scale_log2; mx = fmaxf(mx, v[c]); }
+        for (int c = 0; c < 64; ++c) mx = fmaxf(mx, v[c]);
       } else {
 #pragma unroll
         for (int c = 0; c < 64; ++c) {
           const int key = key0 + c;
-          v[c] = (key <= pos && key >= lo) ? v[c] * p.scale_log2 : -INFINITY;
+          v[c] = (key <= pos && key >= lo) ? v[c] : -INFINITY;
           mx = fmaxf(mx, v[c]);
         }
       }
+      mx *= p.scale_log2;
       xmax[(j & 1) * 256 + half * 128 + row] = mx;
       asm volatile("bar.sync 1, 256;" ::: "memory");
       mx = fmaxf(mx, xmax[(j & 1) * 256 + (half ^ 1) * 128 + row]);
@@ -382,10 +410,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         uint32_t packed[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float e0 = exp2f(v[piece * 8 + 2 * e] - m_used), e1 = exp2f(v[piece * 8 + 2 * e + 1] - m_used);
+          const float e0 = ex2(fmaf(v[piece * 8 + 2 * e], p.scale_log2, -m_used));
+          const float e1 = ex2(fmaf(v[piece * 8 + 2 * e + 1], p.scale_log2, -m_used));
+          sum += e0 + e1;
           __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
-          const float2 r = __bfloat1622float2(h);      // the sum runs over what the P V product will use
-          sum += r.x + r.y;
           packed[e] = *reinterpret_cast<uint32_t*>(&h);
         }
         *reinterpret_cast<uint4*>(prow + ((piece ^ (row % 8)) * 16)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -464,8 +492,8 @@ int encode(CUtensorMap* out, const void* ptr, int rank, const cuuint64_t* dims, 
 }
 
 template <int D>
-int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, int n_tiles,
-           cudaStream_t stream) {
+int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mkr,
+           const CUtensorMap& mvr, const Params& p, int n_tiles, cudaStream_t stream) {
   constexpr int kChunks = D / 64;
   constexpr size_t smem = (size_t)kChunks * kRows * 128 * (1 + 2 * kStages) + 2 * kRows * 128 + 1024 + (8 + 4 * kStages) * 8 + 768 * 4;
   static_assert(smem <= 227 * 1024, "tiles do not fit shared memory");
@@ -475,7 +503,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     if (e != cudaSuccess) return fail("attention (tensor cores): cannot reserve %zu bytes of shared memory", smem);
     configured = true;
   }
-  ilb::launch(prefill_tc_kernel<D>, dim3(n_tiles, p.nkv), dim3(kThreads), smem, stream, mq, mk, mv, p);
+  ilb::launch(prefill_tc_kernel<D>, dim3(n_tiles, p.nkv), dim3(kThreads), smem, stream, mq, mk, mv, mkr, mvr, p);
   return check_launch("attention prefill (tensor cores)");
 }
 
@@ -502,7 +530,7 @@ ILB_EXPORT int ilb_attention_prefill_tc(const void* q, void* out, const void* k_
   ILB_REQUIRE(q_stride % 8 == 0 && out_stride % 8 == 0 && ((uintptr_t)q % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
               ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0), "attention (tensor cores): misaligned operands");
   const int G = nq / nkv;
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mkr, mvr;
   {   // q as (d, heads, tokens); a box is 64 x G x 128/G = the 128 rows of a tile, one slice of the head
     const cuuint64_t dims[3] = {(cuuint64_t)d, (cuuint64_t)nq, (cuuint64_t)n_tokens};
     const cuuint64_t strides[2] = {(cuuint64_t)d * 2, (cuuint64_t)q_stride * 2};
@@ -515,10 +543,14 @@ ILB_EXPORT int ilb_attention_prefill_tc(const void* q, void* out, const void* k_
     const cuuint32_t box[4] = {64, (cuuint32_t)page_size, 1, 1};
     if (encode(&mk, k_cache, 4, dims, strides, box, "k cache")) return -1;
     if (encode(&mv, v_cache, 4, dims, strides, box, "v cache")) return -1;
+    // the same, a box spanning all pages of a 128-key tile when their numbers follow one another
+    const cuuint32_t run[4] = {64, (cuuint32_t)page_size, 1, (cuuint32_t)(kKeys / page_size)};
+    if (encode(&mkr, k_cache, 4, dims, strides, run, "k cache (page run)")) return -1;
+    if (encode(&mvr, v_cache, 4, dims, strides, run, "v cache (page run)")) return -1;
   }
   Params p{(__nv_bfloat16*)out, positions, cu_q, block_table, error_flag, max_blocks, n_seqs, nq, nkv, window,
            out_stride, page_size, num_pages, scale * kLog2e};
-  return d == 64 ? launch<64>(mq, mk, mv, p, n_tiles, stream) : launch<128>(mq, mk, mv, p, n_tiles, stream);
+  return d == 64 ? launch<64>(mq, mk, mv, mkr, mvr, p, n_tiles, stream) : launch<128>(mq, mk, mv, mkr, mvr, p, n_tiles, stream);
 }
 
 ILB_DEFINE_LAST_ERROR()

@@ -382,7 +382,10 @@ struct Pool {
     }
     std::unordered_set<int> once(pages, pages + n);
     if ((int)once.size() != n) return fail(kLedger, "%lld returns a page twice in one call", who);
-    for (int i = 0; i < n; ++i) { owner[(size_t)pages[i]] = -1; free_.push_back(pages[i]); }
+    // pushed last to first, so that whoever takes these pages next gets them in the order
+    // they are given back in: a block table that came back ascending goes out ascending, and
+    // the attention kernels fetch a run of pages that follow one another as one box
+    for (int i = n - 1; i >= 0; --i) { owner[(size_t)pages[i]] = -1; free_.push_back(pages[i]); }
     return kOk;
   }
   int check() const {

@@ -116,12 +116,20 @@ def test_gemm_simt_rows_do_not_depend_on_the_batch():
 
 
 # ------------------------------------------------------------------ attention pieces
-def build_cache(seqs_kv, nkv, d, page_size, num_pages, dtype, seed=0):
-    """Scatter each sequence's keys/values into shuffled pages; returns cache tensors and
-    the block table [S, max_blocks]."""
+def build_cache(seqs_kv, nkv, d, page_size, num_pages, dtype, seed=0, page_order="shuffled"):
+    """Scatter each sequence's keys/values into pages; returns cache tensors and the block
+    table [S, max_blocks].  `page_order`: "shuffled", "ordered" (a sequence's pages follow
+    one another in the pool, as a fresh pool hands them out) or "mixed" (ordered with every
+    fifth pair of neighbours swapped, so that runs and broken runs alternate)."""
     rng = random.Random(seed)
     pages = list(range(num_pages))
-    rng.shuffle(pages)
+    if page_order == "shuffled":
+        rng.shuffle(pages)
+    else:
+        pages.reverse()                       # pop() hands out 0, 1, 2, ...
+        if page_order == "mixed":
+            for i in range(3, num_pages - 1, 5):
+                pages[i], pages[i + 1] = pages[i + 1], pages[i]
     k_cache = torch.full((num_pages, nkv, page_size, d), 7.0)      # stale contents must not matter
     v_cache = torch.full((num_pages, nkv, page_size, d), -9.0)
     max_blocks = max(-(-k.shape[0] // page_size) for k, _ in seqs_kv)
@@ -364,14 +372,15 @@ class _Step:
         self.decode_only = all(n == 1 for n in q_lens)
 
 
-def run_flash(q, seqs, lens, q_lens, nq, nkv, d, page_size, window, chunk=256, seed=0, cluster=True):
+def run_flash(q, seqs, lens, q_lens, nq, nkv, d, page_size, window, chunk=256, seed=0, cluster=True,
+              page_order="shuffled"):
     """`cluster`: split-KV decode merges inside a thread-block cluster (the default of the
     dispatcher) or through scratch records and tickets."""
     from inferloop_b200.parts import Workspace
     o = ops()
     n_pages = sum(-(-n // page_size) for n in lens) + 3
     k_cache, v_cache, table = build_cache([(k.float(), v.float()) for k, v in seqs], nkv, d, page_size, n_pages,
-                                          torch.bfloat16, seed=seed)
+                                          torch.bfloat16, seed=seed, page_order=page_order)
     positions, seq_of, cu = [], [], [0]
     for s, (n, ql) in enumerate(zip(lens, q_lens)):
         positions += list(range(n - ql, n))
@@ -491,6 +500,22 @@ def test_tc_prefill_mixed_batch(nq, nkv, d, page_size, window):
     finally:
         o.TC_ATTENTION_ENABLED = True
     close_flash(out2, ref, max(float(v.abs().max()) for _, v in seqs), "flash prefill")
+
+
+@pytest.mark.parametrize("page_order", ["ordered", "mixed"])
+@pytest.mark.parametrize("nq,nkv,d,page_size,window", [(32, 8, 128, 16, 0), (4, 2, 64, 32, 70)])
+def test_tc_prefill_and_decode_with_pages_in_runs(nq, nkv, d, page_size, window, page_order):
+    """Pages that follow one another in the pool are fetched as one box per tile; tiles whose
+    run is broken, and the last tile of a sequence, take the box-per-page path."""
+    torch.manual_seed(nq + d + page_size)
+    for lens, q_lens in (([300, 1000, 129], [300, 260, 129]), ([513, 77, 1024, 130], [1, 1, 1, 1])):
+        seqs = [(torch.randn(n, nkv, d).to(torch.bfloat16).double(), torch.randn(n, nkv, d).to(torch.bfloat16).double()) for n in lens]
+        q = torch.randn(sum(q_lens), nq * d).to(torch.bfloat16)
+        out, positions, seq_of = run_flash(q, seqs, lens, q_lens, nq, nkv, d, page_size, window, page_order=page_order)
+        ops().check_device_errors()
+        ref = torch.stack([ref_attention(q[t].double().view(nq, d), *seqs[seq_of[t]], positions[t], window).reshape(-1)
+                           for t in range(len(positions))])
+        close_flash(out, ref, max(float(v.abs().max()) for _, v in seqs), f"pages {page_order}")
 
 
 def test_tc_prefill_finds_one_far_key_and_respects_the_window_edge():
