@@ -42,8 +42,19 @@ CONFIG_C = dict(
     sliding_window=20)
 SEED_C, PAGE_C = 5, 16
 
+# Small D: the geometry the serving kernels are built for (head size 128, groups of four,
+# 16-token pages, widths that are multiples of 64), so that the engine-level cases also run
+# through the tcgen05 prefill attention, the TMA decode attention, the cluster-reduced GEMM
+# and the SwiGLU epilogue, not only through their general-purpose fallbacks.
+CONFIG_D = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=256,
+    num_attention_heads=8, num_key_value_heads=2, head_dim=128, intermediate_size=384,
+    vocab_size=1000, rope_theta=1000000.0, rms_norm_eps=1e-6, attention_bias=False,
+    tie_word_embeddings=False, max_position_embeddings=2048, hidden_act="silu")
+SEED_D, PAGE_D = 7, 16
+
 CONFIGS = {"A": (CONFIG_A, SEED_A, PAGE_A), "B": (CONFIG_B, SEED_B, PAGE_B),
-           "C": (CONFIG_C, SEED_C, PAGE_C)}
+           "C": (CONFIG_C, SEED_C, PAGE_C), "D": (CONFIG_D, SEED_D, PAGE_D)}
 
 # |x - ref| <= atol + rtol * |ref| per element, the reference's own rule and defaults
 # (crates/diagnostics/quality/src/verification.rs:22-67; crates/service/cli/src/constants.rs:19-22).

@@ -15,7 +15,8 @@ from helpers import (BF16_REL_OF_MAX, CONFIGS, Trace, assert_close, check_trace,
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [1, 7, 16, 33, 90, 120], "B": [3, 12, 31, 64, 100, 150], "C": [5, 40, 77, 130, 200, 64]}
+LENGTHS = {"A": [1, 7, 16, 33, 90, 120], "B": [3, 12, 31, 64, 100, 150], "C": [5, 40, 77, 130, 200, 64],
+           "D": [5, 64, 130, 300, 520, 33]}
 DTYPES = ["float32", "bfloat16"]
 
 
@@ -61,7 +62,7 @@ def runner_for(folders, name, dtype, num_pages=256):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_each_request_alone_and_whole(folders, requests_of, name, dtype):
     trace = Trace()
     for rid, toks in requests_of[name].items():
@@ -73,7 +74,7 @@ def test_each_request_alone_and_whole(folders, requests_of, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_most_in_one_step_then_the_last_32_one_by_one(folders, requests_of, name, dtype):
     trace = Trace()
     for rid, toks in requests_of[name].items():
@@ -88,7 +89,7 @@ def test_most_in_one_step_then_the_last_32_one_by_one(folders, requests_of, name
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_portions_of_changing_size(folders, requests_of, name, dtype):
     sizes = [7, 2, 13, 3, 2, 21, 5, 2, 9, 1, 17]
     trace = Trace()
@@ -141,7 +142,7 @@ def mixed_trace(reqs, seed=0, tail=12):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_mixed_batches_on_few_pages(folders, requests_of, name, dtype):
     from inferloop_b200.engine import ModelRunner
     reqs = requests_of[name]
@@ -201,7 +202,7 @@ def test_the_first_tokens_of_a_sequence(folders, requests_of, name, dtype):
     check_trace(run_trace_inprocess(r, trace), trace, {"r3": ref}, dtype, f"{name} first tokens")
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_float32_logits_do_not_depend_on_the_cut_at_all(folders, requests_of, name):
     """On the 32-bit path the order of every sum is fixed per position, so two ways of
     cutting give the same bits."""
@@ -212,7 +213,7 @@ def test_float32_logits_do_not_depend_on_the_cut_at_all(folders, requests_of, na
     r.end("w")
     parts, i = [], 0
     other = requests_of[name]["r2"]
-    for n in [5, 2, 30, 1, 1, 9, 400]:
+    for n in [5, 2, 30, 1, 1, 9, len(toks)]:          # the last portion takes what is left
         n = min(n, len(toks) - i)
         if n <= 0:
             break
@@ -225,7 +226,7 @@ def test_float32_logits_do_not_depend_on_the_cut_at_all(folders, requests_of, na
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 def test_greedy_generation_through_the_entry_point(folders, name, dtype):
     from inferloop_b200 import Engine, SamplingParams
     cfg, _, page = CONFIGS[name]
