@@ -94,6 +94,10 @@ class StepStager:
             self._events[i].synchronize()
         return i, self._host[i]
 
+    def release(self, turn: int) -> None:
+        """Give a claimed buffer back unsent (the step was refused)."""
+        self._turn = turn
+
     def send(self, turn: int, total: int, dest: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Copy the first `total` elements of the claimed buffer to the device (to `dest`
         if given, else to the stager's own buffer); returns the device buffer."""

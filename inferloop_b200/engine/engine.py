@@ -12,7 +12,7 @@ max_output_tokens, max_num_seqs, gpu_memory_utilization, device.
 from __future__ import annotations
 
 import os
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Mapping, Optional, Sequence, Union
 
 import torch
@@ -22,10 +22,20 @@ from ..sampling.device import DeviceSampler
 from ..sampling.params import SamplingParams
 from .batch import StepEntry
 from .runner import ModelRunner, parse_dtype, require_cuda
-from .scheduler import CapacityError, Request, Scheduler, SchedulerConfig, StepPlan
+from .scheduler import CapacityError, PlannedWork, Request, Scheduler, SchedulerConfig, StepPlan
 
 DEFAULT_BLOCK_SIZE = 16            # crates/engine/runtime/src/config.rs:19
 DEFAULT_GPU_MEMORY_UTILIZATION = 0.9
+
+
+@dataclass
+class _Flight:
+    """A step that is on the device."""
+    plan: StepPlan
+    sampling_work: list
+    drawn: Optional[torch.Tensor]               # ids still on the device (plain greedy), or None
+    sampled: Optional[Dict[Hashable, int]]      # ids on the host, once known
+    dropped: set = field(default_factory=set)   # requests that ended before this step's ids were read
 
 
 @dataclass
@@ -80,6 +90,9 @@ class Engine:
         self.cuda_graphs = cuda_graphs
         self._next_id = 0
         self._steps_since_check = 0
+        self._ahead: Optional[_Flight] = None
+        self.steps_launched_ahead = 0
+        self.lookahead = True                   # launch the next decode step before reading this one's ids
         self.requests: Dict[Hashable, Request] = {}
 
     # ------------------------------------------------------------------ sizing
@@ -126,38 +139,101 @@ class Engine:
         self.requests[request_id] = req
         return request_id
 
+    def abort(self, request_id: Hashable) -> None:
+        """End a request now (the reference's cancel: its resources are released at once,
+        crates/engine/runtime/src/pipeline/lifecycle.rs:242-251)."""
+        if self._ahead is not None:
+            self._ahead.dropped.add(request_id)
+        self.scheduler.abort(request_id)
+
     def is_idle(self) -> bool:
         return not self.scheduler.has_work()
 
     # ------------------------------------------------------------------ one step
     def step(self) -> List[TokenOutput]:
-        """Plan one step, run it, draw the tokens it yields; returns them."""
+        """Plan one step, run it, draw the tokens it yields; returns them.
+
+        While the device runs a greedy decode step, the step after it is usually known
+        already: the same requests, each with whatever token this step draws.  That step is
+        then launched before this step's ids are read back (its tokens are copied on the
+        device), so the device does not wait for the host between steps.  If a request
+        turns out to have finished (an end-of-sequence token), its row of the step already
+        running is computed in vain and dropped."""
+        flight = self._ahead
+        self._ahead = None
+        if flight is None:
+            flight = self._launch()
+            if flight is None:
+                return []
+        if flight.sampled is None:
+            handle = self.sampler.start_read(flight.drawn)
+            self._ahead = self._launch_ahead(flight)
+            ids = self.sampler.finish_read(handle)
+            flight.sampled = {w.request.id: t for w, t in zip(flight.sampling_work, ids)}
+        # a kernel that gave up a bounded wait leaves a flag on the device; looking costs a
+        # small read, so it is done now and then and at the end of generate()
+        self._steps_since_check += 1
+        if self.sampler is not None and self._steps_since_check >= 64:
+            self.check_device()
+        plan, work = flight.plan, flight.sampling_work
+        if flight.dropped:
+            work = [w for w in work if w.request.id not in flight.dropped]
+            plan = StepPlan([w for w in plan.work if w.request.id not in flight.dropped], plan.preempted)
+        finished = {r.id for r in self.scheduler.complete(plan, flight.sampled)}
+        if self._ahead is not None:
+            self._ahead.dropped |= finished
+            if all(w.request.id in self._ahead.dropped for w in self._ahead.plan.work):
+                self._ahead = None               # nothing of it is wanted any more
+        out = []
+        for w in work:
+            r = w.request
+            out.append(TokenOutput(r.id, flight.sampled[r.id], len(r.generated) - 1, r.id in finished,
+                                   r.finish_reason if r.id in finished else None))
+        return out
+
+    def _launch(self) -> Optional["_Flight"]:
+        """Plan a step and put it on the device.  Plain greedy steps come back with their
+        ids still on the device; every other kind is sampled before returning."""
         plan = self.scheduler.plan()
         if not plan.work:
-            return []
+            return None
         entries = [StepEntry(w.request.id, w.tokens, [w.count - 1] if w.samples else []) for w in plan.work]
         sampling_work = [w for w in plan.work if w.samples]
         if (self.sampler is not None and sampling_work
                 and all(w.request.params.uses_plain_greedy() for w in sampling_work)):
             # the arg-max rides in the step's own launch sequence; only ids come back
             _, drawn = self.runner.step(entries, draw_greedy=True)
-            ids = self.sampler.read_ids(drawn)
-            sampled = {w.request.id: t for w, t in zip(sampling_work, ids)}
-        else:
-            logits = self.runner.step(entries)
-            sampled = self._sample(logits, sampling_work)
-        # a kernel that gave up a bounded wait leaves a flag on the device; looking costs a
-        # small read, so it is done now and then and at the end of generate()
-        self._steps_since_check += 1
-        if self.sampler is not None and self._steps_since_check >= 64:
-            self.check_device()
-        finished = {r.id for r in self.scheduler.complete(plan, sampled)}
-        out = []
-        for w in sampling_work:
+            return _Flight(plan, sampling_work, drawn, None)
+        logits = self.runner.step(entries)
+        return _Flight(plan, sampling_work, None, self._sample(logits, sampling_work))
+
+    def _launch_ahead(self, flight: "_Flight") -> Optional["_Flight"]:
+        """Launch the step after `flight` if it is certain what it holds: `flight` is a
+        decode step of every running request, nobody waits, and nobody can reach a length
+        limit with the token being drawn.  (A stop token may still end a request; its row
+        is then dropped.)"""
+        if not self.cuda_graphs or self.lookahead is False or getattr(self.runner, "step_ahead", None) is None:
+            return None
+        s = self.scheduler
+        work = flight.plan.work
+        if (flight.plan.preempted or s.waiting or len(work) != len(s.running) or flight.dropped
+                or len(flight.sampling_work) != len(work)):
+            return None
+        for w in work:
             r = w.request
-            out.append(TokenOutput(r.id, sampled[r.id], len(r.generated) - 1, r.id in finished,
-                                   r.finish_reason if r.id in finished else None))
-        return out
+            if (w.count != 1 or len(r.generated) + 2 > r.max_new_tokens
+                    or r.total_len() + 2 > s.config.max_model_len or not r.params.uses_plain_greedy()):
+                return None
+        if any(w.request is not r for w, r in zip(work, s.running)):
+            return None
+        entries = [StepEntry(w.request.id, [0], [0]) for w in work]
+        drawn = self.runner.step_ahead(entries, flight.drawn)
+        if drawn is None:
+            return None
+        s.stats["steps"] += 1
+        self.steps_launched_ahead += 1
+        nxt = [PlannedWork(w.request, w.start + 1, 1, True) for w in work]
+        return _Flight(StepPlan(nxt, []), nxt, drawn, None)
 
     def _sample(self, logits: torch.Tensor, work) -> Dict[Hashable, int]:
         """Row i of `logits` belongs to work[i].  Plain greedy and plain temperature rows
@@ -228,7 +304,8 @@ class Engine:
         return {
             "waiting": len(s.waiting), "running": len(s.running), "finished": len(s.finished),
             "steps": getattr(self.runner, "steps_run", 0), "tokens": getattr(self.runner, "tokens_run", 0),
-            "scheduler": dict(s.stats), "cache": self.runner.cache.inspect(),
+            "scheduler": dict(s.stats), "steps_launched_ahead": self.steps_launched_ahead,
+            "cache": self.runner.cache.inspect(),
             "max_model_len": self.max_model_len,
             "max_num_seqs": s.config.max_num_seqs,
             "max_num_batched_tokens": s.config.max_num_batched_tokens,

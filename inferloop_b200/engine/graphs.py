@@ -110,6 +110,33 @@ class DecodeGraphs:
         self._recorded[key] = rec
         return rec
 
+    def _prepare_replay(self, entries: Sequence[StepEntry], bucket: int, rec: "_Recorded") -> None:
+        """What `_prepare` does for a recorded bucket, in one call of the host library and
+        without building views nobody reads: check, pages, arrays into the graph's buffer."""
+        import ctypes
+        from .. import host
+        from .runner import _raise_step_error
+        r = self.runner
+        cache = r.cache
+        n = len(entries)
+        try:
+            req = (ctypes.c_longlong * n)(*[cache.id_of(e.request) for e in entries])
+            tok = (ctypes.c_int * n)(*[int(e.tokens[0]) for e in entries])
+        except KeyError:                      # a request that is not live yet: the general path begins it
+            self._prepare(entries, bucket, rec.ints)
+            return
+        except (OverflowError, TypeError, ValueError):
+            raise ValueError("token ids must be integers of the vocabulary") from None
+        turn, hostbuf = r.stager.claim(rec.ints.numel())
+        offsets = (ctypes.c_longlong * (7 + len(cache.groups)))()
+        total = host.lib().ilb_step_decode(cache.handle, n, req, tok, bucket - n, self.max_blocks,
+                                           r.spec.vocab_size, r.spec.max_positions,
+                                           ctypes.c_void_p(hostbuf.data_ptr()), hostbuf.numel(), offsets)
+        if total < 0:
+            r.stager.release(turn)
+            _raise_step_error(int(total), entries)
+        r.stager.send(turn, int(total), rec.ints)
+
     def step(self, entries: Sequence[StepEntry], with_argmax: bool = False):
         """Run a decode-only step.  Returns (logits[:n], drawn[:n] or None, kernels
         launched).  The very first step of a bucket runs eagerly while it is recorded."""
@@ -125,10 +152,34 @@ class DecodeGraphs:
         if rec is None:
             rec = self._record(key, entries, bucket, with_argmax)     # ran the step eagerly
         else:
-            self._prepare(entries, bucket, rec.ints)
+            self._prepare_replay(entries, bucket, rec)
             rec.graph.replay()
             self.replays += 1
         return rec.logits[:n], (rec.drawn[:n] if with_argmax else None), rec.kernels
+
+    def step_ahead(self, entries: Sequence[StepEntry], previous_drawn: torch.Tensor) -> Optional[torch.Tensor]:
+        """The decode step that follows one whose tokens are still being computed: the same
+        requests in the same order, each continuing with the token the previous step draws.
+        The ids never visit the host: they are copied on the device from `previous_drawn`
+        into this step's token array before the replay.  Returns the device tensor the new
+        ids will be in, or None when the step cannot be launched this way (no recorded graph
+        for this size yet, or not enough pages), in which case nothing has changed."""
+        from ..cache.pages import OutOfPages
+        n = len(entries)
+        bucket = bucket_for(n)
+        if bucket is None:
+            return None
+        rec = self._recorded.get((bucket, True))
+        if rec is None or rec.workspace_generation != self.runner.ctx.workspace.generation:
+            return None
+        try:
+            self._prepare_replay(entries, bucket, rec)
+        except OutOfPages:
+            return None
+        rec.ctx.tokens[:n].copy_(previous_drawn[:n])
+        rec.graph.replay()
+        self.replays += 1
+        return rec.drawn[:n]
 
     def recorded(self, n: int, with_argmax: bool) -> Optional[_Recorded]:
         return self._recorded.get((bucket_for(n), with_argmax))

@@ -261,6 +261,25 @@ class ModelRunner:
         """Whether every group has the pages this step would take."""
         return step_fits(self.cache, entries)
 
+    def step_ahead(self, entries: Sequence[StepEntry], previous_drawn: torch.Tensor) -> Optional[torch.Tensor]:
+        """Launch the decode step after one that is still running (see
+        `DecodeGraphs.step_ahead`); the entries' tokens are placeholders.  Returns the device
+        tensor of the ids it will draw, or None if it was not launched."""
+        if self.graphs is None or not self.graphs.eligible(entries):
+            return None
+        drawn = self.graphs.step_ahead(entries, previous_drawn)
+        if drawn is None:
+            return None
+        n = len(entries)
+        req = (ctypes.c_longlong * n)(*[self.cache.id_of(e.request) for e in entries])
+        ones = (ctypes.c_int * n)(*([1] * n))
+        rc = host.lib().ilb_step_commit(self.cache.handle, n, req, ones)
+        if rc < 0:
+            _raise_step_error(rc, entries)
+        self.steps_run += 1
+        self.tokens_run += n
+        return drawn
+
     # ------------------------------------------------------------------ the step
     def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
         """Take pages for the step (all entries or none) and stage its arrays."""
@@ -287,8 +306,12 @@ class ModelRunner:
                 drawn = self.ctx.workspace.buffer("runner.drawn", (logits.shape[0],), torch.int32)
                 ops.argmax(logits, drawn, None)
             self.kernels_last_step = ops.LAUNCHES - before
-        for e in entries:
-            self.cache.commit(e.request, self.cache.length(e.request) + len(e.tokens))
+        n = len(entries)
+        req = (ctypes.c_longlong * n)(*[self.cache.id_of(e.request) for e in entries])
+        n_tok = (ctypes.c_int * n)(*[len(e.tokens) for e in entries])
+        rc = host.lib().ilb_step_commit(self.cache.handle, n, req, n_tok)
+        if rc < 0:
+            _raise_step_error(rc, entries)
         self.steps_run += 1
         self.tokens_run += n_tokens
         return (logits, drawn) if draw_greedy else logits

@@ -86,7 +86,13 @@ class PlannedWork:
 
     @property
     def tokens(self) -> List[int]:
-        return self.request.sequence[self.start:self.start + self.count]
+        r, a, b = self.request, self.start, self.start + self.count
+        n = len(r.prompt)                    # without joining the two lists every step
+        if b <= n:
+            return r.prompt[a:b]
+        if a >= n:
+            return r.generated[a - n:b - n]
+        return r.prompt[a:] + r.generated[:b - n]
 
 
 @dataclass

@@ -154,6 +154,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ilb_ledger_stats": (None, [c_vp, llp]),
         "ilb_step_check": (c_int, [c_vp, c_int, llp, ip, ip, ip, ip, c_ll, c_ll]),
         "ilb_step_fits": (c_int, [c_vp, c_int, llp, ip]),
+        "ilb_step_decode": (c_ll, [c_vp, c_int, llp, ip, c_int, c_int, c_ll, c_ll, c_vp, c_ll, llp]),
+        "ilb_step_commit": (c_int, [c_vp, c_int, llp, ip]),
         "ilb_step_build": (c_ll, [c_vp, c_int, llp, ip, ip, ip, ip, c_int, c_int, c_ll, c_ll, c_vp, c_ll, llp]),
     }
     for name, (res, args) in sig.items():

@@ -839,3 +839,37 @@ ILB_API long long ilb_step_build(void* h, int n, const long long* req, const int
   }
   return off;
 }
+
+// One call for the commonest step: every request live and bringing exactly one token whose
+// logits are wanted.  Checks, takes the pages (all or none) and packs the arrays.
+ILB_API long long ilb_step_decode(void* h, int n, const long long* req, const int* tok, int pad_seqs, int max_blocks,
+                                  long long vocab, long long max_positions, int* out, long long cap, long long* offsets) {
+  Ledger* l = static_cast<Ledger*>(h);
+  if (n <= 0) return fail(kInvalid, "a step needs at least one entry");
+  std::vector<int> ones((size_t)n, 1), zeros((size_t)n, 0);
+  int rc = ilb_step_check(h, n, req, ones.data(), tok, ones.data(), zeros.data(), vocab, max_positions);
+  if (rc) return rc;
+  for (int i = 0; i < n; ++i)
+    if (req[i] < 0) return fail(kInvalid, "request #%d is not live", i);
+  rc = ilb_step_fits(h, n, req, ones.data());
+  if (rc < 0) return rc;
+  if (rc == 0) return fail(kOutOfPages, "step of %d tokens does not fit the free pages", n);
+  for (int i = 0; i < n; ++i) {
+    rc = l->ensure(req[i], l->length[req[i]] + 1);
+    if (rc) return rc;
+  }
+  return ilb_step_build(h, n, req, ones.data(), tok, ones.data(), zeros.data(), pad_seqs, max_blocks, vocab, max_positions,
+                        out, cap, offsets);
+}
+
+// Every request's committed length grows by its token count (after the step has run).
+ILB_API int ilb_step_commit(void* h, int n, const long long* req, const int* n_tok) {
+  Ledger* l = static_cast<Ledger*>(h);
+  for (int i = 0; i < n; ++i) {
+    auto it = l->length.find(req[i]);
+    if (it == l->length.end()) return fail(kInvalid, "request #%d is not live", i);
+    const int rc = l->commit(req[i], it->second + n_tok[i]);
+    if (rc) return rc;
+  }
+  return kOk;
+}

@@ -57,12 +57,25 @@ class DeviceSampler:
             raise ValueError("invalid sampling logits (a non-finite value)")
         return vals[:rows]
 
-    def read_ids(self, drawn: torch.Tensor) -> List[int]:
-        """Token ids that a step already drew on the device (synchronises)."""
+    def start_read(self, drawn: torch.Tensor):
+        """Begin copying token ids that a step drew on the device to the host; work that
+        is launched after this call does not delay the ids.  Returns a handle for
+        `finish_read`."""
         rows = drawn.numel()
         if rows > self._cap:
             self._grow(max(rows, 2 * self._cap))
         self.h_out[:rows].copy_(drawn, non_blocking=True)
-        torch.cuda.current_stream(self.device).synchronize()
+        event = torch.cuda.Event()
+        event.record(torch.cuda.current_stream(self.device))
         self.d2h_bytes_last = rows * 4
+        return rows, event
+
+    def finish_read(self, handle) -> List[int]:
+        """Wait for the copy begun by `start_read` and return the ids."""
+        rows, event = handle
+        event.synchronize()
         return self.h_out[:rows].tolist()
+
+    def read_ids(self, drawn: torch.Tensor) -> List[int]:
+        """Token ids that a step already drew on the device (synchronises)."""
+        return self.finish_read(self.start_read(drawn))

@@ -276,6 +276,42 @@ def test_temperature_generation_matches_the_plain_sampler(folders):
             seq.append(t)
 
 
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("D", "bfloat16")])
+def test_steps_launched_ahead_give_the_same_tokens(folders, name, dtype):
+    """The engine launches the next decode step before it has read the ids of the running
+    one.  With stop tokens some requests end while their row of the next step is already
+    being computed: that row is dropped, everybody else's tokens are what they are without
+    the lookahead, and every page comes back."""
+    from inferloop_b200 import Engine, SamplingParams
+    cfg, _, page = CONFIGS[name]
+    prompts = [random_tokens(n, cfg["vocab_size"], 300 + n) for n in (9, 40, 17, 33)]
+
+    def run(lookahead, params, new=24):
+        e = Engine(folders[name], dtype=dtype, block_size=page, num_gpu_blocks_override=96, max_num_seqs=4,
+                   prefill_chunk_tokens=64)
+        e.lookahead = lookahead
+        out = e.generate(prompts, params, max_new_tokens=new)
+        info = e.inspect()
+        assert info["running"] == 0 and all(g["free"] == g["total"] for g in info["cache"]["groups"])
+        return out, info
+
+    free_run, _ = run(False, SamplingParams())
+    # stop tokens taken from the middle of two of the free-running answers
+    stops = (free_run[0][7], free_run[2][13])
+    params = SamplingParams(eos_tokens=stops)
+    want, info_off = run(False, params)
+    got, info_on = run(True, params)
+    assert got == want
+    assert any(len(g) < 24 for g in got) and any(len(g) == 24 for g in got) or all(len(g) < 24 for g in got)
+    assert info_off["steps_launched_ahead"] == 0 and info_on["steps_launched_ahead"] > 5
+    if dtype == "float32":
+        model = plain.PlainModel(folders[name])
+        for p, g in zip(prompts, got):
+            ref = plain.generate(model, p, 24)
+            cut = next((i + 1 for i, t in enumerate(ref) if t in stops), 24)
+            assert g == ref[:cut]
+
+
 def test_page_pressure_in_the_engine_gives_the_same_tokens(folders):
     """So few pages that requests are preempted and recomputed: tokens do not change."""
     from inferloop_b200 import Engine, SamplingParams
