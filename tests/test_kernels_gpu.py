@@ -415,7 +415,8 @@ def test_flash_prefill_mixed_batch(nq, nkv, d, page_size, window):
 
 
 @pytest.mark.parametrize("nq,nkv,d,page_size,window,chunk", [(4, 2, 32, 4, 0, 256), (6, 2, 64, 8, 0, 256), (5, 5, 96, 16, 300, 256),
-                                                               (32, 8, 128, 16, 0, 256), (8, 1, 128, 16, 0, 512), (40, 2, 64, 32, 0, 256)])
+                                                               (32, 8, 128, 16, 0, 256), (8, 1, 128, 16, 0, 512), (40, 2, 64, 32, 0, 256),
+                                                               (8, 2, 128, 16, 100, 256), (6, 3, 64, 64, 40, 256)])
 @pytest.mark.parametrize("cluster", [True, False])
 def test_flash_decode_split_kv(nq, nkv, d, page_size, window, chunk, cluster):
     """One token per sequence, lengths below, at and far above the chunk length (ticketed
