@@ -206,6 +206,17 @@ class CacheManager:
         del self._live[request]
         self._ids.forget(request)
 
+    def released_in_ledger(self, request: Hashable) -> None:
+        """The scheduler (C++) has already given back this request's pages and slot in the
+        ledger; drop it from the table of live requests here too."""
+        if self._live.pop(request, None) is not None:
+            self._ids.forget(request)
+
+    @property
+    def ids(self) -> OwnerIds:
+        """Numbers of the requests, shared with the scheduler."""
+        return self._ids
+
     # ------------------------------------------------------------------ views
     def block_table(self, group: int, request: Hashable) -> List[int]:
         n = self._lib.ilb_ledger_table_len(self._h, int(group), self._live[request])

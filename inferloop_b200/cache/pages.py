@@ -32,6 +32,7 @@ class OwnerIds:
     def __init__(self) -> None:
         self._id: Dict[Hashable, int] = {}
         self._name: Dict[int, Hashable] = {}
+        self._pinned = set()
         self._next = 0
 
     def of(self, owner: Hashable) -> int:
@@ -45,7 +46,19 @@ class OwnerIds:
     def name(self, i: int) -> Optional[Hashable]:
         return self._name.get(i)
 
+    def pin(self, owner: Hashable) -> int:
+        """Keep this owner's number until `unpin` (a scheduled request is known by it for its
+        whole life, across preemptions)."""
+        i = self.of(owner)
+        self._pinned.add(owner)
+        return i
+
+    def unpin(self, owner: Hashable) -> None:
+        self._pinned.discard(owner)
+
     def forget(self, owner: Hashable) -> None:
+        if owner in self._pinned:
+            return
         i = self._id.pop(owner, None)
         if i is not None:
             self._name.pop(i, None)

@@ -14,7 +14,6 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
-import numpy as np
 import torch
 
 
@@ -52,9 +51,10 @@ class StepContext:
 
 
 class StepStager:
-    """Packs a step's integer arrays into pinned host memory and copies them to the
-    device with one transfer.  Two staging buffers alternate, each guarded by an event,
-    so packing step n+1 never overwrites memory that step n's copy still reads."""
+    """Pinned host memory that a step's integer arrays are packed into (by the C++ host
+    library) and the one transfer that takes them to the device.  Two staging buffers
+    alternate, each guarded by an event, so packing step n+1 never overwrites memory that
+    step n's copy still reads."""
 
     def __init__(self, device: torch.device, capacity: int = 1 << 16) -> None:
         self.device = device
@@ -110,35 +110,6 @@ class StepStager:
         self._events[turn] = ev
         self.last_elements = total
         return dev
-
-    def stage(self, arrays: Sequence[np.ndarray], dest: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
-        """Copy the int32 arrays to the device; returns one device view per array.
-        Each array starts on a 16-byte boundary.  `dest`, if given, is the device buffer
-        that receives them (it must be large enough); otherwise the stager's own."""
-        offsets, total = [], 0
-        for a in arrays:
-            offsets.append(total)
-            total += (a.size + 3) // 4 * 4
-        if total > self._cap:
-            torch.cuda.current_stream(self.device).synchronize()
-            self._grow(max(total, 2 * self._cap))
-        i = self._turn
-        self._turn ^= 1
-        if self._events[i] is not None:
-            self._events[i].synchronize()
-        host = self._host[i]
-        hv = host.numpy()
-        for a, off in zip(arrays, offsets):
-            hv[off:off + a.size] = a.reshape(-1)
-        dev = self._dev if dest is None else dest
-        if dev.numel() < total:
-            raise ValueError(f"staging destination holds {dev.numel()} elements, {total} are needed")
-        dev[:total].copy_(host[:total], non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record(torch.cuda.current_stream(self.device))
-        self._events[i] = ev
-        self.last_elements = total
-        return [dev[off:off + a.size].view(*a.shape) for a, off in zip(arrays, offsets)]
 
     @property
     def bytes_last(self) -> int:

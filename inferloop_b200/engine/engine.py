@@ -216,7 +216,8 @@ class Engine:
             return None
         s = self.scheduler
         work = flight.plan.work
-        if (flight.plan.preempted or s.waiting or len(work) != len(s.running) or flight.dropped
+        n_waiting, n_running = s.counts()
+        if (flight.plan.preempted or n_waiting or len(work) != n_running or flight.dropped
                 or len(flight.sampling_work) != len(work)):
             return None
         for w in work:
@@ -224,13 +225,11 @@ class Engine:
             if (w.count != 1 or len(r.generated) + 2 > r.max_new_tokens
                     or r.total_len() + 2 > s.config.max_model_len or not r.params.uses_plain_greedy()):
                 return None
-        if any(w.request is not r for w, r in zip(work, s.running)):
-            return None
         entries = [StepEntry(w.request.id, [0], [0]) for w in work]
         drawn = self.runner.step_ahead(entries, flight.drawn)
         if drawn is None:
             return None
-        s.stats["steps"] += 1
+        s.count_step()
         self.steps_launched_ahead += 1
         nxt = [PlannedWork(w.request, w.start + 1, 1, True) for w in work]
         return _Flight(StepPlan(nxt, []), nxt, drawn, None)

@@ -1,4 +1,4 @@
-"""Continuous batching above the step function.
+"""Continuous batching above the step function (policy in C++, see `Scheduler`).
 
 Each call of :meth:`Scheduler.plan` builds ONE step under a token budget and a sequence
 cap: every request that is decoding brings one token, prompts are cut into portions,
@@ -28,10 +28,12 @@ arrival order.
 """
 from __future__ import annotations
 
-from collections import deque
+import ctypes
+import re
 from dataclasses import dataclass, field
-from typing import Deque, Dict, Hashable, List, Optional, Sequence
+from typing import Dict, Hashable, List, Optional, Sequence
 
+from .. import host
 from ..cache.manager import CacheManager
 from ..sampling.params import SamplingParams
 
@@ -110,180 +112,130 @@ class CapacityError(RuntimeError):
 
 
 class Scheduler:
+    """The planning itself is the C++ host library's (`host/ilb_host.cpp`, `Sched`): it works
+    on the ledger directly and knows requests by the ledger's numbers and by their lengths.
+    This class keeps the request objects (token values, sampling options), gives each
+    request its number, and turns the library's answers into plans."""
+
     def __init__(self, cache: CacheManager, config: SchedulerConfig) -> None:
         self.cache = cache
         self.config = config
-        self.waiting: Deque[Request] = deque()
-        self.running: List[Request] = []          # in admission order
+        self._lib = host.lib()
+        h = ctypes.c_void_p()
+        rc = self._lib.ilb_sched_new(cache.handle, config.max_num_seqs, config.max_num_batched_tokens,
+                                     config.prefill_chunk_tokens, config.max_model_len, ctypes.byref(h))
+        if rc:
+            raise ValueError(host.last_error())
+        self._h = h
+        self._by_number: Dict[int, Request] = {}
         self.finished: Dict[Hashable, Request] = {}
-        self._arrivals = 0
-        self.stats = {"steps": 0, "preemptions": 0, "admitted": 0, "finished": 0}
+        cap = max(config.max_num_seqs, 1) + 8
+        self._work = (ctypes.c_longlong * (4 * cap))()
+        self._victims = (ctypes.c_longlong * (4 * cap))()
+        self._cap = cap
+
+    def __del__(self) -> None:
+        h = getattr(self, "_h", None)
+        if h is not None and h.value:
+            self._lib.ilb_sched_free(h)
+            self._h = None
+
+    def _message(self) -> str:
+        """The library names requests by number; the message names them as the caller does."""
+        return re.sub(r"request #(\d+)", lambda m: f"request {self._by_number[int(m.group(1))].id!r}"
+                      if int(m.group(1)) in self._by_number else m.group(0), host.last_error())
+
+    def _listed(self, which: int) -> List[Request]:
+        n = self._lib.ilb_sched_list(self._h, which, self._victims, 0)
+        if n == 0:
+            return []
+        buf = (ctypes.c_longlong * n)()
+        self._lib.ilb_sched_list(self._h, which, buf, n)
+        return [self._by_number[i] for i in buf]
+
+    @property
+    def waiting(self) -> List[Request]:
+        return self._listed(0)
+
+    @property
+    def running(self) -> List[Request]:
+        """In admission order."""
+        return self._listed(1)
+
+    @property
+    def stats(self) -> Dict[str, int]:
+        out = (ctypes.c_longlong * 6)()
+        self._lib.ilb_sched_stats(self._h, out)
+        return {"steps": out[0], "preemptions": out[1], "admitted": out[2], "finished": out[3]}
+
+    def count_step(self) -> None:
+        """A step that was launched without a plan of its own (the engine's lookahead)."""
+        self._lib.ilb_sched_count_step(self._h)
 
     # ------------------------------------------------------------------ intake
     def add(self, request: Request) -> None:
-        if request.max_new_tokens <= 0:
-            raise ValueError("max_new_tokens must be positive")
-        if not request.prompt:
-            raise ValueError("empty input")
-        if any(r.id == request.id for r in self.waiting) or any(r.id == request.id for r in self.running):
-            raise ValueError(f"request id {request.id!r} is already queued")
-        total = len(request.prompt) + request.max_new_tokens
-        if total > self.config.max_model_len:
-            # reserved_tokens = prompt + max_new_tokens must fit the context
-            # (crates/engine/workloads/src/native.rs:91-111)
-            raise ValueError(f"request {request.id!r}: prompt {len(request.prompt)} + max_new_tokens "
-                             f"{request.max_new_tokens} exceeds max_model_len {self.config.max_model_len}")
-        pages = -(-total // self.cache.page_size)
-        for g in self.cache.groups:
-            reach = pages if g.need.window is None else min(
-                pages, -(-(g.need.window + self.config.prefill_chunk_tokens) // self.cache.page_size) + 1)
-            if reach > g.pool.num_pages:
-                raise CapacityError(f"request {request.id!r} needs {reach} pages of group {g.index}, "
-                                    f"the pool has {g.pool.num_pages}")
-        request.arrival = self._arrivals
-        self._arrivals += 1
+        known = self.cache.ids.of(request.id) in self._by_number      # queued already: the library will refuse it
+        number = self.cache.ids.pin(request.id)
+        if not known:
+            self._by_number[number] = request
+        rc = self._lib.ilb_sched_add(self._h, number, len(request.prompt), int(request.max_new_tokens))
+        if rc:
+            msg = self._message()
+            if not known:
+                del self._by_number[number]
+                self.cache.ids.unpin(request.id)
+                if not self.cache.has(request.id):
+                    self.cache.ids.forget(request.id)
+            if rc == host.CAPACITY:
+                raise CapacityError(msg)
+            raise ValueError(msg)
         request.status = WAITING
-        self.waiting.append(request)
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        out = (ctypes.c_longlong * 6)()
+        self._lib.ilb_sched_stats(self._h, out)
+        return bool(out[4] or out[5])
+
+    def counts(self):
+        """(waiting, running)."""
+        out = (ctypes.c_longlong * 6)()
+        self._lib.ilb_sched_stats(self._h, out)
+        return out[4], out[5]
 
     # ------------------------------------------------------------------ planning
-    def _computed(self, r: Request) -> int:
-        return self.cache.length(r.id) if self.cache.has(r.id) else 0
-
-    def _pages_for(self, r: Request, new_len: int) -> Dict[int, int]:
-        if self.cache.has(r.id):
-            return self.cache.pages_needed(r.id, new_len)
-        return {g.index: -(-new_len // self.cache.page_size) for g in self.cache.groups}
-
-    def _preempt(self, victim: Request, plan: StepPlan) -> None:
-        """Recompute preemption: give everything back, restart its prefill later."""
-        if self.cache.has(victim.id):
-            self.cache.release(victim.id)
-        self.running.remove(victim)
-        victim.status = WAITING
-        victim.preemptions += 1
-        self.waiting.appendleft(victim)       # it keeps its place ahead of newer arrivals
-        plan.preempted.append(victim.id)
-        self.stats["preemptions"] += 1
-
     def plan(self) -> StepPlan:
         """One step.  If nothing can run although requests hold pages (every one of them
         blocked on pages the others hold), the youngest is preempted and the plan is made
         again, so the oldest request always makes progress."""
+        c = self.config                     # the limits may be changed between steps
+        if c.max_num_seqs + 8 > self._cap:
+            self._cap = c.max_num_seqs + 8
+            self._work = (ctypes.c_longlong * (4 * self._cap))()
+            self._victims = (ctypes.c_longlong * (4 * self._cap))()
+        if self._lib.ilb_sched_set_limits(self._h, c.max_num_seqs, c.max_num_batched_tokens, c.prefill_chunk_tokens,
+                                          c.max_model_len):
+            raise ValueError(host.last_error())
+        n_work, n_victims = ctypes.c_int(), ctypes.c_int()
+        rc = self._lib.ilb_sched_plan(self._h, self._work, self._cap, ctypes.byref(n_work), self._victims,
+                                      ctypes.byref(n_victims))
         plan = StepPlan()
-        while True:
-            self._fill(plan)
-            if plan.work or not self.running:
-                break
-            if len(self.running) == 1:
-                raise CapacityError(
-                    f"request {self.running[0].id!r} cannot grow: the cache is too small for it alone")
-            self._preempt(self.running[-1], plan)
-        if not plan.work and self.waiting and not self.running:
-            raise CapacityError(
-                f"request {self.waiting[0].id!r} cannot start: the cache is too small for it alone")
-        if plan.work:
-            self.stats["steps"] += 1
-        return plan
-
-    def _held(self, r: Request) -> Dict[int, int]:
-        if not self.cache.has(r.id):
-            return {}
-        return {g.index: sum(1 for p in self.cache.block_table(g.index, r.id) if p >= 0)
-                for g in self.cache.groups}
-
-    def _fill(self, plan: StepPlan) -> None:
-        cfg = self.config
-        budget = cfg.max_num_batched_tokens
-        free = dict(self.cache.free_pages())
-        page = self.cache.page_size
-
-        def fits(need: Dict[int, int]) -> bool:
-            return all(need.get(g, 0) <= free[g] for g in free)
-
-        def charge(need: Dict[int, int]) -> None:
-            for g, n in need.items():
-                free[g] -= n
-
-        def planned(r: Request) -> bool:
-            return any(w.request is r for w in plan.work)
-
-        def is_decode(r: Request) -> bool:
-            return self._computed(r) == r.total_len() - 1
-
-        # 1. decoding requests, oldest first; a blocked one preempts the youngest running
-        for r in [r for r in self.running if is_decode(r)]:
-            if r not in self.running:          # became a victim meanwhile
-                continue
-            if budget <= 0 or len(plan.work) >= cfg.max_num_seqs:
-                break
-            need = self._pages_for(r, r.total_len())
-            while not fits(need):
-                victims = [v for v in reversed(self.running) if v is not r and not planned(v)]
-                if not victims:
-                    break
-                held = self._held(victims[0])
-                self._preempt(victims[0], plan)
-                for g, n in held.items():
-                    free[g] += n
-            if not fits(need):
-                continue                       # waits; something else may finish first
-            charge(need)
-            plan.work.append(PlannedWork(r, r.total_len() - 1, 1, True))
-            budget -= 1
-
-        # 2. prompt portions: requests already running, then new arrivals in order
-        def grant(r: Request) -> Optional[PlannedWork]:
-            nonlocal budget
-            done = self._computed(r)
-            portion = min(cfg.prefill_chunk_tokens, r.total_len() - done)
-            if budget >= portion:
-                count = portion
-            elif budget >= 1 and budget * 2 >= portion:
-                count = budget
-            else:
-                return None
-            need = self._pages_for(r, done + count)
-            if not fits(need):
-                # take what the free pages can hold, if that is still progress
-                held = self._held(r)
-                room = min((len(self.cache.block_table(g.index, r.id)) if self.cache.has(r.id) else 0)
-                           + free[g.index] for g in self.cache.groups) * page if self.cache.groups else done + count
-                count = min(count, room - done)
-                if count <= 0:
-                    return None
-                need = self._pages_for(r, done + count)
-                if not fits(need):
-                    return None
-            charge(need)
-            budget -= count
-            return PlannedWork(r, done, count, done + count == r.total_len())
-
-        for r in list(self.running):
-            if planned(r) or is_decode(r):
-                continue
-            if budget <= 0 or len(plan.work) >= cfg.max_num_seqs:
-                break
-            w = grant(r)
-            if w is not None:
-                plan.work.append(w)
-
-        while (self.waiting and budget > 0 and len(plan.work) < cfg.max_num_seqs
-               and len(self.running) < cfg.max_num_seqs and self.cache.slots.num_free > len(
-                   [w for w in plan.work if not self.cache.has(w.request.id)])):
-            r = self.waiting[0]
-            if r.id in plan.preempted and self.running:
-                break          # a victim of this very step waits for the next one
-            w = grant(r)
-            if w is None:
-                break          # first come first served: nobody overtakes the head
-            self.waiting.popleft()
+        for i in range(n_victims.value):
+            r = self._by_number[self._victims[i]]
+            r.status = WAITING
+            r.preemptions += 1
+            self.cache.released_in_ledger(r.id)
+            plan.preempted.append(r.id)
+        if rc:
+            msg = self._message()
+            if rc == host.CAPACITY:
+                raise CapacityError(msg)
+            raise ValueError(msg)
+        w = self._work
+        for i in range(n_work.value):
+            r = self._by_number[w[4 * i]]
             r.status = RUNNING
-            self.running.append(r)
-            self.stats["admitted"] += 1
-            plan.work.append(w)
+            plan.work.append(PlannedWork(r, w[4 * i + 1], w[4 * i + 2], bool(w[4 * i + 3])))
+        return plan
 
     # ------------------------------------------------------------------ results
     def complete(self, plan: StepPlan, sampled: Dict[Hashable, int]) -> List[Request]:
@@ -296,34 +248,26 @@ class Scheduler:
             r = w.request
             token = int(sampled[r.id])
             r.generated.append(token)
-            reason = None
-            if r.params.is_eos(token):
-                reason = "eos"
-            elif len(r.generated) >= r.max_new_tokens:
-                reason = "length"
-            elif r.total_len() >= self.config.max_model_len:
-                reason = "length"
-            if reason is not None:
+            number = self.cache.ids.of(r.id)
+            reason = self._lib.ilb_sched_token(self._h, number, 1 if r.params.is_eos(token) else 0)
+            if reason < 0:
+                raise ValueError(self._message())
+            if reason:
                 r.status = FINISHED
-                r.finish_reason = reason
-                self.running.remove(r)
-                if self.cache.has(r.id):
-                    self.cache.release(r.id)
-                self.finished[r.id] = r
-                self.stats["finished"] += 1
+                r.finish_reason = "eos" if reason == 1 else "length"
+                self._retire(r, number)
                 done.append(r)
         return done
 
+    def _retire(self, r: Request, number: int) -> None:
+        self.cache.ids.unpin(r.id)
+        self.cache.released_in_ledger(r.id)
+        self.cache.ids.forget(r.id)
+        self._by_number.pop(number, None)
+        self.finished[r.id] = r
+
     def abort(self, request_id: Hashable) -> None:
-        for r in list(self.running):
-            if r.id == request_id:
-                self.running.remove(r)
-                if self.cache.has(r.id):
-                    self.cache.release(r.id)
+        for number, r in list(self._by_number.items()):
+            if r.id == request_id and self._lib.ilb_sched_abort(self._h, number):
                 r.status, r.finish_reason = FINISHED, "abort"
-                self.finished[r.id] = r
-        for r in list(self.waiting):
-            if r.id == request_id:
-                self.waiting.remove(r)
-                r.status, r.finish_reason = FINISHED, "abort"
-                self.finished[r.id] = r
+                self._retire(r, number)

@@ -1,8 +1,8 @@
 """The C++ host runtime (`ilb_host.cpp`) and its loader.
 
 The library holds what the CPU does for every model load and every step: reading and
-checking the safetensors container, the ledger of cache pages and state slots, and the
-packing of a step's integer arrays into the staging buffer.  It is compiled with the
+checking the safetensors container, the ledger of cache pages and state slots, the
+scheduler's planning, and the packing of a step's integer arrays into the staging buffer.  It is compiled with the
 C++ compiler the first time it is needed and kept beside the source (`_build/`), or
 under the temporary directory when the package folder cannot be written.  There is no
 Python stand-in: if it cannot be built, loading fails with the compiler's message.
@@ -25,7 +25,7 @@ SOURCE = "ilb_host.cpp"
 CXX_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall"]
 
 # return codes of the library
-OK, INVALID, OUT_OF_PAGES, OUT_OF_SLOTS, LEDGER, FORMAT, IO = 0, -1, -2, -3, -4, -5, -6
+OK, INVALID, OUT_OF_PAGES, OUT_OF_SLOTS, LEDGER, FORMAT, IO, CAPACITY = 0, -1, -2, -3, -4, -5, -6, -7
 
 _LOCK = threading.Lock()
 _LIB: Optional[ctypes.CDLL] = None
@@ -154,6 +154,17 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ilb_ledger_stats": (None, [c_vp, llp]),
         "ilb_step_check": (c_int, [c_vp, c_int, llp, ip, ip, ip, ip, c_ll, c_ll]),
         "ilb_step_fits": (c_int, [c_vp, c_int, llp, ip]),
+        "ilb_sched_new": (c_int, [c_vp, c_ll, c_ll, c_ll, c_ll, ctypes.POINTER(c_vp)]),
+        "ilb_sched_free": (None, [c_vp]),
+        "ilb_sched_set_limits": (c_int, [c_vp, c_ll, c_ll, c_ll, c_ll]),
+        "ilb_sched_add": (c_int, [c_vp, c_ll, c_ll, c_ll]),
+        "ilb_sched_plan": (c_int, [c_vp, llp, c_int, ip, llp, ip]),
+        "ilb_sched_token": (c_int, [c_vp, c_ll, c_int]),
+        "ilb_sched_abort": (c_int, [c_vp, c_ll]),
+        "ilb_sched_list": (c_int, [c_vp, c_int, llp, c_int]),
+        "ilb_sched_stats": (None, [c_vp, llp]),
+        "ilb_sched_count_step": (None, [c_vp]),
+        "ilb_sched_preemptions_of": (c_int, [c_vp, c_ll]),
         "ilb_step_decode": (c_ll, [c_vp, c_int, llp, ip, c_int, c_int, c_ll, c_ll, c_vp, c_ll, llp]),
         "ilb_step_commit": (c_int, [c_vp, c_int, llp, ip]),
         "ilb_step_build": (c_ll, [c_vp, c_int, llp, ip, ip, ip, ip, c_int, c_int, c_ll, c_ll, c_vp, c_ll, llp]),

@@ -105,12 +105,12 @@ struct Json {
         case 'r': out += '\r'; break;
         case 't': out += '\t'; break;
         case 'u': {
-          uint32_t cp;
+          uint32_t cp = 0;
           if (!hex4(cp)) return false;
           if (cp >= 0xD800 && cp < 0xDC00) {            // a surrogate pair
             if (end - p < 6 || p[0] != '\\' || p[1] != 'u') return fail_at("lone surrogate");
             p += 2;
-            uint32_t lo;
+            uint32_t lo = 0;
             if (!hex4(lo)) return false;
             if (lo < 0xDC00 || lo > 0xDFFF) return fail_at("bad surrogate pair");
             cp = 0x10000 + ((cp - 0xD800) << 10) + (lo - 0xDC00);
@@ -871,5 +871,286 @@ ILB_API int ilb_step_commit(void* h, int n, const long long* req, const int* n_t
     const int rc = l->commit(req[i], it->second + n_tok[i]);
     if (rc) return rc;
   }
+  return kOk;
+}
+
+// ------------------------------------------------------------------ the scheduler
+// Continuous batching above the step function: each plan() builds ONE step under a token
+// budget and a sequence cap.  Decoding requests bring one token each (oldest first; one that
+// cannot get its next page preempts the youngest running request that is not yet in the plan,
+// by recompute: pages and slot returned, back to the head of the waiting queue); then prompt
+// portions of running requests, then new arrivals first come first served.  A portion is
+// granted whole if the budget funds it, or the remainder if that is at least half a portion
+// (crates/engine/scheduler/src/policy/packing.rs:328-347); what the free pages cannot hold is
+// shrunk to what they can.  Requests are known by the ledger's numbers; token values never
+// come here, only counts.  Reference: crates/engine/scheduler/src/preemption.rs:59-119,
+// crates/engine/runtime/src/pipeline/scheduling/{ready.rs:105-117, preemption.rs:67-76}.
+namespace {
+
+constexpr int kCapacity = -7;
+
+struct SReq { long long prompt_len = 0, generated = 0, max_new = 0, arrival = 0; int preemptions = 0; };
+struct Work { long long id, start, count; int samples; };
+
+struct Sched {
+  Ledger* l;
+  long long max_num_seqs, max_batched, chunk, max_model_len;
+  std::vector<long long> waiting;              // front = index 0
+  std::vector<long long> running;              // admission order
+  std::unordered_map<long long, SReq> reqs;
+  long long arrivals = 0, steps = 0, preemptions = 0, admitted = 0, finished = 0;
+  std::vector<Work> work;
+  std::vector<long long> preempted;
+
+  long long total_len(long long id) const { const SReq& r = reqs.at(id); return r.prompt_len + r.generated; }
+  bool live(long long id) const { return l->length.count(id) != 0; }
+  long long computed(long long id) const { auto it = l->length.find(id); return it == l->length.end() ? 0 : it->second; }
+  bool is_decode(long long id) const { return computed(id) == total_len(id) - 1; }
+  bool planned(long long id) const { for (const Work& w : work) if (w.id == id) return true; return false; }
+  void pages_for(long long id, long long new_len, std::vector<long long>& need) const {
+    need.assign(l->groups.size(), 0);
+    if (live(id)) {
+      std::vector<int> per(l->groups.size() ? l->groups.size() : 1, 0);
+      l->pages_needed(id, new_len, per.data());
+      for (size_t g = 0; g < need.size(); ++g) need[g] = per[g];
+    } else {
+      for (size_t g = 0; g < need.size(); ++g) need[g] = l->blocks_for(new_len);
+    }
+  }
+  void held(long long id, std::vector<long long>& out) const {
+    out.assign(l->groups.size(), 0);
+    if (!live(id)) return;
+    for (size_t g = 0; g < out.size(); ++g)
+      for (int p : l->groups[g].tables.at(id)) out[g] += p >= 0;
+  }
+  void preempt(long long victim) {
+    if (live(victim)) l->release(victim);
+    running.erase(std::find(running.begin(), running.end(), victim));
+    reqs[victim].preemptions += 1;
+    waiting.insert(waiting.begin(), victim);   // it keeps its place ahead of newer arrivals
+    preempted.push_back(victim);
+    ++preemptions;
+  }
+  void fill() {
+    long long budget = max_batched;
+    const size_t G = l->groups.size();
+    std::vector<long long> free_(G), need, hold;
+    for (size_t g = 0; g < G; ++g) free_[g] = (long long)l->groups[g].pool.free_.size();
+    auto fits = [&](const std::vector<long long>& n) { for (size_t g = 0; g < G; ++g) if (n[g] > free_[g]) return false; return true; };
+    auto charge = [&](const std::vector<long long>& n) { for (size_t g = 0; g < G; ++g) free_[g] -= n[g]; };
+    // 1. decoding requests, oldest first; a blocked one preempts the youngest running
+    std::vector<long long> decoders;
+    for (long long id : running) if (is_decode(id)) decoders.push_back(id);
+    for (long long id : decoders) {
+      if (std::find(running.begin(), running.end(), id) == running.end()) continue;   // became a victim meanwhile
+      if (budget <= 0 || (long long)work.size() >= max_num_seqs) break;
+      pages_for(id, total_len(id), need);
+      while (!fits(need)) {
+        long long victim = -1;
+        for (auto it = running.rbegin(); it != running.rend(); ++it)
+          if (*it != id && !planned(*it)) { victim = *it; break; }
+        if (victim < 0) break;
+        held(victim, hold);
+        preempt(victim);
+        for (size_t g = 0; g < G; ++g) free_[g] += hold[g];
+      }
+      if (!fits(need)) continue;               // waits; something else may finish first
+      charge(need);
+      work.push_back({id, total_len(id) - 1, 1, 1});
+      budget -= 1;
+    }
+    // 2. prompt portions: requests already running, then new arrivals in order
+    auto grant = [&](long long id, Work& w) {
+      const long long done = computed(id);
+      const long long portion = std::min(chunk, total_len(id) - done);
+      long long count;
+      if (budget >= portion) count = portion;
+      else if (budget >= 1 && budget * 2 >= portion) count = budget;
+      else return false;
+      pages_for(id, done + count, need);
+      if (!fits(need)) {
+        // take what the free pages can hold, if that is still progress
+        long long room = done + count;
+        if (G > 0) {
+          room = -1;
+          for (size_t g = 0; g < G; ++g) {
+            const long long have = live(id) ? (long long)l->groups[g].tables.at(id).size() : 0;
+            const long long r = (have + free_[g]) * l->page_size;
+            room = room < 0 ? r : std::min(room, r);
+          }
+        }
+        count = std::min(count, room - done);
+        if (count <= 0) return false;
+        pages_for(id, done + count, need);
+        if (!fits(need)) return false;
+      }
+      charge(need);
+      budget -= count;
+      w = {id, done, count, done + count == total_len(id) ? 1 : 0};
+      return true;
+    };
+    const std::vector<long long> snapshot = running;
+    for (long long id : snapshot) {
+      if (planned(id) || is_decode(id)) continue;
+      if (budget <= 0 || (long long)work.size() >= max_num_seqs) break;
+      Work w;
+      if (grant(id, w)) work.push_back(w);
+    }
+    for (;;) {
+      if (waiting.empty() || budget <= 0 || (long long)work.size() >= max_num_seqs || (long long)running.size() >= max_num_seqs) break;
+      long long fresh = 0;
+      for (const Work& w : work) fresh += !live(w.id);
+      if ((long long)l->slots.free_.size() <= fresh) break;
+      const long long id = waiting.front();
+      if (std::find(preempted.begin(), preempted.end(), id) != preempted.end() && !running.empty())
+        break;                                  // a victim of this very step waits for the next one
+      Work w;
+      if (!grant(id, w)) break;                 // first come first served: nobody overtakes the head
+      waiting.erase(waiting.begin());
+      running.push_back(id);
+      ++admitted;
+      work.push_back(w);
+    }
+  }
+  int plan() {
+    work.clear();
+    preempted.clear();
+    for (;;) {
+      fill();
+      if (!work.empty() || running.empty()) break;
+      if (running.size() == 1)
+        return fail(kCapacity, "request #%lld cannot grow: the cache is too small for it alone", running[0]);
+      preempt(running.back());
+    }
+    if (work.empty() && !waiting.empty() && running.empty())
+      return fail(kCapacity, "request #%lld cannot start: the cache is too small for it alone", waiting.front());
+    if (!work.empty()) ++steps;
+    return kOk;
+  }
+};
+
+}  // namespace
+
+ILB_API int ilb_sched_new(void* ledger, long long max_num_seqs, long long max_batched, long long chunk, long long max_model_len,
+                          void** out) {
+  *out = nullptr;
+  if (max_num_seqs <= 0 || max_batched <= 0 || chunk <= 0 || max_model_len <= 0) return fail(kInvalid, "scheduler limits must be positive");
+  Sched* s = new Sched();
+  s->l = static_cast<Ledger*>(ledger);
+  s->max_num_seqs = max_num_seqs; s->max_batched = max_batched; s->chunk = chunk; s->max_model_len = max_model_len;
+  *out = s;
+  return kOk;
+}
+ILB_API void ilb_sched_free(void* h) { delete static_cast<Sched*>(h); }
+
+// A new request: `id` is the ledger's number for it.  `generated` tokens it already has
+// (0 for a fresh one).
+ILB_API int ilb_sched_add(void* h, long long id, long long prompt_len, long long max_new) {
+  Sched* s = static_cast<Sched*>(h);
+  if (max_new <= 0) return fail(kInvalid, "max_new_tokens must be positive");
+  if (prompt_len <= 0) return fail(kInvalid, "empty input");
+  if (std::find(s->waiting.begin(), s->waiting.end(), id) != s->waiting.end() ||
+      std::find(s->running.begin(), s->running.end(), id) != s->running.end())
+    return fail(kInvalid, "request #%lld is already queued", id);
+  const long long total = prompt_len + max_new;
+  if (total > s->max_model_len)
+    // reserved tokens = prompt + max_new_tokens must fit the context (crates/engine/workloads/src/native.rs:91-111)
+    return fail(kInvalid, "request #%lld: prompt %lld + max_new_tokens %lld exceeds max_model_len %lld", id, prompt_len, max_new,
+                s->max_model_len);
+  const long long pages = s->l->blocks_for(total);
+  for (size_t g = 0; g < s->l->groups.size(); ++g) {
+    const Group& grp = s->l->groups[g];
+    long long reach = pages;
+    if (grp.window >= 0) reach = std::min(pages, s->l->blocks_for(grp.window + s->chunk) + 1);
+    if (reach > grp.pool.num_pages)
+      return fail(kCapacity, "request #%lld needs %lld pages of group %zu, the pool has %d", id, reach, g, grp.pool.num_pages);
+  }
+  SReq r;
+  r.prompt_len = prompt_len; r.max_new = max_new; r.arrival = s->arrivals++;
+  s->reqs[id] = r;
+  s->waiting.push_back(id);
+  return kOk;
+}
+
+// One step.  work receives (id, start, count, samples) per entry, preempted the requests that
+// lost their pages (they are waiting again).  Returns 0, or the capacity code when a request
+// cannot run even alone.
+ILB_API int ilb_sched_plan(void* h, long long* work, int cap, int* n_work, long long* preempted, int* n_preempted) {
+  Sched* s = static_cast<Sched*>(h);
+  const int rc = s->plan();
+  // victims are reported whether or not the plan stands: their pages are gone either way
+  *n_preempted = (int)std::min<size_t>(s->preempted.size(), (size_t)cap);
+  for (int i = 0; i < *n_preempted; ++i) preempted[i] = s->preempted[(size_t)i];
+  *n_work = 0;
+  if (rc) return rc;
+  if ((int)s->work.size() > cap) return fail(kInvalid, "the plan has %zu entries, room for %d", s->work.size(), cap);
+  *n_work = (int)s->work.size();
+  for (int i = 0; i < *n_work; ++i) {
+    const Work& w = s->work[(size_t)i];
+    work[4 * i] = w.id; work[4 * i + 1] = w.start; work[4 * i + 2] = w.count; work[4 * i + 3] = w.samples;
+  }
+  return kOk;
+}
+
+// A token was drawn for a running request (`stop`: it is one of its stop tokens).  Returns
+// 0 (goes on), 1 (ended on the stop token) or 2 (ended on a length limit); an ended request's
+// pages and slot are released here.
+ILB_API int ilb_sched_token(void* h, long long id, int stop) {
+  Sched* s = static_cast<Sched*>(h);
+  auto it = s->reqs.find(id);
+  if (it == s->reqs.end() || std::find(s->running.begin(), s->running.end(), id) == s->running.end())
+    return fail(kInvalid, "request #%lld is not running", id);
+  SReq& r = it->second;
+  r.generated += 1;
+  int reason = 0;
+  if (stop) reason = 1;
+  else if (r.generated >= r.max_new) reason = 2;
+  else if (r.prompt_len + r.generated >= s->max_model_len) reason = 2;
+  if (reason) {
+    s->running.erase(std::find(s->running.begin(), s->running.end(), id));
+    if (s->live(id)) s->l->release(id);
+    s->reqs.erase(it);
+    ++s->finished;
+  }
+  return reason;
+}
+
+// Returns 1 if the request was known (running or waiting) and is now gone, 0 otherwise.
+ILB_API int ilb_sched_abort(void* h, long long id) {
+  Sched* s = static_cast<Sched*>(h);
+  auto r = std::find(s->running.begin(), s->running.end(), id);
+  if (r != s->running.end()) {
+    s->running.erase(r);
+    if (s->live(id)) s->l->release(id);
+    s->reqs.erase(id);
+    return 1;
+  }
+  auto w = std::find(s->waiting.begin(), s->waiting.end(), id);
+  if (w != s->waiting.end()) { s->waiting.erase(w); s->reqs.erase(id); return 1; }
+  return 0;
+}
+
+// which: 0 waiting, 1 running.  Copies up to cap ids in order; returns how many there are.
+ILB_API int ilb_sched_list(void* h, int which, long long* out, int cap) {
+  Sched* s = static_cast<Sched*>(h);
+  const std::vector<long long>& v = which == 0 ? s->waiting : s->running;
+  for (size_t i = 0; i < v.size() && (int)i < cap; ++i) out[i] = v[i];
+  return (int)v.size();
+}
+ILB_API void ilb_sched_stats(void* h, long long* out) {
+  Sched* s = static_cast<Sched*>(h);
+  out[0] = s->steps; out[1] = s->preemptions; out[2] = s->admitted; out[3] = s->finished;
+  out[4] = (long long)s->waiting.size(); out[5] = (long long)s->running.size();
+}
+ILB_API void ilb_sched_count_step(void* h) { static_cast<Sched*>(h)->steps += 1; }
+ILB_API int ilb_sched_preemptions_of(void* h, long long id) {
+  Sched* s = static_cast<Sched*>(h);
+  auto it = s->reqs.find(id);
+  return it == s->reqs.end() ? 0 : it->second.preemptions;
+}
+ILB_API int ilb_sched_set_limits(void* h, long long max_num_seqs, long long max_batched, long long chunk, long long max_model_len) {
+  if (max_num_seqs <= 0 || max_batched <= 0 || chunk <= 0 || max_model_len <= 0) return fail(kInvalid, "scheduler limits must be positive");
+  Sched* s = static_cast<Sched*>(h);
+  s->max_num_seqs = max_num_seqs; s->max_batched = max_batched; s->chunk = chunk; s->max_model_len = max_model_len;
   return kOk;
 }
