@@ -136,7 +136,7 @@ def main() -> int:
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
-                          "pip: '/root/reference is not installable: neither setup.py nor pyproject.toml found' (a Rust workspace; no cargo/rustc "
+                          "pip: the reference checkout 'is not installable: neither setup.py nor pyproject.toml found' (a Rust workspace; no cargo/rustc "
                           "on this machine; it has no Python API)"}))
         return 0
     if args.gpus != 1:

@@ -252,12 +252,12 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
   const int n_my = rank < n_tiles ? (n_tiles - rank + kSplit - 1) / kSplit : 0;
   const int* table = p.block_table + (size_t)seq * p.max_blocks;
   const int rows16 = (G + 15) / 16 * 16;
-  const int n_rounds = rows16 / 16;
+  const int n_passes = rows16 / 16;
   auto key_of = [&](int j) { return (first_tile + rank + j * kSplit) * kKeys; };
 
-  for (int round = 0; round < n_rounds; ++round) {         // 16 query heads of the group at a time
-    const int rb = round * 16;
-    const int it0 = round * n_my;                          // tiles this CTA has streamed before this round
+  for (int pass = 0; pass < n_passes; ++pass) {            // 16 query heads of the group at a time
+    const int rb = pass * 16;
+    const int it0 = pass * n_my;                           // tiles this CTA has streamed in earlier passes
     if (warp == kConsumers) {
       // ------------------------------------------------------------ producer
       const int box_keys = p.page_size < kKeys ? p.page_size : kKeys;
@@ -395,7 +395,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
       p.out[(size_t)tok * p.out_stride + (size_t)(kvh * G + rb + row) * D + c] = __float2bfloat16_rn(l_all > 0.f ? o / l_all : 0.f);
     }
     cluster_sync_all();                                    // the records stay until every peer has read them
-    // the next round's TMA writes land where ordinary stores and loads have just been
+    // the next pass's TMA writes land where ordinary stores and loads have just been
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
 }

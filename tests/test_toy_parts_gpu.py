@@ -1,0 +1,184 @@
+"""Two more toy parts, defined HERE and registered without a change to the framework's files
+(GPU): a feed-forward that routes every token to one of three small experts, and a position
+encoding other than the architecture's (rotary angles of positions divided by a factor).
+
+The toy architecture alternates them layer by layer: layer 0 has the stock attention with the
+stock rotary encoding and the routed feed-forward, layer 1 the stock attention with the scaled
+encoding and the stock SwiGLU.  Whole prompts, portions and single tokens must agree with the
+plain 64-bit statement of the same model.
+"""
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from helpers import random_tokens
+from inferloop_b200.config import Architecture, ArchitectureRegistry, LayerSpec, ModelSpec, PartSpec, RunEntry
+from inferloop_b200.parts import FeedForward, PositionEncoding, register, unregister
+from inferloop_b200.weights.decl import WeightDecl
+
+pytestmark = pytest.mark.gpu
+
+H, V, E, I = 48, 131, 3, 40
+
+
+class RoutedFeedForward(FeedForward):
+    """Router logits in 32-bit from the normed input; the best expert alone runs (ties to the
+    lower index); its output, scaled by its softmax weight among all experts, is added to the
+    residual.  Each expert is y = W2 relu(W1 x)."""
+
+    def __init__(self, spec, ctx, prefix=""):
+        super().__init__(spec, ctx, prefix)
+        self.hidden, self.experts, self.inter = int(spec["hidden_size"]), int(spec["experts"]), int(spec["inter"])
+        self.p = prefix
+
+    def declare_weights(self):
+        out = [WeightDecl(self.p + "router.weight", (self.experts, self.hidden))]
+        for e in range(self.experts):
+            out += [WeightDecl(f"{self.p}experts.{e}.w1.weight", (self.inter, self.hidden)),
+                    WeightDecl(f"{self.p}experts.{e}.w2.weight", (self.hidden, self.inter))]
+        return out
+
+    def bind(self, tensors):
+        self.router = tensors[self.p + "router.weight"].float()
+        self.w1 = [tensors[f"{self.p}experts.{e}.w1.weight"].float() for e in range(self.experts)]
+        self.w2 = [tensors[f"{self.p}experts.{e}.w2.weight"].float() for e in range(self.experts)]
+
+    def forward(self, x, residual, step):
+        xf = x.float()
+        logits = xf @ self.router.T                       # [T, E], 32-bit
+        weight = torch.softmax(logits, dim=-1)
+        choice = logits.argmax(dim=-1)
+        for e in range(self.experts):
+            rows = torch.nonzero(choice == e).flatten()
+            if rows.numel():
+                y = torch.relu(xf[rows] @ self.w1[e].T) @ self.w2[e].T
+                residual[rows] += y * weight[rows, e:e + 1]
+
+
+class ScaledRope(PositionEncoding):
+    """The stock table format ([T, rd/2, 2] cos/sin), but of positions divided by `factor`."""
+
+    def __init__(self, spec, ctx, prefix=""):
+        super().__init__(spec, ctx, prefix)
+        self.theta, self.rd, self.factor = float(spec["theta"]), int(spec["rotary_dim"]), float(spec["factor"])
+
+    def table(self, step):
+        key = ("scaled_rope", self.theta, self.rd, self.factor)
+        t = step.position_tables.get(key)
+        if t is None:
+            half = self.rd // 2
+            inv = torch.tensor([self.theta ** (-(2.0 * i) / self.rd) for i in range(half)], dtype=torch.float64,
+                               device=step.positions.device)
+            ang = step.positions.double()[:, None] / self.factor * inv[None, :]
+            t = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).float().contiguous()
+            step.position_tables[key] = t
+        return t
+
+
+def toy_spec(cfg):
+    norm = PartSpec.make("rms", eps=cfg["eps"])
+
+    def attn(position):
+        return PartSpec.make("gqa_attention", hidden_size=H, num_heads=3, num_kv_heads=3, head_dim=16, qk_norm=True,
+                             qk_norm_eps=cfg["eps"], bias=False, window=None, position=position)
+
+    rope = PartSpec.make("rope_neox", theta=1e4, rotary_dim=16, head_dim=16)
+    scaled = PartSpec.make("scaled_rope", theta=1e4, rotary_dim=16, head_dim=16, factor=cfg["factor"])
+    routed = PartSpec.make("routed_relu", hidden_size=H, experts=E, inter=I)
+    dense = PartSpec.make("swiglu", hidden_size=H, intermediate_size=64)
+    block = PartSpec.make("pre_norm", hidden_size=H)
+    layers = (LayerSpec("layers.0.", block, attn(rope), routed, norm), LayerSpec("layers.1.", block, attn(scaled), dense, norm))
+    return ModelSpec("Toy2ForCausalLM", V, H, 512, "embed_tokens.weight", "lm_head.weight", "norm.weight", norm,
+                     layers, run_order=(RunEntry(0, 0), RunEntry(1, 1)), weight_prefixes=("model.",))
+
+
+def plain_toy(w, cfg, tokens):
+    T = len(tokens)
+    x = w["embed_tokens.weight"][torch.tensor(tokens)]
+    pos = torch.arange(T)
+    acfg = dict(num_attention_heads=3, num_key_value_heads=3, head_dim=16, attention_bias=False,
+                rms_norm_eps=cfg["eps"], partial_rotary_factor=1.0, rope_theta=1e4)
+    # layer 0: stock attention, routed feed-forward
+    p = "layers.0."
+    n = plain.rms_norm(x, w[p + "input_layernorm.weight"], cfg["eps"])
+    x = x + plain.attention_block(n, w, p + "self_attn.", acfg, pos, None)
+    n = plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg["eps"])
+    logits = n @ w[p + "mlp.router.weight"].T
+    weight = torch.softmax(logits, dim=-1)
+    top2 = logits.topk(2, dim=-1).values
+    margin = (top2[:, 0] - top2[:, 1]) / logits.abs().max()      # how decided each token's routing is
+    for t in range(T):
+        e = int(logits[t].argmax())
+        y = torch.relu(n[t] @ w[f"{p}mlp.experts.{e}.w1.weight"].T) @ w[f"{p}mlp.experts.{e}.w2.weight"].T
+        x[t] = x[t] + y * weight[t, e]
+    # layer 1: attention with positions divided by the factor, stock SwiGLU
+    p = "layers.1."
+    a = p + "self_attn."
+    n = plain.rms_norm(x, w[p + "input_layernorm.weight"], cfg["eps"])
+    scaled = pos.double() / cfg["factor"]
+    q = plain.rope_neox(plain.rms_norm(plain.linear(n, w[a + "q_proj.weight"]).view(T, 3, 16), w[a + "q_norm.weight"], cfg["eps"]), scaled, 1e4, 16)
+    k = plain.rope_neox(plain.rms_norm(plain.linear(n, w[a + "k_proj.weight"]).view(T, 3, 16), w[a + "k_norm.weight"], cfg["eps"]), scaled, 1e4, 16)
+    v = plain.linear(n, w[a + "v_proj.weight"]).view(T, 3, 16)
+    o = plain.causal_attention(q, k, v, pos, None).reshape(T, 48)
+    x = x + plain.linear(o, w[a + "o_proj.weight"])
+    n = plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg["eps"])
+    x = x + plain.swiglu_mlp(n, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    return plain.linear(plain.rms_norm(x, w["norm.weight"], cfg["eps"]), w["lm_head.weight"]), margin
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_routed_feed_forward_and_another_position_encoding(dtype):
+    from inferloop_b200.engine import ModelRunner, StepEntry
+    from inferloop_b200.models.decoder import declare_weights
+    from inferloop_b200.weights import random_tensor, target_dtype
+    register("feed_forward", "routed_relu", RoutedFeedForward)
+    register("position", "scaled_rope", ScaledRope)
+    try:
+        registry = ArchitectureRegistry()
+        registry.register(Architecture("toy2", ("Toy2ForCausalLM",), dict, toy_spec))
+        cfg = {"architectures": ["Toy2ForCausalLM"], "eps": 1e-6, "factor": 4.0}
+        runner = ModelRunner.from_config(cfg, seed=9, dtype=dtype, page_size=8, num_pages=32, max_requests=3,
+                                         registry=registry)
+        assert runner.graphs is None          # the toy parts read the batch on the host: no replayed graphs
+        DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+        w = {d.name: random_tensor(d, 9, target_dtype(d.role, DT), "cuda").double().cpu() for d in declare_weights(toy_spec(cfg))}
+        toks = {"a": random_tokens(50, V, 11), "b": random_tokens(37, V, 12)}
+        both = {rid: plain_toy(w, cfg, t) for rid, t in toks.items()}
+        ref = {rid: b[0] for rid, b in both.items()}
+        margin = {rid: b[1] for rid, b in both.items()}
+        # a whole, b in portions beside a's decode steps
+        got = {"a": [], "b": []}
+        got["a"].append(runner.step([StepEntry("a", toks["a"][:30], list(range(30)))]).double().cpu().clone())
+        ia, ib = 30, 0
+        for cut in (5, 2, 11, 1, 18):
+            entries = [StepEntry("b", toks["b"][ib:ib + cut], list(range(cut)))]
+            if ia < 50:
+                entries.insert(0, StepEntry("a", [toks["a"][ia]], [0]))
+            out = runner.step(entries).double().cpu().clone()
+            if ia < 50:
+                got["a"].append(out[:1]); out = out[1:]; ia += 1
+            got["b"].append(out)
+            ib += cut
+        while ia < 50:
+            got["a"].append(runner.step([StepEntry("a", [toks["a"][ia]], [0])]).double().cpu().clone())
+            ia += 1
+        for rid in toks:
+            runner.end(rid)
+            g = torch.cat(got[rid])
+            assert g.shape == ref[rid].shape and torch.isfinite(g).all()
+            err = (g - ref[rid]).abs()
+            if dtype == "float32":
+                assert (err <= 1e-5 + 1e-5 * ref[rid].abs()).all(), (rid, err.max().item())
+            else:
+                # in bfloat16 a router logit within rounding of the best may pick the other
+                # expert, and every later token (which attends to that one) then differs for a
+                # reason that is no fault: rows are compared up to the first token whose plain
+                # routing margin is below 0.5 % of the largest router logit (bfloat16 keeps 8 bits)
+                close = (margin[rid] < 0.005).nonzero()
+                upto = int(close[0]) if close.numel() else len(margin[rid])
+                assert upto >= 5, "the seed gives no decided prefix to compare"
+                lim = 3e-2 * float(ref[rid].abs().max())
+                assert (err[:upto] <= lim).all(), (rid, upto, err[:upto].max().item())
+    finally:
+        unregister("feed_forward", "routed_relu")
+        unregister("position", "scaled_rope")
