@@ -332,6 +332,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       }
       if (!ok) { flags[0] = 1; if (p.error_flag) *p.error_flag = 1; }
     }
+    if (!SWAP && p.cluster > 1) cluster_sync_all();          // the epilogue warps meet the cluster; so must every thread
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
@@ -370,6 +371,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         tcgen05_commit(tfull0); tcgen05_commit(tfull0 + 8);       // let the epilogue leave its wait
       }
     }
+    if (!SWAP && p.cluster > 1) cluster_sync_all();
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5, and 6..9 for the second row block)
     pdl_wait();                               // outputs, shares and tickets belong to earlier kernels until now
@@ -379,6 +381,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     constexpr int CH = BN < 32 ? BN : 32;     // columns per tensor-memory read
     uint32_t seg = 0;
     bool failed = false;
+    bool met_cluster = false;                 // many-token form with a cluster: every thread meets it exactly once
     Segments segs(p, sch, blockIdx.x, gridDim.x);
     long long tile, tile_first;
     int kb0, cnt;
@@ -390,6 +393,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       tcgen05_fence_after();
       failed = flags[0] != 0;
       if (failed) break;
+      int col_lo = 0, col_hi = BN;             // columns this CTA writes out
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (MS == 1 ? b : (uint32_t)ms) * kAccCols;
       const bool whole = cnt == p.k_blocks;
       bool last = whole;
@@ -420,6 +424,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         c_first = sch.cta_of(tile_first);
         c_last = sch.cta_of(tile_first + p.k_blocks - 1);
         __threadfence();
+        if (!SWAP && p.cluster > 1) {
+          // The sharers of this tile are the CTAs of this cluster and all of them are here:
+          // after the barrier every CTA adds the shares of ITS columns (in K order) and writes
+          // them out, instead of one CTA doing the whole tile behind a ticket.
+          cluster_sync_all();
+          met_cluster = true;
+          const int per = BN / p.cluster;
+          col_lo = (int)cluster_rank() * per;
+          col_hi = col_lo + per;
+          last = true;
+        } else {
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
         if (threadIdx.x == 64) {
           const int t = atomicAdd(p.tickets + tile, 1);
@@ -431,6 +446,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         last = flags[1] != 0;
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");        // flags[1] is reused by the next segment
         if (last) __threadfence();
+        }
       }
       if (last) {
         // values of columns c0 .. c0 + CH of this thread's row: from the accumulator, or the
@@ -491,7 +507,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             }
           } else {
             // columns come in blocks of 64 gate then 64 up; a thread holds both halves
-            for (int cb = 0; cb < BN; cb += 128) {
+            for (int cb = col_lo; cb < col_hi; cb += 128) {
               for (int c0 = cb; c0 < cb + 64; c0 += CH) {
                 float g[32], u[32];
                 fetch(c0, g);
@@ -529,7 +545,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             }
           }
         } else
-        for (int c0 = 0; c0 < BN; c0 += CH) {
+        for (int c0 = col_lo; c0 < col_hi; c0 += CH) {
           float v[32];
           fetch(c0, v);
           if (SWAP) {
@@ -619,6 +635,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
       }
     }
+    if (!SWAP && p.cluster > 1 && !met_cluster) cluster_sync_all();   // a thread that gave up still meets its peers
   }
   if (SWAP && p.cluster > 1) {
     // The S CTAs of a cluster hold the S consecutive K ranges of one tile.  CTA r adds, in the
@@ -862,15 +879,25 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   } else {
     // Many tokens: the tile shape that keeps the most SMs busy in whole rounds, larger tiles
     // counting for more because they move fewer bytes per flop.
+    // Few tiles are cut into equal K ranges; with one 128-row block per tile the ranges of a
+    // tile run as a cluster that shares the write-out, with two they go through a ticket.
     const struct { int ms, bn; double worth; } shapes[4] = {{2, 256, 1.0}, {2, 192, 0.93}, {1, 256, 0.85}, {1, 128, 0.7}};
+    const long long kb = (K + kBlockK - 1) / kBlockK;
     double best = -1.0;
     bn = 128;
     for (const auto& c : shapes) {
       if (c.bn > 128 && N < 256) continue;
       if (c.bn % 128 != 0 && accumulate == 2) continue;        // the SwiGLU epilogue pairs 64-column blocks
       const long long t = (long long)((M + c.ms * kTileX - 1) / (c.ms * kTileX)) * ((N + c.bn - 1) / c.bn);
-      const long long rounds = (t + sm_count() - 1) / sm_count();
-      const double score = (double)t / (double)(rounds * sm_count()) * c.worth;
+      double score;
+      if (t * 2 <= sm_count()) {
+        long long split = 1;
+        while (split < 8 && t * split * 2 <= sm_count() && split * 2 <= kb) split *= 2;
+        score = (double)(t * split) / sm_count() * c.worth * (c.ms == 1 ? 0.9 : 0.6);
+      } else {
+        const long long rounds = (t + sm_count() - 1) / sm_count();
+        score = (double)t / (double)(rounds * sm_count()) * c.worth;
+      }
       if (score > best) { best = score; bn = c.bn; ms = c.ms; }
     }
   }
@@ -907,9 +934,16 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
     // every tile is cut into the same number of K ranges instead.
     const long long sms = sm_count();
     if (tiles * 2 <= sms) {
-      long long split = sms / tiles;
-      if (split > 8) split = 8;
-      if (split > p.k_blocks) split = p.k_blocks;
+      long long split = 1;
+      while (split < 8 && tiles * split * 2 <= sms && split * 2 <= p.k_blocks) split *= 2;
+      if (ms == 1 && split > 1) {
+        // the K ranges of a tile as one cluster (all resident, or a second round costs more than it saves)
+        while (split > 1 && (bn == 256 ? active_clusters<256, 4, false>((int)split) : active_clusters<128, 6, false>((int)split)) < tiles)
+          split /= 2;
+        while (split > 1 && bn / split < 32) split /= 2;        // a CTA writes out whole 32-column chunks
+        if (accumulate == 2) while (split > 1 && (bn / split) % 128 != 0) split /= 2;   // SwiGLU pairs 64-column blocks
+        p.cluster = (int)split;
+      }
       grid = tiles * split;
       p.dp_waves = 0;
       p.sk_tile0 = 0;
@@ -927,6 +961,7 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
     p.sk_tile0 = (long long)p.dp_waves * grid;
   }
   p.units = (tiles - p.sk_tile0) * p.k_blocks;
+  ILB_REQUIRE(swap || p.cluster == 1 || (bn / p.cluster) % 32 == 0, "gemm_tc: %d columns do not divide among %d CTAs", bn, p.cluster);
   ILB_REQUIRE(2 * grid * ms * bn * kTileX <= workspace_floats, "gemm_tc: workspace too small");
 
   CUtensorMap mx, my;

@@ -290,7 +290,11 @@ def test_kernels_refuse_what_they_cannot_do():
 # (256, 19200, 64) and (300, 9728, 128): one whole-tile round, then 2 tiles of 1-2 K blocks
 # shared by far fewer CTAs than the grid holds
 TC_SHAPES = [(256, 19200, 64), (300, 9728, 128), (1, 128, 64), (3, 200, 72), (8, 512, 4096), (16, 4096, 1024), (17, 300, 136), (33, 96, 512),
-             (64, 1000, 1024), (65, 256, 256), (128, 384, 320), (129, 520, 264), (300, 515 * 1 + 5, 96), (512, 1024, 2048)]
+             (64, 1000, 1024), (65, 256, 256), (128, 384, 320), (129, 520, 264), (300, 515 * 1 + 5, 96), (512, 1024, 2048),
+             # few tiles of many tokens: the K ranges of a tile run as a cluster that shares the write-out
+             (200, 700, 1024), (129, 256, 1024), (256, 4096, 1024), (500, 1100, 4096), (1024, 520, 512),
+             # 256 x 192 and 256 x 256 tiles in whole rounds, a last round that is not full
+             (2048, 6144, 256), (1500, 4100, 192)]
 
 
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)
