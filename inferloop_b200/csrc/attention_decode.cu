@@ -109,6 +109,14 @@ struct Params {
   int max_blocks, n_seqs, nq, nkv, window, q_stride, out_stride, page_size, num_pages;
   int split;                           // CTAs of a cluster = ways a sequence's tiles are dealt out
   float scale_log2;
+  // Fused input stage (qkv != null): q, k, v of the step's token are taken from the fused
+  // projection output; per-head RMSNorm (weights may be null) and the rotation (table may be
+  // null) are applied here, the new key and value are written to the cache (unless the caches
+  // to write are null) and patched into the tile that holds their position.
+  const __nv_bfloat16* qkv; int qkv_stride;
+  const float* q_weight; const float* k_weight; float eps;
+  const float2* rope;                  // [tokens][D / 2] (cos, sin), rotation over the whole head
+  __nv_bfloat16* k_write; __nv_bfloat16* v_write;
 };
 
 // Address of the 16-byte piece `chunk` (0..7) of row `row` in a [rows][128 bytes] slice
@@ -208,6 +216,118 @@ __device__ __forceinline__ void tile_step(RowState<D>& st, const uint32_t (&q)[D
     mma_16816(st.o[2 * nd], a, r0, r1);
     mma_16816(st.o[2 * nd + 1], a, r2, r3);
   }
+}
+
+// Rows g and g + 8 of the warp's query heads from the fused projection output, as A
+// fragments: per-head RMSNorm in 32-bit (sum over the row's four threads), then the rotation
+// of pairs (i, i + D/2), which a thread holds both members of; rounded to bfloat16 once.
+template <int D>
+__device__ __forceinline__ void load_q_fused(uint32_t (&q)[D / 16][4], const __nv_bfloat16* row0, const __nv_bfloat16* row1,
+                                             const float* weight, float eps, const float2* cs, int lane) {
+  const int t = lane & 3;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const __nv_bfloat16* row = r == 0 ? row0 : row1;
+    float x[D / 16][4];                                  // [kk][c, c+1, c+8, c+9], c = 16 kk + 2 t
+    float ss = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      const int c = kk * 16 + 2 * t;
+      __nv_bfloat162 a = __floats2bfloat162_rn(0.f, 0.f), b = a;
+      if (row) {
+        a = *reinterpret_cast<const __nv_bfloat162*>(row + c);
+        b = *reinterpret_cast<const __nv_bfloat162*>(row + c + 8);
+      }
+      x[kk][0] = __low2float(a); x[kk][1] = __high2float(a); x[kk][2] = __low2float(b); x[kk][3] = __high2float(b);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) ss = fmaf(x[kk][e], x[kk][e], ss);
+    }
+    if (weight != nullptr) {
+      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+      const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const int c = kk * 16 + 2 * t;
+        x[kk][0] = x[kk][0] * inv * __ldg(weight + c);     x[kk][1] = x[kk][1] * inv * __ldg(weight + c + 1);
+        x[kk][2] = x[kk][2] * inv * __ldg(weight + c + 8); x[kk][3] = x[kk][3] * inv * __ldg(weight + c + 9);
+      }
+    }
+    if (cs != nullptr) {
+#pragma unroll
+      for (int kk = 0; kk < D / 32; ++kk) {                // column i < D/2 pairs with i + D/2 = block kk + D/32
+        const int c = kk * 16 + 2 * t;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = c + (e & 1) + (e >> 1) * 8;
+          const float2 w = __ldg(cs + i);
+          const float a = x[kk][e], b = x[kk + D / 32][e];
+          // products and sums rounded separately, as the reference's scalar code does
+          x[kk][e] = __fsub_rn(__fmul_rn(a, w.x), __fmul_rn(b, w.y));
+          x[kk + D / 32][e] = __fadd_rn(__fmul_rn(a, w.y), __fmul_rn(b, w.x));
+        }
+      }
+    }
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      q[kk][r] = row ? pack_bf16(x[kk][0], x[kk][1]) : 0u;
+      q[kk][2 + r] = row ? pack_bf16(x[kk][2], x[kk][3]) : 0u;
+    }
+  }
+}
+
+// The step's own key and value (row `r` of a tile whose K slices start at `ks`, V slices at
+// `vs`): normed and rotated key, raw value, written over what TMA brought for that row, and
+// to the cache at `k_dst` / `v_dst` if those are not null.  Lane l holds elements
+// E l .. E l + E - 1 of each half of the head (E = D / 64), the members of its rotation pairs.
+template <int D>
+__device__ __forceinline__ void patch_new_key(uint32_t ks, uint32_t vs, int r, const __nv_bfloat16* k_src,
+                                              const __nv_bfloat16* v_src, const float* k_weight, float eps, const float2* cs,
+                                              __nv_bfloat16* k_dst, __nv_bfloat16* v_dst, int lane) {
+  constexpr int E = D / 64;
+  constexpr uint32_t kSlice = kKeys * 128;
+  float k[2][E], v[2][E];
+  float ss = 0.f;
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      const int e = h * (D / 2) + E * lane + i;
+      k[h][i] = __bfloat162float(k_src[e]);
+      v[h][i] = __bfloat162float(v_src[e]);
+      ss = fmaf(k[h][i], k[h][i], ss);
+    }
+  if (k_weight != nullptr) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int i = 0; i < E; ++i) k[h][i] = k[h][i] * inv * __ldg(k_weight + h * (D / 2) + E * lane + i);
+  }
+  if (cs != nullptr) {
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      const float2 w = __ldg(cs + E * lane + i);
+      const float a = k[0][i], b = k[1][i];
+      k[0][i] = __fsub_rn(__fmul_rn(a, w.x), __fmul_rn(b, w.y));
+      k[1][i] = __fadd_rn(__fmul_rn(a, w.y), __fmul_rn(b, w.x));
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      const int e = h * (D / 2) + E * lane + i;
+      const __nv_bfloat16 kb = __float2bfloat16_rn(k[h][i]), vb = __float2bfloat16_rn(v[h][i]);
+      const uint32_t off = (uint32_t)(e >> 6) * kSlice + (uint32_t)r * 128u +
+                           (uint32_t)(((((e & 63) * 2) >> 4) ^ (r & 7)) << 4) + (uint32_t)(((e & 63) * 2) & 15);
+      asm volatile("st.shared.b16 [%0], %1;" ::"r"(ks + off), "h"(*reinterpret_cast<const unsigned short*>(&kb)) : "memory");
+      asm volatile("st.shared.b16 [%0], %1;" ::"r"(vs + off), "h"(*reinterpret_cast<const unsigned short*>(&vb)) : "memory");
+      if (k_dst != nullptr) { k_dst[e] = kb; v_dst[e] = vb; }
+    }
+  __syncwarp();
 }
 
 template <int D, int kStages>
@@ -319,7 +439,11 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
       uint32_t q[D / 16][4];
 #pragma unroll
       for (int r = 0; r < 2; ++r) live[r] = rb + g + 8 * r < G;
-      {
+      if (p.qkv != nullptr) {
+        const __nv_bfloat16* base_q = p.qkv + (size_t)tok * p.qkv_stride + (size_t)(kvh * G + rb) * D;
+        load_q_fused<D>(q, live[0] ? base_q + (size_t)g * D : nullptr, live[1] ? base_q + (size_t)(g + 8) * D : nullptr,
+                        p.q_weight, p.eps, p.rope ? p.rope + (size_t)tok * (D / 2) : nullptr, lane);
+      } else {
         const __nv_bfloat16* row0 = live[0] ? p.q + (size_t)tok * p.q_stride + (size_t)(kvh * G + rb + g) * D : nullptr;
         const __nv_bfloat16* row1 = live[1] ? p.q + (size_t)tok * p.q_stride + (size_t)(kvh * G + rb + g + 8) * D : nullptr;
 #pragma unroll
@@ -337,6 +461,21 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         ok = mbar_wait(full0 + 8 * s, (it / kStages) & 1);
         if (!ok) break;
         const int key0 = key_of(j) + warp * 16;
+        if (p.qkv != nullptr && p.k_write != nullptr && pos >= key0 && pos < key0 + 16) {
+          // this warp's slice of this tile holds the step's own position: its key and value
+          // are not in the cache yet (the tile came with whatever the page held there)
+          const __nv_bfloat16* row = p.qkv + (size_t)tok * p.qkv_stride;
+          const int blk = pos / p.page_size;
+          const int pg = blk < p.max_blocks ? __ldg(table + blk) : -1;
+          const bool store = pass == 0 && pg >= 0 && pg < p.num_pages;     // never write outside the pool
+          const size_t at = store ? (((size_t)pg * p.nkv + kvh) * p.page_size + (pos % p.page_size)) * D : 0;
+          patch_new_key<D>(base + s * kStage, base + s * kStage + kTensor, pos % kKeys,
+                           row + (size_t)(p.nq + kvh) * D, row + (size_t)(p.nq + p.nkv + kvh) * D, p.k_weight, p.eps,
+                           p.rope ? p.rope + (size_t)tok * (D / 2) : nullptr, store ? p.k_write + at : nullptr,
+                           store ? p.v_write + at : nullptr, lane);
+          // TMA will write this stage again later: order these ordinary stores before it
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
         if (key0 < hi)
           tile_step<D>(st, q, base + s * kStage, base + s * kStage + kTensor, warp * 16, key0, live, lo, hi, p.scale_log2, lane);
         __syncwarp();
@@ -524,26 +663,66 @@ ILB_EXPORT int ilb_attention_decode_tma_supported(int nq, int nkv, int d, int pa
   return ((d == 64 || d == 128) && (page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128)) ? 1 : 0;
 }
 
-ILB_EXPORT int ilb_attention_decode_tma(const void* q, void* out, const void* k_cache, const void* v_cache,
-                                        const int* positions, const int* cu_q, const int* block_table,
-                                        int max_blocks, int page_size, int num_pages, int window, float scale,
-                                        int n_seqs, int nq, int nkv, int d, int q_stride, int out_stride,
-                                        int* error_flag, cudaStream_t stream) {
+namespace {
+int decode_common(const void* q, const void* qkv, int qkv_stride, const float* q_weight, const float* k_weight, float eps,
+                  const float* rope, int write_kv, void* out, const void* k_cache, const void* v_cache, const int* positions,
+                  const int* cu_q, const int* block_table, int max_blocks, int page_size, int num_pages, int window,
+                  float scale, int n_seqs, int nq, int nkv, int d, int q_stride, int out_stride, int* error_flag,
+                  cudaStream_t stream) {
   ILB_REQUIRE(ilb_attention_decode_tma_supported(nq, nkv, d, page_size),
               "attention decode: heads %d/%d, head size %d, page size %d are not built", nq, nkv, d, page_size);
   ILB_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && nkv <= 65535 && max_blocks > 0 && num_pages > 0 && window >= 0,
               "attention decode: bad sizes");
-  ILB_REQUIRE(q_stride % 2 == 0 && ((uintptr_t)q % 4 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0),
-              "attention decode: misaligned operands");
+  ILB_REQUIRE(((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0), "attention decode: misaligned cache");
+  if (qkv != nullptr)
+    ILB_REQUIRE(qkv_stride % 2 == 0 && qkv_stride >= (nq + 2 * nkv) * d && ((uintptr_t)qkv % 4 == 0) &&
+                ((uintptr_t)rope % 8 == 0) && eps > 0.f, "attention decode: bad fused inputs");
+  else
+    ILB_REQUIRE(q_stride % 2 == 0 && ((uintptr_t)q % 4 == 0), "attention decode: misaligned operands");
   CUtensorMap m[4];                      // K, V, and the same with boxes of two pages
   const int run = page_size < kKeys ? kKeys / page_size : 1;
   if (cache_map(&m[0], k_cache, d, page_size, nkv, num_pages, 1)) return -1;
   if (cache_map(&m[1], v_cache, d, page_size, nkv, num_pages, 1)) return -1;
   if (cache_map(&m[2], k_cache, d, page_size, nkv, num_pages, run)) return -1;
   if (cache_map(&m[3], v_cache, d, page_size, nkv, num_pages, run)) return -1;
-  Params p{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, positions, cu_q, block_table, error_flag,
-           max_blocks, n_seqs, nq, nkv, window, q_stride, out_stride, page_size, num_pages, 1, scale * kLog2e};
+  Params p{};
+  p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out;
+  p.positions = positions; p.cu_q = cu_q; p.block_table = block_table; p.error_flag = error_flag;
+  p.max_blocks = max_blocks; p.n_seqs = n_seqs; p.nq = nq; p.nkv = nkv; p.window = window;
+  p.q_stride = q_stride; p.out_stride = out_stride; p.page_size = page_size; p.num_pages = num_pages;
+  p.split = 1; p.scale_log2 = scale * kLog2e;
+  p.qkv = (const __nv_bfloat16*)qkv; p.qkv_stride = qkv_stride; p.q_weight = q_weight; p.k_weight = k_weight; p.eps = eps;
+  p.rope = (const float2*)rope;
+  p.k_write = (qkv != nullptr && write_kv) ? (__nv_bfloat16*)const_cast<void*>(k_cache) : nullptr;
+  p.v_write = (qkv != nullptr && write_kv) ? (__nv_bfloat16*)const_cast<void*>(v_cache) : nullptr;
   return d == 64 ? launch_for<64>(m, p, stream) : launch_for<128>(m, p, stream);
+}
+}  // namespace
+
+ILB_EXPORT int ilb_attention_decode_tma(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                        const int* positions, const int* cu_q, const int* block_table,
+                                        int max_blocks, int page_size, int num_pages, int window, float scale,
+                                        int n_seqs, int nq, int nkv, int d, int q_stride, int out_stride,
+                                        int* error_flag, cudaStream_t stream) {
+  return decode_common(q, nullptr, 0, nullptr, nullptr, 1.f, nullptr, 0, out, k_cache, v_cache, positions, cu_q, block_table,
+                       max_blocks, page_size, num_pages, window, scale, n_seqs, nq, nkv, d, q_stride, out_stride, error_flag,
+                       stream);
+}
+
+// The same with the step's q/k/v taken from the fused projection output `qkv`
+// [tokens, (nq + 2 nkv) d]: per-head RMSNorm (q_weight / k_weight [d], or null), rotation over
+// the whole head (rope [tokens, d/2, 2] cos/sin, or null), and, if write_kv, the new key and
+// value stored to the cache.  What qk_norm_rope.cu and this kernel do in two launches.
+ILB_EXPORT int ilb_attention_decode_fused(const void* qkv, int qkv_stride, const float* q_weight, const float* k_weight,
+                                          float eps, const float* rope, int write_kv, void* out, void* k_cache,
+                                          void* v_cache, const int* positions, const int* cu_q, const int* block_table,
+                                          int max_blocks, int page_size, int num_pages, int window, float scale,
+                                          int n_seqs, int nq, int nkv, int d, int out_stride, int* error_flag,
+                                          cudaStream_t stream) {
+  ILB_REQUIRE(qkv != nullptr, "attention decode: no projection output");
+  return decode_common(nullptr, qkv, qkv_stride, q_weight, k_weight, eps, rope, write_kv, out, k_cache, v_cache, positions,
+                       cu_q, block_table, max_blocks, page_size, num_pages, window, scale, n_seqs, nq, nkv, d, 0, out_stride,
+                       error_flag, stream);
 }
 
 ILB_DEFINE_LAST_ERROR()

@@ -368,6 +368,33 @@ def attention_decode_tma(q, out, k_cache, v_cache, positions, cu_q, block_table,
           _i(out.shape[1]), _ptr(st.error), _stream(q))
 
 
+def attention_decode_fused_supported(dtype: torch.dtype, cache_dtype: torch.dtype, nq: int, nkv: int, d: int,
+                                     page_size: int, rotary_dim: int, has_rope: bool) -> bool:
+    """Whether a decode-only step can take q/k/v straight from the fused projection output:
+    the TMA decode kernel's geometry, bfloat16 throughout, rotation over the whole head."""
+    return (DECODE_CLUSTER_ENABLED and DECODE_FUSED_ENABLED and FLASH_ENABLED and dtype == torch.bfloat16
+            and cache_dtype == torch.bfloat16 and attention_decode_tma_supported(nq, nkv, d, page_size)
+            and (not has_rope or rotary_dim == d))
+
+
+def attention_decode_fused(qkv, out, q_weight, k_weight, eps, rope_table, k_cache, v_cache, write_kv, positions, cu_q,
+                           block_table, window, scale, n_seqs, nq, nkv, d) -> None:
+    """Decode attention with the per-head q/k norm, the rotation and the cache write of the
+    step's own key and value inside the attention kernel (one launch instead of two)."""
+    for t, w in ((qkv, "qkv"), (out, "out"), (k_cache, "k cache"), (v_cache, "v cache")):
+        _need(t, "attention " + w, torch.bfloat16)
+    for t, w in ((q_weight, "q norm weight"), (k_weight, "k norm weight"), (rope_table, "rope table")):
+        if t is not None:
+            _need(t, "attention " + w, torch.float32)
+    num_pages, _, page_size, _ = k_cache.shape
+    st = _tc_state(qkv.device)
+    _call("attention_decode", "ilb_attention_decode_fused", _ptr(qkv), _i(qkv.shape[1]), _ptr(q_weight), _ptr(k_weight),
+          _f(eps if eps and eps > 0 else 1e-6), _ptr(rope_table), _i(1 if write_kv else 0), _ptr(out), _ptr(k_cache),
+          _ptr(v_cache), _ptr(positions),
+          _ptr(cu_q), _ptr(block_table), _i(block_table.shape[1]), _i(page_size), _i(num_pages), _i(window or 0),
+          _f(scale), _i(n_seqs), _i(nq), _i(nkv), _i(d), _i(out.shape[1]), _ptr(st.error), _stream(qkv))
+
+
 def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
               step, block_table: torch.Tensor, window: int, scale: float, nq: int, nkv: int,
               d: int, workspace=None, decode_chunk: int = DECODE_CHUNK_MIN) -> None:
@@ -403,6 +430,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
                           step.n_seqs, n_tiles, nq, nkv, d)
 
 
+DECODE_FUSED_ENABLED = True     # tests switch it off to run q/k norm + rotation + cache write as a launch of its own
 DECODE_CLUSTER_ENABLED = True   # tests switch it off to reach the ticketed split-KV decode kernel
 FLASH_ENABLED = True       # tests switch it off to exercise the exact kernel in bfloat16
 TC_ATTENTION_ENABLED = True   # tests switch it off to reach the mma.sync prefill kernel at its geometries

@@ -436,6 +436,64 @@ def test_flash_decode_split_kv(nq, nkv, d, page_size, window, chunk, cluster):
     close_flash(out, ref, max(float(v.abs().max()) for _, v in seqs), "flash decode")
 
 
+@pytest.mark.parametrize("nq,nkv,d,page_size,window,use_norm,use_rope", [(32, 8, 128, 16, 0, True, True), (8, 2, 64, 32, 50, True, True),
+                                                                         (40, 2, 128, 16, 0, False, True), (4, 4, 128, 64, 0, True, False)])
+def test_decode_attention_with_the_input_stage_inside(nq, nkv, d, page_size, window, use_norm, use_rope):
+    """One launch takes q, k, v of the step's token from the fused projection output: per-head
+    norm, rotation, the cache write of the new key and value, and attention over old keys plus
+    the new one.  Lengths put the new position at the start, the middle and the end of a
+    32-key tile and of a page, and on tiles of every CTA of the cluster."""
+    o = ops()
+    torch.manual_seed(nq + d + page_size)
+    eps, theta = 1e-6, 1e4
+    lens = [1, 2, 16, 17, 32, 33, 48, 64, 65, 100, 257, 700, 1031]
+    S = len(lens)
+    G = nq // nkv
+    old = [(torch.randn(n - 1, nkv, d).to(torch.bfloat16).double(), torch.randn(n - 1, nkv, d).to(torch.bfloat16).double()) for n in lens]
+    qkv = torch.randn(S, (nq + 2 * nkv) * d).to(torch.bfloat16)
+    qw, kw = (1 + 0.1 * torch.randn(d)).float(), (1 + 0.1 * torch.randn(d)).float()
+    positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+    inv = torch.tensor([theta ** (-(2.0 * i) / d) for i in range(d // 2)], dtype=torch.float64)
+    table = torch.empty(S, d // 2, 2, device="cuda")
+    o.rope_table(positions.cuda(), inv.cuda(), table)
+
+    def norm(t, w):
+        return t / torch.sqrt((t * t).mean(-1, keepdim=True) + eps) * w.double() if use_norm else t
+
+    def rope(t, pos):
+        if not use_rope:
+            return t
+        ang = pos.double()[:, None] * inv[None, :]
+        c, s_ = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        a, b = t[..., :d // 2], t[..., d // 2:]
+        return torch.cat([a * c - b * s_, a * s_ + b * c], dim=-1)
+
+    x = qkv.double()
+    q_new = rope(norm(x[:, :nq * d].view(S, nq, d), qw), positions).to(torch.bfloat16).double()
+    k_new = rope(norm(x[:, nq * d:(nq + nkv) * d].view(S, nkv, d), kw), positions).to(torch.bfloat16).double()
+    v_new = x[:, (nq + nkv) * d:].view(S, nkv, d)
+    # the cache holds the old keys; the slot of the new position holds something else
+    padded = [(torch.cat([k, torch.full((1, nkv, d), 5.0, dtype=torch.float64)]), torch.cat([v, torch.full((1, nkv, d), -3.0, dtype=torch.float64)]))
+              for k, v in old]
+    n_pages = sum(-(-n // page_size) for n in lens) + 3
+    k_cache, v_cache, btable = build_cache(padded, nkv, d, page_size, n_pages, torch.bfloat16, seed=3, page_order="mixed")
+    k_cache, v_cache = k_cache.cuda(), v_cache.cuda()
+    out = torch.full((S, nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    cu = torch.arange(S + 1, dtype=torch.int32).cuda()
+    for _ in range(2):                       # the second run finds the new key already in the cache: same answer
+        o.attention_decode_fused(qkv.cuda(), out, qw.cuda() if use_norm else None, kw.cuda() if use_norm else None, eps,
+                                 table if use_rope else None, k_cache, v_cache, True, positions.cuda(), cu, btable.cuda(),
+                                 window, 1.0 / math.sqrt(d), S, nq, nkv, d)
+    o.check_device_errors()
+    ref = torch.stack([ref_attention(q_new[s], torch.cat([old[s][0], k_new[s:s + 1]]), torch.cat([old[s][1], v_new[s:s + 1]]),
+                                     lens[s] - 1, window).reshape(-1) for s in range(S)])
+    close_flash(out, ref, max(float(v.abs().max()) for _, v in padded), "decode with input stage")
+    for s, n in enumerate(lens):             # the new key and value are in the cache now, exactly as the separate kernel rounds them
+        page, slot = int(btable[s, (n - 1) // page_size]), (n - 1) % page_size
+        assert torch.equal(v_cache[page, :, slot].cpu().double(), v_new[s])
+        close(k_cache[page, :, slot], k_new[s], "bfloat16", scale=float(k_new[s].abs().max()), what="new key")
+
+
 @pytest.mark.parametrize("q_len,cluster", [(1, True), (1, False), (5, True)])
 def test_flash_attention_finds_one_far_key_and_respects_the_window_edge(q_len, cluster):
     nq, nkv, d, page = 4, 1, 64, 16
