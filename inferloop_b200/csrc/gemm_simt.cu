@@ -1,9 +1,12 @@
 // out[M,N] (+)= A[M,K] * W[N,K]^T (+ bias[N]) on the ordinary 32-bit pipes.
 //
-// This is the exact path: every product and sum is an IEEE 32-bit fused multiply-add,
-// no tensor-core mode is involved, and each output element is ONE chain of additions
-// over k = 0..K-1 in increasing order.  The chain does not depend on the tile shape, so
-// a row of A gives bit-identical results whatever other rows share the launch.
+// This is the exact path: every product and sum is an IEEE 32-bit operation, no tensor-core
+// mode is involved.  Each output element is summed the same way whatever the tile shape, so a
+// row of A gives bit-identical results whatever other rows share the launch: blocks of 16
+// consecutive k are each one chain of fused multiply-adds from zero, and the block sums are
+// added in increasing order with the rounding error of every addition carried along in a
+// second 32-bit word (Knuth's two-sum) and added at the end.  A plain chain over K = 12288
+// terms loses about sqrt(K) units in the last place; this one stays near sqrt(16).
 // With bfloat16 inputs it doubles as the any-shape fallback of the bfloat16 path.
 //
 // Reference formula: y = W x, weights stored [out, in]
@@ -26,11 +29,11 @@ gemm_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W,
   const int tid = threadIdx.x;
   const int tx = tid % (BN / TN), ty = tid / (BN / TN);
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  float acc[TM][TN];
+  float acc[TM][TN], lost[TM][TN];
 #pragma unroll
   for (int i = 0; i < TM; ++i)
 #pragma unroll
-    for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+    for (int j = 0; j < TN; ++j) { acc[i][j] = 0.f; lost[i][j] = 0.f; }
 
   for (int k0 = 0; k0 < K; k0 += BK) {
     for (int idx = tid; idx < BM * BK; idx += THREADS) {
@@ -45,6 +48,11 @@ gemm_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W,
     }
     __syncthreads();
     const int kmax = (K - k0) < BK ? (K - k0) : BK;
+    float part[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) part[i][j] = 0.f;
     for (int kk = 0; kk < kmax; ++kk) {
       float a[TM], w[TN];
 #pragma unroll
@@ -54,8 +62,17 @@ gemm_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W,
 #pragma unroll
       for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        for (int j = 0; j < TN; ++j) part[i][j] = fmaf(a[i], w[j], part[i][j]);
     }
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) {
+        const float s = __fadd_rn(acc[i][j], part[i][j]);
+        const float bp = __fsub_rn(s, acc[i][j]);
+        lost[i][j] = __fadd_rn(lost[i][j], __fadd_rn(__fsub_rn(acc[i][j], __fsub_rn(s, bp)), __fsub_rn(part[i][j], bp)));
+        acc[i][j] = s;
+      }
     __syncthreads();
   }
 #pragma unroll
@@ -66,7 +83,7 @@ gemm_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W,
     for (int j = 0; j < TN; ++j) {
       const int gn = n0 + tx * TN + j;
       if (gn >= N) continue;
-      float v = acc[i][j];
+      float v = __fadd_rn(acc[i][j], lost[i][j]);
       if (bias != nullptr) v += bias[gn];
       TO* o = out + (size_t)gm * ldo + gn;
       if (accumulate) v = to_float(*o) + v;
