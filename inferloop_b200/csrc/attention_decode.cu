@@ -357,7 +357,13 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  pdl_wait();
+  // The step's positions and block tables were on the device before the step's first kernel
+  // began, and the cache rows of earlier positions are older still.  When this kernel is the
+  // one that writes the new position's key and value, nothing the producer warp reads comes
+  // from the preceding kernel: it starts the stream of tiles without waiting for it.  Everyone
+  // else reads the projection output and waits.
+  const bool stream_early = p.qkv != nullptr && p.k_write != nullptr;
+  if (!(stream_early && (threadIdx.x >> 5) == kConsumers)) pdl_wait();
 
   const int G = p.nq / p.nkv;
   const int rank = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;

@@ -152,6 +152,17 @@ __device__ __forceinline__ float ld_peer_f32(uint32_t local_addr, uint32_t rank)
   return v;
 }
 
+// Four floats into a peer's shared memory; the bytes count towards the peer's mbarrier.
+__device__ __forceinline__ void st_peer_v4(uint32_t remote_addr, uint32_t remote_bar, float a, float b, float c, float d) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
+               ::"r"(remote_addr), "f"(a), "f"(b), "f"(c), "f"(d), "r"(remote_bar) : "memory");
+}
+__device__ __forceinline__ uint32_t peer_addr(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  return remote;
+}
+
 struct Params {
   void* out;                 // [M, N], bf16 or f32
   const float* bias;         // [N] or null
@@ -227,6 +238,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   constexpr int kTileFloats = BN * kTileX;                     // one 128-row block of a tile
   constexpr int kBufs = MS == 1 ? 2 : 1;                       // tiles that tensor memory holds
   constexpr int kEpiThreads = 128 * MS;
+  // Few tokens and a cluster: every CTA SENDS the rows of its share to the CTA that owns them
+  // (asynchronous stores that count on the owner's mbarrier), so the owner waits for bytes,
+  // not for the whole cluster, and nobody reads a peer's memory.  Wider token tiles keep the
+  // form in which the owner fetches the shares.
+  constexpr bool kPush = SWAP && BN <= 32;
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // dynamic shared memory is only 16-byte aligned by contract; align by hand
@@ -237,7 +253,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* flags = reinterpret_cast<volatile int*>(bars + 2 * STAGES + 5);   // [0] = failed, [1] = last ticket
-  float* xch = reinterpret_cast<float*>(bars + 2 * STAGES + 6);                    // [32][64], SwiGLU exchange (swap mode)
+  const uint32_t red_bar = smem_u32(bars + 2 * STAGES + 6);                        // counts the bytes of the shares sent here
+  // [32][64] SwiGLU exchange of whole tiles (swap mode), or the shares sent by the cluster:
+  // [source CTA][gate, up][BN / 4][rows of this CTA][4]
+  float* xch = reinterpret_cast<float*>(bars + 2 * STAGES + 8);
+  const bool push = kPush && p.cluster > 1;
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -248,68 +268,71 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const bool in_sk = p.units > 0 && (int)blockIdx.x < sk_grid;
   const long long u_begin = in_sk ? sch.start(blockIdx.x) : 0, u_end = in_sk ? sch.start(blockIdx.x + 1) : 0;
 
+  // The units of this CTA in order, one K block a step; the divisions that find a tile's
+  // place happen once per segment, not per block: the producer lane's issue rate bounds the ring.
+  struct Units {
+    Segments segs;
+    int tiles_x, kb, left, x0, y0;
+    __device__ Units(const Params& p, const Schedule& sch) : segs(p, sch, blockIdx.x, gridDim.x), tiles_x(p.tiles_x), kb(0), left(0), x0(0), y0(0) {}
+    __device__ __forceinline__ bool next(int& kcol, int& x, int& y) {
+      if (left == 0) {
+        long long tile, sk_first;
+        int kb0, cnt;
+        if (!segs.next(tile, kb0, cnt, sk_first)) return false;
+        kb = kb0; left = cnt;
+        x0 = (int)(tile % tiles_x) * (MS * kTileX);
+        y0 = (int)(tile / tiles_x) * BN;
+      }
+      kcol = kb * kBlockK; x = x0; y = y0;
+      ++kb; --left;
+      return true;
+    }
+  };
+  auto load_x = [&](uint32_t dst, uint32_t bar, int kcol, int x0) {
+#pragma unroll
+    for (int ms = 0; ms < MS; ++ms) tma_load_2d(dst + ms * kBytesX1, &map_x, bar, kcol, x0 + ms * kTileX);
+  };
+  uint32_t n_units = 0, n_early = 0;            // of the producer lane (thread 0)
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, kEpiThreads); }
+    if (push) mbar_init(red_bar, 1);
     flags[0] = 0; flags[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (push) mbar_expect_tx(red_bar, (uint32_t)(kTileX * BN * 4));   // one whole tile's worth of rows arrives here
+    // The weight operand depends on no earlier kernel and on no other thread of this CTA:
+    // the first ring of weight tiles is requested right here, before tensor memory is
+    // allocated and before this kernel waits for its predecessor; the activation tiles of
+    // those stages follow the wait.
+    long long my_tiles = (long long)blockIdx.x < p.sk_tile0 ? (p.sk_tile0 - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+    if (my_tiles > p.dp_waves) my_tiles = p.dp_waves;
+    const uint32_t n_dp = (uint32_t)my_tiles * (uint32_t)p.k_blocks;
+    n_units = n_dp + (uint32_t)(u_end - u_begin);
+    n_early = n_units < (uint32_t)STAGES ? n_units : (uint32_t)STAGES;
+    Units early(p, sch);
+    for (uint32_t it = 0; it < n_early; ++it) {
+      int kcol, x0, y0;
+      early.next(kcol, x0, y0);
+      const uint32_t dst = base + it * kStageBytes;
+      mbar_expect_tx(full0 + 8 * it, kStageBytes);
+      if (SWAP) load_x(dst, full0 + 8 * it, kcol, x0);
+      else tma_load_2d(dst + kBytesX, &map_y, full0 + 8 * it, kcol, y0);
+    }
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tcgen05_fence_before();
-  __syncthreads();
+  if (push) cluster_sync_all();          // every peer's mbarrier is ready before anything is sent to it
+  else __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
-    // The weight operand depends on no earlier kernel, so the first ring of weight
-    // tiles is requested before this kernel waits for its predecessor; the activation
-    // tiles of those stages follow the wait.
     if (lane == 0) {
       bool ok = true;
-      long long my_tiles = (long long)blockIdx.x < p.sk_tile0 ? (p.sk_tile0 - 1 - blockIdx.x) / gridDim.x + 1 : 0;
-      if (my_tiles > p.dp_waves) my_tiles = p.dp_waves;
-      const uint32_t n_dp = (uint32_t)my_tiles * (uint32_t)p.k_blocks;
-      const uint32_t n_units = n_dp + (uint32_t)(u_end - u_begin);
-      const uint32_t n_early = n_units < (uint32_t)STAGES ? n_units : (uint32_t)STAGES;
-      // The units of this CTA in order, one K block a step; the divisions that find a tile's
-      // place happen once per segment, not per block: this lane's issue rate bounds the ring.
-      struct Units {
-        Segments segs;
-        int tiles_x, kb, left, x0, y0;
-        __device__ Units(const Params& p, const Schedule& sch) : segs(p, sch, blockIdx.x, gridDim.x), tiles_x(p.tiles_x), kb(0), left(0), x0(0), y0(0) {}
-        __device__ __forceinline__ bool next(int& kcol, int& x, int& y) {
-          if (left == 0) {
-            long long tile, sk_first;
-            int kb0, cnt;
-            if (!segs.next(tile, kb0, cnt, sk_first)) return false;
-            kb = kb0; left = cnt;
-            x0 = (int)(tile % tiles_x) * (MS * kTileX);
-            y0 = (int)(tile / tiles_x) * BN;
-          }
-          kcol = kb * kBlockK; x = x0; y = y0;
-          ++kb; --left;
-          return true;
-        }
-      };
-      auto load_x = [&](uint32_t dst, uint32_t bar, int kcol, int x0) {
-#pragma unroll
-        for (int ms = 0; ms < MS; ++ms) tma_load_2d(dst + ms * kBytesX1, &map_x, bar, kcol, x0 + ms * kTileX);
-      };
-      {
-        Units early(p, sch);
-        for (uint32_t it = 0; it < n_early; ++it) {
-          int kcol, x0, y0;
-          early.next(kcol, x0, y0);
-          const uint32_t dst = base + it * kStageBytes;
-          mbar_expect_tx(full0 + 8 * it, kStageBytes);
-          if (SWAP) load_x(dst, full0 + 8 * it, kcol, x0);
-          else tma_load_2d(dst + kBytesX, &map_y, full0 + 8 * it, kcol, y0);
-        }
-      }
       pdl_wait();
       Units units(p, sch);
       for (uint32_t it = 0; it < n_early; ++it) {
@@ -398,6 +421,74 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       const bool whole = cnt == p.k_blocks;
       bool last = whole;
       int c_first = 0, c_last = 0;
+      if (kPush && !whole && p.cluster > 1) {
+        // The S CTAs of a cluster hold the S consecutive K ranges of one tile.  CTA r owns 1/S
+        // of the tile's rows (of its gate rows and their up rows): every CTA sends the rows of
+        // its share to their owners, [source][gate, up][column / 4][row][4].
+        const int S = p.cluster;
+        const bool sw = p.epilogue == kSwiGLU;
+        const int parts = sw ? 2 : 1;
+        const int rows_per = (sw ? 64 : kTileX) / S;
+        const int rr = sw ? (row & 63) : row;
+        const uint32_t owner = (uint32_t)(rr / rows_per);
+        const int rl = rr % rows_per, part = sw ? (row >> 6) : 0;
+        const uint32_t me = cluster_rank();
+        const uint32_t dst0 = peer_addr(smem_u32(xch) + 16u * (uint32_t)(((int)me * parts + part) * (BN / 4) * rows_per + rl), owner);
+        const uint32_t bar = peer_addr(red_bar, owner);
+        {
+          float v[32];
+          if (CH == 32) tmem_load_32(taddr, v); else tmem_load_16(taddr, v);
+#pragma unroll
+          for (int g = 0; g < BN / 4; ++g)
+            st_peer_v4(dst0 + 16u * (uint32_t)(g * rows_per), bar, v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+        }
+        // ... and adds, in the order of increasing K, the shares of the rows it owns.
+        const int r = (int)me;
+        const int t = (int)threadIdx.x - 64;
+        const int my_rl = t % rows_per;
+        const int my_row = r * rows_per + my_rl;
+        const int n = sw ? (x0 / kTileX) * 64 + my_row : x0 + my_row;       // output feature
+        const int n_end = sw ? p.N / 2 : p.N;
+        const float bv = (p.bias && n < n_end) ? p.bias[n] : 0.f;
+        bool arrived = false;
+        for (int cg = t / rows_per; cg < BN / 4; cg += 128 / rows_per) {
+          float old[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int m = y0 + cg * 4 + j;
+            old[j] = (p.epilogue == kAccumulate && m < p.M && n < n_end) ? __ldcg((const float*)p.out + (size_t)m * p.ldo + n) : 0.f;
+          }
+          if (!arrived) {
+            if (!mbar_wait(red_bar, 0)) { flags[0] = 1; if (p.error_flag) *p.error_flag = 1; break; }
+            arrived = true;
+          }
+          float acc[4] = {0.f, 0.f, 0.f, 0.f}, up[4] = {0.f, 0.f, 0.f, 0.f};
+          const float4* slots = reinterpret_cast<const float4*>(xch);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            if (q < S) {
+              const float4 a = slots[((q * parts) * (BN / 4) + cg) * rows_per + my_rl];
+              acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+              if (sw) {
+                const float4 u = slots[((q * parts + 1) * (BN / 4) + cg) * rows_per + my_rl];
+                up[0] += u.x; up[1] += u.y; up[2] += u.z; up[3] += u.w;
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int m = y0 + cg * 4 + j;
+            if (m < p.M && n < n_end) {
+              const float val = sw ? silu_mul(acc[j], up[j]) : acc[j] + bv + old[j];
+              const size_t o = (size_t)m * p.ldo + n;
+              if (p.out_f32) ((float*)p.out)[o] = val; else ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(val);
+            }
+          }
+        }
+        // a thread without rows of its own still stays until the shares sent here have landed
+        if (!arrived && !mbar_wait(red_bar, 0)) { flags[0] = 1; if (p.error_flag) *p.error_flag = 1; }
+        break;
+      }
       if (SWAP && !whole && p.cluster > 1) {
         // This CTA's share goes to its own shared memory ([col][row]; the stage ring is idle,
         // every load into it has been consumed); the cluster adds the shares after the roles.
@@ -637,7 +728,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
     if (!SWAP && p.cluster > 1 && !met_cluster) cluster_sync_all();   // a thread that gave up still meets its peers
   }
-  if (SWAP && p.cluster > 1) {
+  if (SWAP && p.cluster > 1 && !push) {
     // The S CTAs of a cluster hold the S consecutive K ranges of one tile.  CTA r adds, in the
     // order of increasing K, the shares of its 1/S of the tile's rows and writes them out.
     cluster_sync_all();
@@ -771,7 +862,9 @@ int sm_count() {
 
 template <int BN, int STAGES, bool SWAP, int MS = 1>
 constexpr size_t smem_bytes() {
-  return (size_t)STAGES * (MS * kTileX * kBlockK * 2 + BN * kBlockK * 2) + 1024 + (2 * STAGES + 6) * 8 + (SWAP ? 32 * 64 * 4 : 0);
+  // ring, alignment slack, barriers and flags, then the exchange area (whole-tile SwiGLU, or the shares a cluster sends here)
+  return (size_t)STAGES * (MS * kTileX * kBlockK * 2 + BN * kBlockK * 2) + 1024 + (2 * STAGES + 8) * 8 +
+         (SWAP ? (BN <= 32 && kTileX * BN * 4 > 32 * 64 * 4 ? kTileX * BN * 4 : 32 * 64 * 4) : 0);
 }
 
 template <int BN, int STAGES, bool SWAP, int MS = 1>
@@ -813,7 +906,7 @@ int active_clusters(int split) {
 int active_clusters_for(int bn, int split) {
   switch (bn) {
     case 16: return active_clusters<16, 5, true>(split);
-    case 32: return active_clusters<32, 5, true>(split);
+    case 32: return active_clusters<32, 4, true>(split);
     case 64: return active_clusters<64, 4, true>(split);
     default: return active_clusters<128, 3, true>(split);
   }
@@ -974,7 +1067,7 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   if (swap) {
     switch (bn) {
       case 16: return launch<16, 5, true>(mx, my, p, (int)grid, stream);
-      case 32: return launch<32, 5, true>(mx, my, p, (int)grid, stream);
+      case 32: return launch<32, 4, true>(mx, my, p, (int)grid, stream);
       case 64: return launch<64, 4, true>(mx, my, p, (int)grid, stream);
       default: return launch<128, 3, true>(mx, my, p, (int)grid, stream);
     }
