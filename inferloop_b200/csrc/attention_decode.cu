@@ -102,12 +102,28 @@ __device__ __forceinline__ float ld_peer_f32(uint32_t local_addr, uint32_t rank)
   return v;
 }
 
+// Floats into a peer's shared memory; the bytes count towards the peer's mbarrier.
+__device__ __forceinline__ uint32_t peer_addr(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ void st_peer_v4(uint32_t remote_addr, uint32_t remote_bar, float a, float b, float c, float d) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
+               ::"r"(remote_addr), "f"(a), "f"(b), "f"(c), "f"(d), "r"(remote_bar) : "memory");
+}
+__device__ __forceinline__ void st_peer_v2(uint32_t remote_addr, uint32_t remote_bar, float a, float b) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%1, %2}, [%3];"
+               ::"r"(remote_addr), "f"(a), "f"(b), "r"(remote_bar) : "memory");
+}
+
 struct Params {
   const __nv_bfloat16* q; __nv_bfloat16* out;
   const int* positions; const int* cu_q; const int* block_table;
   int* error_flag;
   int max_blocks, n_seqs, nq, nkv, window, q_stride, out_stride, page_size, num_pages;
   int split;                           // CTAs of a cluster = ways a sequence's tiles are dealt out
+  int rows_cap;                        // rows of the group that one CTA of the cluster owns at most
   float scale_log2;
   // Fused input stage (qkv != null): q, k, v of the step's token are taken from the fused
   // projection output; per-head RMSNorm (weights may be null) and the rotation (table may be
@@ -348,15 +364,33 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStage);
   const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * kStages;
   volatile int* failed = reinterpret_cast<volatile int*>(bars + 2 * kStages);
+  // Records that the cluster sends here: [source CTA][row of this CTA][D + 4] (O, max, sum)
+  constexpr int kRecIn = D + 4;
+  const uint32_t inbox_bar = smem_u32(bars + 2 * kStages + 1);
+  float* inbox = reinterpret_cast<float*>(bars + 2 * kStages + 2);
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // A group of at most 16 query heads (one pass) over a cluster: CTA r OWNS rows r, r + S, ...
+  // of the group; every warp sends each row of its record to the row's owner, and an owner
+  // waits only for the bytes of its rows.  Larger groups keep the form in which records stay
+  // where they are and the cluster reads them between two barriers.
+  const bool push = p.split > 1 && p.nq / p.nkv <= 16;
+  const int rows_cap = p.rows_cap;                         // rows an owner holds at most (push)
+  int rows_mine = 0;
+  if (push) {
+    const int G0 = p.nq / p.nkv, r0 = (int)blockIdx.x;
+    rows_mine = G0 > r0 ? (G0 - r0 + p.split - 1) / p.split : 0;
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, kConsumers); }
+    if (push) mbar_init(inbox_bar, 1);
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (push && rows_mine > 0) mbar_expect_tx(inbox_bar, (uint32_t)(rows_mine * p.split * (D * 4 + 8)));
   }
-  __syncthreads();
+  if (push) cluster_sync_all();          // every owner's mbarrier is ready before anything is sent to it
+  else __syncthreads();
   // The step's positions and block tables were on the device before the step's first kernel
   // began, and the cache rows of earlier positions are older still.  When this kernel is the
   // one that writes the new position's key and value, nothing the producer warp reads comes
@@ -489,6 +523,68 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
       }
       if (!ok && lane == 0) { *failed = 1; if (p.error_flag) *p.error_flag = 1; }
       __syncwarp();
+      if (push) {
+        // The two warps' records become one (in the order warp 0, warp 1): warp 1 leaves its
+        // fragments in the ring, lane by lane, once both warps are past their last tile.
+        float l2[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          float l = st.l[r];
+          l += __shfl_xor_sync(0xffffffffu, l, 1);
+          l += __shfl_xor_sync(0xffffffffu, l, 2);
+          l2[r] = l;
+        }
+        constexpr int kDump = D / 2 + 4;                     // floats a lane leaves: O fragments, two maxima, two sums
+        float* dump = reinterpret_cast<float*>(smem);        // [kDump][32]
+        static_assert(kDump * 32 * 4 <= kStages * (int)kStage, "a warp's fragments must fit the tile ring");
+        asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
+        if (warp == 1) {
+#pragma unroll
+          for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) dump[(i * 4 + c) * 32 + lane] = st.o[i][c];
+#pragma unroll
+          for (int r = 0; r < 2; ++r) { dump[(D / 2 + r) * 32 + lane] = st.m[r]; dump[(D / 2 + 2 + r) * 32 + lane] = l2[r]; }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
+        if (warp == 0) {
+          float f0[2], f1[2];
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const float m1 = dump[(D / 2 + r) * 32 + lane], l1 = dump[(D / 2 + 2 + r) * 32 + lane];
+            const float m = fmaxf(st.m[r], m1);
+            f0[r] = st.m[r] == -INFINITY ? 0.f : exp2f(st.m[r] - m);
+            f1[r] = m1 == -INFINITY ? 0.f : exp2f(m1 - m);
+            st.m[r] = m;
+            l2[r] = l2[r] * f0[r] + l1 * f1[r];
+          }
+#pragma unroll
+          for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) st.o[i][c] = st.o[i][c] * f0[c >> 1] + dump[(i * 4 + c) * 32 + lane] * f1[c >> 1];
+          // Row g + 8r goes to CTA (row % S), place row / S.  A lane holds pairs of columns;
+          // neighbours of a quad trade one pair so that each sends 16 bytes at a time.
+          const uint32_t me = (uint32_t)rank;
+          const bool odd = (t & 1) != 0;
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const int row = g + 8 * r;
+            const uint32_t owner = (uint32_t)(row % kSplit);
+            const uint32_t at = smem_u32(inbox) + 4u * (uint32_t)((me * rows_cap + row / kSplit) * kRecIn);
+            const uint32_t dst = peer_addr(at, owner), bar = peer_addr(inbox_bar, owner);
+#pragma unroll
+            for (int i0 = 0; i0 < D / 8; i0 += 2) {
+              const float ax = st.o[i0][2 * r], ay = st.o[i0][2 * r + 1], bx = st.o[i0 + 1][2 * r], by = st.o[i0 + 1][2 * r + 1];
+              const float rx = __shfl_xor_sync(0xffffffffu, odd ? ax : bx, 1), ry = __shfl_xor_sync(0xffffffffu, odd ? ay : by, 1);
+              if (live[r]) {
+                if (!odd) st_peer_v4(dst + 4u * (uint32_t)(i0 * 8 + 2 * t), bar, ax, ay, rx, ry);
+                else st_peer_v4(dst + 4u * (uint32_t)((i0 + 1) * 8 + 2 * (t - 1)), bar, rx, ry, bx, by);
+              }
+            }
+            if (live[r] && t == 0) st_peer_v2(dst + 4u * (uint32_t)D, bar, st.m[r], l2[r]);
+          }
+        }
+      } else {
       // both consumer warps are past their last tile before a record overwrites the ring
       asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
 #pragma unroll
@@ -501,6 +597,30 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         for (int i = 0; i < D / 8; ++i) { row[i * 8 + 2 * t] = st.o[i][2 * r]; row[i * 8 + 2 * t + 1] = st.o[i][2 * r + 1]; }
         if (t == 0) { row[D] = st.m[r]; row[D + 1] = l; }
       }
+      }
+    }
+    if (push) {
+      // ---- merge of the rows this CTA owns, from its own shared memory, CTA after CTA
+      if (rows_mine > 0) {
+        if (!mbar_wait(inbox_bar, 0)) { *failed = 1; if (p.error_flag) *p.error_flag = 1; return; }
+        const int n_rec = kSplit;
+        for (int e = threadIdx.x; e < rows_mine * D; e += kThreads) {
+          const int slot = e / D, c = e % D, row = slot * kSplit + rank;
+          const float* first = inbox + (size_t)slot * kRecIn;
+          float m_all = -INFINITY;
+          for (int i = 0; i < n_rec; ++i) m_all = fmaxf(m_all, first[(size_t)i * rows_cap * kRecIn + D]);
+          float l_all = 0.f, o = 0.f;
+          for (int i = 0; i < n_rec; ++i) {
+            const float* rcd = first + (size_t)i * rows_cap * kRecIn;
+            const float m = rcd[D];
+            const float f = (m == -INFINITY) ? 0.f : exp2f(m - m_all);
+            l_all += rcd[D + 1] * f;
+            o += rcd[c] * f;
+          }
+          p.out[(size_t)tok * p.out_stride + (size_t)(kvh * G + row) * D + c] = __float2bfloat16_rn(l_all > 0.f ? o / l_all : 0.f);
+        }
+      }
+      return;
     }
     cluster_sync_all();
     // ---- merge: element e of the group's output from all records, CTA after CTA, warp after warp
@@ -601,14 +721,20 @@ int cache_map(CUtensorMap* out, const void* ptr, int d, int page_size, int nkv, 
   return 0;
 }
 
+// Ring, alignment slack, barriers and the flag; the records that a cluster sends to this CTA follow.
 template <int D, int STAGES>
-constexpr size_t smem_bytes() { return (size_t)STAGES * 2 * (D / 64) * kKeys * 128 + 1024 + (2 * STAGES + 1) * 8; }
+constexpr size_t ring_bytes() { return (size_t)STAGES * 2 * (D / 64) * kKeys * 128 + 1024 + (2 * STAGES + 2) * 8; }
+
+// Rows of a group of `group` query heads that one CTA of a cluster of `split` owns at most,
+// and the bytes of the records sent to it (none when the records stay where they are).
+inline int rows_cap_of(int group, int split) { return (split > 1 && group <= 16) ? (group + split - 1) / split : 0; }
+inline size_t inbox_bytes(int d, int group, int split) { return (size_t)split * rows_cap_of(group, split) * (d + 4) * 4; }
 
 template <int D, int STAGES>
 int configure() {
   static bool configured = false;
   if (!configured) {
-    constexpr size_t smem = smem_bytes<D, STAGES>();
+    constexpr size_t smem = ring_bytes<D, STAGES>() + (size_t)2 * kMaxSplit * (D + 4) * 4;   // the most a launch asks for
     static_assert(smem <= 227 * 1024, "tile ring does not fit shared memory");
     cudaError_t e = cudaFuncSetAttribute(decode_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail("attention decode: cannot reserve %zu bytes of shared memory", smem);
@@ -619,31 +745,37 @@ int configure() {
   return 0;
 }
 
-// Clusters of `split` CTAs of this kernel that the device holds at a time (0 if it cannot tell or cannot run them).
+// Clusters of `split` CTAs of this kernel, each with `extra` more bytes of shared memory, that
+// the device holds at a time (0 if it cannot tell or cannot run them).
 template <int D, int STAGES>
-int active_clusters(int split) {
-  static int cache[kMaxSplit + 1] = {};
+int active_clusters(int split, size_t extra) {
+  static std::unordered_map<long long, int> cache;
+  static std::mutex mu;
   if (split < 1 || split > kMaxSplit) return 0;
-  if (cache[split] != 0) return cache[split] < 0 ? 0 : cache[split];
+  const long long key = (long long)extra * 64 + split;
+  std::lock_guard<std::mutex> g(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
   if (configure<D, STAGES>()) return 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(split, 64, 8);
   cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = smem_bytes<D, STAGES>();
+  cfg.dynamicSmemBytes = ring_bytes<D, STAGES>() + extra;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = (unsigned)split; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr; cfg.numAttrs = 1;
   int n = 0;
   if (cudaOccupancyMaxActiveClusters(&n, decode_kernel<D, STAGES>, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
-  cache[split] = n > 0 ? n : -1;
-  return n > 0 ? n : 0;
+  if (n < 0) n = 0;
+  cache.emplace(key, n);
+  return n;
 }
 
 template <int D, int STAGES>
-int launch(const CUtensorMap (&m)[4], const Params& p, cudaStream_t stream) {
+int launch(const CUtensorMap (&m)[4], const Params& p, size_t extra, cudaStream_t stream) {
   if (configure<D, STAGES>()) return -1;
-  ilb::launch_cluster(decode_kernel<D, STAGES>, dim3(p.split, p.nkv, p.n_seqs), dim3(kThreads), smem_bytes<D, STAGES>(), stream,
+  ilb::launch_cluster(decode_kernel<D, STAGES>, dim3(p.split, p.nkv, p.n_seqs), dim3(kThreads), ring_bytes<D, STAGES>() + extra, stream,
                       p.split, m[0], m[1], m[2], m[3], p);
   return check_launch("attention decode");
 }
@@ -651,14 +783,25 @@ int launch(const CUtensorMap (&m)[4], const Params& p, cudaStream_t stream) {
 // The ways a sequence's tiles are dealt out and the depth of the tile ring: as many CTAs as
 // fit the device at once, and the shared memory that this leaves to each of them.
 template <int D>
+void plan_for(int n_seqs, int nq, int nkv, int& split, int& stages) {
+  const long long pairs = (long long)n_seqs * nkv;
+  const int group = nq / nkv;
+  split = kMaxSplit;
+  while (split > 1 && active_clusters<D, 3>(split, inbox_bytes(D, group, split)) < pairs) split /= 2;
+  const size_t extra = inbox_bytes(D, group, split);
+  stages = active_clusters<D, 12>(split, extra) >= pairs ? 12 : active_clusters<D, 6>(split, extra) >= pairs ? 6 : 3;
+}
+
+template <int D>
 int launch_for(const CUtensorMap (&m)[4], Params& p, cudaStream_t stream) {
-  const long long pairs = (long long)p.n_seqs * p.nkv;
-  int split = kMaxSplit;
-  while (split > 1 && active_clusters<D, 3>(split) < pairs) split /= 2;
-  p.split = split;
-  if (active_clusters<D, 12>(split) >= pairs) return launch<D, 12>(m, p, stream);
-  if (active_clusters<D, 6>(split) >= pairs) return launch<D, 6>(m, p, stream);
-  return launch<D, 3>(m, p, stream);
+  int stages = 3;
+  plan_for<D>(p.n_seqs, p.nq, p.nkv, p.split, stages);
+  const int group = p.nq / p.nkv;
+  p.rows_cap = rows_cap_of(group, p.split);
+  const size_t extra = inbox_bytes(D, group, p.split);
+  if (stages == 12) return launch<D, 12>(m, p, extra, stream);
+  if (stages == 6) return launch<D, 6>(m, p, extra, stream);
+  return launch<D, 3>(m, p, extra, stream);
 }
 
 }  // namespace
@@ -667,6 +810,13 @@ int launch_for(const CUtensorMap (&m)[4], Params& p, cudaStream_t stream) {
 ILB_EXPORT int ilb_attention_decode_tma_supported(int nq, int nkv, int d, int page_size) {
   if (nkv <= 0 || nq <= 0 || nq % nkv != 0) return 0;
   return ((d == 64 || d == 128) && (page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128)) ? 1 : 0;
+}
+
+// The cluster size and ring depth a launch of this geometry would get (for tests and notes).
+ILB_EXPORT int ilb_attention_decode_plan(int n_seqs, int nq, int nkv, int d, int page_size, int* split, int* stages) {
+  ILB_REQUIRE(ilb_attention_decode_tma_supported(nq, nkv, d, page_size) && n_seqs > 0 && split && stages, "attention decode: no plan for this geometry");
+  if (d == 64) plan_for<64>(n_seqs, nq, nkv, *split, *stages); else plan_for<128>(n_seqs, nq, nkv, *split, *stages);
+  return 0;
 }
 
 namespace {

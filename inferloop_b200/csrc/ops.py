@@ -354,6 +354,16 @@ def attention_decode_tma_supported(nq: int, nkv: int, d: int, page_size: int) ->
     return nkv > 0 and nq > 0 and nq % nkv == 0 and d in (64, 128) and page_size in (16, 32, 64, 128)
 
 
+def attention_decode_plan(n_seqs: int, nq: int, nkv: int, d: int, page_size: int) -> tuple:
+    """(CTAs of a cluster, stages of the tile ring) that a decode step of this geometry gets."""
+    lib = load_module("attention_decode")
+    split, stages = ctypes.c_int(0), ctypes.c_int(0)
+    lib.ilb_attention_decode_plan.restype = ctypes.c_int
+    if lib.ilb_attention_decode_plan(_i(n_seqs), _i(nq), _i(nkv), _i(d), _i(page_size), ctypes.byref(split), ctypes.byref(stages)) != 0:
+        raise KernelError(lib.ilb_last_error().decode())
+    return split.value, stages.value
+
+
 def attention_decode_tma(q, out, k_cache, v_cache, positions, cu_q, block_table, window, scale, n_seqs,
                          nq, nkv, d) -> None:
     """Split-KV decode whose tiles come by TMA and whose partial results meet inside a
