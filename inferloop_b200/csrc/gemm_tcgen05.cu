@@ -242,7 +242,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   // (asynchronous stores that count on the owner's mbarrier), so the owner waits for bytes,
   // not for the whole cluster, and nobody reads a peer's memory.  Wider token tiles keep the
   // form in which the owner fetches the shares.
-  constexpr bool kPush = SWAP && BN <= 32;
+  constexpr bool kPush = SWAP && BN <= 64;
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // dynamic shared memory is only 16-byte aligned by contract; align by hand
@@ -435,12 +435,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         const uint32_t me = cluster_rank();
         const uint32_t dst0 = peer_addr(smem_u32(xch) + 16u * (uint32_t)(((int)me * parts + part) * (BN / 4) * rows_per + rl), owner);
         const uint32_t bar = peer_addr(red_bar, owner);
-        {
+        for (int c0 = 0; c0 < BN; c0 += CH) {
           float v[32];
-          if (CH == 32) tmem_load_32(taddr, v); else tmem_load_16(taddr, v);
+          if (CH == 32) tmem_load_32(taddr + c0, v); else tmem_load_16(taddr + c0, v);
 #pragma unroll
-          for (int g = 0; g < BN / 4; ++g)
-            st_peer_v4(dst0 + 16u * (uint32_t)(g * rows_per), bar, v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+          for (int g = 0; g < CH / 4; ++g)
+            st_peer_v4(dst0 + 16u * (uint32_t)((c0 / 4 + g) * rows_per), bar, v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
         }
         // ... and adds, in the order of increasing K, the shares of the rows it owns.
         const int r = (int)me;
@@ -860,11 +860,12 @@ int sm_count() {
   return n;
 }
 
+// Ring, alignment slack, barriers and flags, then the exchange area: the whole-tile SwiGLU
+// exchange, or (`sent`) the shares that the CTAs of a cluster send here.
 template <int BN, int STAGES, bool SWAP, int MS = 1>
-constexpr size_t smem_bytes() {
-  // ring, alignment slack, barriers and flags, then the exchange area (whole-tile SwiGLU, or the shares a cluster sends here)
+constexpr size_t smem_bytes(bool sent = true) {
   return (size_t)STAGES * (MS * kTileX * kBlockK * 2 + BN * kBlockK * 2) + 1024 + (2 * STAGES + 8) * 8 +
-         (SWAP ? (BN <= 32 && kTileX * BN * 4 > 32 * 64 * 4 ? kTileX * BN * 4 : 32 * 64 * 4) : 0);
+         (SWAP ? (sent && BN <= 64 && kTileX * BN * 4 > 32 * 64 * 4 ? kTileX * BN * 4 : 32 * 64 * 4) : 0);
 }
 
 template <int BN, int STAGES, bool SWAP, int MS = 1>
@@ -907,14 +908,14 @@ int active_clusters_for(int bn, int split) {
   switch (bn) {
     case 16: return active_clusters<16, 5, true>(split);
     case 32: return active_clusters<32, 4, true>(split);
-    case 64: return active_clusters<64, 4, true>(split);
+    case 64: return active_clusters<64, 3, true>(split);
     default: return active_clusters<128, 3, true>(split);
   }
 }
 
 template <int BN, int STAGES, bool SWAP, int MS = 1>
 int launch(const CUtensorMap& mx, const CUtensorMap& my, const Params& p, int grid, cudaStream_t stream) {
-  constexpr size_t smem = smem_bytes<BN, STAGES, SWAP, MS>();
+  const size_t smem = smem_bytes<BN, STAGES, SWAP, MS>(p.cluster > 1);
   if (configure<BN, STAGES, SWAP, MS>()) return -1;
   ilb::launch_cluster(gemm_tc_kernel<BN, STAGES, SWAP, MS>, dim3(grid), dim3(threads_for(MS)), smem, stream, p.cluster, mx, my, p);
   return check_launch("gemm_tc");
@@ -1068,7 +1069,8 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
     switch (bn) {
       case 16: return launch<16, 5, true>(mx, my, p, (int)grid, stream);
       case 32: return launch<32, 4, true>(mx, my, p, (int)grid, stream);
-      case 64: return launch<64, 4, true>(mx, my, p, (int)grid, stream);
+      // the shares sent to a CTA take the room of a stage: a shallower ring for clusters only
+      case 64: return p.cluster > 1 ? launch<64, 3, true>(mx, my, p, (int)grid, stream) : launch<64, 4, true>(mx, my, p, (int)grid, stream);
       default: return launch<128, 3, true>(mx, my, p, (int)grid, stream);
     }
   }
