@@ -14,12 +14,21 @@
 //   warps 0-1  consumers: the group's query heads are the 16 rows of an m16n8k16 MMA; each
 //            warp takes 16 keys of every tile: S = Q K^T, online softmax in 32-bit, O += P V
 //            with ldmatrix from the swizzled tiles.
-//   merge    every warp leaves (max, sum, O) of its keys in its CTA's shared memory; after a
-//            cluster barrier the threads of the whole cluster each take output elements and
-//            add the cluster's records in a fixed order, reading the peers' shared memory directly.
-//            No scratch buffer, no tickets, no second pass through L2.
-// Every mbarrier wait is bounded; on expiry a flag is raised and the CTA still walks to
-// the cluster barriers, so nobody is left waiting.  No multicast.
+//   merge    a group of up to 16 query heads: the two warps' (max, sum, O) become one record
+//            in the CTA; row r of it is SENT to CTA r % S of the cluster (asynchronous stores
+//            that count on the owner's mbarrier), and the owner adds the S records of its rows
+//            in the order of the CTAs from its own shared memory.  One cluster barrier, at
+//            the start (so that every mbarrier is ready); no scratch buffer, no tickets, no
+//            second pass through L2.  Larger groups run in passes of 16 heads whose records
+//            stay where they are and are read by the cluster between two barriers.
+//   input    with the fused projection output as input, the consumers norm and rotate q on
+//            the way into their MMA fragments, and the warp whose keys include the step's own
+//            position norms and rotates the new key, writes it and the new value to the cache
+//            and patches them into the tile in shared memory.  The producer warp then reads
+//            nothing that the preceding kernel writes and starts its stream before the
+//            dependency wait.
+// Every mbarrier wait is bounded; on expiry a flag is raised and the CTA leaves (or, in the
+// form with cluster barriers, still walks to them), so nobody is left waiting.  No multicast.
 //
 // Reference counterparts: `partial_gqa_lanes` + `merge_gqa`, split-KV decode with the
 // group's heads padded to 16 MMA rows

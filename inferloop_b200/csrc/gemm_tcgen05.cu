@@ -10,24 +10,33 @@
 // kernel is a pure stream of weight tiles; with many tokens X is a 128-token tile and Y a
 // tile of BN weight rows.
 //
-// The grid is persistent: one CTA per SM, each taking an equal, contiguous run of
-// (output tile, 64-wide K block) units ("stream-K"), so all SMs stream operands for the
-// whole kernel whatever the number of tiles.  Per CTA (192 threads):
+// Per CTA (192 threads, 320 with two row blocks per tile):
 //   warp 0      one lane issues the TMA loads (cp.async.bulk.tensor, 128-byte swizzle,
-//               no cluster multicast) into a ring of STAGES buffers;
+//               no cluster multicast) into a ring of STAGES buffers; the first ring of WEIGHT
+//               tiles is requested before tensor memory is allocated and before the kernel
+//               waits for its predecessor (the weights depend on neither);
 //   warp 1      allocates tensor memory (two accumulators); one lane issues tcgen05.mma
 //               (4 per 64-wide K block) and tcgen05.commit to hand buffers back and to
 //               signal that an accumulator is complete;
 //   warps 2-5   read an accumulator with tcgen05.ld and write the result while the next
 //               tile accumulates in the other one.
-// A tile whose K range is shared by several CTAs: each stores its share to a 32-bit
-// workspace slot and takes a ticket; the CTA that takes the last ticket of the tile adds
-// the shares in K order, so the sum does not depend on which CTA finished first, and
-// writes the result.  There is no spin-wait on another CTA anywhere.
-// Decode-shaped launches keep their ring below half of an SM's shared memory, so the CTA
-// of the NEXT product can become resident beside this one and have its weight tiles in
-// flight before this kernel has finished (dependent launch, see common.cuh).  Every mbarrier wait is bounded: on expiry the kernel raises a
-// flag in global memory, drains what it armed, frees its tensor memory and returns.
+// How the work is dealt out (host side, end of this file):
+//   few tokens, tiles <= 2 CTAs per SM: every tile's K range is cut into 1, 2, 4 or 8 equal
+//     parts, one per CTA of a thread-block cluster.  Each CTA SENDS the rows of its share to
+//     the CTA that owns them (st.async, counted by the owner's mbarrier); the owner adds the
+//     shares in K order from its own shared memory and writes out (token tiles up to 64; the
+//     128-token tile keeps the older form in which owners read their peers' shares between
+//     two cluster barriers).  One cluster barrier, at the start.
+//   few tokens, many tiles (the output matrix): a persistent grid takes equal, contiguous runs
+//     of (tile, K block) units ("stream-K"); a tile shared by two CTAs goes through a 32-bit
+//     workspace slot and a ticket: the CTA that takes the tile's last ticket adds the shares in
+//     K order, so the sum does not depend on which CTA finished first.
+//   many tokens: whole tiles in rounds of equal size, all CTAs of a round starting at K block
+//     0 together so that they share operand blocks in L2; with few tiles, equal K ranges per
+//     tile (a cluster that shares the write-out by columns, or tickets for two-block tiles).
+// There is no spin-wait on another CTA anywhere.  Decode-shaped launches keep their ring below
+// half of an SM's shared memory: two CTAs per SM.  Every mbarrier wait is bounded: on expiry the
+// kernel raises a flag in global memory, drains what it armed, frees its tensor memory and returns.
 //
 // The reference computes these products with JIT-compiled tile kernels that target no
 // architecture in particular, or with cuBLAS (crates/backend/cuda-kernels/src/tile/
