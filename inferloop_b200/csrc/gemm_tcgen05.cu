@@ -187,6 +187,7 @@ struct Params {
   int epilogue;              // Epilogue
   int out_f32;               // element type of out
   int cluster;               // > 1: a tile's K ranges belong to the CTAs of one cluster, added through their shared memory
+  int tma_out;               // many tokens: the result leaves through shared memory and TMA stores (adds, when accumulating)
 };
 
 // Work: first `dp_waves` rounds of WHOLE tiles in wave order (round w: CTA c takes tile
@@ -236,7 +237,8 @@ struct Segments {
 // tile, and eight epilogue warps drain them together.
 template <int BN, int STAGES, bool SWAP, int MS>
 __global__ void __launch_bounds__(threads_for(MS), SWAP ? 2 : 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, const Params p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
+               const __grid_constant__ CUtensorMap map_out, const Params p) {
   static_assert(MS == 1 || (MS == 2 && !SWAP), "two row blocks per tile only for the many-token form");
   constexpr uint32_t kBytesX1 = kTileX * kBlockK * 2;          // one 128-row block of X
   constexpr uint32_t kBytesX = MS * kBytesX1;
@@ -257,7 +259,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   // dynamic shared memory is only 16-byte aligned by contract; align by hand
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * kStageBytes);
+  // many tokens: one 128-row x 128-byte block per row block of the tile, where results are laid
+  // out (128-byte swizzle) for the TMA store that takes them to memory
+  constexpr uint32_t kStagingBytes = SWAP ? 0u : (uint32_t)MS * kTileX * 128u;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * kStageBytes + kStagingBytes);
   const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES;
   const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * STAGES + 4);
@@ -575,6 +580,90 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             }
           }
         };
+        if (!SWAP && p.tma_out) {
+          // A thread's 128 bytes of one output row go to the staging block (row = its tile row,
+          // 16-byte pieces swizzled as the tensor map says); one thread of the row block then
+          // hands the block to TMA, which writes whole lines, clips what lies outside the
+          // matrix and, when accumulating, adds in memory instead of storing.
+          const uint32_t stg = base + STAGES * kStageBytes + (uint32_t)ms * (kTileX * 128u);
+          const bool elected = row == 0;
+          auto group_sync = [&]() {                          // the 128 threads of this row block
+            if (ms == 0) asm volatile("bar.sync 2, 128;" ::: "memory");
+            else asm volatile("bar.sync 3, 128;" ::: "memory");
+          };
+          auto flush_row = [&](const uint4 (&piece)[8], int out_col) {
+            if (elected) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");     // the block's last reader is done
+            group_sync();
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stg + (uint32_t)row * 128u + (uint32_t)((j ^ (row & 7)) << 4)),
+                           "r"(piece[j].x), "r"(piece[j].y), "r"(piece[j].z), "r"(piece[j].w) : "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            group_sync();
+            if (elected) {
+              if (p.epilogue == kAccumulate)
+                asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                             ::"l"(&map_out), "r"(stg), "r"(out_col), "r"(x0) : "memory");
+              else
+                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                             ::"l"(&map_out), "r"(stg), "r"(out_col), "r"(x0) : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+          };
+          auto pack8 = [&](const float* r8) {                // eight floats as bf16 in 16 bytes
+            uint4 q;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(r8[0], r8[1]), h1 = __floats2bfloat162_rn(r8[2], r8[3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(r8[4], r8[5]), h3 = __floats2bfloat162_rn(r8[6], r8[7]);
+            q.x = *reinterpret_cast<uint32_t*>(&h0); q.y = *reinterpret_cast<uint32_t*>(&h1);
+            q.z = *reinterpret_cast<uint32_t*>(&h2); q.w = *reinterpret_cast<uint32_t*>(&h3);
+            return q;
+          };
+          uint4 piece[8];
+          if (p.epilogue == kSwiGLU) {
+            // columns come in blocks of 64 gate then 64 up: 64 outputs = one 128-byte row of bf16
+            for (int cb = 0; cb < BN; cb += 128) {
+#pragma unroll
+              for (int half = 0; half < 2; ++half) {
+                float g[32], u[32], r[32];
+                fetch(cb + 32 * half, g);
+                fetch(cb + 64 + 32 * half, u);
+#pragma unroll
+                for (int c = 0; c < 32; ++c) r[c] = silu_mul(g[c], u[c]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) piece[4 * half + j] = pack8(r + 8 * j);
+              }
+              flush_row(piece, (y0 + cb) / 2);
+            }
+          } else if (p.out_f32) {
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+              float v[32];
+              fetch(c0, v);
+              if (p.bias) {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) v[c] += (y0 + c0 + c < p.N) ? p.bias[y0 + c0 + c] : 0.f;
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                piece[j] = make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]), __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3]));
+              flush_row(piece, y0 + c0);
+            }
+          } else {
+            for (int c0 = 0; c0 < BN; c0 += 64) {
+#pragma unroll
+              for (int half = 0; half < 2; ++half) {
+                float v[32];
+                fetch(c0 + 32 * half, v);
+                if (p.bias) {
+#pragma unroll
+                  for (int c = 0; c < 32; ++c) v[c] += (y0 + c0 + 32 * half + c < p.N) ? p.bias[y0 + c0 + 32 * half + c] : 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) piece[4 * half + j] = pack8(v + 8 * j);
+              }
+              flush_row(piece, y0 + c0);
+            }
+          }
+        } else
         if (p.epilogue == kSwiGLU) {
           // The weight rows come in blocks of 64 gate rows followed by their 64 up rows; the
           // output has half as many features: out[m, i] = silu(gate_i) * up_i.
@@ -736,6 +825,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       }
     }
     if (!SWAP && p.cluster > 1 && !met_cluster) cluster_sync_all();   // a thread that gave up still meets its peers
+    if (!SWAP && p.tma_out) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // the staging block is read, the stores are done
   }
   if (SWAP && p.cluster > 1 && !push) {
     // The S CTAs of a cluster hold the S consecutive K ranges of one tile.  CTA r adds, in the
@@ -859,6 +949,30 @@ int make_map(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int 
   return 0;
 }
 
+// The [rows, cols] output (32-bit or bf16, leading dimension ld elements); box = 128 rows x 128 bytes.
+int make_out_map(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, bool f32) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  const MapKey key{ptr, rows, cols, ld, f32 ? 4 : 2};
+  std::lock_guard<std::mutex> g(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return 0; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail("gemm_tc: cuTensorMapEncodeTiled is not available from this driver");
+  const int es = f32 ? 4 : 2;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * es};
+  const cuuint32_t box[2] = {(cuuint32_t)(128 / es), (cuuint32_t)kTileX};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("gemm_tc: cuTensorMapEncodeTiled failed with code %d for the output (rows %d cols %d ld %d)", (int)r, rows, cols, ld);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return 0;
+}
+
 int sm_count() {
   static int n = 0;
   if (n == 0) {
@@ -874,6 +988,7 @@ int sm_count() {
 template <int BN, int STAGES, bool SWAP, int MS = 1>
 constexpr size_t smem_bytes(bool sent = true) {
   return (size_t)STAGES * (MS * kTileX * kBlockK * 2 + BN * kBlockK * 2) + 1024 + (2 * STAGES + 8) * 8 +
+         (SWAP ? 0 : MS * kTileX * 128) +       // many tokens: the staging block of each row block
          (SWAP ? (sent && BN <= 64 && kTileX * BN * 4 > 32 * 64 * 4 ? kTileX * BN * 4 : 32 * 64 * 4) : 0);
 }
 
@@ -923,10 +1038,10 @@ int active_clusters_for(int bn, int split) {
 }
 
 template <int BN, int STAGES, bool SWAP, int MS = 1>
-int launch(const CUtensorMap& mx, const CUtensorMap& my, const Params& p, int grid, cudaStream_t stream) {
+int launch(const CUtensorMap& mx, const CUtensorMap& my, const CUtensorMap& mo, const Params& p, int grid, cudaStream_t stream) {
   const size_t smem = smem_bytes<BN, STAGES, SWAP, MS>(p.cluster > 1);
   if (configure<BN, STAGES, SWAP, MS>()) return -1;
-  ilb::launch_cluster(gemm_tc_kernel<BN, STAGES, SWAP, MS>, dim3(grid), dim3(threads_for(MS)), smem, stream, p.cluster, mx, my, p);
+  ilb::launch_cluster(gemm_tc_kernel<BN, STAGES, SWAP, MS>, dim3(grid), dim3(threads_for(MS)), smem, stream, p.cluster, mx, my, mo, p);
   return check_launch("gemm_tc");
 }
 
@@ -1073,20 +1188,25 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   const int ldx = swap ? ldw : lda, ldy = swap ? lda : ldw;
   if (make_map(&mx, X, x_rows, K, ldx, kTileX)) return -1;
   if (make_map(&my, Y, y_rows, K, ldy, bn)) return -1;
+  // Many tokens, one CTA per tile's write-out: the result leaves by TMA (rows of 16-byte multiples from a 16-byte base)
+  CUtensorMap mo = mx;
+  const int es = out_f32 ? 4 : 2, out_cols = accumulate == 2 ? N / 2 : N;
+  p.tma_out = (!swap && p.cluster == 1 && !(accumulate == 2 && out_f32) && ((uintptr_t)out % 16 == 0) && ((long long)ldo * es) % 16 == 0) ? 1 : 0;
+  if (p.tma_out && make_out_map(&mo, out, M, out_cols, ldo, out_f32 != 0)) return -1;
 
   if (swap) {
     switch (bn) {
-      case 16: return launch<16, 5, true>(mx, my, p, (int)grid, stream);
-      case 32: return launch<32, 4, true>(mx, my, p, (int)grid, stream);
+      case 16: return launch<16, 5, true>(mx, my, mo, p, (int)grid, stream);
+      case 32: return launch<32, 4, true>(mx, my, mo, p, (int)grid, stream);
       // the shares sent to a CTA take the room of a stage: a shallower ring for clusters only
-      case 64: return p.cluster > 1 ? launch<64, 3, true>(mx, my, p, (int)grid, stream) : launch<64, 4, true>(mx, my, p, (int)grid, stream);
-      default: return launch<128, 3, true>(mx, my, p, (int)grid, stream);
+      case 64: return p.cluster > 1 ? launch<64, 3, true>(mx, my, mo, p, (int)grid, stream) : launch<64, 4, true>(mx, my, mo, p, (int)grid, stream);
+      default: return launch<128, 3, true>(mx, my, mo, p, (int)grid, stream);
     }
   }
-  if (bn == 256 && ms == 2) return launch<256, 3, false, 2>(mx, my, p, (int)grid, stream);
-  if (bn == 192) return launch<192, 3, false, 2>(mx, my, p, (int)grid, stream);
-  if (bn == 256) return launch<256, 4, false>(mx, my, p, (int)grid, stream);
-  return launch<128, 6, false>(mx, my, p, (int)grid, stream);
+  if (bn == 256 && ms == 2) return launch<256, 3, false, 2>(mx, my, mo, p, (int)grid, stream);
+  if (bn == 192) return launch<192, 3, false, 2>(mx, my, mo, p, (int)grid, stream);
+  if (bn == 256) return launch<256, 4, false>(mx, my, mo, p, (int)grid, stream);
+  return launch<128, 6, false>(mx, my, mo, p, (int)grid, stream);
 }
 
 ILB_DEFINE_LAST_ERROR()
