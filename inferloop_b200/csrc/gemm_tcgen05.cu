@@ -1064,32 +1064,12 @@ ILB_EXPORT int ilb_gemm_tc_supported(int M, int N, int K, int lda, int ldw) {
   return (M > 0 && N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0) ? 1 : 0;
 }
 
-// max_ctas > 0 sets the grid (tests use it to force many shared tiles).
-ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void* out, int out_f32,
-                           int M, int N, int K, int lda, int ldw, int ldo, int accumulate /* Epilogue */,
-                           float* workspace, long long workspace_floats, int* tickets, int n_tickets,
-                           int* error_flag, int max_ctas, cudaStream_t stream) {
-  ILB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
-  ILB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
-              "gemm_tc: K (%d) and the leading dimensions (%d, %d) must be multiples of 8", K, lda, ldw);
-  ILB_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
-  ILB_REQUIRE(accumulate >= 0 && accumulate <= 2, "gemm_tc: unknown epilogue %d", accumulate);
-  ILB_REQUIRE(accumulate != 1 || out_f32, "gemm_tc: accumulation needs a 32-bit output");
-  if (accumulate == 2) {
-    ILB_REQUIRE(N % 128 == 0 && bias == nullptr, "gemm_tc: the SwiGLU epilogue needs N (%d) a multiple of 128 and no bias", N);
-    ILB_REQUIRE(ldo >= N / 2, "gemm_tc: output leading dimension too small");
-  } else {
-    ILB_REQUIRE(ldo >= N, "gemm_tc: output leading dimension too small");
-  }
-  ILB_REQUIRE(workspace != nullptr && tickets != nullptr, "gemm_tc: workspace and tickets are required");
+namespace {
+// How a product is dealt out: orientation, tile shape, grid, cluster, rounds (fills the
+// scheduling fields of `p`, which must hold M, N, K, k_blocks and the epilogue already).
+struct Plan { bool swap; int bn, ms, x_rows, y_rows; long long grid; };
 
-  Params p{};
-  p.out = out; p.bias = bias; p.partial = workspace; p.tickets = tickets; p.error_flag = error_flag;
-  p.M = M; p.N = N; p.K = K; p.ldo = ldo;
-  p.k_blocks = (K + kBlockK - 1) / kBlockK;
-  p.epilogue = accumulate;
-  p.out_f32 = out_f32;
-
+int make_plan(Params& p, int M, int N, int K, int accumulate, int n_tickets, int max_ctas, Plan& plan) {
   const bool swap = M <= 128;
   int bn, ms = 1;                                    // ms: 128-row blocks of X per tile
   if (swap) {
@@ -1106,7 +1086,10 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
     for (const auto& c : shapes) {
       if (c.bn > 128 && N < 256) continue;
       if (c.bn % 128 != 0 && accumulate == 2) continue;        // the SwiGLU epilogue pairs 64-column blocks
-      const long long t = (long long)((M + c.ms * kTileX - 1) / (c.ms * kTileX)) * ((N + c.bn - 1) / c.bn);
+      const long long tm = (M + c.ms * kTileX - 1) / (c.ms * kTileX), tn = (N + c.bn - 1) / c.bn;
+      const long long t = tm * tn;
+      // the part of the tiles' area that holds real rows and columns
+      const double filled = ((double)M / (double)(tm * c.ms * kTileX)) * ((double)N / (double)(tn * c.bn));
       double score;
       if (t * 2 <= sm_count()) {
         long long split = 1;
@@ -1116,6 +1099,7 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
         const long long rounds = (t + sm_count() - 1) / sm_count();
         score = (double)t / (double)(rounds * sm_count()) * c.worth;
       }
+      score *= filled;
       if (score > best) { best = score; bn = c.bn; ms = c.ms; }
     }
   }
@@ -1179,6 +1163,43 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
     p.sk_tile0 = (long long)p.dp_waves * grid;
   }
   p.units = (tiles - p.sk_tile0) * p.k_blocks;
+  plan.swap = swap; plan.bn = bn; plan.ms = ms; plan.x_rows = x_rows; plan.y_rows = y_rows; plan.grid = grid;
+  return 0;
+}
+
+}  // namespace
+
+// max_ctas > 0 sets the grid (tests use it to force many shared tiles).
+ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void* out, int out_f32,
+                           int M, int N, int K, int lda, int ldw, int ldo, int accumulate /* Epilogue */,
+                           float* workspace, long long workspace_floats, int* tickets, int n_tickets,
+                           int* error_flag, int max_ctas, cudaStream_t stream) {
+  ILB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
+  ILB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
+              "gemm_tc: K (%d) and the leading dimensions (%d, %d) must be multiples of 8", K, lda, ldw);
+  ILB_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
+  ILB_REQUIRE(accumulate >= 0 && accumulate <= 2, "gemm_tc: unknown epilogue %d", accumulate);
+  ILB_REQUIRE(accumulate != 1 || out_f32, "gemm_tc: accumulation needs a 32-bit output");
+  if (accumulate == 2) {
+    ILB_REQUIRE(N % 128 == 0 && bias == nullptr, "gemm_tc: the SwiGLU epilogue needs N (%d) a multiple of 128 and no bias", N);
+    ILB_REQUIRE(ldo >= N / 2, "gemm_tc: output leading dimension too small");
+  } else {
+    ILB_REQUIRE(ldo >= N, "gemm_tc: output leading dimension too small");
+  }
+  ILB_REQUIRE(workspace != nullptr && tickets != nullptr, "gemm_tc: workspace and tickets are required");
+
+  Params p{};
+  p.out = out; p.bias = bias; p.partial = workspace; p.tickets = tickets; p.error_flag = error_flag;
+  p.M = M; p.N = N; p.K = K; p.ldo = ldo;
+  p.k_blocks = (K + kBlockK - 1) / kBlockK;
+  p.epilogue = accumulate;
+  p.out_f32 = out_f32;
+
+  Plan plan{};
+  if (make_plan(p, M, N, K, accumulate, n_tickets, max_ctas, plan)) return -1;
+  const bool swap = plan.swap;
+  const int bn = plan.bn, ms = plan.ms, x_rows = plan.x_rows, y_rows = plan.y_rows;
+  const long long grid = plan.grid;
   ILB_REQUIRE(swap || p.cluster == 1 || (bn / p.cluster) % 32 == 0, "gemm_tc: %d columns do not divide among %d CTAs", bn, p.cluster);
   ILB_REQUIRE(2 * grid * ms * bn * kTileX <= workspace_floats, "gemm_tc: workspace too small");
 
@@ -1207,6 +1228,20 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   if (bn == 192) return launch<192, 3, false, 2>(mx, my, mo, p, (int)grid, stream);
   if (bn == 256) return launch<256, 4, false>(mx, my, mo, p, (int)grid, stream);
   return launch<128, 6, false>(mx, my, mo, p, (int)grid, stream);
+}
+
+// What a product of these sizes would get (for tests and notes): out[0..7] = swapped operands,
+// token-tile / weight-tile width, 128-row blocks per tile, grid, cluster, whole-tile rounds,
+// tiles, tiles handled stream-K fashion.
+ILB_EXPORT int ilb_gemm_tc_plan(int M, int N, int K, int epilogue, int* out) {
+  ILB_REQUIRE(M > 0 && N > 0 && K > 0 && out != nullptr && epilogue >= 0 && epilogue <= 2, "gemm_tc: bad sizes for a plan");
+  Params p{};
+  p.M = M; p.N = N; p.K = K; p.k_blocks = (K + kBlockK - 1) / kBlockK; p.epilogue = epilogue;
+  Plan plan{};
+  if (make_plan(p, M, N, K, epilogue, 1 << 30, 0, plan)) return -1;
+  out[0] = plan.swap ? 1 : 0; out[1] = plan.bn; out[2] = plan.ms; out[3] = (int)plan.grid; out[4] = p.cluster;
+  out[5] = p.dp_waves; out[6] = p.tiles_x * p.tiles_y; out[7] = (int)(p.tiles_x * (long long)p.tiles_y - p.sk_tile0);
+  return 0;
 }
 
 ILB_DEFINE_LAST_ERROR()

@@ -277,6 +277,18 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
           _ptr(st.tickets), _i(st.n_tickets), _ptr(st.error), _i(max_ctas), _stream(out))
 
 
+def gemm_tc_plan(M: int, N: int, K: int, accumulate: bool = False, swiglu: bool = False) -> dict:
+    """How `gemm_tc` deals out a product of these sizes (needs a device: the answer depends
+    on how many CTAs fit it)."""
+    lib = load_module("gemm_tcgen05")
+    out = (ctypes.c_int * 8)()
+    lib.ilb_gemm_tc_plan.restype = ctypes.c_int
+    if lib.ilb_gemm_tc_plan(_i(M), _i(N), _i(K), _i(2 if swiglu else (1 if accumulate else 0)), out) != 0:
+        raise KernelError(lib.ilb_last_error().decode())
+    keys = ("swap", "tile_n", "row_blocks", "grid", "cluster", "rounds", "tiles", "tiles_stream_k")
+    return dict(zip(keys, list(out)))
+
+
 def check_device_errors() -> None:
     """Raise if a kernel gave up a bounded wait since the last check (synchronises)."""
     for dev, st in _TC.items():
