@@ -351,6 +351,41 @@ def test_gemm_tcgen05_refuses_unaligned_rows():
         o.gemm_tc(a, w, out)
 
 
+def test_gemm_tcgen05_plans_cover_every_tile_once():
+    """What the launcher decides for the layer shapes of a served model: few tokens put the
+    weight on the MMA's rows and cut the K range of a tile over a cluster that fits the device
+    at once; many tokens run whole tiles in rounds.  In every case tiles = whole + shared."""
+    o = ops()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    for M in (1, 8, 16, 33, 64, 128, 200, 384, 1024, 2048):
+        for N, K, kw in ((6144, 4096, {}), (4096, 4096, {"accumulate": True}), (24576, 4096, {"swiglu": True}),
+                         (4096, 12288, {"accumulate": True}), (151936, 4096, {})):
+            plan = o.gemm_tc_plan(M, N, K, **kw)
+            what = f"M={M} N={N} K={K}: {plan}"
+            assert plan["swap"] == (1 if M <= 128 else 0), what
+            assert plan["cluster"] in (1, 2, 4, 8) and plan["grid"] % plan["cluster"] == 0, what
+            assert 0 <= plan["tiles_stream_k"] <= plan["tiles"], what
+            if plan["swap"]:
+                assert plan["tile_n"] >= min(M, 128) and plan["grid"] <= 2 * sms, what
+                if plan["cluster"] > 1:
+                    assert plan["grid"] == plan["tiles"] * plan["cluster"], what
+            else:
+                assert plan["grid"] <= sms, what
+                assert plan["rounds"] * plan["grid"] >= plan["tiles"] - plan["tiles_stream_k"], what
+
+
+def test_decode_attention_plan_keeps_the_launch_resident():
+    o = ops()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    last = 17
+    for n_seqs in (1, 2, 4, 8, 16, 64, 256):
+        split, stages = o.attention_decode_plan(n_seqs, 32, 8, 128, 16)
+        assert split in (1, 2, 4, 8, 16) and stages in (3, 6, 12)
+        assert split <= last                      # more sequences never widen the clusters
+        assert split == 1 or split * n_seqs * 8 <= 4 * sms, (n_seqs, split, stages)
+        last = split
+
+
 # ------------------------------------------------------------------ tensor-core attention
 def close_flash(got, ref, vmax, what):
     """The tensor-core kernels round the probabilities to bfloat16 before the value
