@@ -269,7 +269,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       }
       if (!ok) { flags[0] = 1; if (p.error_flag) *p.error_flag = 1; }
     }
-    if (!SWAP && p.cluster > 1) cluster_sync_all();          // the epilogue warps meet the cluster; so must every thread
+    if (!SWAP && p.cluster > 1) { cluster_sync_all(); cluster_sync_all(); }   // the epilogue warps meet the cluster twice; so must every thread
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
@@ -308,7 +308,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         tcgen05_commit(tfull0); tcgen05_commit(tfull0 + 8);       // let the epilogue leave its wait
       }
     }
-    if (!SWAP && p.cluster > 1) cluster_sync_all();
+    if (!SWAP && p.cluster > 1) { cluster_sync_all(); cluster_sync_all(); }
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5, and 6..9 for the second row block)
     pdl_wait();                               // outputs, shares and tickets belong to earlier kernels until now
@@ -415,7 +415,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         break;
       }
-      if (!whole) {
+      const bool peers = !SWAP && !whole && p.cluster > 1;     // many tokens, a tile's K ranges over a cluster
+      if (peers) {
+        // The sharers of this tile are the CTAs of this cluster.  Each parks its share in its
+        // own shared memory ([col][row]; the stage ring is idle, every load into it has been
+        // consumed); after the barrier every CTA adds the shares of ITS columns, in K order,
+        // straight from its peers' shared memory, and writes them out.
+        float* red = reinterpret_cast<float*>(smem);
+        for (int c0 = 0; c0 < BN; c0 += CH) {
+          float v[32];
+          if (CH == 32) tmem_load_32(taddr + c0, v); else tmem_load_16(taddr + c0, v);
+#pragma unroll
+          for (int c = 0; c < CH; ++c) red[(c0 + c) * kTileX + row] = v[c];
+        }
+        cluster_sync_all();
+        met_cluster = true;
+        const int per = BN / p.cluster;
+        col_lo = (int)cluster_rank() * per;
+        col_hi = col_lo + per;
+        last = true;
+      } else if (!whole) {
         // 1. park this CTA's share of the tile: [col][row], a warp writes 128 contiguous bytes
         float* mine = p.partial + ((size_t)sch.slot(blockIdx.x, tile_first) * MS + ms) * kTileFloats;
         for (int c0 = 0; c0 < BN; c0 += CH) {
@@ -429,17 +448,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         c_first = sch.cta_of(tile_first);
         c_last = sch.cta_of(tile_first + p.k_blocks - 1);
         __threadfence();
-        if (!SWAP && p.cluster > 1) {
-          // The sharers of this tile are the CTAs of this cluster and all of them are here:
-          // after the barrier every CTA adds the shares of ITS columns (in K order) and writes
-          // them out, instead of one CTA doing the whole tile behind a ticket.
-          cluster_sync_all();
-          met_cluster = true;
-          const int per = BN / p.cluster;
-          col_lo = (int)cluster_rank() * per;
-          col_hi = col_lo + per;
-          last = true;
-        } else {
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
         if (threadIdx.x == 64) {
           const int t = atomicAdd(p.tickets + tile, 1);
@@ -451,7 +459,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         last = flags[1] != 0;
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");        // flags[1] is reused by the next segment
         if (last) __threadfence();
-        }
       }
       if (last) {
         // values of columns c0 .. c0 + CH of this thread's row: from the accumulator, or the
@@ -459,6 +466,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         auto fetch = [&](int c0, float (&v)[32]) {
           if (whole) {
             if (CH == 32) tmem_load_32(taddr + c0, v); else tmem_load_16(taddr + c0, v);
+          } else if (peers) {
+#pragma unroll
+            for (int c = 0; c < CH; ++c) v[c] = 0.f;
+            for (int q0 = 0; q0 < p.cluster; q0 += 2) {        // two peers' loads in flight together
+              float a[2][CH];
+#pragma unroll
+              for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int c = 0; c < CH; ++c)
+                  a[j][c] = q0 + j < p.cluster ? ld_peer_f32(base + (uint32_t)((c0 + c) * kTileX + row) * 4u, (uint32_t)(q0 + j)) : 0.f;
+#pragma unroll
+              for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int c = 0; c < CH; ++c) v[c] += a[j][c];
+            }
           } else {
 #pragma unroll
             for (int c = 0; c < CH; ++c) v[c] = 0.f;
@@ -521,7 +543,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           uint4 piece[8];
           if (p.epilogue == kSwiGLU) {
             // columns come in blocks of 64 gate then 64 up: 64 outputs = one 128-byte row of bf16
-            for (int cb = 0; cb < BN; cb += 128) {
+            for (int cb = col_lo; cb < col_hi; cb += 128) {
 #pragma unroll
               for (int half = 0; half < 2; ++half) {
                 float g[32], u[32], r[32];
@@ -535,7 +557,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
               flush_row(piece, (y0 + cb) / 2);
             }
           } else if (p.out_f32) {
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = col_lo; c0 < col_hi; c0 += 32) {
               float v[32];
               fetch(c0, v);
               if (p.bias) {
@@ -548,7 +570,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
               flush_row(piece, y0 + c0);
             }
           } else {
-            for (int c0 = 0; c0 < BN; c0 += 64) {
+            for (int c0 = col_lo; c0 < col_hi; c0 += 64) {
 #pragma unroll
               for (int half = 0; half < 2; ++half) {
                 float v[32];
@@ -724,7 +746,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
       }
     }
-    if (!SWAP && p.cluster > 1 && !met_cluster) cluster_sync_all();   // a thread that gave up still meets its peers
+    if (!SWAP && p.cluster > 1) {
+      if (!met_cluster) cluster_sync_all();            // a thread that gave up still meets its peers
+      cluster_sync_all();                              // nobody leaves while a peer may still read its share
+    }
     if (!SWAP && p.tma_out) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // the staging block is read, the stores are done
   }
   if (SWAP && p.cluster > 1 && !push) {
@@ -1095,7 +1120,10 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   // Many tokens, one CTA per tile's write-out: the result leaves by TMA (rows of 16-byte multiples from a 16-byte base)
   CUtensorMap mo = mx;
   const int es = out_f32 ? 4 : 2, out_cols = accumulate == 2 ? N / 2 : N;
-  p.tma_out = (!swap && p.cluster == 1 && !(accumulate == 2 && out_f32) && ((uintptr_t)out % 16 == 0) && ((long long)ldo * es) % 16 == 0) ? 1 : 0;
+  // (a cluster's CTAs each write a share of the columns: whole 128-byte rows of it, or per-thread stores)
+  const int share_cols = bn / (p.cluster > 0 ? p.cluster : 1);
+  const bool whole_rows = p.cluster == 1 || (accumulate == 2 ? share_cols % 128 == 0 : share_cols % (128 / es) == 0);
+  p.tma_out = (!swap && whole_rows && !(accumulate == 2 && out_f32) && ((uintptr_t)out % 16 == 0) && ((long long)ldo * es) % 16 == 0) ? 1 : 0;
   if (p.tma_out && make_out_map(&mo, out, M, out_cols, ldo, out_f32 != 0)) return -1;
 
   if (swap) {
