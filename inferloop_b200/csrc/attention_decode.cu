@@ -3,9 +3,13 @@
 // V tiles brought by TMA straight from the cache pages, the partial results merged through
 // the cluster's shared memory.
 //
-//   grid     (S, kv heads, sequences), clusters of S = 1..16 along x, S chosen so that all
+//   grid     (S, kv heads, sequences x Z), clusters of S = 1..16 along x, S chosen so that all
 //            CTAs of the launch are resident at once.  The visible keys are cut into 32-key
-//            tiles; tile i goes to CTA i % S of the cluster.
+//            tiles; tile i goes to CTA i % S of the cluster.  Few sequences with many keys
+//            (the caller says so): Z = 2..8 clusters share a (sequence, kv head), each taking a
+//            contiguous run of its tiles, as many of them as the sequence's length calls for;
+//            their merged records meet in a scratch buffer and the owner that takes the last
+//            ticket of its rows adds them in the order of the runs (no CTA waits for another).
 //   warp 2   producer: 8 lanes look up the pages of a tile (lookups of the next four tiles are
 //            always in flight) and issue its boxes: K and V, each as one box per page part
 //            and 64-wide slice of the head, 128-byte swizzle, into a ring of 3 to 12 stages guarded
@@ -50,6 +54,7 @@ constexpr int kMaxSplit = 16;          // CTAs of a cluster: 1, 2, 4, 8 or 16
 constexpr int kConsumers = 2;          // warps, 16 keys of a tile each
 constexpr int kThreads = (kConsumers + 1) * 32;
 constexpr int kAhead = 4;              // tiles whose page lookups are in flight
+constexpr int kChunkTiles = 8;         // tiles a CTA should have before another cluster joins its sequence
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct Params {
@@ -59,6 +64,12 @@ struct Params {
   int max_blocks, n_seqs, nq, nkv, window, q_stride, out_stride, page_size, num_pages;
   int split;                           // CTAs of a cluster = ways a sequence's tiles are dealt out
   int rows_cap;                        // rows of the group that one CTA of the cluster owns at most
+  // Few sequences with many keys: `chunks` clusters share a (sequence, kv head), each taking a
+  // contiguous run of its tiles (as many of them as leave kChunkTiles tiles to every CTA).
+  // Their merged records meet in `scratch` [sequence][kv head][chunk][16][D + 2]; the owner
+  // that takes the last ticket of its rows (`counters` [sequence][kv head][16], zero between
+  // launches) adds them in chunk order and writes the result.
+  int chunks; float* scratch; int* counters;
   float scale_log2;
   // Fused input stage (qkv != null): q, k, v of the step's token are taken from the fused
   // projection output; per-head RMSNorm (weights may be null) and the rotation (table may be
@@ -335,15 +346,21 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
   if (!(stream_early && (threadIdx.x >> 5) == kConsumers)) pdl_wait();
 
   const int G = p.nq / p.nkv;
-  const int rank = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+  const int rank = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z / p.chunks, chunk = blockIdx.z % p.chunks;
   const int tok = p.cu_q[seq];
   if (p.cu_q[seq + 1] - tok != 1) return;                  // the whole cluster leaves together
   const int pos = p.positions[tok];
   const int lo = (p.window > 0 && pos + 1 > p.window) ? pos + 1 - p.window : 0;
   const int hi = pos + 1;
-  const int first_tile = lo / kKeys;
-  const int n_tiles = (hi + kKeys - 1) / kKeys - first_tile;
   const int kSplit = p.split;
+  const int all_tiles = (hi + kKeys - 1) / kKeys - lo / kKeys;
+  // the clusters that take part for this sequence, and this one's run of tiles
+  int chunks_on = all_tiles / (kSplit * kChunkTiles);
+  chunks_on = chunks_on < 1 ? 1 : (chunks_on > p.chunks ? p.chunks : chunks_on);
+  if (chunk >= chunks_on) return;                          // (the whole cluster: nothing has been sent yet)
+  const int per_chunk = (all_tiles + chunks_on - 1) / chunks_on;
+  const int first_tile = lo / kKeys + chunk * per_chunk;
+  const int n_tiles = min(per_chunk, all_tiles - chunk * per_chunk);
   const int n_my = rank < n_tiles ? (n_tiles - rank + kSplit - 1) / kSplit : 0;
   const int* table = p.block_table + (size_t)seq * p.max_blocks;
   const int rows16 = (G + 15) / 16 * 16;
@@ -552,7 +569,47 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
             l_all += rcd[D + 1] * f;
             o += rcd[c] * f;
           }
-          p.out[(size_t)tok * p.out_stride + (size_t)(kvh * G + row) * D + c] = __float2bfloat16_rn(l_all > 0.f ? o / l_all : 0.f);
+          if (chunks_on == 1) {
+            p.out[(size_t)tok * p.out_stride + (size_t)(kvh * G + row) * D + c] = __float2bfloat16_rn(l_all > 0.f ? o / l_all : 0.f);
+          } else {
+            // this cluster's record of the row, for the owner that comes last
+            float* rcd = p.scratch + ((((size_t)seq * p.nkv + kvh) * p.chunks + chunk) * 16 + row) * (D + 2);
+            rcd[c] = o;
+            if (c == 0) { rcd[D] = m_all; rcd[D + 1] = l_all; }
+          }
+        }
+        if (chunks_on > 1) {
+          // One ticket per (sequence, kv head, owner): the owners of the same rows in the other
+          // clusters take theirs when their records are written; the last one adds the records
+          // in the order of the chunks.  Nobody waits for anybody.
+          volatile int& last_ticket = const_cast<volatile int*>(failed)[1];    // the flag's word neighbour
+          __threadfence();
+          __syncthreads();
+          if (threadIdx.x == 0) {
+            int* counter = p.counters + ((size_t)seq * p.nkv + kvh) * 16 + rank;
+            const int t = atomicAdd(counter, 1);
+            last_ticket = (t == chunks_on - 1) ? 1 : 0;
+            if (t == chunks_on - 1) *counter = 0;            // ready for the next launch
+          }
+          __syncthreads();
+          if (last_ticket) {
+            __threadfence();
+            const float* base_rec = p.scratch + (((size_t)seq * p.nkv + kvh) * p.chunks) * 16 * (D + 2);
+            for (int e = threadIdx.x; e < rows_mine * D; e += kThreads) {
+              const int c = e % D, row = (e / D) * kSplit + rank;
+              float m_all = -INFINITY;
+              for (int z = 0; z < chunks_on; ++z) m_all = fmaxf(m_all, __ldcg(base_rec + ((size_t)z * 16 + row) * (D + 2) + D));
+              float l_all = 0.f, o = 0.f;
+              for (int z = 0; z < chunks_on; ++z) {
+                const float* rcd = base_rec + ((size_t)z * 16 + row) * (D + 2);
+                const float m = __ldcg(rcd + D);
+                const float f = (m == -INFINITY) ? 0.f : exp2f(m - m_all);
+                l_all += __ldcg(rcd + D + 1) * f;
+                o += __ldcg(rcd + c) * f;
+              }
+              p.out[(size_t)tok * p.out_stride + (size_t)(kvh * G + row) * D + c] = __float2bfloat16_rn(l_all > 0.f ? o / l_all : 0.f);
+            }
+          }
         }
       }
       return;
@@ -693,28 +750,50 @@ int active_clusters(int split, size_t extra) {
 template <int D, int STAGES>
 int launch(const CUtensorMap (&m)[4], const Params& p, size_t extra, cudaStream_t stream) {
   if (configure<D, STAGES>()) return -1;
-  ilb::launch_cluster(decode_kernel<D, STAGES>, dim3(p.split, p.nkv, p.n_seqs), dim3(kThreads), ring_bytes<D, STAGES>() + extra, stream,
+  ilb::launch_cluster(decode_kernel<D, STAGES>, dim3(p.split, p.nkv, p.n_seqs * p.chunks), dim3(kThreads), ring_bytes<D, STAGES>() + extra, stream,
                       p.split, m[0], m[1], m[2], m[3], p);
   return check_launch("attention decode");
 }
 
 // The ways a sequence's tiles are dealt out and the depth of the tile ring: as many CTAs as
 // fit the device at once, and the shared memory that this leaves to each of them.
+constexpr int kMaxChunks = 8;
+
+// `long_context`: the step's longest sequence is long enough for several clusters per
+// (sequence, kv head) to pay; the launch is then shaped for the most CTAs at work, not for the
+// widest cluster.
 template <int D>
-void plan_for(int n_seqs, int nq, int nkv, int& split, int& stages) {
+void plan_for(int n_seqs, int nq, int nkv, int long_context, int& split, int& stages, int& chunks) {
   const long long pairs = (long long)n_seqs * nkv;
   const int group = nq / nkv;
   split = kMaxSplit;
   while (split > 1 && active_clusters<D, 3>(split, inbox_bytes(D, group, split)) < pairs) split /= 2;
+  chunks = 1;
+  if (long_context && split > 1 && group <= 16) {
+    long long best = 0;
+    int best_split = split;
+    for (int s = split; s >= 2; s /= 2) {
+      long long c = active_clusters<D, 3>(s, inbox_bytes(D, group, s)) / pairs;
+      c = c > kMaxChunks ? kMaxChunks : c;
+      if (c * s > best) { best = c * s; best_split = s; chunks = (int)c; }
+    }
+    split = best_split;
+  }
   const size_t extra = inbox_bytes(D, group, split);
-  stages = active_clusters<D, 12>(split, extra) >= pairs ? 12 : active_clusters<D, 6>(split, extra) >= pairs ? 6 : 3;
+  const long long clusters = pairs * chunks;
+  stages = active_clusters<D, 12>(split, extra) >= clusters ? 12 : active_clusters<D, 6>(split, extra) >= clusters ? 6 : 3;
 }
 
 template <int D>
-int launch_for(const CUtensorMap (&m)[4], Params& p, cudaStream_t stream) {
+int launch_for(const CUtensorMap (&m)[4], Params& p, int long_context, long long scratch_floats, long long n_counters, cudaStream_t stream) {
   int stages = 3;
-  plan_for<D>(p.n_seqs, p.nq, p.nkv, p.split, stages);
+  plan_for<D>(p.n_seqs, p.nq, p.nkv, long_context, p.split, stages, p.chunks);
   const int group = p.nq / p.nkv;
+  if (p.chunks > 1) {
+    const long long need_f = (long long)p.n_seqs * p.nkv * p.chunks * 16 * (D + 2), need_c = (long long)p.n_seqs * p.nkv * 16;
+    if (p.scratch == nullptr || p.counters == nullptr || need_f > scratch_floats || need_c > n_counters)
+      plan_for<D>(p.n_seqs, p.nq, p.nkv, 0, p.split, stages, p.chunks);       // no room for the records: one cluster each
+  }
   p.rows_cap = rows_cap_of(group, p.split);
   const size_t extra = inbox_bytes(D, group, p.split);
   if (stages == 12) return launch<D, 12>(m, p, extra, stream);
@@ -731,18 +810,28 @@ ILB_EXPORT int ilb_attention_decode_tma_supported(int nq, int nkv, int d, int pa
 }
 
 // The cluster size and ring depth a launch of this geometry would get (for tests and notes).
-ILB_EXPORT int ilb_attention_decode_plan(int n_seqs, int nq, int nkv, int d, int page_size, int* split, int* stages) {
-  ILB_REQUIRE(ilb_attention_decode_tma_supported(nq, nkv, d, page_size) && n_seqs > 0 && split && stages, "attention decode: no plan for this geometry");
-  if (d == 64) plan_for<64>(n_seqs, nq, nkv, *split, *stages); else plan_for<128>(n_seqs, nq, nkv, *split, *stages);
+ILB_EXPORT int ilb_attention_decode_plan(int n_seqs, int nq, int nkv, int d, int page_size, int long_context, int* split, int* stages,
+                                         int* chunks) {
+  ILB_REQUIRE(ilb_attention_decode_tma_supported(nq, nkv, d, page_size) && n_seqs > 0 && split && stages && chunks,
+              "attention decode: no plan for this geometry");
+  if (d == 64) plan_for<64>(n_seqs, nq, nkv, long_context, *split, *stages, *chunks);
+  else plan_for<128>(n_seqs, nq, nkv, long_context, *split, *stages, *chunks);
   return 0;
 }
+
+// 32-bit elements of scratch and counters that a launch of this geometry can use (it runs
+// without them, one cluster per sequence and kv head, when given less).
+ILB_EXPORT long long ilb_attention_decode_scratch_floats(int n_seqs, int nkv, int d) {
+  return (long long)n_seqs * nkv * kMaxChunks * 16 * (d + 2);
+}
+ILB_EXPORT long long ilb_attention_decode_counters(int n_seqs, int nkv) { return (long long)n_seqs * nkv * 16; }
 
 namespace {
 int decode_common(const void* q, const void* qkv, int qkv_stride, const float* q_weight, const float* k_weight, float eps,
                   const float* rope, int write_kv, void* out, const void* k_cache, const void* v_cache, const int* positions,
                   const int* cu_q, const int* block_table, int max_blocks, int page_size, int num_pages, int window,
-                  float scale, int n_seqs, int nq, int nkv, int d, int q_stride, int out_stride, int* error_flag,
-                  cudaStream_t stream) {
+                  float scale, int n_seqs, int nq, int nkv, int d, int q_stride, int out_stride, int long_context,
+                  float* scratch, long long scratch_floats, int* counters, long long n_counters, int* error_flag, cudaStream_t stream) {
   ILB_REQUIRE(ilb_attention_decode_tma_supported(nq, nkv, d, page_size),
               "attention decode: heads %d/%d, head size %d, page size %d are not built", nq, nkv, d, page_size);
   ILB_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && nkv <= 65535 && max_blocks > 0 && num_pages > 0 && window >= 0,
@@ -769,7 +858,9 @@ int decode_common(const void* q, const void* qkv, int qkv_stride, const float* q
   p.rope = (const float2*)rope;
   p.k_write = (qkv != nullptr && write_kv) ? (__nv_bfloat16*)const_cast<void*>(k_cache) : nullptr;
   p.v_write = (qkv != nullptr && write_kv) ? (__nv_bfloat16*)const_cast<void*>(v_cache) : nullptr;
-  return d == 64 ? launch_for<64>(m, p, stream) : launch_for<128>(m, p, stream);
+  p.chunks = 1; p.scratch = scratch; p.counters = counters;
+  return d == 64 ? launch_for<64>(m, p, long_context, scratch_floats, n_counters, stream)
+                 : launch_for<128>(m, p, long_context, scratch_floats, n_counters, stream);
 }
 }  // namespace
 
@@ -777,10 +868,11 @@ ILB_EXPORT int ilb_attention_decode_tma(const void* q, void* out, const void* k_
                                         const int* positions, const int* cu_q, const int* block_table,
                                         int max_blocks, int page_size, int num_pages, int window, float scale,
                                         int n_seqs, int nq, int nkv, int d, int q_stride, int out_stride,
+                                        int long_context, float* scratch, long long scratch_floats, int* counters, long long n_counters,
                                         int* error_flag, cudaStream_t stream) {
   return decode_common(q, nullptr, 0, nullptr, nullptr, 1.f, nullptr, 0, out, k_cache, v_cache, positions, cu_q, block_table,
-                       max_blocks, page_size, num_pages, window, scale, n_seqs, nq, nkv, d, q_stride, out_stride, error_flag,
-                       stream);
+                       max_blocks, page_size, num_pages, window, scale, n_seqs, nq, nkv, d, q_stride, out_stride, long_context,
+                       scratch, scratch_floats, counters, n_counters, error_flag, stream);
 }
 
 // The same with the step's q/k/v taken from the fused projection output `qkv`
@@ -791,12 +883,13 @@ ILB_EXPORT int ilb_attention_decode_fused(const void* qkv, int qkv_stride, const
                                           float eps, const float* rope, int write_kv, void* out, void* k_cache,
                                           void* v_cache, const int* positions, const int* cu_q, const int* block_table,
                                           int max_blocks, int page_size, int num_pages, int window, float scale,
-                                          int n_seqs, int nq, int nkv, int d, int out_stride, int* error_flag,
+                                          int n_seqs, int nq, int nkv, int d, int out_stride, int long_context,
+                                          float* scratch, long long scratch_floats, int* counters, long long n_counters, int* error_flag,
                                           cudaStream_t stream) {
   ILB_REQUIRE(qkv != nullptr, "attention decode: no projection output");
   return decode_common(nullptr, qkv, qkv_stride, q_weight, k_weight, eps, rope, write_kv, out, k_cache, v_cache, positions,
                        cu_q, block_table, max_blocks, page_size, num_pages, window, scale, n_seqs, nq, nkv, d, 0, out_stride,
-                       error_flag, stream);
+                       long_context, scratch, scratch_floats, counters, n_counters, error_flag, stream);
 }
 
 ILB_DEFINE_LAST_ERROR()

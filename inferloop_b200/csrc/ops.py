@@ -233,6 +233,9 @@ class _TcState:
         self.workspace = torch.empty(self.floats, dtype=torch.float32, device=device)
         self.tickets = torch.zeros(self.n_tickets, dtype=torch.int32, device=device)
         self.error = torch.zeros(1, dtype=torch.int32, device=device)
+        # decode attention of few, long sequences: records of the clusters that share a sequence, and their tickets
+        self.attn_scratch = torch.empty(1 << 20, dtype=torch.float32, device=device)
+        self.attn_counters = torch.zeros(1 << 14, dtype=torch.int32, device=device)
 
 
 _TC: dict = {}
@@ -366,18 +369,26 @@ def attention_decode_tma_supported(nq: int, nkv: int, d: int, page_size: int) ->
     return nkv > 0 and nq > 0 and nq % nkv == 0 and d in (64, 128) and page_size in (16, 32, 64, 128)
 
 
-def attention_decode_plan(n_seqs: int, nq: int, nkv: int, d: int, page_size: int) -> tuple:
-    """(CTAs of a cluster, stages of the tile ring) that a decode step of this geometry gets."""
+# A decode step whose longest sequence holds at least this many keys is launched for the most
+# CTAs at work: narrower clusters, several of them sharing a (sequence, kv head) when the
+# sequences are few.  Recorded decode graphs are kept apart by this flag.
+DECODE_LONG_CONTEXT = 8192
+
+
+def attention_decode_plan(n_seqs: int, nq: int, nkv: int, d: int, page_size: int, long_context: bool = False) -> tuple:
+    """(CTAs of a cluster, stages of the tile ring, clusters that may share a long sequence)
+    that a decode step of this geometry gets."""
     lib = load_module("attention_decode")
-    split, stages = ctypes.c_int(0), ctypes.c_int(0)
+    split, stages, chunks = ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
     lib.ilb_attention_decode_plan.restype = ctypes.c_int
-    if lib.ilb_attention_decode_plan(_i(n_seqs), _i(nq), _i(nkv), _i(d), _i(page_size), ctypes.byref(split), ctypes.byref(stages)) != 0:
+    if lib.ilb_attention_decode_plan(_i(n_seqs), _i(nq), _i(nkv), _i(d), _i(page_size), _i(1 if long_context else 0), ctypes.byref(split),
+                                     ctypes.byref(stages), ctypes.byref(chunks)) != 0:
         raise KernelError(lib.ilb_last_error().decode())
-    return split.value, stages.value
+    return split.value, stages.value, chunks.value
 
 
 def attention_decode_tma(q, out, k_cache, v_cache, positions, cu_q, block_table, window, scale, n_seqs,
-                         nq, nkv, d) -> None:
+                         nq, nkv, d, long_context: bool = False) -> None:
     """Split-KV decode whose tiles come by TMA and whose partial results meet inside a
     thread-block cluster (no scratch)."""
     for t, w in ((q, "q"), (out, "out"), (k_cache, "k cache"), (v_cache, "v cache")):
@@ -387,7 +398,8 @@ def attention_decode_tma(q, out, k_cache, v_cache, positions, cu_q, block_table,
     _call("attention_decode", "ilb_attention_decode_tma", _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache),
           _ptr(positions), _ptr(cu_q), _ptr(block_table), _i(block_table.shape[1]), _i(page_size),
           _i(num_pages), _i(window or 0), _f(scale), _i(n_seqs), _i(nq), _i(nkv), _i(d), _i(q.shape[1]),
-          _i(out.shape[1]), _ptr(st.error), _stream(q))
+          _i(out.shape[1]), _i(1 if long_context else 0), _ptr(st.attn_scratch), ctypes.c_longlong(st.attn_scratch.numel()), _ptr(st.attn_counters),
+          ctypes.c_longlong(st.attn_counters.numel()), _ptr(st.error), _stream(q))
 
 
 def attention_decode_fused_supported(dtype: torch.dtype, cache_dtype: torch.dtype, nq: int, nkv: int, d: int,
@@ -400,7 +412,7 @@ def attention_decode_fused_supported(dtype: torch.dtype, cache_dtype: torch.dtyp
 
 
 def attention_decode_fused(qkv, out, q_weight, k_weight, eps, rope_table, k_cache, v_cache, write_kv, positions, cu_q,
-                           block_table, window, scale, n_seqs, nq, nkv, d) -> None:
+                           block_table, window, scale, n_seqs, nq, nkv, d, long_context: bool = False) -> None:
     """Decode attention with the per-head q/k norm, the rotation and the cache write of the
     step's own key and value inside the attention kernel (one launch instead of two)."""
     for t, w in ((qkv, "qkv"), (out, "out"), (k_cache, "k cache"), (v_cache, "v cache")):
@@ -414,7 +426,9 @@ def attention_decode_fused(qkv, out, q_weight, k_weight, eps, rope_table, k_cach
           _f(eps if eps and eps > 0 else 1e-6), _ptr(rope_table), _i(1 if write_kv else 0), _ptr(out), _ptr(k_cache),
           _ptr(v_cache), _ptr(positions),
           _ptr(cu_q), _ptr(block_table), _i(block_table.shape[1]), _i(page_size), _i(num_pages), _i(window or 0),
-          _f(scale), _i(n_seqs), _i(nq), _i(nkv), _i(d), _i(out.shape[1]), _ptr(st.error), _stream(qkv))
+          _f(scale), _i(n_seqs), _i(nq), _i(nkv), _i(d), _i(out.shape[1]), _i(1 if long_context else 0), _ptr(st.attn_scratch),
+          ctypes.c_longlong(st.attn_scratch.numel()), _ptr(st.attn_counters), ctypes.c_longlong(st.attn_counters.numel()),
+          _ptr(st.error), _stream(qkv))
 
 
 def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -432,7 +446,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
     G = nq // nkv
     if step.decode_only and DECODE_CLUSTER_ENABLED and attention_decode_tma_supported(nq, nkv, d, k_cache.shape[2]):
         attention_decode_tma(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
-                             step.n_seqs, nq, nkv, d)
+                             step.n_seqs, nq, nkv, d, getattr(step, "max_kv_len", 0) >= DECODE_LONG_CONTEXT)
     elif step.decode_only:
         page_size = k_cache.shape[2]
         capacity = block_table.shape[1] * page_size

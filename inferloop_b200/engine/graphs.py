@@ -65,6 +65,17 @@ class DecodeGraphs:
     def eligible(entries: Sequence[StepEntry]) -> bool:
         return all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
 
+    def _key(self, entries: Sequence[StepEntry], bucket: int, with_argmax: bool) -> tuple:
+        """Recorded graphs are kept apart by size, by what follows the logits, and, for the
+        few-sequence sizes whose attention launch depends on it, by whether the longest
+        sequence has reached ops.DECODE_LONG_CONTEXT keys."""
+        long_context = False
+        if bucket <= 4:
+            cache = self.runner.cache
+            long_context = any(cache.has(e.request) and cache.length(e.request) + 1 >= ops.DECODE_LONG_CONTEXT
+                               for e in entries)
+        return (bucket, with_argmax, long_context)
+
     def _shapes(self, bucket: int) -> List[tuple]:
         groups = len(self.runner.cache.groups)
         return [(bucket,), (bucket,), (bucket,), (bucket + 1,), (bucket,), (bucket,), (bucket,)] + \
@@ -144,7 +155,7 @@ class DecodeGraphs:
         bucket = bucket_for(n)
         if bucket is None:
             raise ValueError(f"{n} sequences exceed the largest decode bucket {BUCKETS[-1]}")
-        key = (bucket, with_argmax)
+        key = self._key(entries, bucket, with_argmax)
         rec = self._recorded.get(key)
         if rec is not None and rec.workspace_generation != self.runner.ctx.workspace.generation:
             del self._recorded[key]
@@ -169,7 +180,7 @@ class DecodeGraphs:
         bucket = bucket_for(n)
         if bucket is None:
             return None
-        rec = self._recorded.get((bucket, True))
+        rec = self._recorded.get(self._key(entries, bucket, True))
         if rec is None or rec.workspace_generation != self.runner.ctx.workspace.generation:
             return None
         try:
@@ -182,7 +193,12 @@ class DecodeGraphs:
         return rec.drawn[:n]
 
     def recorded(self, n: int, with_argmax: bool) -> Optional[_Recorded]:
-        return self._recorded.get((bucket_for(n), with_argmax))
+        """The graph recorded for this many sequences (the short-context one if both exist)."""
+        for long_context in (False, True):
+            rec = self._recorded.get((bucket_for(n), with_argmax, long_context))
+            if rec is not None:
+                return rec
+        return None
 
     def run_greedy(self, entries: Sequence[StepEntry], n_steps: int) -> torch.Tensor:
         """`n_steps` greedy decode steps back to back without a host round trip: each
@@ -211,7 +227,7 @@ class DecodeGraphs:
         for e in entries:
             r.cache.ensure(e.request, r.cache.length(e.request) + n_steps)
         out = torch.empty((n_steps, bucket), dtype=torch.int32, device=r.device)
-        key = (bucket, True)
+        key = self._key(entries, bucket, True)
         rec = self._recorded.get(key)
         if rec is not None and rec.workspace_generation != r.ctx.workspace.generation:
             del self._recorded[key]

@@ -99,7 +99,8 @@ class GQAttention(Mixer):
             o = ws.buffer("attn.o", (T, self.nq * self.d), dt)
             ops.attention_decode_fused(qkv, o, self.q_norm, self.k_norm, self.qk_norm_eps, rope, cache.k, cache.v,
                                        cache.writable, step.positions, step.cu_q, table, self.window or 0, self.scale,
-                                       step.n_seqs, self.nq, self.nkv, self.d)
+                                       step.n_seqs, self.nq, self.nkv, self.d,
+                                       long_context=step.max_kv_len >= ops.DECODE_LONG_CONTEXT)
             linear(o, self.w_o, residual, self.b_o, accumulate=True)
             return
         q = ws.buffer("attn.q", (T, self.nq * self.d), dt)

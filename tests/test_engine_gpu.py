@@ -188,6 +188,34 @@ def test_long_decoding(folders, dtype, tmp_path):
     assert_close(torch.cat(got), ref, dtype, "long decoding")
 
 
+def test_decoding_across_the_long_context_mark(folders, monkeypatch):
+    """A sequence that grows past ops.DECODE_LONG_CONTEXT (lowered here) gets a second recorded
+    graph whose attention launch is shaped for long sequences (narrower clusters, several per
+    sequence and kv head when it is long enough); the logits stay those of the plain model on
+    both sides of the mark, and a second request beside it changes nothing."""
+    from inferloop_b200.csrc import ops
+    from inferloop_b200.engine import ModelRunner, StepEntry
+    monkeypatch.setattr(ops, "DECODE_LONG_CONTEXT", 600)
+    cfg = CONFIGS["D"][0]
+    toks = random_tokens(1400, cfg["vocab_size"], 77)
+    other = random_tokens(40, cfg["vocab_size"], 78)
+    ref = plain.PlainModel(folders["D"], round_to_bf16=True).logits(toks)
+    r = ModelRunner.from_folder(folders["D"], dtype="bfloat16", page_size=16, num_pages=120, max_requests=2)
+    got = [r.step([StepEntry("x", toks[:560], [559])]).float().cpu().clone()]
+    keys_before = set(r.graphs._recorded)
+    for i in range(560, 640):
+        got.append(r.step([StepEntry("x", [toks[i]], [0])]).float().cpu().clone())
+    assert {k[2] for k in r.graphs._recorded} == {False, True} and len(r.graphs._recorded) == len(keys_before) + 2
+    got.append(r.step([StepEntry("x", toks[640:1300], [659])]).float().cpu().clone())
+    r.step([StepEntry("y", other, [])])
+    for i in range(1300, 1400):               # 41 tiles and more: two clusters share each kv head
+        out = r.step([StepEntry("x", [toks[i]], [0]), StepEntry("y", [other[i % 40]], [0])])
+        got.append(out[:1].float().cpu().clone())
+    rows = [559] + list(range(560, 640)) + [1299] + list(range(1300, 1400))
+    assert_close(torch.cat(got), ref[rows], "bfloat16", "across the long-context mark")
+    ops.check_device_errors()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_the_first_tokens_of_a_sequence(folders, requests_of, name, dtype):

@@ -379,7 +379,8 @@ def test_decode_attention_plan_keeps_the_launch_resident():
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     last = 17
     for n_seqs in (1, 2, 4, 8, 16, 64, 256):
-        split, stages = o.attention_decode_plan(n_seqs, 32, 8, 128, 16)
+        split, stages, chunks = o.attention_decode_plan(n_seqs, 32, 8, 128, 16)
+        assert 1 <= chunks <= 8 and (chunks == 1 or split == 16)
         assert split in (1, 2, 4, 8, 16) and stages in (3, 6, 12)
         assert split <= last                      # more sequences never widen the clusters
         assert split == 1 or split * n_seqs * 8 <= 4 * sms, (n_seqs, split, stages)
@@ -478,10 +479,26 @@ def test_decode_attention_with_the_input_stage_inside(nq, nkv, d, page_size, win
     norm, rotation, the cache write of the new key and value, and attention over old keys plus
     the new one.  Lengths put the new position at the start, the middle and the end of a
     32-key tile and of a page, and on tiles of every CTA of the cluster."""
+    run_fused_decode(nq, nkv, d, page_size, window, use_norm, use_rope, [1, 2, 16, 17, 32, 33, 48, 64, 65, 100, 257, 700, 1031])
+
+
+@pytest.mark.parametrize("lens,window", [([9000], 0), ([5000, 70], 0), ([3, 8200], 3000), ([4100, 4200, 300], 0)])
+def test_decode_attention_of_few_long_sequences(lens, window):
+    """With few sequences several clusters share one (sequence, kv head): each takes a run of
+    the tiles, their records meet in a scratch buffer and the owner with the last ticket adds
+    them.  Short sequences in the same launch keep to one cluster; a window moves the runs."""
+    o = ops()
+    split, stages, chunks = o.attention_decode_plan(len(lens), 32, 8, 128, 16, long_context=True)
+    assert chunks >= 2, "this device leaves no room for a second cluster per sequence"
+    run_fused_decode(32, 8, 128, 16, window, True, True, lens, long_context=True)
+    from inferloop_b200.csrc.ops import _tc_state
+    assert int(_tc_state(torch.device("cuda", 0)).attn_counters.abs().sum()) == 0       # tickets are back at zero
+
+
+def run_fused_decode(nq, nkv, d, page_size, window, use_norm, use_rope, lens, long_context=False):
     o = ops()
     torch.manual_seed(nq + d + page_size)
     eps, theta = 1e-6, 1e4
-    lens = [1, 2, 16, 17, 32, 33, 48, 64, 65, 100, 257, 700, 1031]
     S = len(lens)
     G = nq // nkv
     old = [(torch.randn(n - 1, nkv, d).to(torch.bfloat16).double(), torch.randn(n - 1, nkv, d).to(torch.bfloat16).double()) for n in lens]
@@ -518,7 +535,7 @@ def test_decode_attention_with_the_input_stage_inside(nq, nkv, d, page_size, win
     for _ in range(2):                       # the second run finds the new key already in the cache: same answer
         o.attention_decode_fused(qkv.cuda(), out, qw.cuda() if use_norm else None, kw.cuda() if use_norm else None, eps,
                                  table if use_rope else None, k_cache, v_cache, True, positions.cuda(), cu, btable.cuda(),
-                                 window, 1.0 / math.sqrt(d), S, nq, nkv, d)
+                                 window, 1.0 / math.sqrt(d), S, nq, nkv, d, long_context=long_context)
     o.check_device_errors()
     ref = torch.stack([ref_attention(q_new[s], torch.cat([old[s][0], k_new[s:s + 1]]), torch.cat([old[s][1], v_new[s:s + 1]]),
                                      lens[s] - 1, window).reshape(-1) for s in range(S)])
