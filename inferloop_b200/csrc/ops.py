@@ -33,7 +33,8 @@ def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
 
 
 def _stream(t: torch.Tensor) -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+    """torch's current stream on the tensor's device, as the raw handle the launchers take."""
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(t.device.index))
 
 
 def _need(t: Optional[torch.Tensor], what: str, dtype: Optional[torch.dtype] = None,
@@ -51,15 +52,21 @@ def _need(t: Optional[torch.Tensor], what: str, dtype: Optional[torch.dtype] = N
 LAUNCHES = 0          # kernels launched through this module since import
 
 
+_FUNCTIONS: dict = {}  # launcher name -> (function, its library)
+
+
 def _call(module: str, fn: str, *args) -> None:
     global LAUNCHES
     LAUNCHES += 1
-    lib = load_module(module)
-    f = getattr(lib, fn)
-    f.restype = ctypes.c_int
-    rc = f(*args)
+    entry = _FUNCTIONS.get(fn)
+    if entry is None:
+        lib = load_module(module)
+        f = getattr(lib, fn)
+        f.restype = ctypes.c_int
+        entry = _FUNCTIONS[fn] = (f, lib)
+    rc = entry[0](*args)
     if rc != 0:
-        raise KernelError(lib.ilb_last_error().decode())
+        raise KernelError(entry[1].ilb_last_error().decode())
 
 
 def _i(v) -> ctypes.c_int:
