@@ -473,7 +473,8 @@ def test_flash_decode_split_kv(nq, nkv, d, page_size, window, chunk, cluster):
 
 
 @pytest.mark.parametrize("nq,nkv,d,page_size,window,use_norm,use_rope", [(32, 8, 128, 16, 0, True, True), (8, 2, 64, 32, 50, True, True),
-                                                                         (40, 2, 128, 16, 0, False, True), (4, 4, 128, 64, 0, True, False)])
+                                                                         (40, 2, 128, 16, 0, False, True), (4, 4, 128, 64, 0, True, False),
+                                                                         (12, 2, 128, 16, 0, True, True), (3, 1, 64, 16, 7, True, True), (32, 2, 64, 32, 0, True, True)])
 def test_decode_attention_with_the_input_stage_inside(nq, nkv, d, page_size, window, use_norm, use_rope):
     """One launch takes q, k, v of the step's token from the fused projection output: per-head
     norm, rotation, the cache write of the new key and value, and attention over old keys plus
