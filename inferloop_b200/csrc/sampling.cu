@@ -15,6 +15,7 @@
 // differs, which can move the crossing point by rounding of the sums alone.
 #include <math.h>
 #include "common.cuh"
+#include "sm100.cuh"
 
 using namespace ilb;
 
@@ -24,6 +25,12 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
   return v > bv || (v == bv && i < bi);
 }
 
+// A row is shared by the kArgmaxCtas CTAs of a thread-block cluster (contiguous parts of the
+// vocabulary); each leaves its best (value, index) and its flag in shared memory, and after a
+// cluster barrier CTA 0 takes the best of them from its peers' memory.  One CTA per row read
+// 600 KB by itself at Qwen3's vocabulary and took 14 us.
+constexpr int kArgmaxCtas = 8;
+
 __global__ void __launch_bounds__(kThreads)
 argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int* __restrict__ bad,
               int vocab, int stride) {
@@ -32,13 +39,18 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int* __re
   __shared__ float sv[32];
   __shared__ int si[32];
   __shared__ int sbad;
-  const float* row = logits + (size_t)blockIdx.x * stride;
+  __shared__ float best_v;             // this CTA's result, read by CTA 0 of the cluster
+  __shared__ int best_i, best_bad;
+  const int part = blockIdx.x, n_parts = gridDim.x;
+  const float* row = logits + (size_t)blockIdx.y * stride;
+  const int per = (vocab + n_parts - 1) / n_parts;
+  const int lo = part * per, hi = min(vocab, lo + per);
   if (threadIdx.x == 0) sbad = 0;
   __syncthreads();
   float bv = -INFINITY;
   int bi = 0x7fffffff;
   bool nonfinite = false;
-  for (int i = threadIdx.x; i < vocab; i += kThreads) {
+  for (int i = lo + threadIdx.x; i < hi; i += kThreads) {
     const float v = row[i];
     if (!isfinite(v)) nonfinite = true;
     if (better(v, i, bv, bi)) { bv = v; bi = i; }
@@ -61,18 +73,38 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int* __re
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
     }
+    if (lane == 0) { best_v = bv; best_i = bi; best_bad = sbad; }
+  }
+  cluster_sync_all();
+  if (part == 0 && warp == 0) {
+    float v = -INFINITY;
+    int i = 0x7fffffff, b = 0;
+    if (lane < n_parts) {
+      v = ld_peer_f32(smem_u32(&best_v), (uint32_t)lane);
+      i = __float_as_int(ld_peer_f32(smem_u32(&best_i), (uint32_t)lane));
+      b = __float_as_int(ld_peer_f32(smem_u32(&best_bad), (uint32_t)lane));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+      b |= __shfl_xor_sync(0xffffffffu, b, o);
+      if (better(ov, oi, v, i)) { v = ov; i = oi; }
+    }
     if (lane == 0) {
-      out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
-      if (bad != nullptr) bad[blockIdx.x] = sbad;
+      out[blockIdx.y] = i == 0x7fffffff ? 0 : i;
+      if (bad != nullptr) bad[blockIdx.y] = b;
     }
   }
+  cluster_sync_all();                  // nobody leaves while CTA 0 may still read its result
 }
 
 ILB_EXPORT int ilb_argmax(const float* logits, int* out, int* bad, int rows, int vocab, int stride,
                           cudaStream_t stream) {
-  ILB_REQUIRE(rows >= 0 && vocab > 0 && stride >= vocab, "argmax: bad sizes");
+  ILB_REQUIRE(rows >= 0 && rows <= 65535 && vocab > 0 && stride >= vocab, "argmax: bad sizes");
   if (rows == 0) return 0;
-  ilb::launch(argmax_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, out, bad, vocab, stride);
+  const int parts = vocab >= 8 * kThreads ? kArgmaxCtas : 1;      // a small vocabulary is one CTA's work
+  ilb::launch_cluster(argmax_kernel, dim3(parts, rows), dim3(kThreads), 0, stream, parts, logits, out, bad, vocab, stride);
   return check_launch("argmax");
 }
 
