@@ -216,11 +216,219 @@ sample_temperature_kernel(const float* __restrict__ logits, const float* __restr
   }
 }
 
+// ---------------------------------------------------------------- the same draw, shared by a cluster
+// One CTA walking a row of 150,000 logits 35 times, with a 64-bit exponential per element and
+// pass, took 8 to 12 ms.  Here a row belongs to a cluster of kSampleCtas CTAs (contiguous
+// parts of the vocabulary).  Every thread keeps the ordered keys of its elements in registers
+// and their 64-bit weights in shared memory, so a bisection pass is a compare and an add per
+// element, a block sum and one exchange over the cluster's shared memory; every CTA adds the
+// cluster's parts in the same order and so takes the same decisions.  The rule is the one
+// above: candidates from the highest logit down, lower index first among equals, the first
+// whose cumulative weight exceeds u.  Among equal logits the weights are equal, so the place
+// of the crossing among them is a count, and the element at that place is found by index.
+constexpr int kSampleCtas = 8;
+constexpr int kSampleRegs = 24;        // elements a thread can hold: vocabularies up to 8 * 1024 * 24
+
+__device__ __forceinline__ double ld_peer_f64(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  double v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f64 %0, [%1];" : "=d"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+// Sum (or maximum) of one value per thread over the whole cluster, the same bits in every
+// thread of every CTA.  `slots` [2] alternate between calls (`turn`), so that a CTA that is
+// already at its next call does not overwrite what a peer still reads.
+struct ClusterReduce {
+  double* scratch;                     // [34]
+  double* slots;                       // [2]
+  int n_parts, turn;
+  __device__ __forceinline__ double finish(double block_value, bool take_max) {
+    if (n_parts == 1) return block_value;
+    if (threadIdx.x == 0) slots[turn & 1] = block_value;
+    cluster_sync_all();
+    if (threadIdx.x == 0) {
+      double part[kSampleCtas];
+#pragma unroll
+      for (int q = 0; q < kSampleCtas; ++q) part[q] = q < n_parts ? ld_peer_f64(smem_u32(slots + (turn & 1)), (uint32_t)q) : 0.0;
+      double t = part[0];
+#pragma unroll
+      for (int q = 1; q < kSampleCtas; ++q)
+        if (q < n_parts) t = take_max ? fmax(t, part[q]) : t + part[q];
+      scratch[33] = t;
+    }
+    ++turn;
+    __syncthreads();
+    return scratch[33];
+  }
+  __device__ __forceinline__ double sum(double v) { return finish(block_sum_f64(v, scratch), false); }
+  __device__ __forceinline__ double max(double v) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmax(v, __shfl_xor_sync(0xffffffffu, v, o));
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+      double t = scratch[lane];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) t = fmax(t, __shfl_xor_sync(0xffffffffu, t, o));
+      if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return finish(scratch[32], true);
+  }
+};
+
+__global__ void __launch_bounds__(kThreads)
+sample_temperature_cluster_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+                                  const double* __restrict__ uniform, int* __restrict__ out,
+                                  int* __restrict__ bad, int vocab, int stride, int regs) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  extern __shared__ double weights[];                    // [regs][kThreads]
+  __shared__ double scratch[34];
+  __shared__ double slots[2];
+  const int part = blockIdx.x, n_parts = gridDim.x, t = threadIdx.x;
+  const float* row = logits + (size_t)blockIdx.y * stride;
+  const double inv_t = 1.0 / (double)temperature[blockIdx.y];
+  const double u = uniform[blockIdx.y];
+  const int per = (vocab + n_parts - 1) / n_parts;
+  const int lo_i = part * per, hi_i = min(vocab, lo_i + per);
+  ClusterReduce red{scratch, slots, n_parts, 0};
+  auto index_of = [&](int j) { return lo_i + j * kThreads + t; };
+
+  // the row's keys into registers; maximum and finiteness
+  unsigned key[kSampleRegs];
+  float mx = -INFINITY;
+  double nonfinite = 0.0;
+#pragma unroll
+  for (int j = 0; j < kSampleRegs; ++j) {
+    key[j] = 0u;                                         // below every real key
+    if (j < regs && index_of(j) < hi_i) {
+      const float v = row[index_of(j)];
+      if (!isfinite(v)) nonfinite = 1.0;
+      mx = fmaxf(mx, v);
+      key[j] = ordered_key(v);
+    }
+  }
+  const bool any_bad = red.sum(nonfinite) > 0.0;
+  if (any_bad) {                                         // (the same verdict in every CTA)
+    if (part == 0 && t == 0) { out[blockIdx.y] = 0; if (bad) bad[blockIdx.y] = 1; }
+    cluster_sync_all();
+    return;
+  }
+  const double mxd = red.max((double)mx);
+  auto value_of = [&](unsigned k) { return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k); };
+  // 64-bit weights, once
+  double mine = 0.0;
+#pragma unroll
+  for (int j = 0; j < kSampleRegs; ++j)
+    if (j < regs) {
+      const bool on = index_of(j) < hi_i;
+      const double w = on ? exp(((double)value_of(key[j]) - mxd) * inv_t) : 0.0;
+      weights[j * kThreads + t] = w;
+      mine += w;
+    }
+  const double target = u * red.sum(mine);
+  auto above_key = [&](unsigned k) {                     // weight of the logits whose key is above k
+    double a = 0.0;
+#pragma unroll
+    for (int j = 0; j < kSampleRegs; ++j)
+      if (j < regs && key[j] > k) a += weights[j * kThreads + t];
+    return red.sum(a);
+  };
+  // Bisection: the smallest key K with weight(> K) <= target; the crossing happens among the
+  // logits whose key equals it.
+  unsigned lo = 0u, hi = ordered_key((float)mxd);
+  while (lo < hi) {
+    const unsigned mid = lo + ((hi - lo) >> 1);
+    if (above_key(mid) <= target) hi = mid; else lo = mid + 1;
+  }
+  const double above = above_key(hi);
+  // the equals of the crossing value: how many, and the weight of one
+  double n_equal_mine = 0.0, w_equal_mine = 0.0;
+#pragma unroll
+  for (int j = 0; j < kSampleRegs; ++j)
+    if (j < regs && key[j] == hi && index_of(j) < hi_i) { n_equal_mine += 1.0; w_equal_mine = weights[j * kThreads + t]; }
+  const long long n_equal = (long long)red.sum(n_equal_mine);
+  const double w_equal = red.max(w_equal_mine);
+  // which key's equals hold the answer, and the place (1-based, by index) of the answer among them
+  unsigned pick_key = hi;
+  long long place = 1, count = n_equal;
+  if (n_equal > 0) {
+    // equals weigh the same: the cumulative weight after k of them is above + k w
+    long long k = w_equal > 0.0 ? (long long)floor((target - above) / w_equal) + 1 : n_equal;
+    k = k < 1 ? 1 : (k > n_equal ? n_equal : k);
+    while (k > 1 && target < above + (double)(k - 1) * w_equal) --k;
+    while (k < n_equal && !(target < above + (double)k * w_equal)) ++k;
+    place = k;                                           // never crossed: the last equal
+  } else {
+    // u at the very end: the last candidate of the walk, the lowest logit's highest index
+    double lowest = 4294967296.0;
+#pragma unroll
+    for (int j = 0; j < kSampleRegs; ++j)
+      if (j < regs && index_of(j) < hi_i) lowest = fmin(lowest, (double)key[j]);
+    pick_key = (unsigned)(-red.max(-lowest));
+    double n_mine = 0.0;
+#pragma unroll
+    for (int j = 0; j < kSampleRegs; ++j)
+      if (j < regs && index_of(j) < hi_i && key[j] == pick_key) n_mine += 1.0;
+    count = (long long)red.sum(n_mine);
+    place = count;
+  }
+  auto is_pick = [&](int j) { return j < regs && index_of(j) < hi_i && key[j] == pick_key; };
+  int chosen;
+  if (place == 1 || place == count) {
+    // the first or the last of the equals: one reduction over their indices
+    const double sign = place == 1 ? -1.0 : 1.0;         // (one equal: both are the same element)
+    double best = -4294967296.0;
+#pragma unroll
+    for (int j = 0; j < kSampleRegs; ++j)
+      if (is_pick(j)) best = fmax(best, sign * (double)index_of(j));
+    chosen = (int)(sign * red.max(best));
+  } else {
+    // the smallest index with `place` equals at or below it
+    int ilo = 0, ihi = vocab - 1;
+    while (ilo < ihi) {
+      const int mid = ilo + ((ihi - ilo) >> 1);
+      double n = 0.0;
+#pragma unroll
+      for (int j = 0; j < kSampleRegs; ++j)
+        if (is_pick(j) && index_of(j) <= mid) n += 1.0;
+      if ((long long)red.sum(n) >= place) ihi = mid; else ilo = mid + 1;
+    }
+    chosen = ilo;
+  }
+  if (part == 0 && t == 0) {
+    out[blockIdx.y] = chosen;
+    if (bad) bad[blockIdx.y] = 0;
+  }
+  cluster_sync_all();                                    // nobody leaves while a peer may still read its slot
+}
+
+
 ILB_EXPORT int ilb_sample_temperature(const float* logits, const float* temperature,
                                       const double* uniform, int* out, int* bad, int rows,
                                       int vocab, int stride, cudaStream_t stream) {
   ILB_REQUIRE(rows >= 0 && vocab > 0 && stride >= vocab, "sample_temperature: bad sizes");
   if (rows == 0) return 0;
+  const int parts = vocab >= 8 * kThreads ? kSampleCtas : 1;
+  const int per = (vocab + parts - 1) / parts, regs = (per + kThreads - 1) / kThreads;
+  if (regs <= kSampleRegs && rows <= 65535) {
+    const size_t smem = (size_t)regs * kThreads * sizeof(double);
+    static bool configured = false;
+    if (!configured) {
+      cudaFuncSetAttribute(sample_temperature_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)(kSampleRegs * kThreads * sizeof(double)));
+      configured = true;
+    }
+    ilb::launch_cluster(sample_temperature_cluster_kernel, dim3(parts, rows), dim3(kThreads), smem, stream, parts, logits,
+                        temperature, uniform, out, bad, vocab, stride, regs);
+    return check_launch("sample_temperature");
+  }
+  // a vocabulary beyond what the cluster's registers hold: one CTA per row walks it
   ilb::launch(sample_temperature_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, temperature, uniform, out, bad,
                                                            vocab, stride);
   return check_launch("sample_temperature");

@@ -67,7 +67,7 @@ def test_device_argmax(vocab):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("vocab", [320, 5003])
+@pytest.mark.parametrize("vocab", [320, 5003, 9000, 151936, 200003])
 def test_device_temperature_draw_equals_the_host_rule(vocab):
     from inferloop_b200.csrc import ops
     rows = 64
