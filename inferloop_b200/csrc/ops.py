@@ -217,14 +217,25 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, bad: Optional[torch.Tensor] 
           _i(logits.stride(0)), _stream(logits))
 
 
+def sample_filter_max_vocab() -> int:
+    """Largest vocabulary whose draws can be filtered (top-k, top-p, min-p) on the device."""
+    lib = load_module("sampling")
+    lib.ilb_sample_filter_max_vocab.restype = ctypes.c_int
+    return int(lib.ilb_sample_filter_max_vocab())
+
+
 def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
-                       out: torch.Tensor, bad: Optional[torch.Tensor] = None) -> None:
+                       out: torch.Tensor, bad: Optional[torch.Tensor] = None, top_k: Optional[torch.Tensor] = None,
+                       top_p: Optional[torch.Tensor] = None, min_p: Optional[torch.Tensor] = None) -> None:
+    """One draw per row from softmax(logits / T) by the reference's sorted-walk rule, after
+    its filters if given: top_k [rows] int32 (0 = none), top_p and min_p [rows] float32."""
     _need(logits, "sample logits", torch.float32); _need(temperature, "temperature", torch.float32)
     _need(uniform, "uniform", torch.float64); _need(out, "sample out", torch.int32)
-    _need(bad, "sample flags", torch.int32)
+    _need(bad, "sample flags", torch.int32); _need(top_k, "top-k", torch.int32)
+    _need(top_p, "top-p", torch.float32); _need(min_p, "min-p", torch.float32)
     rows, vocab = logits.shape
-    _call("sampling", "ilb_sample_temperature", _ptr(logits), _ptr(temperature), _ptr(uniform),
-          _ptr(out), _ptr(bad), _i(rows), _i(vocab), _i(logits.stride(0)), _stream(logits))
+    _call("sampling", "ilb_sample_temperature", _ptr(logits), _ptr(temperature), _ptr(uniform), _ptr(top_k), _ptr(top_p),
+          _ptr(min_p), _ptr(out), _ptr(bad), _i(rows), _i(vocab), _i(logits.stride(0)), _stream(logits))
 
 
 # --------------------------------------------------------------------------- tensor-core GEMM

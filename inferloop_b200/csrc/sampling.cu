@@ -283,8 +283,9 @@ struct ClusterReduce {
 
 __global__ void __launch_bounds__(kThreads)
 sample_temperature_cluster_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
-                                  const double* __restrict__ uniform, int* __restrict__ out,
-                                  int* __restrict__ bad, int vocab, int stride, int regs) {
+                                  const double* __restrict__ uniform, const int* __restrict__ top_k,
+                                  const float* __restrict__ top_p, const float* __restrict__ min_p,
+                                  int* __restrict__ out, int* __restrict__ bad, int vocab, int stride, int regs) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
   extern __shared__ double weights[];                    // [regs][kThreads]
@@ -331,7 +332,7 @@ sample_temperature_cluster_kernel(const float* __restrict__ logits, const float*
       weights[j * kThreads + t] = w;
       mine += w;
     }
-  const double target = u * red.sum(mine);
+  const double total_all = red.sum(mine);
   auto above_key = [&](unsigned k) {                     // weight of the logits whose key is above k
     double a = 0.0;
 #pragma unroll
@@ -339,25 +340,102 @@ sample_temperature_cluster_kernel(const float* __restrict__ logits, const float*
       if (j < regs && key[j] > k) a += weights[j * kThreads + t];
     return red.sum(a);
   };
+  auto count_above = [&](unsigned k) {                   // how many logits have a key above k (padding has key 0)
+    double n = 0.0;
+#pragma unroll
+    for (int j = 0; j < kSampleRegs; ++j)
+      if (j < regs && key[j] > k) n += 1.0;
+    return (long long)red.sum(n);
+  };
+  auto equals_of = [&](unsigned k, long long& n, double& w) {   // the logits with exactly this key: how many, the weight of one
+    double n_mine = 0.0, w_mine = 0.0;
+#pragma unroll
+    for (int j = 0; j < kSampleRegs; ++j)
+      if (j < regs && key[j] == k && index_of(j) < hi_i) { n_mine += 1.0; w_mine = weights[j * kThreads + t]; }
+    n = (long long)red.sum(n_mine);
+    w = red.max(w_mine);
+  };
+  // The candidates that stay are a PREFIX of the order (highest logit first, lower index first
+  // among equals): everything above key `pk` and the first `pc` of its equals; (0, 0) = all.
+  // top-k, min-p and top-p each name a prefix; the shortest holds.
+  unsigned pk = 0u;
+  long long pc = 0;
+  auto shorten = [&](unsigned k, long long c) {
+    if (k > pk || (k == pk && (pk == 0u || c < pc))) { pk = k; pc = c; }
+  };
+  const unsigned top_key = ordered_key((float)mxd);
+  const int k_limit = top_k ? top_k[blockIdx.y] : 0;
+  if (k_limit > 0 && k_limit < vocab) {
+    unsigned lo = 0u, hi = top_key;                      // the smallest key with fewer than k logits above it
+    while (lo < hi) {
+      const unsigned mid = lo + ((hi - lo) >> 1);
+      if (count_above(mid) <= (long long)k_limit - 1) hi = mid; else lo = mid + 1;
+    }
+    shorten(hi, (long long)k_limit - count_above(hi));
+  }
+  const double floor_w = min_p ? (double)min_p[blockIdx.y] : 0.0;
+  if (floor_w > 0.0) {
+    // weights fall with the logit: the leading run with weight >= min_p ends at the lowest such key (the best always stays)
+    double lowest = 4294967296.0;
+#pragma unroll
+    for (int j = 0; j < kSampleRegs; ++j)
+      if (j < regs && index_of(j) < hi_i && (weights[j * kThreads + t] >= floor_w || key[j] == top_key))
+        lowest = fmin(lowest, (double)key[j]);
+    const unsigned km = (unsigned)(-red.max(-lowest));
+    long long n;
+    double w;
+    equals_of(km, n, w);
+    shorten(km, n);
+  }
+  auto prefix_weight = [&]() {
+    if (pk == 0u) return total_all;
+    long long n;
+    double w;
+    equals_of(pk, n, w);
+    return above_key(pk) + (double)pc * w;
+  };
+  const double mass = top_p ? (double)top_p[blockIdx.y] : 1.0;
+  if (mass < 1.0) {
+    // the shortest prefix whose weight reaches mass * (weight of what stayed so far)
+    const double threshold = prefix_weight() * mass;
+    unsigned lo = 0u, hi = top_key;                      // the smallest key with less than the threshold above it
+    while (lo < hi) {
+      const unsigned mid = lo + ((hi - lo) >> 1);
+      if (above_key(mid) < threshold) hi = mid; else lo = mid + 1;
+    }
+    long long n;
+    double w;
+    equals_of(hi, n, w);
+    if (n > 0) {
+      const double a = above_key(hi);
+      long long c = w > 0.0 ? (long long)ceil((threshold - a) / w) : n;
+      c = c < 1 ? 1 : (c > n ? n : c);
+      while (c > 1 && a + (double)(c - 1) * w >= threshold) --c;
+      while (c < n && !(a + (double)c * w >= threshold)) ++c;
+      shorten(hi, c);
+    }
+  }
+  const double target = u * prefix_weight();
   // Bisection: the smallest key K with weight(> K) <= target; the crossing happens among the
   // logits whose key equals it.
-  unsigned lo = 0u, hi = ordered_key((float)mxd);
+  unsigned lo = 0u, hi = top_key;
   while (lo < hi) {
     const unsigned mid = lo + ((hi - lo) >> 1);
     if (above_key(mid) <= target) hi = mid; else lo = mid + 1;
   }
+  long long n_equal, n_true;
+  double w_equal;
+  bool past_the_prefix = pk != 0u && hi < pk;            // the crossing lies beyond what stayed: the last that stayed
+  if (past_the_prefix) hi = pk;
   const double above = above_key(hi);
-  // the equals of the crossing value: how many, and the weight of one
-  double n_equal_mine = 0.0, w_equal_mine = 0.0;
-#pragma unroll
-  for (int j = 0; j < kSampleRegs; ++j)
-    if (j < regs && key[j] == hi && index_of(j) < hi_i) { n_equal_mine += 1.0; w_equal_mine = weights[j * kThreads + t]; }
-  const long long n_equal = (long long)red.sum(n_equal_mine);
-  const double w_equal = red.max(w_equal_mine);
+  equals_of(hi, n_true, w_equal);
+  n_equal = (pk != 0u && hi == pk && pc < n_true) ? pc : n_true;   // of the prefix key's equals only the first pc stayed
   // which key's equals hold the answer, and the place (1-based, by index) of the answer among them
   unsigned pick_key = hi;
-  long long place = 1, count = n_equal;
-  if (n_equal > 0) {
+  long long place = 1, count = n_true;
+  if (past_the_prefix) {
+    place = n_equal;
+  } else if (n_equal > 0) {
     // equals weigh the same: the cumulative weight after k of them is above + k w
     long long k = w_equal > 0.0 ? (long long)floor((target - above) / w_equal) + 1 : n_equal;
     k = k < 1 ? 1 : (k > n_equal ? n_equal : k);
@@ -409,8 +487,13 @@ sample_temperature_cluster_kernel(const float* __restrict__ logits, const float*
 }
 
 
+// Largest vocabulary whose draws can be filtered (top-k, top-p, min-p) on the device.
+ILB_EXPORT int ilb_sample_filter_max_vocab() { return kSampleCtas * kThreads * kSampleRegs; }
+
+// top_k [rows] (0 = no limit), top_p [rows] (1 = no limit), min_p [rows] (0 = no limit): each may be null.
 ILB_EXPORT int ilb_sample_temperature(const float* logits, const float* temperature,
-                                      const double* uniform, int* out, int* bad, int rows,
+                                      const double* uniform, const int* top_k, const float* top_p,
+                                      const float* min_p, int* out, int* bad, int rows,
                                       int vocab, int stride, cudaStream_t stream) {
   ILB_REQUIRE(rows >= 0 && vocab > 0 && stride >= vocab, "sample_temperature: bad sizes");
   if (rows == 0) return 0;
@@ -425,10 +508,12 @@ ILB_EXPORT int ilb_sample_temperature(const float* logits, const float* temperat
       configured = true;
     }
     ilb::launch_cluster(sample_temperature_cluster_kernel, dim3(parts, rows), dim3(kThreads), smem, stream, parts, logits,
-                        temperature, uniform, out, bad, vocab, stride, regs);
+                        temperature, uniform, top_k, top_p, min_p, out, bad, vocab, stride, regs);
     return check_launch("sample_temperature");
   }
-  // a vocabulary beyond what the cluster's registers hold: one CTA per row walks it
+  // a vocabulary beyond what the cluster's registers hold: one CTA per row walks it (no filters there)
+  ILB_REQUIRE(top_k == nullptr && top_p == nullptr && min_p == nullptr,
+              "sample_temperature: filtered draws are built for vocabularies up to %d", kSampleCtas * kThreads * kSampleRegs);
   ilb::launch(sample_temperature_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, temperature, uniform, out, bad,
                                                            vocab, stride);
   return check_launch("sample_temperature");

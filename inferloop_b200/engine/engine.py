@@ -235,16 +235,20 @@ class Engine:
         return _Flight(StepPlan(nxt, []), nxt, drawn, None)
 
     def _sample(self, logits: torch.Tensor, work) -> Dict[Hashable, int]:
-        """Row i of `logits` belongs to work[i].  Plain greedy and plain temperature rows
-        are drawn on the device; rows with filters or penalties are read back and drawn by
-        the host sampler.  The draw's position is the index of the token being generated
+        """Row i of `logits` belongs to work[i].  Greedy rows and draws with a temperature
+        (with or without top-k / top-p / min-p) are made on the device; rows with penalties,
+        which need the request's token history, are read back and drawn by the host sampler
+        (so are filtered draws over a vocabulary the device kernel is not built for).
+        The draw's position is the index of the token being generated
         (crates/engine/runtime/src/pipeline/completion/cpu.rs:104)."""
         if not work:
             return {}
         rows = len(work)
         out: Dict[Hashable, int] = {}
+        filters_fit = self._filters_fit(logits.shape[1])
         kinds = ["greedy" if w.request.params.uses_plain_greedy()
-                 else "temperature" if w.request.params.uses_plain_temperature() else "host" for w in work]
+                 else "temperature" if (w.request.params.uses_plain_temperature()
+                                        or (filters_fit and w.request.params.uses_device_draw())) else "host" for w in work]
         if self.sampler is None:
             kinds = ["host"] * rows
         if "greedy" in kinds:
@@ -257,7 +261,9 @@ class Engine:
             temps = [w.request.params.temperature if k == "temperature" else 1.0 for w, k in zip(work, kinds)]
             us = [host_sampler.uniform(w.request.params.seed, host_sampler.request_key(w.request.id),
                                        len(w.request.generated)) for w in work]
-            self.sampler.temperature_launch(logits, temps, us)
+            plain = SamplingParams(temperature=1.0)
+            self.sampler.temperature_launch(logits, temps, us,
+                                            [w.request.params if k == "temperature" else plain for w, k in zip(work, kinds)])
             ids = self.sampler.read(rows)
             for w, k, t in zip(work, kinds, ids):
                 if k == "temperature":
@@ -271,6 +277,15 @@ class Engine:
                     host[j], r.params, host_sampler.request_key(r.id), len(r.generated),
                     prompt=r.prompt, generated=r.generated)
         return out
+
+    def _filters_fit(self, vocab: int) -> bool:
+        """Whether the device draws with filters over a vocabulary of this size."""
+        if self.sampler is None:
+            return False
+        if getattr(self, "_filter_max_vocab", None) is None:
+            from ..csrc import ops
+            self._filter_max_vocab = ops.sample_filter_max_vocab()
+        return vocab <= self._filter_max_vocab
 
     def check_device(self) -> None:
         """Raise if any kernel reported that it gave up waiting (its outputs are invalid)."""

@@ -1,5 +1,6 @@
-"""Token selection on the device for the two plain cases: the highest logit, and a draw
-from softmax(logits / T).  Only token ids (and a finiteness flag) come back to the host.
+"""Token selection on the device: the highest logit, and a draw from softmax(logits / T)
+after the reference's filters (top-k, min-p, top-p).  Only token ids (and a finiteness flag)
+come back to the host.  Penalties, which need a request's token history, stay on the host.
 """
 from __future__ import annotations
 
@@ -27,6 +28,9 @@ class DeviceSampler:
         self.h_out = torch.empty(2 * rows, dtype=torch.int32).pin_memory()
         self.h_temp = torch.empty(rows, dtype=torch.float32).pin_memory()
         self.h_uniform = torch.empty(rows, dtype=torch.float64).pin_memory()
+        # per-row filters, staged as one block: top_k (int32 bits), top_p, min_p
+        self.filters = torch.empty(3 * rows, dtype=torch.float32, device=self.device)
+        self.h_filters = torch.empty(3 * rows, dtype=torch.float32).pin_memory()
 
     def greedy_launch(self, logits: torch.Tensor) -> None:
         """Arg-max of every row into `self.out` (no synchronisation)."""
@@ -36,7 +40,9 @@ class DeviceSampler:
         ops.argmax(logits, self.out[:rows], self.bad[:rows])
 
     def temperature_launch(self, logits: torch.Tensor, temperatures: Sequence[float],
-                           uniforms: Sequence[float]) -> None:
+                           uniforms: Sequence[float], params: Sequence[SamplingParams] = ()) -> None:
+        """One draw per row into `self.out` (no synchronisation).  `params`, if given, carry
+        each row's top-k / top-p / min-p."""
         rows = logits.shape[0]
         if rows > self._cap:
             self._grow(max(rows, 2 * self._cap))
@@ -44,8 +50,17 @@ class DeviceSampler:
         self.h_uniform[:rows] = torch.tensor(list(uniforms), dtype=torch.float64)
         self.temperature[:rows].copy_(self.h_temp[:rows], non_blocking=True)
         self.uniform[:rows].copy_(self.h_uniform[:rows], non_blocking=True)
+        top_k = top_p = min_p = None
+        if any(p.top_k is not None or p.top_p < 1.0 or p.min_p > 0.0 for p in params):
+            cap = self._cap
+            self.h_filters[:rows].view(torch.int32)[:] = torch.tensor([p.top_k or 0 for p in params], dtype=torch.int32)
+            self.h_filters[cap:cap + rows] = torch.tensor([p.top_p for p in params], dtype=torch.float32)
+            self.h_filters[2 * cap:2 * cap + rows] = torch.tensor([p.min_p for p in params], dtype=torch.float32)
+            self.filters.copy_(self.h_filters, non_blocking=True)
+            top_k = self.filters[:rows].view(torch.int32)
+            top_p, min_p = self.filters[cap:cap + rows], self.filters[2 * cap:2 * cap + rows]
         ops.sample_temperature(logits, self.temperature[:rows], self.uniform[:rows],
-                               self.out[:rows], self.bad[:rows])
+                               self.out[:rows], self.bad[:rows], top_k, top_p, min_p)
 
     def read(self, rows: int) -> List[int]:
         """Token ids of the last launch (synchronises); raises on non-finite logits."""

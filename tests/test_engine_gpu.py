@@ -293,7 +293,7 @@ def test_temperature_generation_matches_the_plain_sampler(folders):
     model = plain.PlainModel(folders["B"])
     for rid, (p, g) in enumerate(zip(prompts, got)):
         assert g == plain.generate(model, p, 24, temperature=0.8, seed=1234, request=rid)
-    # filters go through the host sampler
+    # filters are applied by the device kernel too (penalties alone go through the host sampler)
     engine2 = Engine(folders["B"], dtype="float32", block_size=page, num_gpu_blocks_override=64, max_num_seqs=4)
     g2 = engine2.generate(prompts[:2], SamplingParams(temperature=0.9, top_k=5, top_p=0.9, seed=7), 8)
     for rid, (p, g) in enumerate(zip(prompts[:2], g2)):

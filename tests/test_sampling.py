@@ -97,3 +97,43 @@ def test_device_temperature_draw_equals_the_host_rule(vocab):
             k = list(order).index(got[i])
             assert abs(c[k] - us[i]) < 1e-9 or (k > 0 and abs(c[k - 1] - us[i]) < 1e-9), (i, got[i], want)
     assert same >= rows - 1
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("vocab", [320, 9000, 151936])
+def test_device_filtered_draw_equals_the_host_rule(vocab):
+    """top-k, min-p and top-p on the device: the same token as the host sampler (the
+    reference's rule step by step) for the same uniform number, row by row with different
+    filters, with equal logits at the top, inside the kept prefix and everywhere."""
+    from inferloop_b200.csrc import ops
+    rows = 40
+    g = torch.Generator().manual_seed(vocab + 7)
+    logits = torch.randn(rows, vocab, generator=g) * 2.5
+    logits[3, 5] = logits[3, 100] = logits[3, 17] = logits[3].max() + 0.5      # three equals at the top
+    logits[4, :] = 0.25                                                         # all equal
+    logits[6, 10:30] = 1.5                                                      # a run of equals inside
+    ks = [None, 1, 5, 50, 1000, 3]
+    ps = [1.0, 0.9, 0.5, 0.1, 0.999]
+    ms = [0.0, 0.05, 0.5, 0.0]
+    params = [SamplingParams(temperature=0.4 + 0.03 * i, top_k=ks[i % len(ks)], top_p=ps[i % len(ps)],
+                             min_p=ms[i % len(ms)], seed=21) for i in range(rows)]
+    us = [host.uniform(21, i, 0) for i in range(rows)]
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    bad = torch.empty(rows, dtype=torch.int32, device="cuda")
+    ops.sample_temperature(
+        logits.cuda(), torch.tensor([p.temperature for p in params], dtype=torch.float32).cuda(),
+        torch.tensor(us, dtype=torch.float64).cuda(), out, bad,
+        torch.tensor([p.top_k or 0 for p in params], dtype=torch.int32).cuda(),
+        torch.tensor([p.top_p for p in params], dtype=torch.float32).cuda(),
+        torch.tensor([p.min_p for p in params], dtype=torch.float32).cuda())
+    got = out.tolist()
+    assert bad.tolist() == [0] * rows
+    same = 0
+    for i in range(rows):
+        want = host.sample(logits[i].numpy(), params[i], i, 0)
+        if got[i] == want:
+            same += 1
+        else:   # sums in another order can move a boundary by rounding: then the two are neighbours in the order
+            order = list(np.lexsort((np.arange(vocab), -logits[i].double().numpy())))
+            assert abs(order.index(got[i]) - order.index(want)) == 1, (i, got[i], want, params[i])
+    assert same >= rows - 2, same
