@@ -69,7 +69,7 @@ def sample(logits: np.ndarray, params: SamplingParams, request: int, position: i
         values[pos] = values[pos] / rp
         values[gen] = values[gen] - np.float32(params.presence_penalty)
     # descending by value, ascending index among equals (sampling.rs:146)
-    order = np.lexsort((np.arange(values.size), -values.astype(np.float64)))
+    order = np.argsort(-values.astype(np.float64), kind="stable")       # a stable sort keeps equals in index order
     if params.temperature == 0.0:
         return int(order[0])
     if params.top_k is not None and params.top_k < order.size:
@@ -81,23 +81,16 @@ def sample(logits: np.ndarray, params: SamplingParams, request: int, position: i
     below = np.nonzero(weights < float(np.float32(params.min_p)))[0]
     keep = max(int(below[0]) if below.size else weights.size, 1)
     weights, order = weights[:keep], order[:keep]
+    # The running sums below are numpy's accumulate: one addition after the other in the
+    # order of the candidates, the same 64-bit sums as a loop over them.
     if params.top_p < 1.0:              # sampling.rs:291-305
         threshold = float(np.sum(weights)) * float(np.float32(params.top_p))
-        c, n = 0.0, 0
-        for w in weights:
-            c += float(w)
-            n += 1
-            if c >= threshold:
-                break
+        reached = np.nonzero(np.add.accumulate(weights) >= threshold)[0]
+        n = int(reached[0]) + 1 if reached.size else weights.size
         weights, order = weights[:n], order[:n]
     # cumulative draw over F32-rounded normalised weights (sampling.rs:210-226)
-    total = 0.0
-    for w in weights:
-        total += float(w)
+    total = float(np.add.accumulate(weights)[-1])
     u = uniform(params.seed, request, position)
-    c = 0.0
-    for idx, w in zip(order, weights):
-        c += float(np.float32(w / total))
-        if u < c:
-            return int(idx)
-    return int(order[-1])
+    steps = np.add.accumulate((weights / total).astype(np.float32).astype(np.float64))
+    crossed = np.nonzero(u < steps)[0]
+    return int(order[int(crossed[0])]) if crossed.size else int(order[-1])
