@@ -224,18 +224,39 @@ def sample_filter_max_vocab() -> int:
     return int(lib.ilb_sample_filter_max_vocab())
 
 
+def mark_tokens(rows: torch.Tensor, tokens: torch.Tensor, is_generated: torch.Tensor, seen: torch.Tensor,
+                generated: torch.Tensor, vocab: int) -> None:
+    """Set bit t of row r of `seen` ([rows, ceil(vocab / 32)] int32, zeroed by the caller) for
+    every entry (r, t), and of `generated` for entries flagged as generated."""
+    for t, w in ((rows, "rows"), (tokens, "tokens"), (is_generated, "flags"), (seen, "seen bits"), (generated, "generated bits")):
+        _need(t, "mark_tokens " + w, torch.int32)
+    _call("sampling", "ilb_mark_tokens", _ptr(rows), _ptr(tokens), _ptr(is_generated), _i(tokens.numel()), _ptr(seen),
+          _ptr(generated), _i(seen.shape[0]), _i(vocab), _stream(seen))
+
+
 def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
                        out: torch.Tensor, bad: Optional[torch.Tensor] = None, top_k: Optional[torch.Tensor] = None,
-                       top_p: Optional[torch.Tensor] = None, min_p: Optional[torch.Tensor] = None) -> None:
+                       top_p: Optional[torch.Tensor] = None, min_p: Optional[torch.Tensor] = None,
+                       penalties: Optional[tuple] = None) -> None:
     """One draw per row from softmax(logits / T) by the reference's sorted-walk rule, after
-    its filters if given: top_k [rows] int32 (0 = none), top_p and min_p [rows] float32."""
+    its filters if given: top_k [rows] int32 (0 = none), top_p and min_p [rows] float32;
+    `penalties` = (seen bits, generated bits, repetition [rows], presence [rows]) applies
+    the reference's penalties to the logits first (see mark_tokens)."""
     _need(logits, "sample logits", torch.float32); _need(temperature, "temperature", torch.float32)
     _need(uniform, "uniform", torch.float64); _need(out, "sample out", torch.int32)
     _need(bad, "sample flags", torch.int32); _need(top_k, "top-k", torch.int32)
     _need(top_p, "top-p", torch.float32); _need(min_p, "min-p", torch.float32)
     rows, vocab = logits.shape
+    seen = gen = rep = pres = None
+    if penalties is not None:
+        seen, gen, rep, pres = penalties
+        _need(seen, "seen bits", torch.int32); _need(gen, "generated bits", torch.int32)
+        _need(rep, "repetition penalty", torch.float32); _need(pres, "presence penalty", torch.float32)
+        if tuple(seen.shape) != (rows, (vocab + 31) // 32) or tuple(gen.shape) != tuple(seen.shape):
+            raise KernelError("sample: token bitmaps must be [rows, ceil(vocab / 32)]")
     _call("sampling", "ilb_sample_temperature", _ptr(logits), _ptr(temperature), _ptr(uniform), _ptr(top_k), _ptr(top_p),
-          _ptr(min_p), _ptr(out), _ptr(bad), _i(rows), _i(vocab), _i(logits.stride(0)), _stream(logits))
+          _ptr(min_p), _ptr(seen), _ptr(gen), _ptr(rep), _ptr(pres), _ptr(out), _ptr(bad), _i(rows), _i(vocab),
+          _i(logits.stride(0)), _stream(logits))
 
 
 # --------------------------------------------------------------------------- tensor-core GEMM

@@ -285,6 +285,8 @@ __global__ void __launch_bounds__(kThreads)
 sample_temperature_cluster_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
                                   const double* __restrict__ uniform, const int* __restrict__ top_k,
                                   const float* __restrict__ top_p, const float* __restrict__ min_p,
+                                  const unsigned* __restrict__ seen, const unsigned* __restrict__ generated,
+                                  const float* __restrict__ repetition, const float* __restrict__ presence,
                                   int* __restrict__ out, int* __restrict__ bad, int vocab, int stride, int regs) {
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();
@@ -300,6 +302,8 @@ sample_temperature_cluster_kernel(const float* __restrict__ logits, const float*
   ClusterReduce red{scratch, slots, n_parts, 0};
   auto index_of = [&](int j) { return lo_i + j * kThreads + t; };
 
+  const int words = (vocab + 31) / 32;
+  const float rep = repetition ? repetition[blockIdx.y] : 1.f, pres = presence ? presence[blockIdx.y] : 0.f;
   // the row's keys into registers; maximum and finiteness
   unsigned key[kSampleRegs];
   float mx = -INFINITY;
@@ -308,8 +312,16 @@ sample_temperature_cluster_kernel(const float* __restrict__ logits, const float*
   for (int j = 0; j < kSampleRegs; ++j) {
     key[j] = 0u;                                         // below every real key
     if (j < regs && index_of(j) < hi_i) {
-      const float v = row[index_of(j)];
+      float v = row[index_of(j)];
       if (!isfinite(v)) nonfinite = 1.0;
+      if (seen != nullptr) {
+        // penalties, in 32-bit as the reference applies them: a token of the prompt or of the
+        // output is scaled towards "less likely", a token of the output also loses the presence penalty
+        const int i = index_of(j);
+        const unsigned bit = 1u << (i & 31);
+        if (seen[(size_t)blockIdx.y * words + (i >> 5)] & bit) v = v < 0.f ? v * rep : v / rep;
+        if (generated[(size_t)blockIdx.y * words + (i >> 5)] & bit) v = v - pres;
+      }
       mx = fmaxf(mx, v);
       key[j] = ordered_key(v);
     }
@@ -487,14 +499,42 @@ sample_temperature_cluster_kernel(const float* __restrict__ logits, const float*
 }
 
 
+// Bit t of row r of `seen` for every token t of request r's prompt and output so far, of
+// `generated` for those of its output: entries are (row, token, 1 if generated).
+__global__ void mark_tokens_kernel(const int* __restrict__ rows, const int* __restrict__ tokens,
+                                   const int* __restrict__ is_generated, int n, unsigned* __restrict__ seen,
+                                   unsigned* __restrict__ generated, int words, int vocab) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int tok = tokens[i];
+  if (tok < 0 || tok >= vocab) return;                   // (the caller has checked; never write outside)
+  const size_t at = (size_t)rows[i] * words + (tok >> 5);
+  atomicOr(seen + at, 1u << (tok & 31));
+  if (is_generated[i]) atomicOr(generated + at, 1u << (tok & 31));
+}
+
+ILB_EXPORT int ilb_mark_tokens(const int* rows, const int* tokens, const int* is_generated, int n, unsigned* seen,
+                               unsigned* generated, int n_rows, int vocab, cudaStream_t stream) {
+  ILB_REQUIRE(n >= 0 && n_rows > 0 && vocab > 0, "mark_tokens: bad sizes");
+  if (n == 0) return 0;
+  ilb::launch(mark_tokens_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, rows, tokens, is_generated, n, seen, generated,
+              (vocab + 31) / 32, vocab);
+  return check_launch("mark_tokens");
+}
+
 // Largest vocabulary whose draws can be filtered (top-k, top-p, min-p) on the device.
 ILB_EXPORT int ilb_sample_filter_max_vocab() { return kSampleCtas * kThreads * kSampleRegs; }
 
 // top_k [rows] (0 = no limit), top_p [rows] (1 = no limit), min_p [rows] (0 = no limit): each may be null.
+// seen / generated [rows][ceil(vocab / 32)] (see ilb_mark_tokens) with repetition / presence [rows], or null: penalties.
 ILB_EXPORT int ilb_sample_temperature(const float* logits, const float* temperature,
                                       const double* uniform, const int* top_k, const float* top_p,
-                                      const float* min_p, int* out, int* bad, int rows,
+                                      const float* min_p, const unsigned* seen, const unsigned* generated,
+                                      const float* repetition, const float* presence, int* out, int* bad, int rows,
                                       int vocab, int stride, cudaStream_t stream) {
+  ILB_REQUIRE((seen == nullptr) == (generated == nullptr), "sample_temperature: both token bitmaps or none");
   ILB_REQUIRE(rows >= 0 && vocab > 0 && stride >= vocab, "sample_temperature: bad sizes");
   if (rows == 0) return 0;
   const int parts = vocab >= 8 * kThreads ? kSampleCtas : 1;
@@ -508,11 +548,11 @@ ILB_EXPORT int ilb_sample_temperature(const float* logits, const float* temperat
       configured = true;
     }
     ilb::launch_cluster(sample_temperature_cluster_kernel, dim3(parts, rows), dim3(kThreads), smem, stream, parts, logits,
-                        temperature, uniform, top_k, top_p, min_p, out, bad, vocab, stride, regs);
+                        temperature, uniform, top_k, top_p, min_p, seen, generated, repetition, presence, out, bad, vocab, stride, regs);
     return check_launch("sample_temperature");
   }
   // a vocabulary beyond what the cluster's registers hold: one CTA per row walks it (no filters there)
-  ILB_REQUIRE(top_k == nullptr && top_p == nullptr && min_p == nullptr,
+  ILB_REQUIRE(top_k == nullptr && top_p == nullptr && min_p == nullptr && seen == nullptr,
               "sample_temperature: filtered draws are built for vocabularies up to %d", kSampleCtas * kThreads * kSampleRegs);
   ilb::launch(sample_temperature_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, temperature, uniform, out, bad,
                                                            vocab, stride);

@@ -11,6 +11,8 @@ max_output_tokens, max_num_seqs, gpu_memory_utilization, device.
 """
 from __future__ import annotations
 
+import dataclasses
+
 import os
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Mapping, Optional, Sequence, Union
@@ -235,10 +237,10 @@ class Engine:
         return _Flight(StepPlan(nxt, []), nxt, drawn, None)
 
     def _sample(self, logits: torch.Tensor, work) -> Dict[Hashable, int]:
-        """Row i of `logits` belongs to work[i].  Greedy rows and draws with a temperature
-        (with or without top-k / top-p / min-p) are made on the device; rows with penalties,
-        which need the request's token history, are read back and drawn by the host sampler
-        (so are filtered draws over a vocabulary the device kernel is not built for).
+        """Row i of `logits` belongs to work[i].  Every row is drawn on the device: the
+        highest logit, or a draw after the reference's penalties and filters (top-k, min-p,
+        top-p).  Only over a vocabulary the filtering kernel is not built for are rows with
+        filters or penalties read back and drawn by the host sampler.
         The draw's position is the index of the token being generated
         (crates/engine/runtime/src/pipeline/completion/cpu.rs:104)."""
         if not work:
@@ -247,8 +249,7 @@ class Engine:
         out: Dict[Hashable, int] = {}
         filters_fit = self._filters_fit(logits.shape[1])
         kinds = ["greedy" if w.request.params.uses_plain_greedy()
-                 else "temperature" if (w.request.params.uses_plain_temperature()
-                                        or (filters_fit and w.request.params.uses_device_draw())) else "host" for w in work]
+                 else "temperature" if (w.request.params.uses_plain_temperature() or filters_fit) else "host" for w in work]
         if self.sampler is None:
             kinds = ["host"] * rows
         if "greedy" in kinds:
@@ -258,12 +259,16 @@ class Engine:
                 if k == "greedy":
                     out[w.request.id] = t
         if "temperature" in kinds:
-            temps = [w.request.params.temperature if k == "temperature" else 1.0 for w, k in zip(work, kinds)]
+            # a row without a temperature but with penalties is the best of the penalised logits: top-k 1
+            plain = SamplingParams(temperature=1.0)
+            drawn_with = [plain if k != "temperature" else w.request.params if w.request.params.temperature > 0.0
+                          else dataclasses.replace(w.request.params, temperature=1.0, top_k=1, top_p=1.0, min_p=0.0)
+                          for w, k in zip(work, kinds)]
+            temps = [p.temperature for p in drawn_with]
             us = [host_sampler.uniform(w.request.params.seed, host_sampler.request_key(w.request.id),
                                        len(w.request.generated)) for w in work]
-            plain = SamplingParams(temperature=1.0)
-            self.sampler.temperature_launch(logits, temps, us,
-                                            [w.request.params if k == "temperature" else plain for w, k in zip(work, kinds)])
+            histories = [(w.request.prompt, w.request.generated) if k == "temperature" else None for w, k in zip(work, kinds)]
+            self.sampler.temperature_launch(logits, temps, us, drawn_with, histories)
             ids = self.sampler.read(rows)
             for w, k, t in zip(work, kinds, ids):
                 if k == "temperature":

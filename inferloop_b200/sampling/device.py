@@ -1,6 +1,7 @@
 """Token selection on the device: the highest logit, and a draw from softmax(logits / T)
-after the reference's filters (top-k, min-p, top-p).  Only token ids (and a finiteness flag)
-come back to the host.  Penalties, which need a request's token history, stay on the host.
+after the reference's penalties (the request's prompt and output go up as token lists and
+become bitmaps there) and filters (top-k, min-p, top-p).  Only token ids (and a finiteness
+flag) come back to the host.
 """
 from __future__ import annotations
 
@@ -17,6 +18,7 @@ class DeviceSampler:
     def __init__(self, device: torch.device, max_rows: int = 256) -> None:
         self.device = device
         self._cap = 0
+        self._bits = None                  # [2, rows, words]: seen and generated token bitmaps
         self._grow(max_rows)
 
     def _grow(self, rows: int) -> None:
@@ -40,9 +42,10 @@ class DeviceSampler:
         ops.argmax(logits, self.out[:rows], self.bad[:rows])
 
     def temperature_launch(self, logits: torch.Tensor, temperatures: Sequence[float],
-                           uniforms: Sequence[float], params: Sequence[SamplingParams] = ()) -> None:
+                           uniforms: Sequence[float], params: Sequence[SamplingParams] = (), histories=None) -> None:
         """One draw per row into `self.out` (no synchronisation).  `params`, if given, carry
-        each row's top-k / top-p / min-p."""
+        each row's top-k / top-p / min-p and penalties; `histories[i]` = (prompt, generated)
+        token ids of row i for the rows that have a penalty."""
         rows = logits.shape[0]
         if rows > self._cap:
             self._grow(max(rows, 2 * self._cap))
@@ -59,8 +62,37 @@ class DeviceSampler:
             self.filters.copy_(self.h_filters, non_blocking=True)
             top_k = self.filters[:rows].view(torch.int32)
             top_p, min_p = self.filters[cap:cap + rows], self.filters[2 * cap:2 * cap + rows]
+        penalties = None
+        if histories is not None and any(p.presence_penalty != 0.0 or p.repetition_penalty != 1.0 for p in params):
+            penalties = self._penalties(rows, logits.shape[1], params, histories)
         ops.sample_temperature(logits, self.temperature[:rows], self.uniform[:rows],
-                               self.out[:rows], self.bad[:rows], top_k, top_p, min_p)
+                               self.out[:rows], self.bad[:rows], top_k, top_p, min_p, penalties)
+
+    def _penalties(self, rows: int, vocab: int, params: Sequence[SamplingParams], histories) -> tuple:
+        """Token bitmaps of the rows that have a penalty (prompt + output, and output alone)
+        and the per-row penalty values, on the device."""
+        words = (vocab + 31) // 32
+        if self._bits is None or self._bits.shape[1] < rows or self._bits.shape[2] != words:
+            self._bits = torch.empty(2, max(rows, self._cap), words, dtype=torch.int32, device=self.device)
+        bits = self._bits[:, :rows]
+        bits.zero_()
+        r_idx, toks, flags = [], [], []
+        for i, (p, h) in enumerate(zip(params, histories)):
+            if h is None or (p.presence_penalty == 0.0 and p.repetition_penalty == 1.0):
+                continue
+            prompt, generated = h
+            for t in list(prompt) + list(generated):
+                if not (0 <= int(t) < vocab):
+                    raise ValueError("history token outside vocabulary")
+            r_idx += [i] * (len(prompt) + len(generated))
+            toks += list(prompt) + list(generated)
+            flags += [0] * len(prompt) + [1] * len(generated)
+        if toks:
+            entries = torch.tensor([r_idx, toks, flags], dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+            ops.mark_tokens(entries[0], entries[1], entries[2], bits[0], bits[1], vocab)
+        pen = torch.tensor([[p.repetition_penalty for p in params], [p.presence_penalty for p in params]],
+                           dtype=torch.float32).pin_memory().to(self.device, non_blocking=True)
+        return bits[0], bits[1], pen[0], pen[1]
 
     def read(self, rows: int) -> List[int]:
         """Token ids of the last launch (synchronises); raises on non-finite logits."""

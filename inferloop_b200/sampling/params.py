@@ -42,10 +42,5 @@ class SamplingParams:
                 and self.min_p == 0.0 and self.presence_penalty == 0.0
                 and self.repetition_penalty == 1.0)
 
-    def uses_device_draw(self) -> bool:
-        """A draw that the device kernel makes: a temperature, any of top-k / top-p / min-p,
-        no penalty (penalties need the request's token history and stay on the host)."""
-        return (self.temperature > 0.0 and self.presence_penalty == 0.0 and self.repetition_penalty == 1.0)
-
     def is_eos(self, token: int) -> bool:
         return token == self.eos_token or token in self.eos_tokens

@@ -137,3 +137,37 @@ def test_device_filtered_draw_equals_the_host_rule(vocab):
             order = list(np.lexsort((np.arange(vocab), -logits[i].double().numpy())))
             assert abs(order.index(got[i]) - order.index(want)) == 1, (i, got[i], want, params[i])
     assert same >= rows - 2, same
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("vocab", [515, 151936])
+def test_device_penalties_equal_the_host_rule(vocab):
+    """Repetition and presence penalties applied by the device kernel (token bitmaps made
+    from each row's prompt and output) before the filters and the draw: the same token as
+    the host sampler, also for a row without a temperature (the best penalised logit)."""
+    import dataclasses
+    from inferloop_b200.sampling.device import DeviceSampler
+    rows = 24
+    g = torch.Generator().manual_seed(vocab + 3)
+    logits = torch.randn(rows, vocab, generator=g) * 2.0
+    rng = np.random.default_rng(vocab)
+    params, hist = [], []
+    for i in range(rows):
+        top = [int(t) for t in torch.topk(logits[i], 6).indices]          # penalise what would win
+        prompt = top[:3] + [int(t) for t in rng.integers(0, vocab, 20)]
+        generated = top[3:5] + [int(t) for t in rng.integers(0, vocab, 7)] + top[3:4]
+        params.append(SamplingParams(temperature=0.0 if i % 6 == 0 else 0.5 + 0.05 * i,
+                                     top_k=None if i % 3 else 40, top_p=1.0 if i % 2 else 0.8,
+                                     presence_penalty=[0.0, 1.5, -0.7][i % 3], repetition_penalty=[1.3, 1.0, 2.5, 0.8][i % 4],
+                                     seed=5))
+        hist.append((prompt, generated))
+    sampler = DeviceSampler(torch.device("cuda", 0), max_rows=8)           # grows on demand
+    drawn_with = [p if p.temperature > 0 else dataclasses.replace(p, temperature=1.0, top_k=1, top_p=1.0) for p in params]
+    us = [host.uniform(5, i, len(hist[i][1])) for i in range(rows)]
+    sampler.temperature_launch(logits.cuda(), [p.temperature for p in drawn_with], us, drawn_with, hist)
+    got = sampler.read(rows)
+    same = 0
+    for i in range(rows):
+        want = host.sample(logits[i].numpy(), params[i], i, len(hist[i][1]), prompt=hist[i][0], generated=hist[i][1])
+        same += int(got[i] == want)
+    assert same >= rows - 1, (same, got)
