@@ -263,6 +263,53 @@ struct ClusterReduce {
     return scratch[33];
   }
   __device__ __forceinline__ double sum(double v) { return finish(block_sum_f64(v, scratch), false); }
+  // Three sums at once (a search step looks at three keys): `wide` [3 * 33 + 3], `slots3` [2][3].
+  double* wide;
+  double* slots3;
+  __device__ __forceinline__ void sum3(double (&v)[3]) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int i = 0; i < 3; ++i)
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v[i] += __shfl_xor_sync(0xffffffffu, v[i], o);
+    __syncthreads();
+    if (lane == 0) {
+#pragma unroll
+      for (int i = 0; i < 3; ++i) wide[i * 33 + warp] = v[i];
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        double t = wide[i * 33 + lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (lane == 0) { wide[i * 33 + 32] = t; if (n_parts > 1) slots3[(turn & 1) * 3 + i] = t; }
+      }
+    }
+    if (n_parts > 1) {
+      cluster_sync_all();
+      if (threadIdx.x < 3) {                               // one thread per sum, the parts in the order of the CTAs
+        double part[kSampleCtas];
+#pragma unroll
+        for (int q = 0; q < kSampleCtas; ++q)
+          part[q] = q < n_parts ? ld_peer_f64(smem_u32(slots3 + (turn & 1) * 3 + threadIdx.x), (uint32_t)q) : 0.0;
+        double t = part[0];
+#pragma unroll
+        for (int q = 1; q < kSampleCtas; ++q)
+          if (q < n_parts) t += part[q];
+        wide[99 + threadIdx.x] = t;
+      }
+      ++turn;
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < 3; ++i) v[i] = wide[99 + i];
+    } else {
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < 3; ++i) v[i] = wide[i * 33 + 32];
+    }
+  }
   __device__ __forceinline__ double max(double v) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
@@ -293,13 +340,15 @@ sample_temperature_cluster_kernel(const float* __restrict__ logits, const float*
   extern __shared__ double weights[];                    // [regs][kThreads]
   __shared__ double scratch[34];
   __shared__ double slots[2];
+  __shared__ double wide[3 * 33 + 3];
+  __shared__ double slots3[6];
   const int part = blockIdx.x, n_parts = gridDim.x, t = threadIdx.x;
   const float* row = logits + (size_t)blockIdx.y * stride;
   const double inv_t = 1.0 / (double)temperature[blockIdx.y];
   const double u = uniform[blockIdx.y];
   const int per = (vocab + n_parts - 1) / n_parts;
   const int lo_i = part * per, hi_i = min(vocab, lo_i + per);
-  ClusterReduce red{scratch, slots, n_parts, 0};
+  ClusterReduce red{scratch, slots, n_parts, 0, wide, slots3};
   auto index_of = [&](int j) { return lo_i + j * kThreads + t; };
 
   const int words = (vocab + 31) / 32;
@@ -367,6 +416,32 @@ sample_temperature_cluster_kernel(const float* __restrict__ logits, const float*
     n = (long long)red.sum(n_mine);
     w = red.max(w_mine);
   };
+  // The smallest key for which `pred(measure above the key)` holds, where the measure (a count
+  // or a weight) falls as the key rises and pred holds from some key on.  A step looks at three
+  // keys at once and keeps a quarter of the range: 16 steps instead of 32.
+  auto search = [&](bool by_count, auto pred) {
+    unsigned lo = 0u, hi = ordered_key((float)mxd);
+    while (lo < hi) {
+      const unsigned q2 = lo + ((hi - lo) >> 1);
+      const unsigned q1 = lo + ((hi - lo) >> 2), q3 = q2 + ((hi - q2) >> 1);     // lo <= q1 <= q2 <= q3 < hi
+      double a[3] = {0.0, 0.0, 0.0};
+#pragma unroll
+      for (int j = 0; j < kSampleRegs; ++j)
+        if (j < regs) {
+          const double w = by_count ? 1.0 : weights[j * kThreads + t];
+          const unsigned k = key[j];
+          if (k > q1) a[0] += w;
+          if (k > q2) a[1] += w;
+          if (k > q3) a[2] += w;
+        }
+      red.sum3(a);
+      if (pred(a[0])) hi = q1;
+      else if (pred(a[1])) { lo = q1 + 1; hi = q2; }
+      else if (pred(a[2])) { lo = q2 + 1; hi = q3; }
+      else lo = q3 + 1;
+    }
+    return hi;
+  };
   // The candidates that stay are a PREFIX of the order (highest logit first, lower index first
   // among equals): everything above key `pk` and the first `pc` of its equals; (0, 0) = all.
   // top-k, min-p and top-p each name a prefix; the shortest holds.
@@ -378,11 +453,8 @@ sample_temperature_cluster_kernel(const float* __restrict__ logits, const float*
   const unsigned top_key = ordered_key((float)mxd);
   const int k_limit = top_k ? top_k[blockIdx.y] : 0;
   if (k_limit > 0 && k_limit < vocab) {
-    unsigned lo = 0u, hi = top_key;                      // the smallest key with fewer than k logits above it
-    while (lo < hi) {
-      const unsigned mid = lo + ((hi - lo) >> 1);
-      if (count_above(mid) <= (long long)k_limit - 1) hi = mid; else lo = mid + 1;
-    }
+    const double most = (double)k_limit - 1.0;            // the smallest key with fewer than k logits above it
+    const unsigned hi = search(true, [&](double n) { return n <= most; });
     shorten(hi, (long long)k_limit - count_above(hi));
   }
   const double floor_w = min_p ? (double)min_p[blockIdx.y] : 0.0;
@@ -410,11 +482,8 @@ sample_temperature_cluster_kernel(const float* __restrict__ logits, const float*
   if (mass < 1.0) {
     // the shortest prefix whose weight reaches mass * (weight of what stayed so far)
     const double threshold = prefix_weight() * mass;
-    unsigned lo = 0u, hi = top_key;                      // the smallest key with less than the threshold above it
-    while (lo < hi) {
-      const unsigned mid = lo + ((hi - lo) >> 1);
-      if (above_key(mid) < threshold) hi = mid; else lo = mid + 1;
-    }
+    // the smallest key with less than the threshold above it
+    const unsigned hi = search(false, [&](double a) { return a < threshold; });
     long long n;
     double w;
     equals_of(hi, n, w);
@@ -430,11 +499,7 @@ sample_temperature_cluster_kernel(const float* __restrict__ logits, const float*
   const double target = u * prefix_weight();
   // Bisection: the smallest key K with weight(> K) <= target; the crossing happens among the
   // logits whose key equals it.
-  unsigned lo = 0u, hi = top_key;
-  while (lo < hi) {
-    const unsigned mid = lo + ((hi - lo) >> 1);
-    if (above_key(mid) <= target) hi = mid; else lo = mid + 1;
-  }
+  unsigned hi = search(false, [&](double a) { return a <= target; });
   long long n_equal, n_true;
   double w_equal;
   bool past_the_prefix = pk != 0u && hi < pk;            // the crossing lies beyond what stayed: the last that stayed
