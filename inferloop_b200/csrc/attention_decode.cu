@@ -707,15 +707,15 @@ inline size_t inbox_bytes(int d, int group, int split) { return (size_t)split * 
 
 template <int D, int STAGES>
 int configure() {
-  static bool configured = false;
-  if (!configured) {
+  static OncePerDevice once;
+  if (once.first()) {
     constexpr size_t smem = ring_bytes<D, STAGES>() + (size_t)2 * kMaxSplit * (D + 4) * 4;   // the most a launch asks for
     static_assert(smem <= 227 * 1024, "tile ring does not fit shared memory");
     cudaError_t e = cudaFuncSetAttribute(decode_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) once.forget();
     if (e != cudaSuccess) return fail("attention decode: cannot reserve %zu bytes of shared memory", smem);
     cudaFuncSetAttribute(decode_kernel<D, STAGES>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     cudaFuncSetAttribute(decode_kernel<D, STAGES>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-    configured = true;
   }
   return 0;
 }

@@ -513,12 +513,12 @@ template <int D> size_t decode_smem() {
 
 template <int D>
 int launch_prefill(const PrefillParams& p, int n_tiles, cudaStream_t stream) {
-  static bool configured = false;
+  static OncePerDevice once;
   const size_t smem = prefill_smem<D>();
-  if (!configured) {
+  if (once.first()) {
     cudaError_t e = cudaFuncSetAttribute(prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) once.forget();
     if (e != cudaSuccess) return fail("attention prefill: cannot reserve %zu bytes of shared memory", smem);
-    configured = true;
   }
   ilb::launch(prefill_kernel<D>, dim3(n_tiles, p.cache.nkv), dim3(kWarps * 32), smem, stream, p);
   return check_launch("attention prefill");
@@ -526,12 +526,12 @@ int launch_prefill(const PrefillParams& p, int n_tiles, cudaStream_t stream) {
 
 template <int D>
 int launch_decode(const DecodeParams& p, cudaStream_t stream) {
-  static bool configured = false;
+  static OncePerDevice once;
   const size_t smem = decode_smem<D>();
-  if (!configured) {
+  if (once.first()) {
     cudaError_t e = cudaFuncSetAttribute(decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) once.forget();
     if (e != cudaSuccess) return fail("attention decode: cannot reserve %zu bytes of shared memory", smem);
-    configured = true;
   }
   ilb::launch(decode_kernel<D>, dim3(p.cache.nkv, p.n_seqs, p.max_chunks), dim3(kWarps * 32), smem, stream, p);
   return check_launch("attention decode");
@@ -578,6 +578,18 @@ ILB_EXPORT int ilb_attention_decode(const void* q, void* out, const void* k_cach
   ILB_REQUIRE(page_size > 0 && max_blocks > 0 && num_pages > 0 && window >= 0, "attention decode: bad cache geometry");
   const int G = nq / nkv, rows16 = (G + 15) / 16 * 16;
   ILB_REQUIRE((long long)n_seqs * nkv * max_chunks * G * (d + 2) <= scratch_floats, "attention decode: scratch too small");
+  // Every key the block tables can name must fall into one of the chunks: a sequence longer
+  // than max_chunks * chunk would wait for chunks that the grid does not hold, and its row
+  // would never be written.
+  ILB_REQUIRE((long long)max_chunks * chunk >= (long long)max_blocks * page_size,
+              "attention decode: %d chunks of %d keys do not cover the %d x %d keys the block tables can name",
+              max_chunks, chunk, max_blocks, page_size);
+  // The last chunk's merge keeps one weight per (head of the group, chunk) in the shared
+  // memory the tiles used.
+  const size_t smem_bytes = d == 32 ? decode_smem<32>() : d == 64 ? decode_smem<64>() : d == 96 ? decode_smem<96>() : decode_smem<128>();
+  ILB_REQUIRE((long long)G * max_chunks * 4 <= (long long)smem_bytes,
+              "attention decode: %d heads a group x %d chunks need %lld bytes of merge weights, the kernel has %zu; "
+              "use longer chunks", G, max_chunks, (long long)G * max_chunks * 4, smem_bytes);
   ILB_REQUIRE(n_seqs * nkv <= n_tickets, "attention decode: too few tickets");
   DecodeParams p{(const __nv_bfloat16*)q, (__nv_bfloat16*)out,
                  Cache{(const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, page_size, num_pages, nkv},

@@ -419,11 +419,11 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
   constexpr int kChunks = D / 64;
   constexpr size_t smem = (size_t)kChunks * kRows * 128 * (1 + 2 * kStages) + 2 * kRows * 128 + 1024 + (8 + 4 * kStages) * 8 + 768 * 4;
   static_assert(smem <= 227 * 1024, "tiles do not fit shared memory");
-  static bool configured = false;
-  if (!configured) {
+  static OncePerDevice once;
+  if (once.first()) {
     cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) once.forget();
     if (e != cudaSuccess) return fail("attention (tensor cores): cannot reserve %zu bytes of shared memory", smem);
-    configured = true;
   }
   ilb::launch(prefill_tc_kernel<D>, dim3(n_tiles, p.nkv), dim3(kThreads), smem, stream, mq, mk, mv, mkr, mvr, p);
   return check_launch("attention prefill (tensor cores)");

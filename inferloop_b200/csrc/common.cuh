@@ -31,6 +31,24 @@ static inline int check_launch(const char* what) {
   return 0;
 }
 
+// Kernel attributes (shared-memory size, cluster size) are kept per device: a launcher asks
+// `first()` with the launch's device current and sets them when it answers true.  A
+// launcher that fails to set them calls `forget()` so that the next call tries again.
+struct OncePerDevice {
+  static constexpr int kMax = 64;
+  bool done[kMax] = {};
+  int last = -1;
+  bool first() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMax) { last = -1; return true; }
+    last = dev;
+    if (done[dev]) return false;
+    done[dev] = true;
+    return true;
+  }
+  void forget() { if (last >= 0) done[last] = false; }
+};
+
 #define ILB_REQUIRE(cond, ...)            \
   do {                                    \
     if (!(cond)) return ilb::fail(__VA_ARGS__); \

@@ -904,13 +904,13 @@ template <int BN, int STAGES, bool SWAP, int MS = 1>
 int configure() {
   constexpr size_t smem = smem_bytes<BN, STAGES, SWAP, MS>();
   static_assert(smem <= 227 * 1024, "stage ring does not fit shared memory");
-  static bool configured = false;
-  if (!configured) {
+  static OncePerDevice once;
+  if (once.first()) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP, MS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) once.forget();
     if (e != cudaSuccess) return fail("gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     // two CTAs of the small rings share an SM only with the largest shared-memory carve-out
     cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP, MS>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    configured = true;
   }
   return 0;
 }

@@ -606,12 +606,10 @@ ILB_EXPORT int ilb_sample_temperature(const float* logits, const float* temperat
   const int per = (vocab + parts - 1) / parts, regs = (per + kThreads - 1) / kThreads;
   if (regs <= kSampleRegs && rows <= 65535) {
     const size_t smem = (size_t)regs * kThreads * sizeof(double);
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice once;
+    if (once.first())
       cudaFuncSetAttribute(sample_temperature_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)(kSampleRegs * kThreads * sizeof(double)));
-      configured = true;
-    }
     ilb::launch_cluster(sample_temperature_cluster_kernel, dim3(parts, rows), dim3(kThreads), smem, stream, parts, logits,
                         temperature, uniform, top_k, top_p, min_p, seen, generated, repetition, presence, out, bad, vocab, stride, regs);
     return check_launch("sample_temperature");
