@@ -50,13 +50,14 @@ def build_parser() -> argparse.ArgumentParser:
     gen.add_argument("model_path", metavar="MODEL_PATH")
     gen.add_argument("--tokens", required=True, help="comma-separated token ids")
     gen.add_argument("--max-new-tokens", type=int, default=16)
-    gen.add_argument("--temperature", type=float, default=0.0)
-    gen.add_argument("--top-k", type=int, default=None)
-    gen.add_argument("--top-p", type=float, default=1.0)
-    gen.add_argument("--min-p", type=float, default=0.0)
-    gen.add_argument("--presence-penalty", type=float, default=0.0)
-    gen.add_argument("--repetition-penalty", type=float, default=1.0)
-    gen.add_argument("--seed", type=int, default=0)
+    # what is not given comes from the folder's generation_config.json / config.json
+    gen.add_argument("--temperature", type=float, default=None)
+    gen.add_argument("--top-k", type=int, default=None, help="0 disables the filter")
+    gen.add_argument("--top-p", type=float, default=None)
+    gen.add_argument("--min-p", type=float, default=None)
+    gen.add_argument("--presence-penalty", type=float, default=None)
+    gen.add_argument("--repetition-penalty", type=float, default=None)
+    gen.add_argument("--seed", type=int, default=None)
     gen.add_argument("--eos-token", type=int, default=None)
     _add_engine_options(gen)
     ins = sub.add_parser("inspect-model", help="print the typed configuration")
@@ -84,14 +85,10 @@ def _engine(args, folder: str):
                   random_weights_seed=args.random_weights)
 
 
-def _sampling(d: Dict[str, Any]):
-    from .sampling.params import SamplingParams
-    known = {"temperature", "top_k", "top_p", "min_p", "presence_penalty", "repetition_penalty",
-             "eos_tokens", "seed", "eos_token"}
-    extra = set(d) - known
-    if extra:
-        raise ValueError(f"unknown sampling fields {sorted(extra)}")   # deny_unknown_fields
-    return SamplingParams(**d)
+def _sampling(engine, d: Dict[str, Any]):
+    """A request's sampling fields over the folder's generation defaults, field by field
+    (crates/model/package/src/generation/mod.rs:68-128); unknown fields are refused."""
+    return engine.generation_defaults.resolve(d)
 
 
 def cmd_run(args) -> int:
@@ -109,7 +106,7 @@ def cmd_run(args) -> int:
             max_new = r["workload"]["Generate"]["max_new_tokens"]
         except (KeyError, TypeError):
             raise ValueError("only Sequence input with a Generate workload is served") from None
-        ids.append(engine.submit(tokens, _sampling(r.get("sampling", {})), max_new, request_id=r["id"]))
+        ids.append(engine.submit(tokens, _sampling(engine, r.get("sampling", {})), max_new, request_id=r["id"]))
     while not engine.is_idle():
         engine.step()
     results = []
@@ -123,13 +120,10 @@ def cmd_run(args) -> int:
 
 
 def cmd_generate(args) -> int:
-    from .sampling.params import SamplingParams
     tokens = [int(t) for t in args.tokens.replace(" ", "").split(",") if t]
-    params = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
-                            min_p=args.min_p, presence_penalty=args.presence_penalty,
-                            repetition_penalty=args.repetition_penalty, seed=args.seed,
-                            eos_token=args.eos_token)
     engine = _engine(args, args.model_path)
+    params = _sampling(engine, {k: getattr(args, k) for k in (
+        "temperature", "top_k", "top_p", "min_p", "presence_penalty", "repetition_penalty", "seed", "eos_token")})
     out = engine.generate([tokens], params, args.max_new_tokens)[0]
     print(json.dumps({"tokens": out, "reason": engine.result(0).finish_reason}))
     return 0

@@ -21,8 +21,17 @@ using namespace ilb;
 
 constexpr int kThreads = 1024;
 
+// Bit pattern whose unsigned order is the total order of the floats (-0 below +0).
+__device__ __forceinline__ unsigned ordered_key(float v) {
+  const unsigned u = __float_as_uint(v);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// The reference's greedy rule is the total order of the values, signed zero included, lowest
+// index among equals (crates/engine/workloads/src/sampling.rs:175-192).
 __device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
-  return v > bv || (v == bv && i < bi);
+  const unsigned k = ordered_key(v), bk = ordered_key(bv);
+  return k > bk || (k == bk && i < bi);
 }
 
 // A row is shared by the kArgmaxCtas CTAs of a thread-block cluster (contiguous parts of the
@@ -106,12 +115,6 @@ ILB_EXPORT int ilb_argmax(const float* logits, int* out, int* bad, int rows, int
   const int parts = vocab >= 8 * kThreads ? kArgmaxCtas : 1;      // a small vocabulary is one CTA's work
   ilb::launch_cluster(argmax_kernel, dim3(parts, rows), dim3(kThreads), 0, stream, parts, logits, out, bad, vocab, stride);
   return check_launch("argmax");
-}
-
-// Map a float to an unsigned key whose order is the order of the floats.
-__device__ __forceinline__ unsigned ordered_key(float v) {
-  const unsigned u = __float_as_uint(v);
-  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
 __device__ __forceinline__ double block_sum_f64(double v, double* scratch) {

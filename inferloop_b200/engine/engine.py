@@ -21,6 +21,7 @@ import torch
 
 from ..sampling import host as host_sampler
 from ..sampling.device import DeviceSampler
+from ..sampling.defaults import GenerationDefaults
 from ..sampling.params import SamplingParams
 from .batch import StepEntry
 from .runner import ModelRunner, parse_dtype, require_cuda
@@ -61,6 +62,14 @@ class Engine:
         together with `random_weights_seed` (weights are then made on the device)."""
         self.block_size = int(block_size)
         self.max_output_tokens = max_output_tokens
+        # what a request without sampling fields gets, and the folder's stop tokens
+        # (generation_config.json / eos_token_id: crates/model/package/src/generation/read.rs:9-100)
+        if isinstance(model, (str, os.PathLike)):
+            self.generation_defaults = GenerationDefaults.from_folder(str(model))
+        elif isinstance(model, Mapping):
+            self.generation_defaults = GenerationDefaults.from_configs(model)
+        else:
+            self.generation_defaults = GenerationDefaults()
         if runner is not None:
             self.runner = runner
         else:
@@ -121,7 +130,8 @@ class Engine:
     # ------------------------------------------------------------------ requests
     def submit(self, tokens: Sequence[int], sampling: Optional[SamplingParams] = None,
                max_new_tokens: int = 16, request_id: Optional[Hashable] = None) -> Hashable:
-        params = sampling or SamplingParams()
+        params = (self.generation_defaults.base if sampling is None
+                  else self.generation_defaults.with_stop_tokens(sampling))
         if request_id is None:
             while self._next_id in self.requests:
                 self._next_id += 1

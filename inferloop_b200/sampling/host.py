@@ -35,12 +35,19 @@ def request_key(request) -> int:
     return int.from_bytes(hashlib.sha256(repr(request).encode()).digest()[:8], "little")
 
 
+def total_order_keys(values: np.ndarray) -> np.ndarray:
+    """Unsigned keys whose order is the total order of 32-bit floats (-0 below +0), the
+    order the reference compares logits in (`f32::total_cmp`)."""
+    bits = np.ascontiguousarray(values, dtype=np.float32).view(np.uint32)
+    return np.where(bits & np.uint32(0x80000000), ~bits, bits | np.uint32(0x80000000))
+
+
 def greedy(logits: np.ndarray) -> int:
-    """Highest value, lowest index among equals; non-finite input is an error
-    (sampling.rs:175-192)."""
+    """Highest value in the total order, lowest index among equals; non-finite input is
+    an error (sampling.rs:175-192)."""
     if logits.size == 0 or not np.isfinite(logits).all():
         raise ValueError("invalid sampling logits")
-    return int(np.argmax(logits))     # numpy returns the first maximum
+    return int(np.argmax(total_order_keys(logits)))     # numpy returns the first maximum
 
 
 def sample(logits: np.ndarray, params: SamplingParams, request: int, position: int,
@@ -69,7 +76,8 @@ def sample(logits: np.ndarray, params: SamplingParams, request: int, position: i
         values[pos] = values[pos] / rp
         values[gen] = values[gen] - np.float32(params.presence_penalty)
     # descending by value, ascending index among equals (sampling.rs:146)
-    order = np.argsort(-values.astype(np.float64), kind="stable")       # a stable sort keeps equals in index order
+    # (total order: -0 sorts below +0; a stable sort keeps equals in index order)
+    order = np.argsort(~total_order_keys(values), kind="stable")
     if params.temperature == 0.0:
         return int(order[0])
     if params.top_k is not None and params.top_k < order.size:

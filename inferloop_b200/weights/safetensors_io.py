@@ -188,6 +188,7 @@ class TensorSource:
                     if self.where.get(name) != shard:
                         raise SafetensorsError(
                             f"{shard}: holds {name}, which the index does not map to it")
+            self._check_total_size(index_path, index)
         elif os.path.exists(single):
             self.files["model.safetensors"] = SafetensorsFile(single)
             for name in self.files["model.safetensors"].entries:
@@ -195,6 +196,30 @@ class TensorSource:
         else:
             raise SafetensorsError(
                 f"{folder}: neither model.safetensors nor model.safetensors.index.json exists")
+
+    def _check_total_size(self, index_path: str, index: Mapping) -> None:
+        """`metadata.total_size`, when the index declares one, must equal the shards'
+        payload bytes, or the payload plus the shards' headers (some exporters count
+        those): crates/model/package/src/storage/source.rs:160-181.  A whole number written
+        as a float is taken (index.rs:60-81); absence is not an error."""
+        meta = index.get("metadata") if isinstance(index, dict) else None
+        if not isinstance(meta, dict) or "total_size" not in meta:
+            return
+        declared = meta["total_size"]
+        if isinstance(declared, bool) or not isinstance(declared, (int, float)):
+            raise SafetensorsError(f"{index_path}: invalid total_size {declared!r}")
+        if isinstance(declared, float):
+            if declared != declared or declared in (float("inf"), float("-inf")) or declared != int(declared):
+                raise SafetensorsError(f"{index_path}: invalid total_size {declared!r}")
+            declared = int(declared)
+        if declared <= 0:
+            raise SafetensorsError(f"{index_path}: total_size {declared} declares empty weights")
+        payload = sum(e.end - e.begin for f in self.files.values() for e in f.entries.values())
+        with_headers = payload + sum(int(f.data_start) for f in self.files.values())
+        if declared not in (payload, with_headers):
+            raise SafetensorsError(
+                f"{index_path}: total_size {declared} disagrees with the shards "
+                f"({payload} bytes of tensors, {with_headers} with their headers)")
 
     def names(self) -> List[str]:
         return list(self.where)

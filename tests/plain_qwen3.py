@@ -207,9 +207,16 @@ def greedy(logits: Sequence[float]) -> int:
     for i, v in enumerate(logits):
         if not math.isfinite(v):
             raise ValueError("invalid sampling logits")
-        if best_v is None or v > best_v:
+        if best_v is None or _total_key(v) > _total_key(best_v):
             best, best_v = i, v
+    if best_v is None:
+        raise ValueError("invalid sampling logits")
     return best
+
+
+def _total_key(v: float):
+    """Sort key of f32::total_cmp for finite values: by value, -0.0 below +0.0."""
+    return (v, math.copysign(1.0, v))
 
 
 def sample(logits: Sequence[float], temperature: float, seed: int, request: int, position: int,
@@ -218,7 +225,7 @@ def sample(logits: Sequence[float], temperature: float, seed: int, request: int,
     :282-298 filters, :210-226 cumulative draw over F32-rounded normalised weights)."""
     if temperature == 0.0:
         return greedy(logits)
-    cand = sorted(((i, float(v)) for i, v in enumerate(logits)), key=lambda c: (-c[1], c[0]))
+    cand = sorted(((i, float(v)) for i, v in enumerate(logits)), key=lambda c: (-c[1], -math.copysign(1.0, c[1]), c[0]))
     if top_k is not None and 0 < top_k < len(cand):
         cand = cand[:top_k]
     mx = cand[0][1]

@@ -330,7 +330,7 @@ def test_steps_launched_ahead_give_the_same_tokens(folders, name, dtype):
     want, info_off = run(False, params)
     got, info_on = run(True, params)
     assert got == want
-    assert any(len(g) < 24 for g in got) and any(len(g) == 24 for g in got) or all(len(g) < 24 for g in got)
+    assert len(got[0]) <= 8 and len(got[2]) <= 14, "the requests whose own tokens are the stop tokens end there"
     assert info_off["steps_launched_ahead"] == 0 and info_on["steps_launched_ahead"] > 5
     if dtype == "float32":
         model = plain.PlainModel(folders[name])

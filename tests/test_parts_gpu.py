@@ -170,3 +170,21 @@ def test_block_part(dtype):
                rms_norm_eps=1e-5, partial_rotary_factor=1.0, rope_theta=1e4)
     ref = plain.decoder_layer(x.double(), w, "L.", cfg, torch.arange(21), None)
     assert ((hidden.double().cpu() - ref).abs() <= bound(dtype, ref)).all()
+
+
+def test_one_seed_gives_one_model_on_every_device():
+    """The random-weights generator is integer arithmetic and IEEE multiply/add only: a
+    tensor made on the GPU has the bits of the one made on the CPU, in both dtypes, across
+    the generator's chunk edge too."""
+    from inferloop_b200.weights import random_init
+    from inferloop_b200.weights.decl import WeightDecl
+    big = random_init._CHUNK + 12_345
+    a = random_init.standard_normal(2024, big, "cuda")
+    b = random_init.standard_normal(2024, big, "cpu")
+    assert torch.equal(a.cpu(), b)
+    for decl in (WeightDecl("x.weight", (130, 77)), WeightDecl("n.weight", (515,), "vector", "norm"),
+                 WeightDecl("b.bias", (96,), "vector", "bias")):
+        for dtype in (torch.float32, torch.bfloat16):
+            on_gpu = random_init.random_tensor(decl, 5, dtype, "cuda")
+            on_cpu = random_init.random_tensor(decl, 5, dtype, "cpu")
+            assert on_gpu.dtype == dtype and torch.equal(on_gpu.cpu(), on_cpu), decl.name

@@ -47,6 +47,132 @@ def test_penalties():
         host.sample(np.array([0.0, np.inf], dtype=np.float32), SamplingParams(), 0, 0)
 
 
+# ---------------------------------------------------------------- the reference's own expectations
+# Literal inputs and answers of the reference's sampler tests
+# (crates/engine/workloads/tests/unit/sampling.rs): these pin the samplers here to the
+# reference's output, not to a reading of its source.
+F32_MIN, F32_MAX = float(np.finfo(np.float32).min), float(np.finfo(np.float32).max)
+REFERENCE_GREEDY = [([2.0, 2.0, 1.0], 0), ([-0.0, 0.0, 0.0], 1), ([F32_MIN, -5.0, -6.0], 1), ([F32_MAX, F32_MAX], 0)]   # :5-12
+
+
+def test_reference_expectations_greedy():
+    """sampling.rs (tests) :4-19 and :98-99: ties, signed zero (total order: -0 < +0), the
+    extremes of the range, non-finite and empty input refused."""
+    for logits, want in REFERENCE_GREEDY:
+        assert plain.greedy(logits) == want
+        assert host.greedy(np.array(logits, dtype=np.float32)) == want
+        assert host.sample(np.array(logits, dtype=np.float32), SamplingParams(), 1, 0) == want
+    for invalid in (float("nan"), float("inf"), float("-inf")):
+        with pytest.raises(ValueError):
+            plain.greedy([F32_MAX, invalid])
+        with pytest.raises(ValueError):
+            host.sample(np.array([F32_MAX, invalid], dtype=np.float32), SamplingParams(), 1, 0)
+    with pytest.raises(ValueError):
+        host.sample(np.array([], dtype=np.float32), SamplingParams(), 1, 0)
+    with pytest.raises(ValueError):
+        plain.greedy([])
+    assert host.sample(np.ones(1024, dtype=np.float32), SamplingParams(), 1, 0) == 0
+    assert plain.greedy([1.0] * 1024) == 0
+
+
+def test_reference_expectations_filters_and_penalties():
+    """sampling.rs (tests) :103-140: nucleus 0.5 over [3, 1, 0] keeps token 0 for seeds
+    0..20; min-p 0.9 keeps token 0; presence 2.0 with generated [0, 0] turns [3, 2] to token
+    1; repetition 2.0 with prompt [0] does too."""
+    logits = np.array([3.0, 1.0, 0.0], dtype=np.float32)
+    for seed in range(20):
+        assert host.sample(logits, SamplingParams(temperature=1.0, top_p=0.5, seed=seed), 1, 0) == 0
+        assert plain.sample(logits.tolist(), 1.0, seed, 1, 0, top_p=0.5) == 0
+        assert host.sample(logits, SamplingParams(temperature=1.0, min_p=0.9, seed=seed), 1, 0) == 0
+        assert plain.sample(logits.tolist(), 1.0, seed, 1, 0, min_p=0.9) == 0
+    two = np.array([3.0, 2.0], dtype=np.float32)
+    assert host.sample(two, SamplingParams(temperature=0.0, min_p=0.9, presence_penalty=2.0), 1, 0,
+                       prompt=[1], generated=[0, 0]) == 1
+    assert host.sample(two, SamplingParams(temperature=0.0, min_p=0.9, repetition_penalty=2.0), 1, 0,
+                       prompt=[0], generated=[]) == 1
+
+
+def test_reference_expectations_top_k_trajectory():
+    """sampling.rs (tests) :49-77: logits (17 i + seed) mod 53 over 257 tokens, T = 0.7,
+    top-k in {none, 1, 7, 256, 1024}, request seed + 1, positions 0..8: the selection with a
+    partial top-k equals the full sort's.  Here: the host sampler equals the plain one."""
+    for seed in range(0, 128, 9):
+        logits = np.array([float((i * 17 + seed) % 53) for i in range(257)], dtype=np.float32)
+        for top_k in (None, 1, 7, 256, 1024):
+            p = SamplingParams(seed=seed, top_k=top_k, temperature=0.7)
+            for position in range(8):
+                assert host.sample(logits, p, seed + 1, position) == \
+                    plain.sample(logits.tolist(), 0.7, seed, seed + 1, position, top_k=top_k)
+
+
+def test_generation_defaults_from_the_folder(tmp_path):
+    """generation_config.json and eos_token_id as the reference reads them
+    (crates/model/package/src/generation/read.rs:9-100) and a request's overrides field by
+    field (generation/mod.rs:68-128)."""
+    import json
+    from inferloop_b200.sampling import GenerationDefaults
+    d = GenerationDefaults.from_configs({"eos_token_id": 7})
+    assert d.base == SamplingParams(eos_tokens=(7,)) and d.sources["eos_tokens"] == "config.json"
+    d = GenerationDefaults.from_configs({"text_config": {"eos_token_id": [3, 4]}, "eos_token_id": 9})
+    assert d.base.eos_tokens == (3, 4)
+    gen = {"do_sample": True, "temperature": 0.6, "top_k": 20, "top_p": 0.95, "eos_token_id": [151645, 151643]}
+    d = GenerationDefaults.from_configs({"eos_token_id": 1}, gen)
+    assert d.base == SamplingParams(temperature=0.6, top_k=20, top_p=0.95, eos_tokens=(151645, 151643))
+    assert d.sources["eos_tokens"] == "generation_config.json" and d.sources["min_p"] == "runtime fallback"
+    # do_sample false (or absent) forces greedy whatever temperature the file names
+    assert GenerationDefaults.from_configs({}, {"do_sample": False, "temperature": 0.6}).base.temperature == 0.0
+    assert GenerationDefaults.from_configs({}, {"temperature": 0.6}).base.temperature == 0.0
+    assert GenerationDefaults.from_configs({}, {"do_sample": True}).base.temperature == 1.0
+    assert GenerationDefaults.from_configs({}, {"do_sample": True, "top_k": 0}).base.top_k is None
+    for bad in ({"do_sample": 1}, {"top_k": -1}, {"top_k": 1.5}, {"eos_token_id": -1}, {"eos_token_id": "x"}, {"temperature": "hot"}):
+        with pytest.raises(ValueError):
+            GenerationDefaults.from_configs({}, bad)
+    # overrides
+    assert d.resolve({}) == d.base
+    assert d.resolve({"temperature": 0.0}).temperature == 0.0 and d.resolve({"top_k": 0}).top_k is None
+    assert d.resolve({"do_sample": False}).temperature == 0.0
+    g = GenerationDefaults.from_configs({"eos_token_id": 1})
+    assert g.resolve({"do_sample": True}).temperature == 1.0 and g.resolve({"do_sample": True, "temperature": 0.3}).temperature == pytest.approx(0.3)
+    r = d.resolve({"eos_token": 5})
+    assert r.eos_token == 5 and r.eos_tokens == () and r.is_eos(5) and not r.is_eos(151645)
+    r = d.resolve({"eos_tokens": [8, 9], "seed": 3})
+    assert r.eos_tokens == (8, 9) and r.eos_token is None and r.seed == 3
+    with pytest.raises(ValueError, match="unknown sampling fields"):
+        d.resolve({"temperatur": 1.0})
+    # an explicit SamplingParams that names no stop token inherits the folder's
+    assert d.with_stop_tokens(SamplingParams(temperature=0.2)).eos_tokens == (151645, 151643)
+    assert d.with_stop_tokens(SamplingParams(eos_token=2)).eos_tokens == ()
+    # from a folder
+    folder = tmp_path / "m"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps({"eos_token_id": 11}))
+    assert GenerationDefaults.from_folder(str(folder)).base.eos_tokens == (11,)
+    (folder / "generation_config.json").write_text(json.dumps({"eos_token_id": [12]}))
+    assert GenerationDefaults.from_folder(str(folder)).base.eos_tokens == (12,)
+    (folder / "generation_config.json").write_text("[1]")
+    with pytest.raises(ValueError):
+        GenerationDefaults.from_folder(str(folder))
+
+
+@pytest.mark.gpu
+def test_device_argmax_reference_expectations():
+    """The reference's literal greedy cases on the device kernel, one row each, and one wide
+    row where the only +0 sits among -0 in another CTA's part of the vocabulary."""
+    from inferloop_b200.csrc import ops
+    for logits, want in REFERENCE_GREEDY:
+        dev = torch.tensor([logits], dtype=torch.float32, device="cuda")
+        out = torch.empty(1, dtype=torch.int32, device="cuda")
+        bad = torch.empty(1, dtype=torch.int32, device="cuda")
+        ops.argmax(dev, out, bad)
+        assert out.tolist() == [want] and bad.tolist() == [0]
+    wide = torch.full((1, 151936), -0.0)
+    wide[0, 100000] = 0.0
+    wide[0, 140000] = 0.0
+    out = torch.empty(1, dtype=torch.int32, device="cuda")
+    ops.argmax(wide.cuda(), out, None)
+    assert out.tolist() == [100000]
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("vocab", [257, 1000, 151936])
 def test_device_argmax(vocab):

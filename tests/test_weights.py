@@ -90,6 +90,56 @@ def test_index_and_shard_path_escape(tmp_path):
     TensorSource(d)   # s2 is not named: fine, it is not a shard of this model
 
 
+def test_index_total_size_must_agree_with_the_shards(tmp_path):
+    """metadata.total_size is accepted as the tensors' bytes, or as those plus the shards'
+    headers, as an integer or a whole float; anything else is refused
+    (crates/model/package/src/storage/source.rs:160-181)."""
+    d = str(tmp_path)
+    write_safetensors(os.path.join(d, "s1.safetensors"), {"a": torch.zeros(2)})
+    write_safetensors(os.path.join(d, "s2.safetensors"), {"b": torch.ones(3, dtype=torch.bfloat16)})
+    wm = {"a": "s1.safetensors", "b": "s2.safetensors"}
+    payload = 2 * 4 + 3 * 2
+    headers = sum(SafetensorsFile(os.path.join(d, f)).data_start for f in ("s1.safetensors", "s2.safetensors"))
+
+    def index(meta):
+        with open(os.path.join(d, "model.safetensors.index.json"), "w") as fh:
+            json.dump({"metadata": meta, "weight_map": wm}, fh)
+
+    for good in (payload, float(payload), payload + headers):
+        index({"total_size": good})
+        assert sorted(TensorSource(d).names()) == ["a", "b"]
+    index({})                                            # some exporters omit it
+    TensorSource(d)
+    for bad, why in ((payload + 2, "disagrees"), (payload - 1, "disagrees"), (0, "empty"), (payload + 0.5, "invalid"),
+                     ("14", "invalid"), (True, "invalid")):
+        index({"total_size": bad})
+        with pytest.raises(SafetensorsError, match=why):
+            TensorSource(d)
+
+
+def test_random_weights_in_memory_equal_the_written_folder(tmp_path):
+    """One seed, one model: the tensors made directly (the path `--random-weights S` takes,
+    there on the device) are the ones a folder written with the same seed loads as."""
+    from inferloop_b200.config.registry import read_model_config
+    from inferloop_b200.models.decoder import declare_weights
+    from inferloop_b200.weights.loader import load_weights
+    from inferloop_b200.weights.random_init import random_weights, standard_normal
+    d = make_model_folder(str(tmp_path / "m"), CONFIG_B, 11)
+    _, _, spec = read_model_config(json.dumps(CONFIG_B))
+    decls = declare_weights(spec)
+    for dtype in (torch.float32, torch.bfloat16):
+        made = random_weights(decls, 11, dtype, "cpu")
+        loaded, _ = load_weights(d, decls, spec.weight_prefixes, spec.embedding_name, dtype, "cpu")
+        assert set(made) == set(loaded)
+        for name in made:
+            assert made[name].dtype == loaded[name].dtype and torch.equal(made[name], loaded[name]), name
+    # the stream: element i depends on (key, i) alone, and looks like a standard normal
+    x = standard_normal(99, 400_000, "cpu")
+    assert torch.equal(x[1000:2000], standard_normal(99, 2000, "cpu")[1000:])
+    assert abs(float(x.mean())) < 0.01 and abs(float(x.std()) - 1.0) < 0.01
+    assert abs(float((x.abs() > 2).float().mean()) - 0.0455) < 0.003 and float(x.abs().max()) < 4.7
+
+
 def test_random_model_is_seeded_by_name(tmp_path):
     d1 = make_model_folder(str(tmp_path / "m1"), CONFIG_B, 1)
     d2 = make_model_folder(str(tmp_path / "m2"), CONFIG_B, 1)
