@@ -186,7 +186,7 @@ def main() -> int:
             for i in range(0, len(t), chunk):
                 part = t[i:i + chunk]
                 logits, drawn = runner.step([StepEntry(rid, part, [len(part) - 1])], draw_greedy=True)
-            last[rid] = int(drawn[0].item())
+            last[rid] = int(drawn.ids[0].item())
         return last
 
     def decode_device(batch, steps, warmup, tag):

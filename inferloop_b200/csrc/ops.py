@@ -331,6 +331,13 @@ def gemm_tc_plan(M: int, N: int, K: int, accumulate: bool = False, swiglu: bool 
     return dict(zip(keys, list(out)))
 
 
+def device_error_tensor(device) -> Optional[torch.Tensor]:
+    """The one-int flag that kernels on `device` raise when a bounded wait runs out (None
+    while no tensor-core kernel has run there yet)."""
+    st = _TC.get(torch.device(device))
+    return None if st is None else st.error
+
+
 def check_device_errors() -> None:
     """Raise if a kernel gave up a bounded wait since the last check (synchronises)."""
     for dev, st in _TC.items():

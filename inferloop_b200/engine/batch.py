@@ -25,6 +25,23 @@ class StepEntry:
 
 
 @dataclass
+class Drawn:
+    """Token ids a step drew on the device with their flags side by side: `pair` is int32
+    [2, capacity], row 0 the arg-max of each logits row, row 1 non-zero where that row held a
+    non-finite value; the first `n` columns belong to the step."""
+    pair: torch.Tensor
+    n: int
+
+    @property
+    def ids(self) -> torch.Tensor:
+        return self.pair[0, :self.n]
+
+    @property
+    def flags(self) -> torch.Tensor:
+        return self.pair[1, :self.n]
+
+
+@dataclass
 class StepContext:
     n_tokens: int
     n_seqs: int

@@ -36,7 +36,7 @@ class _Flight:
     """A step that is on the device."""
     plan: StepPlan
     sampling_work: list
-    drawn: Optional[torch.Tensor]               # ids still on the device (plain greedy), or None
+    drawn: Optional[object]                     # `Drawn`: ids still on the device (plain greedy), or None
     sampled: Optional[Dict[Hashable, int]]      # ids on the host, once known
     dropped: set = field(default_factory=set)   # requests that ended before this step's ids were read
 
@@ -88,8 +88,9 @@ class Engine:
                     model, random_weights_seed, dtype=dt, device=dev, page_size=self.block_size,
                     num_pages=first_pages, max_requests=max(max_num_seqs, 1))
             if pages is None:
+                step_tokens = max_num_batched_tokens or max(prefill_chunk_tokens + max_num_seqs - 1, 1)
                 self.runner.resize_cache(self._pages_from_memory(dev, gpu_memory_utilization, max_num_seqs,
-                                                                 max_model_len), max(max_num_seqs, 1))
+                                                                 max_model_len, step_tokens), max(max_num_seqs, 1))
         spec_len = self.runner.spec.max_positions
         self.max_model_len = min(int(max_model_len), spec_len) if max_model_len else spec_len
         cfg = SchedulerConfig(
@@ -104,17 +105,23 @@ class Engine:
         self._ahead: Optional[_Flight] = None
         self.steps_launched_ahead = 0
         self.lookahead = True                   # launch the next decode step before reading this one's ids
+        self.max_finished_kept = 1024
         self.requests: Dict[Hashable, Request] = {}
 
     # ------------------------------------------------------------------ sizing
     def _pages_from_memory(self, dev, utilization: float, max_num_seqs: int,
-                           max_model_len: Optional[int]) -> int:
+                           max_model_len: Optional[int], step_tokens: int) -> int:
         """budget = min(total * utilization - used, free - 1 GiB)
-        (crates/service/cli/src/backend/cuda.rs:52-64), less room for activations."""
+        (crates/service/cli/src/backend/cuda.rs:52-64), less what the largest step's
+        activations, logits and kernel scratch take: that is computed from the model's own
+        sizes (`scratch_bytes`), with a quarter on top and 256 MiB for the fixed scratch of
+        the kernels and the sampler."""
         free, total = torch.cuda.mem_get_info(dev)
         used = total - free
         budget = min(total * utilization - used, free - (1 << 30))
-        budget -= 4 << 30          # activations and logits of the largest step
+        reserve = self.runner.model.scratch_bytes(int(step_tokens), max(max_num_seqs, 1))
+        self.activation_reserve = reserve + reserve // 4 + (256 << 20)
+        budget -= self.activation_reserve
         per_page = sum(g.page_bytes(torch.empty((), dtype=self.runner.cache.dtype).element_size())
                        for g in self.runner.cache.groups)
         if per_page == 0:
@@ -149,6 +156,13 @@ class Engine:
         req = Request(request_id, toks, params, int(max_new_tokens))
         self.scheduler.add(req)
         self.requests[request_id] = req
+        # finished requests stay readable (`result`) until taken (`take_completed`); beyond
+        # `max_finished_kept` the oldest are forgotten so that a long run does not grow
+        finished = self.scheduler.finished
+        while len(finished) > self.max_finished_kept:
+            old = next(iter(finished))
+            del finished[old]
+            self.requests.pop(old, None)
         return request_id
 
     def abort(self, request_id: Hashable) -> None:
@@ -325,6 +339,17 @@ class Engine:
 
     def result(self, request_id: Hashable) -> Request:
         return self.requests[request_id]
+
+    def take_completed(self) -> List[Request]:
+        """Hand over every finished request and forget it (the reference's
+        `Engine::take_completed`, crates/engine/runtime/src/engine/mod.rs:118-159): a
+        long-running caller drains results this way, so that the engine's memory does not
+        grow with the number of requests it has served."""
+        done = list(self.scheduler.finished.values())
+        for r in done:
+            self.requests.pop(r.id, None)
+        self.scheduler.finished.clear()
+        return done
 
     def inspect(self) -> dict:
         """Counterpart of the reference's RuntimeInspection

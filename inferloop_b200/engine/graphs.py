@@ -24,7 +24,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from ..csrc import ops
-from .batch import StepContext, StepEntry, StepStager
+from .batch import Drawn, StepContext, StepEntry, StepStager
 
 BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
@@ -44,7 +44,11 @@ class _Recorded:
     logits: torch.Tensor
     workspace_generation: int
     kernels: int                       # launches recorded
-    drawn: Optional[torch.Tensor] = None
+    pair: Optional[torch.Tensor] = None       # [2, bucket]: drawn ids, and their non-finite flags
+
+    @property
+    def drawn(self) -> Optional[torch.Tensor]:
+        return None if self.pair is None else self.pair[0]
 
 
 class DecodeGraphs:
@@ -91,11 +95,11 @@ class DecodeGraphs:
         r = self.runner
         ints = torch.zeros(StepStager.layout(self._shapes(bucket)), dtype=torch.int32, device=r.device)
         ctx = self._prepare(entries, bucket, ints)
-        drawn = torch.zeros(bucket, dtype=torch.int32, device=r.device) if with_argmax else None
+        pair = torch.zeros((2, bucket), dtype=torch.int32, device=r.device) if with_argmax else None
         # Once eagerly: builds kernels, sizes every scratch buffer, and does this step's work.
         logits = r.model.forward(ctx, r.cache)
         if with_argmax:
-            ops.argmax(logits, drawn, None)
+            ops.argmax(logits, pair[0], pair[1])
         torch.cuda.current_stream(r.device).synchronize()
         generation = r.ctx.workspace.generation
         graph = torch.cuda.CUDAGraph()
@@ -110,14 +114,14 @@ class DecodeGraphs:
             with torch.cuda.graph(graph):
                 logits = r.model.forward(ctx, r.cache)
                 if with_argmax:
-                    ops.argmax(logits, drawn, None)
+                    ops.argmax(logits, pair[0], pair[1])
         finally:
             if gc_was_on:
                 gc.enable()
         kernels = ops.LAUNCHES - before
         if r.ctx.workspace.generation != generation:
             raise RuntimeError("a scratch buffer was reallocated while a graph was recorded")
-        rec = _Recorded(graph, ints, ctx, logits, generation, kernels, drawn)
+        rec = _Recorded(graph, ints, ctx, logits, generation, kernels, pair)
         self._recorded[key] = rec
         return rec
 
@@ -166,14 +170,14 @@ class DecodeGraphs:
             self._prepare_replay(entries, bucket, rec)
             rec.graph.replay()
             self.replays += 1
-        return rec.logits[:n], (rec.drawn[:n] if with_argmax else None), rec.kernels
+        return rec.logits[:n], (Drawn(rec.pair, n) if with_argmax else None), rec.kernels
 
-    def step_ahead(self, entries: Sequence[StepEntry], previous_drawn: torch.Tensor) -> Optional[torch.Tensor]:
+    def step_ahead(self, entries: Sequence[StepEntry], previous_drawn: Drawn) -> Optional[Drawn]:
         """The decode step that follows one whose tokens are still being computed: the same
         requests in the same order, each continuing with the token the previous step draws.
         The ids never visit the host: they are copied on the device from `previous_drawn`
-        into this step's token array before the replay.  Returns the device tensor the new
-        ids will be in, or None when the step cannot be launched this way (no recorded graph
+        into this step's token array before the replay.  Returns the ids the step will draw
+        (on the device), or None when the step cannot be launched this way (no recorded graph
         for this size yet, or not enough pages), in which case nothing has changed."""
         from ..cache.pages import OutOfPages
         n = len(entries)
@@ -187,10 +191,10 @@ class DecodeGraphs:
             self._prepare_replay(entries, bucket, rec)
         except OutOfPages:
             return None
-        rec.ctx.tokens[:n].copy_(previous_drawn[:n])
+        rec.ctx.tokens[:n].copy_(previous_drawn.ids)
         rec.graph.replay()
         self.replays += 1
-        return rec.drawn[:n]
+        return Drawn(rec.pair, n)
 
     def recorded(self, n: int, with_argmax: bool) -> Optional[_Recorded]:
         """The graph recorded for this many sequences (the short-context one if both exist)."""

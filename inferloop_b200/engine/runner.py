@@ -28,7 +28,7 @@ from ..models.decoder import DecoderModel
 from ..parts.base import BuildContext, Workspace
 from ..weights.loader import load_weights
 from ..weights.random_init import random_weights
-from .batch import StepContext, StepEntry, StepStager
+from .batch import Drawn, StepContext, StepEntry, StepStager
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
           "f32": torch.float32, "fp32": torch.float32}
@@ -261,10 +261,10 @@ class ModelRunner:
         """Whether every group has the pages this step would take."""
         return step_fits(self.cache, entries)
 
-    def step_ahead(self, entries: Sequence[StepEntry], previous_drawn: torch.Tensor) -> Optional[torch.Tensor]:
+    def step_ahead(self, entries: Sequence[StepEntry], previous_drawn: Drawn) -> Optional[Drawn]:
         """Launch the decode step after one that is still running (see
         `DecodeGraphs.step_ahead`); the entries' tokens are placeholders.  Returns the device
-        tensor of the ids it will draw, or None if it was not launched."""
+        ids it will draw (still on the device), or None if it was not launched."""
         if self.graphs is None or not self.graphs.eligible(entries):
             return None
         drawn = self.graphs.step_ahead(entries, previous_drawn)
@@ -290,7 +290,8 @@ class ModelRunner:
         device, in the order of the entries and of each entry's `want`).  The tensor is a
         scratch buffer: it is valid until the next step.  With `draw_greedy` the arg-max
         of every row is computed in the same launch sequence and (logits, ids) is
-        returned, ids being an int32 device tensor."""
+        returned, ids being a `Drawn` (the ids and, beside them, a flag per row that is set
+        where the logits held a non-finite value)."""
         from ..csrc import ops
         before = ops.LAUNCHES
         drawn = None
@@ -303,8 +304,10 @@ class ModelRunner:
             logits = self.model.forward(ctx, self.cache)
             n_tokens = ctx.n_tokens
             if draw_greedy and logits.shape[0]:
-                drawn = self.ctx.workspace.buffer("runner.drawn", (logits.shape[0],), torch.int32)
-                ops.argmax(logits, drawn, None)
+                rows = logits.shape[0]
+                pair = self.ctx.workspace.buffer("runner.drawn", (2, rows), torch.int32)
+                ops.argmax(logits, pair[0], pair[1])
+                drawn = Drawn(pair, rows)
             self.kernels_last_step = ops.LAUNCHES - before
         n = len(entries)
         req = (ctypes.c_longlong * n)(*[self.cache.id_of(e.request) for e in entries])

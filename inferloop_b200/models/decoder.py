@@ -69,6 +69,16 @@ class DecoderModel:
             total += self.head.numel() * self.head.element_size()
         return total
 
+    def scratch_bytes(self, tokens: int, logit_rows: int) -> int:
+        """Workspace a step of `tokens` tokens with `logit_rows` wanted rows asks for: the
+        residual stream, the largest block's buffers (blocks share them by name), the
+        selected rows and their logits."""
+        s = self.spec
+        size = torch.empty((), dtype=self.ctx.dtype).element_size()
+        blocks = max((b.scratch_bytes(tokens) for b in self.blocks), default=0)
+        return (tokens * s.hidden_size * 4 + blocks + logit_rows * s.hidden_size * (4 + size)
+                + logit_rows * s.vocab_size * 4)
+
     # ------------------------------------------------------------------ run
     def forward(self, step, caches) -> torch.Tensor:
         """Run the step's tokens through every run-order entry; returns 32-bit logits

@@ -83,6 +83,11 @@ class GQAttention(Mixer):
     def cache_needs(self) -> CacheNeeds:
         return CacheNeeds(paged=PagedKVNeed(self.nkv, self.d, self.window))
 
+    def scratch_bytes(self, tokens: int) -> int:
+        size = torch.empty((), dtype=self.ctx.dtype).element_size()
+        width = (self.nq + 2 * self.nkv) * self.d
+        return tokens * ((width + 2 * self.nq * self.d) * size + self.rotary_dim * 4)
+
     # ------------------------------------------------------------------ run
     def forward(self, x: torch.Tensor, residual: torch.Tensor, step, cache) -> None:
         T = x.shape[0]

@@ -123,6 +123,11 @@ class Part:
     def cache_needs(self) -> CacheNeeds:
         return CacheNeeds()
 
+    def scratch_bytes(self, tokens: int) -> int:
+        """Bytes of workspace buffers a step of `tokens` tokens makes this part ask for (an
+        estimate from its sizes; the engine reserves this much beside the cache)."""
+        return 0
+
 
 class Norm(Part):
     def forward(self, x: torch.Tensor, out: torch.Tensor) -> None:

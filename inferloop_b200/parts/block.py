@@ -41,6 +41,10 @@ class PreNormBlock(Block):
     def cache_needs(self) -> CacheNeeds:
         return self.mixer.cache_needs()
 
+    def scratch_bytes(self, tokens: int) -> int:
+        size = torch.empty((), dtype=self.ctx.dtype).element_size()
+        return tokens * self.hidden * size + self.mixer.scratch_bytes(tokens) + self.ffn.scratch_bytes(tokens)
+
     def forward(self, hidden: torch.Tensor, step, cache) -> None:
         ws = self.ctx.workspace
         normed = ws.buffer("block.normed", hidden.shape, self.ctx.dtype)

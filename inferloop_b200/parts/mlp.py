@@ -53,6 +53,11 @@ class SwiGLU(FeedForward):
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = tensors[n["down"]].contiguous()
 
+    def scratch_bytes(self, tokens: int) -> int:
+        size = torch.empty((), dtype=self.ctx.dtype).element_size()
+        fused = self.ctx.dtype == torch.bfloat16 and self.inter % 64 == 0 and self.hidden % 8 == 0
+        return tokens * self.inter * size * (1 if fused else 3)
+
     def forward(self, x: torch.Tensor, residual: torch.Tensor, step) -> None:
         T = x.shape[0]
         ws, dt = self.ctx.workspace, self.ctx.dtype

@@ -28,6 +28,7 @@ class DeviceSampler:
         self.temperature = torch.empty(rows, dtype=torch.float32, device=self.device)
         self.uniform = torch.empty(rows, dtype=torch.float64, device=self.device)
         self.h_out = torch.empty(2 * rows, dtype=torch.int32).pin_memory()
+        self.h_error = torch.zeros(1, dtype=torch.int32).pin_memory()
         self.h_temp = torch.empty(rows, dtype=torch.float32).pin_memory()
         self.h_uniform = torch.empty(rows, dtype=torch.float64).pin_memory()
         # per-row filters, staged as one block: top_k (int32 bits), top_p, min_p
@@ -104,25 +105,38 @@ class DeviceSampler:
             raise ValueError("invalid sampling logits (a non-finite value)")
         return vals[:rows]
 
-    def start_read(self, drawn: torch.Tensor):
-        """Begin copying token ids that a step drew on the device to the host; work that
-        is launched after this call does not delay the ids.  Returns a handle for
-        `finish_read`."""
-        rows = drawn.numel()
-        if rows > self._cap:
-            self._grow(max(rows, 2 * self._cap))
-        self.h_out[:rows].copy_(drawn, non_blocking=True)
+    def start_read(self, drawn):
+        """Begin copying to the host what a step drew on the device (`Drawn`: the ids and
+        the flags of non-finite rows, as one contiguous copy) and the flag that kernels raise when
+        they give up a bounded wait; work that is launched after this call does not delay
+        them.  Returns a handle for `finish_read`."""
+        rows, width = drawn.n, drawn.pair.shape[1]
+        if width > self._cap:
+            self._grow(max(width, 2 * self._cap))
+        self.h_out[:2 * width].copy_(drawn.pair.view(-1), non_blocking=True)
+        self.d2h_bytes_last = 2 * width * 4
+        error = ops.device_error_tensor(self.device)
+        if error is not None:
+            self.h_error.copy_(error, non_blocking=True)
+            self.d2h_bytes_last += 4
         event = torch.cuda.Event()
         event.record(torch.cuda.current_stream(self.device))
-        self.d2h_bytes_last = rows * 4
-        return rows, event
+        return rows, width, event
 
     def finish_read(self, handle) -> List[int]:
-        """Wait for the copy begun by `start_read` and return the ids."""
-        rows, event = handle
+        """Wait for the copy begun by `start_read` and return the ids.  Raises, before any
+        id is handed out, if a row held a non-finite logit (the reference's greedy refuses
+        those: crates/engine/workloads/src/sampling.rs:175-180) or a kernel gave up a wait."""
+        rows, width, event = handle
         event.synchronize()
-        return self.h_out[:rows].tolist()
+        ids = self.h_out[:rows].tolist()
+        if int(self.h_error[0]) != 0:
+            self.h_error[0] = 0
+            ops.check_device_errors()
+        if any(self.h_out[width:width + rows].tolist()):
+            raise ValueError("invalid sampling logits (a non-finite value)")
+        return ids
 
-    def read_ids(self, drawn: torch.Tensor) -> List[int]:
+    def read_ids(self, drawn) -> List[int]:
         """Token ids that a step already drew on the device (synchronises)."""
         return self.finish_read(self.start_read(drawn))

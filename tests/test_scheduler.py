@@ -153,3 +153,22 @@ def test_half_portion_rule():
     e2.scheduler.config.max_num_batched_tokens = 7       # 4 left >= half of 8
     e2.step()
     assert dict(e2.runner.steps[-1])["late"] == 4
+
+
+def test_finished_requests_are_handed_over_and_forgotten():
+    """`take_completed` drains results; without it the engine keeps at most
+    `max_finished_kept` finished requests, the newest ones."""
+    e = make(FakeRunner(num_pages=64))
+    ids = [e.submit(p, SamplingParams(), 3) for p in PROMPTS[:3]]
+    while not e.is_idle():
+        e.step()
+    done = e.take_completed()
+    assert sorted(r.id for r in done) == sorted(ids) and all(len(r.generated) == 3 for r in done)
+    assert e.take_completed() == [] and not e.requests and not e.scheduler.finished
+    e.max_finished_kept = 2
+    for k in range(5):
+        e.submit(PROMPTS[k], SamplingParams(), 2, request_id=f"k{k}")
+        while not e.is_idle():
+            e.step()
+    assert len(e.scheduler.finished) <= 3 and "k4" in e.requests and "k0" not in e.requests
+    assert e.result("k4").generated and e.inspect()["finished"] <= 3
