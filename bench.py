@@ -1,21 +1,30 @@
 #!/usr/bin/env python3
-"""Headline measurement: Qwen3-8B-sized random bf16 model, decode tokens per second.
+"""Measurement of the engine on one B200, random bf16 weights, synthetic token ids.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
+                    [--config 8b|14b-mixed|32b-long] [--breakdown]
 
-One JSON line on stdout.  A "step" is one decode step of the whole batch.
+One JSON line on stdout.  The default (`--config 8b`) is the headline: Qwen3-8B layer sizes,
+36 layers, batch 8, 1,024-token prompts; a "step" is one decode step of the whole batch.
   value     decoded tokens per second of K steps run back to back on the device (each
             step's arg-max feeds the next step there), timed with CUDA events;
   e2e       the same through the Python entry point (`Engine.step`): host token ids in,
             host token ids out, every step with its host->device copy of the step's
             arrays from pinned memory and its device->host read of the drawn ids;
-  prefill   one 2,048-token prompt to its last logits;
+  prefill   one 2,048-token prompt to its last logits (median of several);
   roofline  bytes a decode step must read (every weight once + the cache of the live
             requests) / its time, against the measured copy bandwidth;
   points    decode at batch 1 and 64.
+`--config 14b-mixed`: Qwen3-14B layer sizes, 32 requests with prompts of 128 to 3,072 tokens
+through `Engine.generate` with prompt portions of 512 tokens mixed with decoding, 128 greedy
+tokens each; a "step" is one engine step and `--steps` is ignored (the job is run whole, once
+untimed and once timed).  `--config 32b-long`: Qwen3-32B layer sizes, 8,192-token prompts,
+decode at batch 1 and 16.  `--breakdown` adds the share of every op class in a decode step
+and in the prefill step, from a pair of CUDA events around every kernel (the engine's
+`device_timing="node"` mode).
 Peaks come from MEASURED_PEAKS.json beside this file when present, else the fallback
-figures 6.65 TB/s and 1.59 PFLOP/s.  Weights (15 GB) exceed L2 (126 MB), so every step
-reads them from HBM: no L2 flush is needed between timed steps.
+figures 6.65 TB/s and 1.59 PFLOP/s.  Weights (15 GB and more) exceed L2 (126 MB), so every
+step reads them from HBM: no L2 flush is needed between timed steps.
 """
 from __future__ import annotations
 
@@ -31,16 +40,21 @@ import time
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 
-# BASELINE.json configs[2]: Qwen3-8B layer sizes
-QWEN3_8B = dict(
-    architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=36, hidden_size=4096,
-    num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
-    vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, attention_bias=False,
-    tie_word_embeddings=False, max_position_embeddings=4096, hidden_act="silu")
+_COMMON = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", head_dim=128, vocab_size=151936,
+               rope_theta=1000000.0, rms_norm_eps=1e-6, attention_bias=False, tie_word_embeddings=False,
+               hidden_act="silu")
+# layer sizes of Qwen3-8B, Qwen3-14B and Qwen3-32B
+QWEN3_8B = dict(_COMMON, num_hidden_layers=36, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+                intermediate_size=12288, max_position_embeddings=4096)
+QWEN3_14B = dict(_COMMON, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
+                 intermediate_size=17408, max_position_embeddings=4096)
+QWEN3_32B = dict(_COMMON, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8,
+                 intermediate_size=25600, max_position_embeddings=16384)
 FULL_LAYERS = 36
 SEED = 2
 PROMPT_LEN = 1024
 PREFILL_LEN = 2048
+PREFILL_SAMPLES = 5
 PAGE = 16
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -130,69 +144,62 @@ def model_numbers(cfg: dict):
     nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     per_layer = (nq + 2 * nkv) * d * H + nq * d * H + 3 * H * I
     return {"layer_params": per_layer, "head_params": V * H, "kv_bytes_per_token": 2 * nkv * d * 2 * L,
-            "attn_flops_per_pair": 4 * nq * d * L}
+            "attn_flops_per_pair": 4 * nq * d * L, "layers": L}
 
 
-def main() -> int:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=128)
-    ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers (named in config) to save time")
-    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 / prefill side measurements")
-    args = ap.parse_args()
+def step_flops(nums: dict, tokens: int, logit_rows: int, pairs: int) -> float:
+    return (2.0 * tokens * nums["layer_params"] * nums["layers"] + 2.0 * logit_rows * nums["head_params"]
+            + nums["attn_flops_per_pair"] * pairs)
 
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "pip: the reference checkout 'is not installable: neither setup.py nor pyproject.toml found' (a Rust workspace; no cargo/rustc "
-                          "on this machine; it has no Python API)"}))
-        return 0
-    if args.gpus != 1:
-        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
-        return 2
-    if args.warmup < 3:
-        args.warmup = 3
 
-    import torch
-    from inferloop_b200.csrc import ops
-    from inferloop_b200.engine import StepEntry
-    from inferloop_b200.engine.engine import Engine
-    from inferloop_b200.sampling import SamplingParams
+def flat_config(name: str, cfg: dict, **more) -> dict:
+    out = {"model": name, "layers": cfg["num_hidden_layers"], "hidden": cfg["hidden_size"],
+           "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+           "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "kv_page": PAGE, "kv_dtype": "bf16",
+           "sampling": "greedy", "parallelism": "1 GPU"}
+    out.update(more)
+    return out
 
-    dev = torch.device("cuda:0")
-    cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
-    nums = model_numbers(cfg)
-    pk = peaks()
-    max_batch = max(64, args.batch)
-    tokens_per_seq = PROMPT_LEN + args.warmup + args.steps + 64
-    pages = max_batch * (-(-tokens_per_seq // PAGE)) + 256
-    t0 = time.time()
-    engine = Engine(cfg, dtype="bfloat16", device=0, block_size=PAGE, num_gpu_blocks_override=pages,
-                    max_num_seqs=max_batch, max_model_len=4096, prefill_chunk_tokens=PREFILL_LEN,
-                    max_num_batched_tokens=PREFILL_LEN + max_batch, random_weights_seed=SEED)
-    runner = engine.runner
-    print(f"[bench] model ready in {time.time() - t0:.1f} s, weights {runner.model.weight_bytes() / 1e9:.2f} GB",
-          file=sys.stderr, flush=True)
-    gen = torch.Generator().manual_seed(SEED)
 
-    def prompts(n, length):
-        return torch.randint(0, cfg["vocab_size"], (n, length), generator=gen).tolist()
+class Bench:
+    """An engine with random weights and the measurements made on it."""
 
-    def prefill(ids, toks, chunk=PREFILL_LEN):
+    def __init__(self, cfg: dict, seed: int, pages: int, max_seqs: int, max_model_len: int, chunk: int) -> None:
+        import torch
+        from inferloop_b200.engine.engine import Engine
+        self.torch = torch
+        self.cfg, self.nums, self.pk = cfg, model_numbers(cfg), peaks()
+        t0 = time.time()
+        self.engine = Engine(cfg, dtype="bfloat16", device=0, block_size=PAGE, num_gpu_blocks_override=pages,
+                             max_num_seqs=max_seqs, max_model_len=max_model_len, prefill_chunk_tokens=chunk,
+                             max_num_batched_tokens=chunk + max_seqs, random_weights_seed=seed)
+        self.runner = self.engine.runner
+        self.chunk = chunk
+        self.weight_bytes = self.runner.model.weight_bytes()
+        print(f"[bench] model ready in {time.time() - t0:.1f} s, weights {self.weight_bytes / 1e9:.2f} GB",
+              file=sys.stderr, flush=True)
+        self.gen = torch.Generator().manual_seed(seed)
+
+    def prompts(self, n, length):
+        return self.torch.randint(0, self.cfg["vocab_size"], (n, length), generator=self.gen).tolist()
+
+    def prefill(self, ids, toks):
+        """Every prompt in portions of `chunk`; returns each request's first drawn token."""
+        from inferloop_b200.engine import StepEntry
         last = {}
         for rid, t in zip(ids, toks):
-            for i in range(0, len(t), chunk):
-                part = t[i:i + chunk]
-                logits, drawn = runner.step([StepEntry(rid, part, [len(part) - 1])], draw_greedy=True)
+            for i in range(0, len(t), self.chunk):
+                part = t[i:i + self.chunk]
+                _, drawn = self.runner.step([StepEntry(rid, part, [len(part) - 1])], draw_greedy=True)
             last[rid] = int(drawn.ids[0].item())
         return last
 
-    def decode_device(batch, steps, warmup, tag):
-        """K decode steps back to back on the device; returns (tokens/s, ms/step, kernels/step, mean ctx)."""
+    def decode_device(self, batch, steps, warmup, tag, prompt_len):
+        """K decode steps back to back on the device; returns (tokens/s, ms/step, kernels/step, mean context)."""
+        from inferloop_b200.engine import StepEntry
+        torch, runner = self.torch, self.runner
         ids = [f"{tag}{i}" for i in range(batch)]
-        last = prefill(ids, prompts(batch, PROMPT_LEN))
+        last = self.prefill(ids, self.prompts(batch, prompt_len))
         entries = [StepEntry(rid, [last[rid]], [0]) for rid in ids]
         out = runner.graphs.run_greedy(entries, warmup)
         entries = [StepEntry(rid, [int(t)], [0]) for rid, t in zip(ids, out[-1].tolist())]
@@ -209,20 +216,99 @@ def main() -> int:
             runner.end(rid)
         return batch * steps / (ms / 1e3), ms / steps, kernels, start_ctx + steps / 2
 
+    def decode_roofline(self, batch, mean_ctx, ms_per_step) -> dict:
+        step_bytes = self.weight_bytes + batch * mean_ctx * self.nums["kv_bytes_per_token"]
+        achieved = step_bytes / (ms_per_step / 1e3) / 1e9
+        return {"bound": "hbm", "achieved": round(achieved, 1), "peak": self.pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / self.pk["hbm_gbs"], 4)}
+
+    def prefill_timed(self, length, warmup, samples) -> dict:
+        """One prompt of `length` tokens (in portions of `chunk`) to its last logits: the
+        median of `samples` runs after `warmup` untimed ones."""
+        from inferloop_b200.engine import StepEntry
+        torch, runner = self.torch, self.runner
+        toks = self.prompts(warmup + samples, length)
+        times = []
+        for i, t in enumerate(toks):
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for k in range(0, length, self.chunk):
+                part = t[k:k + self.chunk]
+                runner.step([StepEntry("pf", part, [len(part) - 1] if k + self.chunk >= length else [])])
+            b.record()
+            torch.cuda.synchronize()
+            runner.end("pf")
+            if i >= warmup:
+                times.append(a.elapsed_time(b))
+        pms = statistics.median(times)
+        flops = sum(step_flops(self.nums, min(self.chunk, length - k), 1 if k + self.chunk >= length else 0,
+                               sum(range(k + 1, min(k + self.chunk, length) + 1)))
+                    for k in range(0, length, self.chunk))
+        return {"value": round(length / (pms / 1e3), 1), "tokens": length, "ms": round(pms, 3),
+                "frac": round(flops / (pms / 1e3) / (self.pk["bf16_tflops"] * 1e12), 4),
+                "peak_tflops": self.pk["bf16_tflops"],          # the burst figure: the stricter of the two measured peaks
+                "samples": [round(t, 3) for t in times]}
+
+    def breakdown(self, batch, prompt_len, prefill_len) -> dict:
+        """Share of every op class in a decode step of `batch` sequences and in one prefill
+        step, from a pair of events around each kernel (steps run kernel by kernel)."""
+        from inferloop_b200.engine import StepEntry
+        runner = self.runner
+        ids = [f"bd{i}" for i in range(batch)]
+        last = self.prefill(ids, self.prompts(batch, prompt_len))
+        runner.set_device_timing("node")
+        out = {}
+        try:
+            entries = [StepEntry(rid, [last[rid]], [0]) for rid in ids]
+            for i in range(3 + 8):
+                if i == 3:
+                    runner.timer.reset()
+                _, drawn = runner.step(entries, draw_greedy=True)
+                entries = [StepEntry(rid, [int(t)], [0]) for rid, t in zip(ids, drawn.ids.tolist())]
+            out["decode"] = _per_step(runner.timer.summary())
+            for rid in ids:
+                runner.end(rid)
+            toks = self.prompts(3, prefill_len)
+            for i, t in enumerate(toks):
+                if i == 2:
+                    runner.timer.reset()
+                runner.step([StepEntry("bdp", t[:self.chunk], [min(len(t), self.chunk) - 1])], draw_greedy=True)
+                runner.end("bdp")
+            out["prefill"] = _per_step(runner.timer.summary())
+        finally:
+            runner.set_device_timing("off")
+        return out
+
+
+def _per_step(summary: dict) -> dict:
+    n = max(summary.get("steps", {}).get("count", 1), 1)
+    return {"steps": n, "ms_per_step_events_around_step": round(summary["steps"]["ms_total"] / n, 4),
+            "ms_per_step_sum_of_kernels": round(summary["ops_ms_total"] / n, 4),
+            "ops": {k: {"us_per_step": round(1e3 * v["ms"] / n, 2), "launches_per_step": v["launches"] / n,
+                        "share": v["share"]} for k, v in summary["ops"].items()}}
+
+
+# ----------------------------------------------------------------------------- the three configurations
+def run_8b(args) -> dict:
+    import torch
+    from inferloop_b200.sampling import SamplingParams
+    cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    max_batch = max(64, args.batch)
+    tokens_per_seq = PROMPT_LEN + args.warmup + args.steps + 64
+    pages = max_batch * (-(-tokens_per_seq // PAGE)) + 256
+    bench = Bench(cfg, SEED, pages, max_batch, 4096, PREFILL_LEN)
+    engine, runner = bench.engine, bench.runner
+
     # ---------------------------------------------------------------- headline: device-timed decode
     with ClockSampler() as clocks:
-        value, ms_per_step, kernels, mean_ctx = decode_device(args.batch, args.steps, args.warmup, "d")
+        value, ms_per_step, kernels, mean_ctx = bench.decode_device(args.batch, args.steps, args.warmup, "d", PROMPT_LEN)
     clock_info = clocks.summary()
-    weight_bytes = runner.model.weight_bytes()
-    step_bytes = weight_bytes + args.batch * mean_ctx * nums["kv_bytes_per_token"]
-    achieved = step_bytes / (ms_per_step / 1e3) / 1e9
 
     # ---------------------------------------------------------------- end to end through Engine.step
-    e2e_prompts = prompts(args.batch, PROMPT_LEN)
-    for p in e2e_prompts:
+    for p in bench.prompts(args.batch, PROMPT_LEN):
         engine.submit(p, SamplingParams(), max_new_tokens=args.warmup + args.steps + 32)
-    while any(engine.runner.cache.length(r.id) < PROMPT_LEN for r in engine.scheduler.running) \
-            or engine.scheduler.waiting:
+    while any(runner.cache.length(r.id) < PROMPT_LEN for r in engine.scheduler.running) or engine.scheduler.waiting:
         engine.step()
     for _ in range(args.warmup):
         engine.step()
@@ -230,61 +316,160 @@ def main() -> int:
     h2d = d2h = 0
     t_start = time.perf_counter()
     for _ in range(args.steps):
-        outs = engine.step()
+        engine.step()
         h2d += runner.stager.bytes_last
-        d2h += 4 * len(outs)
+        d2h += engine.sampler.d2h_bytes_last
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t_start
     e2e_value = args.batch * args.steps / e2e_s
     while not engine.is_idle():
         engine.step()
+    engine.take_completed()
 
     result = {
         "metric": "Qwen3-8B bf16 decode tok/s", "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random-init weights (seed 2), token ids uniform in [0, vocab)",
-        "config": {"model": "Qwen3-8B sizes", "global_batch": args.batch, "seq_len": 4096,
-                   "prompt_len": PROMPT_LEN, "parallelism": "1 GPU", "layers": args.layers,
-                   "layers_full": FULL_LAYERS, "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
-                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
-                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "kv_page": PAGE,
-                   "kv_dtype": "bf16", "sampling": "greedy", "l2": "inputs larger than L2 (weights 15 GB)",
-                   "peaks": pk["source"]},
+        "config": flat_config("Qwen3-8B sizes", cfg, global_batch=args.batch, seq_len=4096, prompt_len=PROMPT_LEN,
+                              layers_full=FULL_LAYERS, l2="inputs larger than L2 (weights 15 GB)",
+                              peaks=bench.pk["source"]),
         "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": h2d // args.steps,
                 "d2h_bytes_per_step": d2h // args.steps},
         "gpu_launches": kernels * args.steps,
         "clocks": clock_info,
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "roofline": bench.decode_roofline(args.batch, mean_ctx, ms_per_step),
     }
-
     if not args.no_points:
-        # ------------------------------------------------------------ prefill of 2,048 tokens
-        toks = prompts(args.warmup + 1, PREFILL_LEN)
-        for i in range(min(args.warmup, 3)):
-            runner.step([StepEntry(f"pw{i}", toks[i], [PREFILL_LEN - 1])])
-            runner.end(f"pw{i}")
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        runner.step([StepEntry("pf", toks[-1], [PREFILL_LEN - 1])])
-        b.record()
-        torch.cuda.synchronize()
-        runner.end("pf")
-        pms = a.elapsed_time(b)
-        T = PREFILL_LEN
-        flops = 2 * T * nums["layer_params"] * args.layers + 2 * nums["head_params"] \
-            + nums["attn_flops_per_pair"] * T * (T + 1) / 2
-        result["prefill"] = {"value": round(T / (pms / 1e3), 1), "tokens": T, "ms": round(pms, 3),
-                             "frac": round(flops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
-                             "peak_tflops": pk["bf16_tflops"]}      # the burst figure: the stricter of the two measured peaks
-        # ------------------------------------------------------------ decode at batch 1 and 64
+        result["prefill"] = bench.prefill_timed(PREFILL_LEN, min(args.warmup, 3), PREFILL_SAMPLES)
         points = {}
         for b_, steps in ((1, min(args.steps, 64)), (64, min(args.steps, 64))):
-            v, _, _, _ = decode_device(b_, steps, args.warmup, f"p{b_}_")
+            v, _, _, _ = bench.decode_device(b_, steps, args.warmup, f"p{b_}_", PROMPT_LEN)
             points[f"decode_b{b_}"] = round(v, 2)
         result["points"] = points
+    if args.breakdown:
+        result["breakdown"] = bench.breakdown(args.batch, PROMPT_LEN, PREFILL_LEN)
+    return result
+
+
+def run_14b_mixed(args) -> dict:
+    """32 requests, prompts of 128 to 3,072 tokens, portions of 512 mixed with decoding, 128
+    greedy tokens each, through Engine.generate: the scheduler and the mixed step, timed."""
+    import torch
+    from inferloop_b200.sampling import SamplingParams
+    cfg = dict(QWEN3_14B)
+    n_req, new, chunk, seed = 32, 128, 512, 3
+    pages = n_req * (-(-(3072 + new) // PAGE)) + 64
+    bench = Bench(cfg, seed, pages, n_req, 4096, chunk)
+    engine = bench.engine
+    lens = torch.randint(128, 3073, (n_req,), generator=bench.gen).tolist()
+
+    def job():
+        prompts = [bench.prompts(1, n)[0] for n in lens]
+        engine.step_log = []
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = engine.generate(prompts, SamplingParams(), new)
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - t0
+        log, engine.step_log = engine.step_log, None
+        engine.take_completed()
+        assert all(len(g) == new for g in out)
+        return seconds, log
+
+    job()                                           # untimed: records the decode graphs, sizes every buffer
+    before = engine.inspect()["scheduler"]
+    ahead_before = engine.steps_launched_ahead
+    with ClockSampler() as clocks:
+        seconds, log = job()
+    after = engine.inspect()["scheduler"]
+    nums, pk = bench.nums, bench.pk
+    roof_s = 0.0
+    for s in log:
+        t_flop = step_flops(nums, s["tokens"], s["logit_rows"], s["pairs"]) / (pk["bf16_tflops"] * 1e12)
+        t_byte = (bench.weight_bytes + s["keys"] * nums["kv_bytes_per_token"]) / (pk["hbm_gbs"] * 1e9)
+        roof_s += max(t_flop, t_byte)
+    steps = len(log)
+    mixed = sum(1 for s in log if 0 < s["single_token_seqs"] < s["seqs"])
+    decode_only = sum(1 for s in log if s["single_token_seqs"] == s["seqs"])
+    generated, prompt_tokens = n_req * new, sum(lens)
+    return {
+        "metric": "Qwen3-14B-sized bf16 mixed batch: generated tok/s through Engine.generate",
+        "value": round(generated / seconds, 2), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": 1,
+        "ms_per_step": round(1e3 * seconds / steps, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random-init weights (seed 3), prompt lengths uniform in [128, 3072], token ids uniform in [0, vocab)",
+        "config": flat_config("Qwen3-14B sizes", cfg, requests=n_req, prefill_chunk_tokens=chunk, max_new_tokens=new,
+                              seq_len=4096, prompt_tokens=prompt_tokens, peaks=pk["source"]),
+        "e2e": {"value": round(generated / seconds, 2), "unit": "tokens/s", "seconds": round(seconds, 4),
+                "all_tokens_per_s": round((generated + prompt_tokens) / seconds, 1)},
+        "composition": {"steps": steps, "mixed_steps": mixed, "decode_only_steps": decode_only,
+                        "prompt_only_steps": steps - mixed - decode_only,
+                        "mean_tokens_per_step": round(sum(s["tokens"] for s in log) / steps, 1),
+                        "mean_seqs_per_step": round(sum(s["seqs"] for s in log) / steps, 1),
+                        "preemptions": after["preemptions"] - before["preemptions"],
+                        "steps_launched_ahead": engine.steps_launched_ahead - ahead_before},
+        "roofline": {"bound": "per step: the slower of flops / bf16 peak and bytes / HBM", "seconds": round(roof_s, 4),
+                     "frac": round(roof_s / seconds, 4), "peak_tflops": pk["bf16_tflops"], "peak_gbs": pk["hbm_gbs"]},
+        "clocks": clocks.summary(),
+    }
+
+
+def run_32b_long(args) -> dict:
+    """Decode at batch 1 and 16 after 8,192-token prompts: long paged decode attention."""
+    cfg = dict(QWEN3_32B, num_hidden_layers=args.layers if args.layers != FULL_LAYERS else 64)
+    prompt_len, chunk, seed = 8192, 2048, 4
+    steps = min(args.steps, 64)
+    tokens_per_seq = prompt_len + args.warmup + steps + 64
+    pages = 16 * (-(-tokens_per_seq // PAGE)) + 256
+    bench = Bench(cfg, seed, pages, 16, 16384, chunk)
+    points, rooflines = {}, {}
+    with ClockSampler() as clocks:
+        for b_ in (16, 1):
+            v, ms, kernels, ctx = bench.decode_device(b_, steps, args.warmup, f"l{b_}_", prompt_len)
+            points[f"decode_b{b_}"] = {"value": round(v, 2), "ms_per_step": round(ms, 4), "kernels_per_step": kernels}
+            rooflines[f"decode_b{b_}"] = bench.decode_roofline(b_, ctx, ms)
+    result = {
+        "metric": "Qwen3-32B-sized bf16 decode tok/s after 8,192-token prompts", "value": points["decode_b16"]["value"],
+        "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
+        "ms_per_step": points["decode_b16"]["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random-init weights (seed 4), token ids uniform in [0, vocab)",
+        "config": flat_config("Qwen3-32B sizes", cfg, global_batch=16, seq_len=16384, prompt_len=prompt_len,
+                              layers_full=64, prefill_chunk_tokens=chunk, peaks=bench.pk["source"]),
+        "points": points, "roofline": rooflines["decode_b16"], "rooflines": rooflines, "clocks": clocks.summary(),
+    }
+    if not args.no_points:
+        result["prefill"] = bench.prefill_timed(prompt_len, 1, 3)
+    if args.breakdown:
+        result["breakdown"] = bench.breakdown(16, prompt_len, chunk)
+    return result
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="8b", choices=["8b", "14b-mixed", "32b-long"])
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers (named in config) to save time")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 / prefill side measurements")
+    ap.add_argument("--breakdown", action="store_true", help="add the per-op-class share of device time")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "pip: the reference checkout 'is not installable: neither setup.py nor pyproject.toml found' (a Rust workspace; no cargo/rustc "
+                          "on this machine; it has no Python API)"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    result = {"8b": run_8b, "14b-mixed": run_14b_mixed, "32b-long": run_32b_long}[args.config](args)
     print(json.dumps(result))
     return 0
 

@@ -8,7 +8,8 @@
 Options shared with the reference keep its names and meanings: --device,
 --block-size, --num-gpu-blocks-override, --max-num-batched-tokens, --max-model-len,
 --max-output-tokens, --max-num-seqs, --gpu-memory-utilization.  `--dtype` and
-`--random-weights` are this engine's own.  Serving over HTTP is not part of it.
+`--random-weights` are this engine's own; `--device-timing off|graph|node` is the reference's
+(crates/service/cli/src/arguments.rs:69-73).  Serving over HTTP is not part of it.
 
 The requests file is the reference's (examples/generate.json): one object or a list of
     {"id": 1, "model": 1, "input": {"Sequence": {"tokens": [..]}},
@@ -32,6 +33,8 @@ def _add_engine_options(p: argparse.ArgumentParser) -> None:
     p.add_argument("--max-output-tokens", type=int, default=None, metavar="TOKENS")
     p.add_argument("--max-num-seqs", type=int, default=64, metavar="SEQUENCES")
     p.add_argument("--gpu-memory-utilization", type=float, default=0.9)
+    p.add_argument("--device-timing", choices=["off", "graph", "node"], default="off",
+                   help="device time per step (graph) or per kernel and op class (node), reported under runtime")
     p.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     p.add_argument("--random-weights", type=int, default=None, metavar="SEED",
                    help="ignore model.safetensors; make weights from config.json and this seed")
@@ -82,7 +85,7 @@ def _engine(args, folder: str):
                   max_num_batched_tokens=args.max_num_batched_tokens, max_model_len=args.max_model_len,
                   max_output_tokens=args.max_output_tokens, max_num_seqs=args.max_num_seqs,
                   gpu_memory_utilization=args.gpu_memory_utilization,
-                  random_weights_seed=args.random_weights)
+                  random_weights_seed=args.random_weights, device_timing=args.device_timing)
 
 
 def _sampling(engine, d: Dict[str, Any]):

@@ -3,7 +3,9 @@
 // memory, operands brought by TMA straight from the cache pages.
 //
 // One CTA = one kv head and 128 rows, a row being a (token, query head of the group)
-// pair, so 128 / G tokens of one sequence; it walks that sequence's keys 128 at a time.
+// pair, so floor(128 / G) tokens of one sequence (a group size that does not divide 128
+// leaves the last 128 mod G rows unused: 3 of 128 for groups of 5); it walks that
+// sequence's keys 128 at a time.
 //   warp 0   one lane looks up the pages of the next 128 keys in the block table and issues
 //            the TMA loads: K and V each as one box per page and 64-wide slice of the head
 //            (128-byte swizzle; a page that is not held is requested outside the tensor, which
@@ -172,7 +174,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // warp's lanes issue them side by side, lanes 0-15 the K boxes and 16-31 the V boxes,
     // after lane 0 has seen the stage free and armed its barrier.
     if (lane == 0) {
-      mbar_expect_tx(q_full, kQBytes);
+      // the box is G heads x tokens_per_tile tokens: rows_used rows of 128 bytes per slice
+      mbar_expect_tx(q_full, (uint32_t)(kChunks * tokens_per_tile * G * 128));
 #pragma unroll
       for (int c = 0; c < kChunks; ++c) tma_load_3d(q_s + c * kSlice, &map_q, q_full, c * 64, kvh * G, tok0 + t_first);
     }
@@ -277,7 +280,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int row = quad * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     const int tl = t_first + row / G;
-    const bool live = tl < q_len;
+    const bool live = row < tokens_per_tile * G && tl < q_len;     // rows past the last whole token hold no query
     const int head = kvh * G + row % G;
     const int pos = live ? p.positions[tok0 + tl] : -1;
     const int lo = (live && p.window > 0 && pos + 1 > p.window) ? pos + 1 - p.window : 0;
@@ -435,11 +438,11 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
 ILB_EXPORT int ilb_attention_tc_supported(int nq, int nkv, int d, int page_size) {
   if (nkv <= 0 || nq % nkv != 0) return 0;
   const int g = nq / nkv;
-  return ((d == 64 || d == 128) && g <= 128 && 128 % g == 0 &&
+  return ((d == 64 || d == 128) && g <= 128 &&
           (page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128)) ? 1 : 0;
 }
 
-// n_tiles = sum over sequences of ceil(q_len / (128 / G)).
+// n_tiles = sum over sequences of ceil(q_len / floor(128 / G)).
 ILB_EXPORT int ilb_attention_prefill_tc(const void* q, void* out, const void* k_cache, const void* v_cache,
                                         const int* positions, const int* cu_q, const int* block_table,
                                         int max_blocks, int page_size, int num_pages, int window, float scale,
@@ -453,7 +456,7 @@ ILB_EXPORT int ilb_attention_prefill_tc(const void* q, void* out, const void* k_
               ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0), "attention (tensor cores): misaligned operands");
   const int G = nq / nkv;
   CUtensorMap mq, mk, mv, mkr, mvr;
-  {   // q as (d, heads, tokens); a box is 64 x G x 128/G = the 128 rows of a tile, one slice of the head
+  {   // q as (d, heads, tokens); a box is 64 x G x floor(128/G) = the rows of a tile, one slice of the head
     const cuuint64_t dims[3] = {(cuuint64_t)d, (cuuint64_t)nq, (cuuint64_t)n_tokens};
     const cuuint64_t strides[2] = {(cuuint64_t)d * 2, (cuuint64_t)q_stride * 2};
     const cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(kRows / G)};

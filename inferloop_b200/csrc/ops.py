@@ -55,6 +55,17 @@ LAUNCHES = 0          # kernels launched through this module since import
 _FUNCTIONS: dict = {}  # launcher name -> (function, its library)
 
 
+SCOPE = "other"       # the op class the next launches belong to (see `scope`)
+TIMER = None          # an engine.timing.DeviceTimer in "node" mode, or None
+
+
+def scope(name: str) -> None:
+    """Name the op class of the launches that follow (a part calls this before its kernels);
+    it costs one assignment and only the per-kernel device timer reads it."""
+    global SCOPE
+    SCOPE = name
+
+
 def _call(module: str, fn: str, *args) -> None:
     global LAUNCHES
     LAUNCHES += 1
@@ -64,9 +75,13 @@ def _call(module: str, fn: str, *args) -> None:
         f = getattr(lib, fn)
         f.restype = ctypes.c_int
         entry = _FUNCTIONS[fn] = (f, lib)
+    timer = TIMER
+    begin = timer.node_begin() if timer is not None else None
     rc = entry[0](*args)
     if rc != 0:
         raise KernelError(entry[1].ilb_last_error().decode())
+    if begin is not None:
+        timer.node_end(SCOPE, fn, begin)
 
 
 def _i(v) -> ctypes.c_int:
@@ -369,13 +384,13 @@ def attention_tc_supported(nq: int, nkv: int, d: int, page_size: int) -> bool:
     if nkv <= 0 or nq % nkv:
         return False
     g = nq // nkv
-    return d in (64, 128) and g <= 128 and 128 % g == 0 and page_size in (16, 32, 64, 128)
+    return d in (64, 128) and g <= 128 and page_size in (16, 32, 64, 128)
 
 
 def attention_prefill_tc(q, out, k_cache, v_cache, positions, cu_q, block_table, window, scale, n_seqs,
                          n_tiles, nq, nkv, d) -> None:
     """Prefill attention on tcgen05 tensor cores (attention_tc.cu); n_tiles counts tiles of
-    128 / (nq / nkv) tokens over the sequences."""
+    128 // (nq / nkv) tokens over the sequences."""
     for t, w in ((q, "q"), (out, "out"), (k_cache, "k cache"), (v_cache, "v cache")):
         _need(t, "attention " + w, torch.bfloat16)
     num_pages, _, page_size, _ = k_cache.shape

@@ -57,7 +57,7 @@ class Engine:
                  max_output_tokens: Optional[int] = None, max_num_seqs: int = 64,
                  gpu_memory_utilization: float = DEFAULT_GPU_MEMORY_UTILIZATION,
                  prefill_chunk_tokens: int = 512, random_weights_seed: Optional[int] = None,
-                 cuda_graphs: bool = True, runner=None) -> None:
+                 cuda_graphs: bool = True, device_timing: str = "off", runner=None) -> None:
         """`model`: a folder with config.json and safetensors, or a config mapping
         together with `random_weights_seed` (weights are then made on the device)."""
         self.block_size = int(block_size)
@@ -97,6 +97,8 @@ class Engine:
             max_num_seqs=max_num_seqs,
             max_num_batched_tokens=max_num_batched_tokens or max(prefill_chunk_tokens + max_num_seqs - 1, 1),
             prefill_chunk_tokens=prefill_chunk_tokens, max_model_len=self.max_model_len)
+        if device_timing != "off":
+            self.runner.set_device_timing(device_timing)      # off | graph | node (engine/timing.py)
         self.scheduler = Scheduler(self.runner.cache, cfg)
         self.sampler = DeviceSampler(self.runner.device) if getattr(self.runner, "device", None) is not None else None
         self.cuda_graphs = cuda_graphs
@@ -106,6 +108,7 @@ class Engine:
         self.steps_launched_ahead = 0
         self.lookahead = True                   # launch the next decode step before reading this one's ids
         self.max_finished_kept = 1024
+        self.step_log: Optional[List[dict]] = None   # set to a list to have every launched step described in it
         self.requests: Dict[Hashable, Request] = {}
 
     # ------------------------------------------------------------------ sizing
@@ -223,6 +226,8 @@ class Engine:
         plan = self.scheduler.plan()
         if not plan.work:
             return None
+        if self.step_log is not None:
+            self.step_log.append(self._describe(plan.work, len(plan.preempted)))
         entries = [StepEntry(w.request.id, w.tokens, [w.count - 1] if w.samples else []) for w in plan.work]
         sampling_work = [w for w in plan.work if w.samples]
         if (self.sampler is not None and sampling_work
@@ -258,7 +263,19 @@ class Engine:
         s.count_step()
         self.steps_launched_ahead += 1
         nxt = [PlannedWork(w.request, w.start + 1, 1, True) for w in work]
+        if self.step_log is not None:
+            self.step_log.append(self._describe(nxt, 0))
         return _Flight(StepPlan(nxt, []), nxt, drawn, None)
+
+    @staticmethod
+    def _describe(work, preempted: int) -> dict:
+        """What a step holds, for measurements: tokens, sequences, how many of them bring one
+        token, keys in the cache after it, (query, key) pairs its attention covers, logits rows."""
+        return {"tokens": sum(w.count for w in work), "seqs": len(work),
+                "single_token_seqs": sum(1 for w in work if w.count == 1),
+                "keys": sum(w.start + w.count for w in work),
+                "pairs": sum(w.count * w.start + w.count * (w.count + 1) // 2 for w in work),
+                "logit_rows": sum(1 for w in work if w.samples), "preempted": preempted}
 
     def _sample(self, logits: torch.Tensor, work) -> Dict[Hashable, int]:
         """Row i of `logits` belongs to work[i].  Every row is drawn on the device: the
@@ -363,4 +380,6 @@ class Engine:
             "max_model_len": self.max_model_len,
             "max_num_seqs": s.config.max_num_seqs,
             "max_num_batched_tokens": s.config.max_num_batched_tokens,
+            **({"device_timing": self.runner.timer.summary()}
+               if getattr(getattr(self.runner, "timer", None), "mode", "off") != "off" else {}),
         }

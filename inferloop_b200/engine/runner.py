@@ -29,6 +29,7 @@ from ..parts.base import BuildContext, Workspace
 from ..weights.loader import load_weights
 from ..weights.random_init import random_weights
 from .batch import Drawn, StepContext, StepEntry, StepStager
+from .timing import DeviceTimer
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
           "f32": torch.float32, "fp32": torch.float32}
@@ -196,6 +197,7 @@ class ModelRunner:
         self.steps_run = 0
         self.tokens_run = 0
         self.kernels_last_step = 0
+        self.timer = DeviceTimer(device, "off")
         # Decode-only steps replay recorded graphs when every part reads its batch from
         # device memory (a part that loops over host-side batch facts cannot be replayed).
         self.graphs = None
@@ -247,6 +249,16 @@ class ModelRunner:
             from .graphs import DecodeGraphs
             self.graphs = DecodeGraphs(self, -(-self.spec.max_positions // page_size))
 
+    def set_device_timing(self, mode: str) -> None:
+        """"off", "graph" (two events around every step) or "node" (two events around every
+        kernel, steps run kernel by kernel): see engine/timing.py."""
+        from ..csrc import ops
+        self.timer = DeviceTimer(self.device, mode)
+        ops.TIMER = self.timer if mode == "node" else None
+
+    def _graphs_usable(self) -> bool:
+        return self.graphs is not None and self.timer.mode != "node"
+
     # ------------------------------------------------------------------ requests
     def begin(self, request: Hashable) -> None:
         self.cache.begin(request)
@@ -265,11 +277,13 @@ class ModelRunner:
         """Launch the decode step after one that is still running (see
         `DecodeGraphs.step_ahead`); the entries' tokens are placeholders.  Returns the device
         ids it will draw (still on the device), or None if it was not launched."""
-        if self.graphs is None or not self.graphs.eligible(entries):
+        if not self._graphs_usable() or not self.graphs.eligible(entries):
             return None
+        self.timer.step_begin()
         drawn = self.graphs.step_ahead(entries, previous_drawn)
         if drawn is None:
             return None
+        self.timer.step_end(len(entries))
         n = len(entries)
         req = (ctypes.c_longlong * n)(*[self.cache.id_of(e.request) for e in entries])
         ones = (ctypes.c_int * n)(*([1] * n))
@@ -295,7 +309,8 @@ class ModelRunner:
         from ..csrc import ops
         before = ops.LAUNCHES
         drawn = None
-        if self.graphs is not None and self.graphs.eligible(entries) and len(entries) <= 256:
+        self.timer.step_begin()
+        if self._graphs_usable() and self.graphs.eligible(entries) and len(entries) <= 256:
             logits, drawn, kernels = self.graphs.step(entries, with_argmax=draw_greedy)
             self.kernels_last_step = kernels
             n_tokens = len(entries)
@@ -306,9 +321,12 @@ class ModelRunner:
             if draw_greedy and logits.shape[0]:
                 rows = logits.shape[0]
                 pair = self.ctx.workspace.buffer("runner.drawn", (2, rows), torch.int32)
+                ops.scope("sampling")
                 ops.argmax(logits, pair[0], pair[1])
+                ops.scope("other")
                 drawn = Drawn(pair, rows)
             self.kernels_last_step = ops.LAUNCHES - before
+        self.timer.step_end(n_tokens)
         n = len(entries)
         req = (ctypes.c_longlong * n)(*[self.cache.id_of(e.request) for e in entries])
         n_tok = (ctypes.c_int * n)(*[len(e.tokens) for e in entries])

@@ -86,9 +86,11 @@ class DecoderModel:
         s, ws = self.spec, self.ctx.workspace
         T = step.n_tokens
         hidden = ws.buffer("model.hidden", (T, s.hidden_size), torch.float32)
+        ops.scope("embedding")
         ops.embed(step.tokens, self.embedding, hidden)
         for entry in s.run_order:
             self.blocks[entry.layer].forward(hidden, step, caches.layer_cache(entry))
+        ops.scope("head.rows_norm")
         R = step.n_logit_rows
         if R == 0:
             return ws.buffer("model.logits", (0, s.vocab_size), torch.float32)
@@ -97,7 +99,9 @@ class DecoderModel:
         normed = ws.buffer("model.rows_normed", (R, s.hidden_size), self.ctx.dtype)
         self.final_norm.forward(rows, normed)
         logits = ws.buffer("model.logits", (R, s.vocab_size), torch.float32)
+        ops.scope("head.output_matrix")
         linear(normed, self.head, logits)
+        ops.scope("other")
         return logits
 
 

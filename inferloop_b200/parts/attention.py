@@ -94,29 +94,36 @@ class GQAttention(Mixer):
         ws, dt = self.ctx.workspace, self.ctx.dtype
         width = (self.nq + 2 * self.nkv) * self.d
         qkv = ws.buffer("attn.qkv", (T, width), dt)
+        ops.scope("attention.qkv_projection")
         linear(x, self.w_qkv, qkv, self.b_qkv)
         table = step.block_tables[cache.group]
+        ops.scope("attention.position_table")
         rope = self.position.table(step)
         if (step.decode_only and cache.k is not None and ops.attention_decode_fused_supported(
                 dt, cache.k.dtype, self.nq, self.nkv, self.d, cache.page_size, self.rotary_dim, rope is not None)):
             # one token per sequence: norm, rotation and the cache write of the new key and
             # value happen inside the attention kernel
             o = ws.buffer("attn.o", (T, self.nq * self.d), dt)
+            ops.scope("attention.decode (q/k norm, rotation, cache write inside)")
             ops.attention_decode_fused(qkv, o, self.q_norm, self.k_norm, self.qk_norm_eps, rope, cache.k, cache.v,
                                        cache.writable, step.positions, step.cu_q, table, self.window or 0, self.scale,
                                        step.n_seqs, self.nq, self.nkv, self.d,
                                        long_context=step.max_kv_len >= ops.DECODE_LONG_CONTEXT)
+            ops.scope("attention.o_projection")
             linear(o, self.w_o, residual, self.b_o, accumulate=True)
             return
         q = ws.buffer("attn.q", (T, self.nq * self.d), dt)
+        ops.scope("attention.qk_norm_rotation_cache_write")
         ops.qk_norm_rope_cache(
             qkv, q, self.q_norm, self.k_norm, self.qk_norm_eps, rope,
             self.rotary_dim, step.positions, step.seq_of_token, table, cache.page_size,
             cache.k if cache.writable else None, cache.v if cache.writable else None,
             self.nq, self.nkv, self.d)
         o = ws.buffer("attn.o", (T, self.nq * self.d), dt)
+        ops.scope("attention.attention")
         ops.attention(q, o, cache.k, cache.v, step, table, self.window or 0, self.scale,
                       self.nq, self.nkv, self.d, workspace=ws, decode_chunk=self.decode_chunk)
+        ops.scope("attention.o_projection")
         linear(o, self.w_o, residual, self.b_o, accumulate=True)
 
 

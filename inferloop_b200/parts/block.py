@@ -6,6 +6,7 @@ from typing import List, Mapping
 
 import torch
 
+from ..csrc import ops
 from ..weights.decl import WeightDecl
 from . import registry
 from .base import Block, CacheNeeds
@@ -48,9 +49,13 @@ class PreNormBlock(Block):
     def forward(self, hidden: torch.Tensor, step, cache) -> None:
         ws = self.ctx.workspace
         normed = ws.buffer("block.normed", hidden.shape, self.ctx.dtype)
+        ops.scope("norm")
         self.norm1.forward(hidden, normed)
+        ops.scope("mixer")
         self.mixer.forward(normed, hidden, step, cache)
+        ops.scope("norm")
         self.norm2.forward(hidden, normed)
+        ops.scope("feed_forward")
         self.ffn.forward(normed, hidden, step)
 
 

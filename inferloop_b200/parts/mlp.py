@@ -62,6 +62,7 @@ class SwiGLU(FeedForward):
         T = x.shape[0]
         ws, dt = self.ctx.workspace, self.ctx.dtype
         act = ws.buffer("mlp.act", (T, self.inter), dt)
+        ops.scope("feed_forward.gate_up (SwiGLU inside)" if self.fused else "feed_forward.gate_up")
         if self.fused and ops.gemm_tc_eligible(x, self.w_gate_up, act):
             ops.gemm_tc(x, self.w_gate_up, act, swiglu=True)
         elif self.fused:
@@ -69,7 +70,9 @@ class SwiGLU(FeedForward):
         else:
             gate_up = ws.buffer("mlp.gate_up", (T, 2 * self.inter), dt)
             linear(x, self.w_gate_up, gate_up)
+            ops.scope("feed_forward.swiglu")
             ops.silu_mul(gate_up, act)
+        ops.scope("feed_forward.down")
         linear(act, self.w_down, residual, accumulate=True)
 
 

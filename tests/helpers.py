@@ -53,8 +53,25 @@ CONFIG_D = dict(
     tie_word_embeddings=False, max_position_embeddings=2048, hidden_act="silu")
 SEED_D, PAGE_D = 7, 16
 
+# Small E: D's geometry with a window of 40 on every second layer, so that block tables whose
+# leading entries were given back (-1) reach the serving kernels (tcgen05 prefill attention,
+# TMA decode attention with its fused input stage) through the real ledger.
+CONFIG_E = dict(CONFIG_D, num_hidden_layers=3, layer_types=["full_attention", "sliding_attention", "sliding_attention"],
+                sliding_window=40, vocab_size=600, rms_norm_eps=2e-6)
+SEED_E, PAGE_E = 8, 16
+
+# Small F: groups of five query heads per kv head at head size 128 (the geometry of the
+# 14B-sized serving configuration): five does not divide the 128 rows of an attention tile.
+CONFIG_F = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=320,
+    num_attention_heads=10, num_key_value_heads=2, head_dim=128, intermediate_size=448,
+    vocab_size=777, rope_theta=500000.0, rms_norm_eps=1e-5, attention_bias=False,
+    tie_word_embeddings=True, max_position_embeddings=1024, hidden_act="silu")
+SEED_F, PAGE_F = 9, 16
+
 CONFIGS = {"A": (CONFIG_A, SEED_A, PAGE_A), "B": (CONFIG_B, SEED_B, PAGE_B),
-           "C": (CONFIG_C, SEED_C, PAGE_C), "D": (CONFIG_D, SEED_D, PAGE_D)}
+           "C": (CONFIG_C, SEED_C, PAGE_C), "D": (CONFIG_D, SEED_D, PAGE_D),
+           "E": (CONFIG_E, SEED_E, PAGE_E), "F": (CONFIG_F, SEED_F, PAGE_F)}
 
 # |x - ref| <= atol + rtol * |ref| per element, the reference's own rule and defaults
 # (crates/diagnostics/quality/src/verification.rs:22-67; crates/service/cli/src/constants.rs:19-22).

@@ -14,8 +14,10 @@ def test_option_names_follow_the_reference():
     args = build_parser().parse_args([
         "run", "--package", "m", "--requests", "r.json", "--device", "0", "--block-size", "8",
         "--num-gpu-blocks-override", "32", "--max-num-batched-tokens", "64", "--max-model-len", "128",
-        "--max-output-tokens", "16", "--max-num-seqs", "4", "--gpu-memory-utilization", "0.5"])
+        "--max-output-tokens", "16", "--max-num-seqs", "4", "--gpu-memory-utilization", "0.5",
+        "--device-timing", "node"])
     assert (args.block_size, args.num_gpu_blocks_override, args.max_num_seqs) == (8, 32, 4)
+    assert args.device_timing == "node"            # crates/service/cli/src/arguments.rs:69-73
     g = build_parser().parse_args(["generate", "m", "--tokens", "1,2,3", "--temperature", "0.7", "--seed", "4"])
     assert g.model_path == "m" and g.temperature == 0.7
     with pytest.raises(SystemExit):
@@ -43,9 +45,15 @@ def test_run_requests_file(tmp_path):
         json.dump(reqs, fh)
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "infer"), "run", "--package", d,
                           "--requests", str(tmp_path / "r.json"), "--dtype", "float32", "--block-size", str(page),
-                          "--num-gpu-blocks-override", "32"], capture_output=True, text=True, timeout=600)
+                          "--num-gpu-blocks-override", "32", "--device-timing", "node"],
+                         capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stderr
     res = json.loads(out.stdout.strip().splitlines()[-1])
+    timing = res["runtime"]["device_timing"]
+    assert timing["mode"] == "node" and timing["steps"]["count"] == res["runtime"]["steps"]
+    assert {"embedding", "norm", "attention.qkv_projection", "attention.attention", "attention.o_projection",
+            "feed_forward.down", "head.output_matrix", "sampling"} <= set(timing["ops"])
+    assert abs(sum(o["share"] for o in timing["ops"].values()) - 1.0) < 1e-2
     model = plain.PlainModel(d)
     for r, p in zip(res["results"], prompts):
         assert r["output"]["Tokens"] == plain.generate(model, p, 6) and r["reason"] == "Length"

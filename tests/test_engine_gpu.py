@@ -16,7 +16,7 @@ from helpers import (BF16_REL_OF_MAX, CONFIGS, Trace, assert_close, check_trace,
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [1, 7, 16, 33, 90, 120], "B": [3, 12, 31, 64, 100, 150], "C": [5, 40, 77, 130, 200, 64],
-           "D": [5, 64, 130, 300, 520, 33]}
+           "D": [5, 64, 130, 300, 520, 33], "E": [5, 64, 130, 300, 520, 33], "F": [5, 64, 130, 300, 520, 33]}
 DTYPES = ["float32", "bfloat16"]
 
 
@@ -62,7 +62,7 @@ def runner_for(folders, name, dtype, num_pages=256):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_each_request_alone_and_whole(folders, requests_of, name, dtype):
     trace = Trace()
     for rid, toks in requests_of[name].items():
@@ -74,7 +74,7 @@ def test_each_request_alone_and_whole(folders, requests_of, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_most_in_one_step_then_the_last_32_one_by_one(folders, requests_of, name, dtype):
     trace = Trace()
     for rid, toks in requests_of[name].items():
@@ -89,7 +89,7 @@ def test_most_in_one_step_then_the_last_32_one_by_one(folders, requests_of, name
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_portions_of_changing_size(folders, requests_of, name, dtype):
     sizes = [7, 2, 13, 3, 2, 21, 5, 2, 9, 1, 17]
     trace = Trace()
@@ -142,7 +142,7 @@ def mixed_trace(reqs, seed=0, tail=12):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_mixed_batches_on_few_pages(folders, requests_of, name, dtype):
     from inferloop_b200.engine import ModelRunner
     reqs = requests_of[name]
@@ -230,7 +230,7 @@ def test_the_first_tokens_of_a_sequence(folders, requests_of, name, dtype):
     check_trace(run_trace_inprocess(r, trace), trace, {"r3": ref}, dtype, f"{name} first tokens")
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_float32_logits_do_not_depend_on_the_cut_at_all(folders, requests_of, name):
     """On the 32-bit path the order of every sum is fixed per position, so two ways of
     cutting give the same bits."""

@@ -413,9 +413,11 @@ class _Step:
 
 
 def run_flash(q, seqs, lens, q_lens, nq, nkv, d, page_size, window, chunk=256, seed=0, cluster=True,
-              page_order="shuffled"):
+              page_order="shuffled", release_passed_pages=False):
     """`cluster`: split-KV decode merges inside a thread-block cluster (the default of the
-    dispatcher) or through scratch records and tickets."""
+    dispatcher) or through scratch records and tickets.  `release_passed_pages`: pages that
+    lie wholly below the window of the step's first token are taken out of the block table
+    (-1) and overwritten, as the cache manager does once a window has passed them."""
     from inferloop_b200.parts import Workspace
     o = ops()
     n_pages = sum(-(-n // page_size) for n in lens) + 3
@@ -427,6 +429,13 @@ def run_flash(q, seqs, lens, q_lens, nq, nkv, d, page_size, window, chunk=256, s
         seq_of += [s] * ql
         cu.append(cu[-1] + ql)
     step = _Step(positions, seq_of, cu, q_lens)
+    if release_passed_pages:
+        assert window > 0
+        for s, (n, ql) in enumerate(zip(lens, q_lens)):
+            for b in range(max(0, (n - ql) + 1 - window) // page_size):
+                k_cache[table[s, b]] = float("nan")          # whoever follows the entry reads poison
+                v_cache[table[s, b]] = float("nan")
+                table[s, b] = -1
     out = torch.full((len(positions), nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
     ws = Workspace(torch.device("cuda:0"))
     was = o.DECODE_CLUSTER_ENABLED
@@ -594,10 +603,12 @@ def test_gemm_tcgen05_swiglu_epilogue(M, I, K, max_ctas, out_dtype):
 # ------------------------------------------------------------------ tcgen05 prefill attention
 @pytest.mark.parametrize("nq,nkv,d,page_size,window", [(32, 8, 128, 16, 0), (8, 1, 128, 16, 0), (4, 2, 64, 32, 0),
                                                          (16, 16, 64, 16, 0), (32, 8, 128, 64, 100), (2, 2, 128, 128, 0),
-                                                         (64, 2, 64, 16, 300)])
+                                                         (64, 2, 64, 16, 300), (10, 2, 128, 16, 0), (40, 8, 128, 16, 0),
+                                                         (6, 2, 64, 32, 0), (7, 1, 128, 16, 90), (9, 1, 64, 16, 0)])
 def test_tc_prefill_mixed_batch(nq, nkv, d, page_size, window):
     """Whole prompts, a portion that starts mid-sequence, single tokens, a long prompt whose
-    row tiles cross many key tiles; pages shuffled."""
+    row tiles cross many key tiles; pages shuffled.  Groups of 5, 3, 7 and 9 heads do not
+    divide the 128 rows of a tile: its last rows then hold no query."""
     o = ops()
     assert o.attention_tc_supported(nq, nkv, d, page_size)
     torch.manual_seed(nq * 3 + d)
@@ -632,6 +643,24 @@ def test_tc_prefill_and_decode_with_pages_in_runs(nq, nkv, d, page_size, window,
         ref = torch.stack([ref_attention(q[t].double().view(nq, d), *seqs[seq_of[t]], positions[t], window).reshape(-1)
                            for t in range(len(positions))])
         close_flash(out, ref, max(float(v.abs().max()) for _, v in seqs), f"pages {page_order}")
+
+
+@pytest.mark.parametrize("cluster", [True, False])
+@pytest.mark.parametrize("nq,nkv,d,page_size,window", [(8, 2, 128, 16, 40), (4, 2, 64, 32, 100), (10, 2, 128, 16, 70)])
+def test_attention_never_follows_a_released_page(nq, nkv, d, page_size, window, cluster):
+    """Block-table rows whose leading entries are -1 (pages a window has passed, given back
+    and poisoned here) through the tcgen05 prefill kernel, the TMA decode kernel and the
+    ticketed decode kernel."""
+    torch.manual_seed(nq + d + window)
+    for lens, q_lens in (([300, 1000, 129, 40], [30, 260, 2, 40]), ([513, 77, 1024, 130], [1, 1, 1, 1])):
+        seqs = [(torch.randn(n, nkv, d).to(torch.bfloat16).double(), torch.randn(n, nkv, d).to(torch.bfloat16).double()) for n in lens]
+        q = torch.randn(sum(q_lens), nq * d).to(torch.bfloat16)
+        out, positions, seq_of = run_flash(q, seqs, lens, q_lens, nq, nkv, d, page_size, window, cluster=cluster,
+                                           release_passed_pages=True)
+        ops().check_device_errors()
+        ref = torch.stack([ref_attention(q[t].double().view(nq, d), *seqs[seq_of[t]], positions[t], window).reshape(-1)
+                           for t in range(len(positions))])
+        close_flash(out, ref, max(float(v.abs().max()) for _, v in seqs), f"released pages, lens {lens}")
 
 
 def test_tc_prefill_finds_one_far_key_and_respects_the_window_edge():
