@@ -10,17 +10,20 @@
 //            the TMA loads: K and V each as one box per page and 64-wide slice of the head
 //            (128-byte swizzle; a page that is not held is requested outside the tensor, which
 //            TMA fills with zeros); Q once.
-//   warp 1   allocates tensor memory (S: 128 columns, O: head-size columns); one lane issues
-//            S = Q K^T for tile j+1 as soon as the softmax warps have read S of tile j, then
-//            O += P V for tile j when P is in shared memory.  V is used as it lies in the
-//            cache ([key][d], the "MN-major" operand form), no transpose.
+//   warp 1   allocates tensor memory (two S tiles of 128 columns and O of head-size columns);
+//            one lane issues S = Q K^T two tiles ahead (tile j+2 goes to the S tile that held
+//            tile j, right behind O += P V of tile j: the tensor core runs its operations in the
+//            order they were issued), so the tensor core works on tile j+1 and j+2 while the
+//            softmax warps are on tile j+1.  P is the MMA's A operand straight from tensor
+//            memory; V is used as it lies in the cache ([key][d], the "MN-major" operand
+//            form), no transpose.
 //   warps 2-9  two threads per row (row = tensor-memory lane, each thread half of the tile's
 //            keys): read S into registers, exchange the row maximum through shared memory,
-//            keep the running maximum and sum in 32-bit, write P as bfloat16
-//            into the swizzled operand tile, and rescales O in tensor memory only when the
-//            maximum has grown by more than 2^8 (any fixed reference maximum gives the same
-//            quotient; the threshold only bounds the magnitudes).  At the end it divides O by
-//            the sum and writes the row.
+//            keep the running maximum and sum in 32-bit, write P as packed bfloat16 back into
+//            the tensor-memory columns S came from (tcgen05.st), and rescale O in tensor
+//            memory only when the maximum has grown by more than 2^8 (any fixed reference
+//            maximum gives the same quotient; the threshold only bounds the magnitudes).  At
+//            the end it divides O by the sum and writes the row.
 // Every mbarrier wait is bounded; on expiry a flag is raised, the CTA drains and frees its
 // tensor memory.  No cluster, no multicast.
 //
@@ -43,7 +46,7 @@ namespace {
 constexpr int kRows = 128;             // rows of a CTA = MMA M
 constexpr int kKeys = 128;             // keys per tile = MMA N of S, K extent of P V
 constexpr int kThreads = 320;           // TMA warp, MMA warp, 8 softmax warps (two threads per row)
-constexpr int kStages = 2;
+constexpr int kStagesK = 3;           // K tiles in flight: S is issued two tiles ahead
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleStep = 8.0f;   // log2 units
 
@@ -81,6 +84,29 @@ __device__ __forceinline__ void tmem_store_32(uint32_t addr, const float (&v)[32
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_store_32u(uint32_t addr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(addr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+        "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+        "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// D (tensor memory) (+)= A (tensor memory: row = lane, two bfloat16 of consecutive K per 32-bit
+// column) * B (shared memory descriptor).
+__device__ __forceinline__ void mma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+
 // 2^x by the special-function unit (2 ulp; the result is rounded to bfloat16 anyway).
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -106,23 +132,24 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   constexpr uint32_t kQBytes = kChunks * kSlice;
   constexpr uint32_t kKBytes = kChunks * kSlice;        // [slice][128 keys][64]
   constexpr uint32_t kVBytes = kChunks * kSlice;        // [slice of d][128 keys][64]
-  constexpr uint32_t kPBytes = 2 * kSlice;              // [slice of keys][128 rows][64]
-  constexpr uint32_t kTmemCols = 256;                   // S: 128, O: D (<= 128)
+  constexpr int kStagesV = D == 128 ? 2 : 3;            // V tiles in flight (what shared memory holds beside Q and three K tiles)
+  constexpr uint32_t kTmemCols = 512;                   // two S tiles of 128 columns, then O: D (<= 128)
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();                      // q, the cache and the step's arrays come from earlier work in the stream
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t q_s = base, k_s = q_s + kQBytes, v_s = k_s + kStages * kKBytes, p_s = v_s + kStages * kVBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (p_s - base) + kPBytes);
+  const uint32_t q_s = base, k_s = q_s + kQBytes, v_s = k_s + kStagesK * kKBytes, end_s = v_s + kStagesV * kVBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (end_s - base));
   const uint32_t bar0 = smem_u32(bars);
-  const uint32_t q_full = bar0, k_full = bar0 + 8, k_empty = k_full + 8 * kStages, v_full = k_empty + 8 * kStages,
-                 v_empty = v_full + 8 * kStages, s_full = v_empty + 8 * kStages, s_free = s_full + 8,
-                 p_full = s_free + 8, o_done = p_full + 8;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 5 + 4 * kStages);
-  volatile int* failed = reinterpret_cast<volatile int*>(bars + 6 + 4 * kStages);
-  float* xmax = reinterpret_cast<float*>(bars + 8 + 4 * kStages);      // [2][2][128] row maxima, then [2][128] row sums
+  // s_full[b], p_full[b]: the S tile b = j & 1 holds the scores of tile j / holds its probabilities
+  const uint32_t q_full = bar0, k_full = bar0 + 8, k_empty = k_full + 8 * kStagesK, v_full = k_empty + 8 * kStagesK,
+                 v_empty = v_full + 8 * kStagesV, s_full = v_empty + 8 * kStagesV, p_full = s_full + 16, o_done = p_full + 16;
+  constexpr int kBars = 1 + 2 * kStagesK + 2 * kStagesV + 5;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + kBars);
+  volatile int* failed = reinterpret_cast<volatile int*>(bars + kBars + 1);
+  float* xmax = reinterpret_cast<float*>(bars + kBars + 2);      // [2][2][128] row maxima, then [2][128] row sums
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = p.nq / p.nkv;
@@ -150,11 +177,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(k_full + 8 * s, 1); mbar_init(k_empty + 8 * s, 1);
-      mbar_init(v_full + 8 * s, 1); mbar_init(v_empty + 8 * s, 1);
-    }
-    mbar_init(s_full, 1); mbar_init(s_free, 256); mbar_init(p_full, 256); mbar_init(o_done, 1);
+    for (int s = 0; s < kStagesK; ++s) { mbar_init(k_full + 8 * s, 1); mbar_init(k_empty + 8 * s, 1); }
+    for (int s = 0; s < kStagesV; ++s) { mbar_init(v_full + 8 * s, 1); mbar_init(v_empty + 8 * s, 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(s_full + 8 * b, 1); mbar_init(p_full + 8 * b, 256); }
+    mbar_init(o_done, 1);
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -166,7 +192,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + kKeys;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * kKeys;       // S tile b at tmem_s + 128 b
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -195,11 +221,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     };
     int page_next = lookup(0);
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int s = j % kStages;
+      const int s = j % kStagesK, sv = j % kStagesV;
       const int page = page_next;
       page_next = lookup(j + 1);                          // in flight while this tile's boxes are issued
       if (lane == 0) {
-        if (j >= kStages) ok = mbar_wait(k_empty + 8 * s, ((j / kStages) - 1) & 1);
+        if (j >= kStagesK) ok = mbar_wait(k_empty + 8 * s, ((j / kStagesK) - 1) & 1);
         if (ok) mbar_expect_tx(k_full + 8 * s, kKBytes);
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -217,16 +243,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         tma_load_4d(k_s + s * kKBytes + box_slice * kSlice + box_page * p.page_size * 128, &map_k, k_full + 8 * s,
                     box_slice * 64, 0, kvh, page);
       if (lane == 0) {
-        if (j >= kStages) ok = mbar_wait(v_empty + 8 * s, ((j / kStages) - 1) & 1);
-        if (ok) mbar_expect_tx(v_full + 8 * s, kVBytes);
+        if (j >= kStagesV) ok = mbar_wait(v_empty + 8 * sv, ((j / kStagesV) - 1) & 1);
+        if (ok) mbar_expect_tx(v_full + 8 * sv, kVBytes);
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       if (run) {
         if (lane >= 16 && lane < 16 + kChunks)
-          tma_load_4d(v_s + s * kVBytes + (lane - 16) * kSlice, &map_v_run, v_full + 8 * s, (lane - 16) * 64, 0, kvh, first_page);
+          tma_load_4d(v_s + sv * kVBytes + (lane - 16) * kSlice, &map_v_run, v_full + 8 * sv, (lane - 16) * 64, 0, kvh, first_page);
       } else if (has_box && lane >= 16)
-        tma_load_4d(v_s + s * kVBytes + box_slice * kSlice + box_page * p.page_size * 128, &map_v, v_full + 8 * s,
+        tma_load_4d(v_s + sv * kVBytes + box_slice * kSlice + box_page * p.page_size * 128, &map_v, v_full + 8 * sv,
                     box_slice * 64, 0, kvh, page);
     }
     if (!ok && lane == 0) { *failed = 1; if (p.error_flag) *p.error_flag = 1; }
@@ -236,39 +262,44 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       constexpr uint32_t idesc_s = instr_desc(kRows, kKeys, 0);
       constexpr uint32_t idesc_o = instr_desc(kRows, D, 1);
       bool ok = mbar_wait(q_full, 0);
-      auto issue_s = [&](int j) {          // S = Q K_j^T
-        const int s = j % kStages;
-        ok = ok && mbar_wait(k_full + 8 * s, (j / kStages) & 1);
-        if (j > 0) ok = ok && mbar_wait(s_free, (j - 1) & 1);
+      auto issue_s = [&](int j) {          // S tile (j & 1) = Q K_j^T
+        const int s = j % kStagesK;
+        ok = ok && mbar_wait(k_full + 8 * s, (j / kStagesK) & 1);
         if (!ok) return;
         tcgen05_fence_after();
+        const uint32_t acc = tmem_s + (uint32_t)(j & 1) * kKeys;
 #pragma unroll
         for (int c = 0; c < kChunks; ++c)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            mma_bf16(tmem_s, desc_k_major(q_s + c * kSlice) + 2 * k, desc_k_major(k_s + s * kKBytes + c * kSlice) + 2 * k,
+            mma_bf16(acc, desc_k_major(q_s + c * kSlice) + 2 * k, desc_k_major(k_s + s * kKBytes + c * kSlice) + 2 * k,
                      idesc_s, (c > 0 || k > 0) ? 1u : 0u);
         tcgen05_commit(k_empty + 8 * s);
-        tcgen05_commit(s_full);
+        tcgen05_commit(s_full + 8 * (j & 1));
       };
+      // Two S tiles: the scores of tile j + 2 are issued right behind O += P_j V_j, into the
+      // tile that P_j is read from.  The tensor core executes what one thread issues in the
+      // order of issue, so the product has read P_j before the new scores overwrite it; and
+      // P_j was only written after the softmax warps had read the scores of tile j.
       if (ok) issue_s(0);
+      if (ok && n_tiles > 1) issue_s(1);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles) issue_s(j + 1);
-        const int s = j % kStages;
-        ok = ok && mbar_wait(p_full, j & 1);
-        ok = ok && mbar_wait(v_full + 8 * s, (j / kStages) & 1);
+        const int sv = j % kStagesV, b = j & 1;
+        ok = ok && mbar_wait(p_full + 8 * b, (j >> 1) & 1);
+        ok = ok && mbar_wait(v_full + 8 * sv, (j / kStagesV) & 1);
         if (!ok) break;
         tcgen05_fence_after();
+        const uint32_t p_t = tmem_s + (uint32_t)b * kKeys;     // P_j: 64 columns, two bfloat16 of consecutive keys each
 #pragma unroll
-        for (int k = 0; k < kKeys / 16; ++k)   // 16 keys a step: 32 bytes along P's rows, two 8-key groups of V
-          mma_bf16(tmem_o, desc_k_major(p_s + (k / 4) * kSlice) + 2 * (k % 4),
-                   desc_mn_major(v_s + s * kVBytes + k * 2048, kSlice), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
-        tcgen05_commit(v_empty + 8 * s);
+        for (int k = 0; k < kKeys / 16; ++k)   // 16 keys a step: 8 columns of P, two 8-key groups of V
+          mma_bf16_ts(tmem_o, p_t + 8 * k, desc_mn_major(v_s + sv * kVBytes + k * 2048, kSlice), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+        tcgen05_commit(v_empty + 8 * sv);
         tcgen05_commit(o_done);
+        if (j + 2 < n_tiles) issue_s(j + 2);
       }
       if (!ok) {
         *failed = 1; if (p.error_flag) *p.error_flag = 1;
-        tcgen05_commit(s_full); tcgen05_commit(o_done);       // let the softmax warps leave their waits
+        tcgen05_commit(s_full); tcgen05_commit(s_full + 8); tcgen05_commit(o_done);       // let the softmax warps leave their waits
       }
     }
   } else {
@@ -289,21 +320,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int key0 = (first_tile + j) * kKeys + half * 64;
+      const uint32_t s_t = tmem_s + (uint32_t)(j & 1) * kKeys + lane_addr;     // this row of the S tile of tile j
       // `ok` only ever changes through waits that all 256 threads share, so they leave the
       // loop together and nobody is left alone at the named barrier below
-      if (!mbar_wait(s_full, j & 1)) ok = false;
+      if (!mbar_wait(s_full + 8 * (j & 1), (j >> 1) & 1)) ok = false;
       tcgen05_fence_after();
       if (!ok) break;
       float v[64];
       {
         float a[32], b2[32];
-        tmem_load_32(tmem_s + lane_addr + half * 64, a);
-        tmem_load_32(tmem_s + lane_addr + half * 64 + 32, b2);
+        tmem_load_32(s_t + half * 64, a);
+        tmem_load_32(s_t + half * 64 + 32, b2);
 #pragma unroll
         for (int c = 0; c < 32; ++c) { v[c] = a[c]; v[32 + c] = b2[c]; }
       }
-      tcgen05_fence_before();
-      mbar_arrive(s_free);                             // S is in registers: the next Q K^T may overwrite it
       // raw scores stay in v (the scale is positive and folds into the exponent's multiply-add);
       // keys this row may not see become -inf; the maximum is taken in log2 units
       const bool all_visible = key0 + 63 <= pos && key0 >= lo;
@@ -321,15 +351,28 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
       mx *= p.scale_log2;
       xmax[(j & 1) * 256 + half * 128 + row] = mx;
+      // (this barrier also separates every thread's reads of S from the other half's writes of P below)
       asm volatile("bar.sync 1, 256;" ::: "memory");
       mx = fmaxf(mx, xmax[(j & 1) * 256 + (half ^ 1) * 128 + row]);
-      // the operand tile P and the accumulator O are free once the previous P V has run
+      const bool grow = mx > m_used + kRescaleStep;
+      const float m_new = grow ? mx : m_used;
+      // exponentials and the row sum; P as bfloat16, two keys to a 32-bit word
+      float sum = 0.f;
+      uint32_t packed[32];
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const float e0 = ex2(fmaf(v[2 * e], p.scale_log2, -m_new));
+        const float e1 = ex2(fmaf(v[2 * e + 1], p.scale_log2, -m_new));
+        sum += e0 + e1;
+        __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+        packed[e] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      // O is at rest once the previous P V has run (it ran while the exponentials above were
+      // taken; waiting for it every tile also keeps this thread's count of the barrier's phases exact)
       if (j > 0 && !mbar_wait(o_done, (j - 1) & 1)) ok = false;
       tcgen05_fence_after();
       if (!ok) break;
-      const bool grow = mx > m_used + kRescaleStep;
       if (__any_sync(0xffffffffu, grow)) {
-        const float m_new = grow ? mx : m_used;
         const float corr = exp2f(m_used - m_new);
         if (j > 0) {
 #pragma unroll 1
@@ -344,26 +387,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         l *= corr;
         m_used = m_new;
       }
-      // exponentials, row sum, P as bfloat16 into the swizzled operand tile (slice = half)
-      float sum = 0.f;
-      uint8_t* prow = smem + (p_s - base) + half * kSlice + (row / 8) * 1024 + (row % 8) * 128;
-#pragma unroll
-      for (int piece = 0; piece < 8; ++piece) {
-        uint32_t packed[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float e0 = ex2(fmaf(v[piece * 8 + 2 * e], p.scale_log2, -m_used));
-          const float e1 = ex2(fmaf(v[piece * 8 + 2 * e + 1], p.scale_log2, -m_used));
-          sum += e0 + e1;
-          __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
-          packed[e] = *reinterpret_cast<uint32_t*>(&h);
-        }
-        *reinterpret_cast<uint4*>(prow + ((piece ^ (row % 8)) * 16)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-      }
       l += sum;
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core
+      // P_j takes the first 64 columns of the S tile its scores came from: this thread's 64
+      // keys are columns 32 half .. 32 half + 31
+      tmem_store_32u(s_t + half * 32, packed);
       tcgen05_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(p_full + 8 * (j & 1));
     }
     if (ok && !mbar_wait(o_done, (n_tiles - 1) & 1)) ok = false;
     tcgen05_fence_after();
@@ -420,7 +449,8 @@ template <int D>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mkr,
            const CUtensorMap& mvr, const Params& p, int n_tiles, cudaStream_t stream) {
   constexpr int kChunks = D / 64;
-  constexpr size_t smem = (size_t)kChunks * kRows * 128 * (1 + 2 * kStages) + 2 * kRows * 128 + 1024 + (8 + 4 * kStages) * 8 + 768 * 4;
+  constexpr int kStagesV = D == 128 ? 2 : 3;
+  constexpr size_t smem = (size_t)kChunks * kRows * 128 * (1 + kStagesK + kStagesV) + 1024 + (1 + 2 * kStagesK + 2 * kStagesV + 5 + 2) * 8 + 768 * 4;
   static_assert(smem <= 227 * 1024, "tiles do not fit shared memory");
   static OncePerDevice once;
   if (once.first()) {

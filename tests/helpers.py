@@ -77,10 +77,12 @@ CONFIGS = {"A": (CONFIG_A, SEED_A, PAGE_A), "B": (CONFIG_B, SEED_B, PAGE_B),
 # (crates/diagnostics/quality/src/verification.rs:22-67; crates/service/cli/src/constants.rs:19-22).
 F32_RTOL = 1e-5
 F32_ATOL = 1e-5
-# bfloat16 keeps 8 significant bits (unit roundoff 2^-9); a few layers of a handful of
-# rounding points each leave an error of a few 1e-3 of the activation scale (3e-3 is the
-# most these tests have shown).  The bound is 1e-2 of the largest reference logit, for every
-# element and every test.
+# bfloat16 keeps 8 significant bits (unit roundoff 2^-9).  The plain implementation rounds
+# the weights only; the engine also rounds activations wherever a matrix product reads or
+# writes them, which leaves noise on the logits: measured over whole prompts of the small
+# configurations, root-mean-square 0.3e-3 to 0.9e-3 of the largest reference logit and at
+# most 4.3e-3 for any element.  The bounds: every element within 1e-2 of the largest
+# reference logit, and the root-mean-square error of a comparison within a quarter of that.
 BF16_REL_OF_MAX = 1e-2
 
 
@@ -94,7 +96,8 @@ def random_tokens(n: int, vocab: int, seed: int) -> List[int]:
     return [rng.randrange(vocab) for _ in range(n)]
 
 
-def assert_close(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str = "") -> None:
+def assert_close(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str = "",
+                 bf16_rel_of_max: float = BF16_REL_OF_MAX) -> None:
     got = got.to(torch.float64).cpu()
     ref = ref.to(torch.float64).cpu()
     assert got.shape == ref.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(ref.shape)}"
@@ -103,7 +106,10 @@ def assert_close(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str = "
     if dtype == "float32":
         bound = F32_ATOL + F32_RTOL * ref.abs()
     else:
-        bound = torch.full_like(ref, BF16_REL_OF_MAX * float(ref.abs().max()))
+        bound = torch.full_like(ref, bf16_rel_of_max * float(ref.abs().max()))
+        rms = float(err.pow(2).mean().sqrt())
+        assert rms <= 0.25 * float(bound.flatten()[0]) or err.numel() < 64, \
+            f"{what}: root-mean-square error {rms:.3e} exceeds {0.25 * float(bound.flatten()[0]):.3e}"
     bad = err > bound
     if bad.any():
         idx = torch.nonzero(bad)[0].tolist()
@@ -179,10 +185,10 @@ def run_trace_inprocess(runner, trace: Trace) -> Dict[int, np.ndarray]:
 
 
 def check_trace(outputs: Dict[int, np.ndarray], trace: Trace, ref_logits: Dict[str, torch.Tensor],
-                dtype: str, what: str) -> None:
+                dtype: str, what: str, bf16_rel_of_max: float = BF16_REL_OF_MAX) -> None:
     """Every written row against the plain implementation's logits of that request at
     that position."""
     for step, rows in trace.rows.items():
         got = torch.from_numpy(outputs[step])
         ref = torch.stack([ref_logits[rid][pos] for rid, pos in rows])
-        assert_close(got, ref, dtype, f"{what} step {step} rows {rows[:4]}...")
+        assert_close(got, ref, dtype, f"{what} step {step} rows {rows[:4]}...", bf16_rel_of_max)

@@ -2,7 +2,13 @@
 8 key/value heads of size 128, feed-forward 12288) against the plain implementation, in 32-bit
 and in bfloat16 (GPU).  The tiny configurations never reach the shapes the serving kernels are
 tuned for: K ranges of a tile spread over a cluster, the widest SwiGLU epilogue, sums of 12288
-terms.  The vocabulary is kept small and odd; the output matrix is not what differs at size."""
+terms.  The vocabulary is kept small and odd; the output matrix is not what differs at size.
+
+The noise that rounding activations to bfloat16 leaves on the logits grows with the width:
+measured here over a whole prompt, root-mean-square 2.0e-3 of the largest reference logit and
+1.0e-2 for the worst of 600,000 elements (4.5 to 5 times the root-mean-square, as at the
+small configurations, whose figures are 0.9e-3 and 4.3e-3).  This file's bfloat16 bound is
+therefore 2e-2 per element and 5e-3 for the root-mean-square; the 32-bit bound is the common one."""
 import pytest
 import torch
 
@@ -60,7 +66,7 @@ def test_two_layers_of_serving_width(folder, dtype):
     del model
     runner = ModelRunner.from_folder(folder, dtype=dtype, page_size=16, num_pages=24, max_requests=4)
     trace = wide_trace(reqs)
-    check_trace(run_trace_inprocess(runner, trace), trace, ref, dtype, f"wide {dtype}")
+    check_trace(run_trace_inprocess(runner, trace), trace, ref, dtype, f"wide {dtype}", bf16_rel_of_max=2e-2)
     runner.cache.check()
     from inferloop_b200.csrc import ops
     ops.check_device_errors()
