@@ -45,8 +45,11 @@ namespace {
 
 constexpr int kRows = 128;             // rows of a CTA = MMA M
 constexpr int kKeys = 128;             // keys per tile = MMA N of S, K extent of P V
-constexpr int kThreads = 320;           // TMA warp, MMA warp, 8 softmax warps (two threads per row)
-constexpr int kStagesK = 3;           // K tiles in flight: S is issued two tiles ahead
+// Threads: TMA warp, MMA warp, 8 softmax warps (two threads per row) per row block.
+// K and V tiles in flight, by head size and row blocks per CTA (what shared memory holds beside
+// Q; one block issues its scores two key tiles ahead, two blocks one tile ahead).
+__host__ __device__ constexpr int stages_k(int d, int qb) { return qb == 2 ? (d == 128 ? 2 : 3) : 3; }   // scores run one (two blocks) or two tiles ahead
+__host__ __device__ constexpr int stages_v(int d, int qb) { return d == 128 ? 2 : 3; }
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleStep = 8.0f;   // log2 units
 
@@ -97,6 +100,20 @@ __device__ __forceinline__ void tmem_store_32u(uint32_t addr, const uint32_t (&v
       : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+// 32 columns of this thread's lane into v[0..31]; the values may be used after tmem_wait_ld().
+__device__ __forceinline__ void tmem_load_32_nowait(uint32_t addr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(addr));
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // D (tensor memory) (+)= A (tensor memory: row = lane, two bfloat16 of consecutive K per 32-bit
 // column) * B (shared memory descriptor).
 __device__ __forceinline__ void mma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
@@ -120,67 +137,85 @@ struct Params {
   int* error_flag;
   int max_blocks, n_seqs, nq, nkv, window, out_stride, page_size, num_pages;
   float scale_log2;
+  int skip_single;       // sequences that bring one token are somebody else's (the decode kernel's)
 };
 
-template <int D>
-__global__ void __launch_bounds__(kThreads)
+// QB = row blocks of a CTA.  Measured on this part (one thread issuing, operands in place): a
+// tcgen05.mma of 128 rows takes 104 clocks with both operands in shared memory and 87 with A
+// in tensor memory whatever its N up to 128 (170 at N = 256), so a 128 x 128 score tile and
+// its P V cost 8 x 107 + 8 x 87 = 1,550 clocks of the tensor core, and the exponentials
+// 1,024 clocks of the special-function unit (16 a clock and SM).
+//   One block: its scores alternate between two S buffers and are issued two tiles ahead, so
+//   the softmax warps never wait for the tensor core; a tile takes as long as their loop.
+//   Two blocks (256 rows, consecutive tokens of one sequence; for long prompts): they share
+//   every K and V tile that comes in; tensor memory holds one S buffer and O per block (4 x
+//   128 columns), scores are issued one tile ahead, and while one block's warps work on a
+//   tile the tensor core works for the other block.
+template <int D, int QB>
+__global__ void __launch_bounds__(64 + 256 * QB)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_k_run,
                   const __grid_constant__ CUtensorMap map_v_run, const Params p) {
   constexpr int kChunks = D / 64;                       // 64-wide slices of the head
   constexpr uint32_t kSlice = kRows * 128;              // bytes of a [128][64] bf16 slice
-  constexpr uint32_t kQBytes = kChunks * kSlice;
+  constexpr uint32_t kQBytes = kChunks * kSlice;        // one row block of Q
   constexpr uint32_t kKBytes = kChunks * kSlice;        // [slice][128 keys][64]
   constexpr uint32_t kVBytes = kChunks * kSlice;        // [slice of d][128 keys][64]
-  constexpr int kStagesV = D == 128 ? 2 : 3;            // V tiles in flight (what shared memory holds beside Q and three K tiles)
-  constexpr uint32_t kTmemCols = 512;                   // two S tiles of 128 columns, then O: D (<= 128)
+  constexpr int kStagesK = stages_k(D, QB), kStagesV = stages_v(D, QB);
+  constexpr int KS = kKeys;                             // keys of a score tile
+  constexpr int SUB = kKeys / KS;                       // score tiles per K / V tile
+  constexpr int NBUF = QB == 2 ? 1 : 2;                 // S buffers per block = score tiles issued ahead
+  constexpr int E = KS / 2;                             // scores per softmax thread and score tile
+  constexpr uint32_t kTmemCols = 512;                   // S buffers: QB x NBUF x 128 columns = 256; then O of each block: 128 columns apart
   ilb::pdl_launch_dependents();
   ilb::pdl_wait();                      // q, the cache and the step's arrays come from earlier work in the stream
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t q_s = base, k_s = q_s + kQBytes, v_s = k_s + kStagesK * kKBytes, end_s = v_s + kStagesV * kVBytes;
+  const uint32_t q_s = base, k_s = q_s + QB * kQBytes, v_s = k_s + kStagesK * kKBytes, end_s = v_s + kStagesV * kVBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (end_s - base));
   const uint32_t bar0 = smem_u32(bars);
-  // s_full[b], p_full[b]: the S tile b = j & 1 holds the scores of tile j / holds its probabilities
+  // s_full[t], p_full[t]: S tile t holds scores / holds the probabilities made from them;
+  // o_done[q]: the last O += P V of block q that was issued has run
   const uint32_t q_full = bar0, k_full = bar0 + 8, k_empty = k_full + 8 * kStagesK, v_full = k_empty + 8 * kStagesK,
-                 v_empty = v_full + 8 * kStagesV, s_full = v_empty + 8 * kStagesV, p_full = s_full + 16, o_done = p_full + 16;
-  constexpr int kBars = 1 + 2 * kStagesK + 2 * kStagesV + 5;
+                 v_empty = v_full + 8 * kStagesV, s_full = v_empty + 8 * kStagesV, p_full = s_full + 32, o_done = p_full + 32;
+  constexpr int kBars = 1 + 2 * kStagesK + 2 * kStagesV + 10;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + kBars);
   volatile int* failed = reinterpret_cast<volatile int*>(bars + kBars + 1);
-  float* xmax = reinterpret_cast<float*>(bars + kBars + 2);      // [2][2][128] row maxima, then [2][128] row sums
+  float* xmax_all = reinterpret_cast<float*>(bars + kBars + 2);      // per block: [2][2][128] row maxima, then [2][128] row sums
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = p.nq / p.nkv;
-  const int kvh = blockIdx.y;
-  const int tokens_per_tile = kRows / G;
+  const int kvh = blockIdx.x;           // heads vary fastest, so that the longest runs of every head start first
+  const int tokens_per_block = kRows / G;
+  const int tokens_per_cta = QB * tokens_per_block;
 
-  // which sequence and which row tile of it; long tiles first
-  int seq = 0, tile = (int)gridDim.x - 1 - (int)blockIdx.x;
+  // which sequence and which run of its tokens; the runs with the most keys first
+  int seq = 0, tile = (int)gridDim.y - 1 - (int)blockIdx.y;
   for (; seq < p.n_seqs; ++seq) {
     const int n = p.cu_q[seq + 1] - p.cu_q[seq];
-    const int tiles = (n + tokens_per_tile - 1) / tokens_per_tile;
+    const int tiles = (p.skip_single && n == 1) ? 0 : (n + tokens_per_cta - 1) / tokens_per_cta;
     if (tile < tiles) break;
     tile -= tiles;
   }
   if (seq >= p.n_seqs) return;
   const int tok0 = p.cu_q[seq], q_len = p.cu_q[seq + 1] - tok0;
-  const int t_first = tile * tokens_per_tile;
-  const int t_last = min(q_len, t_first + tokens_per_tile) - 1;
+  const int t_first = tile * tokens_per_cta;
+  const int t_last = min(q_len, t_first + tokens_per_cta) - 1;
   // positions are written by the step's staging copy, an earlier operation in the stream
   const int pos_first = p.positions[tok0 + t_first], pos_last = p.positions[tok0 + t_last];
   const int key_lo = (p.window > 0 && pos_first + 1 > p.window) ? pos_first + 1 - p.window : 0;
   const int first_tile = key_lo / kKeys;
-  const int n_tiles = pos_last / kKeys - first_tile + 1;
+  const int n_tiles = pos_last / kKeys - first_tile + 1;      // both blocks walk all of them; what a row may not see is masked
   const int* table = p.block_table + (size_t)seq * p.max_blocks;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < kStagesK; ++s) { mbar_init(k_full + 8 * s, 1); mbar_init(k_empty + 8 * s, 1); }
     for (int s = 0; s < kStagesV; ++s) { mbar_init(v_full + 8 * s, 1); mbar_init(v_empty + 8 * s, 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(s_full + 8 * b, 1); mbar_init(p_full + 8 * b, 256); }
-    mbar_init(o_done, 1);
+    for (int t = 0; t < 4; ++t) { mbar_init(s_full + 8 * t, 1); mbar_init(p_full + 8 * t, 256); }
+    for (int t = 0; t < 2; ++t) mbar_init(o_done + 8 * t, 1);
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -191,8 +226,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * kKeys;       // S tile b at tmem_s + 128 b
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);      // (the same in every lane, and known to be)
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 256;
+  // Score tile u of block q goes to S buffer NBUF q + u % NBUF, and this is use u / NBUF of
+  // it; the barrier pairs s_full / p_full are indexed like the buffers.
+  const int n_sub = n_tiles * SUB;
+  auto s_buf = [](int q, int u) { return NBUF * q + (u % NBUF); };
+  auto s_use = [](int u) { return u / NBUF; };
+  auto s_cols = [&](int q, int u) { return tmem_s + (uint32_t)(s_buf(q, u) * KS); };
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -200,10 +241,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     // warp's lanes issue them side by side, lanes 0-15 the K boxes and 16-31 the V boxes,
     // after lane 0 has seen the stage free and armed its barrier.
     if (lane == 0) {
-      // the box is G heads x tokens_per_tile tokens: rows_used rows of 128 bytes per slice
-      mbar_expect_tx(q_full, (uint32_t)(kChunks * tokens_per_tile * G * 128));
+      // a block's box is G heads x tokens_per_block tokens: that many rows of 128 bytes per slice
+      mbar_expect_tx(q_full, (uint32_t)(QB * kChunks * tokens_per_block * G * 128));
 #pragma unroll
-      for (int c = 0; c < kChunks; ++c) tma_load_3d(q_s + c * kSlice, &map_q, q_full, c * 64, kvh * G, tok0 + t_first);
+      for (int q = 0; q < QB; ++q)
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c)
+          tma_load_3d(q_s + q * kQBytes + c * kSlice, &map_q, q_full, c * 64, kvh * G, tok0 + t_first + q * tokens_per_block);
     }
     const int pages_per_tile = kKeys / p.page_size;
     const int box = lane & 15, box_page = box / kChunks, box_slice = box % kChunks;
@@ -219,187 +263,242 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       }
       return page;
     };
-    int page_next = lookup(0);
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int s = j % kStagesK, sv = j % kStagesV;
-      const int page = page_next;
-      page_next = lookup(j + 1);                          // in flight while this tile's boxes are issued
+    // The K ring and the V ring are filled independently, each as soon as it has a free stage
+    // (scores run ahead of the products that free V stages, so K tiles are wanted earlier).
+    // The TMA unit takes tens of nanoseconds per box whatever its size, and a tile is up to
+    // 32 boxes of 2 KB.  When the tile's pages follow one another in the pool (the usual
+    // case: pages are handed out in order) one box per slice spans all of them.
+    int jk = 0, jv = 0;
+    int page_k = lookup(0), page_v = page_k;               // pages of this lane's box of tiles jk and jv
+    uint32_t idle = 0;
+    while ((jk < n_tiles || jv < n_tiles) && ok) {
+      int free_k = 0, free_v = 0;
       if (lane == 0) {
-        if (j >= kStagesK) ok = mbar_wait(k_empty + 8 * s, ((j / kStagesK) - 1) & 1);
-        if (ok) mbar_expect_tx(k_full + 8 * s, kKBytes);
+        free_k = jk < n_tiles && (jk < kStagesK || mbar_test_wait(k_empty + 8 * (jk % kStagesK), ((jk / kStagesK) - 1) & 1));
+        free_v = jv < n_tiles && (jv < kStagesV || mbar_test_wait(v_empty + 8 * (jv % kStagesV), ((jv / kStagesV) - 1) & 1));
       }
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) break;
-      // The TMA unit takes tens of nanoseconds per box whatever its size, and a tile is up to
-      // 32 boxes of 2 KB.  When the tile's pages follow one another in the pool (the usual
-      // case: pages are handed out in order) one box per slice spans all of them.
-      const int first_page = __shfl_sync(0xffffffffu, page, 0);
-      const bool run = __all_sync(0xffffffffu, !has_box || page == first_page + box_page) &&
-                       first_page + pages_per_tile <= p.num_pages;
-      if (run) {
-        if (lane < kChunks)
-          tma_load_4d(k_s + s * kKBytes + lane * kSlice, &map_k_run, k_full + 8 * s, lane * 64, 0, kvh, first_page);
-      } else if (has_box && lane < 16)
-        tma_load_4d(k_s + s * kKBytes + box_slice * kSlice + box_page * p.page_size * 128, &map_k, k_full + 8 * s,
-                    box_slice * 64, 0, kvh, page);
-      if (lane == 0) {
-        if (j >= kStagesV) ok = mbar_wait(v_empty + 8 * sv, ((j / kStagesV) - 1) & 1);
-        if (ok) mbar_expect_tx(v_full + 8 * sv, kVBytes);
+      free_k = __shfl_sync(0xffffffffu, free_k, 0);
+      free_v = __shfl_sync(0xffffffffu, free_v, 0);
+      if (free_k) {
+        const int s = jk % kStagesK;
+        const int page = page_k;
+        page_k = lookup(jk + 1);                            // in flight while this tile's boxes are issued
+        if (lane == 0) mbar_expect_tx(k_full + 8 * s, kKBytes);
+        __syncwarp();
+        const int first_page = __shfl_sync(0xffffffffu, page, 0);
+        const bool run = __all_sync(0xffffffffu, !has_box || page == first_page + box_page) &&
+                         first_page + pages_per_tile <= p.num_pages;
+        if (run) {
+          if (lane < kChunks)
+            tma_load_4d(k_s + s * kKBytes + lane * kSlice, &map_k_run, k_full + 8 * s, lane * 64, 0, kvh, first_page);
+        } else if (has_box && lane < 16)
+          tma_load_4d(k_s + s * kKBytes + box_slice * kSlice + box_page * p.page_size * 128, &map_k, k_full + 8 * s,
+                      box_slice * 64, 0, kvh, page);
+        ++jk;
       }
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) break;
-      if (run) {
-        if (lane >= 16 && lane < 16 + kChunks)
-          tma_load_4d(v_s + sv * kVBytes + (lane - 16) * kSlice, &map_v_run, v_full + 8 * sv, (lane - 16) * 64, 0, kvh, first_page);
-      } else if (has_box && lane >= 16)
-        tma_load_4d(v_s + sv * kVBytes + box_slice * kSlice + box_page * p.page_size * 128, &map_v, v_full + 8 * sv,
-                    box_slice * 64, 0, kvh, page);
+      if (free_v) {
+        const int sv = jv % kStagesV;
+        const int page = page_v;
+        page_v = lookup(jv + 1);
+        if (lane == 0) mbar_expect_tx(v_full + 8 * sv, kVBytes);
+        __syncwarp();
+        const int first_page = __shfl_sync(0xffffffffu, page, 0);
+        const bool run = __all_sync(0xffffffffu, !has_box || page == first_page + box_page) &&
+                         first_page + pages_per_tile <= p.num_pages;
+        if (run) {
+          if (lane >= 16 && lane < 16 + kChunks)
+            tma_load_4d(v_s + sv * kVBytes + (lane - 16) * kSlice, &map_v_run, v_full + 8 * sv, (lane - 16) * 64, 0, kvh, first_page);
+        } else if (has_box && lane >= 16)
+          tma_load_4d(v_s + sv * kVBytes + box_slice * kSlice + box_page * p.page_size * 128, &map_v, v_full + 8 * sv,
+                      box_slice * 64, 0, kvh, page);
+        ++jv;
+      }
+      if (free_k || free_v) idle = 0;
+      else if (++idle > 64u * kWaitLimit) ok = false;       // bounded like every other wait (a poll here returns at once)
     }
     if (!ok && lane == 0) { *failed = 1; if (p.error_flag) *p.error_flag = 1; }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
+    // (One lane issues.  Having the whole warp walk this loop with lane 0 predicated, so that
+    // the operands could stay in uniform registers, was measured and was slower.)
     if (lane == 0) {
-      constexpr uint32_t idesc_s = instr_desc(kRows, kKeys, 0);
+      constexpr uint32_t idesc_s = instr_desc(kRows, KS, 0);
       constexpr uint32_t idesc_o = instr_desc(kRows, D, 1);
       bool ok = mbar_wait(q_full, 0);
-      auto issue_s = [&](int j) {          // S tile (j & 1) = Q K_j^T
-        const int s = j % kStagesK;
+      // scores of (block q, score tile u) = Q_q K^T over the tile's KS keys, into their S buffer
+      auto issue_s = [&](int q, int u) {
+        const int j = u / SUB, h = u % SUB, s = j % kStagesK;
         ok = ok && mbar_wait(k_full + 8 * s, (j / kStagesK) & 1);
         if (!ok) return;
         tcgen05_fence_after();
-        const uint32_t acc = tmem_s + (uint32_t)(j & 1) * kKeys;
+        const uint32_t acc = s_cols(q, u);
 #pragma unroll
         for (int c = 0; c < kChunks; ++c)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            mma_bf16(acc, desc_k_major(q_s + c * kSlice) + 2 * k, desc_k_major(k_s + s * kKBytes + c * kSlice) + 2 * k,
-                     idesc_s, (c > 0 || k > 0) ? 1u : 0u);
-        tcgen05_commit(k_empty + 8 * s);
-        tcgen05_commit(s_full + 8 * (j & 1));
+            mma_bf16(acc, desc_k_major(q_s + q * kQBytes + c * kSlice) + 2 * k,
+                     desc_k_major(k_s + s * kKBytes + c * kSlice + h * (KS * 128)) + 2 * k, idesc_s, (c > 0 || k > 0) ? 1u : 0u);
+        tcgen05_commit(s_full + 8 * s_buf(q, u));
       };
-      // Two S tiles: the scores of tile j + 2 are issued right behind O += P_j V_j, into the
-      // tile that P_j is read from.  The tensor core executes what one thread issues in the
-      // order of issue, so the product has read P_j before the new scores overwrite it; and
-      // P_j was only written after the softmax warps had read the scores of tile j.
-      if (ok) issue_s(0);
-      if (ok && n_tiles > 1) issue_s(1);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int sv = j % kStagesV, b = j & 1;
-        ok = ok && mbar_wait(p_full + 8 * b, (j >> 1) & 1);
-        ok = ok && mbar_wait(v_full + 8 * sv, (j / kStagesV) & 1);
-        if (!ok) break;
-        tcgen05_fence_after();
-        const uint32_t p_t = tmem_s + (uint32_t)b * kKeys;     // P_j: 64 columns, two bfloat16 of consecutive keys each
+      // The scores that next use an S buffer are issued right behind the O += P V that reads P
+      // from it.  The tensor core executes what one thread issues in the order of issue, so
+      // the product has read P before the new scores overwrite it; and P was only written
+      // after the softmax warps had read the scores that were there.
+      // K and V stages go back to the producer once every block has issued its last use of
+      // them (a commit covers everything issued before it).
+      int s_issued[QB], pv_issued[QB], k_released = 0, v_released = 0;
 #pragma unroll
-        for (int k = 0; k < kKeys / 16; ++k)   // 16 keys a step: 8 columns of P, two 8-key groups of V
-          mma_bf16_ts(tmem_o, p_t + 8 * k, desc_mn_major(v_s + sv * kVBytes + k * 2048, kSlice), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
-        tcgen05_commit(v_empty + 8 * sv);
-        tcgen05_commit(o_done);
-        if (j + 2 < n_tiles) issue_s(j + 2);
+      for (int q = 0; q < QB; ++q) { s_issued[q] = 0; pv_issued[q] = 0; }
+      auto release = [&]() {
+        int s_min = s_issued[0], pv_min = pv_issued[0];
+#pragma unroll
+        for (int q = 1; q < QB; ++q) { s_min = min(s_min, s_issued[q]); pv_min = min(pv_min, pv_issued[q]); }
+        for (; k_released < s_min / SUB; ++k_released) tcgen05_commit(k_empty + 8 * (k_released % kStagesK));
+        for (; v_released < pv_min / SUB; ++v_released) tcgen05_commit(v_empty + 8 * (v_released % kStagesV));
+      };
+      for (int u = 0; u < NBUF && u < n_sub; ++u)
+        for (int q = 0; q < QB && ok; ++q) { issue_s(q, u); s_issued[q] = u + 1; }
+      release();
+      // Whichever block has its probabilities ready is served next: the blocks drift apart by
+      // half a tile and then take turns at the special-function unit and at the tensor core.
+      int left = QB * n_sub;
+      uint32_t idle = 0;
+      while (left > 0 && ok) {
+        bool any = false;
+#pragma unroll
+        for (int q = 0; q < QB; ++q) {
+          const int u = pv_issued[q];
+          if (u >= n_sub || !ok) continue;
+          if (!mbar_test_wait(p_full + 8 * s_buf(q, u), s_use(u) & 1)) continue;
+          const int j = u / SUB, h = u % SUB, sv = j % kStagesV;
+          ok = ok && mbar_wait(v_full + 8 * sv, (j / kStagesV) & 1);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t p_t = s_cols(q, u);       // P: KS / 2 columns, two bfloat16 of consecutive keys each
+#pragma unroll
+          for (int k = 0; k < KS / 16; ++k)   // 16 keys a step: 8 columns of P, two 8-key groups of V
+            mma_bf16_ts(tmem_o + (uint32_t)q * 128u, p_t + 8 * k, desc_mn_major(v_s + sv * kVBytes + (h * (KS / 16) + k) * 2048, kSlice),
+                        idesc_o, (u > 0 || k > 0) ? 1u : 0u);
+          tcgen05_commit(o_done + 8 * q);
+          pv_issued[q] = u + 1;
+          if (u + NBUF < n_sub) { issue_s(q, u + NBUF); s_issued[q] = u + NBUF + 1; }
+          release();
+          --left;
+          any = true;
+        }
+        if (any) idle = 0;
+        else if (++idle > 64u * kWaitLimit) ok = false;       // bounded like every other wait (a poll here returns at once)
       }
       if (!ok) {
         *failed = 1; if (p.error_flag) *p.error_flag = 1;
-        tcgen05_commit(s_full); tcgen05_commit(s_full + 8); tcgen05_commit(o_done);       // let the softmax warps leave their waits
+        for (int t = 0; t < 4; ++t) tcgen05_commit(s_full + 8 * t);          // let the softmax warps leave their waits
+        tcgen05_commit(o_done); tcgen05_commit(o_done + 8);
       }
     }
   } else {
     // ---------------------------------------------------------------- softmax, correction, output
-    // Two threads per row: warps 2-5 take keys 0..63 of a tile (and the first half of the
-    // head's columns of O), warps 6-9 keys 64..127 (and the second half).
+    // Per block eight warps, two threads per row: four warps take keys 0..63 of a tile (and the
+    // first half of the head's columns of O), four take keys 64..127 (and the second half).
+    const int q = (warp - 2) >> 3;                       // row block of this warp
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = ((warp - 2) & 7) >> 2;
     const int row = quad * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-    const int tl = t_first + row / G;
-    const bool live = row < tokens_per_tile * G && tl < q_len;     // rows past the last whole token hold no query
+    float* xmax = xmax_all + q * 768;
+    const uint32_t o_t = tmem_o + (uint32_t)q * kKeys + lane_addr;
+    const int tl = t_first + q * tokens_per_block + row / G;
+    const bool live = row < tokens_per_block * G && tl < q_len;     // rows past the last whole token hold no query
     const int head = kvh * G + row % G;
     const int pos = live ? p.positions[tok0 + tl] : -1;
     const int lo = (live && p.window > 0 && pos + 1 > p.window) ? pos + 1 - p.window : 0;
     constexpr int kOCols = D / 2;                      // columns of O this thread owns
     float m_used = -1e30f, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      const int key0 = (first_tile + j) * kKeys + half * 64;
-      const uint32_t s_t = tmem_s + (uint32_t)(j & 1) * kKeys + lane_addr;     // this row of the S tile of tile j
-      // `ok` only ever changes through waits that all 256 threads share, so they leave the
-      // loop together and nobody is left alone at the named barrier below
-      if (!mbar_wait(s_full + 8 * (j & 1), (j >> 1) & 1)) ok = false;
+    auto block_sync = [&]() {                           // the 256 threads of this row block
+      if (q == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
+      else asm volatile("bar.sync 2, 256;" ::: "memory");
+    };
+    for (int u = 0; u < n_sub; ++u) {
+      const int key0 = first_tile * kKeys + u * KS + half * E;
+      const int t = s_buf(q, u);
+      const uint32_t s_t = s_cols(q, u) + lane_addr;     // this row of the S buffer
+      // `ok` only ever changes through waits that all 256 threads of the block share, so they
+      // leave the loop together and nobody is left alone at the named barrier below
+      if (!mbar_wait(s_full + 8 * t, s_use(u) & 1)) ok = false;
       tcgen05_fence_after();
       if (!ok) break;
-      float v[64];
-      {
-        float a[32], b2[32];
-        tmem_load_32(s_t + half * 64, a);
-        tmem_load_32(s_t + half * 64 + 32, b2);
+      float v[E];
 #pragma unroll
-        for (int c = 0; c < 32; ++c) { v[c] = a[c]; v[32 + c] = b2[c]; }
-      }
+      for (int c0 = 0; c0 < E; c0 += 32) tmem_load_32_nowait(s_t + half * E + c0, v + c0);
+      tmem_wait_ld();
       // raw scores stay in v (the scale is positive and folds into the exponent's multiply-add);
-      // keys this row may not see become -inf; the maximum is taken in log2 units
-      const bool all_visible = key0 + 63 <= pos && key0 >= lo;
-      float mx = -INFINITY;
-      if (all_visible) {
+      // keys this row may not see become -inf; the maximum is taken in log2 units, in four
+      // chains so that no instruction waits for the one before it
+      const bool all_visible = key0 + E - 1 <= pos && key0 >= lo;
+      if (!all_visible) {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) mx = fmaxf(mx, v[c]);
-      } else {
-#pragma unroll
-        for (int c = 0; c < 64; ++c) {
+        for (int c = 0; c < E; ++c) {
           const int key = key0 + c;
           v[c] = (key <= pos && key >= lo) ? v[c] : -INFINITY;
-          mx = fmaxf(mx, v[c]);
         }
       }
-      mx *= p.scale_log2;
-      xmax[(j & 1) * 256 + half * 128 + row] = mx;
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < E; c += 4) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) m4[i] = fmaxf(m4[i], v[c + i]);
+      }
+      float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
+      xmax[(u & 1) * 256 + half * 128 + row] = mx;
       // (this barrier also separates every thread's reads of S from the other half's writes of P below)
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      mx = fmaxf(mx, xmax[(j & 1) * 256 + (half ^ 1) * 128 + row]);
+      block_sync();
+      mx = fmaxf(mx, xmax[(u & 1) * 256 + (half ^ 1) * 128 + row]);
       const bool grow = mx > m_used + kRescaleStep;
       const float m_new = grow ? mx : m_used;
-      // exponentials and the row sum; P as bfloat16, two keys to a 32-bit word
-      float sum = 0.f;
-      uint32_t packed[32];
+      // exponentials and the row sum (two chains); P as bfloat16, two keys to a 32-bit word
+      float sum0 = 0.f, sum1 = 0.f;
+      uint32_t packed[E / 2];
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
+      for (int e = 0; e < E / 2; ++e) {
         const float e0 = ex2(fmaf(v[2 * e], p.scale_log2, -m_new));
         const float e1 = ex2(fmaf(v[2 * e + 1], p.scale_log2, -m_new));
-        sum += e0 + e1;
-        __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
-        packed[e] = *reinterpret_cast<uint32_t*>(&h);
+        sum0 += e0; sum1 += e1;
+        __nv_bfloat162 hh = __floats2bfloat162_rn(e0, e1);
+        packed[e] = *reinterpret_cast<uint32_t*>(&hh);
       }
-      // O is at rest once the previous P V has run (it ran while the exponentials above were
-      // taken; waiting for it every tile also keeps this thread's count of the barrier's phases exact)
-      if (j > 0 && !mbar_wait(o_done, (j - 1) & 1)) ok = false;
-      tcgen05_fence_after();
+      // O is at rest once the block's previous P V has run (it ran while the exponentials above
+      // were taken; waiting for it every tile also keeps this thread's count of the barrier's phases exact)
+      if (u > 0 && !mbar_wait(o_done + 8 * q, (u - 1) & 1)) ok = false;
       if (!ok) break;
       if (__any_sync(0xffffffffu, grow)) {
         const float corr = exp2f(m_used - m_new);
-        if (j > 0) {
+        if (u > 0) {
+          tcgen05_fence_after();
 #pragma unroll 1
           for (int c0 = 0; c0 < kOCols; c0 += 32) {
             float o[32];
-            tmem_load_32(tmem_o + lane_addr + half * kOCols + c0, o);
+            tmem_load_32(o_t + half * kOCols + c0, o);
 #pragma unroll
             for (int c = 0; c < 32; ++c) o[c] *= corr;
-            tmem_store_32(tmem_o + lane_addr + half * kOCols + c0, o);
+            tmem_store_32(o_t + half * kOCols + c0, o);
           }
         }
         l *= corr;
         m_used = m_new;
       }
-      l += sum;
-      // P_j takes the first 64 columns of the S tile its scores came from: this thread's 64
-      // keys are columns 32 half .. 32 half + 31
-      tmem_store_32u(s_t + half * 32, packed);
+      l += sum0 + sum1;
+      // P takes the first KS / 2 columns of the S buffer its scores came from: this thread's
+      // keys are columns (E / 2) half .. (E / 2) half + E / 2 - 1
+      tmem_store_32u(s_t + half * (E / 2), packed);
       tcgen05_fence_before();
-      mbar_arrive(p_full + 8 * (j & 1));
+      mbar_arrive(p_full + 8 * t);
     }
-    if (ok && !mbar_wait(o_done, (n_tiles - 1) & 1)) ok = false;
+    if (ok && !mbar_wait(o_done + 8 * q, (n_sub - 1) & 1)) ok = false;
     tcgen05_fence_after();
     if (!ok) { *failed = 1; if (p.error_flag) *p.error_flag = 1; }
     // the two halves of a row add their sums
     xmax[512 + half * 128 + row] = l;
-    asm volatile("bar.sync 1, 256;" ::: "memory");
+    block_sync();
     l += xmax[512 + (half ^ 1) * 128 + row];
     if (ok) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -407,18 +506,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll 1
       for (int c0 = 0; c0 < kOCols; c0 += 32) {
         float o[32];
-        tmem_load_32(tmem_o + lane_addr + half * kOCols + c0, o);       // collective: every lane of the warp takes part
+        tmem_load_32(o_t + half * kOCols + c0, o);       // collective: every lane of the warp takes part
         if (live) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
+          for (int g = 0; g < 4; ++g) {
             uint4 w;
-            __nv_bfloat162 h0 = __floats2bfloat162_rn(o[8 * q] * inv, o[8 * q + 1] * inv);
-            __nv_bfloat162 h1 = __floats2bfloat162_rn(o[8 * q + 2] * inv, o[8 * q + 3] * inv);
-            __nv_bfloat162 h2 = __floats2bfloat162_rn(o[8 * q + 4] * inv, o[8 * q + 5] * inv);
-            __nv_bfloat162 h3 = __floats2bfloat162_rn(o[8 * q + 6] * inv, o[8 * q + 7] * inv);
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(o[8 * g] * inv, o[8 * g + 1] * inv);
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(o[8 * g + 2] * inv, o[8 * g + 3] * inv);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(o[8 * g + 4] * inv, o[8 * g + 5] * inv);
+            __nv_bfloat162 h3 = __floats2bfloat162_rn(o[8 * g + 6] * inv, o[8 * g + 7] * inv);
             w.x = *reinterpret_cast<uint32_t*>(&h0); w.y = *reinterpret_cast<uint32_t*>(&h1);
             w.z = *reinterpret_cast<uint32_t*>(&h2); w.w = *reinterpret_cast<uint32_t*>(&h3);
-            *reinterpret_cast<uint4*>(dst + c0 + 8 * q) = w;
+            *reinterpret_cast<uint4*>(dst + c0 + 8 * g) = w;
           }
         }
       }
@@ -445,20 +544,21 @@ int encode(CUtensorMap* out, const void* ptr, int rank, const cuuint64_t* dims, 
   return 0;
 }
 
-template <int D>
+template <int D, int QB>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mkr,
            const CUtensorMap& mvr, const Params& p, int n_tiles, cudaStream_t stream) {
   constexpr int kChunks = D / 64;
-  constexpr int kStagesV = D == 128 ? 2 : 3;
-  constexpr size_t smem = (size_t)kChunks * kRows * 128 * (1 + kStagesK + kStagesV) + 1024 + (1 + 2 * kStagesK + 2 * kStagesV + 5 + 2) * 8 + 768 * 4;
+  constexpr int kStagesK = stages_k(D, QB), kStagesV = stages_v(D, QB);
+  constexpr size_t smem = (size_t)kChunks * kRows * 128 * (QB + kStagesK + kStagesV) + 1024 +
+                          (1 + 2 * kStagesK + 2 * kStagesV + 10 + 2) * 8 + (size_t)QB * 768 * 4;
   static_assert(smem <= 227 * 1024, "tiles do not fit shared memory");
   static OncePerDevice once;
   if (once.first()) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<D, QB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) once.forget();
     if (e != cudaSuccess) return fail("attention (tensor cores): cannot reserve %zu bytes of shared memory", smem);
   }
-  ilb::launch(prefill_tc_kernel<D>, dim3(n_tiles, p.nkv), dim3(kThreads), smem, stream, mq, mk, mv, mkr, mvr, p);
+  ilb::launch(prefill_tc_kernel<D, QB>, dim3(p.nkv, n_tiles), dim3(64 + 256 * QB), smem, stream, mq, mk, mv, mkr, mvr, p);
   return check_launch("attention prefill (tensor cores)");
 }
 
@@ -472,15 +572,19 @@ ILB_EXPORT int ilb_attention_tc_supported(int nq, int nkv, int d, int page_size)
           (page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128)) ? 1 : 0;
 }
 
-// n_tiles = sum over sequences of ceil(q_len / floor(128 / G)).
+// row_blocks = 1 or 2 blocks of 128 rows per CTA (two share every K and V tile: for long
+// portions); n_tiles = sum over sequences of ceil(q_len / (row_blocks * floor(128 / G))),
+// without the sequences of one token if skip_single is set (their rows of `out` are then
+// left alone).
 ILB_EXPORT int ilb_attention_prefill_tc(const void* q, void* out, const void* k_cache, const void* v_cache,
                                         const int* positions, const int* cu_q, const int* block_table,
                                         int max_blocks, int page_size, int num_pages, int window, float scale,
-                                        int n_tokens, int n_seqs, int n_tiles, int nq, int nkv, int d,
+                                        int n_tokens, int n_seqs, int n_tiles, int row_blocks, int skip_single, int nq, int nkv, int d,
                                         int q_stride, int out_stride, int* error_flag, cudaStream_t stream) {
+  ILB_REQUIRE(row_blocks == 1 || row_blocks == 2, "attention (tensor cores): %d row blocks per CTA (1 or 2)", row_blocks);
   ILB_REQUIRE(ilb_attention_tc_supported(nq, nkv, d, page_size),
               "attention (tensor cores): heads %d/%d, head size %d, page size %d are not built", nq, nkv, d, page_size);
-  ILB_REQUIRE(n_tokens > 0 && n_seqs > 0 && n_tiles > 0 && nkv <= 65535 && max_blocks > 0 && num_pages > 0 && window >= 0,
+  ILB_REQUIRE(n_tokens > 0 && n_seqs > 0 && n_tiles > 0 && n_tiles <= 65535 && max_blocks > 0 && num_pages > 0 && window >= 0,
               "attention (tensor cores): bad sizes");
   ILB_REQUIRE(q_stride % 8 == 0 && out_stride % 8 == 0 && ((uintptr_t)q % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
               ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0), "attention (tensor cores): misaligned operands");
@@ -504,8 +608,10 @@ ILB_EXPORT int ilb_attention_prefill_tc(const void* q, void* out, const void* k_
     if (encode(&mvr, v_cache, 4, dims, strides, run, "v cache (page run)")) return -1;
   }
   Params p{(__nv_bfloat16*)out, positions, cu_q, block_table, error_flag, max_blocks, n_seqs, nq, nkv, window,
-           out_stride, page_size, num_pages, scale * kLog2e};
-  return d == 64 ? launch<64>(mq, mk, mv, mkr, mvr, p, n_tiles, stream) : launch<128>(mq, mk, mv, mkr, mvr, p, n_tiles, stream);
+           out_stride, page_size, num_pages, scale * kLog2e, skip_single ? 1 : 0};
+  if (row_blocks == 2)
+    return d == 64 ? launch<64, 2>(mq, mk, mv, mkr, mvr, p, n_tiles, stream) : launch<128, 2>(mq, mk, mv, mkr, mvr, p, n_tiles, stream);
+  return d == 64 ? launch<64, 1>(mq, mk, mv, mkr, mvr, p, n_tiles, stream) : launch<128, 1>(mq, mk, mv, mkr, mvr, p, n_tiles, stream);
 }
 
 ILB_DEFINE_LAST_ERROR()

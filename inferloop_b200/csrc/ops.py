@@ -388,16 +388,18 @@ def attention_tc_supported(nq: int, nkv: int, d: int, page_size: int) -> bool:
 
 
 def attention_prefill_tc(q, out, k_cache, v_cache, positions, cu_q, block_table, window, scale, n_seqs,
-                         n_tiles, nq, nkv, d) -> None:
-    """Prefill attention on tcgen05 tensor cores (attention_tc.cu); n_tiles counts tiles of
-    128 // (nq / nkv) tokens over the sequences."""
+                         n_tiles, nq, nkv, d, row_blocks: int = 1, skip_single: bool = False) -> None:
+    """Prefill attention on tcgen05 tensor cores (attention_tc.cu); a CTA takes `row_blocks`
+    (1 or 2) blocks of 128 // (nq / nkv) tokens of one sequence, and n_tiles counts the CTAs
+    over the sequences (with `skip_single`, over those that bring more than one token: the
+    others' rows of `out` are left alone)."""
     for t, w in ((q, "q"), (out, "out"), (k_cache, "k cache"), (v_cache, "v cache")):
         _need(t, "attention " + w, torch.bfloat16)
     num_pages, _, page_size, _ = k_cache.shape
     st = _tc_state(q.device)
     _call("attention_tc", "ilb_attention_prefill_tc", _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache),
           _ptr(positions), _ptr(cu_q), _ptr(block_table), _i(block_table.shape[1]), _i(page_size),
-          _i(num_pages), _i(window or 0), _f(scale), _i(q.shape[0]), _i(n_seqs), _i(n_tiles), _i(nq), _i(nkv),
+          _i(num_pages), _i(window or 0), _f(scale), _i(q.shape[0]), _i(n_seqs), _i(n_tiles), _i(row_blocks), _i(1 if skip_single else 0), _i(nq), _i(nkv),
           _i(d), _i(q.shape[1]), _i(out.shape[1]), _ptr(st.error), _stream(q))
 
 
@@ -517,10 +519,23 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
         attention_decode(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
                          step.n_seqs, nq, nkv, d, decode_chunk, max_chunks, scratch, tickets)
     elif TC_ATTENTION_ENABLED and attention_tc_supported(nq, nkv, d, k_cache.shape[2]):
-        per_tile = 128 // G
-        n_tiles = sum(-(-n // per_tile) for n in step.h_q_len)
+        # A mixed step: the sequences that bring one token go to the split-KV decode kernel
+        # (it leaves the others alone), the portions to the prefill kernel (which leaves those).
+        lens = step.h_q_len
+        split = (MIXED_SPLIT_ENABLED and DECODE_CLUSTER_ENABLED and 1 in lens and max(lens) > 1
+                 and attention_decode_tma_supported(nq, nkv, d, k_cache.shape[2]))
+        if split:
+            attention_decode_tma(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
+                                 step.n_seqs, nq, nkv, d, False)
+            lens = [n for n in lens if n > 1]
+        # Two row blocks per CTA share the K and V tiles (faster per tile, half as many CTAs):
+        # taken when there are still enough CTAs for every SM.
+        per_block = 128 // G
+        n_two = sum(-(-n // (2 * per_block)) for n in lens)
+        blocks = TC_ATTENTION_ROW_BLOCKS or (2 if n_two * nkv >= _sm_count(q.device) else 1)
+        n_tiles = n_two if blocks == 2 else sum(-(-n // per_block) for n in lens)
         attention_prefill_tc(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
-                             step.n_seqs, n_tiles, nq, nkv, d)
+                             step.n_seqs, n_tiles, nq, nkv, d, blocks, skip_single=split)
     else:
         n_tiles = sum(-(-n * G // 64) for n in step.h_q_len)
         attention_prefill(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
@@ -531,3 +546,14 @@ DECODE_FUSED_ENABLED = True     # tests switch it off to run q/k norm + rotation
 DECODE_CLUSTER_ENABLED = True   # tests switch it off to reach the ticketed split-KV decode kernel
 FLASH_ENABLED = True       # tests switch it off to exercise the exact kernel in bfloat16
 TC_ATTENTION_ENABLED = True   # tests switch it off to reach the mma.sync prefill kernel at its geometries
+TC_ATTENTION_ROW_BLOCKS = 0   # tests set 1 or 2 to force the row blocks per CTA of the tcgen05 prefill kernel
+MIXED_SPLIT_ENABLED = True    # tests switch it off to send a mixed step's single tokens through the prefill kernel
+
+_SM_COUNT: dict = {}
+
+
+def _sm_count(device) -> int:
+    n = _SM_COUNT.get(device)
+    if n is None:
+        n = _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return n

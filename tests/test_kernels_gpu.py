@@ -605,12 +605,17 @@ def test_gemm_tcgen05_swiglu_epilogue(M, I, K, max_ctas, out_dtype):
                                                          (16, 16, 64, 16, 0), (32, 8, 128, 64, 100), (2, 2, 128, 128, 0),
                                                          (64, 2, 64, 16, 300), (10, 2, 128, 16, 0), (40, 8, 128, 16, 0),
                                                          (6, 2, 64, 32, 0), (7, 1, 128, 16, 90), (9, 1, 64, 16, 0)])
-def test_tc_prefill_mixed_batch(nq, nkv, d, page_size, window):
+@pytest.mark.parametrize("row_blocks,split", [(1, True), (2, True), (0, False)])
+def test_tc_prefill_mixed_batch(nq, nkv, d, page_size, window, row_blocks, split, monkeypatch):
     """Whole prompts, a portion that starts mid-sequence, single tokens, a long prompt whose
     row tiles cross many key tiles; pages shuffled.  Groups of 5, 3, 7 and 9 heads do not
-    divide the 128 rows of a tile: its last rows then hold no query."""
+    divide the 128 rows of a tile: its last rows then hold no query.  With one block of 128
+    rows per CTA and with two that share the key and value tiles; the single tokens through
+    the decode kernel (as the dispatcher sends them) or through the prefill kernel too."""
     o = ops()
     assert o.attention_tc_supported(nq, nkv, d, page_size)
+    monkeypatch.setattr(o, "TC_ATTENTION_ROW_BLOCKS", row_blocks)
+    monkeypatch.setattr(o, "MIXED_SPLIT_ENABLED", split)
     torch.manual_seed(nq * 3 + d)
     lens, q_lens = [37, 390, 131, 700, 129], [37, 123, 1, 700, 2]
     seqs = [(torch.randn(n, nkv, d).to(torch.bfloat16).double(), torch.randn(n, nkv, d).to(torch.bfloat16).double()) for n in lens]
@@ -620,6 +625,8 @@ def test_tc_prefill_mixed_batch(nq, nkv, d, page_size, window):
     ref = torch.stack([ref_attention(q[t].double().view(nq, d), *seqs[seq_of[t]], positions[t], window).reshape(-1)
                        for t in range(len(positions))])
     close_flash(out, ref, max(float(v.abs().max()) for _, v in seqs), "tc prefill")
+    if row_blocks != 1:
+        return
     # the mma.sync kernel at the same geometry, for the record that both paths are alive
     o.TC_ATTENTION_ENABLED = False
     try:
