@@ -60,10 +60,12 @@ class PageGroup:
 
 
 class CacheManager:
-    def __init__(self, layer_needs: Sequence[CacheNeeds], page_size: int, num_pages: int,
+    def __init__(self, layer_needs: Sequence[CacheNeeds], page_size: int, num_pages,
                  max_requests: int, dtype: torch.dtype = torch.float32,
                  device: Optional[torch.device] = None,
                  run_order: Optional[Sequence[RunEntry]] = None) -> None:
+        """`num_pages`: one number for every page group, or one number per group in the
+        order of :meth:`group_needs` (a group that reads a window needs fewer)."""
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.page_size = int(page_size)
@@ -91,7 +93,13 @@ class CacheManager:
             self._group_of_layer[layer] = gi
             self._index_in_group[layer] = len(found[gi][1])
             found[gi][1].append(layer)
-        if found and num_pages <= 0:
+        if isinstance(num_pages, (list, tuple)):
+            if len(num_pages) != len(found):
+                raise ValueError(f"{len(num_pages)} pool sizes for {len(found)} page groups")
+            pages_of = [int(n) for n in num_pages]
+        else:
+            pages_of = [int(num_pages)] * len(found)
+        if any(n <= 0 for n in pages_of):
             raise ValueError("a page pool needs at least one page")
         if max_requests <= 0:
             raise ValueError("a slot pool needs at least one slot")
@@ -99,17 +107,18 @@ class CacheManager:
         self._ids = OwnerIds()
         windows = (ctypes.c_int * max(1, len(found)))(*[(-1 if n.window is None else int(n.window)) for n, _ in found])
         h = ctypes.c_void_p()
-        rc = self._lib.ilb_ledger_new(len(found), windows, int(num_pages), self.page_size, int(max_requests), ctypes.byref(h))
+        sizes = (ctypes.c_int * max(1, len(found)))(*pages_of)
+        rc = self._lib.ilb_ledger_new(len(found), windows, sizes, self.page_size, int(max_requests), ctypes.byref(h))
         if rc:
             raise_for(rc)
         self._h = h
         for gi, (need, layers) in enumerate(found):
-            pool = PagePool(num_pages, _handle=self._lib.ilb_ledger_pool(self._h, gi), _ids=self._ids)
+            pool = PagePool(pages_of[gi], _handle=self._lib.ilb_ledger_pool(self._h, gi), _ids=self._ids)
             self.groups.append(PageGroup(gi, need, layers, pool, self.page_size))
         if device is not None:
             for g in self.groups:
                 g.storage = torch.zeros(
-                    (len(g.layers), 2, num_pages, g.need.kv_heads, self.page_size, g.need.head_dim),
+                    (len(g.layers), 2, g.pool.num_pages, g.need.kv_heads, self.page_size, g.need.head_dim),
                     dtype=dtype, device=device)
         # fixed-size state
         self.slots = SlotPool(max_requests, _handle=self._lib.ilb_ledger_slots(self._h), _ids=self._ids)
@@ -130,6 +139,25 @@ class CacheManager:
         if h is not None and h.value:
             self._lib.ilb_ledger_free(h)
             self._h = None
+
+    @staticmethod
+    def group_needs(layer_needs: Sequence[CacheNeeds], run_order: Optional[Sequence[RunEntry]] = None) -> List[Tuple[PagedKVNeed, List[int]]]:
+        """The page groups a model gets, in group order: (need, layers of the group).  For
+        callers that size every pool by itself before the manager exists."""
+        needs = list(layer_needs)
+        order = list(run_order) if run_order is not None else [RunEntry(i, i) for i in range(len(needs))]
+        found: List[Tuple[PagedKVNeed, List[int]]] = []
+        for layer in sorted({e.cache_of for e in order}):
+            need = needs[layer].paged
+            if need is None:
+                continue
+            for n, layers in found:
+                if n == need:
+                    layers.append(layer)
+                    break
+            else:
+                found.append((need, [layer]))
+        return found
 
     @property
     def stats(self) -> Dict[str, int]:

@@ -88,6 +88,14 @@ class ModelSpec:
     # Prefixes tried in order for every prefix-relative name; the first one under which
     # `embedding_name` exists is used (crates/model/package/src/storage/package.rs:231-237).
     weight_prefixes: Tuple[str, ...] = ("",)
+    # What some architectures put around the layers: a multiplier on the embedding rows, and
+    # a part of role "logits" that maps the logits in place (a soft cap, a scale).
+    embedding_scale: Optional[float] = None
+    logits_post: Optional[PartSpec] = None
+    # Integer inputs per token beside its id and position (name, width): a position encoding
+    # with several axes, say.  Steps carry them (StepEntry.extras); parts read
+    # step.extras[name] as an int32 [tokens, width] device tensor.
+    token_extras: Tuple[Tuple[str, int], ...] = ()
 
     def __post_init__(self) -> None:
         if not self.run_order:

@@ -271,6 +271,29 @@ ILB_EXPORT int ilb_add_inplace(float* x, const float* y, long long n, cudaStream
   return check_launch("add_inplace");
 }
 
+// ---------------------------------------------------------------- x *= s, and the soft cap c * tanh(x / c) (32-bit)
+// Two element-wise maps a model description may ask for: a multiplier on the embedding rows
+// and a cap on the logits.  cap = 0 means "scale only".
+__global__ void scale_cap_inplace_kernel(float* __restrict__ x, float scale, float cap, size_t n) {
+  ilb::pdl_launch_dependents();
+  ilb::pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float v = x[i] * scale;
+    if (cap > 0.f) v = cap * tanhf(v / cap);
+    x[i] = v;
+  }
+}
+
+ILB_EXPORT int ilb_scale_cap_inplace(float* x, float scale, float cap, long long n, cudaStream_t stream) {
+  ILB_REQUIRE(n >= 0 && cap >= 0.f, "scale_cap_inplace: bad arguments");
+  if (n == 0) return 0;
+  const int threads = 256;
+  long long blocks = (n + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  ilb::launch(scale_cap_inplace_kernel, dim3((int)blocks), dim3(threads), 0, stream, x, scale, cap, (size_t)n);
+  return check_launch("scale_cap_inplace");
+}
+
 // ---------------------------------------------------------------- decode feedback
 // After a decode step drew one token per sequence: make the next step's inputs on the
 // device (token <- drawn id, position and cache length advance by one), so that a run of

@@ -150,6 +150,12 @@ def add_inplace(x: torch.Tensor, y: torch.Tensor) -> None:
     _call("elementwise", "ilb_add_inplace", _ptr(x), _ptr(y), ctypes.c_longlong(x.numel()), _stream(x))
 
 
+def scale_cap_inplace(x: torch.Tensor, scale: float = 1.0, cap: float = 0.0) -> None:
+    """x = x * scale, then (cap > 0) x = cap * tanh(x / cap); x is 32-bit."""
+    _need(x, "scale_cap x", torch.float32)
+    _call("elementwise", "ilb_scale_cap_inplace", _ptr(x), _f(scale), _f(cap), ctypes.c_longlong(x.numel()), _stream(x))
+
+
 def decode_advance(tokens: torch.Tensor, positions: torch.Tensor, kv_len: torch.Tensor,
                    drawn: torch.Tensor, n_live: int) -> None:
     """tokens[:n_live] = drawn[:n_live]; positions and kv_len of those advance by one."""

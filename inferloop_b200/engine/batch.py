@@ -22,6 +22,9 @@ class StepEntry:
     request: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()      # indices into `tokens` whose logits are wanted
+    # integer inputs per token that the model's description declares (`ModelSpec.token_extras`):
+    # name -> len(tokens) * width values, token by token
+    extras: Optional[dict] = None
 
 
 @dataclass
@@ -55,6 +58,7 @@ class StepContext:
     slots: torch.Tensor            # [S] state slot of each sequence
     logit_rows: torch.Tensor       # [R] token rows whose logits are wanted
     block_tables: Dict[int, torch.Tensor]   # group -> [S, max_blocks]
+    extras: Dict[str, torch.Tensor] = field(default_factory=dict)   # declared per-token inputs: name -> [T, width]
     # host copies, for planning launches and for parts written in Python
     requests: List[Hashable] = field(default_factory=list)
     h_q_start: List[int] = field(default_factory=list)     # first position of each sequence's tokens

@@ -113,7 +113,7 @@ class Engine:
 
     # ------------------------------------------------------------------ sizing
     def _pages_from_memory(self, dev, utilization: float, max_num_seqs: int,
-                           max_model_len: Optional[int], step_tokens: int) -> int:
+                           max_model_len: Optional[int], step_tokens: int):
         """budget = min(total * utilization - used, free - 1 GiB)
         (crates/service/cli/src/backend/cuda.rs:52-64), less what the largest step's
         activations, logits and kernel scratch take: that is computed from the model's own
@@ -125,21 +125,30 @@ class Engine:
         reserve = self.runner.model.scratch_bytes(int(step_tokens), max(max_num_seqs, 1))
         self.activation_reserve = reserve + reserve // 4 + (256 << 20)
         budget -= self.activation_reserve
-        per_page = sum(g.page_bytes(torch.empty((), dtype=self.runner.cache.dtype).element_size())
-                       for g in self.runner.cache.groups)
-        if per_page == 0:
+        groups = self.runner.cache.groups
+        if not groups:
             return 1
-        pages = int(max(budget, 0) // per_page)
+        element = torch.empty((), dtype=self.runner.cache.dtype).element_size()
         want = (max_model_len or self.runner.spec.max_positions)
-        cap = -(-want // self.block_size) * max(max_num_seqs, 1)   # no request set can use more
-        pages = min(pages, cap)
-        if pages < 1:
+        # Pages one request holds at full length, per group: every key, or (with a window) the
+        # window, the largest step's own tokens and a page of slack.  Every group gets room
+        # for the same number of such requests; no set of requests can use more than
+        # max_num_seqs of them.
+        per_request = [-(-(want if g.need.window is None else min(want, g.need.window + int(step_tokens) + self.block_size))
+                         // self.block_size) + (0 if g.need.window is None else 1) for g in groups]
+        bytes_per_request = sum(n * g.page_bytes(element) for n, g in zip(per_request, groups))
+        requests = min(max(budget, 0) / bytes_per_request, float(max(max_num_seqs, 1)))
+        pages = [int(requests * n) for n in per_request]
+        if min(pages) < 1:
             raise CapacityError("no device memory is left for the cache")
         return pages
 
     # ------------------------------------------------------------------ requests
     def submit(self, tokens: Sequence[int], sampling: Optional[SamplingParams] = None,
-               max_new_tokens: int = 16, request_id: Optional[Hashable] = None) -> Hashable:
+               max_new_tokens: int = 16, request_id: Optional[Hashable] = None,
+               extras: Optional[Mapping[str, Sequence[int]]] = None) -> Hashable:
+        """`extras`: for a model whose description declares per-token inputs beside ids and
+        positions (`ModelSpec.token_extras`), their values for the prompt's tokens."""
         params = (self.generation_defaults.base if sampling is None
                   else self.generation_defaults.with_stop_tokens(sampling))
         if request_id is None:
@@ -157,6 +166,11 @@ class Engine:
         if self.max_output_tokens is not None:
             max_new_tokens = min(max_new_tokens, int(self.max_output_tokens))
         req = Request(request_id, toks, params, int(max_new_tokens))
+        declared = getattr(getattr(self.runner, "spec", None), "token_extras", ()) or ()
+        if declared:
+            req.extras = {k: [int(x) for x in v] for k, v in (extras or {}).items()}
+            for name, width in declared:
+                req.extras_of(name, int(width), 0, 0)          # raises if the prompt's values are missing
         self.scheduler.add(req)
         self.requests[request_id] = req
         # finished requests stay readable (`result`) until taken (`take_completed`); beyond
@@ -228,7 +242,10 @@ class Engine:
             return None
         if self.step_log is not None:
             self.step_log.append(self._describe(plan.work, len(plan.preempted)))
-        entries = [StepEntry(w.request.id, w.tokens, [w.count - 1] if w.samples else []) for w in plan.work]
+        declared = getattr(getattr(self.runner, "spec", None), "token_extras", ()) or ()
+        entries = [StepEntry(w.request.id, w.tokens, [w.count - 1] if w.samples else [],
+                             {name: w.request.extras_of(name, int(width), w.start, w.count) for name, width in declared}
+                             if declared else None) for w in plan.work]
         sampling_work = [w for w in plan.work if w.samples]
         if (self.sampler is not None and sampling_work
                 and all(w.request.params.uses_plain_greedy() for w in sampling_work)):

@@ -13,6 +13,12 @@ sequences that hold no pages.
 A recorded graph also holds the addresses of the model's scratch buffers; when one of
 them has been reallocated since (a larger prompt step grew it), the graph is recorded
 again.
+
+A step is recorded in SEGMENTS.  A block is recorded only if it says that it reads the
+batch from device memory alone (`graph_safe`); a block that loops over host-side batch
+facts (a mixer with sequential state written in Python, say) runs kernel by kernel between
+two recorded segments, with the step's host-side facts refreshed.  A model whose blocks are
+all safe is one segment, and only such a model has its next step launched ahead.
 """
 from __future__ import annotations
 
@@ -38,7 +44,7 @@ def bucket_for(n: int) -> Optional[int]:
 
 @dataclass
 class _Recorded:
-    graph: torch.cuda.CUDAGraph
+    segments: List[tuple]              # ("graph", CUDAGraph) | ("entries", first, last) run kernel by kernel
     ints: torch.Tensor                 # the batch arrays, fixed address
     ctx: StepContext                   # views into `ints`
     logits: torch.Tensor
@@ -50,6 +56,17 @@ class _Recorded:
     def drawn(self) -> Optional[torch.Tensor]:
         return None if self.pair is None else self.pair[0]
 
+    @property
+    def whole(self) -> bool:
+        """One recorded graph holds the whole step."""
+        return len(self.segments) == 1 and self.segments[0][0] == "graph"
+
+    @property
+    def graph(self) -> torch.cuda.CUDAGraph:
+        if not self.whole:
+            raise RuntimeError("this step is recorded in several segments")
+        return self.segments[0][1]
+
 
 class DecodeGraphs:
     def __init__(self, runner, max_blocks: int) -> None:
@@ -57,6 +74,20 @@ class DecodeGraphs:
         self.max_blocks = int(max_blocks)
         self._recorded: Dict[tuple, _Recorded] = {}
         self.replays = 0
+        # run-order entries in maximal runs of blocks that may / may not be recorded
+        model = runner.model
+        self.plan: List[tuple] = []          # (recorded?, first entry, last entry)
+        order = runner.spec.run_order
+        i = 0
+        while i < len(order):
+            safe = bool(model.blocks[order[i].layer].graph_safe)
+            j = i
+            while j < len(order) and bool(model.blocks[order[j].layer].graph_safe) == safe:
+                j += 1
+            self.plan.append((safe, i, j))
+            i = j
+        self.head_safe = bool(model.graph_safe)
+        self.whole = self.head_safe and all(safe for safe, _, _ in self.plan)
 
     @property
     def runner(self):
@@ -83,13 +114,14 @@ class DecodeGraphs:
     def _shapes(self, bucket: int) -> List[tuple]:
         groups = len(self.runner.cache.groups)
         return [(bucket,), (bucket,), (bucket,), (bucket + 1,), (bucket,), (bucket,), (bucket,)] + \
-               [(bucket, self.max_blocks)] * groups
+               [(bucket, self.max_blocks)] * groups + [(bucket, int(w)) for _, w in self.runner.spec.token_extras]
 
     def _prepare(self, entries: Sequence[StepEntry], bucket: int, ints: torch.Tensor) -> StepContext:
         from .runner import prepare_step
         r = self.runner
         return prepare_step(r.cache, r.stager, entries, r.spec.vocab_size, r.spec.max_positions,
-                            pad_seqs=bucket - len(entries), max_blocks=self.max_blocks, dest=ints)
+                            pad_seqs=bucket - len(entries), max_blocks=self.max_blocks, dest=ints,
+                            token_extras=r.spec.token_extras)
 
     def _record(self, key: tuple, entries: Sequence[StepEntry], bucket: int, with_argmax: bool) -> _Recorded:
         r = self.runner
@@ -102,26 +134,63 @@ class DecodeGraphs:
             ops.argmax(logits, pair[0], pair[1])
         torch.cuda.current_stream(r.device).synchronize()
         generation = r.ctx.workspace.generation
-        graph = torch.cuda.CUDAGraph()
         before = ops.LAUNCHES
         ctx.position_tables.clear()
-        # Nothing may be destroyed on the device while the recording is open: an older
+        # The step as pieces: embedding with the first run of blocks if that run is recorded,
+        # the last run with the head if both are, eager runs in between.
+        model, cache = r.model, r.cache
+        pieces: List[tuple] = []               # (recorded?, [callables])
+        hidden_of: Dict[str, torch.Tensor] = {}
+
+        def embed():
+            hidden_of["h"] = model.forward_embed(ctx)
+
+        def entries(first, last):
+            return lambda: model.forward_entries(hidden_of["h"], ctx, cache, first, last)
+
+        def head():
+            out = model.forward_head(hidden_of["h"], ctx)
+            if with_argmax:
+                ops.argmax(out, pair[0], pair[1])
+            hidden_of["logits"] = out
+
+        pieces.append((True, [embed]))
+        for safe, first, last in self.plan:
+            if safe and pieces[-1][0]:
+                pieces[-1][1].append(entries(first, last))
+            else:
+                pieces.append((safe, [entries(first, last)] if safe else [("entries", first, last)]))
+        if self.head_safe and pieces[-1][0]:
+            pieces[-1][1].append(head)
+        else:
+            pieces.append((self.head_safe, [head] if self.head_safe else [("head",)]))
+        segments: List[tuple] = []
+        # Nothing may be destroyed on the device while a recording is open: an older
         # graph released by the garbage collector in that window invalidates it.
         gc.collect()
         gc_was_on = gc.isenabled()
         gc.disable()
         try:
-            with torch.cuda.graph(graph):
-                logits = r.model.forward(ctx, r.cache)
-                if with_argmax:
-                    ops.argmax(logits, pair[0], pair[1])
+            for recorded, calls in pieces:
+                if recorded:
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        for call in calls:
+                            call()
+                    segments.append(("graph", graph))
+                else:
+                    # not recorded: nothing runs now (the eager pass above has done this step's
+                    # work exactly once); it runs kernel by kernel at every replay
+                    segments.extend(calls)
         finally:
             if gc_was_on:
                 gc.enable()
+        if "logits" in hidden_of:
+            logits = hidden_of["logits"]          # (else the head is not recorded: the eager pass's buffer, same address)
         kernels = ops.LAUNCHES - before
         if r.ctx.workspace.generation != generation:
             raise RuntimeError("a scratch buffer was reallocated while a graph was recorded")
-        rec = _Recorded(graph, ints, ctx, logits, generation, kernels, pair)
+        rec = _Recorded(segments, ints, ctx, logits, generation, kernels, pair)
         self._recorded[key] = rec
         return rec
 
@@ -134,6 +203,9 @@ class DecodeGraphs:
         r = self.runner
         cache = r.cache
         n = len(entries)
+        if r.spec.token_extras:               # the library's fast path packs ids and positions only
+            self._prepare(entries, bucket, rec.ints)
+            return
         try:
             req = (ctypes.c_longlong * n)(*[cache.id_of(e.request) for e in entries])
             tok = (ctypes.c_int * n)(*[int(e.tokens[0]) for e in entries])
@@ -166,11 +238,33 @@ class DecodeGraphs:
             rec = None
         if rec is None:
             rec = self._record(key, entries, bucket, with_argmax)     # ran the step eagerly
-        else:
+        elif rec.whole:
             self._prepare_replay(entries, bucket, rec)
             rec.graph.replay()
             self.replays += 1
+        else:
+            self._replay_segments(entries, bucket, rec, with_argmax)
         return rec.logits[:n], (Drawn(rec.pair, n) if with_argmax else None), rec.kernels
+
+    def _replay_segments(self, entries: Sequence[StepEntry], bucket: int, rec: "_Recorded", with_argmax: bool) -> None:
+        """A step recorded in several segments: the recorded ones are replayed, the others run
+        kernel by kernel with this step's host-side facts (the device arrays are the ones the
+        recorded segments read)."""
+        r = self.runner
+        ctx = self._prepare(entries, bucket, rec.ints)
+        hidden = r.ctx.workspace.buffer("model.hidden", (ctx.n_tokens, r.spec.hidden_size), torch.float32)
+        for seg in rec.segments:
+            if seg[0] == "graph":
+                seg[1].replay()
+            elif seg[0] == "entries":
+                r.model.forward_entries(hidden, ctx, r.cache, seg[1], seg[2])
+            else:
+                logits = r.model.forward_head(hidden, ctx)
+                if with_argmax:
+                    ops.argmax(logits, rec.pair[0], rec.pair[1])
+        if r.ctx.workspace.generation != rec.workspace_generation:
+            raise RuntimeError("a scratch buffer was reallocated by a part that runs between recorded segments")
+        self.replays += 1
 
     def step_ahead(self, entries: Sequence[StepEntry], previous_drawn: Drawn) -> Optional[Drawn]:
         """The decode step that follows one whose tokens are still being computed: the same
@@ -184,8 +278,10 @@ class DecodeGraphs:
         bucket = bucket_for(n)
         if bucket is None:
             return None
+        if self.runner.spec.token_extras:     # the next step's extra inputs are the caller's to give
+            return None
         rec = self._recorded.get(self._key(entries, bucket, True))
-        if rec is None or rec.workspace_generation != self.runner.ctx.workspace.generation:
+        if rec is None or not rec.whole or rec.workspace_generation != self.runner.ctx.workspace.generation:
             return None
         try:
             self._prepare_replay(entries, bucket, rec)
@@ -214,6 +310,9 @@ class DecodeGraphs:
         n = len(entries)
         if not self.eligible(entries):
             raise ValueError("run_greedy takes one token per request, logits wanted")
+        if not self.whole or r.spec.token_extras:
+            raise ValueError("run_greedy needs a model whose whole step is recorded as one graph and that "
+                             "takes no inputs per token beside ids and positions")
         bucket = bucket_for(n)
         if bucket is None:
             raise ValueError(f"{n} sequences exceed the largest decode bucket")

@@ -107,13 +107,16 @@ def step_fits(cache: CacheManager, entries: Sequence[StepEntry]) -> bool:
 
 def prepare_step(cache: CacheManager, stager: StepStager, entries: Sequence[StepEntry],
                  vocab_size: int, max_positions: int, pad_seqs: int = 0,
-                 max_blocks: Optional[int] = None, dest: Optional[torch.Tensor] = None) -> StepContext:
+                 max_blocks: Optional[int] = None, dest: Optional[torch.Tensor] = None,
+                 token_extras: Sequence = ()) -> StepContext:
     """Take pages for the step (all entries or none) and stage its arrays.
 
     `pad_seqs` appends that many one-token dummy sequences (token 0, position 0, no pages,
     slot -1): their cache writes are dropped and their rows are never read, which lets a
     step of any size run in a launch shape made for a larger one.  `max_blocks` fixes the
     width of the block tables; `dest` receives the arrays instead of the stager's buffer.
+    `token_extras` = ((name, width), ...): per-token integer inputs that every entry must
+    bring (`StepEntry.extras`); they travel in the same buffer, behind the block tables.
     Checking, page accounting and packing are the C++ host library's."""
     if not entries:
         raise ValueError("a step needs at least one entry")
@@ -123,6 +126,11 @@ def prepare_step(cache: CacheManager, stager: StepStager, entries: Sequence[Step
         if e.request in seen:
             raise ValueError(f"request {e.request!r} appears twice in one step")
         seen.add(e.request)
+    for name, width in token_extras:
+        for e in entries:
+            got = None if e.extras is None else e.extras.get(name)
+            if got is None or len(got) != len(e.tokens) * int(width):
+                raise ValueError(f"request {e.request!r} must bring {len(e.tokens)} x {width} values of {name!r}")
     pk = _Packed(cache, entries)
     rc = lib.ilb_step_check(cache.handle, pk.n, pk.req, pk.n_tok, pk.ptr(pk.tok), pk.n_want, pk.ptr(pk.want),
                             int(vocab_size), int(max_positions))
@@ -153,7 +161,8 @@ def prepare_step(cache: CacheManager, stager: StepStager, entries: Sequence[Step
     elif need_blocks > max_blocks:
         raise ValueError(f"a request holds {need_blocks} blocks, the table is {max_blocks} wide")
     n_groups = len(cache.groups)
-    bound = StepStager.layout([(T,), (T,), (T,), (S + 1,), (S,), (S,), (R,)] + [(S, max_blocks)] * n_groups)
+    bound = StepStager.layout([(T,), (T,), (T,), (S + 1,), (S,), (S,), (R,)] + [(S, max_blocks)] * n_groups
+                              + [(T, int(w)) for _, w in token_extras])
     turn, hostbuf = stager.claim(bound)
     offsets = (ctypes.c_longlong * (7 + n_groups))()
     total = lib.ilb_step_build(cache.handle, pk.n, pk.req, pk.n_tok, pk.ptr(pk.tok), pk.n_want, pk.ptr(pk.want),
@@ -161,10 +170,22 @@ def prepare_step(cache: CacheManager, stager: StepStager, entries: Sequence[Step
                                ctypes.c_void_p(hostbuf.data_ptr()), hostbuf.numel(), offsets)
     if total < 0:
         _raise_step_error(int(total), entries)
-    dev = stager.send(turn, int(total), dest)
+    hv = hostbuf.numpy()
+    end, extra_at = int(total), {}
+    for name, width in token_extras:            # behind what the library packed: [T, width] each, dummy rows zero
+        width = int(width)
+        rows = hv[end:end + T * width]
+        rows[:] = 0
+        try:
+            rows[:int(pk.tok.size) * width] = np.fromiter((int(x) for e in entries for x in e.extras[name]), dtype=np.int64,
+                                                          count=int(pk.tok.size) * width).astype(np.int32)
+        except (TypeError, ValueError, OverflowError):
+            raise ValueError(f"values of {name!r} must be 32-bit integers") from None
+        extra_at[name] = (end, width)
+        end += (T * width + 3) // 4 * 4
+    dev = stager.send(turn, end, dest)
     view = lambda k, n, shape=None: (dev[offsets[k]:offsets[k] + n] if shape is None
                                      else dev[offsets[k]:offsets[k] + n].view(*shape))
-    hv = hostbuf.numpy()
     kv_len = hv[offsets[4]:offsets[4] + S]
     slots = hv[offsets[5]:offsets[5] + len(entries)]
     q_len = [len(e.tokens) for e in entries]
@@ -175,6 +196,7 @@ def prepare_step(cache: CacheManager, stager: StepStager, entries: Sequence[Step
         tokens=view(0, T), positions=view(1, T), seq_of_token=view(2, T), cu_q=view(3, S + 1),
         kv_len=view(4, S), slots=view(5, S), logit_rows=view(6, R),
         block_tables={g.index: view(7 + i, S * max_blocks, (S, max_blocks)) for i, g in enumerate(cache.groups)},
+        extras={name: dev[at:at + T * w].view(T, w) for name, (at, w) in extra_at.items()},
         requests=reqs, h_q_start=q_start, h_q_len=q_len, h_kv_len=h_kv,
         h_slots=[int(x) for x in slots], max_q_len=max(q_len), max_kv_len=max(h_kv),
         decode_only=all(n == 1 for n in q_len))
@@ -198,10 +220,11 @@ class ModelRunner:
         self.tokens_run = 0
         self.kernels_last_step = 0
         self.timer = DeviceTimer(device, "off")
-        # Decode-only steps replay recorded graphs when every part reads its batch from
-        # device memory (a part that loops over host-side batch facts cannot be replayed).
+        # Decode-only steps replay recorded graphs: whole, when every part reads its batch from
+        # device memory; in segments around the blocks that do not (they loop over host-side
+        # batch facts and run kernel by kernel), when at least one block does.
         self.graphs = None
-        if cuda_graphs and all(b.graph_safe for b in self.model.blocks):
+        if cuda_graphs and any(b.graph_safe for b in self.model.blocks):
             from .graphs import DecodeGraphs
             self.graphs = DecodeGraphs(self, -(-spec.max_positions // page_size))
 
@@ -236,8 +259,9 @@ class ModelRunner:
         tensors = random_weights(decls, seed, dt, dev)
         return cls(spec, tensors, dt, dev, page_size, num_pages, max_requests)
 
-    def resize_cache(self, num_pages: int, max_requests: int) -> None:
-        """Replace the cache by one of another size; only while no request is live."""
+    def resize_cache(self, num_pages, max_requests: int) -> None:
+        """Replace the cache by one of another size (`num_pages`: one number, or one per page
+        group); only while no request is live."""
         if self.cache.live_requests():
             raise RuntimeError("the cache cannot be resized while requests are live")
         page_size = self.cache.page_size
@@ -297,7 +321,8 @@ class ModelRunner:
     # ------------------------------------------------------------------ the step
     def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
         """Take pages for the step (all entries or none) and stage its arrays."""
-        return prepare_step(self.cache, self.stager, entries, self.spec.vocab_size, self.spec.max_positions)
+        return prepare_step(self.cache, self.stager, entries, self.spec.vocab_size, self.spec.max_positions,
+                            token_extras=self.spec.token_extras)
 
     def step(self, entries: Sequence[StepEntry], draw_greedy: bool = False):
         """Run the entries as one batch; returns logits [wanted, vocab] (32-bit, on the

@@ -69,6 +69,25 @@ class Request:
     status: str = WAITING
     finish_reason: Optional[str] = None
     preemptions: int = 0
+    # per-token integer inputs the model's description declares (name -> values of the prompt's
+    # tokens, token by token); a generated token continues them: every value of the last
+    # prompt token plus the token's index among the generated ones plus one (what position-like
+    # inputs do when text continues)
+    extras: Optional[Dict[str, List[int]]] = None
+
+    def extras_of(self, name: str, width: int, start: int, count: int) -> List[int]:
+        """Values of `name` for tokens start .. start + count - 1 of the sequence."""
+        values = (self.extras or {}).get(name)
+        n = len(self.prompt)
+        if values is None or len(values) != n * width:
+            raise ValueError(f"request {self.id!r} has no {n} x {width} values of {name!r}")
+        out: List[int] = []
+        for t in range(start, start + count):
+            if t < n:
+                out += values[t * width:(t + 1) * width]
+            else:
+                out += [v + (t - n + 1) for v in values[(n - 1) * width:n * width]]
+        return out
 
     @property
     def sequence(self) -> List[int]:

@@ -136,7 +136,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ilb_slots_slot_of": (c_int, [c_vp, c_ll]),
         "ilb_slots_num_free": (c_int, [c_vp]),
         "ilb_slots_check": (c_int, [c_vp]),
-        "ilb_ledger_new": (c_int, [c_int, ip, c_int, c_int, c_int, ctypes.POINTER(c_vp)]),
+        "ilb_ledger_new": (c_int, [c_int, ip, ip, c_int, c_int, ctypes.POINTER(c_vp)]),
         "ilb_ledger_free": (None, [c_vp]),
         "ilb_ledger_begin": (c_int, [c_vp, c_ll]),
         "ilb_ledger_has": (c_int, [c_vp, c_ll]),

@@ -460,10 +460,12 @@ struct Ledger {
   std::unordered_map<long long, long long> length;
   long long begun = 0, released = 0, window_pages_released = 0;
 
-  Ledger(int n_groups, const int* windows, int num_pages, int page_size_, int max_requests)
+  // Every group has a pool of its own size: a group whose layers read a window of the keys
+  // needs fewer pages than one that keeps them all.
+  Ledger(int n_groups, const int* windows, const int* num_pages, int page_size_, int max_requests)
       : page_size(page_size_), slots(max_requests) {
     groups.reserve((size_t)n_groups);
-    for (int g = 0; g < n_groups; ++g) groups.emplace_back(windows[g], num_pages);
+    for (int g = 0; g < n_groups; ++g) groups.emplace_back(windows[g], num_pages[g]);
   }
   long long blocks_for(long long tokens) const { return (tokens + page_size - 1) / page_size; }
   // Blocks below this index hold only keys that no present or future token reads.
@@ -658,10 +660,13 @@ ILB_API int ilb_slots_num_free(void* h) { return (int)static_cast<Slots*>(h)->fr
 ILB_API int ilb_slots_check(void* h) { return static_cast<Slots*>(h)->check(); }
 
 // ------------------------------------------------------------------ ledger, C interface
-ILB_API int ilb_ledger_new(int n_groups, const int* windows, int num_pages, int page_size, int max_requests, void** out) {
+// num_pages: one entry per group.
+ILB_API int ilb_ledger_new(int n_groups, const int* windows, const int* num_pages, int page_size, int max_requests, void** out) {
   *out = nullptr;
   if (page_size <= 0) return fail(kInvalid, "page_size must be positive");
-  if (n_groups < 0 || (n_groups > 0 && num_pages <= 0)) return fail(kInvalid, "a page pool needs at least one page");
+  if (n_groups < 0) return fail(kInvalid, "a negative number of page groups");
+  for (int g = 0; g < n_groups; ++g)
+    if (num_pages[g] <= 0) return fail(kInvalid, "a page pool needs at least one page");
   if (max_requests <= 0) return fail(kInvalid, "a slot pool needs at least one slot");
   *out = new Ledger(n_groups, windows, num_pages, page_size, max_requests);
   return kOk;

@@ -27,8 +27,10 @@ class DecoderModel:
         self.blocks = [registry.build_block(layer, ctx, layer.prefix) for layer in spec.layers]
         self.final_norm = registry.build_norm(
             spec.final_norm, ctx, _strip_weight(spec.final_norm_name), width=spec.hidden_size)
+        self.logits_post = (registry.build("logits", spec.logits_post, ctx) if spec.logits_post is not None else None)
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
+        self._weight_bytes = 0
 
     # ------------------------------------------------------------------ weights
     def declare_weights(self) -> List[WeightDecl]:
@@ -52,22 +54,24 @@ class DecoderModel:
             b.bind(tensors)
         self.final_norm.bind(tensors)
         self.head = self.embedding if s.head_name is None else tensors[s.head_name].contiguous()
+        # Every declared tensor is read once by a step, except the token table, of which a step
+        # reads one row per token (unless it is also the output matrix).
+        self._weight_bytes = sum(tensors[d.name].numel() * tensors[d.name].element_size() for d in self.declare_weights()
+                                 if d.name != s.embedding_name or s.head_name is None)
 
     def cache_needs(self) -> List[CacheNeeds]:
         return [b.cache_needs() for b in self.blocks]
 
     def weight_bytes(self) -> int:
-        """Bytes of every weight one step reads once (the table is read by row only)."""
-        seen, total = set(), 0
-        for b in self.blocks:
-            for part in (b,) + tuple(getattr(b, n) for n in ("norm1", "mixer", "norm2", "ffn") if hasattr(b, n)):
-                for v in vars(part).values():
-                    if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
-                        seen.add(v.data_ptr())
-                        total += v.numel() * v.element_size()
-        if self.head is not None:
-            total += self.head.numel() * self.head.element_size()
-        return total
+        """Bytes of every weight one step reads once: the tensors the parts declared, as they
+        were bound (the token table is read by row only, unless it is the output matrix too)."""
+        return self._weight_bytes
+
+    @property
+    def graph_safe(self) -> bool:
+        """Whether embedding, final norm, output matrix and the logits map read the batch from
+        device memory alone (the blocks answer for themselves)."""
+        return self.final_norm.graph_safe and (self.logits_post is None or self.logits_post.graph_safe)
 
     def scratch_bytes(self, tokens: int, logit_rows: int) -> int:
         """Workspace a step of `tokens` tokens with `logit_rows` wanted rows asks for: the
@@ -83,13 +87,27 @@ class DecoderModel:
     def forward(self, step, caches) -> torch.Tensor:
         """Run the step's tokens through every run-order entry; returns 32-bit logits
         [len(step.logit_rows), vocab] (a workspace buffer, valid until the next step)."""
+        hidden = self.forward_embed(step)
+        self.forward_entries(hidden, step, caches, 0, len(self.spec.run_order))
+        return self.forward_head(hidden, step)
+
+    # The three pieces of `forward`, for a caller that runs (or records) a step in segments.
+    def forward_embed(self, step) -> torch.Tensor:
         s, ws = self.spec, self.ctx.workspace
-        T = step.n_tokens
-        hidden = ws.buffer("model.hidden", (T, s.hidden_size), torch.float32)
+        hidden = ws.buffer("model.hidden", (step.n_tokens, s.hidden_size), torch.float32)
         ops.scope("embedding")
         ops.embed(step.tokens, self.embedding, hidden)
-        for entry in s.run_order:
+        if s.embedding_scale is not None and s.embedding_scale != 1.0:
+            ops.scale_cap_inplace(hidden, float(s.embedding_scale), 0.0)
+        return hidden
+
+    def forward_entries(self, hidden: torch.Tensor, step, caches, first: int, last: int) -> None:
+        """Run-order entries first .. last - 1."""
+        for entry in self.spec.run_order[first:last]:
             self.blocks[entry.layer].forward(hidden, step, caches.layer_cache(entry))
+
+    def forward_head(self, hidden: torch.Tensor, step) -> torch.Tensor:
+        s, ws = self.spec, self.ctx.workspace
         ops.scope("head.rows_norm")
         R = step.n_logit_rows
         if R == 0:
@@ -101,6 +119,9 @@ class DecoderModel:
         logits = ws.buffer("model.logits", (R, s.vocab_size), torch.float32)
         ops.scope("head.output_matrix")
         linear(normed, self.head, logits)
+        if self.logits_post is not None:
+            ops.scope("head.logits_map")
+            self.logits_post.forward(logits)
         ops.scope("other")
         return logits
 

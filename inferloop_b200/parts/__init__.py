@@ -1,9 +1,9 @@
-from .base import (Block, BuildContext, CacheNeeds, FeedForward, Mixer, Norm, PagedKVNeed, Part,
+from .base import (Block, BuildContext, CacheNeeds, FeedForward, LogitsPost, Mixer, Norm, PagedKVNeed, Part,
                    PositionEncoding, SlotStateNeed, Workspace)
 from .registry import build, build_block, build_norm, kinds, register, unregister
 
 __all__ = [
-    "Block", "BuildContext", "CacheNeeds", "FeedForward", "Mixer", "Norm", "PagedKVNeed", "Part",
+    "Block", "BuildContext", "CacheNeeds", "FeedForward", "LogitsPost", "Mixer", "Norm", "PagedKVNeed", "Part",
     "PositionEncoding", "SlotStateNeed", "Workspace", "build", "build_block", "build_norm",
     "kinds", "register", "unregister",
 ]

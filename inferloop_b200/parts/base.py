@@ -11,6 +11,7 @@ model-specific reaches it through its spec.
   Mixer             cache_needs(); forward(x, residual, step, cache)    residual += mix(x)
   FeedForward       forward(x, residual, step)                           residual += ffn(x)
   Block             cache_needs(); forward(hidden, step, cache)          hidden updated in place
+  LogitsPost        forward(logits)                                      logits mapped in place
 
 `hidden` / `residual` is the 32-bit residual stream [tokens, hidden]; `x` is a normed
 copy in the compute dtype.  `step` is the :class:`~inferloop_b200.engine.batch.StepContext`
@@ -151,4 +152,11 @@ class FeedForward(Part):
 
 class Block(Part):
     def forward(self, hidden: torch.Tensor, step, cache) -> None:
+        raise NotImplementedError
+
+
+class LogitsPost(Part):
+    """Maps the 32-bit logits [rows, vocab] in place, after the output matrix."""
+
+    def forward(self, logits: torch.Tensor) -> None:
         raise NotImplementedError

@@ -6,7 +6,7 @@ from typing import Callable, Dict, Type
 from ..config.spec import PartSpec
 from .base import BuildContext, Part
 
-ROLES = ("norm", "position", "mixer", "feed_forward", "block")
+ROLES = ("norm", "position", "mixer", "feed_forward", "block", "logits")
 _REGISTRY: Dict[str, Dict[str, Type[Part]]] = {r: {} for r in ROLES}
 
 
@@ -65,4 +65,4 @@ def _ensure_builtin() -> None:
     if _BUILTIN_DONE:
         return
     _BUILTIN_DONE = True
-    from . import attention, block, mlp, norm, rope  # noqa: F401  (they register themselves)
+    from . import attention, block, logits, mlp, norm, rope  # noqa: F401  (they register themselves)

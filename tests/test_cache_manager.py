@@ -99,6 +99,34 @@ def test_groups_by_need_and_window_release():
     assert m.free_pages() == {0: 8, 1: 8}
 
 
+def test_every_group_has_a_pool_of_its_own_size():
+    """A group that reads a window can be given fewer pages than the group that keeps every
+    key: a long request then fits although the small pool never holds more than the window."""
+    needs = [FULL, WIN, FULL, WIN]
+    assert [(n.window, layers) for n, layers in CacheManager.group_needs(needs)] == [(None, [0, 2]), (10, [1, 3])]
+    m = CacheManager(needs, page_size=4, num_pages=[16, 5], max_requests=2)
+    assert [g.pool.num_pages for g in m.groups] == [16, 5] and m.free_pages() == {0: 16, 1: 5}
+    m.begin("a")
+    for n in range(1, 61):                       # one token at a time: 15 pages of the full group in the end
+        m.ensure("a", n); m.commit("a", n)
+        m.check()
+    assert m.free_pages()[0] == 1 and m.free_pages()[1] >= 1
+    m.begin("b")
+    with pytest.raises(OutOfPages):              # the full group is what runs out
+        m.ensure("b", 8)
+    m.release("a"); m.release("b")
+    assert m.free_pages() == {0: 16, 1: 5}
+    with pytest.raises(ValueError, match="pool sizes"):
+        CacheManager(needs, page_size=4, num_pages=[16], max_requests=2)
+    with pytest.raises(ValueError, match="at least one page"):
+        CacheManager(needs, page_size=4, num_pages=[16, 0], max_requests=2)
+    # a whole prompt at once needs the window's pages beside the step's own
+    m = CacheManager(needs, page_size=4, num_pages=[16, 5], max_requests=2)
+    m.begin("c")
+    with pytest.raises(OutOfPages):
+        m.ensure("c", 40)                        # 10 pages of the window group in one step
+
+
 def test_borrowed_cache_allocates_nothing_and_slot_state_is_declared():
     needs = [CacheNeeds(paged=PagedKVNeed(1, 16, None)),
              CacheNeeds(paged=PagedKVNeed(4, 32, None)),

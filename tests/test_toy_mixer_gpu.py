@@ -140,5 +140,23 @@ def test_toy_mixer_registered_built_and_stepped(dtype):
             err = (torch.cat(got) - ref).abs()
             lim = 1e-5 + 1e-5 * ref.abs() if dtype == "float32" else torch.full_like(ref, 1e-2 * float(ref.abs().max()))
             assert (err <= lim).all(), (rid, err.max().item())
+        # Two requests decoding side by side, one token each per step: the attention layers
+        # around the toy mixer are replayed as recorded graph segments, the toy mixer (which
+        # loops over the batch on the host) runs kernel by kernel between them.
+        assert runner.graphs is not None and not runner.graphs.whole
+        assert [safe for safe, _, _ in runner.graphs.plan] == [True, False, True]
+        seqs = {"d": random_tokens(34, V, 8), "e": random_tokens(29, V, 9)}
+        refs = {rid: plain_toy(tensors, cfg, toks) for rid, toks in seqs.items()}
+        runner.step([StepEntry("d", seqs["d"][:14], []), StepEntry("e", seqs["e"][:9], [])])
+        before = runner.graphs.replays
+        for i in range(20):
+            out = runner.step([StepEntry("d", [seqs["d"][14 + i]], [0]), StepEntry("e", [seqs["e"][9 + i]], [0])]).double().cpu()
+            ref = torch.stack([refs["d"][14 + i], refs["e"][9 + i]])
+            err = (out - ref).abs()
+            lim = 1e-5 + 1e-5 * ref.abs() if dtype == "float32" else torch.full_like(ref, 1e-2 * float(ref.abs().max()))
+            assert (err <= lim).all(), (i, err.max().item())
+        assert runner.graphs.replays - before >= 18
+        rec = next(iter(runner.graphs._recorded.values()))
+        assert [seg[0] for seg in rec.segments] == ["graph", "entries", "graph"]
     finally:
         unregister("mixer", "decay_state")

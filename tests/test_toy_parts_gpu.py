@@ -182,3 +182,130 @@ def test_routed_feed_forward_and_another_position_encoding(dtype):
     finally:
         unregister("feed_forward", "routed_relu")
         unregister("position", "scaled_rope")
+
+
+# ------------------------------------------------------------------ what sits around the layers
+class TwoAxisRope(PositionEncoding):
+    """Rotary angles from TWO position axes per token (rows and columns of a grid, say): the
+    first half of the rotation pairs turns with axis 0, the second half with axis 1.  The
+    axes come as a declared per-token input, `pos2` [tokens, 2], not from the 1-D positions."""
+
+    def __init__(self, spec, ctx, prefix=""):
+        super().__init__(spec, ctx, prefix)
+        self.theta, self.rd = float(spec["theta"]), int(spec["rotary_dim"])
+
+    def table(self, step):
+        key = ("two_axis_rope", self.theta, self.rd)
+        t = step.position_tables.get(key)
+        if t is None:
+            half = self.rd // 2
+            inv = torch.tensor([self.theta ** (-(2.0 * i) / self.rd) for i in range(half)], dtype=torch.float64,
+                               device=step.positions.device)
+            axes = step.extras["pos2"].double()                        # [T, 2]
+            which = (torch.arange(half, device=axes.device) >= half // 2).long()
+            ang = axes[:, which] * inv[None, :]
+            t = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).float().contiguous()
+            step.position_tables[key] = t
+        return t
+
+
+EMBED_SCALE, LOGIT_CAP, LOGIT_SCALE = 1.75, 2.5, 3.0
+
+
+def toy3_spec(cfg):
+    norm = PartSpec.make("rms", eps=cfg["eps"])
+    pos = PartSpec.make("two_axis_rope", theta=1e4, rotary_dim=16, head_dim=16)
+    attn = PartSpec.make("gqa_attention", hidden_size=H, num_heads=3, num_kv_heads=3, head_dim=16, qk_norm=True,
+                         qk_norm_eps=cfg["eps"], bias=False, window=None, position=pos)
+    dense = PartSpec.make("swiglu", hidden_size=H, intermediate_size=64)
+    block = PartSpec.make("pre_norm", hidden_size=H)
+    layers = (LayerSpec("layers.0.", block, attn, dense, norm), LayerSpec("layers.1.", block, attn, dense, norm))
+    return ModelSpec("Toy3ForCausalLM", V, H, 512, "embed_tokens.weight", None, "norm.weight", norm, layers,
+                     weight_prefixes=("model.",), embedding_scale=EMBED_SCALE,
+                     logits_post=PartSpec.make("soft_cap", cap=LOGIT_CAP, scale=LOGIT_SCALE),
+                     token_extras=(("pos2", 2),))
+
+
+def plain_toy3(w, cfg, tokens, pos2):
+    T = len(tokens)
+    x = w["embed_tokens.weight"][torch.tensor(tokens)] * EMBED_SCALE
+    pos = torch.arange(T)
+    inv = torch.tensor([1e4 ** (-(2.0 * i) / 16) for i in range(8)], dtype=torch.float64)
+    axes = torch.tensor(pos2, dtype=torch.float64)
+    ang = axes[:, (torch.arange(8) >= 4).long()] * inv[None, :]             # [T, 8]
+
+    def rotate(v):                                                        # v [T, heads, 16], pairs (i, i + 8)
+        a, b = v[..., :8], v[..., 8:]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        return torch.cat([a * c - b * s, a * s + b * c], dim=-1)
+
+    for layer in range(2):
+        p = f"layers.{layer}."
+        a = p + "self_attn."
+        n = plain.rms_norm(x, w[p + "input_layernorm.weight"], cfg["eps"])
+        q = rotate(plain.rms_norm(plain.linear(n, w[a + "q_proj.weight"]).view(T, 3, 16), w[a + "q_norm.weight"], cfg["eps"]))
+        k = rotate(plain.rms_norm(plain.linear(n, w[a + "k_proj.weight"]).view(T, 3, 16), w[a + "k_norm.weight"], cfg["eps"]))
+        v = plain.linear(n, w[a + "v_proj.weight"]).view(T, 3, 16)
+        x = x + plain.linear(plain.causal_attention(q, k, v, pos, None).reshape(T, 48), w[a + "o_proj.weight"])
+        n = plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg["eps"])
+        x = x + plain.swiglu_mlp(n, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    logits = plain.linear(plain.rms_norm(x, w["norm.weight"], cfg["eps"]), w["embed_tokens.weight"])
+    return LOGIT_CAP * torch.tanh(logits * LOGIT_SCALE / LOGIT_CAP)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding_multiplier_logits_map_and_inputs_per_token(dtype):
+    """A description with a multiplier on the embedding rows, a soft cap on the logits (a part of
+    role "logits") and a position encoding that reads two axes per token from a declared
+    per-token input: portions, single tokens through recorded graphs, and the entry point
+    (which continues the axes for generated tokens), all against the plain statement."""
+    from inferloop_b200 import Engine, SamplingParams
+    from inferloop_b200.engine import ModelRunner, StepEntry
+    from inferloop_b200.models.decoder import declare_weights
+    from inferloop_b200.weights import random_tensor, target_dtype
+    register("position", "two_axis_rope", TwoAxisRope)
+    try:
+        registry = ArchitectureRegistry()
+        registry.register(Architecture("toy3", ("Toy3ForCausalLM",), dict, toy3_spec))
+        cfg = {"architectures": ["Toy3ForCausalLM"], "eps": 1e-6}
+        runner = ModelRunner.from_config(cfg, seed=13, dtype=dtype, page_size=8, num_pages=32, max_requests=3,
+                                         registry=registry)
+        DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+        w = {d.name: random_tensor(d, 13, target_dtype(d.role, DT), "cuda").double().cpu() for d in declare_weights(toy3_spec(cfg))}
+        toks = random_tokens(40, V, 21)
+        pos2 = [[t // 7, t % 7] for t in range(40)]                     # a grid seven wide, row by row
+        ref = plain_toy3(w, cfg, toks, pos2)
+        flat = lambda a, b: [x for row in pos2[a:b] for x in row]
+        got, i = [], 0
+        for cut in (9, 2, 12, 1, 1, 1, 14):                            # single tokens: recorded graphs
+            got.append(runner.step([StepEntry("a", toks[i:i + cut], list(range(cut)), {"pos2": flat(i, i + cut)})]).double().cpu().clone())
+            i += cut
+        runner.end("a")
+        assert runner.graphs is not None and runner.graphs.replays >= 2
+        g = torch.cat(got)
+        err = (g - ref).abs()
+        lim = 1e-5 + 1e-5 * ref.abs() if dtype == "float32" else torch.full_like(ref, 1e-2 * float(ref.abs().max()))
+        assert (err <= lim).all(), err.max().item()
+        assert float(g.abs().max()) <= LOGIT_CAP
+        with pytest.raises(ValueError, match="must bring"):
+            runner.step([StepEntry("b", toks[:3], [2])])
+        # through the entry point: generated tokens continue both axes by one each
+        engine = Engine(None, runner=runner, max_num_seqs=2, prefill_chunk_tokens=16)
+        prompt = toks[:11]
+        rid = engine.submit(prompt, SamplingParams(), 6, extras={"pos2": flat(0, 11)})
+        while not engine.is_idle():
+            engine.step()
+        out = engine.result(rid).generated
+        seq, axes = list(prompt), [list(r) for r in pos2[:11]]
+        for n in range(6):
+            axes.append([pos2[10][0] + n + 1, pos2[10][1] + n + 1])
+            logits = plain_toy3(w, cfg, seq + [out[n]], axes)[-2]
+            if dtype == "float32":
+                assert out[n] == int(logits.argmax())
+            else:
+                assert logits[out[n]] >= logits.max() - 2e-2 * float(logits.abs().max())
+            seq.append(out[n])
+        with pytest.raises(ValueError, match="values of 'pos2'"):
+            engine.submit(prompt, SamplingParams(), 2)
+    finally:
+        unregister("position", "two_axis_rope")
