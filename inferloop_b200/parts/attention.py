@@ -28,7 +28,11 @@ from .linear import linear
 
 
 class GQAttention(Mixer):
-    graph_safe = True
+    @property
+    def graph_safe(self) -> bool:
+        """The kernels read the batch from device memory; the position encoding answers for itself."""
+        return bool(self.position.graph_safe)
+
     def __init__(self, spec, ctx, prefix: str = "") -> None:
         super().__init__(spec, ctx, prefix)
         self.hidden = int(spec["hidden_size"])

@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
     return {name: make_model_folder(str(tmp_path_factory.mktemp("model") / name), CONFIGS[name][0], CONFIGS[name][1])
-            for name in ("B", "D", "F")}
+            for name in ("B", "D", "E", "F")}
 
 
 _PLAIN = {}
@@ -170,6 +170,25 @@ def test_default_cache_size_and_abort_with_a_step_in_flight(folders):
     assert e.result("a1").generated == want[1][:len(e.result("a1").generated)]
     info = e.inspect()
     assert info["running"] == 0 and all(g["free"] == g["total"] for g in info["cache"]["groups"])
+    e.runner.cache.check()
+
+
+def test_default_sizes_give_a_windowed_group_a_smaller_pool(folders):
+    """Layers that read a window of 40 keys share a page group whose pool the default sizing
+    makes as large as the window, the largest step and a page of slack need, not as large as
+    the pool of the layers that keep every key; generation is what the plain model generates."""
+    from inferloop_b200 import Engine, SamplingParams
+    cfg, _, page = CONFIGS["E"]
+    e = Engine(folders["E"], dtype="float32", block_size=page, max_num_seqs=4, max_model_len=1024, prefill_chunk_tokens=64)
+    groups = {g["window"]: g for g in e.inspect()["cache"]["groups"]}
+    assert groups[None]["total"] == (1024 // page) * 4
+    per_request = -(-(40 + (64 + 3) + page) // page) + 1
+    assert groups[40]["total"] == per_request * 4 < groups[None]["total"]
+    prompts = [random_tokens(n, cfg["vocab_size"], 1500 + n) for n in (150, 60, 33, 97)]
+    model = plain_model(folders, "E", "float32")
+    assert e.generate(prompts, SamplingParams(), 40) == [plain.generate(model, p, 40) for p in prompts]
+    info = e.inspect()
+    assert all(g["free"] == g["total"] for g in info["cache"]["groups"]) and info["cache"]["window_pages_released"] > 0
     e.runner.cache.check()
 
 

@@ -190,20 +190,23 @@ class TwoAxisRope(PositionEncoding):
     first half of the rotation pairs turns with axis 0, the second half with axis 1.  The
     axes come as a declared per-token input, `pos2` [tokens, 2], not from the 1-D positions."""
 
+    graph_safe = True        # device operations on device tensors only (its constants are made at construction)
+
     def __init__(self, spec, ctx, prefix=""):
         super().__init__(spec, ctx, prefix)
         self.theta, self.rd = float(spec["theta"]), int(spec["rotary_dim"])
+        half = self.rd // 2
+        if ctx.device is not None:
+            self.inv = torch.tensor([self.theta ** (-(2.0 * i) / self.rd) for i in range(half)], dtype=torch.float64,
+                                    device=ctx.device)
+            self.which = (torch.arange(half, device=ctx.device) >= half // 2).long()
 
     def table(self, step):
         key = ("two_axis_rope", self.theta, self.rd)
         t = step.position_tables.get(key)
         if t is None:
-            half = self.rd // 2
-            inv = torch.tensor([self.theta ** (-(2.0 * i) / self.rd) for i in range(half)], dtype=torch.float64,
-                               device=step.positions.device)
             axes = step.extras["pos2"].double()                        # [T, 2]
-            which = (torch.arange(half, device=axes.device) >= half // 2).long()
-            ang = axes[:, which] * inv[None, :]
+            ang = axes[:, self.which] * self.inv[None, :]
             t = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).float().contiguous()
             step.position_tables[key] = t
         return t
