@@ -380,9 +380,18 @@ def run_14b_mixed(args) -> dict:
     job()                                           # untimed: records the decode graphs, sizes every buffer
     before = engine.inspect()["scheduler"]
     ahead_before = engine.steps_launched_ahead
+    engine.runner.set_device_timing("graph")        # two events around every step: device time beside wall time
     with ClockSampler() as clocks:
         seconds, log = job()
     after = engine.inspect()["scheduler"]
+    torch.cuda.synchronize()
+    step_ms = [a.elapsed_time(b) for _, a, b in engine.runner.timer._steps]
+    engine.runner.set_device_timing("off")
+    kinds = {"mixed": [0, 0.0, 0], "decode_only": [0, 0.0, 0], "prompt_only": [0, 0.0, 0]}
+    if len(step_ms) == len(log):
+        for s, ms in zip(log, step_ms):
+            k = "decode_only" if s["single_token_seqs"] == s["seqs"] else "mixed" if s["single_token_seqs"] else "prompt_only"
+            kinds[k][0] += 1; kinds[k][1] += ms; kinds[k][2] += s["tokens"]
     nums, pk = bench.nums, bench.pk
     roof_s = 0.0
     for s in log:
@@ -409,6 +418,9 @@ def run_14b_mixed(args) -> dict:
                         "mean_seqs_per_step": round(sum(s["seqs"] for s in log) / steps, 1),
                         "preemptions": after["preemptions"] - before["preemptions"],
                         "steps_launched_ahead": engine.steps_launched_ahead - ahead_before},
+        "device_time": {"seconds_on_device": round(sum(step_ms) / 1e3, 4), "seconds_wall": round(seconds, 4),
+                        "by_step_kind": {k: {"steps": v[0], "ms_mean": round(v[1] / max(v[0], 1), 3), "tokens_mean": round(v[2] / max(v[0], 1), 1)}
+                                         for k, v in kinds.items()}},
         "roofline": {"bound": "per step: the slower of flops / bf16 peak and bytes / HBM", "seconds": round(roof_s, 4),
                      "frac": round(roof_s / seconds, 4), "peak_tflops": pk["bf16_tflops"], "peak_gbs": pk["hbm_gbs"]},
         "clocks": clocks.summary(),

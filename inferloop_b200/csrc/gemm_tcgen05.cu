@@ -987,18 +987,23 @@ int make_plan(Params& p, int M, int N, int K, int accumulate, int n_tickets, int
     // counting for more because they move fewer bytes per flop.
     // Few tiles are cut into equal K ranges; with one 128-row block per tile the ranges of a
     // tile run as a cluster that shares the write-out, with two they go through a ticket.
-    const struct { int ms, bn; double worth; } shapes[4] = {{2, 256, 1.0}, {2, 192, 0.93}, {1, 256, 0.85}, {1, 128, 0.7}};
+    // (160 columns: 32 column tiles for a width of 5120, where 256 and 192 leave a quarter of
+    // the SMs idle; its 32-bit write-out goes in 32-column pieces, the 16-bit one needs 64)
+    const struct { int ms, bn; double worth; } shapes[6] = {{2, 256, 1.0}, {2, 192, 0.93}, {2, 160, 0.9}, {1, 256, 0.85},
+                                                            {1, 160, 0.78}, {1, 128, 0.7}};
     const long long kb = (K + kBlockK - 1) / kBlockK;
     double best = -1.0;
     bn = 128;
     for (const auto& c : shapes) {
       if (c.bn > 128 && N < 256) continue;
       if (c.bn % 128 != 0 && accumulate == 2) continue;        // the SwiGLU epilogue pairs 64-column blocks
+      if (c.bn % 64 != 0 && !(p.out_f32 || accumulate == 1)) continue;   // 16-bit results leave in 64-column pieces
       const long long tm = (M + c.ms * kTileX - 1) / (c.ms * kTileX), tn = (N + c.bn - 1) / c.bn;
       const long long t = tm * tn;
       // the part of the tiles' area that holds real rows and columns
       const double filled = ((double)M / (double)(tm * c.ms * kTileX)) * ((double)N / (double)(tn * c.bn));
       double score;
+      if (c.bn == 160 && t * 2 <= sm_count()) continue;        // (few tiles are cut into K ranges whose CTAs share 32-column pieces of 128 or 256)
       if (t * 2 <= sm_count()) {
         long long split = 1;
         while (split < 8 && t * split * 2 <= sm_count() && split * 2 <= kb) split *= 2;
@@ -1137,6 +1142,8 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   }
   if (bn == 256 && ms == 2) return launch<256, 3, false, 2>(mx, my, mo, p, (int)grid, stream);
   if (bn == 192) return launch<192, 3, false, 2>(mx, my, mo, p, (int)grid, stream);
+  if (bn == 160 && ms == 2) return launch<160, 3, false, 2>(mx, my, mo, p, (int)grid, stream);
+  if (bn == 160) return launch<160, 5, false>(mx, my, mo, p, (int)grid, stream);
   if (bn == 256) return launch<256, 4, false>(mx, my, mo, p, (int)grid, stream);
   return launch<128, 6, false>(mx, my, mo, p, (int)grid, stream);
 }

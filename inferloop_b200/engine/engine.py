@@ -96,7 +96,8 @@ class Engine:
         cfg = SchedulerConfig(
             max_num_seqs=max_num_seqs,
             max_num_batched_tokens=max_num_batched_tokens or max(prefill_chunk_tokens + max_num_seqs - 1, 1),
-            prefill_chunk_tokens=prefill_chunk_tokens, max_model_len=self.max_model_len)
+            prefill_chunk_tokens=prefill_chunk_tokens, max_model_len=self.max_model_len,
+            step_token_multiple=int(getattr(self.runner, "token_multiple", 1)))
         if device_timing != "off":
             self.runner.set_device_timing(device_timing)      # off | graph | node (engine/timing.py)
         self.scheduler = Scheduler(self.runner.cache, cfg)

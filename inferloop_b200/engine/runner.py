@@ -220,6 +220,9 @@ class ModelRunner:
         self.tokens_run = 0
         self.kernels_last_step = 0
         self.timer = DeviceTimer(device, "off")
+        # tokens per row tile of the many-token matrix kernel: a step a few tokens past a
+        # multiple costs a whole tile more (the scheduler trims portions to it)
+        self.token_multiple = 128 if dtype == torch.bfloat16 else 1
         # Decode-only steps replay recorded graphs: whole, when every part reads its batch from
         # device memory; in segments around the blocks that do not (they loop over host-side
         # batch facts and run kernel by kernel), when at least one block does.

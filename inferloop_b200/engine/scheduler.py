@@ -15,7 +15,10 @@ What the reference does and what is kept of it:
     (crates/engine/scheduler/src/policy.rs:203-233);
   * a prompt portion is granted whole if the remaining budget funds it; when decodes have
     eaten into the budget it gets the remainder only if that is at least half a portion,
-    else it waits (crates/engine/scheduler/src/policy/packing.rs:328-347);
+    else it waits (crates/engine/scheduler/src/policy/packing.rs:328-347); this engine's own
+    addition: a whole portion that shares its step is trimmed to the next lower multiple of
+    `step_token_multiple` tokens for the step (the matrix kernels' token tile), under the
+    same half-portion floor;
   * finish on an end-of-sequence token or on `max_new_tokens`
     (crates/engine/runtime/src/pipeline/completion/mod.rs:402-408);
   * when pages run out: the blocked work waits if something else can run; if a decoding
@@ -46,6 +49,9 @@ class SchedulerConfig:
     max_num_batched_tokens: int = 2048
     prefill_chunk_tokens: int = 512
     max_model_len: int = 4096
+    # A whole portion that shares a step with other work is trimmed so that the step's tokens
+    # are a multiple of this (the token tile of the matrix kernels; 1 = never trimmed).
+    step_token_multiple: int = 1
 
     def __post_init__(self) -> None:
         for name in ("max_num_seqs", "max_num_batched_tokens", "prefill_chunk_tokens", "max_model_len"):
@@ -232,7 +238,8 @@ class Scheduler:
             self._work = (ctypes.c_longlong * (4 * self._cap))()
             self._victims = (ctypes.c_longlong * (4 * self._cap))()
         if self._lib.ilb_sched_set_limits(self._h, c.max_num_seqs, c.max_num_batched_tokens, c.prefill_chunk_tokens,
-                                          c.max_model_len):
+                                          c.max_model_len) or \
+                self._lib.ilb_sched_set_token_multiple(self._h, int(c.step_token_multiple)):
             raise ValueError(host.last_error())
         n_work, n_victims = ctypes.c_int(), ctypes.c_int()
         rc = self._lib.ilb_sched_plan(self._h, self._work, self._cap, ctypes.byref(n_work), self._victims,

@@ -157,6 +157,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ilb_sched_new": (c_int, [c_vp, c_ll, c_ll, c_ll, c_ll, ctypes.POINTER(c_vp)]),
         "ilb_sched_free": (None, [c_vp]),
         "ilb_sched_set_limits": (c_int, [c_vp, c_ll, c_ll, c_ll, c_ll]),
+        "ilb_sched_set_token_multiple": (c_int, [c_vp, c_ll]),
         "ilb_sched_add": (c_int, [c_vp, c_ll, c_ll, c_ll]),
         "ilb_sched_plan": (c_int, [c_vp, llp, c_int, ip, llp, ip]),
         "ilb_sched_token": (c_int, [c_vp, c_ll, c_int]),

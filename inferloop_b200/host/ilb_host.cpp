@@ -900,6 +900,7 @@ struct Work { long long id, start, count; int samples; };
 struct Sched {
   Ledger* l;
   long long max_num_seqs, max_batched, chunk, max_model_len;
+  long long token_multiple = 1;                // a whole portion beside other work is trimmed so that the step's tokens are a multiple of this
   std::vector<long long> waiting;              // front = index 0
   std::vector<long long> running;              // admission order
   std::unordered_map<long long, SReq> reqs;
@@ -972,6 +973,16 @@ struct Sched {
       if (budget >= portion) count = portion;
       else if (budget >= 1 && budget * 2 >= portion) count = budget;
       else return false;
+      // The matrix kernels work on tiles of `token_multiple` tokens: a whole portion that
+      // rides beside other work (decode tokens, another portion) would push the step a few
+      // tokens past a tile edge and cost a whole tile more.  It is trimmed to the edge, as
+      // long as at least half a portion stays (the same floor as above); the prompt's tail
+      // is never trimmed.
+      if (token_multiple > 1 && portion == chunk) {
+        const long long used = max_batched - budget;
+        const long long edge = (used + count) / token_multiple * token_multiple;
+        if (used > 0 && edge < used + count && (edge - used) * 2 >= portion) count = edge - used;
+      }
       pages_for(id, done + count, need);
       if (!fits(need)) {
         // take what the free pages can hold, if that is still progress
@@ -1152,6 +1163,11 @@ ILB_API int ilb_sched_preemptions_of(void* h, long long id) {
   Sched* s = static_cast<Sched*>(h);
   auto it = s->reqs.find(id);
   return it == s->reqs.end() ? 0 : it->second.preemptions;
+}
+ILB_API int ilb_sched_set_token_multiple(void* h, long long multiple) {
+  if (multiple <= 0) return fail(kInvalid, "the token multiple must be positive");
+  static_cast<Sched*>(h)->token_multiple = multiple;
+  return kOk;
 }
 ILB_API int ilb_sched_set_limits(void* h, long long max_num_seqs, long long max_batched, long long chunk, long long max_model_len) {
   if (max_num_seqs <= 0 || max_batched <= 0 || chunk <= 0 || max_model_len <= 0) return fail(kInvalid, "scheduler limits must be positive");

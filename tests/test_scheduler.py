@@ -172,3 +172,35 @@ def test_finished_requests_are_handed_over_and_forgotten():
             e.step()
     assert len(e.scheduler.finished) <= 3 and "k4" in e.requests and "k0" not in e.requests
     assert e.result("k4").generated and e.inspect()["finished"] <= 3
+
+
+def test_a_whole_portion_beside_decodes_is_trimmed_to_the_token_tile():
+    """With `step_token_multiple` m, a step that holds decode tokens and a whole portion has a
+    multiple of m tokens (the matrix kernels' tile), as long as half a portion stays; a
+    prompt's tail and a portion alone in its step are left as they are; tokens do not change."""
+    prompts = [random_tokens(n, 50, 700 + n) for n in (5, 6, 7, 100, 45)]
+
+    def run(multiple):
+        runner = FakeRunner(num_pages=128)
+        e = make(runner, max_num_seqs=5, prefill_chunk_tokens=32, max_num_batched_tokens=40)
+        e.scheduler.config.step_token_multiple = multiple
+        ids = [e.submit(p, SamplingParams(), 12, request_id=i) for i, p in enumerate(prompts)]
+        while not e.is_idle():
+            e.step()
+        return [e.result(i).generated for i in ids], runner.steps
+
+    plain_tokens, plain_steps = run(1)
+    tokens, steps = run(16)
+    assert tokens == plain_tokens
+    assert any(sum(n for _, n in s) == 35 for s in plain_steps)              # three decodes + a portion of 32
+    sizes = [[n for _, n in s] for s in steps]
+    assert [1, 1, 1, 32] in [[n for _, n in s] for s in plain_steps] and [1, 1, 1, 32] not in sizes
+    assert sizes.count([1, 1, 1, 29]) == 2                                    # 3 + 29 = 32 tokens: two tiles of 16
+    # the prompt's tail (20 tokens) is not trimmed, and the newcomer beside it gets what the
+    # budget leaves (17 of its 32: more than half), not the 9 that would reach the tile's edge
+    assert [1, 1, 1, 20, 17] in sizes
+    e = make(FakeRunner(num_pages=128), max_num_seqs=2, prefill_chunk_tokens=32, max_num_batched_tokens=40)
+    e.scheduler.config.step_token_multiple = 16
+    e.submit(random_tokens(70, 50, 1), SamplingParams(), 2)
+    e.step()
+    assert e.runner.steps[0] == [(0, 32)]                                     # alone in its step: whole
