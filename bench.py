@@ -2,7 +2,7 @@
 """Measurement of the engine on one B200, random bf16 weights, synthetic token ids.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
-                    [--config 8b|14b-mixed|32b-long] [--breakdown]
+                    [--config 8b|14b-mixed|32b-long] [--breakdown] [--kernels]
 
 One JSON line on stdout.  The default (`--config 8b`) is the headline: Qwen3-8B layer sizes,
 36 layers, batch 8, 1,024-token prompts; a "step" is one decode step of the whole batch.
@@ -21,7 +21,11 @@ tokens each; a "step" is one engine step and `--steps` is ignored (the job is ru
 untimed and once timed).  `--config 32b-long`: Qwen3-32B layer sizes, 8,192-token prompts,
 decode at batch 1 and 16.  `--breakdown` adds the share of every op class in a decode step
 and in the prefill step, from a pair of CUDA events around every kernel (the engine's
-`device_timing="node"` mode).
+`device_timing="node"` mode; every kernel's figure carries the few microseconds that a pair
+of events around a lone launch costs).  `--kernels` times kernels alone instead, at the layer
+sizes of `--config`: the prefill attention at several lengths, and the layer's matrix products
+at several token counts beside `torch.matmul` on the same shapes (the library's plain product,
+for comparison only; it has no epilogue).
 Peaks come from MEASURED_PEAKS.json beside this file when present, else the fallback
 figures 6.65 TB/s and 1.59 PFLOP/s.  Weights (15 GB and more) exceed L2 (126 MB), so every
 step reads them from HBM: no L2 flush is needed between timed steps.
@@ -458,6 +462,77 @@ def run_32b_long(args) -> dict:
     return result
 
 
+def run_kernels(args) -> dict:
+    """Kernels alone (CUDA events around 20 launches after 3; weights rotate over four copies
+    so that nothing stays in L2)."""
+    import math
+    import torch
+    from inferloop_b200.csrc import ops
+    from inferloop_b200.parts import Workspace
+    cfg = {"8b": QWEN3_8B, "14b-mixed": QWEN3_14B, "32b-long": QWEN3_32B}[args.config]
+    nq, nkv, d, H, I = (cfg[k] for k in ("num_attention_heads", "num_key_value_heads", "head_dim", "hidden_size", "intermediate_size"))
+    bf = torch.bfloat16
+
+    def timed(f, n=20):
+        for _ in range(3):
+            f()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            f()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n * 1e3            # microseconds
+
+    class Step:
+        pass
+    ws = Workspace(torch.device("cuda:0"))
+    attention = {}
+    for T in (512, 1024, 2048, 4096, 8192):
+        pages = T // PAGE + 4
+        q = torch.randn(T, nq * d, device="cuda").to(bf)
+        out = torch.empty_like(q)
+        kc = torch.randn(pages, nkv, PAGE, d, device="cuda").to(bf)
+        vc = torch.randn_like(kc)
+        st = Step()
+        st.positions = torch.arange(T, dtype=torch.int32, device="cuda")
+        st.seq_of_token = torch.zeros(T, dtype=torch.int32, device="cuda")
+        st.cu_q = torch.tensor([0, T], dtype=torch.int32, device="cuda")
+        st.h_q_len, st.n_seqs, st.decode_only = [T], 1, False
+        table = torch.arange(T // PAGE, dtype=torch.int32, device="cuda").view(1, -1).contiguous()
+        us = timed(lambda: ops.attention(q, out, kc, vc, st, table, 0, 1 / math.sqrt(d), nq, nkv, d, workspace=ws))
+        flops = 4.0 * nq * d * T * (T + 1) / 2
+        attention[f"prefill_{T}"] = {"us": round(us, 1), "tflops": round(flops / us / 1e6, 1)}
+    products = {}
+    shapes = [("qkv", (nq + 2 * nkv) * d, H, {}), ("o", H, nq * d, {"accumulate": True}),
+              ("gate_up", 2 * I, H, {"swiglu": True}), ("down", H, I, {"accumulate": True})]
+    for M in (8, 64, 512, 2048):
+        for name, N, K, kw in shapes:
+            a = torch.randn(M, K, device="cuda").to(bf)
+            weights = [torch.randn(N, K, device="cuda").to(bf) * 0.02 for _ in range(4)]
+            n_out = N // 2 if kw.get("swiglu") else N
+            out = torch.zeros(M, n_out, device="cuda", dtype=torch.float32 if kw.get("accumulate") else bf)
+            plain = torch.empty(M, N, device="cuda", dtype=bf)
+            turn = [0]
+
+            def ours():
+                ops.gemm_tc(a, weights[turn[0] % 4], out, None, **kw)
+                turn[0] += 1
+
+            def library():
+                torch.matmul(a, weights[turn[0] % 4].T, out=plain)
+                turn[0] += 1
+            t_ours, t_lib = timed(ours), timed(library)
+            products[f"{name}_m{M}"] = {"us": round(t_ours, 1), "tflops": round(2.0 * M * N * K / t_ours / 1e6, 1),
+                                        "weights_gbs": round(2.0 * N * K / t_ours / 1e3, 1),
+                                        "torch_matmul_us": round(t_lib, 1)}
+            del weights
+    ops.check_device_errors()
+    return {"metric": "kernels alone", "config": flat_config(args.config, cfg), "attention": attention, "products": products,
+            "peaks": peaks()}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -469,6 +544,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers (named in config) to save time")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 / prefill side measurements")
     ap.add_argument("--breakdown", action="store_true", help="add the per-op-class share of device time")
+    ap.add_argument("--kernels", action="store_true", help="time kernels alone at the layer sizes of --config")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -481,6 +557,9 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.kernels:
+        print(json.dumps(run_kernels(args)))
+        return 0
     result = {"8b": run_8b, "14b-mixed": run_14b_mixed, "32b-long": run_32b_long}[args.config](args)
     print(json.dumps(result))
     return 0
