@@ -285,12 +285,45 @@ class Bench:
         return out
 
 
+    def breakdown_mixed(self, singles, context, portion) -> dict:
+        """Share of every op class in a mixed step: `singles` requests that decode at
+        `context` keys beside a `portion` of one long prompt whose earlier part is in the cache."""
+        from inferloop_b200.engine import StepEntry
+        runner = self.runner
+        ids = [f"bm{i}" for i in range(singles)]
+        last = self.prefill(ids, self.prompts(singles, context))
+        steps = 3 + 5
+        done = 1024                                   # of the long prompt, before the measured portions
+        long_prompt = self.prompts(1, done + steps * portion)[0]
+        self.prefill(["bmp"], [long_prompt[:done]])
+        runner.set_device_timing("node")
+        try:
+            entries = [StepEntry(rid, [last[rid]], [0]) for rid in ids]
+            for i in range(steps):
+                if i == 3:
+                    runner.timer.reset()
+                part = long_prompt[done + i * portion:done + (i + 1) * portion]
+                _, drawn = runner.step(entries + [StepEntry("bmp", part, [])], draw_greedy=True)
+                entries = [StepEntry(rid, [int(t)], [0]) for rid, t in zip(ids, drawn.ids.tolist())]
+            out = _per_step(runner.timer.summary())
+        finally:
+            runner.set_device_timing("off")
+        for rid in ids + ["bmp"]:
+            runner.end(rid)
+        out["step"] = {"single_token_seqs": singles, "context": context, "portion_tokens": portion,
+                       "portion_starts_at": f"{done} to {done + (steps - 1) * portion}"}
+        return out
+
+
 def _per_step(summary: dict) -> dict:
     n = max(summary.get("steps", {}).get("count", 1), 1)
     return {"steps": n, "ms_per_step_events_around_step": round(summary["steps"]["ms_total"] / n, 4),
             "ms_per_step_sum_of_kernels": round(summary["ops_ms_total"] / n, 4),
             "ops": {k: {"us_per_step": round(1e3 * v["ms"] / n, 2), "launches_per_step": v["launches"] / n,
-                        "share": v["share"]} for k, v in summary["ops"].items()}}
+                        "share": v["share"],
+                        **({"kernels_us_per_step": {name: round(1e3 * per["ms"] / n, 2) for name, per in v["kernels"].items()}}
+                           if len(v["kernels"]) > 1 else {})}
+                    for k, v in summary["ops"].items()}}
 
 
 # ----------------------------------------------------------------------------- the three configurations
@@ -428,6 +461,7 @@ def run_14b_mixed(args) -> dict:
         "roofline": {"bound": "per step: the slower of flops / bf16 peak and bytes / HBM", "seconds": round(roof_s, 4),
                      "frac": round(roof_s / seconds, 4), "peak_tflops": pk["bf16_tflops"], "peak_gbs": pk["hbm_gbs"]},
         "clocks": clocks.summary(),
+        **({"breakdown": {"mixed": bench.breakdown_mixed(24, 1536, 384)}} if args.breakdown else {}),
     }
 
 

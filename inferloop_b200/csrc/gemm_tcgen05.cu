@@ -82,6 +82,7 @@ struct Params {
   int tiles_x, tiles_y;      // tiles of the X operand (128 rows) and of the Y operand (BN rows)
   int k_blocks;              // ceil(K / 64)
   long long units;           // K blocks of the tiles that are shared out stream-K fashion
+  int sk_ctas;               // CTAs that share them (0: all of the grid, or one per unit if those are fewer)
   int dp_waves;              // whole-tile rounds before that: CTA c takes tiles c, c + grid, ...
   long long sk_tile0;        // tiles of those rounds (the last round may be short) = first tile of the stream-K part
   int epilogue;              // Epilogue
@@ -177,7 +178,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // The stream-K part is shared by the first min(grid, units) CTAs, so that every CTA that
   // takes part holds at least one unit (a tile's sharers are then consecutive CTAs).
-  const int sk_grid = p.units < (long long)gridDim.x ? (int)p.units : (int)gridDim.x;
+  const int sk_grid = p.sk_ctas > 0 ? p.sk_ctas : p.units < (long long)gridDim.x ? (int)p.units : (int)gridDim.x;
   const Schedule sch{p.units > 0 ? p.units : 1, sk_grid > 0 ? sk_grid : 1, p.k_blocks};
   const bool in_sk = p.units > 0 && (int)blockIdx.x < sk_grid;
   const long long u_begin = in_sk ? sch.start(blockIdx.x) : 0, u_end = in_sk ? sch.start(blockIdx.x + 1) : 0;
@@ -332,7 +333,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       if (failed) break;
       int col_lo = 0, col_hi = BN;             // columns this CTA writes out
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (MS == 1 ? b : (uint32_t)ms) * kAccCols;
-      const bool whole = cnt == p.k_blocks;
+      // Many tokens, accumulating into the 32-bit output through TMA: the write-out ADDS in
+      // memory, so a K range of a tile is written out like a whole tile and the ranges of a
+      // tile meet in memory (in whatever order they finish: a 32-bit sum of the same terms).
+      const bool additive = !SWAP && p.tma_out && p.epilogue == kAccumulate && p.cluster == 1;
+      const bool whole = cnt == p.k_blocks || additive;
+      const bool with_bias = p.bias != nullptr && (kb0 == 0 || !additive);   // once per output: of the ranges that meet in memory, the first adds it
       bool last = whole;
       int c_first = 0, c_last = 0;
       if (kPush && !whole && p.cluster > 1) {
@@ -560,7 +566,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             for (int c0 = col_lo; c0 < col_hi; c0 += 32) {
               float v[32];
               fetch(c0, v);
-              if (p.bias) {
+              if (with_bias) {
 #pragma unroll
                 for (int c = 0; c < 32; ++c) v[c] += (y0 + c0 + c < p.N) ? p.bias[y0 + c0 + c] : 0.f;
               }
@@ -975,10 +981,21 @@ ILB_EXPORT int ilb_gemm_tc_supported(int M, int N, int K, int lda, int ldw) {
 namespace {
 // How a product is dealt out: orientation, tile shape, grid, cluster, rounds (fills the
 // scheduling fields of `p`, which must hold M, N, K, k_blocks and the epilogue already).
-struct Plan { bool swap; int bn, ms, x_rows, y_rows; long long grid; };
+struct Plan { bool swap, tail, additive; int bn, ms, x_rows, y_rows; long long grid; };
 
-int make_plan(Params& p, int M, int N, int K, int accumulate, int n_tickets, int max_ctas, Plan& plan) {
+// Equal K ranges per tile when `rest` tiles share the SMs: as many as fit, none shorter than
+// four K blocks.
+long long add_split(long long rest, long long k_blocks) {
+  long long split = sm_count() / rest;
+  if (split > k_blocks / 4) split = k_blocks / 4;
+  return split < 1 ? 1 : split;
+}
+
+// `can_add`: the product accumulates into a 32-bit output that the TMA write-out can reach,
+// so that the K ranges of a tile may be added in memory.
+int make_plan(Params& p, int M, int N, int K, int accumulate, int n_tickets, int max_ctas, bool can_add, Plan& plan) {
   const bool swap = M <= 128;
+  bool tail = false;
   int bn, ms = 1;                                    // ms: 128-row blocks of X per tile
   if (swap) {
     bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
@@ -1015,6 +1032,28 @@ int make_plan(Params& p, int M, int N, int K, int accumulate, int n_tickets, int
       score *= filled;
       if (score > best) { best = score; bn = c.bn; ms = c.ms; }
     }
+    // A short last round: the tiles left over after the whole rounds (all of them, when they
+    // are fewer than the SMs) are each cut into as many equal K ranges as the SMs allow, so the
+    // last round is as short as its tiles are few and the largest tile serves whatever the
+    // sizes.  (Equal ranges, not equal runs over all the tiles' K blocks: CTAs that share an
+    // operand block must reach it together, or each streams its own copy from memory.)  Only
+    // where the product accumulates into a 32-bit output: there the ranges of a tile meet in
+    // memory at the cost of a second write-out.  (Through the workspace and a ticket instead,
+    // for the other epilogues, the last round's 32-bit round trip cost more than the idle SMs:
+    // 30 -> 47 us for 512 x 6144 x 4096, 113 -> 166 us for 2048 x 7168 x 5120.)
+    if (can_add && accumulate == 1 && max_ctas <= 0 && N >= 256) {
+      for (int cms = 2; cms >= 1; --cms) {
+        const long long tm = (M + cms * kTileX - 1) / (cms * kTileX), tn = (N + 255) / 256, t = tm * tn;
+        const long long rounds = t / sm_count(), rest = t - rounds * sm_count();
+        if (rest == 0) continue;                                   // whole rounds: nothing to share out
+        const long long split = add_split(rest, kb);
+        if (split < 2) continue;
+        const double filled = ((double)M / (double)(tm * cms * kTileX)) * ((double)N / (double)(tn * 256));
+        const double time = (double)rounds + 1.0 / (double)split + 0.03;      // in tile times; the last term: a second write-out
+        const double score = (cms == 2 ? 1.0 : 0.85) * filled * ((double)t / (double)sm_count()) / time;
+        if (score > best) { best = score; bn = 256; ms = cms; tail = true; }
+      }
+    }
   }
   const int x_rows = swap ? N : M, y_rows = swap ? M : N;
   p.tiles_x = (x_rows + ms * kTileX - 1) / (ms * kTileX);
@@ -1048,7 +1087,13 @@ int make_plan(Params& p, int M, int N, int K, int accumulate, int n_tickets, int
     // of a round starting at K block 0 together; when the tiles would leave most SMs idle,
     // every tile is cut into the same number of K ranges instead.
     const long long sms = sm_count();
-    if (tiles * 2 <= sms) {
+    if (tail) {
+      p.dp_waves = (int)(tiles / sms);
+      p.sk_tile0 = (long long)p.dp_waves * sms;
+      const long long rest = tiles - p.sk_tile0;
+      p.sk_ctas = (int)(rest * add_split(rest, p.k_blocks));
+      grid = p.dp_waves > 0 ? sms : p.sk_ctas;
+    } else if (tiles * 2 <= sms) {
       long long split = 1;
       while (split < 8 && tiles * split * 2 <= sms && split * 2 <= p.k_blocks) split *= 2;
       if (ms == 1 && split > 1) {
@@ -1076,7 +1121,7 @@ int make_plan(Params& p, int M, int N, int K, int accumulate, int n_tickets, int
     p.sk_tile0 = (long long)p.dp_waves * grid;
   }
   p.units = (tiles - p.sk_tile0) * p.k_blocks;
-  plan.swap = swap; plan.bn = bn; plan.ms = ms; plan.x_rows = x_rows; plan.y_rows = y_rows; plan.grid = grid;
+  plan.swap = swap; plan.tail = tail; plan.additive = tail && can_add && accumulate == 1; plan.bn = bn; plan.ms = ms; plan.x_rows = x_rows; plan.y_rows = y_rows; plan.grid = grid;
   return 0;
 }
 
@@ -1109,7 +1154,9 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   p.out_f32 = out_f32;
 
   Plan plan{};
-  if (make_plan(p, M, N, K, accumulate, n_tickets, max_ctas, plan)) return -1;
+  const int es = out_f32 ? 4 : 2, out_cols = accumulate == 2 ? N / 2 : N;
+  const bool tma_reach = ((uintptr_t)out % 16 == 0) && ((long long)ldo * es) % 16 == 0;   // rows of 16-byte multiples from a 16-byte base
+  if (make_plan(p, M, N, K, accumulate, n_tickets, max_ctas, tma_reach && out_f32 && accumulate == 1, plan)) return -1;
   const bool swap = plan.swap;
   const int bn = plan.bn, ms = plan.ms, x_rows = plan.x_rows, y_rows = plan.y_rows;
   const long long grid = plan.grid;
@@ -1124,11 +1171,11 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   if (make_map(&my, Y, y_rows, K, ldy, bn)) return -1;
   // Many tokens, one CTA per tile's write-out: the result leaves by TMA (rows of 16-byte multiples from a 16-byte base)
   CUtensorMap mo = mx;
-  const int es = out_f32 ? 4 : 2, out_cols = accumulate == 2 ? N / 2 : N;
   // (a cluster's CTAs each write a share of the columns: whole 128-byte rows of it, or per-thread stores)
   const int share_cols = bn / (p.cluster > 0 ? p.cluster : 1);
   const bool whole_rows = p.cluster == 1 || (accumulate == 2 ? share_cols % 128 == 0 : share_cols % (128 / es) == 0);
-  p.tma_out = (!swap && whole_rows && !(accumulate == 2 && out_f32) && ((uintptr_t)out % 16 == 0) && ((long long)ldo * es) % 16 == 0) ? 1 : 0;
+  p.tma_out = (!swap && whole_rows && !(accumulate == 2 && out_f32) && tma_reach) ? 1 : 0;
+  ILB_REQUIRE(!plan.additive || p.tma_out, "gemm_tc: partial sums that meet in memory need the TMA write-out");
   if (p.tma_out && make_out_map(&mo, out, M, out_cols, ldo, out_f32 != 0)) return -1;
 
   if (swap) {
@@ -1148,17 +1195,18 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   return launch<128, 6, false>(mx, my, mo, p, (int)grid, stream);
 }
 
-// What a product of these sizes would get (for tests and notes): out[0..7] = swapped operands,
+// What a product of these sizes would get (for tests and notes): out[0..8] = swapped operands,
 // token-tile / weight-tile width, 128-row blocks per tile, grid, cluster, whole-tile rounds,
-// tiles, tiles handled stream-K fashion.
+// tiles, tiles handled stream-K fashion, whether the K ranges of a tile are added in memory.
 ILB_EXPORT int ilb_gemm_tc_plan(int M, int N, int K, int epilogue, int* out) {
   ILB_REQUIRE(M > 0 && N > 0 && K > 0 && out != nullptr && epilogue >= 0 && epilogue <= 2, "gemm_tc: bad sizes for a plan");
   Params p{};
   p.M = M; p.N = N; p.K = K; p.k_blocks = (K + kBlockK - 1) / kBlockK; p.epilogue = epilogue;
   Plan plan{};
-  if (make_plan(p, M, N, K, epilogue, 1 << 30, 0, plan)) return -1;
+  if (make_plan(p, M, N, K, epilogue, 1 << 30, 0, epilogue == 1, plan)) return -1;
   out[0] = plan.swap ? 1 : 0; out[1] = plan.bn; out[2] = plan.ms; out[3] = (int)plan.grid; out[4] = p.cluster;
   out[5] = p.dp_waves; out[6] = p.tiles_x * p.tiles_y; out[7] = (int)(p.tiles_x * (long long)p.tiles_y - p.sk_tile0);
+  out[8] = plan.additive ? 1 : 0;
   return 0;
 }
 

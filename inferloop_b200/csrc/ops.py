@@ -344,11 +344,11 @@ def gemm_tc_plan(M: int, N: int, K: int, accumulate: bool = False, swiglu: bool 
     """How `gemm_tc` deals out a product of these sizes (needs a device: the answer depends
     on how many CTAs fit it)."""
     lib = load_module("gemm_tcgen05")
-    out = (ctypes.c_int * 8)()
+    out = (ctypes.c_int * 9)()
     lib.ilb_gemm_tc_plan.restype = ctypes.c_int
     if lib.ilb_gemm_tc_plan(_i(M), _i(N), _i(K), _i(2 if swiglu else (1 if accumulate else 0)), out) != 0:
         raise KernelError(lib.ilb_last_error().decode())
-    keys = ("swap", "tile_n", "row_blocks", "grid", "cluster", "rounds", "tiles", "tiles_stream_k")
+    keys = ("swap", "tile_n", "row_blocks", "grid", "cluster", "rounds", "tiles", "tiles_stream_k", "sums_meet_in_memory")
     return dict(zip(keys, list(out)))
 
 

@@ -73,7 +73,8 @@ class DeviceTimer:
     # ---------------------------------------------------------------- reading
     def summary(self) -> dict:
         """{"mode", "steps": {"count", "ms_total", "ms_mean", "tokens"}, "ops": {scope:
-        {"launches", "ms", "share", "kernels": [...]}}}; synchronises the device."""
+        {"launches", "ms", "share", "kernels": {entry point: {"launches", "ms"}}}}};
+        synchronises the device."""
         torch.cuda.synchronize(self.device)
         out: dict = {"mode": self.mode}
         if self._steps:
@@ -83,15 +84,19 @@ class DeviceTimer:
         if self._nodes:
             ops: "OrderedDict[str, dict]" = OrderedDict()
             for scope, kernel, a, b in self._nodes:
-                rec = ops.setdefault(scope, {"launches": 0, "ms": 0.0, "kernels": []})
+                rec = ops.setdefault(scope, {"launches": 0, "ms": 0.0, "kernels": {}})
+                ms = a.elapsed_time(b)
                 rec["launches"] += 1
-                rec["ms"] += a.elapsed_time(b)
-                if kernel not in rec["kernels"]:
-                    rec["kernels"].append(kernel)
+                rec["ms"] += ms
+                per = rec["kernels"].setdefault(kernel, {"launches": 0, "ms": 0.0})
+                per["launches"] += 1
+                per["ms"] += ms
             total = sum(r["ms"] for r in ops.values()) or 1.0
             for r in ops.values():
                 r["share"] = round(r["ms"] / total, 4)
                 r["ms"] = round(r["ms"], 4)
+                for per in r["kernels"].values():
+                    per["ms"] = round(per["ms"], 4)
             out["ops"] = dict(ops)
             out["ops_ms_total"] = round(total, 4)
         return out

@@ -294,7 +294,10 @@ TC_SHAPES = [(256, 19200, 64), (300, 9728, 128), (1, 128, 64), (3, 200, 72), (8,
              # few tiles of many tokens: the K ranges of a tile run as a cluster that shares the write-out
              (200, 700, 1024), (129, 256, 1024), (256, 4096, 1024), (500, 1100, 4096), (1024, 520, 512),
              # 256 x 192 and 256 x 256 tiles in whole rounds, a last round that is not full
-             (2048, 6144, 256), (1500, 4100, 192)]
+             (2048, 6144, 256), (1500, 4100, 192),
+             # accumulating: whole rounds and 12 tiles dealt out by K blocks; fewer tiles than SMs, all
+             # dealt out by K blocks; one row block per tile.  The K ranges of a tile are added in memory.
+             (2048, 5120, 512), (512, 4096, 2048), (200, 1024, 4096)]
 
 
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)
@@ -365,6 +368,7 @@ def test_gemm_tcgen05_plans_cover_every_tile_once():
             assert plan["swap"] == (1 if M <= 128 else 0), what
             assert plan["cluster"] in (1, 2, 4, 8) and plan["grid"] % plan["cluster"] == 0, what
             assert 0 <= plan["tiles_stream_k"] <= plan["tiles"], what
+            assert not plan["sums_meet_in_memory"] or (kw.get("accumulate") and not plan["swap"] and plan["cluster"] == 1), what
             if plan["swap"]:
                 assert plan["tile_n"] >= min(M, 128) and plan["grid"] <= 2 * sms, what
                 if plan["cluster"] > 1:
