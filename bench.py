@@ -2,7 +2,7 @@
 """Measurement of the engine on one B200, random bf16 weights, synthetic token ids.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
-                    [--config 8b|14b-mixed|32b-long] [--breakdown] [--kernels]
+                    [--config 8b|14b-mixed|32b-long] [--breakdown] [--kernels [attention|products]]
 
 One JSON line on stdout.  The default (`--config 8b`) is the headline: Qwen3-8B layer sizes,
 36 layers, batch 8, 1,024-token prompts; a "step" is one decode step of the whole batch.
@@ -523,25 +523,29 @@ def run_kernels(args) -> dict:
         pass
     ws = Workspace(torch.device("cuda:0"))
     attention = {}
-    for T in (512, 1024, 2048, 4096, 8192):
-        pages = T // PAGE + 4
+    # whole prompts, then a portion of 512 tokens behind 3,584 cached ones, its pages in order and scattered over the pool
+    cases = [(f"prefill_{T}", T, 0, False) for T in (512, 1024, 2048, 4096, 8192)]
+    cases += [("portion_512_after_3584", 512, 3584, False), ("portion_512_after_3584_pages_scattered", 512, 3584, True)]
+    for name, T, start, scattered in cases if args.kernels in ("all", "attention") else ():
+        n_pages = (start + T) // PAGE
         q = torch.randn(T, nq * d, device="cuda").to(bf)
         out = torch.empty_like(q)
-        kc = torch.randn(pages, nkv, PAGE, d, device="cuda").to(bf)
+        kc = torch.randn(n_pages + 4, nkv, PAGE, d, device="cuda").to(bf)
         vc = torch.randn_like(kc)
         st = Step()
-        st.positions = torch.arange(T, dtype=torch.int32, device="cuda")
+        st.positions = torch.arange(start, start + T, dtype=torch.int32, device="cuda")
         st.seq_of_token = torch.zeros(T, dtype=torch.int32, device="cuda")
         st.cu_q = torch.tensor([0, T], dtype=torch.int32, device="cuda")
         st.h_q_len, st.n_seqs, st.decode_only = [T], 1, False
-        table = torch.arange(T // PAGE, dtype=torch.int32, device="cuda").view(1, -1).contiguous()
+        order = torch.randperm(n_pages) if scattered else torch.arange(n_pages)
+        table = order.to(torch.int32).cuda().view(1, -1).contiguous()
         us = timed(lambda: ops.attention(q, out, kc, vc, st, table, 0, 1 / math.sqrt(d), nq, nkv, d, workspace=ws))
-        flops = 4.0 * nq * d * T * (T + 1) / 2
-        attention[f"prefill_{T}"] = {"us": round(us, 1), "tflops": round(flops / us / 1e6, 1)}
+        flops = 4.0 * nq * d * (T * start + T * (T + 1) / 2)
+        attention[name] = {"us": round(us, 1), "tflops": round(flops / us / 1e6, 1)}
     products = {}
     shapes = [("qkv", (nq + 2 * nkv) * d, H, {}), ("o", H, nq * d, {"accumulate": True}),
               ("gate_up", 2 * I, H, {"swiglu": True}), ("down", H, I, {"accumulate": True})]
-    for M in (8, 64, 512, 2048):
+    for M in (8, 64, 512, 2048) if args.kernels in ("all", "products") else ():
         for name, N, K, kw in shapes:
             a = torch.randn(M, K, device="cuda").to(bf)
             weights = [torch.randn(N, K, device="cuda").to(bf) * 0.02 for _ in range(4)]
@@ -578,7 +582,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers (named in config) to save time")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 / prefill side measurements")
     ap.add_argument("--breakdown", action="store_true", help="add the per-op-class share of device time")
-    ap.add_argument("--kernels", action="store_true", help="time kernels alone at the layer sizes of --config")
+    ap.add_argument("--kernels", nargs="?", const="all", default=None, choices=["all", "attention", "products"],
+                    help="time kernels alone at the layer sizes of --config")
     args = ap.parse_args()
 
     if args.impl == "reference":

@@ -983,6 +983,10 @@ namespace {
 // scheduling fields of `p`, which must hold M, N, K, k_blocks and the epilogue already).
 struct Plan { bool swap, tail, additive; int bn, ms, x_rows, y_rows; long long grid; };
 
+// Whether the K ranges of a tile may meet in memory (the sum's order is then not fixed: runs
+// agree beyond rounding, not bit for bit).  `ilb_gemm_tc_sums_in_memory(0)` turns it off.
+bool g_sums_in_memory = true;
+
 // Equal K ranges per tile when `rest` tiles share the SMs: as many as fit, none shorter than
 // four K blocks.
 long long add_split(long long rest, long long k_blocks) {
@@ -1041,11 +1045,13 @@ int make_plan(Params& p, int M, int N, int K, int accumulate, int n_tickets, int
     // memory at the cost of a second write-out.  (Through the workspace and a ticket instead,
     // for the other epilogues, the last round's 32-bit round trip cost more than the idle SMs:
     // 30 -> 47 us for 512 x 6144 x 4096, 113 -> 166 us for 2048 x 7168 x 5120.)
-    if (can_add && accumulate == 1 && max_ctas <= 0 && N >= 256) {
+    // (Not for a handful of tiles: there it gains little, and small products keep sums whose
+    // bits do not change from run to run.)
+    if (can_add && g_sums_in_memory && accumulate == 1 && max_ctas <= 0 && N >= 256) {
       for (int cms = 2; cms >= 1; --cms) {
         const long long tm = (M + cms * kTileX - 1) / (cms * kTileX), tn = (N + 255) / 256, t = tm * tn;
         const long long rounds = t / sm_count(), rest = t - rounds * sm_count();
-        if (rest == 0) continue;                                   // whole rounds: nothing to share out
+        if (rest == 0 || rest * 8 < sm_count()) continue;          // whole rounds, or too few tiles to matter
         const long long split = add_split(rest, kb);
         if (split < 2) continue;
         const double filled = ((double)M / (double)(tm * cms * kTileX)) * ((double)N / (double)(tn * 256));
@@ -1193,6 +1199,12 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   if (bn == 160) return launch<160, 5, false>(mx, my, mo, p, (int)grid, stream);
   if (bn == 256) return launch<256, 4, false>(mx, my, mo, p, (int)grid, stream);
   return launch<128, 6, false>(mx, my, mo, p, (int)grid, stream);
+}
+
+// 1: the K ranges of a tile may meet in memory (the default); 0: every split sum is added in K order.
+ILB_EXPORT int ilb_gemm_tc_sums_in_memory(int on) {
+  g_sums_in_memory = on != 0;
+  return 0;
 }
 
 // What a product of these sizes would get (for tests and notes): out[0..8] = swapped operands,

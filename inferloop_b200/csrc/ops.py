@@ -340,6 +340,14 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
           _ptr(st.tickets), _i(st.n_tickets), _ptr(st.error), _i(max_ctas), _stream(out))
 
 
+def gemm_sums_in_memory(on: bool) -> None:
+    """Whether products of many tokens that accumulate into a 32-bit output may cut the tiles of
+    their last round into K ranges that meet in memory (faster; the order of that 32-bit sum
+    is not fixed, so two runs agree beyond rounding but not bit for bit).  On by default;
+    off gives sums whose bits do not change from run to run."""
+    load_module("gemm_tcgen05").ilb_gemm_tc_sums_in_memory(_i(1 if on else 0))
+
+
 def gemm_tc_plan(M: int, N: int, K: int, accumulate: bool = False, swiglu: bool = False) -> dict:
     """How `gemm_tc` deals out a product of these sizes (needs a device: the answer depends
     on how many CTAs fit it)."""
@@ -528,24 +536,39 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
         # A mixed step: the sequences that bring one token go to the split-KV decode kernel
         # (it leaves the others alone), the portions to the prefill kernel (which leaves those).
         lens = step.h_q_len
+        kv_lens = getattr(step, "h_kv_len", None) or lens
         split = (MIXED_SPLIT_ENABLED and DECODE_CLUSTER_ENABLED and 1 in lens and max(lens) > 1
                  and attention_decode_tma_supported(nq, nkv, d, k_cache.shape[2]))
         if split:
             attention_decode_tma(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
                                  step.n_seqs, nq, nkv, d, False)
+            kv_lens = [k for n, k in zip(lens, kv_lens) if n > 1]
             lens = [n for n in lens if n > 1]
-        # Two row blocks per CTA share the K and V tiles (faster per tile, half as many CTAs):
-        # taken when there are still enough CTAs for every SM.
         per_block = 128 // G
+        n_one = sum(-(-n // per_block) for n in lens)
         n_two = sum(-(-n // (2 * per_block)) for n in lens)
-        blocks = TC_ATTENTION_ROW_BLOCKS or (2 if n_two * nkv >= _sm_count(q.device) else 1)
-        n_tiles = n_two if blocks == 2 else sum(-(-n // per_block) for n in lens)
+        blocks = TC_ATTENTION_ROW_BLOCKS or tc_row_blocks(n_one * nkv, n_two * nkv, _sm_count(q.device),
+                                                          all(k >= 2 * n for n, k in zip(lens, kv_lens)))
+        n_tiles = n_two if blocks == 2 else n_one
         attention_prefill_tc(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
                              step.n_seqs, n_tiles, nq, nkv, d, blocks, skip_single=split)
     else:
         n_tiles = sum(-(-n * G // 64) for n in step.h_q_len)
         attention_prefill(q, out, k_cache, v_cache, step.positions, step.cu_q, block_table, window, scale,
                           step.n_seqs, n_tiles, nq, nkv, d)
+
+
+def tc_row_blocks(ctas_one: int, ctas_two: int, sms: int, behind_cache: bool) -> int:
+    """Row blocks per CTA of the tcgen05 prefill kernel.  Two blocks share the K and V tiles
+    and keep the tensor core busier, but a tile then takes 4,150 clocks for the pair against
+    2,400 for one block (measured), and there are half as many CTAs.
+    Portions behind a long cached prefix: every CTA walks about as many keys, the launch runs
+    in rounds of one CTA per SM, and the cheaper of rounds x tile time wins (512 tokens of 40 / 8
+    heads behind 3,584: 168 CTAs in two rounds, or 88 in one).  Prompts from their start: the
+    CTAs' runs differ and pack well, and two blocks pay once there is a CTA for every SM."""
+    if behind_cache:
+        return 2 if -(-ctas_two // sms) * 1.7 < -(-ctas_one // sms) else 1
+    return 2 if ctas_two >= sms else 1
 
 
 DECODE_FUSED_ENABLED = True     # tests switch it off to run q/k norm + rotation + cache write as a launch of its own

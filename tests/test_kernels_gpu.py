@@ -344,6 +344,37 @@ def test_gemm_tcgen05_shared_tiles_are_deterministic_and_reusable(max_ctas, M, N
     assert int(_tc_state(a.device).tickets.abs().sum()) == 0
 
 
+def test_gemm_tcgen05_last_round_in_memory_can_be_switched_off():
+    """Accumulating products of many tokens cut the tiles of their last round into K ranges
+    that meet in memory; switched off, the same product runs whole tiles and gives the same
+    bits every time.  Both agree with the plain product."""
+    o = ops()
+    M, N, K = 2048, 5120, 1024                  # 160 tiles of 256 x 256: one round and 12 tiles
+    torch.manual_seed(5)
+    a = torch.randn(M, K).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16).cuda()
+    base = torch.randn(M, N).cuda()
+    ref = base.double().cpu() + a.double().cpu() @ w.double().cpu().T
+    assert o.gemm_tc_plan(M, N, K, accumulate=True)["sums_meet_in_memory"] == 1
+    assert o.gemm_tc_plan(200, 256, 1024, accumulate=True)["sums_meet_in_memory"] == 0      # a handful of tiles: never
+    out = base.clone()
+    o.gemm_tc(a, w, out, accumulate=True)
+    close(out, ref, "float32", scale=float(ref.abs().max()), what="last round in memory")
+    o.gemm_sums_in_memory(False)
+    try:
+        assert o.gemm_tc_plan(M, N, K, accumulate=True)["sums_meet_in_memory"] == 0
+        outs = []
+        for _ in range(3):
+            out = base.clone()
+            o.gemm_tc(a, w, out, accumulate=True)
+            outs.append(out)
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+        close(outs[0], ref, "float32", scale=float(ref.abs().max()), what="whole tiles only")
+    finally:
+        o.gemm_sums_in_memory(True)
+    o.check_device_errors()
+
+
 def test_gemm_tcgen05_refuses_unaligned_rows():
     o = ops()
     a = torch.randn(4, 100).to(torch.bfloat16).cuda()       # 200-byte rows: not a multiple of 16
