@@ -536,7 +536,7 @@ def run_kernels(args) -> dict:
         st.positions = torch.arange(start, start + T, dtype=torch.int32, device="cuda")
         st.seq_of_token = torch.zeros(T, dtype=torch.int32, device="cuda")
         st.cu_q = torch.tensor([0, T], dtype=torch.int32, device="cuda")
-        st.h_q_len, st.n_seqs, st.decode_only = [T], 1, False
+        st.h_q_len, st.h_kv_len, st.n_seqs, st.decode_only = [T], [start + T], 1, False
         order = torch.randperm(n_pages) if scattered else torch.arange(n_pages)
         table = order.to(torch.int32).cuda().view(1, -1).contiguous()
         us = timed(lambda: ops.attention(q, out, kc, vc, st, table, 0, 1 / math.sqrt(d), nq, nkv, d, workspace=ws))
