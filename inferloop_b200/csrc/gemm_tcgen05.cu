@@ -1010,8 +1010,8 @@ int make_plan(Params& p, int M, int N, int K, int accumulate, int n_tickets, int
     // tile run as a cluster that shares the write-out, with two they go through a ticket.
     // (160 columns: 32 column tiles for a width of 5120, where 256 and 192 leave a quarter of
     // the SMs idle; its 32-bit write-out goes in 32-column pieces, the 16-bit one needs 64)
-    const struct { int ms, bn; double worth; } shapes[6] = {{2, 256, 1.0}, {2, 192, 0.93}, {2, 160, 0.9}, {1, 256, 0.85},
-                                                            {1, 160, 0.78}, {1, 128, 0.7}};
+    const struct { int ms, bn; double worth; } shapes[7] = {{2, 256, 1.0}, {2, 192, 0.93}, {2, 160, 0.9}, {1, 256, 0.85},
+                                                            {1, 192, 0.8}, {1, 160, 0.78}, {1, 128, 0.7}};
     const long long kb = (K + kBlockK - 1) / kBlockK;
     double best = -1.0;
     bn = 128;
@@ -1024,7 +1024,7 @@ int make_plan(Params& p, int M, int N, int K, int accumulate, int n_tickets, int
       // the part of the tiles' area that holds real rows and columns
       const double filled = ((double)M / (double)(tm * c.ms * kTileX)) * ((double)N / (double)(tn * c.bn));
       double score;
-      if (c.bn == 160 && t * 2 <= sm_count()) continue;        // (few tiles are cut into K ranges whose CTAs share 32-column pieces of 128 or 256)
+      if ((c.bn == 160 || (c.bn == 192 && c.ms == 1)) && t * 2 <= sm_count()) continue;   // (few tiles are cut into K ranges whose CTAs share 32-column pieces of 128 or 256)
       if (t * 2 <= sm_count()) {
         long long split = 1;
         while (split < 8 && t * split * 2 <= sm_count() && split * 2 <= kb) split *= 2;
@@ -1051,7 +1051,7 @@ int make_plan(Params& p, int M, int N, int K, int accumulate, int n_tickets, int
       for (int cms = 2; cms >= 1; --cms) {
         const long long tm = (M + cms * kTileX - 1) / (cms * kTileX), tn = (N + 255) / 256, t = tm * tn;
         const long long rounds = t / sm_count(), rest = t - rounds * sm_count();
-        if (rest == 0 || rest * 8 < sm_count()) continue;          // whole rounds, or too few tiles to matter
+        if (rest == 0 || t * 8 < sm_count()) continue;             // whole rounds, or a product of a handful of tiles
         const long long split = add_split(rest, kb);
         if (split < 2) continue;
         const double filled = ((double)M / (double)(tm * cms * kTileX)) * ((double)N / (double)(tn * 256));
@@ -1194,7 +1194,8 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
     }
   }
   if (bn == 256 && ms == 2) return launch<256, 3, false, 2>(mx, my, mo, p, (int)grid, stream);
-  if (bn == 192) return launch<192, 3, false, 2>(mx, my, mo, p, (int)grid, stream);
+  if (bn == 192 && ms == 2) return launch<192, 3, false, 2>(mx, my, mo, p, (int)grid, stream);
+  if (bn == 192) return launch<192, 5, false>(mx, my, mo, p, (int)grid, stream);
   if (bn == 160 && ms == 2) return launch<160, 3, false, 2>(mx, my, mo, p, (int)grid, stream);
   if (bn == 160) return launch<160, 5, false>(mx, my, mo, p, (int)grid, stream);
   if (bn == 256) return launch<256, 4, false>(mx, my, mo, p, (int)grid, stream);

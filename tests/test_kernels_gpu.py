@@ -297,7 +297,9 @@ TC_SHAPES = [(256, 19200, 64), (300, 9728, 128), (1, 128, 64), (3, 200, 72), (8,
              (2048, 6144, 256), (1500, 4100, 192),
              # accumulating: whole rounds and 12 tiles dealt out by K blocks; fewer tiles than SMs, all
              # dealt out by K blocks; one row block per tile.  The K ranges of a tile are added in memory.
-             (2048, 5120, 512), (512, 4096, 2048), (200, 1024, 4096)]
+             (2048, 5120, 512), (512, 4096, 2048), (200, 1024, 4096),
+             # 128 x 192 tiles: 128 of them where 256-wide ones would be 96
+             (512, 6144, 320)]
 
 
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)
