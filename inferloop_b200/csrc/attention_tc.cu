@@ -6,10 +6,12 @@
 // pair, so floor(128 / G) tokens of one sequence (a group size that does not divide 128
 // leaves the last 128 mod G rows unused: 3 of 128 for groups of 5); it walks that
 // sequence's keys 128 at a time.
-//   warp 0   one lane looks up the pages of the next 128 keys in the block table and issues
-//            the TMA loads: K and V each as one box per page and 64-wide slice of the head
-//            (128-byte swizzle; a page that is not held is requested outside the tensor, which
-//            TMA fills with zeros); Q once.
+//   warp 0   looks up the pages of the next 128 keys in the block table and issues the TMA
+//            loads: K and V each as one box per page (the tensor map has the key's place in
+//            its group of 8, the 64-wide slice of the head and the group as dimensions, so a
+//            whole page lands in the operand layout; 128-byte swizzle; a page that is not held
+//            is requested outside the tensor, which TMA fills with zeros), or one box for the
+//            tile when its pages follow one another in the pool; Q once.
 //   warp 1   allocates tensor memory (two S tiles of 128 columns and O of head-size columns);
 //            one lane issues S = Q K^T two tiles ahead (tile j+2 goes to the S tile that held
 //            tile j, right behind O += P V of tile j: the tensor core runs its operations in the
@@ -53,16 +55,16 @@ __host__ __device__ constexpr int stages_v(int d, int qb) { return d == 128 ? 2 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleStep = 8.0f;   // log2 units
 
-// K-major operand (rows of 128 bytes along K, 8-row groups 1024 bytes apart), 128-byte swizzle.
-__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
-  return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+// K-major operand (rows of 128 bytes along K, 8-row groups `group_bytes` apart), 128-byte swizzle.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr, uint32_t group_bytes = 1024) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)((group_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) | (2ull << 61);
 }
 // MN-major operand: 128-byte rows run along MN (64 elements), one row per K index, 8 K
-// indices per 1024-byte group (stride byte offset); the next 64 MN elements are
-// `mn_group_bytes` further (leading byte offset).  128-byte swizzle.
-__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t mn_group_bytes) {
+// indices per 1024-byte group, the groups `k_group_bytes` apart (stride byte offset); the next
+// 64 MN elements are `mn_group_bytes` further (leading byte offset).  128-byte swizzle.
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t mn_group_bytes, uint32_t k_group_bytes) {
   return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)((mn_group_bytes >> 4) & 0x3FFF) << 16) |
-         ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+         ((uint64_t)((k_group_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) | (2ull << 61);
 }
 // D 32-bit, A bfloat16 K-major, B bfloat16 K-major or MN-major.
 __host__ __device__ constexpr uint32_t instr_desc(int mma_m, int mma_n, int b_mn_major) {
@@ -159,8 +161,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   constexpr int kChunks = D / 64;                       // 64-wide slices of the head
   constexpr uint32_t kSlice = kRows * 128;              // bytes of a [128][64] bf16 slice
   constexpr uint32_t kQBytes = kChunks * kSlice;        // one row block of Q
-  constexpr uint32_t kKBytes = kChunks * kSlice;        // [slice][128 keys][64]
-  constexpr uint32_t kVBytes = kChunks * kSlice;        // [slice of d][128 keys][64]
+  // A K or V tile lies as [group of 8 keys][slice of the head][8 keys][64]: a page of the
+  // cache, whole, is one TMA box (key in group, slice, group in page are dimensions of the
+  // tensor map), and so is a run of pages that follow one another in the pool.  (With one box
+  // per page and slice, pages scattered over the pool cost 32 boxes of 2 KB per tile of K and
+  // V, and the TMA unit takes ≈26 ns per box whatever its size: 512 tokens behind 3,584 took
+  // 72 us against 48 us with the pages in order; whole pages: 58 us.  In order this layout is
+  // 2 % slower than slice-major tiles were; choosing between the two per stage cost the
+  // issuing thread more than that.)
+  constexpr uint32_t kKBytes = kChunks * kSlice;
+  constexpr uint32_t kVBytes = kChunks * kSlice;
+  constexpr uint32_t kGroup = kChunks * 1024;           // bytes from one group of 8 keys to the next
   constexpr int kStagesK = stages_k(D, QB), kStagesV = stages_v(D, QB);
   constexpr int KS = kKeys;                             // keys of a score tile
   constexpr int SUB = kKeys / KS;                       // score tiles per K / V tile
@@ -250,8 +261,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           tma_load_3d(q_s + q * kQBytes + c * kSlice, &map_q, q_full, c * 64, kvh * G, tok0 + t_first + q * tokens_per_block);
     }
     const int pages_per_tile = kKeys / p.page_size;
-    const int box = lane & 15, box_page = box / kChunks, box_slice = box % kChunks;
-    const bool has_box = box < pages_per_tile * kChunks;
+    const int box_page = lane & 15;                       // lanes 0-15 bring K pages, 16-31 V pages
+    const bool has_box = box_page < pages_per_tile;
+    const uint32_t page_bytes = (uint32_t)p.page_size * D * 2;
+    const int groups_per_page = p.page_size / 8;
+    const int run_boxes = pages_per_tile > 1 ? 2 : 1;     // a run of pages comes as two boxes side by side (one, if the tile is one page)
+
     bool ok = true;
     auto lookup = [&](int j) {                            // page of this lane's box of tile j
       int page = p.num_pages;                             // outside the tensor: TMA fills zeros
@@ -265,9 +280,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     };
     // The K ring and the V ring are filled independently, each as soon as it has a free stage
     // (scores run ahead of the products that free V stages, so K tiles are wanted earlier).
-    // The TMA unit takes tens of nanoseconds per box whatever its size, and a tile is up to
-    // 32 boxes of 2 KB.  When the tile's pages follow one another in the pool (the usual
-    // case: pages are handed out in order) one box per slice spans all of them.
+    // The TMA unit takes tens of nanoseconds per box whatever its size: a box is a whole page
+    // (up to 8 boxes of 4 KB per tile and tensor), or, when the tile's pages follow one another
+    // in the pool (pages are handed out in order), half the tile.
     int jk = 0, jv = 0;
     int page_k = lookup(0), page_v = page_k;               // pages of this lane's box of tiles jk and jv
     uint32_t idle = 0;
@@ -283,34 +298,34 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const int s = jk % kStagesK;
         const int page = page_k;
         page_k = lookup(jk + 1);                            // in flight while this tile's boxes are issued
-        if (lane == 0) mbar_expect_tx(k_full + 8 * s, kKBytes);
-        __syncwarp();
         const int first_page = __shfl_sync(0xffffffffu, page, 0);
         const bool run = __all_sync(0xffffffffu, !has_box || page == first_page + box_page) &&
                          first_page + pages_per_tile <= p.num_pages;
+        if (lane == 0) mbar_expect_tx(k_full + 8 * s, kKBytes);
+        __syncwarp();
         if (run) {
-          if (lane < kChunks)
-            tma_load_4d(k_s + s * kKBytes + lane * kSlice, &map_k_run, k_full + 8 * s, lane * 64, 0, kvh, first_page);
+          if (lane < run_boxes)
+            tma_load_5d(k_s + s * kKBytes + lane * (kKBytes / 2), &map_k_run, k_full + 8 * s, 0, 0, 0, kvh * groups_per_page,
+                        first_page + lane * (pages_per_tile / 2));
         } else if (has_box && lane < 16)
-          tma_load_4d(k_s + s * kKBytes + box_slice * kSlice + box_page * p.page_size * 128, &map_k, k_full + 8 * s,
-                      box_slice * 64, 0, kvh, page);
+          tma_load_5d(k_s + s * kKBytes + box_page * page_bytes, &map_k, k_full + 8 * s, 0, 0, 0, 0, page * p.nkv + kvh);
         ++jk;
       }
       if (free_v) {
         const int sv = jv % kStagesV;
         const int page = page_v;
         page_v = lookup(jv + 1);
-        if (lane == 0) mbar_expect_tx(v_full + 8 * sv, kVBytes);
-        __syncwarp();
         const int first_page = __shfl_sync(0xffffffffu, page, 0);
         const bool run = __all_sync(0xffffffffu, !has_box || page == first_page + box_page) &&
                          first_page + pages_per_tile <= p.num_pages;
+        if (lane == 0) mbar_expect_tx(v_full + 8 * sv, kVBytes);
+        __syncwarp();
         if (run) {
-          if (lane >= 16 && lane < 16 + kChunks)
-            tma_load_4d(v_s + sv * kVBytes + (lane - 16) * kSlice, &map_v_run, v_full + 8 * sv, (lane - 16) * 64, 0, kvh, first_page);
+          if (lane >= 16 && lane < 16 + run_boxes)
+            tma_load_5d(v_s + sv * kVBytes + (lane - 16) * (kVBytes / 2), &map_v_run, v_full + 8 * sv, 0, 0, 0, kvh * groups_per_page,
+                        first_page + (lane - 16) * (pages_per_tile / 2));
         } else if (has_box && lane >= 16)
-          tma_load_4d(v_s + sv * kVBytes + box_slice * kSlice + box_page * p.page_size * 128, &map_v, v_full + 8 * sv,
-                      box_slice * 64, 0, kvh, page);
+          tma_load_5d(v_s + sv * kVBytes + box_page * page_bytes, &map_v, v_full + 8 * sv, 0, 0, 0, 0, page * p.nkv + kvh);
         ++jv;
       }
       if (free_k || free_v) idle = 0;
@@ -337,7 +352,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             mma_bf16(acc, desc_k_major(q_s + q * kQBytes + c * kSlice) + 2 * k,
-                     desc_k_major(k_s + s * kKBytes + c * kSlice + h * (KS * 128)) + 2 * k, idesc_s, (c > 0 || k > 0) ? 1u : 0u);
+                     desc_k_major(k_s + s * kKBytes + c * 1024 + h * (KS / 8) * kGroup, kGroup) + 2 * k, idesc_s, (c > 0 || k > 0) ? 1u : 0u);
         tcgen05_commit(s_full + 8 * s_buf(q, u));
       };
       // The scores that next use an S buffer are issued right behind the O += P V that reads P
@@ -377,7 +392,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           const uint32_t p_t = s_cols(q, u);       // P: KS / 2 columns, two bfloat16 of consecutive keys each
 #pragma unroll
           for (int k = 0; k < KS / 16; ++k)   // 16 keys a step: 8 columns of P, two 8-key groups of V
-            mma_bf16_ts(tmem_o + (uint32_t)q * 128u, p_t + 8 * k, desc_mn_major(v_s + sv * kVBytes + (h * (KS / 16) + k) * 2048, kSlice),
+            mma_bf16_ts(tmem_o + (uint32_t)q * 128u, p_t + 8 * k, desc_mn_major(v_s + sv * kVBytes + (h * (KS / 16) + k) * 2 * kGroup, 1024, kGroup),
                         idesc_o, (u > 0 || k > 0) ? 1u : 0u);
           tcgen05_commit(o_done + 8 * q);
           pv_issued[q] = u + 1;
@@ -596,16 +611,25 @@ ILB_EXPORT int ilb_attention_prefill_tc(const void* q, void* out, const void* k_
     const cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(kRows / G)};
     if (encode(&mq, q, 3, dims, strides, box, "q")) return -1;
   }
-  {   // cache as (d, key in page, kv head, page); a box is one page of one head, one slice of the head
-    const cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)page_size, (cuuint64_t)nkv, (cuuint64_t)num_pages};
-    const cuuint64_t strides[3] = {(cuuint64_t)d * 2, (cuuint64_t)d * 2 * page_size, (cuuint64_t)d * 2 * page_size * nkv};
-    const cuuint32_t box[4] = {64, (cuuint32_t)page_size, 1, 1};
-    if (encode(&mk, k_cache, 4, dims, strides, box, "k cache")) return -1;
-    if (encode(&mv, v_cache, 4, dims, strides, box, "v cache")) return -1;
-    // the same, a box spanning all pages of a 128-key tile when their numbers follow one another
-    const cuuint32_t run[4] = {64, (cuuint32_t)page_size, 1, (cuuint32_t)(kKeys / page_size)};
-    if (encode(&mkr, k_cache, 4, dims, strides, run, "k cache (page run)")) return -1;
-    if (encode(&mvr, v_cache, 4, dims, strides, run, "v cache (page run)")) return -1;
+  {   // The cache [page][kv head][key][d] as (64 of d, key in its group of 8, slice of the head,
+      // group in the page, page x kv head): a box is the whole page of one head and lands as
+      // [group][slice][8 keys][64], the operand layout with its groups 1 or 2 KB apart.
+      // (The strides are not ascending: the encoder takes that; the coordinates are all zero
+      // but the last, so every copy starts on a 16-byte boundary.)
+    const cuuint64_t slices = (cuuint64_t)d / 64, groups = (cuuint64_t)page_size / 8;
+    const cuuint64_t dims[5] = {64, 8, slices, groups, (cuuint64_t)num_pages * nkv};
+    const cuuint64_t strides[4] = {(cuuint64_t)d * 2, 128, (cuuint64_t)d * 2 * 8, (cuuint64_t)d * 2 * page_size};
+    const cuuint32_t box[5] = {64, 8, (cuuint32_t)slices, (cuuint32_t)groups, 1};
+    if (encode(&mk, k_cache, 5, dims, strides, box, "k cache")) return -1;
+    if (encode(&mv, v_cache, 5, dims, strides, box, "v cache")) return -1;
+    // the same with (group in the page, kv head) as one dimension and the page as the last: a
+    // box spans half the pages of a 128-key tile when their numbers follow one another
+    const cuuint64_t rdims[5] = {64, 8, slices, groups * nkv, (cuuint64_t)num_pages};
+    const cuuint64_t rstrides[4] = {(cuuint64_t)d * 2, 128, (cuuint64_t)d * 2 * 8, (cuuint64_t)d * 2 * page_size * nkv};
+    const int pages_per_tile = kKeys / page_size;
+    const cuuint32_t run[5] = {64, 8, (cuuint32_t)slices, (cuuint32_t)groups, (cuuint32_t)(pages_per_tile > 1 ? pages_per_tile / 2 : 1)};
+    if (encode(&mkr, k_cache, 5, rdims, rstrides, run, "k cache (page run)")) return -1;
+    if (encode(&mvr, v_cache, 5, rdims, rstrides, run, "v cache (page run)")) return -1;
   }
   Params p{(__nv_bfloat16*)out, positions, cu_q, block_table, error_flag, max_blocks, n_seqs, nq, nkv, window,
            out_stride, page_size, num_pages, scale * kLog2e, skip_single ? 1 : 0};
