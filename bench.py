@@ -545,7 +545,7 @@ def run_kernels(args) -> dict:
     products = {}
     shapes = [("qkv", (nq + 2 * nkv) * d, H, {}), ("o", H, nq * d, {"accumulate": True}),
               ("gate_up", 2 * I, H, {"swiglu": True}), ("down", H, I, {"accumulate": True})]
-    for M in (8, 64, 512, 2048) if args.kernels in ("all", "products") else ():
+    for M in (8, 64, 128, 256, 512, 2048) if args.kernels in ("all", "products") else ():
         for name, N, K, kw in shapes:
             a = torch.randn(M, K, device="cuda").to(bf)
             weights = [torch.randn(N, K, device="cuda").to(bf) * 0.02 for _ in range(4)]
