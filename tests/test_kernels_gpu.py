@@ -81,7 +81,9 @@ def test_gather_rows_and_rope_table():
         assert (table.double().cpu() - ref).abs().max() < 1e-7      # one rounding to 32-bit
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 96, 64), (5, 100, 72), (16, 515, 80), (17, 64, 200), (130, 224, 96), (64, 1000, 1024)])
+# (K = 70, 50: rows that are no multiple of 16 bytes take the kernel that reads element by element)
+@pytest.mark.parametrize("M,N,K", [(1, 96, 64), (5, 100, 72), (16, 515, 80), (17, 64, 200), (130, 224, 96), (64, 1000, 1024),
+                                   (3, 50, 70), (40, 70, 50), (8, 300, 4096), (300, 260, 1040)])
 @pytest.mark.parametrize("in_dtype,out_dtype", [("float32", "float32"), ("bfloat16", "bfloat16"), ("bfloat16", "float32")])
 @pytest.mark.parametrize("bias,accumulate", [(False, False), (True, True)])
 def test_gemm_simt(M, N, K, in_dtype, out_dtype, bias, accumulate):
@@ -113,6 +115,27 @@ def test_gemm_simt_rows_do_not_depend_on_the_batch():
         outs.append(out[0].clone())
     for o in outs[1:]:
         assert torch.equal(o, outs[0])
+
+
+@pytest.mark.parametrize("M", [4, 40])
+def test_gemm_simt_kernels_agree_bit_for_bit(M):
+    """Operands that start on a 16-byte boundary take the kernels that read four k at a time,
+    others the kernel that reads element by element: the sums are the same chains in the same
+    order, so the same numbers give the same bits."""
+    K, N = 136, 200
+    torch.manual_seed(M)
+    a = torch.randn(M, K).cuda()
+    w = torch.randn(N, K).cuda()
+    out = torch.empty(M, N, device="cuda")
+    ops().gemm_simt(a, w, out)
+    shifted_a = torch.empty(M * K + 1, device="cuda")[1:].view(M, K)       # 4 bytes past a 16-byte boundary
+    shifted_a.copy_(a)
+    shifted_w = torch.empty(N * K + 1, device="cuda")[1:].view(N, K)
+    shifted_w.copy_(w)
+    assert shifted_a.data_ptr() % 16 != 0 and shifted_w.data_ptr() % 16 != 0
+    out2 = torch.empty(M, N, device="cuda")
+    ops().gemm_simt(shifted_a, shifted_w, out2)
+    assert torch.equal(out, out2)
 
 
 # ------------------------------------------------------------------ attention pieces
