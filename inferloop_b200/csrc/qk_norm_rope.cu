@@ -86,11 +86,27 @@ qk_norm_rope_kernel(const TQ* __restrict__ qkv, TQ* __restrict__ q_out,
 }
 
 // The common geometry, bfloat16 throughout, head size 128, rotation over the whole head: one
-// CTA per token, a warp takes every 8th head, a lane holds elements 2l, 2l+1 of each half of
-// the head (the two members of its rotation pairs) in registers: 4-byte accesses, no shared
-// memory, the loads of three heads in flight together.
-constexpr int kFastWarps = 8;
+// CTA per token; eight lanes take a head, a lane holding elements 8l .. 8l+7 of each half of
+// the head (the two members of its eight rotation pairs) in registers: 16-byte accesses, no
+// shared memory, a warp works on four heads at a time and has the loads of all its heads in
+// flight together (up to kFastUnroll passes).
+constexpr int kFastWarps = 4;
 constexpr int kFastUnroll = 3;
+
+__device__ __forceinline__ void unpack8(const uint4& r, float* x) {
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { x[2 * i] = __uint_as_float(w[i] << 16); x[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
+}
+__device__ __forceinline__ uint4 pack8(const float* x) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+    w[i] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
 
 __global__ void __launch_bounds__(kFastWarps * 32)
 qk_norm_rope_d128_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
@@ -103,10 +119,27 @@ qk_norm_rope_d128_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* _
   ilb::pdl_wait();
   constexpr int d = 128;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slot = lane >> 3, l8 = lane & 7;           // which of the warp's four heads; which eighth of each half
   const int t = blockIdx.x;
   const int total_heads = nq + 2 * nkv;
   const __nv_bfloat16* row = qkv + (size_t)t * qkv_stride;
-  // where this token's key and value go: looked up by the warps that hold a k or v head only
+  // the loads of all this lane's heads first
+  const int stride = kFastWarps * 4 * gridDim.y;       // heads between two passes (the CTAs of a token deal its heads out four by four)
+  const int h0 = (blockIdx.y * kFastWarps + warp) * 4 + slot;
+  uint4 raw[kFastUnroll][2];
+#pragma unroll
+  for (int u = 0; u < kFastUnroll; ++u) {
+    const int head = h0 + u * stride;
+    if (head < total_heads) {
+      const uint4* src = reinterpret_cast<const uint4*>(row + (size_t)head * d);
+      raw[u][0] = __ldg(src + l8);
+      raw[u][1] = __ldg(src + 8 + l8);
+    } else {
+      raw[u][0] = make_uint4(0u, 0u, 0u, 0u);
+      raw[u][1] = raw[u][0];
+    }
+  }
+  // where this token's key and value go: looked up by the lanes that hold a k or v head only
   size_t cache_off = 0;
   int cache_state = 0;                                // 0 not looked up, 1 held, -1 no page
   auto cache_row = [&]() {
@@ -126,65 +159,64 @@ qk_norm_rope_d128_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* _
     }
     return cache_state == 1;
   };
-  float2 cs[2] = {make_float2(1.f, 0.f), make_float2(1.f, 0.f)};
+  // cos and sin of this lane's eight pairs (j, j + 64), j = 8 l8 .. 8 l8 + 7
+  float2 cs[8];
   if (rope_table != nullptr) {
-    const float4 c = *reinterpret_cast<const float4*>(rope_table + (size_t)t * (d / 2) + 2 * lane);
-    cs[0] = make_float2(c.x, c.y);
-    cs[1] = make_float2(c.z, c.w);
+    const float4* c = reinterpret_cast<const float4*>(rope_table + (size_t)t * (d / 2) + 8 * l8);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 v = __ldg(c + i);
+      cs[2 * i] = make_float2(v.x, v.y);
+      cs[2 * i + 1] = make_float2(v.z, v.w);
+    }
   }
-  float wq[4] = {1.f, 1.f, 1.f, 1.f}, wk[4] = {1.f, 1.f, 1.f, 1.f};
-  if (q_weight != nullptr) { wq[0] = q_weight[2 * lane]; wq[1] = q_weight[2 * lane + 1]; wq[2] = q_weight[64 + 2 * lane]; wq[3] = q_weight[65 + 2 * lane]; }
-  if (k_weight != nullptr) { wk[0] = k_weight[2 * lane]; wk[1] = k_weight[2 * lane + 1]; wk[2] = k_weight[64 + 2 * lane]; wk[3] = k_weight[65 + 2 * lane]; }
-
-  // the CTAs of a token (gridDim.y of them: several when the tokens are few) deal its heads out warp by warp
-  const int stride = kFastWarps * gridDim.y;
-  for (int h0 = blockIdx.y * kFastWarps + warp; h0 < total_heads; h0 += stride * kFastUnroll) {
-    uint32_t raw[kFastUnroll][2];
+  auto weight8 = [&](const float* w, int half, float* out8) {      // weights of elements 64 half + 8 l8 .. + 7
+    const float4 a = __ldg(reinterpret_cast<const float4*>(w + 64 * half + 8 * l8));
+    const float4 b = __ldg(reinterpret_cast<const float4*>(w + 64 * half + 8 * l8) + 1);
+    out8[0] = a.x; out8[1] = a.y; out8[2] = a.z; out8[3] = a.w; out8[4] = b.x; out8[5] = b.y; out8[6] = b.z; out8[7] = b.w;
+  };
 #pragma unroll
-    for (int u = 0; u < kFastUnroll; ++u) {
-      const int head = h0 + u * stride;
-      if (head < total_heads) {
-        const uint32_t* src = reinterpret_cast<const uint32_t*>(row + (size_t)head * d);
-        raw[u][0] = src[lane];
-        raw[u][1] = src[32 + lane];
+  for (int u = 0; u < kFastUnroll; ++u) {
+    const int head = h0 + u * stride;
+    const bool valid = head < total_heads;
+    const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
+    float x[16];                                       // [0..7]: lower half, [8..15]: upper half
+    unpack8(raw[u][0], x);
+    unpack8(raw[u][1], x + 8);
+    const float* w = is_q ? q_weight : (is_k ? k_weight : nullptr);
+    // (every lane takes part in the exchange; a head past the end holds zeros)
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) ss = fmaf(x[i], x[i], ss);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+    if (!valid) continue;
+    if (w != nullptr) {
+      const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+      float wl[8], wh[8];
+      weight8(w, 0, wl);
+      weight8(w, 1, wh);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { x[i] = x[i] * inv * wl[i]; x[8 + i] = x[8 + i] * inv * wh[i]; }
+    }
+    if ((is_q || is_k) && rope_table != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float a = x[i], b = x[8 + i];
+        // Products and sums rounded separately, as the reference's scalar code does.
+        x[i] = __fsub_rn(__fmul_rn(a, cs[i].x), __fmul_rn(b, cs[i].y));
+        x[8 + i] = __fadd_rn(__fmul_rn(a, cs[i].y), __fmul_rn(b, cs[i].x));
       }
     }
-#pragma unroll
-    for (int u = 0; u < kFastUnroll; ++u) {
-      const int head = h0 + u * stride;
-      if (head >= total_heads) continue;                        // uniform over the warp
-      const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
-      const __nv_bfloat162 lo2 = *reinterpret_cast<const __nv_bfloat162*>(&raw[u][0]);
-      const __nv_bfloat162 hi2 = *reinterpret_cast<const __nv_bfloat162*>(&raw[u][1]);
-      float x[4] = {__low2float(lo2), __high2float(lo2), __low2float(hi2), __high2float(hi2)};
-      const float* w = is_q ? (q_weight ? wq : nullptr) : (is_k ? (k_weight ? wk : nullptr) : nullptr);
-      if (w != nullptr) {
-        float ss = fmaf(x[0], x[0], 0.f);
-        ss = fmaf(x[1], x[1], ss); ss = fmaf(x[2], x[2], ss); ss = fmaf(x[3], x[3], ss);
-        ss = warp_sum(ss);
-        const float inv = 1.0f / sqrtf(ss / (float)d + eps);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) x[i] = x[i] * inv * w[i];
-      }
-      if ((is_q || is_k) && rope_table != nullptr) {
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const float a = x[i], b = x[2 + i];
-          // Products and sums rounded separately, as the reference's scalar code does.
-          x[i] = __fsub_rn(__fmul_rn(a, cs[i].x), __fmul_rn(b, cs[i].y));
-          x[2 + i] = __fadd_rn(__fmul_rn(a, cs[i].y), __fmul_rn(b, cs[i].x));
-        }
-      }
-      __nv_bfloat16* dst;
-      if (is_q) dst = q_out + (size_t)t * q_out_stride + (size_t)head * d;
-      else {
-        if (!cache_row()) continue;
-        dst = (is_k ? k_cache : v_cache) + cache_off + (size_t)(is_k ? head - nq : head - nq - nkv) * page_size * d;
-      }
-      __nv_bfloat162 o0 = __floats2bfloat162_rn(x[0], x[1]), o1 = __floats2bfloat162_rn(x[2], x[3]);
-      reinterpret_cast<uint32_t*>(dst)[lane] = *reinterpret_cast<uint32_t*>(&o0);
-      reinterpret_cast<uint32_t*>(dst)[32 + lane] = *reinterpret_cast<uint32_t*>(&o1);
+    __nv_bfloat16* dst;
+    if (is_q) dst = q_out + (size_t)t * q_out_stride + (size_t)head * d;
+    else {
+      if (!cache_row()) continue;
+      dst = (is_k ? k_cache : v_cache) + cache_off + (size_t)(is_k ? head - nq : head - nq - nkv) * page_size * d;
     }
+    reinterpret_cast<uint4*>(dst)[l8] = pack8(x);
+    reinterpret_cast<uint4*>(dst)[8 + l8] = pack8(x + 8);
   }
 }
 
@@ -211,11 +243,15 @@ ILB_EXPORT int ilb_qk_norm_rope_cache(
               (dtype == kBF16 && cache_dtype == kF32), "qk_norm_rope: unknown dtypes");
   if (n_tokens == 0) return 0;
   if (dtype == kBF16 && (cache_dtype == kBF16 || k_cache == nullptr) && d == 128 && (rope_table == nullptr || rotary_dim == d) &&
-      qkv_stride % 2 == 0 && q_out_stride % 2 == 0 && ((uintptr_t)qkv % 4 == 0) && ((uintptr_t)q_out % 4 == 0) &&
-      ((uintptr_t)k_cache % 4 == 0) && ((uintptr_t)v_cache % 4 == 0) && ((uintptr_t)rope_table % 16 == 0)) {
-    const int per_token = (nq + 2 * nkv + kFastWarps - 1) / kFastWarps;      // CTAs that give every warp one head
-    int ny = 1;
-    while (ny < per_token && (long long)n_tokens * ny < 592) ++ny;
+      qkv_stride % 8 == 0 && q_out_stride % 8 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
+      ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0) && ((uintptr_t)rope_table % 16 == 0) &&
+      ((uintptr_t)q_weight % 16 == 0) && ((uintptr_t)k_weight % 16 == 0)) {
+    // CTAs per token: one takes kFastWarps x 4 heads per pass and up to kFastUnroll passes; more
+    // CTAs when the heads need them, and when the tokens are too few to fill the device
+    const int heads = nq + 2 * nkv, per_pass = kFastWarps * 4;
+    int ny = (heads + per_pass * kFastUnroll - 1) / (per_pass * kFastUnroll);
+    const int most = (heads + per_pass - 1) / per_pass;
+    while (ny < most && (long long)n_tokens * ny < 1184) ++ny;
     ilb::launch(qk_norm_rope_d128_kernel, dim3(n_tokens, ny), dim3(kFastWarps * 32), 0, stream,
                 (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, q_weight, k_weight, eps, (const float2*)rope_table,
                 positions, seq_of_token, block_table, max_blocks, page_size, num_pages, (__nv_bfloat16*)k_cache,
