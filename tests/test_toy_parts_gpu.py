@@ -1,6 +1,8 @@
-"""Two more toy parts, defined HERE and registered without a change to the framework's files
+"""More toy parts, defined HERE and registered without a change to the framework's files
 (GPU): a feed-forward that routes every token to one of three small experts, and a position
-encoding other than the architecture's (rotary angles of positions divided by a factor).
+encoding other than the architecture's (rotary angles of positions divided by a factor);
+further down a position encoding of two axes with what sits around the layers, and a norm
+and a block of another kind.
 
 The toy architecture alternates them layer by layer: layer 0 has the stock attention with the
 stock rotary encoding and the routed feed-forward, layer 1 the stock attention with the scaled
@@ -13,7 +15,8 @@ import torch
 import plain_qwen3 as plain
 from helpers import random_tokens
 from inferloop_b200.config import Architecture, ArchitectureRegistry, LayerSpec, ModelSpec, PartSpec, RunEntry
-from inferloop_b200.parts import FeedForward, PositionEncoding, register, unregister
+from inferloop_b200.parts import Block, FeedForward, Norm, PositionEncoding, register, unregister
+from inferloop_b200.parts import registry as parts_registry
 from inferloop_b200.weights.decl import WeightDecl
 
 pytestmark = pytest.mark.gpu
@@ -312,3 +315,143 @@ def test_embedding_multiplier_logits_map_and_inputs_per_token(dtype):
             engine.submit(prompt, SamplingParams(), 2)
     finally:
         unregister("position", "two_axis_rope")
+
+
+# ------------------------------------------------------------------ another norm and another arrangement of a block
+class CenteredNorm(Norm):
+    """(x - mean) / sqrt(var + eps) * weight + bias over the last dimension, in 32-bit: a norm
+    with two tensors, written with library elementwise operations (a toy, not a model's)."""
+
+    graph_safe = True
+
+    def __init__(self, spec, ctx, prefix="", width=0):
+        super().__init__(spec, ctx, prefix)
+        self.eps, self.width, self.p = float(spec["eps"]), int(width), prefix
+
+    def declare_weights(self):
+        return [WeightDecl(self.p + "weight", (self.width,), role="vector", init="norm"),
+                WeightDecl(self.p + "bias", (self.width,), role="vector", init="bias")]
+
+    def bind(self, tensors):
+        self.weight, self.bias = tensors[self.p + "weight"], tensors[self.p + "bias"]
+
+    def forward(self, x, out):
+        mean = x.mean(dim=-1, keepdim=True)
+        var = ((x - mean) ** 2).mean(dim=-1, keepdim=True)
+        out.copy_((x - mean) * torch.rsqrt(var + self.eps) * self.weight + self.bias)
+
+
+class ParallelBlock(Block):
+    """h += mixer(norm(h)) + ffn(norm(h)): ONE norm per layer, both branches read it."""
+
+    def __init__(self, spec, ctx, prefix="", layer=None):
+        super().__init__(spec, ctx, prefix)
+        self.hidden = int(spec["hidden_size"])
+        self.norm = parts_registry.build_norm(layer.norm, ctx, prefix + "ln.", width=self.hidden)
+        self.mixer = parts_registry.build("mixer", layer.mixer, ctx, prefix + "self_attn.")
+        self.ffn = parts_registry.build("feed_forward", layer.feed_forward, ctx, prefix + "mlp.")
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in (self.norm, self.mixer, self.ffn))
+
+    def declare_weights(self):
+        return self.norm.declare_weights() + self.mixer.declare_weights() + self.ffn.declare_weights()
+
+    def bind(self, tensors):
+        for part in (self.norm, self.mixer, self.ffn):
+            part.bind(tensors)
+
+    def cache_needs(self):
+        return self.mixer.cache_needs()
+
+    def scratch_bytes(self, tokens):
+        return tokens * self.hidden * 4 + self.mixer.scratch_bytes(tokens) + self.ffn.scratch_bytes(tokens)
+
+    def forward(self, hidden, step, cache):
+        normed = self.ctx.workspace.buffer("toy4.normed", hidden.shape, self.ctx.dtype)
+        self.norm.forward(hidden, normed)
+        self.mixer.forward(normed, hidden, step, cache)       # both branches add into the residual
+        self.ffn.forward(normed, hidden, step)
+
+
+def toy4_spec(cfg):
+    norm = PartSpec.make("centered", eps=cfg["eps"])
+    pos = PartSpec.make("rope_neox", theta=1e4, rotary_dim=16, head_dim=16)
+    attn = PartSpec.make("gqa_attention", hidden_size=H, num_heads=3, num_kv_heads=1, head_dim=16, qk_norm=False,
+                         qk_norm_eps=cfg["eps"], bias=False, window=None, position=pos)
+    dense = PartSpec.make("swiglu", hidden_size=H, intermediate_size=64)
+    block = PartSpec.make("parallel", hidden_size=H)
+    layers = tuple(LayerSpec(f"layers.{i}.", block, attn, dense, norm) for i in range(3))
+    return ModelSpec("Toy4ForCausalLM", V, H, 512, "embed_tokens.weight", None, "norm.weight", norm, layers,
+                     weight_prefixes=("model.",))
+
+
+def plain_toy4(w, cfg, tokens):
+    T = len(tokens)
+    x = w["embed_tokens.weight"][torch.tensor(tokens)]
+    pos = torch.arange(T)
+
+    def centered(v, p):
+        m = v.mean(dim=-1, keepdim=True)
+        var = ((v - m) ** 2).mean(dim=-1, keepdim=True)
+        return (v - m) / torch.sqrt(var + cfg["eps"]) * w[p + "weight"] + w[p + "bias"]
+
+    for layer in range(3):
+        p = f"layers.{layer}."
+        a = p + "self_attn."
+        n = centered(x, p + "ln.")
+        q = plain.rope_neox(plain.linear(n, w[a + "q_proj.weight"]).view(T, 3, 16), pos, 1e4, 16)
+        k = plain.rope_neox(plain.linear(n, w[a + "k_proj.weight"]).view(T, 1, 16), pos, 1e4, 16)
+        v = plain.linear(n, w[a + "v_proj.weight"]).view(T, 1, 16)
+        attn = plain.linear(plain.causal_attention(q, k, v, pos, None).reshape(T, 48), w[a + "o_proj.weight"])
+        x = x + attn + plain.swiglu_mlp(n, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    return plain.linear(centered(x, "norm."), w["embed_tokens.weight"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_another_norm_and_another_arrangement_of_a_block(dtype):
+    """A norm with a mean and a bias and a block whose two branches read one norm, both defined
+    in this file: built by name from the description, stepped in portions and single tokens
+    (through recorded graphs) and generated from through the entry point, against the plain
+    statement of the same model."""
+    from inferloop_b200 import Engine, SamplingParams
+    from inferloop_b200.engine import ModelRunner, StepEntry
+    from inferloop_b200.models.decoder import declare_weights
+    from inferloop_b200.weights import random_tensor, target_dtype
+    register("norm", "centered", CenteredNorm)
+    register("block", "parallel", ParallelBlock)
+    try:
+        registry = ArchitectureRegistry()
+        registry.register(Architecture("toy4", ("Toy4ForCausalLM",), dict, toy4_spec))
+        cfg = {"architectures": ["Toy4ForCausalLM"], "eps": 1e-5}
+        runner = ModelRunner.from_config(cfg, seed=17, dtype=dtype, page_size=8, num_pages=32, max_requests=3,
+                                         registry=registry)
+        DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+        w = {d.name: random_tensor(d, 17, target_dtype(d.role, DT), "cuda").double().cpu() for d in declare_weights(toy4_spec(cfg))}
+        assert "layers.1.ln.bias" in w and "norm.bias" in w and "layers.0.post_attention_layernorm.weight" not in w
+        toks = random_tokens(45, V, 23)
+        ref = plain_toy4(w, cfg, toks)
+        got, i = [], 0
+        for cut in (17, 2, 9, 1, 1, 1, 14):
+            got.append(runner.step([StepEntry("a", toks[i:i + cut], list(range(cut)))]).double().cpu().clone())
+            i += cut
+        runner.end("a")
+        assert runner.graphs is not None and runner.graphs.replays >= 2
+        g = torch.cat(got)
+        err = (g - ref).abs()
+        lim = 1e-5 + 1e-5 * ref.abs() if dtype == "float32" else torch.full_like(ref, 1e-2 * float(ref.abs().max()))
+        assert (err <= lim).all(), err.max().item()
+        engine = Engine(None, runner=runner, max_num_seqs=2, prefill_chunk_tokens=16)
+        out = engine.generate([toks[:13]], SamplingParams(), 5)[0]
+        seq = list(toks[:13])
+        for n in range(5):
+            logits = plain_toy4(w, cfg, seq)[-1]
+            if dtype == "float32":
+                assert out[n] == int(logits.argmax())
+            else:
+                assert logits[out[n]] >= logits.max() - 2e-2 * float(logits.abs().max())
+            seq.append(out[n])
+    finally:
+        unregister("norm", "centered")
+        unregister("block", "parallel")
