@@ -2,7 +2,7 @@
 """Measurement of the engine on one B200, random bf16 weights, synthetic token ids.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
-                    [--config 8b|14b-mixed|32b-long] [--breakdown] [--kernels [attention|products]]
+                    [--config 8b|14b-mixed|32b-long] [--breakdown] [--kernels [attention|products]] [--further]
 
 One JSON line on stdout.  The default (`--config 8b`) is the headline: Qwen3-8B layer sizes,
 36 layers, batch 8, 1,024-token prompts; a "step" is one decode step of the whole batch.
@@ -25,7 +25,8 @@ and in the prefill step, from a pair of CUDA events around every kernel (the eng
 of events around a lone launch costs).  `--kernels` times kernels alone instead, at the layer
 sizes of `--config`: the prefill attention at several lengths, and the layer's matrix products
 at several token counts beside `torch.matmul` on the same shapes (the library's plain product,
-for comparison only; it has no epilogue).
+for comparison only; it has no epilogue).  `--further` measures further sizes at the 8B layer
+sizes: decode at batches 16 to 256, a prompt of 32,768 tokens in portions, the 32-bit path.
 Peaks come from MEASURED_PEAKS.json beside this file when present, else the fallback
 figures 6.65 TB/s and 1.59 PFLOP/s.  Weights (15 GB and more) exceed L2 (126 MB), so every
 step reads them from HBM: no L2 flush is needed between timed steps.
@@ -571,6 +572,62 @@ def run_kernels(args) -> dict:
             "peaks": peaks()}
 
 
+def run_further(args) -> dict:
+    """Further sizes at the 8B layer sizes: decode at batches 16 to 256 (1,024-token prompts),
+    a prompt of 32,768 tokens in portions of 2,048 and of 8,192, and the 32-bit path (four
+    layers: 512-token prompts and decode at batch 8)."""
+    import torch
+    from inferloop_b200.engine import StepEntry
+    from inferloop_b200.engine.engine import Engine
+    out = {"metric": "further sizes, Qwen3-8B layer sizes", "decode": {}, "prefill_32768": {}, "float32_4_layers": {}, "peaks": peaks()}
+    cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    max_batch = 256
+    bench = Bench(cfg, SEED, max_batch * (-(-(PROMPT_LEN + 128) // PAGE)) + 256, max_batch, 4096, PREFILL_LEN)
+    for batch in (16, 32, 128, 256):
+        value, ms, kernels, ctx = bench.decode_device(batch, 32, 4, f"f{batch}_", PROMPT_LEN)
+        out["decode"][f"b{batch}"] = {"value": round(value, 1), "ms_per_step": round(ms, 3),
+                                      "roofline_frac": bench.decode_roofline(batch, ctx, ms)["frac"]}
+    del bench
+    torch.cuda.empty_cache()
+    length = 32768
+    long_cfg = dict(cfg, max_position_embeddings=length + 4096)
+    for chunk in (2048, 8192):
+        bench = Bench(long_cfg, SEED, (length + 4096) // PAGE + 64, 2, length + 1024, chunk)
+        r = bench.prefill_timed(length, 1, 3)
+        out["prefill_32768"][f"portions_of_{chunk}"] = {k: r[k] for k in ("value", "ms", "frac")}
+        del bench
+        torch.cuda.empty_cache()
+    cfg4 = dict(QWEN3_8B, num_hidden_layers=4)
+    engine = Engine(cfg4, dtype="float32", device=0, block_size=PAGE, num_gpu_blocks_override=8 * 40 + 64, max_num_seqs=8,
+                    max_model_len=2048, prefill_chunk_tokens=512, max_num_batched_tokens=520, random_weights_seed=SEED)
+    runner = engine.runner
+    ids = [f"x{i}" for i in range(8)]
+    toks = torch.randint(0, cfg4["vocab_size"], (8, 512), generator=torch.Generator().manual_seed(1)).tolist()
+    runner.step([StepEntry("warm", toks[0], [511])], draw_greedy=True)
+    runner.end("warm")
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for rid, t in zip(ids, toks):
+        runner.step([StepEntry(rid, t, [511])], draw_greedy=True)
+    b.record()
+    torch.cuda.synchronize()
+    out["float32_4_layers"]["prefill_512_ms"] = round(a.elapsed_time(b) / 8, 2)
+    entries = [StepEntry(rid, [1], [0]) for rid in ids]
+    for _ in range(3):
+        runner.step(entries, draw_greedy=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(20):
+        runner.step(entries, draw_greedy=True)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / 20
+    out["float32_4_layers"]["decode_b8_ms_per_step"] = round(ms, 3)
+    out["float32_4_layers"]["weights_gbs"] = round(runner.model.weight_bytes() / (ms / 1e3) / 1e9, 1)
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -582,6 +639,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers (named in config) to save time")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 / prefill side measurements")
     ap.add_argument("--breakdown", action="store_true", help="add the per-op-class share of device time")
+    ap.add_argument("--further", action="store_true", help="further sizes: batches to 256, a 32,768-token prompt, the 32-bit path")
     ap.add_argument("--kernels", nargs="?", const="all", default=None, choices=["all", "attention", "products"],
                     help="time kernels alone at the layer sizes of --config")
     args = ap.parse_args()
@@ -598,6 +656,9 @@ def main() -> int:
         args.warmup = 3
     if args.kernels:
         print(json.dumps(run_kernels(args)))
+        return 0
+    if args.further:
+        print(json.dumps(run_further(args)))
         return 0
     result = {"8b": run_8b, "14b-mixed": run_14b_mixed, "32b-long": run_32b_long}[args.config](args)
     print(json.dumps(result))
