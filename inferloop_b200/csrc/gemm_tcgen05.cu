@@ -998,10 +998,24 @@ long long add_split(long long rest, long long k_blocks) {
 // `can_add`: the product accumulates into a 32-bit output that the TMA write-out can reach,
 // so that the K ranges of a tile may be added in memory.
 int make_plan(Params& p, int M, int N, int K, int accumulate, int n_tickets, int max_ctas, bool can_add, Plan& plan) {
-  const bool swap = M <= 128;
+  // 33 to 128 tokens of a product that accumulates into a wide 32-bit output: tokens on the
+  // MMA's rows after all, 128 x 256 tiles cut into equal K ranges that meet in memory.  With
+  // the weight on the rows the K ranges of a tile are a cluster that exchanges 32-bit shares;
+  // here nothing is exchanged (4,096 x 4,096 at 128 tokens 16.4 -> 12.7 us, 5,120 x 25,600 at
+  // 64 tokens 56.0 -> 46.3 us; below 33 tokens the weight on the rows is as fast or faster).
+  bool few_in_memory = false;
+  if (M > 32 && M <= 128 && can_add && accumulate == 1 && g_sums_in_memory && max_ctas <= 0 && N >= 3072) {
+    const long long t = (N + 255) / 256, kb = (K + kBlockK - 1) / kBlockK;
+    const long long rest = t % sm_count();
+    few_in_memory = rest != 0 && t * 12 >= sm_count() && add_split(rest, kb) >= 2;
+  }
+  const bool swap = M <= 128 && !few_in_memory;
   bool tail = false;
   int bn, ms = 1;                                    // ms: 128-row blocks of X per tile
-  if (swap) {
+  if (few_in_memory) {
+    bn = 256;
+    tail = true;
+  } else if (swap) {
     bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
   } else {
     // Many tokens: the tile shape that keeps the most SMs busy in whole rounds, larger tiles
@@ -1051,12 +1065,12 @@ int make_plan(Params& p, int M, int N, int K, int accumulate, int n_tickets, int
       for (int cms = 2; cms >= 1; --cms) {
         const long long tm = (M + cms * kTileX - 1) / (cms * kTileX), tn = (N + 255) / 256, t = tm * tn;
         const long long rounds = t / sm_count(), rest = t - rounds * sm_count();
-        if (rest == 0 || t * 8 < sm_count()) continue;             // whole rounds, or a product of a handful of tiles
+        if (rest == 0 || t * 12 < sm_count()) continue;            // whole rounds, or a product of a handful of tiles
         const long long split = add_split(rest, kb);
         if (split < 2) continue;
         const double filled = ((double)M / (double)(tm * cms * kTileX)) * ((double)N / (double)(tn * 256));
         const double time = (double)rounds + 1.0 / (double)split + 0.03;      // in tile times; the last term: a second write-out
-        const double score = (cms == 2 ? 1.0 : 0.85) * filled * ((double)t / (double)sm_count()) / time;
+        const double score = (cms == 2 ? 1.0 : 0.95) * filled * ((double)t / (double)sm_count()) / time;
         if (score > best) { best = score; bn = 256; ms = cms; tail = true; }
       }
     }
