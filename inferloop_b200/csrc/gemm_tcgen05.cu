@@ -998,13 +998,15 @@ long long add_split(long long rest, long long k_blocks) {
 // `can_add`: the product accumulates into a 32-bit output that the TMA write-out can reach,
 // so that the K ranges of a tile may be added in memory.
 int make_plan(Params& p, int M, int N, int K, int accumulate, int n_tickets, int max_ctas, bool can_add, Plan& plan) {
-  // 33 to 128 tokens of a product that accumulates into a wide 32-bit output: tokens on the
+  // 65 to 128 tokens of a product that accumulates into a wide 32-bit output: tokens on the
   // MMA's rows after all, 128 x 256 tiles cut into equal K ranges that meet in memory.  With
   // the weight on the rows the K ranges of a tile are a cluster that exchanges 32-bit shares;
   // here nothing is exchanged (4,096 x 4,096 at 128 tokens 16.4 -> 12.7 us, 5,120 x 25,600 at
-  // 64 tokens 56.0 -> 46.3 us; below 33 tokens the weight on the rows is as fast or faster).
+  // 64 tokens 56.0 -> 46.3 us alone; but inside a decode step, between its neighbours, the
+  // weight on the rows stays ahead up to 64 tokens: 5.86 against 5.90 ms at batch 64, and
+  // 8.35 against 7.86 ms at batch 96).
   bool few_in_memory = false;
-  if (M > 32 && M <= 128 && can_add && accumulate == 1 && g_sums_in_memory && max_ctas <= 0 && N >= 3072) {
+  if (M > 64 && M <= 128 && can_add && accumulate == 1 && g_sums_in_memory && max_ctas <= 0 && N >= 3072) {
     const long long t = (N + 255) / 256, kb = (K + kBlockK - 1) / kBlockK;
     const long long rest = t % sm_count();
     few_in_memory = rest != 0 && t * 12 >= sm_count() && add_split(rest, kb) >= 2;

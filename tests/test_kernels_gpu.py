@@ -323,8 +323,8 @@ TC_SHAPES = [(256, 19200, 64), (300, 9728, 128), (1, 128, 64), (3, 200, 72), (8,
              (2048, 5120, 512), (512, 4096, 2048), (200, 1024, 4096),
              # 128 x 192 tiles: 128 of them where 256-wide ones would be 96
              (512, 6144, 320),
-             # 33 to 128 tokens into a wide output: accumulating, tokens go on the MMA's rows and the K ranges meet in memory
-             (100, 4096, 1024), (48, 5120, 2048)]
+             # 65 to 128 tokens into a wide output: accumulating, tokens go on the MMA's rows and the K ranges meet in memory
+             (100, 4096, 1024), (72, 5120, 2048)]
 
 
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)
@@ -384,9 +384,9 @@ def test_gemm_tcgen05_last_round_in_memory_can_be_switched_off():
     ref = base.double().cpu() + a.double().cpu() @ w.double().cpu().T
     assert o.gemm_tc_plan(M, N, K, accumulate=True)["sums_meet_in_memory"] == 1
     assert o.gemm_tc_plan(200, 256, 1024, accumulate=True)["sums_meet_in_memory"] == 0      # a handful of tiles: never
-    few = o.gemm_tc_plan(100, 4096, 1024, accumulate=True)                                  # 33 to 128 tokens, a wide output
+    few = o.gemm_tc_plan(100, 4096, 1024, accumulate=True)                                  # 65 to 128 tokens, a wide output
     assert few["sums_meet_in_memory"] == 1 and few["swap"] == 0 and few["row_blocks"] == 1
-    assert o.gemm_tc_plan(32, 4096, 1024, accumulate=True)["swap"] == 1 and o.gemm_tc_plan(100, 4096, 1024)["swap"] == 1
+    assert o.gemm_tc_plan(64, 4096, 1024, accumulate=True)["swap"] == 1 and o.gemm_tc_plan(100, 4096, 1024)["swap"] == 1
     out = base.clone()
     o.gemm_tc(a, w, out, accumulate=True)
     close(out, ref, "float32", scale=float(ref.abs().max()), what="last round in memory")
