@@ -238,7 +238,7 @@ def test_attention_finds_one_far_key_and_respects_the_window_edge(dtype):
 
 
 @pytest.mark.parametrize("nq,nkv,d,rd,page_size", [(4, 2, 16, 16, 4), (6, 2, 32, 32, 8), (5, 5, 48, 24, 16), (8, 2, 128, 128, 16), (2, 1, 80, 80, 32),
-                                                    (3, 1, 128, 128, 32), (26, 2, 128, 128, 16), (8, 2, 128, 64, 16)])
+                                                    (3, 1, 128, 128, 32), (26, 2, 128, 128, 16), (8, 2, 128, 64, 16), (64, 8, 128, 128, 16), (40, 8, 128, 128, 16)])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("use_norm", [True, False])
 def test_qk_norm_rope_cache(nq, nkv, d, rd, page_size, dtype, use_norm):
