@@ -104,12 +104,13 @@ def test_portions_of_changing_size(folders, requests_of, name, dtype):
     check_trace(run_trace_inprocess(r, trace), trace, reference(folders, requests_of, name, dtype), dtype, f"{name} portions")
 
 
-def mixed_trace(reqs, seed=0, tail=12):
+def mixed_trace(reqs, seed=0, tail=12, sizes=(2, 3, 5, 8, 13, 17, 29), live_max=4):
     """Up to four live requests; each step holds portions of some beside single decoded
     tokens of others, some requests sit a step out; a finished request's place is taken
     by the next one.  Returns the trace and the most tokens held at any time (each
     request rounded up to 64)."""
     rng = random.Random(seed)
+    sizes = list(sizes)
     # every request runs twice, so late arrivals land on pages others have given back
     queue = [(f"{rid}.{rep}", rid) for rep in range(2) for rid in reqs]
     rng.shuffle(queue)
@@ -117,7 +118,7 @@ def mixed_trace(reqs, seed=0, tail=12):
     trace, peak = Trace(), 0
     alias = {}
     while queue or live:
-        while queue and len(live) < 4:
+        while queue and len(live) < live_max:
             tid, rid = queue.pop()
             live.append(tid); cursor[tid] = 0; alias[tid] = rid
         entries, ended = [], []
@@ -126,7 +127,7 @@ def mixed_trace(reqs, seed=0, tail=12):
             if len(live) > 1 and rng.random() < 0.25:
                 continue                                       # sits this step out
             left = len(toks) - cursor[tid]
-            n = 1 if left <= tail else min(left - tail, rng.choice([2, 3, 5, 8, 13, 17, 29]))
+            n = 1 if left <= tail else min(left - tail, rng.choice(sizes))
             want = list(range(n)) if rng.random() < 0.7 else [n - 1]
             entries.append((tid, toks[cursor[tid]:cursor[tid] + n], want))
             cursor[tid] += n
@@ -157,6 +158,28 @@ def test_mixed_batches_on_few_pages(folders, requests_of, name, dtype):
     assert all(g["free"] == g["total"] for g in info["groups"])
     assert any(len(s["entries"]) >= 3 and any(len(e["tokens"]) > 1 for e in s["entries"])
                and any(len(e["tokens"]) == 1 for e in s["entries"]) for s in trace.steps)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,seed", [("C", 0), ("D", 1), ("E", 2), ("F", 3), ("D", 4), ("F", 5)])
+def test_random_mixed_traces(folders, requests_of, name, seed, dtype):
+    """Schedules drawn at random beyond the fixed ones above: portions up to 260 tokens (the
+    many-token kernels beside single tokens), up to six live requests, decoding tails from none
+    to 33 tokens, pages two and four times the configuration's, pools with and without slack.
+    (Thousands of such traces were run once while the kernels were written; these stay.)"""
+    from inferloop_b200.engine import ModelRunner
+    rng = random.Random(77 * seed + 5)
+    sizes = rng.choice([[1, 2, 40, 70, 150], [16, 32, 64, 128, 129, 200], [3, 97, 260], [2, 3, 5, 8, 13, 17, 29]])
+    tail, live_max = rng.choice([0, 1, 12, 33]), rng.choice([2, 4, 6])
+    page = min(128, CONFIGS[name][2] * rng.choice([1, 2, 4]))
+    reqs = requests_of[name]
+    trace, peak, alias = mixed_trace(reqs, seed=seed, tail=tail, sizes=sizes, live_max=live_max)
+    pages = -(-(peak + 64 * live_max) // page) if page > 64 else (peak + rng.choice([0, 64])) // page
+    r = ModelRunner.from_folder(folders[name], dtype=dtype, page_size=page, num_pages=pages, max_requests=8)
+    out = run_trace_inprocess(r, trace)
+    ref = reference(folders, requests_of, name, dtype)
+    check_trace(out, trace, {tid: ref[rid] for tid, rid in alias.items()}, dtype, f"{name} random trace {seed}")
+    assert all(g["free"] == g["total"] for g in r.cache.inspect()["groups"])
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
