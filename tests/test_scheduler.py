@@ -204,3 +204,73 @@ def test_a_whole_portion_beside_decodes_is_trimmed_to_the_token_tile():
     e.submit(random_tokens(70, 50, 1), SamplingParams(), 2)
     e.step()
     assert e.runner.steps[0] == [(0, 32)]                                     # alone in its step: whole
+
+
+# ------------------------------------------------------------------ random workloads
+from hypothesis import HealthCheck, given, settings, strategies as st
+
+
+@settings(max_examples=60, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@given(st.data())
+def test_random_workloads_keep_the_invariants(data):
+    """Requests of random lengths arrive before and between steps, some are aborted, the pool
+    is anywhere from one request's need to plenty, budgets and the token tile vary.  Whatever
+    the schedule: every step fits its budgets and the pages (the runner asserts that), every
+    request that is not aborted gets exactly the tokens of a run alone, stops at its stop
+    token or its length, and every page and slot is back at the end."""
+    draw = data.draw
+    page = draw(st.sampled_from([2, 4, 8]))
+    window = draw(st.sampled_from([None, None, 6, 16]))
+    chunk = draw(st.sampled_from([2, 5, 8, 16]))
+    max_seqs = draw(st.integers(1, 5))
+    budget = chunk + draw(st.integers(0, 6))
+    multiple = draw(st.sampled_from([1, 1, 4]))
+    n_req = draw(st.integers(1, 9))
+    lens = [draw(st.integers(1, 40)) for _ in range(n_req)]
+    news = [draw(st.integers(1, 12)) for _ in range(n_req)]
+    stop = tuple(draw(st.lists(st.integers(0, 49), max_size=6, unique=True)))
+    arrive = [draw(st.integers(0, 6)) for _ in range(n_req)]          # the step before which a request is submitted
+    abort_at = {i: draw(st.integers(1, 10)) for i in range(n_req) if draw(st.integers(0, 5)) == 0}
+    longest = max(l + n for l, n in zip(lens, news))
+    pages = -(-longest // page) + 1 + draw(st.sampled_from([0, 1, 3, 20, 200]))
+    params = SamplingParams(eos_tokens=stop) if draw(st.booleans()) else SamplingParams(temperature=0.9, seed=7, eos_tokens=stop)
+    prompts = [random_tokens(l, 50, 900 + 13 * i + l) for i, l in enumerate(lens)]
+
+    def alone(i):
+        e = make(FakeRunner(num_pages=400, page_size=page, window=window), max_num_seqs=1, prefill_chunk_tokens=chunk,
+                 max_num_batched_tokens=chunk + 1)
+        e.submit(prompts[i], params, news[i], request_id=i)
+        while not e.is_idle():
+            e.step()
+        return e.result(i).generated
+
+    runner = FakeRunner(num_pages=pages, page_size=page, window=window, max_requests=8)
+    e = make(runner, max_num_seqs=max_seqs, prefill_chunk_tokens=chunk, max_num_batched_tokens=budget)
+    e.scheduler.config.step_token_multiple = multiple
+    submitted, aborted, step = set(), set(), 0
+    while len(submitted) < n_req or not e.is_idle():
+        for i in range(n_req):
+            if i not in submitted and arrive[i] <= step:
+                e.submit(prompts[i], params, news[i], request_id=i)
+                submitted.add(i)
+        for i, when in abort_at.items():
+            if i in submitted and i not in aborted and when == step:
+                e.abort(i)
+                aborted.add(i)
+        e.step()
+        step += 1
+        assert step < 2000, "the schedule does not end"
+    budget = e.scheduler.config.max_num_batched_tokens       # (raised to a portion beside every other sequence's token, if below)
+    for s in runner.steps:
+        assert sum(n for _, n in s) <= budget and len(s) <= max_seqs and all(n <= chunk for _, n in s)
+    for i in range(n_req):
+        got = e.result(i).generated
+        if i in aborted:
+            want = alone(i)
+            assert got == want[:len(got)]
+            continue
+        assert got == alone(i)
+        hits = [k for k, t in enumerate(got) if t in stop]
+        assert (hits and hits[0] == len(got) - 1) or (not hits and len(got) == news[i])
+    assert all(v == pages for v in runner.cache.free_pages().values())
+    assert runner.cache.slots.num_free == runner.cache.slots.num_slots
