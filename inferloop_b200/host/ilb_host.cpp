@@ -223,6 +223,31 @@ int dtype_width(const std::string& d) {
   return 0;
 }
 
+// Well-formed UTF-8 (RFC 3629: no overlong forms, no surrogates, nothing past U+10FFFF); the
+// offset of the first byte that is not, or -1.  JSON text is UTF-8 (RFC 8259 section 8.1), and a
+// tensor's name reaches the caller as a string.
+long long first_bad_utf8(const unsigned char* s, long long n) {
+  long long i = 0;
+  while (i < n) {
+    const unsigned char c = s[i];
+    int more;
+    uint32_t cp, low;
+    if (c < 0x80) { ++i; continue; }
+    else if (c >= 0xC2 && c <= 0xDF) { more = 1; cp = c & 0x1F; low = 0x80; }
+    else if (c >= 0xE0 && c <= 0xEF) { more = 2; cp = c & 0x0F; low = 0x800; }
+    else if (c >= 0xF0 && c <= 0xF4) { more = 3; cp = c & 0x07; low = 0x10000; }
+    else return i;
+    if (i + more >= n) return i;
+    for (int k = 1; k <= more; ++k) {
+      if ((s[i + k] & 0xC0) != 0x80) return i;
+      cp = (cp << 6) | (s[i + k] & 0x3F);
+    }
+    if (cp < low || cp > 0x10FFFF || (cp >= 0xD800 && cp <= 0xDFFF)) return i;
+    i += more + 1;
+  }
+  return -1;
+}
+
 int st_parse(StFile& f, const char* path) {
   if (f.size < 8) return fail(kFormat, "%s: file is shorter than its 8-byte length field", path);
   unsigned long long n = 0;
@@ -231,6 +256,8 @@ int st_parse(StFile& f, const char* path) {
   if (8 + n > f.size) return fail(kFormat, "%s: header length %llu runs past the end of the file", path, n);
   f.data_start = 8 + (long long)n;
   const long long payload = (long long)f.size - f.data_start;
+  const long long bad = first_bad_utf8(f.map + 8, (long long)n);
+  if (bad >= 0) return fail(kFormat, "%s: header is not valid UTF-8 at byte %lld", path, bad);
   Json j;
   j.begin = j.p = reinterpret_cast<const char*>(f.map + 8);
   j.end = j.p + n;
@@ -305,11 +332,14 @@ int st_parse(StFile& f, const char* path) {
         if (width == 0) return fail(kFormat, "%s: %s: unsupported dtype %s", path, name.c_str(), e.dtype.c_str());
         if (e.end < e.begin || e.end > payload)
           return fail(kFormat, "%s: %s: offsets [%lld, %lld) outside payload", path, name.c_str(), e.begin, e.end);
-        unsigned long long count = 1;
+        unsigned long long count = 1, span = 1;     // elements; the same with empty dimensions counted as one (what strides are made of)
         bool over = false;
         for (long long s : e.shape) {
           if (s != 0 && count > 0x7FFFFFFFFFFFFFFFull / (unsigned long long)s) over = true;
           count *= (unsigned long long)s;
+          const unsigned long long d = s > 0 ? (unsigned long long)s : 1ull;
+          if (span > 0x7FFFFFFFFFFFFFFFull / d) over = true;       // [0, 2^62, 2^62] holds nothing, and no tensor library can stride it
+          span *= d;
         }
         if (over || count > 0x7FFFFFFFFFFFFFFFull / (unsigned)width || (long long)(count * width) != e.end - e.begin) {
           std::string shp = "[";

@@ -71,6 +71,17 @@ def test_container_checks(tmp_path):
         fh.write(struct.pack("<Q", 1 << 40))
     with pytest.raises(SafetensorsError, match="exceeds"):
         SafetensorsFile(p)
+    with open(p, "wb") as fh:       # a name that is not UTF-8 (found by mutating headers at random)
+        blob = b'{"a\xd9\x20":{"dtype":"F32","shape":[1],"data_offsets":[0,4]}}'
+        fh.write(struct.pack("<Q", len(blob)) + blob + b"\0" * 4)
+    with pytest.raises(SafetensorsError, match="UTF-8"):
+        SafetensorsFile(p)
+    # an empty tensor whose other dimensions no strides can span
+    _raw_file(p, {"a": {"dtype": "F32", "shape": [0, 1 << 62, 8], "data_offsets": [0, 0]}}, b"")
+    with pytest.raises(SafetensorsError, match="needs"):
+        SafetensorsFile(p)
+    _raw_file(p, {"a": {"dtype": "F32", "shape": [0, 1 << 40], "data_offsets": [0, 0]}}, b"")
+    assert SafetensorsFile(p).tensor("a").shape == (0, 1 << 40)
 
 
 def test_index_and_shard_path_escape(tmp_path):
