@@ -69,9 +69,6 @@ class Qwen3Config:
 
     # ------------------------------------------------------------- validation
     def __post_init__(self) -> None:
-        if not self.layer_types:
-            object.__setattr__(
-                self, "layer_types", ("full_attention",) * self.num_hidden_layers)
         for name in ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers",
                      "num_attention_heads", "num_key_value_heads", "head_dim",
                      "max_position_embeddings"):
@@ -80,6 +77,9 @@ class Qwen3Config:
                 raise ConfigError(f"{name} must be a positive integer, found {v!r}")
         if self.num_hidden_layers > MAX_HIDDEN_LAYERS:
             raise ConfigError("invalid layer count")
+        if not self.layer_types:
+            object.__setattr__(
+                self, "layer_types", ("full_attention",) * self.num_hidden_layers)
         if self.num_attention_heads % self.num_key_value_heads != 0:
             raise ConfigError(
                 f"num_attention_heads ({self.num_attention_heads}) must be a multiple of "

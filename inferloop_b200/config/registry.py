@@ -49,12 +49,21 @@ class ArchitectureRegistry:
         out: List[str] = []
 
         def collect(d: Mapping[str, Any]) -> None:
-            for name in d.get("architectures") or ():
+            names = d.get("architectures") or ()
+            if isinstance(names, str):
+                names = (names,)
+            elif not isinstance(names, (list, tuple)):
+                raise ConfigError(f"architectures must be a list of names, found {names!r}")
+            for name in names:
+                if not isinstance(name, str):
+                    raise ConfigError(f"architectures must be a list of names, found {names!r}")
                 if name not in out:
-                    out.append(str(name))
+                    out.append(name)
             mt = d.get("model_type")
+            if mt is not None and not isinstance(mt, str):
+                raise ConfigError(f"model_type must be a name, found {mt!r}")
             if mt is not None and mt not in out:
-                out.append(str(mt))
+                out.append(mt)
             tc = d.get("text_config")
             if isinstance(tc, Mapping):
                 collect(tc)

@@ -104,3 +104,22 @@ def test_config_round_trip():
     for raw in (CONFIG_A, CONFIG_B, CONFIG_C):
         cfg = Qwen3Config.from_dict(raw)
         assert Qwen3Config.from_dict(cfg.to_dict()) == cfg
+
+
+@pytest.mark.parametrize("patch", [{"architectures": 64}, {"architectures": True}, {"architectures": [7]}, {"model_type": 3, "architectures": None},
+                                   {"num_hidden_layers": 1 << 40}, {"architectures": 1e30}])
+def test_malformed_values_are_refused_with_the_package_own_error(patch):
+    """Found by mutating configurations at random: values of the wrong kind where names are
+    expected, and a layer count that no memory holds, used to surface as TypeError and
+    MemoryError."""
+    from inferloop_b200.config import default_registry
+    raw = dict(CONFIG_A, **patch)
+    with pytest.raises(ConfigError):
+        arch = default_registry().resolve(raw)
+        arch.build_spec(arch.read_config(raw))
+
+
+def test_architectures_may_be_one_name():
+    from inferloop_b200.config import default_registry
+    raw = dict(CONFIG_A, architectures="Qwen3ForCausalLM")
+    assert default_registry().resolve(raw).name
