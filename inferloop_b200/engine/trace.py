@@ -54,16 +54,26 @@ def main(argv: List[str] | None = None) -> int:
         args.model, dtype=args.dtype, device=args.device, page_size=args.block_size,
         num_pages=num_pages, max_requests=16,
         progress=lambda m: print(f"[trace_run] {m}", file=sys.stderr, flush=True))
-    for line in sys.stdin:
+    for line_no, line in enumerate(sys.stdin, 1):
         line = line.strip()
         if not line:
             continue
-        rec = json.loads(line)
-        step_no = rec["step"]
-        entries = [StepEntry(e["id"], [int(t) for t in e["tokens"]], [int(w) for w in e.get("want", [])])
-                   for e in rec.get("entries", [])]
+        try:
+            rec = json.loads(line)
+            step_no = rec["step"]
+            entries = [StepEntry(e["id"], [int(t) for t in e["tokens"]], [int(w) for w in e.get("want", [])])
+                       for e in rec.get("entries", [])]
+            ended = list(rec.get("end", []))
+        except (json.JSONDecodeError, KeyError, TypeError, ValueError, AttributeError) as e:
+            print(f"trace_run: line {line_no} is not a step ({type(e).__name__}: {e}); expected "
+                  '{"step": n, "entries": [{"id": ..., "tokens": [...], "want": [...]}], "end": [...]}', file=sys.stderr)
+            return 2
         if entries:
-            logits = runner.step(entries)
+            try:
+                logits = runner.step(entries)
+            except ValueError as e:                 # what the step function refuses: tokens outside the vocabulary, no room, ...
+                print(f"trace_run: step {step_no}: {e}", file=sys.stderr)
+                return 2
             if logits.shape[0] > 0:
                 host = logits.to("cpu", torch.float32).contiguous().numpy().astype("<f4", copy=False)
                 host.tofile(os.path.join(args.out, f"{step_no}.f32"))
@@ -71,7 +81,7 @@ def main(argv: List[str] | None = None) -> int:
                 torch.cuda.current_stream(runner.device).synchronize()
             from ..csrc import ops
             ops.check_device_errors()
-        for rid in rec.get("end", []):
+        for rid in ended:
             if runner.is_live(rid):
                 runner.end(rid)
         print(f"done {step_no}", flush=True)

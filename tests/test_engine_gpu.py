@@ -196,6 +196,25 @@ def test_the_trace_program_itself(folders, requests_of, dtype, tmp_path):
     assert written == sorted(trace.rows)           # a file exactly where something was wanted
 
 
+def test_the_trace_program_says_what_is_wrong_with_a_step(folders, tmp_path):
+    """A line that is no step, and a step that the step function refuses (a token outside the
+    vocabulary), end the program with status 2 and one line that names the place; the steps
+    before them were run and reported."""
+    import subprocess
+    import sys
+    from helpers import ROOT
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folders["A"], "--dtype", "float32",
+           "--out", str(tmp_path / "out"), "--max-tokens", "128", "--block-size", str(CONFIGS["A"][2])]
+    good = '{"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [2]}], "end": []}\n'
+    for bad, needle in (('{"step": 1, "entries": [{"id": "a", "tokens": "x"}]}\n', "line 2 is not a step"),
+                        ('not json\n', "line 2 is not a step"),
+                        ('{"step": 1, "entries": [{"id": "a", "tokens": [999999], "want": [0]}], "end": []}\n', "step 1:")):
+        proc = subprocess.run(cmd, input=good + bad, capture_output=True, text=True, timeout=600)
+        assert proc.returncode == 2, (proc.returncode, proc.stderr)
+        assert proc.stdout.splitlines() == ["done 0"]
+        assert needle in proc.stderr and "Traceback" not in proc.stderr, proc.stderr
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_long_decoding(folders, dtype, tmp_path):
     """A short prompt, then 700 tokens one by one: every page edge is crossed many times."""
