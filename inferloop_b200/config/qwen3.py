@@ -195,7 +195,7 @@ class Qwen3Config:
     def from_json(cls, text: str) -> "Qwen3Config":
         try:
             raw = json.loads(text)
-        except json.JSONDecodeError as e:
+        except (json.JSONDecodeError, RecursionError) as e:
             raise ConfigError(f"config.json is not valid JSON: {e}") from None
         return cls.from_dict(raw)
 

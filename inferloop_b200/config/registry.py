@@ -102,7 +102,7 @@ def read_model_config(text: str, registry: ArchitectureRegistry | None = None):
     """Parse config.json text; return (architecture entry, typed config, ModelSpec)."""
     try:
         raw = json.loads(text)
-    except json.JSONDecodeError as e:
+    except (json.JSONDecodeError, RecursionError) as e:      # (brackets nested thousands deep end the parser's recursion)
         raise ConfigError(f"config.json is not valid JSON: {e}") from None
     reg = registry or default_registry()
     arch = reg.resolve(raw)

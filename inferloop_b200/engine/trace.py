@@ -64,7 +64,7 @@ def main(argv: List[str] | None = None) -> int:
             entries = [StepEntry(e["id"], [int(t) for t in e["tokens"]], [int(w) for w in e.get("want", [])])
                        for e in rec.get("entries", [])]
             ended = list(rec.get("end", []))
-        except (json.JSONDecodeError, KeyError, TypeError, ValueError, AttributeError) as e:
+        except (json.JSONDecodeError, RecursionError, KeyError, TypeError, ValueError, AttributeError) as e:
             print(f"trace_run: line {line_no} is not a step ({type(e).__name__}: {e}); expected "
                   '{"step": n, "entries": [{"id": ..., "tokens": [...], "want": [...]}], "end": [...]}', file=sys.stderr)
             return 2

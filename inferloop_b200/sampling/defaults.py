@@ -36,7 +36,7 @@ def _read_json(path: str) -> Dict[str, Any]:
     with open(path, "r", encoding="utf-8") as fh:
         try:
             data = json.load(fh)
-        except json.JSONDecodeError as e:
+        except (json.JSONDecodeError, RecursionError) as e:
             raise ValueError(f"{path}: malformed JSON: {e}") from None
     if not isinstance(data, dict):
         raise ValueError(f"{path}: not a JSON object")

@@ -48,7 +48,7 @@ def _no_duplicates(pairs):
     seen = {}
     for k, v in pairs:
         if k in seen:
-            raise SafetensorsError(f"duplicate tensor name {k!r} in header")
+            raise SafetensorsError(f"duplicate name {k!r}")
         seen[k] = v
     return seen
 
@@ -165,13 +165,13 @@ class TensorSource:
                 raise SafetensorsError(f"{index_path}: larger than {MAX_INDEX_BYTES} bytes")
             try:
                 with open(index_path, "r", encoding="utf-8") as fh:
-                    index = json.load(fh)
+                    index = json.load(fh, object_pairs_hook=_no_duplicates)
                 weight_map = dict(index["weight_map"])
-            except (json.JSONDecodeError, KeyError, TypeError, ValueError) as e:
+            except (json.JSONDecodeError, RecursionError, KeyError, TypeError, ValueError) as e:
                 raise SafetensorsError(f"{index_path}: malformed index: {e}") from None
             root = os.path.realpath(folder)
             for name, shard in weight_map.items():
-                if (not isinstance(shard, str) or os.path.isabs(shard)
+                if (not isinstance(shard, str) or "\x00" in shard or os.path.isabs(shard)
                         or os.path.realpath(os.path.join(folder, shard)) != os.path.join(root, shard)
                         or os.sep in shard or shard in ("", ".", "..")):
                     raise SafetensorsError(f"{index_path}: shard path {shard!r} leaves the folder")

@@ -123,3 +123,13 @@ def test_architectures_may_be_one_name():
     from inferloop_b200.config import default_registry
     raw = dict(CONFIG_A, architectures="Qwen3ForCausalLM")
     assert default_registry().resolve(raw).name
+
+
+def test_text_that_is_no_json_is_refused_with_the_package_own_error():
+    """Truncated text, and brackets nested so deep that the parser's recursion ends."""
+    from inferloop_b200.config import Qwen3Config, read_model_config
+    for text in ('{"vocab_size": 5', "[" * 100000, '{"a":' * 50000 + "1" + "}" * 50000):
+        with pytest.raises(ConfigError, match="not valid JSON"):
+            read_model_config(text)
+        with pytest.raises(ConfigError, match="not valid JSON"):
+            Qwen3Config.from_json(text)

@@ -99,6 +99,16 @@ def test_index_and_shard_path_escape(tmp_path):
     with open(os.path.join(d, "model.safetensors.index.json"), "w") as fh:
         json.dump({"weight_map": {"a": "s1.safetensors"}}, fh)
     TensorSource(d)   # s2 is not named: fine, it is not a shard of this model
+    # what a damaged or hostile index can hold, each refused with the reader's own error
+    for text, why in (('{"weight_map": {"a": "s1.safetensors\\u0000"}}', "leaves the folder"),
+                      ('{"weight_map": {"a": "s2.safetensors", "a": "s1.safetensors"}}', "duplicate"),
+                      ("[" * 100000, "malformed index"),
+                      ('{"weight_map": [1, 2]}', "malformed index"),
+                      ('{"weight_map": {"a": 7}}', "leaves the folder")):
+        with open(os.path.join(d, "model.safetensors.index.json"), "w") as fh:
+            fh.write(text)
+        with pytest.raises(SafetensorsError, match=why):
+            TensorSource(d)
 
 
 def test_index_total_size_must_agree_with_the_shards(tmp_path):
