@@ -825,6 +825,253 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   }
 }
 
+// ------------------------------------------------------------------ many tokens: pairs of CTAs
+// A tile of 256 tokens x 256 weight rows belongs to a cluster of two CTAs on the two SMs of a
+// TPC, which the tensor cores treat as one unit (tcgen05.mma.cta_group::2, M = 256): each CTA
+// loads its own 128 token rows and its own HALF of the weight block, so a weight byte crosses
+// from L2 into one of the two SMs only, a stage is 32 KB instead of 64 (six stages), and each
+// CTA's 128 x 256 accumulator takes half of its tensor memory, so the write-out of a tile runs
+// under the MMAs of the next one.  One thread of the leader (rank 0) issues for both SMs.
+//   full[s]   (leader)  one arrival with 64 KB expected: the loads of BOTH CTAs count here
+//   empty[s]  (each)    the leader's commit, sent to both CTAs
+//   tfull[b]  (each)    the leader's commit after a tile's last MMA, sent to both CTAs
+//   tempty[b] (leader)  two arrivals, one per CTA, when its epilogue has read accumulator b
+// Items are (tile, K range): first the tiles of the whole rounds, one item each, then the tiles
+// left over, each cut into `split` equal K ranges (all ranges 0, then all ranges 1, ...).  Only
+// products that add into a 32-bit output are cut; their ranges meet in memory through the TMA
+// reduce of the write-out.
+constexpr int kPairStages = 6;
+constexpr int kPairN = 256;
+constexpr uint32_t kPairBytesA = kTileX * kBlockK * 2, kPairBytesB = (kPairN / 2) * kBlockK * 2;
+constexpr uint32_t kPairStageBytes = kPairBytesA + kPairBytesB;
+constexpr uint32_t kPairStaging = 2 * kTileX * 128;      // two blocks: one is read by TMA while the next is filled
+constexpr size_t kPairSmem = (size_t)kPairStages * kPairStageBytes + kPairStaging + 1024 + (2 * kPairStages + 8) * 8;
+
+struct PairParams {
+  const float* bias;
+  int* error_flag;
+  int M, N;
+  int tiles_m;               // 256-token tiles; tile = column tile * tiles_m + token tile
+  int k_blocks;              // K blocks of the product
+  int n_whole, rest, split;  // tiles that are one item each; tiles cut into `split` K ranges
+  int n_items;               // n_whole + rest * split
+  int epilogue, out_f32;
+};
+
+__global__ void __launch_bounds__(192, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
+                 const __grid_constant__ CUtensorMap map_out, const PairParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes + kPairStaging);
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * kPairStages;
+  const uint32_t tfull0 = empty0 + 8 * kPairStages, tempty0 = tfull0 + 16;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * kPairStages + 4);
+  volatile int* flags = reinterpret_cast<volatile int*>(bars + 2 * kPairStages + 5);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const bool leader = rank == 0;
+  const int pair = (int)(blockIdx.x >> 1), n_pairs = (int)(gridDim.x >> 1);
+
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 2); }
+    flags[0] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  cluster_sync_all();                    // both CTAs' barriers are ready before anything is sent to them
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
+
+  // item -> first token row of the pair's tile, first weight row, K range
+  auto place = [&](int item, int& x0, int& y0, int& kb0, int& cnt) {
+    int tile = item, ks = 0, s = 1;
+    if (item >= p.n_whole) {
+      const int j = item - p.n_whole;
+      tile = p.n_whole + j % p.rest; ks = j / p.rest; s = p.split;
+    }
+    x0 = (tile % p.tiles_m) * 2 * kTileX; y0 = (tile / p.tiles_m) * kPairN;
+    kb0 = (int)((long long)ks * p.k_blocks / s);
+    cnt = (int)((long long)(ks + 1) * p.k_blocks / s) - kb0;
+  };
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer (both CTAs)
+    if (lane == 0) {
+      const uint32_t lead_full0 = peer_addr(full0, 0);
+      bool ok = true;
+      uint32_t it = 0;
+      for (int item = pair; ok && item < p.n_items; item += n_pairs) {
+        int x0, y0, kb0, cnt;
+        place(item, x0, y0, kb0, cnt);
+        for (int i = 0; i < cnt; ++i, ++it) {
+          const uint32_t s = it % kPairStages;
+          if (it >= (uint32_t)kPairStages) {
+            ok = mbar_wait(empty0 + 8 * s, ((it / kPairStages) - 1) & 1);
+            if (!ok) break;
+          }
+          if (leader) mbar_expect_tx(full0 + 8 * s, 2 * kPairStageBytes);
+          const uint32_t dst = base + s * kPairStageBytes;
+          const int kcol = (kb0 + i) * kBlockK;
+          tma_load_2d_pair(dst, &map_x, lead_full0 + 8 * s, kcol, x0 + (int)rank * kTileX);
+          tma_load_2d_pair(dst + kPairBytesA, &map_y, lead_full0 + 8 * s, kcol, y0 + (int)rank * (kPairN / 2));
+        }
+      }
+      if (!ok) { flags[0] = 1; if (p.error_flag) *p.error_flag = 1; }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer (the leader's)
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = instr_desc(2 * kTileX, kPairN);
+      bool ok = true;
+      uint32_t it = 0, n = 0;
+      for (int item = pair; ok && item < p.n_items; item += n_pairs, ++n) {
+        int x0, y0, kb0, cnt;
+        place(item, x0, y0, kb0, cnt);
+        const uint32_t b = n & 1;
+        ok = mbar_wait(tempty0 + 8 * b, ((n >> 1) & 1) ^ 1);      // both epilogues have read this accumulator
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t acc = tmem_base + b * kPairN;
+        for (int i = 0; i < cnt; ++i, ++it) {
+          const uint32_t s = it % kPairStages;
+          ok = mbar_wait(full0 + 8 * s, (it / kPairStages) & 1);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t a = base + s * kPairStageBytes;
+          const uint64_t da = smem_desc(a), db = smem_desc(a + kPairBytesA);
+#pragma unroll
+          for (int k = 0; k < kBlockK / 16; ++k)
+            mma_bf16_pair(acc, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          tcgen05_commit_pair(empty0 + 8 * s, (uint16_t)3);
+        }
+        if (ok) tcgen05_commit_pair(tfull0 + 8 * b, (uint16_t)3);
+      }
+      if (!ok) {
+        flags[0] = 1; if (p.error_flag) *p.error_flag = 1;
+        tcgen05_commit_pair(tfull0, (uint16_t)3); tcgen05_commit_pair(tfull0 + 8, (uint16_t)3);   // let the epilogues leave their waits
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5 of both CTAs)
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t stg0 = base + kPairStages * kPairStageBytes;
+    const uint32_t lead_tempty0 = peer_addr(tempty0, 0);
+    const bool elected = row == 0;
+    uint32_t n = 0, flushes = 0;
+    for (int item = pair; item < p.n_items; item += n_pairs, ++n) {
+      int x0, y0, kb0, cnt;
+      place(item, x0, y0, kb0, cnt);
+      const uint32_t b = n & 1;
+      if (!mbar_wait(tfull0 + 8 * b, (n >> 1) & 1)) { flags[0] = 1; if (p.error_flag) *p.error_flag = 1; }
+      tcgen05_fence_after();
+      if (flags[0] != 0) break;
+      const int xr0 = x0 + (int)rank * kTileX;              // first output row of this CTA's half
+      const bool rows_live = xr0 < p.M;
+      const bool with_bias = p.bias != nullptr && kb0 == 0;  // of the ranges that meet in memory, the first adds it
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + b * kPairN;
+      auto flush_row = [&](const uint4 (&piece)[8], int out_col) {
+        const uint32_t stg = stg0 + (flushes++ & 1u) * (kTileX * 128u);
+        if (elected) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");     // this block's last reader is done (the other's may still run)
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stg + (uint32_t)row * 128u + (uint32_t)((j ^ (row & 7)) << 4)),
+                       "r"(piece[j].x), "r"(piece[j].y), "r"(piece[j].z), "r"(piece[j].w) : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (elected) {
+          // (a half that lies wholly beyond M still commits a group, empty, so that the count above holds)
+          if (!rows_live) {}
+          else if (p.epilogue == kAccumulate)
+            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                         ::"l"(&map_out), "r"(stg), "r"(out_col), "r"(xr0) : "memory");
+          else
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                         ::"l"(&map_out), "r"(stg), "r"(out_col), "r"(xr0) : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+      };
+      auto pack8 = [&](const float* r8) {
+        uint4 q;
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(r8[0], r8[1]), h1 = __floats2bfloat162_rn(r8[2], r8[3]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(r8[4], r8[5]), h3 = __floats2bfloat162_rn(r8[6], r8[7]);
+        q.x = *reinterpret_cast<uint32_t*>(&h0); q.y = *reinterpret_cast<uint32_t*>(&h1);
+        q.z = *reinterpret_cast<uint32_t*>(&h2); q.w = *reinterpret_cast<uint32_t*>(&h3);
+        return q;
+      };
+      uint4 piece[8];
+      if (p.epilogue == kSwiGLU) {
+        // columns come in blocks of 64 gate then 64 up: 64 outputs = one 128-byte row of bf16
+        for (int cb = 0; cb < kPairN; cb += 128) {
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            float g[32], u[32], r[32];
+            tmem_load_32(taddr + cb + 32 * half, g);
+            tmem_load_32(taddr + cb + 64 + 32 * half, u);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) r[c] = silu_mul(g[c], u[c]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) piece[4 * half + j] = pack8(r + 8 * j);
+          }
+          flush_row(piece, (y0 + cb) / 2);
+        }
+      } else if (p.out_f32) {
+        for (int c0 = 0; c0 < kPairN; c0 += 32) {
+          float v[32];
+          tmem_load_32(taddr + c0, v);
+          if (with_bias) {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) v[c] += (y0 + c0 + c < p.N) ? p.bias[y0 + c0 + c] : 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            piece[j] = make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]), __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3]));
+          flush_row(piece, y0 + c0);
+        }
+      } else {
+        for (int c0 = 0; c0 < kPairN; c0 += 64) {
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            float v[32];
+            tmem_load_32(taddr + c0 + 32 * half, v);
+            if (p.bias) {
+#pragma unroll
+              for (int c = 0; c < 32; ++c) v[c] += (y0 + c0 + 32 * half + c < p.N) ? p.bias[y0 + c0 + 32 * half + c] : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) piece[4 * half + j] = pack8(v + 8 * j);
+          }
+          flush_row(piece, y0 + c0);
+        }
+      }
+      // the accumulator is read: one arrival per CTA tells the leader's issuer
+      tcgen05_fence_before();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        if (leader) mbar_arrive(tempty0 + 8 * b); else mbar_arrive_cluster(lead_tempty0 + 8 * b);
+      }
+    }
+    if (elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // the staging block is read, the stores are done
+  }
+  __syncwarp();
+  tcgen05_fence_before();
+  cluster_sync_all();                    // nobody leaves while its peer may still signal it or use its memory
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
 // ------------------------------------------------------------------ host side
 struct MapKey {
   const void* ptr; int rows, cols, ld, box_rows;
@@ -1147,6 +1394,93 @@ int make_plan(Params& p, int M, int N, int K, int accumulate, int n_tickets, int
   return 0;
 }
 
+// ---- pairs of CTAs: how many pairs the device holds at once, the K ranges per tile, the launch
+int pair_capacity() {
+  static int cached = 0;
+  if (cached != 0) return cached < 0 ? 0 : cached;
+  if (cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPairSmem) != cudaSuccess) {
+    cudaGetLastError(); cached = -1; return 0;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * 256);
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = kPairSmem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+  cached = n > 0 ? n : -1;
+  return n > 0 ? n : 0;
+}
+
+// 0: never; 1: where the sizes favour it (the default); 2: wherever the kernel can run (tests).
+int g_pairs = 1;
+int g_pair_split_max = 8;       // tuning runs lower it
+
+struct PairPlan { int n_whole, rest, split, n_pairs; long long items; double fill; bool few; };
+
+// How the tiles of a product are dealt to the pairs.  Every tile one item, in rounds of equal
+// size; or (where the ranges may meet in memory) every tile cut into the same number of K
+// ranges; or whole rounds on every pair and the tiles left over cut so that their ranges
+// fill one more, shorter, round.  The modelled time, in tile times: rounds of whole tiles,
+// plus rounds of ranges / ranges per tile, plus what the extra write-outs cost: every range
+// adds a whole 256 x 256 tile of 32-bit values into memory, and those additions share one
+// throughput (measured: three ranges per tile of a 4,096 x 5,120 x 5,120 product cost 22 %
+// more than their MMA time says; the charge below is half of 0.13 us per extra tile over the
+// tile's own 0.4 us per K block).  No range shorter than 16 K blocks.
+// `fill`: the time of a perfect deal over the modelled one.
+bool pair_plan(int M, int N, int K, bool can_split, int capacity, PairPlan& out) {
+  if (capacity <= 0) return false;
+  const long long t = (long long)((M + 2 * kTileX - 1) / (2 * kTileX)) * ((N + kPairN - 1) / kPairN);
+  const int kb = (K + kBlockK - 1) / kBlockK;
+  const int s_max = can_split ? (kb / 16 < g_pair_split_max ? (kb / 16 < 1 ? 1 : kb / 16) : g_pair_split_max) : 1;
+  double best = 1e30;
+  auto take = [&](double time, long long n_whole, long long rest, int s, long long pairs) {
+    time += 0.5 * (double)(rest * (s - 1)) * 0.13 / (0.4 * kb);
+    if (time < best - 1e-9) {
+      best = time;
+      out.n_whole = (int)n_whole; out.rest = (int)rest; out.split = s; out.n_pairs = (int)pairs; out.items = n_whole + rest * s;
+    }
+  };
+  for (int s = 1; s <= s_max; ++s) {                       // every tile cut alike
+    const long long items = t * s, rounds = (items + capacity - 1) / capacity;
+    take((double)rounds / s, 0, t, s, (items + rounds - 1) / rounds);
+  }
+  const long long whole = t / capacity, rest = t % capacity;
+  if (whole > 0 && rest > 0) {                             // whole rounds, then one round of ranges
+    int s = (int)(capacity / rest);
+    if (s > s_max) s = s_max;
+    if (s > 1) take((double)whole + 1.0 / s, whole * capacity, rest, s, capacity);
+  }
+  // (tiles of 256 tokens hold more empty rows than blocks of 128 would when M leaves the odd block empty)
+  const double rows = (double)((M + kTileX - 1) / kTileX * kTileX) / (double)((M + 2 * kTileX - 1) / (2 * kTileX) * (2 * kTileX));
+  out.fill = ((double)t / capacity) / best * rows;
+  out.few = t < capacity;
+  return true;
+}
+
+// Pairs where the deal keeps them busy: products that add into the 32-bit output have the
+// single-CTA tiles' short last round as the alternative, so they ask for more, except where
+// the tiles are fewer than the pairs (there the single-CTA tiles have no whole round either).
+double g_pair_fill_plain = 0.75, g_pair_fill_adding = 0.85;
+bool pair_wanted(const PairPlan& pp, int epilogue) {
+  if (g_pairs == 2) return true;
+  if (epilogue == 1) return pp.fill >= g_pair_fill_adding || (pp.few && pp.split > 1);
+  return pp.fill >= g_pair_fill_plain;
+}
+
+int launch_pair(const CUtensorMap& mx, const CUtensorMap& my, const CUtensorMap& mo, const PairParams& p, int n_pairs, cudaStream_t stream) {
+  static OncePerDevice once;
+  if (once.first()) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPairSmem);
+    if (e != cudaSuccess) { once.forget(); return fail("gemm_tc: cannot reserve %zu bytes of shared memory: %s", kPairSmem, cudaGetErrorString(e)); }
+  }
+  ilb::launch_cluster(gemm_pair_kernel, dim3(2 * n_pairs), dim3(192), kPairSmem, stream, 2, mx, my, mo, p);
+  return check_launch("gemm_tc");
+}
+
 }  // namespace
 
 // max_ctas > 0 sets the grid (tests use it to force many shared tiles).
@@ -1180,6 +1514,22 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   const bool tma_reach = ((uintptr_t)out % 16 == 0) && ((long long)ldo * es) % 16 == 0;   // rows of 16-byte multiples from a 16-byte base
   if (make_plan(p, M, N, K, accumulate, n_tickets, max_ctas, tma_reach && out_f32 && accumulate == 1, plan)) return -1;
   const bool swap = plan.swap;
+  // Many tokens: a pair of CTAs per 256 x 256 tile where the result can leave by TMA.
+  if (!swap && g_pairs != 0 && max_ctas <= 0 && tma_reach && !(accumulate == 2 && out_f32)) {
+    PairPlan pp{};
+    if (pair_plan(M, N, K, out_f32 && accumulate == 1 && g_sums_in_memory, pair_capacity(), pp) && pair_wanted(pp, accumulate)) {
+      PairParams q{};
+      q.bias = bias; q.error_flag = error_flag; q.M = M; q.N = N;
+      q.tiles_m = (M + 2 * kTileX - 1) / (2 * kTileX);
+      q.k_blocks = p.k_blocks; q.n_whole = pp.n_whole; q.rest = pp.rest; q.split = pp.split; q.n_items = (int)pp.items;
+      q.epilogue = accumulate; q.out_f32 = out_f32;
+      CUtensorMap mx, my, mo;
+      if (make_map(&mx, A, M, K, lda, kTileX)) return -1;
+      if (make_map(&my, W, N, K, ldw, kPairN / 2)) return -1;
+      if (make_out_map(&mo, out, M, out_cols, ldo, out_f32 != 0)) return -1;
+      return launch_pair(mx, my, mo, q, pp.n_pairs, stream);
+    }
+  }
   const int bn = plan.bn, ms = plan.ms, x_rows = plan.x_rows, y_rows = plan.y_rows;
   const long long grid = plan.grid;
   ILB_REQUIRE(swap || p.cluster == 1 || (bn / p.cluster) % 32 == 0, "gemm_tc: %d columns do not divide among %d CTAs", bn, p.cluster);
@@ -1218,6 +1568,21 @@ ILB_EXPORT int ilb_gemm_tc(const void* A, const void* W, const float* bias, void
   return launch<128, 6, false>(mx, my, mo, p, (int)grid, stream);
 }
 
+// Products of many tokens on pairs of CTAs: 0 never, 1 where the sizes favour it, 2 wherever possible.
+ILB_EXPORT int ilb_gemm_tc_pairs(int mode) {
+  g_pairs = mode < 0 ? 0 : mode > 2 ? 2 : mode;
+  return 0;
+}
+
+// Tuning runs: the most K ranges a tile of a pair is cut into (1 to 8), and how well the deal
+// must fill the pairs (in thousandths) for plain and for adding products.
+ILB_EXPORT int ilb_gemm_tc_pair_tuning(int split_max, int fill_plain, int fill_adding) {
+  g_pair_split_max = split_max < 1 ? 1 : split_max > 8 ? 8 : split_max;
+  g_pair_fill_plain = fill_plain / 1000.0;
+  g_pair_fill_adding = fill_adding / 1000.0;
+  return 0;
+}
+
 // 1: the K ranges of a tile may meet in memory (the default); 0: every split sum is added in K order.
 ILB_EXPORT int ilb_gemm_tc_sums_in_memory(int on) {
   g_sums_in_memory = on != 0;
@@ -1226,7 +1591,9 @@ ILB_EXPORT int ilb_gemm_tc_sums_in_memory(int on) {
 
 // What a product of these sizes would get (for tests and notes): out[0..8] = swapped operands,
 // token-tile / weight-tile width, 128-row blocks per tile, grid, cluster, whole-tile rounds,
-// tiles, tiles handled stream-K fashion, whether the K ranges of a tile are added in memory.
+// tiles, tiles handled stream-K fashion, whether the K ranges of a tile are added in memory;
+// out[9..10] = pairs of CTAs and K ranges per tile when the product runs on pairs (else 0, 0;
+// an output that TMA cannot reach keeps the single-CTA tiles whatever this says).
 ILB_EXPORT int ilb_gemm_tc_plan(int M, int N, int K, int epilogue, int* out) {
   ILB_REQUIRE(M > 0 && N > 0 && K > 0 && out != nullptr && epilogue >= 0 && epilogue <= 2, "gemm_tc: bad sizes for a plan");
   Params p{};
@@ -1236,6 +1603,13 @@ ILB_EXPORT int ilb_gemm_tc_plan(int M, int N, int K, int epilogue, int* out) {
   out[0] = plan.swap ? 1 : 0; out[1] = plan.bn; out[2] = plan.ms; out[3] = (int)plan.grid; out[4] = p.cluster;
   out[5] = p.dp_waves; out[6] = p.tiles_x * p.tiles_y; out[7] = (int)(p.tiles_x * (long long)p.tiles_y - p.sk_tile0);
   out[8] = plan.additive ? 1 : 0;
+  out[9] = 0; out[10] = 0;
+  PairPlan pp{};
+  if (!plan.swap && g_pairs != 0 && pair_plan(M, N, K, epilogue == 1 && g_sums_in_memory, pair_capacity(), pp) &&
+      pair_wanted(pp, epilogue)) {
+    out[9] = pp.n_pairs; out[10] = pp.split;
+    out[8] = pp.split > 1 ? 1 : 0;
+  }
   return 0;
 }
 

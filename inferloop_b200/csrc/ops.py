@@ -348,15 +348,23 @@ def gemm_sums_in_memory(on: bool) -> None:
     load_module("gemm_tcgen05").ilb_gemm_tc_sums_in_memory(_i(1 if on else 0))
 
 
+def gemm_pairs(mode: int) -> None:
+    """Products of many tokens on pairs of CTAs that the tensor cores treat as one unit
+    (256 x 256 tiles, `tcgen05.mma.cta_group::2`): 0 never, 1 where the sizes favour it (the
+    default), 2 wherever the kernel can run (tests use it at small sizes)."""
+    load_module("gemm_tcgen05").ilb_gemm_tc_pairs(_i(int(mode)))
+
+
 def gemm_tc_plan(M: int, N: int, K: int, accumulate: bool = False, swiglu: bool = False) -> dict:
     """How `gemm_tc` deals out a product of these sizes (needs a device: the answer depends
     on how many CTAs fit it)."""
     lib = load_module("gemm_tcgen05")
-    out = (ctypes.c_int * 9)()
+    out = (ctypes.c_int * 11)()
     lib.ilb_gemm_tc_plan.restype = ctypes.c_int
     if lib.ilb_gemm_tc_plan(_i(M), _i(N), _i(K), _i(2 if swiglu else (1 if accumulate else 0)), out) != 0:
         raise KernelError(lib.ilb_last_error().decode())
-    keys = ("swap", "tile_n", "row_blocks", "grid", "cluster", "rounds", "tiles", "tiles_stream_k", "sums_meet_in_memory")
+    keys = ("swap", "tile_n", "row_blocks", "grid", "cluster", "rounds", "tiles", "tiles_stream_k", "sums_meet_in_memory",
+            "pairs", "pair_split")
     return dict(zip(keys, list(out)))
 
 

@@ -348,6 +348,47 @@ def test_gemm_tcgen05(M, N, K, out_dtype, bias, accumulate):
     close(out, ref, out_dtype, scale=float(ref.abs().max()), what=f"gemm_tc {M}x{N}x{K}")
 
 
+@pytest.mark.parametrize("epilogue", ["store_bf16", "store_f32", "accumulate", "accumulate_bias", "store_bias", "swiglu"])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (300, 520, 264), (100, 1000, 512), (512, 768, 2048), (1100, 384, 4096),
+                                   (2048, 1280, 1024), (129, 256, 8)])
+def test_gemm_tcgen05_on_pairs_of_ctas(M, N, K, epilogue):
+    """The 256 x 256 tiles of a pair of CTAs (one MMA unit over two SMs), forced at sizes
+    where the launcher would not choose them: token tiles whose second half lies partly or
+    wholly beyond M, widths and depths that fill no tile, every epilogue, and K long
+    enough that the accumulating products cut a tile into ranges that meet in memory."""
+    o = ops()
+    swiglu = epilogue == "swiglu"
+    if swiglu and N % 128:
+        N = (N + 127) // 128 * 128
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.05).to(torch.bfloat16)
+    b = torch.randn(N) if epilogue.endswith("bias") else None
+    base = torch.randn(M, N)
+    ref = a.double() @ w.double().T
+    if b is not None:
+        ref = ref + b.double()
+    if swiglu:
+        g = ref.view(M, N // 128, 2, 64)
+        ref = (torch.nn.functional.silu(g[:, :, 0]) * g[:, :, 1]).reshape(M, N // 2)
+        out = torch.full((M, N // 2), float("nan"), dtype=torch.bfloat16, device="cuda")
+    elif epilogue.startswith("accumulate"):
+        ref = ref + base.double()
+        out = base.clone().cuda()
+    else:
+        out = torch.full((M, N), float("nan"), dtype=torch.float32 if epilogue == "store_f32" else torch.bfloat16, device="cuda")
+    o.gemm_pairs(2)
+    try:
+        plan = o.gemm_tc_plan(M, N, K, accumulate=epilogue.startswith("accumulate"), swiglu=swiglu)
+        if M > 128:
+            assert plan["pairs"] >= 1 and (plan["pair_split"] == 1 or epilogue.startswith("accumulate")), plan
+        o.gemm_tc(a.cuda(), w.cuda(), out, None if b is None else b.cuda(), accumulate=epilogue.startswith("accumulate"), swiglu=swiglu)
+        o.check_device_errors()
+    finally:
+        o.gemm_pairs(1)
+    close(out, ref, "float32" if out.dtype == torch.float32 else "bfloat16", scale=float(ref.abs().max()), what=f"gemm on pairs {M}x{N}x{K} {epilogue}")
+
+
 @pytest.mark.parametrize("max_ctas", [0, 1, 3, 7, 50])
 @pytest.mark.parametrize("M,N,K", [(8, 640, 2048), (200, 700, 1024)])
 def test_gemm_tcgen05_shared_tiles_are_deterministic_and_reusable(max_ctas, M, N, K):
