@@ -34,6 +34,9 @@
 //   many tokens: whole tiles in rounds of equal size, all CTAs of a round starting at K block
 //     0 together so that they share operand blocks in L2; with few tiles, equal K ranges per
 //     tile (a cluster that shares the write-out by columns, or tickets for two-block tiles).
+//   many tokens and enough 256 x 256 tiles: `gemm_pair_kernel` further down, a cluster of two
+//     CTAs per tile that the tensor cores treat as one unit (tcgen05.mma.cta_group::2), each
+//     CTA loading its own half of the weight block.
 // There is no spin-wait on another CTA anywhere.  Decode-shaped launches keep their ring below
 // half of an SM's shared memory: two CTAs per SM.  Every mbarrier wait is bounded: on expiry the
 // kernel raises a flag in global memory, drains what it armed, frees its tensor memory and returns.

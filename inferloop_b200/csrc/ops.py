@@ -357,7 +357,10 @@ def gemm_pairs(mode: int) -> None:
 
 def gemm_tc_plan(M: int, N: int, K: int, accumulate: bool = False, swiglu: bool = False) -> dict:
     """How `gemm_tc` deals out a product of these sizes (needs a device: the answer depends
-    on how many CTAs fit it)."""
+    on how many CTAs fit it).  `pairs` > 0: the product runs on that many pairs of CTAs, each
+    tile left over after the whole rounds (or every tile) cut into `pair_split` K ranges, and
+    `sums_meet_in_memory` speaks of those; the other fields then describe the single-CTA deal
+    that `gemm_pairs(0)` would use."""
     lib = load_module("gemm_tcgen05")
     out = (ctypes.c_int * 11)()
     lib.ilb_gemm_tc_plan.restype = ctypes.c_int

@@ -471,6 +471,8 @@ def test_gemm_tcgen05_plans_cover_every_tile_once():
             assert plan["cluster"] in (1, 2, 4, 8) and plan["grid"] % plan["cluster"] == 0, what
             assert 0 <= plan["tiles_stream_k"] <= plan["tiles"], what
             assert not plan["sums_meet_in_memory"] or (kw.get("accumulate") and not plan["swap"] and plan["cluster"] == 1), what
+            assert 0 <= plan["pairs"] <= sms // 2 and (plan["pairs"] == 0 or (not plan["swap"] and 1 <= plan["pair_split"] <= 8)), what
+            assert plan["pair_split"] <= 1 or kw.get("accumulate"), what             # only adding products are cut on pairs
             if plan["swap"]:
                 assert plan["tile_n"] >= min(M, 128) and plan["grid"] <= 2 * sms, what
                 if plan["cluster"] > 1:
@@ -478,6 +480,14 @@ def test_gemm_tcgen05_plans_cover_every_tile_once():
             else:
                 assert plan["grid"] <= sms, what
                 assert plan["rounds"] * plan["grid"] >= plan["tiles"] - plan["tiles_stream_k"], what
+    # a prompt's worth of tokens runs on pairs of CTAs; a product with too few tiles for them does not
+    assert o.gemm_tc_plan(2048, 24576, 4096, swiglu=True)["pairs"] > 0 and o.gemm_tc_plan(2048, 4096, 12288, accumulate=True)["pairs"] > 0
+    assert o.gemm_tc_plan(512, 6144, 4096)["pairs"] == 0
+    o.gemm_pairs(0)
+    try:
+        assert o.gemm_tc_plan(2048, 24576, 4096, swiglu=True)["pairs"] == 0
+    finally:
+        o.gemm_pairs(1)
 
 
 def test_decode_attention_plan_keeps_the_launch_resident():
