@@ -892,7 +892,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   cluster_sync_all();                    // both CTAs' barriers are ready before anything is sent to them
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  pdl_wait();
 
   // item -> first token row of the pair's tile, first weight row, K range
   auto place = [&](int item, int& x0, int& y0, int& kb0, int& cnt) {
@@ -912,20 +911,33 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       const uint32_t lead_full0 = peer_addr(full0, 0);
       bool ok = true;
       uint32_t it = 0;
+      // The weight depends on no earlier kernel: the weight halves of the first ring are
+      // requested before this kernel waits for its predecessor, the token rows after.
+      uint32_t early = 0;
+      for (int item = pair; item < p.n_items && early < (uint32_t)kPairStages; item += n_pairs) {
+        int x0, y0, kb0, cnt;
+        place(item, x0, y0, kb0, cnt);
+        for (int i = 0; i < cnt && early < (uint32_t)kPairStages; ++i, ++early) {
+          if (leader) mbar_expect_tx(full0 + 8 * early, 2 * kPairStageBytes);
+          tma_load_2d_pair(base + early * kPairStageBytes + kPairBytesA, &map_y, lead_full0 + 8 * early, (kb0 + i) * kBlockK,
+                           y0 + (int)rank * (kPairN / 2));
+        }
+      }
+      pdl_wait();
       for (int item = pair; ok && item < p.n_items; item += n_pairs) {
         int x0, y0, kb0, cnt;
         place(item, x0, y0, kb0, cnt);
         for (int i = 0; i < cnt; ++i, ++it) {
           const uint32_t s = it % kPairStages;
-          if (it >= (uint32_t)kPairStages) {
-            ok = mbar_wait(empty0 + 8 * s, ((it / kPairStages) - 1) & 1);
-            if (!ok) break;
-          }
-          if (leader) mbar_expect_tx(full0 + 8 * s, 2 * kPairStageBytes);
           const uint32_t dst = base + s * kPairStageBytes;
           const int kcol = (kb0 + i) * kBlockK;
+          if (it >= early) {
+            ok = mbar_wait(empty0 + 8 * s, ((it / kPairStages) - 1) & 1);
+            if (!ok) break;
+            if (leader) mbar_expect_tx(full0 + 8 * s, 2 * kPairStageBytes);
+            tma_load_2d_pair(dst + kPairBytesA, &map_y, lead_full0 + 8 * s, kcol, y0 + (int)rank * (kPairN / 2));
+          }
           tma_load_2d_pair(dst, &map_x, lead_full0 + 8 * s, kcol, x0 + (int)rank * kTileX);
-          tma_load_2d_pair(dst + kPairBytesA, &map_y, lead_full0 + 8 * s, kcol, y0 + (int)rank * (kPairN / 2));
         }
       }
       if (!ok) { flags[0] = 1; if (p.error_flag) *p.error_flag = 1; }
@@ -971,6 +983,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const uint32_t lead_tempty0 = peer_addr(tempty0, 0);
     const bool elected = row == 0;
     uint32_t n = 0, flushes = 0;
+    pdl_wait();                               // the output belongs to earlier kernels until now
     for (int item = pair; item < p.n_items; item += n_pairs, ++n) {
       int x0, y0, kb0, cnt;
       place(item, x0, y0, kb0, cnt);
