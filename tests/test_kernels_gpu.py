@@ -350,12 +350,14 @@ def test_gemm_tcgen05(M, N, K, out_dtype, bias, accumulate):
 
 @pytest.mark.parametrize("epilogue", ["store_bf16", "store_f32", "accumulate", "accumulate_bias", "store_bias", "swiglu"])
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (300, 520, 264), (100, 1000, 512), (512, 768, 2048), (1100, 384, 4096),
-                                   (2048, 1280, 1024), (129, 256, 8)])
+                                   (2048, 1280, 1024), (129, 256, 8), (2048, 7168, 128)])
 def test_gemm_tcgen05_on_pairs_of_ctas(M, N, K, epilogue):
     """The 256 x 256 tiles of a pair of CTAs (one MMA unit over two SMs), forced at sizes
     where the launcher would not choose them: token tiles whose second half lies partly or
-    wholly beyond M, widths and depths that fill no tile, every epilogue, and K long
-    enough that the accumulating products cut a tile into ranges that meet in memory."""
+    wholly beyond M, widths and depths that fill no tile, every epilogue, K long enough
+    that the accumulating products cut a tile into ranges that meet in memory, and (the last
+    shape: 224 tiles) four tiles per pair, so that both accumulators and every barrier are
+    used a second time."""
     o = ops()
     swiglu = epilogue == "swiglu"
     if swiglu and N % 128:
