@@ -94,22 +94,50 @@ def _sampling(engine, d: Dict[str, Any]):
     return engine.generation_defaults.resolve(d)
 
 
-def cmd_run(args) -> int:
-    folder = args.package or args.model
-    with open(args.requests) as fh:
-        reqs = json.load(fh)
+def read_requests(path: str) -> List[Dict[str, Any]]:
+    """The requests file: one request object or a list of them, each
+    {"id", "input": {"Sequence": {"tokens": [...]}}, "workload": {"Generate": {"max_new_tokens": n}},
+    "sampling": {...}}.  Anything else is refused with a ValueError that names the request."""
+    try:
+        with open(path, encoding="utf-8") as fh:
+            reqs = json.load(fh)
+    except RecursionError:
+        raise ValueError(f"{path}: nested too deep to be a requests file") from None
     if isinstance(reqs, dict):
         reqs = [reqs]
-    engine = _engine(args, folder)
-    t0 = time.time()
-    ids = []
-    for r in reqs:
+    if not isinstance(reqs, list):
+        raise ValueError(f"{path}: expected a request object or a list of them")
+    out = []
+    for i, r in enumerate(reqs):
+        where = f"{path}: request {i}"
+        if not isinstance(r, dict) or "id" not in r or isinstance(r["id"], (dict, list)):
+            raise ValueError(f"{where}: needs an object with an \"id\"")
         try:
             tokens = r["input"]["Sequence"]["tokens"]
             max_new = r["workload"]["Generate"]["max_new_tokens"]
         except (KeyError, TypeError):
-            raise ValueError("only Sequence input with a Generate workload is served") from None
-        ids.append(engine.submit(tokens, _sampling(engine, r.get("sampling", {})), max_new, request_id=r["id"]))
+            raise ValueError(f"{where} ({r['id']!r}): only Sequence input with a Generate workload is served") from None
+        if not isinstance(tokens, list) or not tokens or any(isinstance(t, bool) or not isinstance(t, int) for t in tokens):
+            raise ValueError(f"{where} ({r['id']!r}): tokens must be a non-empty list of integers")
+        if isinstance(max_new, bool) or not isinstance(max_new, int) or max_new < 1:
+            raise ValueError(f"{where} ({r['id']!r}): max_new_tokens must be a positive integer")
+        sampling = r.get("sampling", {})
+        if sampling is None:
+            sampling = {}
+        if not isinstance(sampling, dict):
+            raise ValueError(f"{where} ({r['id']!r}): sampling must be an object")
+        out.append({"id": r["id"], "tokens": tokens, "max_new_tokens": max_new, "sampling": sampling})
+    return out
+
+
+def cmd_run(args) -> int:
+    folder = args.package or args.model
+    reqs = read_requests(args.requests)
+    engine = _engine(args, folder)
+    t0 = time.time()
+    ids = []
+    for r in reqs:
+        ids.append(engine.submit(r["tokens"], _sampling(engine, r["sampling"]), r["max_new_tokens"], request_id=r["id"]))
     while not engine.is_idle():
         engine.step()
     results = []
@@ -160,7 +188,7 @@ def main(argv: List[str] | None = None) -> int:
     try:
         return {"run": cmd_run, "generate": cmd_generate, "inspect-model": cmd_inspect,
                 "write-random-model": cmd_write_random}[args.command](args)
-    except (ValueError, RuntimeError, OSError) as e:
+    except (ValueError, RuntimeError, OSError, RecursionError) as e:
         print(f"infer: {e}", file=sys.stderr)
         return 1
 

@@ -58,3 +58,38 @@ def test_run_requests_file(tmp_path):
     for r, p in zip(res["results"], prompts):
         assert r["output"]["Tokens"] == plain.generate(model, p, 6) and r["reason"] == "Length"
     assert res["runtime"]["running"] == 0
+
+
+def test_requests_file_is_checked_before_anything_is_built(tmp_path):
+    """One request or a list; whatever is not a request is refused with a message that names
+    it, and `main` answers with status 1 and one line instead of a traceback."""
+    from inferloop_b200.cli import main, read_requests
+    p = str(tmp_path / "r.json")
+
+    def put(obj, raw=None):
+        with open(p, "w") as fh:
+            fh.write(raw if raw is not None else json.dumps(obj))
+
+    good = {"id": "a", "input": {"Sequence": {"tokens": [1, 2, 3]}}, "workload": {"Generate": {"max_new_tokens": 4}}}
+    put(good)
+    assert read_requests(p) == [{"id": "a", "tokens": [1, 2, 3], "max_new_tokens": 4, "sampling": {}}]
+    put([good, dict(good, id=2, sampling={"temperature": 0.5})])
+    assert [r["id"] for r in read_requests(p)] == ["a", 2] and read_requests(p)[1]["sampling"] == {"temperature": 0.5}
+    for bad, why in ((7, "request object or a list"), ([7], "needs an object"), ([{"input": {}}], "needs an object"),
+                     ([dict(good, input={"Text": "hi"})], "only Sequence input"),
+                     ([dict(good, workload={"Score": {}})], "only Sequence input"),
+                     ([dict(good, input={"Sequence": {"tokens": []}})], "non-empty list of integers"),
+                     ([dict(good, input={"Sequence": {"tokens": [1, "2"]}})], "non-empty list of integers"),
+                     ([dict(good, input={"Sequence": {"tokens": [True]}})], "non-empty list of integers"),
+                     ([dict(good, workload={"Generate": {"max_new_tokens": 0}})], "positive integer"),
+                     ([dict(good, workload={"Generate": {"max_new_tokens": 2.5}})], "positive integer"),
+                     ([dict(good, sampling=[1])], "sampling must be an object")):
+        put(bad)
+        with pytest.raises(ValueError, match=why):
+            read_requests(p)
+    for raw in ("{", "[" * 100000):
+        put(None, raw)
+        with pytest.raises(ValueError):
+            read_requests(p)
+        assert main(["run", "--package", str(tmp_path), "--requests", p]) == 1
+    assert main(["run", "--package", str(tmp_path), "--requests", str(tmp_path / "missing.json")]) == 1
