@@ -27,6 +27,8 @@
 //     shares in K order from its own shared memory and writes out (token tiles up to 64; the
 //     128-token tile keeps the older form in which owners read their peers' shares between
 //     two cluster barriers).  One cluster barrier, at the start.
+//     Accumulating products of up to four tokens with a large weight skip the cluster: the K
+//     ranges are separate CTAs that add their shares into the 32-bit output (red.add).
 //   few tokens, many tiles (the output matrix): a persistent grid takes equal, contiguous runs
 //     of (tile, K block) units ("stream-K"); a tile shared by two CTAs goes through a 32-bit
 //     workspace slot and a ticket: the CTA that takes the tile's last ticket adds the shares in
@@ -92,6 +94,7 @@ struct Params {
   int out_f32;               // element type of out
   int cluster;               // > 1: a tile's K ranges belong to the CTAs of one cluster, added through their shared memory
   int tma_out;               // many tokens: the result leaves through shared memory and TMA stores (adds, when accumulating)
+  int red_out;               // few tokens, accumulating: the K ranges of a tile are separate CTAs whose shares meet in memory (red.add)
 };
 
 // Work: first `dp_waves` rounds of WHOLE tiles in wave order (round w: CTA c takes tile
@@ -344,6 +347,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       const bool with_bias = p.bias != nullptr && (kb0 == 0 || !additive);   // once per output: of the ranges that meet in memory, the first adds it
       bool last = whole;
       int c_first = 0, c_last = 0;
+      if (SWAP && !whole && p.red_out) {
+        // Few tokens, accumulating into the 32-bit output: this CTA's K range is added in
+        // memory, where the other ranges of the tile meet it (a 32-bit sum of the same terms
+        // in whatever order they arrive); no cluster, nothing exchanged, nothing waited for.
+        const int n = xr;                                   // output feature of this thread's row
+        const float bv = (p.bias && kb0 == 0 && n < p.N) ? p.bias[n] : 0.f;
+        for (int c0 = 0; c0 < BN; c0 += CH) {
+          float v[32];
+          if (CH == 32) tmem_load_32(taddr + c0, v); else tmem_load_16(taddr + c0, v);
+#pragma unroll
+          for (int c = 0; c < CH; ++c) {
+            const int m = y0 + c0 + c;
+            if (m < p.M && n < p.N) atomicAdd((float*)p.out + (size_t)m * p.ldo + n, v[c] + bv);
+          }
+        }
+        break;
+      }
       if (kPush && !whole && p.cluster > 1) {
         // The S CTAs of a cluster hold the S consecutive K ranges of one tile.  CTA r owns 1/S
         // of the tile's rows (of its gate rows and their up rows): every CTA sends the rows of
@@ -1249,6 +1269,12 @@ struct Plan { bool swap, tail, additive; int bn, ms, x_rows, y_rows; long long g
 // Whether the K ranges of a tile may meet in memory (the sum's order is then not fixed: runs
 // agree beyond rounding, not bit for bit).  `ilb_gemm_tc_sums_in_memory(0)` turns it off.
 bool g_sums_in_memory = true;
+// Accumulating products of up to this many tokens, with a weight of at least 2,048 x 2,048, add
+// the K ranges of a tile in memory (separate CTAs, red.add) instead of inside a cluster.  In a
+// decode step of Qwen3-8B sizes: batch 1 3.41 -> 3.31 ms, batch 2 3.44 -> 3.36, batch 4 3.51 ->
+// 3.47; batch 8 3.62 -> 3.70 and batch 16 3.92 -> 4.26, where the cluster stays.
+int g_red_few_tokens = 4;
+int g_red_few_split = 8;
 
 // Equal K ranges per tile when `rest` tiles share the SMs: as many as fit, none shorter than
 // four K blocks.
@@ -1365,6 +1391,14 @@ int make_plan(Params& p, int M, int N, int K, int accumulate, int n_tickets, int
     while (split > 1 && active_clusters_for(bn, (int)(two_per_sm ? split / 2 : split)) < tiles) split /= 2;
     grid = tiles * split;
     p.cluster = (int)split;
+    if (can_add && g_sums_in_memory && accumulate == 1 && M <= g_red_few_tokens && split > 1 && N >= 2048 && K >= 2048) {
+      // the ranges as separate CTAs that add into the output (as many as the cluster would have held, or more)
+      long long s = split;
+      while (s < g_red_few_split && tiles * s * 2 <= cap && s * 2 <= p.k_blocks) s *= 2;
+      grid = tiles * s;
+      p.cluster = 1;
+      p.red_out = 1;
+    }
   }
   if (!swap && max_ctas <= 0) {
     // Many tokens.  Tiles that share an operand block must want it at the same time, or every
@@ -1590,6 +1624,14 @@ ILB_EXPORT int ilb_gemm_tc_pairs(int mode) {
   return 0;
 }
 
+// Tuning runs: few-token accumulating products of up to `max_tokens` tokens add their K ranges in
+// memory instead of inside a cluster, cut into up to `max_split` ranges.
+ILB_EXPORT int ilb_gemm_tc_red_few(int max_tokens, int max_split) {
+  g_red_few_tokens = max_tokens;
+  g_red_few_split = max_split < 1 ? 1 : max_split > 16 ? 16 : max_split;
+  return 0;
+}
+
 // Tuning runs: the most K ranges a tile of a pair is cut into (1 to 8), and how well the deal
 // must fill the pairs (in thousandths) for plain and for adding products.
 ILB_EXPORT int ilb_gemm_tc_pair_tuning(int split_max, int fill_plain, int fill_adding) {
@@ -1618,7 +1660,7 @@ ILB_EXPORT int ilb_gemm_tc_plan(int M, int N, int K, int epilogue, int* out) {
   if (make_plan(p, M, N, K, epilogue, 1 << 30, 0, epilogue == 1, plan)) return -1;
   out[0] = plan.swap ? 1 : 0; out[1] = plan.bn; out[2] = plan.ms; out[3] = (int)plan.grid; out[4] = p.cluster;
   out[5] = p.dp_waves; out[6] = p.tiles_x * p.tiles_y; out[7] = (int)(p.tiles_x * (long long)p.tiles_y - p.sk_tile0);
-  out[8] = plan.additive ? 1 : 0;
+  out[8] = (plan.additive || p.red_out) ? 1 : 0;
   out[9] = 0; out[10] = 0;
   PairPlan pp{};
   if (!plan.swap && g_pairs != 0 && pair_plan(M, N, K, epilogue == 1 && g_sums_in_memory, pair_capacity(), pp) &&
