@@ -27,8 +27,8 @@
 //     shares in K order from its own shared memory and writes out (token tiles up to 64; the
 //     128-token tile keeps the older form in which owners read their peers' shares between
 //     two cluster barriers).  One cluster barrier, at the start.
-//     Accumulating products of up to four tokens with a large weight skip the cluster: the K
-//     ranges are separate CTAs that add their shares into the 32-bit output (red.add).
+//     Accumulating products of up to eight tokens with a large weight skip the cluster: the K
+//     ranges are separate CTAs that add their shares into the 32-bit output (red.add.v4).
 //   few tokens, many tiles (the output matrix): a persistent grid takes equal, contiguous runs
 //     of (tile, K block) units ("stream-K"); a tile shared by two CTAs goes through a 32-bit
 //     workspace slot and a ticket: the CTA that takes the tile's last ticket adds the shares in
@@ -351,15 +351,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         // Few tokens, accumulating into the 32-bit output: this CTA's K range is added in
         // memory, where the other ranges of the tile meet it (a 32-bit sum of the same terms
         // in whatever order they arrive); no cluster, nothing exchanged, nothing waited for.
-        const int n = xr;                                   // output feature of this thread's row
-        const float bv = (p.bias && kb0 == 0 && n < p.N) ? p.bias[n] : 0.f;
+        // The share goes through shared memory ([token][row]; the stage ring is idle, every load
+        // into it has been consumed) so that a thread adds four neighbouring features at once.
+        float* red = reinterpret_cast<float*>(smem);
+        const float bv = (p.bias && kb0 == 0 && xr < p.N) ? p.bias[xr] : 0.f;
         for (int c0 = 0; c0 < BN; c0 += CH) {
           float v[32];
           if (CH == 32) tmem_load_32(taddr + c0, v); else tmem_load_16(taddr + c0, v);
 #pragma unroll
-          for (int c = 0; c < CH; ++c) {
-            const int m = y0 + c0 + c;
-            if (m < p.M && n < p.N) atomicAdd((float*)p.out + (size_t)m * p.ldo + n, v[c] + bv);
+          for (int c = 0; c < CH; ++c) red[(c0 + c) * kTileX + row] = v[c] + bv;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const bool vec = (p.ldo % 4 == 0) && ((uintptr_t)p.out % 16 == 0) && (x0 + kTileX <= p.N);
+        for (int q = (int)threadIdx.x - 64; q < BN * (kTileX / 4); q += 128) {
+          const int c = q / (kTileX / 4), r4 = (q % (kTileX / 4)) * 4;
+          const int m = y0 + c;
+          if (m >= p.M) break;
+          const float4 val = *reinterpret_cast<const float4*>(red + c * kTileX + r4);
+          float* dst = (float*)p.out + (size_t)m * p.ldo + x0 + r4;
+          if (vec) {
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(val.x), "f"(val.y), "f"(val.z), "f"(val.w) : "memory");
+          } else {
+            const float e[4] = {val.x, val.y, val.z, val.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (x0 + r4 + j < p.N) atomicAdd(dst + j, e[j]);
           }
         }
         break;
@@ -1271,9 +1287,11 @@ struct Plan { bool swap, tail, additive; int bn, ms, x_rows, y_rows; long long g
 bool g_sums_in_memory = true;
 // Accumulating products of up to this many tokens, with a weight of at least 2,048 x 2,048, add
 // the K ranges of a tile in memory (separate CTAs, red.add) instead of inside a cluster.  In a
-// decode step of Qwen3-8B sizes: batch 1 3.41 -> 3.31 ms, batch 2 3.44 -> 3.36, batch 4 3.51 ->
-// 3.47; batch 8 3.62 -> 3.70 and batch 16 3.92 -> 4.26, where the cluster stays.
-int g_red_few_tokens = 4;
+// decode step of Qwen3-8B sizes, one 32-bit value per add: batch 1 3.41 -> 3.31 ms, batch 2
+// 3.44 -> 3.36, batch 4 3.51 -> 3.47, but batch 8 3.62 -> 3.70 and batch 16 3.92 -> 4.26 (the
+// adds are paid per lane); four neighbouring features per add (the share transposed through
+// shared memory): batch 1 3.29, batch 4 3.43, batch 8 3.52 ms.
+int g_red_few_tokens = 8;
 int g_red_few_split = 8;
 
 // Equal K ranges per tile when `rest` tiles share the SMs: as many as fit, none shorter than

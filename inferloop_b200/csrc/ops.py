@@ -343,7 +343,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
 def gemm_sums_in_memory(on: bool) -> None:
     """Whether products that accumulate into a 32-bit output may let the K ranges of a tile meet
     in memory: the tiles of the last round of many tokens (on single CTAs or on pairs), and every
-    tile of up to four tokens when the weight is large (faster; the order of that 32-bit sum
+    tile of up to eight tokens when the weight is large (faster; the order of that 32-bit sum
     is not fixed, so two runs agree beyond rounding but not bit for bit).  On by default;
     off gives sums whose bits do not change from run to run."""
     load_module("gemm_tcgen05").ilb_gemm_tc_sums_in_memory(_i(1 if on else 0))

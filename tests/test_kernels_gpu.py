@@ -448,7 +448,7 @@ def test_gemm_tcgen05_last_round_in_memory_can_be_switched_off():
     o.check_device_errors()
 
 
-@pytest.mark.parametrize("M", [1, 2, 4])
+@pytest.mark.parametrize("M", [1, 2, 4, 7, 8])
 @pytest.mark.parametrize("N,K,bias", [(4096, 4096, False), (2048, 6144, True), (2560, 2048, False)])
 def test_gemm_tcgen05_few_tokens_add_their_ranges_in_memory(M, N, K, bias):
     """Accumulating products of up to four tokens with a large weight: the K ranges of a tile
@@ -463,7 +463,7 @@ def test_gemm_tcgen05_few_tokens_add_their_ranges_in_memory(M, N, K, bias):
     ref = base.double() + a.double() @ w.double().T + (b.double() if bias else 0)
     plan = o.gemm_tc_plan(M, N, K, accumulate=True)
     assert plan["swap"] == 1 and plan["sums_meet_in_memory"] == 1 and plan["cluster"] == 1 and plan["grid"] > plan["tiles"], plan
-    assert o.gemm_tc_plan(8, N, K, accumulate=True)["sums_meet_in_memory"] == 0          # eight tokens keep the cluster
+    assert o.gemm_tc_plan(16, N, K, accumulate=True)["sums_meet_in_memory"] == 0         # sixteen tokens keep the cluster
     assert o.gemm_tc_plan(M, 512, 512, accumulate=True)["sums_meet_in_memory"] == 0      # and so do small weights
     for _ in range(3):
         out = base.clone().cuda()
@@ -505,10 +505,10 @@ def test_gemm_tcgen05_plans_cover_every_tile_once():
                          (4096, 12288, {"accumulate": True}), (151936, 4096, {})):
             plan = o.gemm_tc_plan(M, N, K, **kw)
             what = f"M={M} N={N} K={K}: {plan}"
-            assert plan["swap"] == (1 if M <= 128 and (not plan["sums_meet_in_memory"] or M <= 4) else 0), what
+            assert plan["swap"] == (1 if M <= 128 and (not plan["sums_meet_in_memory"] or M <= 8) else 0), what
             assert plan["cluster"] in (1, 2, 4, 8) and plan["grid"] % plan["cluster"] == 0, what
             assert 0 <= plan["tiles_stream_k"] <= plan["tiles"], what
-            assert not plan["sums_meet_in_memory"] or (kw.get("accumulate") and (not plan["swap"] or M <= 4) and plan["cluster"] == 1), what
+            assert not plan["sums_meet_in_memory"] or (kw.get("accumulate") and (not plan["swap"] or M <= 8) and plan["cluster"] == 1), what
             assert 0 <= plan["pairs"] <= sms // 2 and (plan["pairs"] == 0 or (not plan["swap"] and 1 <= plan["pair_split"] <= 8)), what
             assert plan["pair_split"] <= 1 or kw.get("accumulate"), what             # only adding products are cut on pairs
             if plan["swap"]:
