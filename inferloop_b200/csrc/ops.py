@@ -356,6 +356,22 @@ def gemm_pairs(mode: int) -> None:
     load_module("gemm_tcgen05").ilb_gemm_tc_pairs(_i(int(mode)))
 
 
+def gemm_tuning(few_tokens_in_memory: Optional[int] = None, few_tokens_ranges: int = 8,
+                pair_ranges: Optional[int] = None, pair_fill_plain: float = 0.75, pair_fill_adding: float = 0.85) -> None:
+    """Knobs behind the measured defaults, for A/B runs (the defaults are what the profiles
+    report).  `few_tokens_in_memory`: accumulating products of up to this many tokens (and a
+    weight of at least 2,048 x 2,048) add the K ranges of a tile in memory instead of inside a
+    cluster, cut into up to `few_tokens_ranges` ranges (default 8 tokens; 0: never).
+    `pair_ranges`: the most K ranges a tile of a pair of CTAs is cut into (default 8), with
+    the shares of busy pairs that plain and adding products ask for before they take pairs."""
+    lib = load_module("gemm_tcgen05")
+    if few_tokens_in_memory is not None:
+        lib.ilb_gemm_tc_red_few(_i(int(few_tokens_in_memory)), _i(int(few_tokens_ranges)))
+    if pair_ranges is not None:
+        lib.ilb_gemm_tc_pair_tuning(_i(int(pair_ranges)), _i(int(round(pair_fill_plain * 1000))),
+                                    _i(int(round(pair_fill_adding * 1000))))
+
+
 def gemm_tc_plan(M: int, N: int, K: int, accumulate: bool = False, swiglu: bool = False) -> dict:
     """How `gemm_tc` deals out a product of these sizes (needs a device: the answer depends
     on how many CTAs fit it).  `pairs` > 0: the product runs on that many pairs of CTAs, each

@@ -484,6 +484,24 @@ def test_gemm_tcgen05_few_tokens_add_their_ranges_in_memory(M, N, K, bias):
     o.check_device_errors()
 
 
+def test_gemm_tuning_knobs_move_the_plan():
+    """The knobs behind the measured defaults: how many tokens send their K ranges to memory,
+    and how many ranges a tile of a pair may be cut into."""
+    o = ops()
+    try:
+        assert o.gemm_tc_plan(2, 4096, 4096, accumulate=True)["sums_meet_in_memory"] == 1
+        o.gemm_tuning(few_tokens_in_memory=0)
+        few = o.gemm_tc_plan(2, 4096, 4096, accumulate=True)
+        assert few["sums_meet_in_memory"] == 0 and few["cluster"] > 1
+        o.gemm_tuning(few_tokens_in_memory=8)
+        assert o.gemm_tc_plan(2, 4096, 4096, accumulate=True)["sums_meet_in_memory"] == 1
+        assert o.gemm_tc_plan(2048, 5120, 5120, accumulate=True)["pair_split"] > 1
+        o.gemm_tuning(pair_ranges=1)
+        assert o.gemm_tc_plan(2048, 5120, 5120, accumulate=True)["pair_split"] <= 1
+    finally:
+        o.gemm_tuning(few_tokens_in_memory=8, pair_ranges=8)
+
+
 def test_gemm_tcgen05_refuses_unaligned_rows():
     o = ops()
     a = torch.randn(4, 100).to(torch.bfloat16).cuda()       # 200-byte rows: not a multiple of 16
